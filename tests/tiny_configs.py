@@ -1,0 +1,44 @@
+"""The two tiny Qwen3 configurations that the tests run on, and a few variants.
+
+They differ in every size and option: layers, width, head counts and groups,
+head_dim (B: q width != hidden), intermediate size, vocabulary (B: odd), rope
+base, norm eps, tied or untied head, maximum position and cache page size.
+"""
+
+from __future__ import annotations
+
+TINY_A = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "head_dim": 16, "intermediate_size": 192, "vocab_size": 256, "rope_theta": 10000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "max_position_embeddings": 256,
+}
+TINY_A_INIT = {"seed": 0, "std": 0.02, "norm_std": 0.1}
+TINY_A_PAGE = 16
+
+TINY_B = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "num_hidden_layers": 3, "hidden_size": 96, "num_attention_heads": 6, "num_key_value_heads": 1,
+    "head_dim": 32, "intermediate_size": 160, "vocab_size": 317,
+    "rope_parameters": {"rope_theta": 1000000.0, "rope_type": "default"},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 512,
+}
+TINY_B_INIT = {"seed": 1, "std": 0.05, "norm_std": 0.1}
+TINY_B_PAGE = 8
+
+# A third shape for the window: layer 0 sees everything, layers 1.. only the last 24 positions.
+TINY_W = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "num_hidden_layers": 3, "hidden_size": 80, "num_attention_heads": 5, "num_key_value_heads": 5,
+    "head_dim": 48, "intermediate_size": 112, "vocab_size": 199, "rope_theta": 50000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 384,
+    "use_sliding_window": True, "sliding_window": 24, "max_window_layers": 1,
+}
+TINY_W_INIT = {"seed": 2, "std": 0.04, "norm_std": 0.1}
+TINY_W_PAGE = 16
+
+ALL = {
+    "A": (TINY_A, TINY_A_INIT, TINY_A_PAGE),
+    "B": (TINY_B, TINY_B_INIT, TINY_B_PAGE),
+    "W": (TINY_W, TINY_W_INIT, TINY_W_PAGE),
+}

@@ -1,0 +1,101 @@
+// Shared device helpers of the sm_100a kernels: element conversion, warp and
+// block reductions, and the error word that kernels set instead of trapping.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tk {
+
+// Element types of activations, weights and cache pages, as passed over the C ABI.
+enum DType : int { kF32 = 0, kBF16 = 1 };
+
+// Error codes written to the 4-int error word (code, detail0, detail1, detail2).
+enum ErrCode : int {
+  kErrNone = 0,
+  kErrTokenId = 1,    // token id outside [0, vocab)
+  kErrPage = 2,       // page id outside the pool, or page index outside the table row
+  kErrPosition = 3,   // negative position
+  kErrRequest = 4,    // request row outside the batch
+  kErrWait = 5,       // a bounded wait on a barrier ran out
+};
+
+__device__ __forceinline__ void set_error(int* err, int code, int d0, int d1, int d2) {
+  if (err == nullptr) return;
+  if (atomicCAS(err, 0, code) == 0) {
+    err[1] = d0;
+    err[2] = d1;
+    err[3] = d2;
+  }
+}
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a thread block; `scratch` holds at least 32 floats of shared memory.
+// Every thread receives the result.  Safe to call repeatedly with the same scratch.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = (lane < nwarps) ? scratch[lane] : 0.0f;
+  r = warp_sum(r);
+  return r;
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = (lane < nwarps) ? scratch[lane] : -INFINITY;
+  r = warp_max(r);
+  return r;
+}
+
+}  // namespace tk
+
+// Dispatch a templated launch on the element type code.
+#define TK_DISPATCH_DTYPE(code, T, ...)                 \
+  do {                                                  \
+    if ((code) == tk::kF32) {                           \
+      using T = float;                                  \
+      __VA_ARGS__;                                      \
+    } else if ((code) == tk::kBF16) {                   \
+      using T = __nv_bfloat16;                          \
+      __VA_ARGS__;                                      \
+    } else {                                            \
+      return (int)cudaErrorInvalidValue;                \
+    }                                                   \
+  } while (0)
+
+#define TK_API extern "C" __attribute__((visibility("default")))

@@ -1,0 +1,48 @@
+"""Loads the CUDA library and declares its C interface for ``ctypes``.
+
+The engine has no path without this library: :func:`library` raises if it can
+neither be found nor built.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_uint, c_ulonglong, c_void_p
+from functools import lru_cache
+
+from .build import BuildError, ensure_built
+
+_P = c_void_p
+
+# name -> argument types (every function returns a cudaError_t as int unless noted)
+_SIGNATURES: dict[str, list] = {
+    "tk_embed_gather": [_P, c_int, _P, _P, c_int, c_int, c_int, _P, _P],
+    "tk_add_rmsnorm": [_P, _P, _P, _P, _P, c_int, c_int, c_float, c_int, _P],
+    "tk_swiglu": [_P, _P, c_int, c_int, c_int, _P],
+    "tk_rope_kv": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
+                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                   c_float, c_int, _P],
+    "tk_attention_plain": [_P, _P, _P, _P, _P, _P, _P, _P, _P,
+                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                           c_float, c_int, _P],
+    "tk_gemm_f32": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "tk_sample": [_P, c_longlong, _P, _P, _P, _P, _P, _P, c_int, c_int, _P],
+}
+
+
+@lru_cache(maxsize=1)
+def library() -> ctypes.CDLL:
+    """The loaded library, compiled on first use if it is stale or absent."""
+    try:
+        path = ensure_built()
+    except BuildError as exc:
+        raise RuntimeError(
+            f"tokamak_b200 needs its CUDA extension and could not build it: {exc}") from exc
+    lib = ctypes.CDLL(str(path))
+    for name, argtypes in _SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.argtypes = argtypes
+        fn.restype = c_int
+    lib.tk_philox_u32.argtypes = [c_ulonglong, c_uint, ctypes.POINTER(c_uint)]
+    lib.tk_philox_u32.restype = None
+    return lib

@@ -1,0 +1,199 @@
+"""Python entry points of the CUDA kernels: argument checks, then one C call each.
+
+Every function takes CUDA tensors and launches on PyTorch's current stream, so
+the calls can be recorded into a CUDA graph like any other stream work.  There
+is no CPU path: a tensor that is not on a CUDA device is an error.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .lib import library
+
+DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class KernelError(RuntimeError):
+    """A kernel launch failed or refused its arguments."""
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: CUDA error {code}")
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _want(t: torch.Tensor, dtype: torch.dtype | None, name: str) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (the engine has no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"unsupported element type {dtype}; the kernels take float32 and bfloat16")
+
+
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, resid: torch.Tensor, err: torch.Tensor) -> None:
+    """resid[t] = float32(table[ids[t]])."""
+    _want(table, None, "table"); _want(ids, torch.int32, "ids"); _want(resid, torch.float32, "resid")
+    n = ids.numel()
+    vocab, hidden = table.shape
+    if resid.shape[-1] != hidden or resid.numel() < n * hidden:
+        raise KernelError("resid is too small for the tokens")
+    _check(library().tk_embed_gather(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(),
+                                     resid.data_ptr(), n, hidden, vocab, err.data_ptr(), _stream()),
+           "embed_gather")
+
+
+def add_rmsnorm(resid: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor,
+                out: torch.Tensor, eps: float, rows: torch.Tensor | None = None) -> None:
+    """x = resid (+ delta), written back unless ``rows`` is given; out = weight * x * rsqrt(mean x^2 + eps)."""
+    _want(resid, torch.float32, "resid"); _want(weight, torch.float32, "weight"); _want(out, None, "out")
+    hidden = resid.shape[-1]
+    if weight.numel() != hidden or out.shape[-1] != hidden:
+        raise KernelError("norm width mismatch")
+    if delta is not None:
+        _want(delta, out.dtype, "delta")
+        if delta.shape != resid.shape:
+            raise KernelError("delta and resid differ in shape")
+    if rows is not None:
+        _want(rows, torch.int32, "rows")
+        n_rows = rows.numel()
+    else:
+        n_rows = resid.numel() // hidden
+    if out.numel() < n_rows * hidden:
+        raise KernelError("out is too small")
+    _check(library().tk_add_rmsnorm(resid.data_ptr(), _ptr(delta), weight.data_ptr(), out.data_ptr(),
+                                    _ptr(rows), n_rows, hidden, float(eps), dtype_code(out.dtype),
+                                    _stream()), "add_rmsnorm")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, j] = silu(gate_up[t, j]) * gate_up[t, I + j]."""
+    _want(gate_up, None, "gate_up"); _want(out, gate_up.dtype, "out")
+    n, two_i = gate_up.shape
+    if two_i % 2 or out.shape != (n, two_i // 2):
+        raise KernelError("swiglu shape mismatch")
+    _check(library().tk_swiglu(gate_up.data_ptr(), out.data_ptr(), n, two_i // 2,
+                               dtype_code(out.dtype), _stream()), "swiglu")
+
+
+def rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | None,
+            v_cache: torch.Tensor | None, positions: torch.Tensor, tok_req: torch.Tensor,
+            req_slot: torch.Tensor, block_table: torch.Tensor, q_norm_w: torch.Tensor | None,
+            k_norm_w: torch.Tensor | None, inv_freq: torch.Tensor | None, err: torch.Tensor, *,
+            n_q_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int, eps: float,
+            write_kv: bool = True) -> None:
+    """Per-head norm of q and k, rotation, and the write of k and v into their pages."""
+    _want(qkv, None, "qkv"); _want(q_out, qkv.dtype, "q_out")
+    n = qkv.shape[0]
+    row = qkv.shape[1]
+    need = (n_q_heads + (2 * n_kv_heads if write_kv else 0)) * head_dim
+    if row < need:
+        raise KernelError(f"qkv rows hold {row} values, {need} needed")
+    for name, t in (("positions", positions), ("tok_req", tok_req), ("req_slot", req_slot),
+                    ("block_table", block_table)):
+        _want(t, torch.int32, name)
+    for name, t in (("q_norm_w", q_norm_w), ("k_norm_w", k_norm_w), ("inv_freq", inv_freq)):
+        if t is not None:
+            _want(t, torch.float32, name)
+    if q_norm_w is not None and q_norm_w.numel() != head_dim:
+        raise KernelError("q_norm weight does not match head_dim")
+    if k_norm_w is not None and k_norm_w.numel() != head_dim:
+        raise KernelError("k_norm weight does not match head_dim")
+    if inv_freq is not None and inv_freq.numel() * 2 != rotary_dim:
+        raise KernelError("inv_freq does not match rotary_dim")
+    if write_kv:
+        _want(k_cache, qkv.dtype, "k_cache"); _want(v_cache, qkv.dtype, "v_cache")
+        num_pages, hkv, page_size, d = k_cache.shape
+        if hkv != n_kv_heads or d != head_dim or v_cache.shape != k_cache.shape:
+            raise KernelError("cache pages do not match the heads")
+    else:
+        num_pages, page_size = 0, 1
+    _check(library().tk_rope_kv(qkv.data_ptr(), q_out.data_ptr(), _ptr(k_cache), _ptr(v_cache),
+                                positions.data_ptr(), tok_req.data_ptr(), req_slot.data_ptr(),
+                                block_table.data_ptr(), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq),
+                                err.data_ptr(), n, req_slot.numel(), n_q_heads, n_kv_heads, head_dim,
+                                rotary_dim, row, page_size, block_table.shape[1], num_pages,
+                                1 if write_kv else 0, float(eps), dtype_code(qkv.dtype), _stream()),
+           "rope_kv")
+
+
+def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                    positions: torch.Tensor, tok_req: torch.Tensor, req_slot: torch.Tensor,
+                    block_table: torch.Tensor, err: torch.Tensor, *, scale: float,
+                    window: int | None = None) -> None:
+    """Paged attention of a mixed batch; q and out are [N, Hq, d]."""
+    _want(q, None, "q"); _want(out, q.dtype, "out")
+    _want(k_cache, q.dtype, "k_cache"); _want(v_cache, q.dtype, "v_cache")
+    n, hq, d = q.shape
+    num_pages, hkv, page_size, dk = k_cache.shape
+    if dk != d or v_cache.shape != k_cache.shape or out.shape != q.shape:
+        raise KernelError("attention shape mismatch")
+    if hq % hkv:
+        raise KernelError(f"{hq} query heads are not a multiple of {hkv} key/value heads")
+    if d > 256:
+        raise KernelError(f"head_dim {d} is beyond the kernels' limit of 256")
+    _check(library().tk_attention_plain(q.data_ptr(), out.data_ptr(), k_cache.data_ptr(),
+                                        v_cache.data_ptr(), positions.data_ptr(), tok_req.data_ptr(),
+                                        req_slot.data_ptr(), block_table.data_ptr(), err.data_ptr(),
+                                        n, req_slot.numel(), hq, hkv, d, page_size,
+                                        block_table.shape[1], num_pages, int(window or 0),
+                                        float(scale), dtype_code(q.dtype), _stream()),
+           "attention_plain")
+
+
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[M, N] = a[M, K] @ w[N, K]^T in true float32 (FFMA, ascending k)."""
+    _want(a, torch.float32, "a"); _want(w, torch.float32, "w")
+    m, k = a.shape
+    n, kw = w.shape
+    if k != kw:
+        raise KernelError(f"inner sizes differ: {k} and {kw}")
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.float32, device=a.device)
+    else:
+        _want(out, torch.float32, "out")
+        if out.shape != (m, n):
+            raise KernelError("out has the wrong shape")
+    _check(library().tk_gemm_f32(a.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, k, k, n,
+                                 _stream()), "gemm_f32")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           seed: torch.Tensor, counter: torch.Tensor, out_tokens: torch.Tensor) -> None:
+    """One token per row of float32 logits; see sampling.cu for the exact rule."""
+    _want(logits, torch.float32, "logits"); _want(temperature, torch.float32, "temperature")
+    _want(top_k, torch.int32, "top_k"); _want(top_p, torch.float32, "top_p")
+    _want(seed, torch.int64, "seed"); _want(counter, torch.int32, "counter")
+    _want(out_tokens, torch.int32, "out_tokens")
+    rows, vocab = logits.shape
+    for t in (temperature, top_k, top_p, seed, counter, out_tokens):
+        if t.numel() < rows:
+            raise KernelError("a per-row sampling tensor is shorter than the batch")
+    _check(library().tk_sample(logits.data_ptr(), logits.stride(0), temperature.data_ptr(),
+                               top_k.data_ptr(), top_p.data_ptr(), seed.data_ptr(), counter.data_ptr(),
+                               out_tokens.data_ptr(), rows, vocab, _stream()), "sample")
+
+
+def philox_u32(seed: int, counter: int) -> int:
+    """First word of the generator's block for (seed, counter), computed on the host."""
+    import ctypes
+    out = (ctypes.c_uint * 4)()
+    library().tk_philox_u32(seed & 0xFFFFFFFFFFFFFFFF, counter & 0xFFFFFFFF, out)
+    return int(out[0])

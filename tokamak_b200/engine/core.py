@@ -1,0 +1,104 @@
+"""Loads a model folder and assembles model, cache and step function on one GPU."""
+
+from __future__ import annotations
+
+import logging
+from pathlib import Path
+
+import torch
+
+from ..cache.device import DeviceCache, plan_groups
+from ..cache.manager import CacheManager
+from ..config import architecture_of, read_config_json, read_eos_token_ids
+from ..models.decoder import DecoderModel
+from ..parts.base import Runtime
+from ..weights.loader import load_tensors
+from .step import StepFunction
+
+logger = logging.getLogger(__name__)
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
+           "fp32": torch.float32, "auto": torch.bfloat16}
+
+
+def resolve_dtype(dtype: str | torch.dtype) -> torch.dtype:
+    """``auto`` is bfloat16, the serving dtype (src/tokamak/config.py:167-180); float32
+    selects the true 32-bit path."""
+    if isinstance(dtype, torch.dtype):
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"Unknown dtype spec: {dtype!r}")
+        return dtype
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise ValueError(f"Unknown dtype spec: {dtype!r}") from None
+
+
+def require_cuda(device: str | torch.device = "cuda") -> torch.device:
+    """The engine runs on a CUDA device only; there is no CPU path to fall back to."""
+    dev = torch.device("cuda" if device == "auto" else device)
+    if dev.type != "cuda":
+        raise RuntimeError(f"tokamak_b200 runs on CUDA devices only, got {dev}")
+    if not torch.cuda.is_available():
+        raise RuntimeError("tokamak_b200 needs a CUDA device and none is available")
+    if dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    return dev
+
+
+class EngineCore:
+    """Configuration, model, cache and step function of one model folder.
+
+    Args:
+        model: folder with ``config.json`` and ``*.safetensors``.
+        dtype: ``bfloat16`` (serving kernels) or ``float32`` (everything in true 32-bit).
+        max_seq_len: cap on one request's length; defaults to the model's maximum.
+        page_size: positions per cache page (``block_size`` of the reference).
+        pool_tokens: positions the page pool of every layer group holds; at least
+            ``max_seq_len`` so that any single request can finish alone
+            (src/tokamak/engine/llm.py:157-163).
+        max_slots: most requests that are live at a time.
+        max_step_tokens: most tokens of one step.
+    """
+
+    def __init__(self, model: str | Path, *, dtype: str | torch.dtype = "bfloat16",
+                 device: str | torch.device = "cuda", max_seq_len: int | None = None,
+                 page_size: int = 16, pool_tokens: int | None = None, max_slots: int = 16,
+                 max_step_tokens: int | None = None, tensors: dict | None = None,
+                 raw_config: dict | None = None):
+        self.device = require_cuda(device)
+        self.dtype = resolve_dtype(dtype)
+        torch.cuda.set_device(self.device)
+        if raw_config is None:
+            raw_config = read_config_json(model)
+            eos = read_eos_token_ids(model, raw_config)
+        else:
+            eos = None
+        self.raw_config = raw_config
+        self.architecture = architecture_of(raw_config)
+        self.config = self.architecture.parse_config(raw_config, eos)
+        self.spec = self.architecture.model_spec(self.config)
+        rt = Runtime(device=self.device, dtype=self.dtype)
+        if tensors is None:
+            expected = DecoderModel.expected_tensors(self.spec)
+            tensors = load_tensors(model, expected, self.dtype, self.device)
+        self.model = DecoderModel(self.spec, tensors, rt)
+        del tensors
+
+        model_max = int(getattr(self.config, "max_position_embeddings", max_seq_len or 0))
+        self.max_seq_len = min(max_seq_len or model_max, model_max)
+        pool_tokens = pool_tokens or self.max_seq_len
+        if pool_tokens < self.max_seq_len:
+            raise ValueError(f"kv_pool_tokens ({pool_tokens}) must be >= max_seq_len "
+                             f"({self.max_seq_len}) so any single request can complete alone")
+        if page_size < 1:
+            raise ValueError(f"block_size must be >= 1, got {page_size}")
+        kv_groups, state_groups = plan_groups(self.model.cache_needs(), pool_tokens, page_size)
+        self.manager = CacheManager(kv_groups, state_groups, max_slots)
+        self.cache = DeviceCache(self.manager, self.dtype, self.device, self.max_seq_len)
+        self.page_size = page_size
+        self.max_step_tokens = max_step_tokens or max(self.max_seq_len, max_slots)
+        self.step = StepFunction(self.model, self.cache, self.max_step_tokens, self.max_seq_len)
+        logger.info("Loaded %s (%s) on %s as %s: %d pages of %d tokens per layer group",
+                    model, self.config.architecture, self.device, self.dtype,
+                    kv_groups[0].num_pages if kv_groups else 0, page_size)

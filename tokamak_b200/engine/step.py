@@ -1,0 +1,255 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+The reference runs either one whole prompt or one token of every running
+sequence per step (src/tokamak/engine/llm.py:347-388).  Here a step is a flat
+batch of tokens: portions of prompts beside single decoded tokens, cut anywhere.
+Every entry continues its request at the position the cache has reached, the
+step writes the new keys and values first and then attends over everything up
+to each token (the reference's order, src/tokamak/model/step_context.py:88), and
+logits are produced only for the places that are asked for.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Hashable, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.device import DeviceCache
+from ..csrc import ops
+
+_ERR_NAMES = {1: "token id outside the vocabulary", 2: "page outside the pool or the table",
+              3: "negative position", 4: "request row outside the batch",
+              5: "a bounded wait in a kernel ran out"}
+
+
+class StepError(RuntimeError):
+    """A kernel reported bad input through the error word."""
+
+
+@dataclass
+class StepEntry:
+    """Next tokens of one request and the places among them whose logits are wanted."""
+
+    req_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class SamplingRow:
+    """How to sample at one wanted place (see tokamak_b200.sampling)."""
+
+    temperature: float = 0.0
+    top_k: int = 0
+    top_p: float = 1.0
+    seed: int = 0
+    counter: int = 0
+
+
+@dataclass
+class StepBatch:
+    """Device-side description of a step, handed to every part.
+
+    All index tensors are int32.  ``tok_req[t]`` is the row of token ``t``'s
+    request in the per-request arrays; ``req_slot[r]`` is that request's row in the
+    block tables and state records; ``req_kv_len[r]`` counts the positions of the
+    request after this step, so its tokens sit at ``req_kv_len - req_q_len ...``.
+    The ``host_*`` lists repeat the per-request numbers for parts that plan on the host.
+    """
+
+    n_tokens: int
+    n_reqs: int
+    n_want: int
+    token_ids: torch.Tensor
+    positions: torch.Tensor
+    tok_req: torch.Tensor
+    req_q_start: torch.Tensor
+    req_q_len: torch.Tensor
+    req_kv_len: torch.Tensor
+    req_slot: torch.Tensor
+    logits_rows: torch.Tensor
+    cache: DeviceCache
+    err: torch.Tensor
+    host_q_start: list[int] = field(default_factory=list)
+    host_q_len: list[int] = field(default_factory=list)
+    host_kv_len: list[int] = field(default_factory=list)
+    host_slot: list[int] = field(default_factory=list)
+    max_q_len: int = 0
+    max_kv_len: int = 0
+    scratch: dict = field(default_factory=dict)     # per-step values that parts share (e.g. plans)
+
+
+class StepBuffers:
+    """Pinned host staging and its device twin for the integers that describe a step."""
+
+    def __init__(self, device: torch.device, max_tokens: int, max_reqs: int):
+        self.device = device
+        self.capacity = 6 * max_reqs + 3 * max_tokens + 4 * max_tokens + 64
+        self.host = torch.zeros(self.capacity, dtype=torch.int32).pin_memory()
+        self.dev = torch.zeros(self.capacity, dtype=torch.int32, device=device)
+        # error word and sampled tokens travel back together
+        self.result = torch.zeros(4 + max_tokens, dtype=torch.int32, device=device)
+        self.result_host = torch.zeros(4 + max_tokens, dtype=torch.int32).pin_memory()
+
+    def upload(self, arrays: list[np.ndarray]) -> list[torch.Tensor]:
+        """Copy the arrays (int32 views) to the device in one transfer; returns device views."""
+        total = sum(a.size for a in arrays)
+        if total > self.capacity:
+            raise ValueError(f"step needs {total} staging words, capacity is {self.capacity}")
+        host_np = self.host.numpy()
+        views = []
+        off = 0
+        for a in arrays:
+            host_np[off:off + a.size] = a
+            views.append(self.dev[off:off + a.size])
+            off += a.size
+        if total:
+            self.dev[:total].copy_(self.host[:total], non_blocking=True)
+        return views
+
+
+class StepFunction:
+    """Builds the batch description, runs the model and keeps the cache's lengths."""
+
+    def __init__(self, model, cache: DeviceCache, max_step_tokens: int, max_seq_len: int):
+        self.model = model
+        self.cache = cache
+        self.manager = cache.manager
+        self.device = cache.device
+        self.max_step_tokens = max_step_tokens
+        self.max_seq_len = max_seq_len
+        self.buffers = StepBuffers(self.device, max_step_tokens, self.manager.max_slots)
+        self.lengths: dict[Hashable, int] = {}
+        self.steps_run = 0
+        self.kernel_launches = 0
+
+    # ---- request lifetime ------------------------------------------------------------
+    def admit(self, req_id: Hashable) -> None:
+        self.manager.admit(req_id)
+        self.lengths[req_id] = 0
+
+    def free(self, req_id: Hashable) -> None:
+        self.manager.free(req_id)
+        self.lengths.pop(req_id, None)
+
+    def length(self, req_id: Hashable) -> int:
+        return self.lengths.get(req_id, 0)
+
+    # ---- the step ----------------------------------------------------------------------
+    def build(self, entries: Sequence[StepEntry],
+              sampling: Sequence[SamplingRow] | None = None) -> tuple[StepBatch, dict]:
+        """Reserve pages, lay the batch out and upload its description."""
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        seen = set()
+        tokens: list[int] = []
+        positions: list[int] = []
+        tok_req: list[int] = []
+        q_start: list[int] = []
+        q_len: list[int] = []
+        kv_len: list[int] = []
+        slots: list[int] = []
+        rows: list[int] = []
+        for r, e in enumerate(entries):
+            if e.req_id in seen:
+                raise ValueError(f"request {e.req_id!r} appears twice in one step")
+            seen.add(e.req_id)
+            if not self.manager.has(e.req_id):
+                self.admit(e.req_id)
+            n = len(e.tokens)
+            if n < 1:
+                raise ValueError(f"request {e.req_id!r} brings no tokens")
+            start = self.lengths[e.req_id]
+            if start + n > self.max_seq_len:
+                raise ValueError(f"request {e.req_id!r} would reach {start + n} tokens, "
+                                 f"beyond max_seq_len={self.max_seq_len}")
+            self.manager.grow(e.req_id, start + n)
+            q_start.append(len(tokens))
+            q_len.append(n)
+            kv_len.append(start + n)
+            slots.append(self.manager.slot(e.req_id))
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"request {e.req_id!r} wants place {w} of {n} tokens")
+                rows.append(len(tokens) + w)
+            tokens.extend(int(t) for t in e.tokens)
+            positions.extend(range(start, start + n))
+            tok_req.extend([r] * n)
+        if len(tokens) > self.max_step_tokens:
+            raise ValueError(f"step of {len(tokens)} tokens exceeds max_step_tokens="
+                             f"{self.max_step_tokens}")
+        W = len(rows)
+        if sampling is not None and len(sampling) != W:
+            raise ValueError(f"{len(sampling)} sampling rows for {W} wanted places")
+
+        i32 = lambda x: np.asarray(x, dtype=np.int32)
+        arrays = []
+        if sampling is not None:
+            seeds = np.asarray([s.seed & 0x7FFFFFFFFFFFFFFF for s in sampling], dtype=np.int64)
+            arrays += [seeds.view(np.int32),
+                       np.asarray([s.temperature for s in sampling], dtype=np.float32).view(np.int32),
+                       np.asarray([s.top_p for s in sampling], dtype=np.float32).view(np.int32),
+                       i32([s.top_k for s in sampling]), i32([s.counter for s in sampling])]
+        arrays += [i32(tokens), i32(positions), i32(tok_req), i32(q_start), i32(q_len), i32(kv_len),
+                   i32(slots), i32(rows)]
+        views = self.buffers.upload(arrays)
+        samp = {}
+        if sampling is not None:
+            samp = {"seed": views[0].view(torch.int64), "temperature": views[1].view(torch.float32),
+                    "top_p": views[2].view(torch.float32), "top_k": views[3], "counter": views[4]}
+            views = views[5:]
+        self.cache.sync()
+        batch = StepBatch(
+            n_tokens=len(tokens), n_reqs=len(entries), n_want=W,
+            token_ids=views[0], positions=views[1], tok_req=views[2], req_q_start=views[3],
+            req_q_len=views[4], req_kv_len=views[5], req_slot=views[6], logits_rows=views[7],
+            cache=self.cache, err=self.buffers.result[:4],
+            host_q_start=q_start, host_q_len=q_len, host_kv_len=kv_len, host_slot=slots,
+            max_q_len=max(q_len), max_kv_len=max(kv_len))
+        return batch, samp
+
+    def finish(self, entries: Sequence[StepEntry]) -> None:
+        """Advance the lengths and give back the pages that a window has passed."""
+        for e in entries:
+            self.lengths[e.req_id] += len(e.tokens)
+            self.manager.release_passed(e.req_id, self.lengths[e.req_id])
+        self.steps_run += 1
+
+    @torch.inference_mode()
+    def run(self, entries: Sequence[StepEntry], check: bool = True) -> torch.Tensor:
+        """Float32 logits ``[wanted, vocab]`` on the device, in the order of entries and ``want``."""
+        batch, _ = self.build(entries)
+        logits = self.model.forward(batch)
+        self.finish(entries)
+        if check:
+            self.check_errors()
+        return logits
+
+    @torch.inference_mode()
+    def run_and_sample(self, entries: Sequence[StepEntry], sampling: Sequence[SamplingRow]) -> list[int]:
+        """One token per wanted place, sampled on the device; one copy back for tokens and errors."""
+        batch, samp = self.build(entries, sampling)
+        logits = self.model.forward(batch)
+        W = batch.n_want
+        res = self.buffers.result
+        if W:
+            ops.sample(logits, samp["temperature"], samp["top_k"], samp["top_p"], samp["seed"],
+                       samp["counter"], res[4:4 + W])
+        self.finish(entries)
+        host = self.buffers.result_host
+        host[:4 + W].copy_(res[:4 + W], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self._raise_on_error(host[:4].tolist())
+        return host[4:4 + W].tolist()
+
+    def check_errors(self) -> None:
+        self._raise_on_error(self.buffers.result[:4].cpu().tolist())
+
+    def _raise_on_error(self, word: list[int]) -> None:
+        if word[0] != 0:
+            self.buffers.result[:4].zero_()
+            raise StepError(f"kernel error {word[0]} ({_ERR_NAMES.get(word[0], 'unknown')}); "
+                            f"details {word[1:]}")

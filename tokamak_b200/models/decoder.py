@@ -1,0 +1,95 @@
+"""A decoder described as data: parts, blocks, and the order in which they run."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..parts.base import BLOCKS, NORMS, Runtime, TensorReq
+from ..parts.embedding import Embedding, EmbeddingSpec, Head, HeadSpec
+
+
+@dataclass(frozen=True)
+class LayerCall:
+    """One entry of the schedule: which block runs and which cache it uses.
+
+    Naming a block twice runs its weights twice; two calls that name the same
+    ``cache`` share keys and values (the later one must be built without key and
+    value projections of its own).  ``cache`` is ``None`` for a block that keeps
+    nothing between steps.
+    """
+
+    block: str
+    cache: str | None
+
+
+@dataclass(frozen=True)
+class ModelSpec:
+    embedding: EmbeddingSpec
+    blocks: tuple                      # block specs, each with a unique ``name``
+    schedule: tuple                    # LayerCall entries, in execution order
+    final_norm: object
+    final_norm_name: str
+    head: HeadSpec
+
+    def __post_init__(self) -> None:
+        names = [b.name for b in self.blocks]
+        if len(set(names)) != len(names):
+            raise ValueError("block names must be unique")
+        for call in self.schedule:
+            if call.block not in names:
+                raise ValueError(f"the schedule names an unknown block {call.block!r}")
+
+
+class DecoderModel:
+    """Embedding, the scheduled blocks, final norm and head
+    (src/tokamak/model/transformer.py:112-176), built from a :class:`ModelSpec`."""
+
+    def __init__(self, spec: ModelSpec, tensors: dict[str, torch.Tensor], rt: Runtime):
+        self.spec = spec
+        self.rt = rt
+        self.embedding = Embedding(spec.embedding, tensors, rt)
+        self.blocks = {b.name: BLOCKS.get(b.kind)(b, tensors, rt) for b in spec.blocks}
+        self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, spec.final_norm_name,
+                                                          tensors, rt)
+        self.head = Head(spec.head, self.embedding, tensors, rt)
+
+    @staticmethod
+    def expected_tensors(spec: ModelSpec) -> dict[str, TensorReq]:
+        out: dict[str, TensorReq] = {}
+        out.update(Embedding.expected_tensors(spec.embedding))
+        for b in spec.blocks:
+            out.update(BLOCKS.get(b.kind).expected_tensors(b))
+        out.update(NORMS.get(spec.final_norm.kind).expected_tensors(spec.final_norm,
+                                                                    spec.final_norm_name))
+        out.update(Head.expected_tensors(spec.head))
+        return out
+
+    def cache_needs(self) -> dict[str, object]:
+        """Cache key -> need, checked for agreement between calls that share a key."""
+        needs: dict[str, object] = {}
+        for call in self.spec.schedule:
+            need = self.blocks[call.block].cache_need()
+            if need is None:
+                if call.cache is not None:
+                    raise ValueError(f"block {call.block!r} keeps no cache but is given {call.cache!r}")
+                continue
+            if call.cache is None:
+                raise ValueError(f"block {call.block!r} needs a cache and the schedule names none")
+            if call.cache in needs and needs[call.cache] != need:
+                raise ValueError(f"cache {call.cache!r} is shared by blocks with different needs")
+            needs.setdefault(call.cache, need)
+        return needs
+
+    def forward(self, step) -> torch.Tensor:
+        """Float32 logits ``[len(step.logits_rows), vocab]`` for the rows asked for."""
+        resid = self.embedding.forward(step)
+        pending = None
+        for call in self.spec.schedule:
+            view = step.cache.view(call.cache) if call.cache is not None else None
+            resid, pending = self.blocks[call.block].forward(resid, pending, step, view)
+        if step.n_want == 0:
+            return torch.empty((0, self.spec.head.vocab_size), dtype=torch.float32, device=resid.device)
+        h = self.final_norm.add_norm(resid, pending, rows=step.logits_rows)
+        return self.head.forward(h)

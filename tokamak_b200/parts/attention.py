@@ -1,0 +1,107 @@
+"""The attention mixer: grouped-query attention over paged keys and values."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..cache.manager import KVPagesNeed
+from ..csrc import ops
+from .base import MIXERS, POSITIONS, Runtime, TensorReq, linear
+
+
+@dataclass(frozen=True)
+class AttentionSpec:
+    """Sizes and constants of one attention mixer.
+
+    ``qk_norm_eps`` of ``None`` switches the per-head norm of q and k off;
+    ``window`` of ``None`` means every earlier key is seen; ``own_kv=False``
+    describes a layer without key and value projections that reads the pages
+    another layer wrote (the schedule names which).
+    """
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    position: object                       # a position spec (kind, ...)
+    qk_norm_eps: float | None = None
+    window: int | None = None
+    own_kv: bool = True
+    softmax_scale: float | None = None     # default head_dim ** -0.5
+    kind: str = "attention"
+
+
+@MIXERS.register("attention")
+class Attention:
+    """Projections, per-head q/k norm, rotation, page write and attention
+    (src/tokamak/model/transformer.py:22-86 with the step context's
+    store-then-attend order, src/tokamak/model/step_context.py:88).
+
+    The q, k and v matrices are stacked into one ``[(Hq + 2 Hkv) d, H]`` operand.
+    """
+
+    def __init__(self, spec: AttentionSpec, prefix: str, tensors: dict[str, torch.Tensor], rt: Runtime):
+        if spec.num_heads % spec.num_kv_heads:
+            raise ValueError(f"{spec.num_heads} query heads are not a multiple of "
+                             f"{spec.num_kv_heads} key/value heads")
+        if spec.head_dim > 256:
+            raise ValueError(f"head_dim {spec.head_dim} is beyond the attention kernels' limit of 256")
+        self.spec = spec
+        self.rt = rt
+        mats = [tensors[prefix + "q_proj.weight"]]
+        if spec.own_kv:
+            mats += [tensors[prefix + "k_proj.weight"], tensors[prefix + "v_proj.weight"]]
+        self.w_qkv = torch.cat(mats, dim=0).contiguous() if len(mats) > 1 else mats[0]
+        self.w_o = tensors[prefix + "o_proj.weight"]
+        self.q_norm_w = tensors.get(prefix + "q_norm.weight") if spec.qk_norm_eps is not None else None
+        self.k_norm_w = tensors.get(prefix + "k_norm.weight") if spec.qk_norm_eps is not None else None
+        self.position = POSITIONS.get(spec.position.kind)(spec.position, rt)
+        self.scale = spec.softmax_scale if spec.softmax_scale is not None else spec.head_dim ** -0.5
+
+    @staticmethod
+    def expected_tensors(spec: AttentionSpec, prefix: str) -> dict[str, TensorReq]:
+        h, d = spec.hidden_size, spec.head_dim
+        out = {
+            prefix + "q_proj.weight": TensorReq((spec.num_heads * d, h)),
+            prefix + "o_proj.weight": TensorReq((h, spec.num_heads * d)),
+        }
+        if spec.own_kv:
+            out[prefix + "k_proj.weight"] = TensorReq((spec.num_kv_heads * d, h))
+            out[prefix + "v_proj.weight"] = TensorReq((spec.num_kv_heads * d, h))
+        if spec.qk_norm_eps is not None:
+            out[prefix + "q_norm.weight"] = TensorReq((d,), role="vector")
+            if spec.own_kv:
+                out[prefix + "k_norm.weight"] = TensorReq((d,), role="vector")
+        return out
+
+    def cache_need(self) -> KVPagesNeed:
+        return KVPagesNeed(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
+
+    def forward(self, h: torch.Tensor, step, cache_view) -> torch.Tensor:
+        spec = self.spec
+        n = h.shape[0]
+        qkv = linear(h, self.w_qkv)
+        q = torch.empty((n, spec.num_heads, spec.head_dim), dtype=h.dtype, device=h.device)
+        inv_freq, rotary_dim = self.position.rotary_table()
+        ops.rope_kv(qkv, q, cache_view.k if spec.own_kv else None,
+                    cache_view.v if spec.own_kv else None,
+                    step.positions, step.tok_req, step.req_slot, cache_view.table,
+                    self.q_norm_w, self.k_norm_w, inv_freq, step.err,
+                    n_q_heads=spec.num_heads, n_kv_heads=spec.num_kv_heads, head_dim=spec.head_dim,
+                    rotary_dim=rotary_dim, eps=spec.qk_norm_eps or 0.0, write_kv=spec.own_kv)
+        out = torch.empty_like(q)
+        paged_attention(q, out, cache_view, step, scale=self.scale, window=spec.window)
+        return linear(out.view(n, spec.num_heads * spec.head_dim), self.w_o)
+
+
+def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, scale: float,
+                    window: int | None) -> None:
+    """Attention of every token of the step over the pages of its own request.
+
+    Chooses the kernel: the general one for float32 and for shapes the tiled
+    kernels do not take.
+    """
+    ops.attention_plain(q, out, cache_view.k, cache_view.v, step.positions, step.tok_req,
+                        step.req_slot, cache_view.table, step.err, scale=scale, window=window)

@@ -1,0 +1,112 @@
+"""What every part of a layer has in common: specs, tensor requests, registries.
+
+A *spec* is a frozen dataclass with a ``kind`` string and the sizes and
+constants of one part; it is data, produced by an architecture from its
+configuration.  A *part* is the object built from a spec and the weights; it
+owns its tensors and calls the kernels.  The registries map ``kind`` to the
+class that builds the part, one registry per role:
+
+=============  ==========================================================
+role           interface of the registered class
+=============  ==========================================================
+norm           ``expected_tensors(spec, name)``, ``__init__(spec, name, tensors, rt)``,
+               ``add_norm(resid, delta, rows=None) -> normed``
+position       ``__init__(spec, rt)``, ``rotary_table() -> (inv_freq | None, rotary_dim)``
+mixer          ``expected_tensors(spec, prefix)``, ``__init__(spec, prefix, tensors, rt)``,
+               ``cache_need() -> KVPagesNeed | StateNeed | None``,
+               ``forward(h, step, cache_view) -> [N, hidden]``
+feed_forward   ``expected_tensors(spec, prefix)``, ``__init__(spec, prefix, tensors, rt)``,
+               ``forward(h, step) -> [N, hidden]``
+block          ``expected_tensors(spec)``, ``__init__(spec, tensors, rt)``,
+               ``cache_need()``, ``forward(resid, pending, step, cache_view) -> (resid, pending)``
+=============  ==========================================================
+
+No part knows which model it is in: it sees its spec, its tensors, the step's
+batch description and the view of its own cache.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable
+
+import torch
+
+
+@dataclass(frozen=True)
+class TensorReq:
+    """A tensor that a part expects in the checkpoint.
+
+    ``role`` decides the element type in memory: ``matrix`` takes the engine's
+    dtype; ``vector`` (norm weights and other small per-channel tensors) is held in
+    float32, which keeps a tensor stored in 32-bit exact; ``int_table`` becomes int32.
+    """
+
+    shape: tuple[int, ...]
+    role: str = "matrix"
+    optional: bool = False
+
+
+@dataclass
+class Runtime:
+    """Where and in which element type the parts live."""
+
+    device: torch.device
+    dtype: torch.dtype            # torch.bfloat16 (serving) or torch.float32 (true 32-bit path)
+
+    @property
+    def is_f32(self) -> bool:
+        return self.dtype == torch.float32
+
+
+class Registry:
+    """Maps the ``kind`` of a spec to the class that builds the part."""
+
+    def __init__(self, role: str) -> None:
+        self.role = role
+        self._classes: dict[str, Any] = {}
+
+    def register(self, kind: str) -> Callable[[Any], Any]:
+        def deco(cls: Any) -> Any:
+            if kind in self._classes and self._classes[kind] is not cls:
+                raise ValueError(f"{self.role} kind {kind!r} is already registered")
+            self._classes[kind] = cls
+            return cls
+        return deco
+
+    def unregister(self, kind: str) -> None:
+        self._classes.pop(kind, None)
+
+    def get(self, kind: str) -> Any:
+        try:
+            return self._classes[kind]
+        except KeyError:
+            known = ", ".join(sorted(self._classes)) or "<none>"
+            raise KeyError(f"no {self.role} of kind {kind!r} is registered; known: {known}") from None
+
+    def kinds(self) -> list[str]:
+        return sorted(self._classes)
+
+
+NORMS = Registry("norm")
+POSITIONS = Registry("position")
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed_forward")
+BLOCKS = Registry("block")
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``x @ weight^T`` for ``weight`` of shape [out, in].
+
+    float32: the engine's own FFMA kernel (no TF32, no tensor cores).  bfloat16:
+    the library product, as the reference uses the library for its projections
+    (src/tokamak/model/transformer.py:38-41); ``out_dtype=float32`` keeps the
+    32-bit accumulators instead of rounding them.
+    """
+    from ..csrc import ops
+
+    if x.dtype == torch.float32:
+        return ops.gemm_f32(x, weight)
+    if out_dtype is not None and out_dtype != x.dtype:
+        return torch.mm(x, weight.t(), out_dtype=out_dtype)
+    return torch.mm(x, weight.t())
