@@ -1,0 +1,155 @@
+"""Generation through the Python entry point against the plain implementation."""
+
+from __future__ import annotations
+
+import dataclasses
+
+import pytest
+import torch
+
+import tiny_configs
+from helpers import model_folder, plain_logits, random_tokens
+from plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+
+def llm_for(tag, dtype, **kw):
+    from tokamak_b200 import LLM
+    kw.setdefault("block_size", tiny_configs.ALL[tag][2])
+    return LLM(model_folder(tag, dtype), dtype=dtype, **kw)
+
+
+def prompts_for(tag, lengths):
+    vocab = tiny_configs.ALL[tag][0]["vocab_size"]
+    return [random_tokens(vocab, n, seed=7 * n + 1) for n in lengths]
+
+
+def test_greedy_matches_plain_float32():
+    """Configuration A's workload: prompts of 5, 17 and 33 tokens, 8 greedy tokens each."""
+    from tokamak_b200 import SamplingParams
+    llm = llm_for("A", "float32")
+    prompts = prompts_for("A", [5, 17, 33])
+    outs = llm.generate(prompt_token_ids=prompts,
+                        sampling_params=SamplingParams(temperature=0.0, max_new_tokens=8))
+    cfg, w = plain.load_folder(model_folder("A", "float32"))
+    for p, o in zip(prompts, outs):
+        assert o.output_token_ids == plain.greedy_generate(cfg, w, p, 8)
+        assert o.finish_reason.value == "length" and o.prompt_token_ids == p
+    assert [o.request_id for o in outs] == [0, 1, 2]
+    assert all(0 < o.ttft_s <= o.latency_s for o in outs)
+
+
+def test_chunked_prefill_with_temperature_matches_plain_float32():
+    """Configuration B's workload: prompts of 1/7/31/64/100, portions of 24 beside decodes,
+    temperature 0.8, seed 1, 12 new tokens.  Every token must be the plain sampler's draw
+    from the plain logits of the same prefix."""
+    from tokamak_b200 import SamplingParams
+    llm = llm_for("B", "float32", prefill_chunk=24, max_num_batched_tokens=48, max_batch_size=4)
+    prompts = prompts_for("B", [1, 7, 31, 64, 100])
+    params = SamplingParams(temperature=0.8, seed=1, max_new_tokens=12)
+    outs = llm.generate(prompt_token_ids=prompts, sampling_params=params)
+    assert llm.last_stats["mixed_steps"] > 0
+    folder = model_folder("B", "float32")
+    for p, o in zip(prompts, outs):
+        assert len(o.output_token_ids) == 12
+        seq = list(p)
+        for i, tok in enumerate(o.output_token_ids):
+            logits = plain_logits(folder, seq)[-1]
+            assert tok == plain.sample_token(logits.float(), 0.8, seed=1, token_index=i), (len(p), i)
+            seq.append(tok)
+
+
+def test_preemption_is_invisible_in_greedy_tokens():
+    """A pool so small that sequences are evicted and recomputed gives the same tokens as a
+    large pool (after the reference's tests/integration/test_generate_e2e.py:180-213)."""
+    from tokamak_b200 import SamplingParams
+    prompts = prompts_for("A", [20, 28, 24, 30])
+    params = SamplingParams(temperature=0.0, max_new_tokens=24)
+    big = llm_for("A", "float32", max_seq_len=64, kv_pool_tokens=1024)
+    want = [o.output_token_ids for o in big.generate(prompt_token_ids=prompts, sampling_params=params)]
+    assert big.last_stats["preemptions"] == 0
+    small = llm_for("A", "float32", max_seq_len=64, kv_pool_tokens=128)
+    outs = small.generate(prompt_token_ids=prompts, sampling_params=params)
+    assert small.last_stats["preemptions"] > 0
+    assert [o.output_token_ids for o in outs] == want
+    assert sum(o.num_preemptions for o in outs) == small.last_stats["preemptions"]
+    small.cache_manager.check_invariants()
+    assert all(g.num_free == g.num_pages for g in small.cache_manager.kv_groups)
+
+
+def test_seeded_sampling_is_reproducible_and_independent_of_batching():
+    from tokamak_b200 import SamplingParams
+    prompts = prompts_for("B", [9, 30, 12, 21])
+    params = [SamplingParams(temperature=1.0, top_k=20, top_p=0.9, seed=40 + i, max_new_tokens=10)
+              for i in range(4)]
+    a = llm_for("B", "float32", max_batch_size=4).generate(prompt_token_ids=prompts, sampling_params=params)
+    b = llm_for("B", "float32", max_batch_size=1).generate(prompt_token_ids=prompts, sampling_params=params)
+    c = llm_for("B", "float32", max_batch_size=4, prefill_chunk=5, max_num_batched_tokens=11).generate(
+        prompt_token_ids=prompts, sampling_params=params)
+    toks = lambda outs: [o.output_token_ids for o in outs]
+    assert toks(a) == toks(b) == toks(c)
+    assert len({tuple(t) for t in toks(a)}) == 4
+
+
+def test_finishing_rules_and_errors():
+    from tokamak_b200 import LLM, SamplingParams
+    llm = llm_for("A", "float32", max_seq_len=40)
+    p = prompts_for("A", [10])[0]
+    first = llm.generate(prompt_token_ids=[p], sampling_params=SamplingParams(temperature=0.0, max_new_tokens=3))
+    assert len(first[0].output_token_ids) == 3 and first[0].finish_reason.value == "length"
+    # treat the second generated token as EOS
+    eos = first[0].output_token_ids[1]
+    llm.model_config = dataclasses.replace(llm.model_config, eos_token_ids=(eos,))
+    stop = llm.generate(prompt_token_ids=[p], sampling_params=SamplingParams(temperature=0.0, max_new_tokens=9))
+    assert stop[0].finish_reason.value == "stop" and stop[0].output_token_ids[-1] == eos
+    assert len(stop[0].output_token_ids) <= 2
+    on = llm.generate(prompt_token_ids=[p], sampling_params=SamplingParams(temperature=0.0, max_new_tokens=9,
+                                                                          ignore_eos=True))
+    assert len(on[0].output_token_ids) == 9
+    llm.model_config = dataclasses.replace(llm.model_config, eos_token_ids=())
+    ctx = llm.generate(prompt_token_ids=[p], sampling_params=SamplingParams(temperature=0.0, max_new_tokens=500))
+    assert len(ctx[0].output_token_ids) == 30 and ctx[0].finish_reason.value == "length"   # max_seq_len 40
+    with pytest.raises(ValueError, match="does not fit"):
+        llm.generate(prompt_token_ids=[list(range(40))])
+    with pytest.raises(ValueError, match="exactly one"):
+        llm.generate()
+    with pytest.raises(ValueError, match="SamplingParams for"):
+        llm.generate(prompt_token_ids=[p, p], sampling_params=[SamplingParams()])
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        llm.generate(prompt_token_ids=[[1, 999999]])
+    with pytest.raises(ValueError, match="kv_pool_tokens"):
+        LLM(model_folder("A", "float32"), dtype="float32", max_seq_len=64, kv_pool_tokens=32)
+    with pytest.raises(ValueError, match="Unknown dtype"):
+        LLM(model_folder("A", "float32"), dtype="float16")
+
+
+@pytest.mark.parametrize("tag", ["A", "B"])
+def test_greedy_bfloat16_picks_a_top_token(tag):
+    """In bfloat16 near-ties may flip, so tokens are judged against the plain logits: each
+    generated token must be within a small margin of the plain maximum for its prefix."""
+    from tokamak_b200 import SamplingParams
+    llm = llm_for(tag, "bfloat16", prefill_chunk=16, max_num_batched_tokens=40)
+    prompts = prompts_for(tag, [6, 19, 45])
+    outs = llm.generate(prompt_token_ids=prompts,
+                        sampling_params=SamplingParams(temperature=0.0, max_new_tokens=8))
+    folder = model_folder(tag, "bfloat16")
+    for p, o in zip(prompts, outs):
+        seq = list(p)
+        for tok in o.output_token_ids:
+            logits = plain_logits(folder, seq)[-1]
+            assert logits[tok] >= logits.max() - 0.04 * logits.std()
+            seq.append(tok)
+
+
+def test_window_policy_matches_a_windowed_config():
+    """attention_policy='window:W' equals a config.json that windows every layer."""
+    from tokamak_b200 import SamplingParams
+    llm = llm_for("A", "float32", attention_policy="window:12")
+    prompts = prompts_for("A", [40])
+    outs = llm.generate(prompt_token_ids=prompts, sampling_params=SamplingParams(temperature=0.0, max_new_tokens=6))
+    cfg, w = plain.load_folder(model_folder("A", "float32"))
+    cfg = dict(cfg, use_sliding_window=True, sliding_window=12, max_window_layers=0)
+    assert outs[0].output_token_ids == plain.greedy_generate(cfg, w, prompts[0], 6)
+    with pytest.raises(ValueError, match="attention_policy"):
+        llm_for("A", "float32", attention_policy="streaming:8+2")

@@ -1,0 +1,348 @@
+"""Each kernel alone against a plain PyTorch reference, at sizes other than the engine's."""
+
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+from plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+def err_word():
+    return torch.zeros(4, dtype=torch.int32, device=DEV)
+
+
+# ----------------------------------------------------------------------------- small kernels
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed_gather_and_bad_token(dtype):
+    from tokamak_b200.csrc import ops
+    table = torch.randn(1000, 200, device=DEV).to(dtype)
+    ids = torch.tensor([0, 999, 17, 17, 500], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 200, device=DEV)
+    err = err_word()
+    ops.embed_gather(table, ids, out, err)
+    torch.testing.assert_close(out, table[ids.long()].float(), rtol=0, atol=0)
+    assert err.tolist() == [0, 0, 0, 0]
+    bad = torch.tensor([3, 1000], dtype=torch.int32, device=DEV)
+    ops.embed_gather(table, bad, out[:2], err)
+    assert err.tolist()[:3] == [1, 1, 1000] and out[1].abs().sum() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [80, 320, 4096, 5120])
+def test_add_rmsnorm(dtype, hidden):
+    from tokamak_b200.csrc import ops
+    n, eps = 37, 1e-5
+    resid = torch.randn(n, hidden, device=DEV) * 3
+    delta = torch.randn(n, hidden, device=DEV).to(dtype)
+    w = 1 + 0.1 * torch.randn(hidden, device=DEV)
+    want_sum = resid.double() + delta.double()
+    want = plain.rms_norm(want_sum, w.double(), eps)
+    r = resid.clone()
+    out = torch.empty(n, hidden, device=DEV, dtype=dtype)
+    ops.add_rmsnorm(r, delta, w, out, eps)
+    torch.testing.assert_close(r.double(), want_sum, rtol=1e-6, atol=1e-6)      # the sum is a 32-bit sum
+    torch.testing.assert_close(out.double(), want, **tol(dtype))
+    # without a pending branch, and on chosen rows only
+    r2 = resid.clone()
+    ops.add_rmsnorm(r2, None, w, out, eps)
+    torch.testing.assert_close(out.double(), plain.rms_norm(resid.double(), w.double(), eps), **tol(dtype))
+    assert torch.equal(r2, resid)
+    rows = torch.tensor([5, 0, 36, 5], dtype=torch.int32, device=DEV)
+    out3 = torch.empty(4, hidden, device=DEV, dtype=dtype)
+    r3 = resid.clone()
+    ops.add_rmsnorm(r3, delta, w, out3, eps, rows)
+    torch.testing.assert_close(out3.double(), want[rows.long()], **tol(dtype))
+    assert torch.equal(r3, resid)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(dtype):
+    from tokamak_b200.csrc import ops
+    n, inter = 19, 333
+    gu = (torch.randn(n, 2 * inter, device=DEV) * 4).to(dtype)
+    out = torch.empty(n, inter, device=DEV, dtype=dtype)
+    ops.swiglu(gu, out)
+    g, u = gu[:, :inter].double(), gu[:, inter:].double()
+    torch.testing.assert_close(out.double(), g * torch.sigmoid(g) * u, **tol(dtype))
+
+
+@pytest.mark.parametrize("shape", [(3, 317, 96), (130, 70, 33), (1, 1, 1), (64, 64, 16), (65, 129, 1000)])
+def test_gemm_f32_is_true_float32_and_row_independent(shape):
+    from tokamak_b200.csrc import ops
+    m, n, k = shape
+    a = torch.randn(m, k, device=DEV)
+    w = torch.randn(n, k, device=DEV)
+    out = ops.gemm_f32(a, w)
+    want = a.double() @ w.double().T
+    torch.testing.assert_close(out.double(), want, rtol=1e-5, atol=1e-5 * math.sqrt(k))
+    # a row's result does not depend on the other rows of the batch: bit-equal
+    one = ops.gemm_f32(a[m // 2:m // 2 + 1].contiguous(), w)
+    assert torch.equal(one[0], out[m // 2])
+
+
+def test_gemm_f32_keeps_what_reduced_precision_would_lose():
+    from tokamak_b200.csrc import ops
+    a = torch.tensor([[1.0, 2.0 ** -12]], device=DEV)
+    w = torch.tensor([[1.0, 1.0]], device=DEV)
+    assert ops.gemm_f32(a, w).item() == 1.0 + 2.0 ** -12        # TF32 or bf16 operands would give 1.0
+
+
+# ----------------------------------------------------------------------------- rope + cache write
+
+def make_tables(n_reqs, max_pages, num_pages, seed):
+    """A shuffled, non-monotonic assignment of distinct pages to request rows."""
+    gen = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(num_pages, generator=gen)[: n_reqs * max_pages]
+    return perm.view(n_reqs, max_pages).to(torch.int32)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,page", [(6, 2, 48, 8), (4, 4, 128, 16), (7, 1, 16, 4)])
+def test_rope_kv_write(dtype, hq, hkv, d, page):
+    from tokamak_b200.csrc import ops
+    eps, theta = 1e-6, 1e6
+    q_lens = [5, 1, 9]
+    starts = [0, 40001, 13]                      # one request far out, to test the angle's accuracy
+    n = sum(q_lens)
+    max_pages = max((s + l + page - 1) // page for s, l in zip(starts, q_lens))
+    num_pages = 3 * max_pages + 5
+    table = torch.zeros(3, max_pages, dtype=torch.int32)
+    gen = torch.Generator().manual_seed(0)
+    free = torch.randperm(num_pages, generator=gen).tolist()
+    positions, tok_req = [], []
+    for r, (s, l) in enumerate(zip(starts, q_lens)):
+        for p in range(s, s + l):
+            positions.append(p); tok_req.append(r)
+        for pi in range(s // page, (s + l - 1) // page + 1):
+            table[r, pi] = free.pop()
+    qkv = torch.randn(n, (hq + 2 * hkv) * d, device=DEV).to(dtype)
+    qw = 1 + 0.1 * torch.randn(d, device=DEV)
+    kw = 1 + 0.1 * torch.randn(d, device=DEV)
+    inv_freq = (1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(DEV)
+    kc = torch.full((num_pages, hkv, page, d), float("nan"), device=DEV, dtype=dtype)
+    vc = torch.full_like(kc, float("nan"))
+    q_out = torch.empty(n, hq, d, device=DEV, dtype=dtype)
+    err = err_word()
+    pos_t = torch.tensor(positions, dtype=torch.int32, device=DEV)
+    ops.rope_kv(qkv, q_out, kc, vc, pos_t, torch.tensor(tok_req, dtype=torch.int32, device=DEV),
+                torch.tensor([0, 1, 2], dtype=torch.int32, device=DEV), table.to(DEV), qw, kw, inv_freq,
+                err, n_q_heads=hq, n_kv_heads=hkv, head_dim=d, rotary_dim=d, eps=eps)
+    assert err.tolist()[0] == 0
+    x = qkv.double().cpu()
+    q = x[:, : hq * d].view(n, hq, d)
+    k = x[:, hq * d:(hq + hkv) * d].view(n, hkv, d)
+    v = x[:, (hq + hkv) * d:].view(n, hkv, d)
+    cos, sin = plain.rope_tables(torch.tensor(positions), d, theta, torch.float64)
+    q_want = plain.apply_rope(plain.rms_norm(q, qw.double().cpu(), eps), cos, sin)
+    k_want = plain.apply_rope(plain.rms_norm(k, kw.double().cpu(), eps), cos, sin)
+    t = dict(rtol=3e-5, atol=3e-5) if dtype == torch.float32 else tol(dtype)
+    torch.testing.assert_close(q_out.double().cpu(), q_want, **t)
+    written = torch.zeros(num_pages, page, dtype=torch.bool)
+    for i, (p, r) in enumerate(zip(positions, tok_req)):
+        pg = int(table[r, p // page])
+        torch.testing.assert_close(kc[pg, :, p % page].double().cpu(), k_want[i], **t)
+        torch.testing.assert_close(vc[pg, :, p % page].double().cpu(), v[i], rtol=0, atol=0)
+        written[pg, p % page] = True
+    # nothing else was touched
+    untouched = lambda c: c.float().cpu().permute(0, 2, 1, 3)[~written]
+    assert torch.isnan(untouched(kc)).all() and torch.isnan(untouched(vc)).all()
+
+
+def test_rope_kv_reports_a_page_outside_the_pool():
+    from tokamak_b200.csrc import ops
+    d = 16
+    qkv = torch.randn(1, 3 * d, device=DEV)
+    kc = torch.zeros(4, 1, 4, d, device=DEV); vc = torch.zeros_like(kc)
+    err = err_word()
+    one = lambda v: torch.tensor([v], dtype=torch.int32, device=DEV)
+    ops.rope_kv(qkv, torch.empty(1, 1, d, device=DEV), kc, vc, one(2), one(0), one(0),
+                torch.tensor([[9]], dtype=torch.int32, device=DEV), None, None, None, err,
+                n_q_heads=1, n_kv_heads=1, head_dim=d, rotary_dim=0, eps=0.0)
+    assert err.tolist()[0] == 2 and kc.abs().sum() == 0
+
+
+# ----------------------------------------------------------------------------- attention
+
+def attention_reference(q, k_all, v_all, positions, tok_req, scale, window):
+    """float64 attention per token over its request's keys [lo, pos]."""
+    n, hq, d = q.shape
+    out = torch.zeros(n, hq, d, dtype=torch.float64)
+    for t in range(n):
+        r, pos = tok_req[t], positions[t]
+        lo = max(0, pos - window + 1) if window else 0
+        k = k_all[r][lo:pos + 1].double()        # [keys, hkv, d]
+        v = v_all[r][lo:pos + 1].double()
+        group = hq // k.shape[1]
+        for h in range(hq):
+            s = (k[:, h // group] @ q[t, h].double()) * scale
+            out[t, h] = torch.softmax(s, 0) @ v[:, h // group]
+    return out
+
+
+def fill_cache(k_all, v_all, table, num_pages, page, dtype):
+    hkv, d = k_all[0].shape[1:]
+    kc = torch.full((num_pages, hkv, page, d), float("nan"), dtype=dtype)
+    vc = torch.full_like(kc, float("nan"))
+    for r, (k, v) in enumerate(zip(k_all, v_all)):
+        for p in range(k.shape[0]):
+            pg = int(table[r, p // page])
+            kc[pg, :, p % page] = k[p].to(dtype)
+            vc[pg, :, p % page] = v[p].to(dtype)
+    return kc.to(DEV), vc.to(DEV)
+
+
+def run_attention(fn, q, kc, vc, positions, tok_req, table, scale, window):
+    err = err_word()
+    out = torch.empty_like(q)
+    n_reqs = table.shape[0]
+    fn(q, out, kc, vc, torch.tensor(positions, dtype=torch.int32, device=DEV),
+       torch.tensor(tok_req, dtype=torch.int32, device=DEV),
+       torch.arange(n_reqs, dtype=torch.int32, device=DEV), table.to(DEV), err, scale=scale, window=window)
+    assert err.tolist()[0] == 0
+    return out
+
+
+ATTN_SHAPES = [(4, 2, 16, 16, None), (6, 1, 32, 8, None), (5, 5, 48, 16, 24), (8, 2, 128, 16, None),
+               (3, 3, 80, 4, 7), (32, 8, 128, 16, None), (2, 1, 256, 16, None)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,page,window", ATTN_SHAPES)
+def test_attention_mixed_batch(dtype, hq, hkv, d, page, window):
+    """Portions, single tokens and a whole prompt in one batch over shuffled pages; pages
+    that no request owns are NaN and must never be read."""
+    from tokamak_b200.csrc import ops
+    kv_lens = [37, 1, 150, 64, 3 * page + 1]
+    q_lens = [37, 1, 1, 9, 2]                      # whole prompt, first token, decode, portion, two tokens
+    max_pages = max(-(-l // page) for l in kv_lens)
+    num_pages = len(kv_lens) * max_pages + 7
+    table = make_tables(len(kv_lens), max_pages, num_pages, seed=d)
+    gen = torch.Generator().manual_seed(d + hq)
+    k_all = [torch.randn(l, hkv, d, generator=gen) for l in kv_lens]
+    v_all = [torch.randn(l, hkv, d, generator=gen) for l in kv_lens]
+    if dtype == torch.bfloat16:
+        k_all = [k.bfloat16().float() for k in k_all]; v_all = [v.bfloat16().float() for v in v_all]
+    kc, vc = fill_cache(k_all, v_all, table, num_pages, page, dtype)
+    positions, tok_req = [], []
+    for r, (kl, ql) in enumerate(zip(kv_lens, q_lens)):
+        positions += list(range(kl - ql, kl)); tok_req += [r] * ql
+    q = torch.randn(len(positions), hq, d, generator=gen).to(dtype)
+    scale = d ** -0.5
+    out = run_attention(ops.attention_plain, q.to(DEV), kc, vc, positions, tok_req, table, scale, window)
+    want = attention_reference(q.float(), k_all, v_all, positions, tok_req, scale, window)
+    torch.testing.assert_close(out.double().cpu(), want, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("where", ["first", "far", "page_edge", "last", "window_edge", "just_outside"])
+def test_attention_finds_the_one_key_that_matters(dtype, where):
+    """One key among hundreds is made to dominate the softmax; the output must be its value.
+    Random inputs would hide a key that is skipped at a page's edge or at the window's edge."""
+    from tokamak_b200.csrc import ops
+    hq, hkv, d, page = 4, 2, 64, 16
+    kv_len, window = 700, None
+    target = {"first": 0, "far": 123, "page_edge": 16 * 20 - 1, "last": kv_len - 1,
+              "window_edge": kv_len - 100, "just_outside": kv_len - 101}[where]
+    if where in ("window_edge", "just_outside"):
+        window = 100
+    gen = torch.Generator().manual_seed(3)
+    k = torch.randn(kv_len, hkv, d, generator=gen) * 0.1
+    v = torch.randn(kv_len, hkv, d, generator=gen)
+    q = torch.randn(1, hq, d, generator=gen) * 0.1
+    direction = torch.randn(d, generator=gen)
+    direction /= direction.norm()
+    q[0, :] += 40.0 * direction
+    k[target, :] += 40.0 * direction
+    if dtype == torch.bfloat16:
+        k, v, q = k.bfloat16().float(), v.bfloat16().float(), q.bfloat16().float()
+    max_pages = -(-kv_len // page)
+    table = make_tables(1, max_pages, max_pages + 9, seed=1)
+    kc, vc = fill_cache([k], [v], table, max_pages + 9, page, dtype)
+    out = run_attention(ops.attention_plain, q.to(dtype).to(DEV), kc, vc, [kv_len - 1], [0], table,
+                        1.0, window).double().cpu()
+    want = attention_reference(q, [k], [v], [kv_len - 1], [0], 1.0, window)
+    torch.testing.assert_close(out, want, **tol(dtype))
+    group = hq // hkv
+    hit = torch.stack([v[target, h // group] for h in range(hq)]).double()
+    if where == "just_outside":
+        assert (out[0] - hit).abs().max() > 0.1            # the key is outside the window: not seen
+    else:
+        torch.testing.assert_close(out[0], hit, rtol=5e-2, atol=5e-2)
+
+
+# ----------------------------------------------------------------------------- sampling
+
+def sample_rows(logits, temps, top_ks, top_ps, seeds, counters):
+    from tokamak_b200.csrc import ops
+    n = logits.shape[0]
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops.sample(logits.to(DEV).contiguous(), torch.tensor(temps, dtype=torch.float32, device=DEV),
+               torch.tensor(top_ks, dtype=torch.int32, device=DEV),
+               torch.tensor(top_ps, dtype=torch.float32, device=DEV),
+               torch.tensor(seeds, dtype=torch.int64, device=DEV),
+               torch.tensor(counters, dtype=torch.int32, device=DEV), out)
+    return out.tolist()
+
+
+def test_sample_greedy_takes_the_first_maximum():
+    logits = torch.randn(6, 5003)
+    logits[2, 77] = 50.0; logits[2, 4000] = 50.0
+    logits[3, 5002] = 60.0
+    got = sample_rows(logits, [0.0] * 6, [0] * 6, [1.0] * 6, [0] * 6, [0] * 6)
+    assert got == logits.argmax(-1).tolist() and got[2] == 77 and got[3] == 5002
+
+
+def test_philox_matches_the_plain_generator():
+    from tokamak_b200.csrc import ops
+    for seed, counter in [(0, 0), (1, 5), (2 ** 40 + 17, 123456), (2 ** 62 - 1, 2 ** 31)]:
+        want = plain.philox4x32_10((counter, 0, 0, 0), (seed & 0xFFFFFFFF, seed >> 32))[0]
+        assert ops.philox_u32(seed, counter) == want
+
+
+@pytest.mark.parametrize("vocab", [317, 5003, 151936])
+def test_sample_draws_match_the_plain_sampler(vocab):
+    gen = torch.Generator().manual_seed(vocab)
+    n = 48
+    logits = torch.randn(n, vocab, generator=gen) * 3
+    temps = [0.8 if i % 3 else 1.3 for i in range(n)]
+    top_ks = [0, 50, 0, 7][0:4] * (n // 4)
+    top_ps = [1.0, 1.0, 0.9, 0.5] * (n // 4)
+    seeds = [1000 + i for i in range(n)]
+    counters = [i * 3 for i in range(n)]
+    got = sample_rows(logits, temps, top_ks, top_ps, seeds, counters)
+    miss = 0
+    for i in range(n):
+        want = plain.sample_token(logits[i], temps[i], top_ks[i], top_ps[i], seeds[i], counters[i])
+        probs = plain.filtered_probs(logits[i], temps[i], top_ks[i], top_ps[i])
+        assert probs[got[i]] > 0, f"row {i}: token {got[i]} is outside the kept set"
+        miss += got[i] != want
+    assert miss == 0
+
+
+def test_sample_support_sets_and_distribution():
+    """top-k and top-p keep the right sets; draws follow the probabilities."""
+    vocab = 64
+    logits = torch.linspace(4, -4, vocab)[None].repeat(4000, 1)
+    seeds = list(range(4000))
+    got_k = sample_rows(logits, [1.0] * 4000, [5] * 4000, [1.0] * 4000, seeds, [0] * 4000)
+    assert set(got_k) == {0, 1, 2, 3, 4}
+    probs = plain.filtered_probs(logits[0], 1.0, top_p=0.6)
+    got_p = sample_rows(logits, [1.0] * 4000, [0] * 4000, [0.6] * 4000, seeds, [1] * 4000)
+    assert set(got_p) == set(torch.nonzero(probs > 0).flatten().tolist())
+    got = torch.tensor(sample_rows(logits, [1.0] * 4000, [0] * 4000, [1.0] * 4000, seeds, [2] * 4000))
+    freq = torch.bincount(got, minlength=vocab).double() / 4000
+    want = torch.softmax(logits[0].double(), 0)
+    assert (freq - want).abs().max() < 0.03

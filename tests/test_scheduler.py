@@ -1,0 +1,157 @@
+"""Scheduler decisions, driven by hand without a model (after the reference's
+tests/unit/test_scheduler.py): sequences are advanced exactly as the engine would."""
+
+from __future__ import annotations
+
+import pytest
+
+from tokamak_b200.cache.manager import CacheManager, KVGroup, KVPagesNeed, OutOfPagesError
+from tokamak_b200.engine.scheduler import Scheduler
+from tokamak_b200.engine.sequence import FinishReason, Sequence, SequenceStatus
+from tokamak_b200.sampling import SamplingParams
+
+
+def make(num_pages=8, page=4, slots=4, batch=4, budget=64, chunk=None):
+    m = CacheManager([KVGroup(KVPagesNeed(1, 16), num_pages, page, ["l0"])], [], slots)
+    return m, Scheduler(m, batch, budget, chunk)
+
+
+def seq(i, n_prompt, max_new=8):
+    return Sequence(i, list(range(1, n_prompt + 1)), SamplingParams(temperature=0.0, max_new_tokens=max_new))
+
+
+def run_plan(manager, plan, token=9, finish_at=None):
+    """What the engine does after a step: advance the cache, append sampled tokens, free finished."""
+    for e in plan.entries:
+        manager.advance(e.seq.seq_id, e.count)
+        e.seq.num_computed = e.start + e.count
+    for e in plan.entries:
+        if e.samples:
+            done = e.seq.append_checked(token, eos_token_ids=(), max_total_tokens=10 ** 6)
+            if done:
+                manager.free(e.seq.seq_id)
+
+
+def describe(plan):
+    return [(e.seq.seq_id, e.start, e.count, e.samples) for e in plan.entries]
+
+
+def test_fcfs_admission_under_a_token_budget_and_chunk():
+    m, s = make(num_pages=32, budget=16, chunk=8)
+    a, b, c = seq(0, 20), seq(1, 5), seq(2, 3)
+    for x in (a, b, c):
+        s.add(x)
+    p = s.schedule()
+    assert describe(p) == [(0, 0, 8, False), (1, 0, 5, True), (2, 0, 3, True)]   # 16 tokens, in order
+    run_plan(m, p)
+    p = s.schedule()
+    # decodes first (one token each), then the running prefill's next portion
+    assert describe(p) == [(1, 5, 1, True), (2, 3, 1, True), (0, 8, 8, False)]
+    run_plan(m, p)
+    p = s.schedule()
+    assert describe(p) == [(1, 6, 1, True), (2, 4, 1, True), (0, 16, 4, True)]
+    run_plan(m, p)
+    assert a.num_output_tokens == 1 and b.num_output_tokens == 3
+
+
+def test_budget_smaller_than_the_decodes_serves_the_oldest():
+    m, s = make(num_pages=32, budget=2)
+    for i in range(3):
+        s.add(seq(i, 1))
+    run_plan(m, s.schedule())            # admits 0 and 1 (one token each)
+    p = s.schedule()
+    assert describe(p) == [(0, 1, 1, True), (1, 1, 1, True)]       # 2 waits: no budget left
+
+
+def test_batch_size_gate_and_finish_frees_pages():
+    m, s = make(batch=2)
+    a, b, c = seq(0, 4, max_new=1), seq(1, 4), seq(2, 4)
+    for x in (a, b, c):
+        s.add(x)
+    p = s.schedule()
+    assert [e.seq.seq_id for e in p.entries] == [0, 1]
+    run_plan(m, p)
+    assert a.is_finished and a.finish_reason is FinishReason.LENGTH
+    p = s.schedule()
+    assert [e.seq.seq_id for e in p.entries] == [1, 2]              # 2 takes the place of 0
+    assert m.kv_groups[0].table(0) == []
+
+
+def test_page_gate_makes_the_head_wait_and_nobody_overtakes():
+    m, s = make(num_pages=4, page=4)
+    a, b, c = seq(0, 12), seq(1, 8), seq(2, 2)
+    for x in (a, b, c):
+        s.add(x)
+    p = s.schedule()
+    assert [e.seq.seq_id for e in p.entries] == [0]                 # 1 does not fit; 2 must not overtake
+    run_plan(m, p)
+    assert [e.seq.seq_id for e in s.schedule().entries] == [0]
+
+
+def test_preemption_evicts_the_newest_and_requeues_at_the_front():
+    m, s = make(num_pages=4, page=4, budget=64)
+    a, b = seq(0, 7), seq(1, 7)
+    s.add(a); s.add(b)
+    run_plan(m, s.schedule())            # both prefilled: 2 pages each, pool full
+    waiting_late = seq(2, 2)
+    s.add(waiting_late)
+    p = s.schedule()                     # a and b decode token 8: fits in their last page
+    assert [e.seq.seq_id for e in p.entries] == [0, 1] and not p.preempted
+    run_plan(m, p)
+    p = s.schedule()                     # token 9 of a needs a third page: b is evicted
+    assert p.preempted == [b]
+    assert [e.seq.seq_id for e in p.entries] == [0]
+    assert b.status is SequenceStatus.WAITING and b.num_computed == 0 and b.num_output_tokens == 2
+    assert list(s.waiting) == [b, waiting_late]                     # ahead of what arrived later
+    assert m.kv_groups[0].table(1) == [] and not m.has(1)
+    run_plan(m, p)
+    while not a.is_finished:
+        run_plan(m, s.schedule())
+    p = s.schedule()                     # b resumes over prompt + generated, then samples the next
+    assert describe(p)[0] == (1, 0, 9, True)
+    assert b.num_preemptions == 1 and s.num_preemptions == 1
+
+
+def test_a_starving_sequence_may_evict_itself():
+    m, s = make(num_pages=2, page=4)
+    a = seq(0, 8, max_new=4)
+    s.add(a)
+    run_plan(m, s.schedule())
+    with pytest.raises(OutOfPagesError, match="pool can ever provide"):
+        s.schedule()                     # 9 tokens never fit 2 pages: evicts itself, then cannot re-admit
+
+
+def test_none_when_done_and_validation():
+    m, s = make()
+    assert s.schedule() is None and not s.has_unfinished()
+    a = seq(0, 3, max_new=1)
+    s.add(a)
+    assert s.has_unfinished()
+    run_plan(m, s.schedule())
+    assert s.schedule() is None
+    with pytest.raises(ValueError):
+        Scheduler(m, 0, 8)
+    with pytest.raises(ValueError):
+        Scheduler(m, 2, 0)
+    with pytest.raises(ValueError):
+        Scheduler(m, 99, 8)
+
+
+def test_stop_rules_in_the_reference_order():
+    a = Sequence(0, [1, 2], SamplingParams(max_new_tokens=3))
+    assert not a.append_checked(5, eos_token_ids=(7,), max_total_tokens=100)
+    assert a.append_checked(7, eos_token_ids=(7,), max_total_tokens=100)
+    assert a.finish_reason is FinishReason.STOP and a.output_token_ids == [5, 7]
+    b = Sequence(1, [1, 2], SamplingParams(max_new_tokens=3, ignore_eos=True))
+    b.append_checked(7, eos_token_ids=(7,), max_total_tokens=100)
+    b.append_checked(7, eos_token_ids=(7,), max_total_tokens=100)
+    assert b.append_checked(7, eos_token_ids=(7,), max_total_tokens=100)
+    assert b.finish_reason is FinishReason.LENGTH
+    c = Sequence(2, [1, 2, 3], SamplingParams(max_new_tokens=50))
+    assert c.append_checked(4, eos_token_ids=(), max_total_tokens=4)
+    assert c.finish_reason is FinishReason.LENGTH
+    assert c.tokens_from(2, 2) == [3, 4] and c.tokens_from(0, 4) == [1, 2, 3, 4]
+    with pytest.raises(RuntimeError):
+        c.append_output_token(1)
+    with pytest.raises(ValueError):
+        Sequence(3, [], SamplingParams())

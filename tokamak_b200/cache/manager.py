@@ -203,6 +203,7 @@ class CacheManager:
         self.max_slots = max_slots
         self._free_slots = list(range(max_slots - 1, -1, -1))
         self._slot_of: dict[Hashable, int] = {}
+        self._length: dict[Hashable, int] = {}     # positions of each live request already in the cache
         # slots whose state records must be cleared before their next use
         self.fresh_slots: set[int] = set()
         # (group index, slot) rows of the device tables that differ from the host's
@@ -230,8 +231,19 @@ class CacheManager:
             raise OutOfSlotsError(f"all {self.max_slots} request slots are taken")
         slot = self._free_slots.pop()
         self._slot_of[req_id] = slot
+        self._length[req_id] = 0
         self.fresh_slots.add(slot)
         return slot
+
+    def length(self, req_id: Hashable) -> int:
+        """Positions of the request that the cache holds (0 for an unknown request)."""
+        return self._length.get(req_id, 0)
+
+    def advance(self, req_id: Hashable, count: int) -> int:
+        """Record that ``count`` more positions were written; gives back pages a window has passed."""
+        self._length[req_id] += count
+        self.release_passed(req_id, self._length[req_id])
+        return self._length[req_id]
 
     # ---- pages ---------------------------------------------------------------------
     def fits(self, req_id: Hashable, num_tokens: int) -> bool:
@@ -260,16 +272,12 @@ class CacheManager:
     def free(self, req_id: Hashable) -> None:
         """Give back the pages and the slot of a request; unknown ids are ignored."""
         slot = self._slot_of.pop(req_id, None)
+        self._length.pop(req_id, None)
         for g in self.kv_groups:
             g.free(req_id)
         if slot is not None:
             self._free_slots.append(slot)
             self.fresh_slots.discard(slot)
-
-    def reset_pages(self, req_id: Hashable) -> None:
-        """Give back the pages of a request but keep its slot (preemption by recomputation)."""
-        for g in self.kv_groups:
-            g.free(req_id)
 
     def fits_empty_pool(self, num_tokens: int, max_portion: int) -> bool:
         """Whether one request of ``num_tokens`` tokens fits when it has the pools to itself."""

@@ -59,13 +59,16 @@ class EngineCore:
             (src/tokamak/engine/llm.py:157-163).
         max_slots: most requests that are live at a time.
         max_step_tokens: most tokens of one step.
+        tensors, raw_config: weights and configuration given directly instead of read from
+            the folder (random weights made on the device, for measurements).
+        config_overrides: keys that replace those of ``config.json`` (an engine-wide window).
     """
 
     def __init__(self, model: str | Path, *, dtype: str | torch.dtype = "bfloat16",
                  device: str | torch.device = "cuda", max_seq_len: int | None = None,
                  page_size: int = 16, pool_tokens: int | None = None, max_slots: int = 16,
                  max_step_tokens: int | None = None, tensors: dict | None = None,
-                 raw_config: dict | None = None):
+                 raw_config: dict | None = None, config_overrides: dict | None = None):
         self.device = require_cuda(device)
         self.dtype = resolve_dtype(dtype)
         torch.cuda.set_device(self.device)
@@ -74,6 +77,8 @@ class EngineCore:
             eos = read_eos_token_ids(model, raw_config)
         else:
             eos = None
+        if config_overrides:
+            raw_config = {**raw_config, **config_overrides}
         self.raw_config = raw_config
         self.architecture = architecture_of(raw_config)
         self.config = self.architecture.parse_config(raw_config, eos)

@@ -1,0 +1,258 @@
+"""The offline batch inference entry point: ``LLM(...).generate(prompts, SamplingParams)``.
+
+Names and meanings of the options follow the reference
+(src/tokamak/engine/llm.py:54-122, 265-286).  One ``generate`` call runs a step
+loop: the scheduler plans a mixed batch, the step function runs it and samples
+on the device, one copy brings the sampled tokens back, and finished requests
+give their pages back before the next plan.  Not thread-safe: one ``generate``
+call at a time.
+"""
+
+from __future__ import annotations
+
+import logging
+import time
+from pathlib import Path
+from typing import Sequence as AbcSequence
+
+import torch
+
+from ..sampling.params import SamplingParams
+from .core import EngineCore
+from .outputs import RequestOutput
+from .scheduler import Scheduler, StepPlan
+from .sequence import Sequence
+from .step import SamplingRow, StepEntry
+
+logger = logging.getLogger(__name__)
+
+
+def parse_attention_policy(spec: str) -> int | None:
+    """``"full"`` or ``"window:W"`` (src/tokamak/model/attention_policy.py:63-86): the window in
+    positions, or ``None``.  Sink positions (``streaming:W+S``) are not implemented."""
+    if spec == "full":
+        return None
+    kind, sep, arg = spec.partition(":")
+    if sep and kind == "window":
+        try:
+            window = int(arg)
+        except ValueError as err:
+            raise ValueError(f"Unknown attention_policy: {spec!r}") from err
+        if window < 1:
+            raise ValueError(f"window must be >= 1, got {window}")
+        return window
+    raise ValueError(f"Unknown attention_policy: {spec!r} (expected 'full' or 'window:W')")
+
+
+class LLM:
+    """Loads a model once and serves batch generation requests.
+
+    Args:
+        model: local checkpoint folder (``config.json`` + ``*.safetensors``).
+        device: ``"auto"``/``"cuda"`` or an explicit CUDA device; there is no CPU path.
+        dtype: ``"auto"``/``"bfloat16"`` or ``"float32"`` (the true 32-bit path).
+        max_seq_len: cap on one request's context (prompt + generation); defaults to
+            the model's trained maximum.
+        block_size: tokens per cache page.
+        kv_pool_tokens: token capacity of the page pool; defaults to ``max_seq_len`` and
+            must be at least that, so that any single request can finish alone.
+        max_batch_size: upper bound on concurrently running sequences.
+        max_num_batched_tokens: most tokens of one step (decode tokens plus prompt portions).
+        prefill_chunk: most tokens of one prompt portion; ``None`` leaves it to the budget.
+        attention_policy: ``"full"`` or ``"window:W"``, a window applied to every layer.
+    """
+
+    def __init__(self, model: str | Path, *, device: str | torch.device = "auto",
+                 dtype: str | torch.dtype = "auto", max_seq_len: int | None = None,
+                 block_size: int = 16, kv_pool_tokens: int | None = None, max_batch_size: int = 16,
+                 max_num_batched_tokens: int = 2048, prefill_chunk: int | None = None,
+                 attention_policy: str = "full", _core: EngineCore | None = None) -> None:
+        if block_size < 1:
+            raise ValueError(f"block_size must be >= 1, got {block_size}")
+        if max_batch_size < 1:
+            raise ValueError(f"max_batch_size must be >= 1, got {max_batch_size}")
+        window = parse_attention_policy(attention_policy)
+        if _core is not None:
+            self.core = _core
+        else:
+            overrides = None
+            if window is not None:
+                overrides = {"use_sliding_window": True, "sliding_window": window,
+                             "max_window_layers": 0}
+            self.core = EngineCore(model, dtype=dtype, device=device, max_seq_len=max_seq_len,
+                                   page_size=block_size, pool_tokens=kv_pool_tokens,
+                                   max_slots=max_batch_size,
+                                   max_step_tokens=max(max_num_batched_tokens, max_batch_size),
+                                   config_overrides=overrides)
+        self.model_path = Path(model)
+        self.model_config = self.core.config
+        self.max_seq_len = self.core.max_seq_len
+        self.device = self.core.device
+        self.dtype = self.core.dtype
+        self.block_size = block_size
+        self.max_batch_size = max_batch_size
+        self.max_num_batched_tokens = max(max_num_batched_tokens, 1)
+        self.prefill_chunk = prefill_chunk
+        self.cache_manager = self.core.manager
+        self.model = self.core.model
+        self._tokenizer = None
+        self.last_stats: dict = {}
+
+    # ---- tokenizer (text in and out only; the engine itself works on token ids) ---------
+    @property
+    def tokenizer(self):
+        if self._tokenizer is None:
+            names = ("tokenizer.json", "tokenizer_config.json", "vocab.json", "tokenizer.model")
+            if not any((self.model_path / n).is_file() for n in names):
+                raise RuntimeError(f"{self.model_path} has no tokenizer files; pass prompt_token_ids")
+            from transformers import AutoTokenizer
+            self._tokenizer = AutoTokenizer.from_pretrained(self.model_path)
+        return self._tokenizer
+
+    def _has_tokenizer(self) -> bool:
+        try:
+            return self.tokenizer is not None
+        except RuntimeError:
+            return False
+
+    # ---- generation -------------------------------------------------------------------------
+    def generate(self, prompts: str | AbcSequence[str] | None = None,
+                 sampling_params: SamplingParams | AbcSequence[SamplingParams] | None = None, *,
+                 prompt_token_ids: AbcSequence[AbcSequence[int]] | None = None,
+                 use_tqdm: bool = False) -> list[RequestOutput]:
+        """Generate a completion for each prompt; one ``RequestOutput`` per prompt, in input order.
+
+        Exactly one of ``prompts`` and ``prompt_token_ids`` is given.  ``sampling_params`` is one
+        object for all prompts, a sequence matching them one to one, or ``None`` for defaults.
+        """
+        prompt_texts, token_lists = self._resolve_prompts(prompts, prompt_token_ids)
+        params_list = self._broadcast_params(sampling_params, len(token_lists))
+
+        arrival = time.perf_counter()
+        sequences = []
+        for i, (ids, params) in enumerate(zip(token_lists, params_list, strict=True)):
+            seq = Sequence(seq_id=i, prompt_token_ids=list(ids), sampling_params=params)
+            seq.arrival_time = arrival
+            self._validate_fits(seq)
+            sequences.append(seq)
+
+        scheduler = Scheduler(self.cache_manager, self.max_batch_size, self.max_num_batched_tokens,
+                              self.prefill_chunk)
+        for seq in sequences:
+            scheduler.add(seq)
+
+        bar = None
+        if use_tqdm:
+            from tqdm.auto import tqdm
+            bar = tqdm(total=len(sequences), desc="Generating")
+        stats = {"steps": 0, "tokens_run": 0, "prefill_tokens": 0, "decode_tokens": 0,
+                 "mixed_steps": 0}
+        try:
+            while scheduler.has_unfinished():
+                plan = scheduler.schedule()
+                if plan is None:
+                    raise RuntimeError("scheduler returned no work but is unfinished")
+                done = self._step(plan)
+                stats["steps"] += 1
+                stats["tokens_run"] += plan.num_tokens
+                n_dec = sum(1 for e in plan.entries if e.count == 1 and e.start > 0)
+                stats["decode_tokens"] += n_dec
+                stats["prefill_tokens"] += plan.num_tokens - n_dec
+                stats["mixed_steps"] += int(0 < n_dec < len(plan.entries))
+                if bar is not None:
+                    bar.update(done)
+        finally:
+            for seq in sequences:
+                self.cache_manager.free(seq.seq_id)
+            if bar is not None:
+                bar.close()
+        stats["preemptions"] = scheduler.num_preemptions
+        self.last_stats = stats
+        return [self._to_output(seq, prompt_texts[seq.seq_id] if prompt_texts else None)
+                for seq in sequences]
+
+    def _step(self, plan: StepPlan) -> int:
+        """Run one planned step, append the sampled tokens and free what finished."""
+        entries, rows, samplers = [], [], []
+        for e in plan.entries:
+            toks = e.seq.tokens_from(e.start, e.count)
+            entries.append(StepEntry(e.seq.seq_id, toks, [e.count - 1] if e.samples else []))
+            if e.samples:
+                p = e.seq.sampling_params
+                rows.append(SamplingRow(p.temperature, p.top_k, p.top_p, e.seq.seed,
+                                        e.seq.num_output_tokens))
+                samplers.append(e.seq)
+        tokens = self.core.step.run_and_sample(entries, rows)
+        now = time.perf_counter()
+        for e in plan.entries:
+            e.seq.num_computed = e.start + e.count
+        finished = 0
+        for seq, token in zip(samplers, tokens):
+            done = seq.append_checked(int(token), eos_token_ids=self.model_config.eos_token_ids,
+                                      max_total_tokens=self._max_total_tokens(seq))
+            if seq.first_token_time is None:
+                seq.first_token_time = now
+            if done:
+                seq.finish_time = now
+                self.cache_manager.free(seq.seq_id)
+                finished += 1
+        return finished
+
+    # ---- helpers ------------------------------------------------------------------------------
+    def _max_total_tokens(self, seq: Sequence) -> int:
+        """A request's context budget (src/tokamak/engine/llm.py:483-485)."""
+        return min(self.max_seq_len, seq.num_prompt_tokens + seq.sampling_params.max_new_tokens)
+
+    def _validate_fits(self, seq: Sequence) -> None:
+        if seq.num_prompt_tokens >= self.max_seq_len:
+            raise ValueError(f"Prompt of {seq.num_prompt_tokens} tokens does not fit in "
+                             f"max_seq_len={self.max_seq_len} (room for generation is required)")
+        vocab = self.model_config.vocab_size
+        bad = [t for t in seq.prompt_token_ids if not 0 <= t < vocab]
+        if bad:
+            raise ValueError(f"prompt token id {bad[0]} is outside the vocabulary of {vocab}")
+        total = self._max_total_tokens(seq)
+        for g in self.cache_manager.kv_groups:
+            if g.pages_for(total) > g.num_pages:
+                raise ValueError(f"Request needs {g.pages_for(total)} KV blocks but the pool has "
+                                 f"{g.num_pages}; raise kv_pool_tokens")
+
+    def _resolve_prompts(self, prompts, prompt_token_ids):
+        if (prompts is None) == (prompt_token_ids is None):
+            raise ValueError("provide exactly one of `prompts` or `prompt_token_ids`")
+        if prompt_token_ids is not None:
+            return None, [list(ids) for ids in prompt_token_ids]
+        if isinstance(prompts, str):
+            prompts = [prompts]
+        texts = list(prompts)
+        return texts, [self.tokenizer.encode(text) for text in texts]
+
+    def _to_output(self, seq: Sequence, prompt_text: str | None) -> RequestOutput:
+        if seq.finish_reason is None:
+            raise RuntimeError(f"Sequence {seq.seq_id} completed without a finish reason")
+        ttft = latency = None
+        if seq.arrival_time is not None:
+            if seq.first_token_time is not None:
+                ttft = seq.first_token_time - seq.arrival_time
+            if seq.finish_time is not None:
+                latency = seq.finish_time - seq.arrival_time
+        text = ""
+        if self._has_tokenizer():
+            text = self.tokenizer.decode(seq.output_token_ids, skip_special_tokens=True)
+            if prompt_text is None:
+                prompt_text = self.tokenizer.decode(seq.prompt_token_ids, skip_special_tokens=True)
+        return RequestOutput(request_id=seq.seq_id, prompt=prompt_text,
+                             prompt_token_ids=seq.prompt_token_ids, output_text=text,
+                             output_token_ids=seq.output_token_ids, finish_reason=seq.finish_reason,
+                             ttft_s=ttft, latency_s=latency, num_preemptions=seq.num_preemptions)
+
+    @staticmethod
+    def _broadcast_params(sampling_params, num_prompts: int) -> list[SamplingParams]:
+        if sampling_params is None:
+            return [SamplingParams()] * num_prompts
+        if isinstance(sampling_params, SamplingParams):
+            return [sampling_params] * num_prompts
+        params_list = list(sampling_params)
+        if len(params_list) != num_prompts:
+            raise ValueError(f"Got {len(params_list)} SamplingParams for {num_prompts} prompts")
+        return params_list

@@ -1,0 +1,171 @@
+"""Iteration-level scheduler: admits requests, cuts prompts into portions, decodes, frees.
+
+Policy of the reference (src/tokamak/engine/scheduler.py:1-188): first come first
+served, requests join and leave at token granularity, and when the page pool
+cannot cover a running sequence's next tokens the newest running sequence is
+preempted: its pages and slot are given back and it returns to the *front* of
+the waiting queue with its generated tokens kept, to be recomputed later.
+
+What is added here is the token budget.  The reference computes a whole prompt
+in one step and lets the decodes wait meanwhile (scheduler.py:114-117); this
+scheduler plans one mixed batch per step: every running sequence that only needs
+its next token gets one token, and what is left of ``max_num_batched_tokens``
+goes to prompt portions, running prefills first, then new admissions, each
+portion at most ``prefill_chunk`` tokens.
+
+When pages run out:
+  * a waiting request is admitted only if the pages for all its current tokens
+    are free now (scheduler.py:144-148); they are reserved at admission;
+  * a running sequence that needs a page which is not free preempts the newest
+    running sequence (possibly itself) and tries again (scheduler.py:162-188);
+  * a request alone in an empty pool that still does not fit is an error, which
+    the engine rules out at submission.
+"""
+
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+
+from ..cache.manager import CacheManager, OutOfPagesError
+from .sequence import Sequence, SequenceStatus
+
+
+@dataclass
+class PlannedEntry:
+    """Tokens ``[start, start + count)`` of a sequence run this step; ``samples`` says
+    that they end at its last known token, so the step samples the next one."""
+
+    seq: Sequence
+    start: int
+    count: int
+    samples: bool
+
+
+@dataclass
+class StepPlan:
+    entries: list[PlannedEntry]
+    preempted: list[Sequence] = field(default_factory=list)
+
+    @property
+    def num_tokens(self) -> int:
+        return sum(e.count for e in self.entries)
+
+
+class Scheduler:
+    """FCFS scheduler with a per-step token budget and preemption by recomputation.
+
+    Args:
+        manager: the cache manager to reserve pages and slots from.
+        max_batch_size: most sequences running at a time.
+        max_num_batched_tokens: most tokens of one step.
+        prefill_chunk: most tokens of one sequence's prompt portion in a step
+            (``None``: limited by the budget only).
+    """
+
+    def __init__(self, manager: CacheManager, max_batch_size: int, max_num_batched_tokens: int,
+                 prefill_chunk: int | None = None):
+        if max_batch_size < 1:
+            raise ValueError(f"max_batch_size must be >= 1, got {max_batch_size}")
+        if max_num_batched_tokens < 1:
+            raise ValueError(f"max_num_batched_tokens must be >= 1, got {max_num_batched_tokens}")
+        if prefill_chunk is not None and prefill_chunk < 1:
+            raise ValueError(f"prefill_chunk must be >= 1, got {prefill_chunk}")
+        if max_batch_size > manager.max_slots:
+            raise ValueError(f"max_batch_size ({max_batch_size}) exceeds the cache's request "
+                             f"slots ({manager.max_slots})")
+        self._manager = manager
+        self._max_batch_size = max_batch_size
+        self._budget = max_num_batched_tokens
+        self._chunk = prefill_chunk
+        self.waiting: deque[Sequence] = deque()
+        self.running: list[Sequence] = []
+        self.num_preemptions = 0
+
+    def add(self, seq: Sequence) -> None:
+        seq.status = SequenceStatus.WAITING
+        self.waiting.append(seq)
+
+    def has_unfinished(self) -> bool:
+        return bool(self.waiting) or any(not s.is_finished for s in self.running)
+
+    # ------------------------------------------------------------------------------
+    def schedule(self) -> StepPlan | None:
+        """Plan the next step; ``None`` when everything is finished."""
+        self.running = [s for s in self.running if not s.is_finished]
+        preempted: list[Sequence] = []
+        while True:
+            entries: list[PlannedEntry] = []
+            budget = self._budget
+
+            # 1. running sequences: single next tokens first, then prompt portions
+            decoding = [s for s in self.running if s.num_tokens - s.num_computed == 1]
+            prefilling = [s for s in self.running if s.num_tokens - s.num_computed > 1]
+            for seq in decoding + prefilling:
+                if seq not in self.running:
+                    continue    # preempted while an earlier sequence was served
+                if budget == 0:
+                    break
+                want = seq.num_tokens - seq.num_computed
+                count = min(want, budget, self._chunk or want)
+                if self._reserve(seq, seq.num_computed + count, preempted, entries):
+                    entries.append(PlannedEntry(seq, seq.num_computed, count,
+                                                samples=seq.num_computed + count == seq.num_tokens))
+                    budget -= count
+            # sequences that were preempted after they had been planned drop out
+            entries = [e for e in entries if e.seq in self.running]
+
+            # 2. admissions, strictly in arrival order
+            while self.waiting and len(self.running) < self._max_batch_size and budget > 0:
+                seq = self.waiting[0]
+                if self._manager.num_free_slots == 0 or not self._fits_new(seq):
+                    if not self.running:
+                        raise OutOfPagesError(
+                            f"sequence {seq.seq_id} needs more pages than the pool can ever provide")
+                    break   # pages are busy; decode until some come free
+                self.waiting.popleft()
+                self._manager.admit(seq.seq_id)
+                self._manager.grow(seq.seq_id, seq.num_tokens)
+                seq.status = SequenceStatus.RUNNING
+                seq.num_computed = 0
+                self.running.append(seq)
+                count = min(seq.num_tokens, budget, self._chunk or seq.num_tokens)
+                entries.append(PlannedEntry(seq, 0, count, samples=count == seq.num_tokens))
+                budget -= count
+
+            if entries:
+                return StepPlan(entries, preempted)
+            if self.running:
+                # unreachable: a running sequence is either planned or preempted above
+                raise RuntimeError("scheduler stalled with running sequences")
+            if self.waiting:
+                continue
+            return None
+
+    # ------------------------------------------------------------------------------
+    def _fits_new(self, seq: Sequence) -> bool:
+        return all(g.pages_for(seq.num_tokens) <= g.num_free for g in self._manager.kv_groups)
+
+    def _reserve(self, seq: Sequence, num_tokens: int, preempted: list[Sequence],
+                 entries: list[PlannedEntry]) -> bool:
+        """Pages for ``num_tokens`` positions of a running sequence, preempting on demand."""
+        while True:
+            try:
+                self._manager.grow(seq.seq_id, num_tokens)
+                return True
+            except OutOfPagesError:
+                victim = self.running[-1]   # newest arrival = lowest priority
+                self._preempt(victim)
+                preempted.append(victim)
+                if victim is seq:
+                    return False
+
+    def _preempt(self, victim: Sequence) -> None:
+        """Evict by recomputation: give back pages and slot, requeue at the front."""
+        self._manager.free(victim.seq_id)
+        self.running.remove(victim)
+        victim.status = SequenceStatus.WAITING
+        victim.num_computed = 0
+        victim.num_preemptions += 1
+        self.num_preemptions += 1
+        self.waiting.appendleft(victim)

@@ -122,21 +122,18 @@ class StepFunction:
         self.max_step_tokens = max_step_tokens
         self.max_seq_len = max_seq_len
         self.buffers = StepBuffers(self.device, max_step_tokens, self.manager.max_slots)
-        self.lengths: dict[Hashable, int] = {}
         self.steps_run = 0
         self.kernel_launches = 0
 
     # ---- request lifetime ------------------------------------------------------------
     def admit(self, req_id: Hashable) -> None:
         self.manager.admit(req_id)
-        self.lengths[req_id] = 0
 
     def free(self, req_id: Hashable) -> None:
         self.manager.free(req_id)
-        self.lengths.pop(req_id, None)
 
     def length(self, req_id: Hashable) -> int:
-        return self.lengths.get(req_id, 0)
+        return self.manager.length(req_id)
 
     # ---- the step ----------------------------------------------------------------------
     def build(self, entries: Sequence[StepEntry],
@@ -162,7 +159,7 @@ class StepFunction:
             n = len(e.tokens)
             if n < 1:
                 raise ValueError(f"request {e.req_id!r} brings no tokens")
-            start = self.lengths[e.req_id]
+            start = self.manager.length(e.req_id)
             if start + n > self.max_seq_len:
                 raise ValueError(f"request {e.req_id!r} would reach {start + n} tokens, "
                                  f"beyond max_seq_len={self.max_seq_len}")
@@ -214,8 +211,7 @@ class StepFunction:
     def finish(self, entries: Sequence[StepEntry]) -> None:
         """Advance the lengths and give back the pages that a window has passed."""
         for e in entries:
-            self.lengths[e.req_id] += len(e.tokens)
-            self.manager.release_passed(e.req_id, self.lengths[e.req_id])
+            self.manager.advance(e.req_id, len(e.tokens))
         self.steps_run += 1
 
     @torch.inference_mode()

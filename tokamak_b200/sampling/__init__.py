@@ -1,0 +1,3 @@
+from .params import SamplingParams
+
+__all__ = ["SamplingParams"]
