@@ -1,0 +1,308 @@
+"""Headline measurement: decode tokens per second of the Qwen3-8B layer sizes on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
+
+A *step* is one decode step: every live request advances by one token (model
+forward over the paged cache, greedy sampling on the device, one copy of the
+tokens back).  The default run has the layer sizes of Qwen3-8B with seeded
+random bfloat16 weights, a batch of 8 and a context that ends at 4,096 tokens.
+It prints ONE JSON line:
+
+  value      decoded tokens per second at the default batch, timed with CUDA events
+  e2e        the same through ``LLM.generate`` (host token ids in, host token ids out)
+  prefill    one 2,048-token prompt in one step: tokens/s, ms, fraction of the bf16 peak
+  roofline   bytes the decode step must read (weights once + live cache) / its time
+  points     decode tokens per second at batch 1 and 64
+  clocks     SM clocks and throttle reasons sampled during the timed regions
+
+The engine runs on one GPU only: for ``--gpus N`` with N > 1 it says so and exits with 2.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+QWEN3_8B = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "num_hidden_layers": 36, "hidden_size": 4096, "num_attention_heads": 32,
+    "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 12288, "vocab_size": 151936,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+    "max_position_embeddings": 40960,
+}
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def load_peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            raw = json.loads(path.read_text())
+            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]),
+                    "source": "measured"}
+        except (ValueError, KeyError, TypeError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """nvidia-smi in the background, sampling clocks and throttle reasons (reading only)."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0):
+        self.index = index
+        self.proc = None
+        self.file = None
+
+    def start(self) -> None:
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.file.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[3:7]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        self.file.close()
+        os.unlink(self.file.name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def weight_bytes(core) -> int:
+    """Bytes of every weight a decode step reads once (the embedding table is read by row only)."""
+    import torch
+    m = core.model
+    total = 0
+    for blk in m.blocks.values():
+        for t in (blk.mixer.w_qkv, blk.mixer.w_o, blk.feed_forward.w_gate_up, blk.feed_forward.w_down):
+            total += t.numel() * t.element_size()
+    total += m.head.weight.numel() * m.head.weight.element_size()
+    return total
+
+
+def step_flops(cfg, n_layers: int, tokens: int, ctx_start: int = 0) -> float:
+    """Multiply-adds of a step of ``tokens`` new tokens of one request, counted as 2 flops."""
+    h, d = cfg["hidden_size"], cfg["head_dim"]
+    hq, hkv, inter = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["intermediate_size"]
+    per_layer = 2.0 * tokens * (h * (hq + 2 * hkv) * d + hq * d * h + 3 * h * inter)
+    # causal attention: token i sees ctx_start + i + 1 keys; QK^T and PV
+    keys = tokens * ctx_start + tokens * (tokens + 1) / 2
+    per_layer += 2.0 * 2.0 * keys * hq * d
+    return n_layers * per_layer + 2.0 * 1 * h * cfg["vocab_size"]
+
+
+def fill_context(core, req_ids, length: int, vocab: int, seed: int) -> None:
+    """Put ``length`` random tokens of every request into the cache, 2,048 tokens a step."""
+    import torch
+    from tokamak_b200.engine.step import StepEntry
+    gen = torch.Generator().manual_seed(seed)
+    for rid in req_ids:
+        toks = torch.randint(0, vocab, (length,), generator=gen).tolist()
+        for s in range(0, length, PREFILL_TOKENS):
+            core.step.run([StepEntry(rid, toks[s:s + PREFILL_TOKENS], [])], check=False)
+    core.step.check_errors()
+
+
+def time_decode(core, batch: int, steps: int, warmup: int, ctx_end: int, vocab: int):
+    """Device time of ``steps`` decode steps of ``batch`` requests whose context ends at ``ctx_end``."""
+    import torch
+    from tokamak_b200.csrc import ops
+    from tokamak_b200.engine.step import SamplingRow, StepEntry
+    req_ids = [f"b{batch}_{i}" for i in range(batch)]
+    start_len = ctx_end - (steps + warmup)
+    fill_context(core, req_ids, start_len, vocab, seed=batch)
+    greedy = [SamplingRow(0.0, 0, 1.0, 0, 0) for _ in range(batch)]
+    tokens = [1 + i for i in range(batch)]
+
+    def one_step():
+        nonlocal tokens
+        tokens = core.step.run_and_sample([StepEntry(r, [t], [0]) for r, t in zip(req_ids, tokens)], greedy)
+
+    for _ in range(warmup):
+        one_step()
+    torch.cuda.synchronize()
+    launches0 = ops.LAUNCHES + core.step.graph_launches
+    t_host = time.perf_counter()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(steps):
+        one_step()
+    end.record()
+    torch.cuda.synchronize()
+    ms = begin.elapsed_time(end)
+    wall = time.perf_counter() - t_host
+    launches = ops.LAUNCHES + core.step.graph_launches - launches0
+    kv_bytes = batch * (ctx_end - steps / 2.0) * core.cache.bytes_per_token()
+    for r in req_ids:
+        core.step.free(r)
+    return {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3), "launches": launches,
+            "kv_bytes": kv_bytes, "wall_ms_per_step": wall * 1e3 / steps}
+
+
+def time_prefill(core, vocab: int, repeats: int = 3):
+    import torch
+    from tokamak_b200.engine.step import StepEntry
+    gen = torch.Generator().manual_seed(99)
+    times = []
+    for i in range(repeats + 1):
+        toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
+        rid = f"prefill{i}"
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        core.step.run([StepEntry(rid, toks, [PREFILL_TOKENS - 1])], check=False)
+        end.record()
+        torch.cuda.synchronize()
+        core.step.free(rid)
+        if i > 0:
+            times.append(begin.elapsed_time(end))
+    core.step.check_errors()
+    return statistics.median(times)
+
+
+def time_e2e(core, batch: int, steps: int, warmup: int, ctx_end: int, vocab: int):
+    """Decode tokens per second through ``LLM.generate``: host token ids in and out."""
+    import torch
+    from tokamak_b200 import LLM, SamplingParams
+    llm = LLM("<random>", _core=core, max_batch_size=batch, max_num_batched_tokens=PREFILL_TOKENS,
+              block_size=core.page_size)
+    gen = torch.Generator().manual_seed(7)
+    new_tokens = steps + warmup + 1
+    prompt_len = ctx_end - new_tokens
+    prompts = [torch.randint(0, vocab, (prompt_len,), generator=gen).tolist() for _ in range(batch)]
+    params = SamplingParams(temperature=0.0, max_new_tokens=new_tokens, ignore_eos=True)
+    outs = llm.generate(prompt_token_ids=prompts, sampling_params=params)
+    assert all(len(o.output_token_ids) == new_tokens for o in outs)
+    times = llm.last_stats["decode_step_times"]
+    full = [t for t in times][-steps:]            # the last K decode steps, all at full batch
+    tok_s = batch * len(full) / sum(full)
+    h2d = 4 * (8 * batch + 5 * batch)             # step description + sampling rows, int32 words
+    d2h = 4 * (4 + batch)
+    return {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "ms_per_step": 1e3 * sum(full) / len(full)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the 36 of Qwen3-8B")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "pip install --no-index of WeichunK/tokamak fails offline: its build backend "
+                          "hatchling is neither installed nor in the wheelhouse"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(3, args.warmup)
+    steps = max(1, args.steps)
+
+    import torch
+    from tokamak_b200.engine.core import random_core
+
+    raw = dict(QWEN3_8B)
+    n_layers = args.layers or raw["num_hidden_layers"]
+    raw["num_hidden_layers"] = n_layers
+    vocab = raw["vocab_size"]
+    peaks = load_peaks()
+    max_batch = 64 if not args.skip_points else max(args.batch, 1)
+    core = random_core(raw, seed=0, std=0.02, dtype="bfloat16", max_seq_len=CONTEXT, page_size=16,
+                       pool_tokens=max_batch * CONTEXT, max_slots=max_batch,
+                       max_step_tokens=PREFILL_TOKENS)
+    wbytes = weight_bytes(core)
+
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    main_run = time_decode(core, args.batch, steps, warmup, CONTEXT, vocab)
+    prefill_ms = time_prefill(core, vocab)
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            points[f"decode_b{b}"] = round(time_decode(core, b, steps, warmup, CONTEXT, vocab)["tok_s"], 1)
+    e2e = time_e2e(core, args.batch, steps, warmup, CONTEXT, vocab)
+    clocks = sampler.stop()
+
+    step_bytes = wbytes + main_run["kv_bytes"]
+    achieved = step_bytes / (main_run["ms_per_step"] / 1e3) / 1e9
+    pf_flops = step_flops(raw, n_layers, PREFILL_TOKENS)
+    pf_frac = pf_flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12)
+    line = {
+        "metric": "decode tok/s at batch 8 (Qwen3-8B layer sizes, context 4096)",
+        "value": round(main_run["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(main_run["ms_per_step"], 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded random weights N(0, 0.02), uniform random token ids",
+        "config": {
+            "model": "Qwen3-8B layer sizes", "layers": n_layers, "layers_of_model": 36,
+            "hidden": raw["hidden_size"], "q_heads": raw["num_attention_heads"],
+            "kv_heads": raw["num_key_value_heads"], "head_dim": raw["head_dim"],
+            "intermediate": raw["intermediate_size"], "vocab": vocab, "rope_theta": raw["rope_theta"],
+            "rms_norm_eps": raw["rms_norm_eps"], "tied_head": False, "global_batch": args.batch,
+            "seq_len": CONTEXT, "prefill_tokens": PREFILL_TOKENS, "kv_block": 16,
+            "parallelism": "single GPU", "l2": "inputs larger than L2 (weights read every step)",
+            "peaks": peaks["source"],
+        },
+        "e2e": {k: (round(v, 2) if isinstance(v, float) else v) for k, v in e2e.items()},
+        "gpu_launches": main_run["launches"],
+        "prefill": {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(prefill_ms, 3), "frac": round(pf_frac, 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clocks,
+        "host_ms_per_step": round(main_run["wall_ms_per_step"], 4),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -22,9 +22,14 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+LAUNCHES = 0     # kernels of this library launched (or recorded into a graph) so far
+
+
 def _check(code: int, what: str) -> None:
+    global LAUNCHES
     if code != 0:
         raise KernelError(f"{what}: CUDA error {code}")
+    LAUNCHES += 1
 
 
 def _ptr(t: torch.Tensor | None) -> int | None:

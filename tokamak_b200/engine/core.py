@@ -107,3 +107,26 @@ class EngineCore:
         logger.info("Loaded %s (%s) on %s as %s: %d pages of %d tokens per layer group",
                     model, self.config.architecture, self.device, self.dtype,
                     kv_groups[0].num_pages if kv_groups else 0, page_size)
+
+
+def random_core(raw_config: dict, *, seed: int = 0, std: float = 0.02, norm_std: float = 0.1,
+                dtype: str | torch.dtype = "bfloat16", device: str | torch.device = "cuda",
+                **kwargs) -> EngineCore:
+    """An engine with seeded random weights made directly on the device (no folder is written).
+
+    For measurements at sizes whose checkpoint would take minutes to write and read.  The
+    values come from the device's generator, so they differ from a folder written with the
+    same seed by :func:`tokamak_b200.weights.write_random_model`.
+    """
+    from ..weights.random_init import random_tensors
+
+    dev = require_cuda(device)
+    dt = resolve_dtype(dtype)
+    arch = architecture_of(raw_config)
+    spec = arch.model_spec(arch.parse_config(raw_config))
+    expected = DecoderModel.expected_tensors(spec)
+    tensors = random_tensors(expected, seed, std, norm_std, dt, device=dev)
+    for name, req in expected.items():
+        if req.role == "vector" and name in tensors:
+            tensors[name] = tensors[name].float()
+    return EngineCore("<random>", dtype=dt, device=dev, tensors=tensors, raw_config=raw_config, **kwargs)

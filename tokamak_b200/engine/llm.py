@@ -146,9 +146,11 @@ class LLM:
             from tqdm.auto import tqdm
             bar = tqdm(total=len(sequences), desc="Generating")
         stats = {"steps": 0, "tokens_run": 0, "prefill_tokens": 0, "decode_tokens": 0,
-                 "mixed_steps": 0}
+                 "mixed_steps": 0, "decode_steps": 0, "decode_step_time_s": 0.0,
+                 "decode_step_tokens": 0, "decode_step_times": []}
         try:
             while scheduler.has_unfinished():
+                t_step = time.perf_counter()
                 plan = scheduler.schedule()
                 if plan is None:
                     raise RuntimeError("scheduler returned no work but is unfinished")
@@ -159,6 +161,13 @@ class LLM:
                 stats["decode_tokens"] += n_dec
                 stats["prefill_tokens"] += plan.num_tokens - n_dec
                 stats["mixed_steps"] += int(0 < n_dec < len(plan.entries))
+                if n_dec == len(plan.entries):
+                    # a step of single next tokens only, timed from planning to tokens on the host
+                    dt = time.perf_counter() - t_step
+                    stats["decode_steps"] += 1
+                    stats["decode_step_time_s"] += dt
+                    stats["decode_step_tokens"] += n_dec
+                    stats["decode_step_times"].append(dt)
                 if bar is not None:
                     bar.update(done)
         finally:

@@ -83,12 +83,20 @@ class StepBatch:
 
 
 class StepBuffers:
-    """Pinned host staging and its device twin for the integers that describe a step."""
+    """Pinned host staging and its device twin for the integers that describe a step.
+
+    The host side is a small ring: a copy to the device is asynchronous, so a staging
+    buffer is written again only after the copy that read it has completed.
+    """
+
+    RING = 3
 
     def __init__(self, device: torch.device, max_tokens: int, max_reqs: int):
         self.device = device
         self.capacity = 6 * max_reqs + 3 * max_tokens + 4 * max_tokens + 64
-        self.host = torch.zeros(self.capacity, dtype=torch.int32).pin_memory()
+        self.hosts = [torch.zeros(self.capacity, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+        self.events: list = [None] * self.RING
+        self.turn = 0
         self.dev = torch.zeros(self.capacity, dtype=torch.int32, device=device)
         # error word and sampled tokens travel back together
         self.result = torch.zeros(4 + max_tokens, dtype=torch.int32, device=device)
@@ -99,7 +107,12 @@ class StepBuffers:
         total = sum(a.size for a in arrays)
         if total > self.capacity:
             raise ValueError(f"step needs {total} staging words, capacity is {self.capacity}")
-        host_np = self.host.numpy()
+        i = self.turn
+        self.turn = (i + 1) % self.RING
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        host = self.hosts[i]
+        host_np = host.numpy()
         views = []
         off = 0
         for a in arrays:
@@ -107,7 +120,10 @@ class StepBuffers:
             views.append(self.dev[off:off + a.size])
             off += a.size
         if total:
-            self.dev[:total].copy_(self.host[:total], non_blocking=True)
+            self.dev[:total].copy_(host[:total], non_blocking=True)
+            if self.events[i] is None:
+                self.events[i] = torch.cuda.Event()
+            self.events[i].record()
         return views
 
 
@@ -123,7 +139,7 @@ class StepFunction:
         self.max_seq_len = max_seq_len
         self.buffers = StepBuffers(self.device, max_step_tokens, self.manager.max_slots)
         self.steps_run = 0
-        self.kernel_launches = 0
+        self.graph_launches = 0      # kernels replayed from CUDA graphs (not counted by ops.LAUNCHES)
 
     # ---- request lifetime ------------------------------------------------------------
     def admit(self, req_id: Hashable) -> None:
