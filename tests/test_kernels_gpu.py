@@ -346,3 +346,83 @@ def test_sample_support_sets_and_distribution():
     freq = torch.bincount(got, minlength=vocab).double() / 4000
     want = torch.softmax(logits[0].double(), 0)
     assert (freq - want).abs().max() < 0.03
+
+
+# ----------------------------------------------------------------------------- split-K decode kernel
+
+def run_decode(q, kc, vc, items, positions, tok_req, table, scale, window, n_splits):
+    from tokamak_b200.csrc import ops
+    err = err_word()
+    out = torch.full_like(q, float("nan"))
+    ops.attention_decode(q, out, kc, vc, torch.tensor(items, dtype=torch.int32, device=DEV),
+                         torch.tensor(positions, dtype=torch.int32, device=DEV),
+                         torch.tensor(tok_req, dtype=torch.int32, device=DEV),
+                         torch.arange(table.shape[0], dtype=torch.int32, device=DEV), table.to(DEV), err,
+                         scale=scale, window=window, n_splits=n_splits)
+    assert err.tolist()[0] == 0
+    return out
+
+
+@pytest.mark.parametrize("n_splits", [1, 3, 8, 33])
+@pytest.mark.parametrize("hq,hkv,d,page,window", [(8, 2, 128, 16, None), (32, 8, 128, 16, None),
+                                                    (6, 1, 64, 16, None), (16, 1, 64, 32, None),
+                                                    (4, 4, 128, 16, 24), (14, 2, 64, 16, 7),
+                                                    (5, 5, 128, 64, 100)])
+def test_attention_decode_split_k(hq, hkv, d, page, window, n_splits):
+    """Single next tokens at many lengths over shuffled pages; the last page of every request
+    is only partly filled and everything unwritten is NaN, so a key beyond the end, or a page
+    that the request does not own, shows as NaN in the result."""
+    kv_lens = [1, 15, 16, 17, 700, 2041, 33]
+    max_pages = max(-(-l // page) for l in kv_lens)
+    num_pages = len(kv_lens) * max_pages + 5
+    table = make_tables(len(kv_lens), max_pages, num_pages, seed=hq + d)
+    gen = torch.Generator().manual_seed(hq * 7 + d)
+    k_all = [torch.randn(l, hkv, d, generator=gen).bfloat16().float() for l in kv_lens]
+    v_all = [torch.randn(l, hkv, d, generator=gen).bfloat16().float() for l in kv_lens]
+    kc, vc = fill_cache(k_all, v_all, table, num_pages, page, torch.bfloat16)
+    # the decoded tokens sit among other tokens of the batch: rows 1, 3, 5, ... of q
+    n = 2 * len(kv_lens)
+    items = [2 * r + 1 for r in range(len(kv_lens))]
+    positions = [0] * n
+    tok_req = [0] * n
+    for r, l in enumerate(kv_lens):
+        positions[2 * r + 1] = l - 1
+        tok_req[2 * r + 1] = r
+    q = torch.randn(n, hq, d, generator=gen).bfloat16()
+    scale = d ** -0.5
+    out = run_decode(q.to(DEV), kc, vc, items, positions, tok_req, table, scale, window, n_splits)
+    want = attention_reference(q.float()[items], k_all, v_all, [positions[i] for i in items],
+                               [tok_req[i] for i in items], scale, window)
+    torch.testing.assert_close(out[items].double().cpu(), want, **tol(torch.bfloat16))
+    assert torch.isnan(out[[i - 1 for i in items]].float()).all()       # other rows are not touched
+
+
+@pytest.mark.parametrize("where", ["first", "far", "page_edge", "last", "window_edge", "just_outside"])
+def test_attention_decode_finds_the_one_key_that_matters(where):
+    hq, hkv, d, page = 8, 2, 128, 16
+    kv_len, window = 1500, None
+    target = {"first": 0, "far": 123, "page_edge": 16 * 40 - 1, "last": kv_len - 1,
+              "window_edge": kv_len - 200, "just_outside": kv_len - 201}[where]
+    if where in ("window_edge", "just_outside"):
+        window = 200
+    gen = torch.Generator().manual_seed(11)
+    k = torch.randn(kv_len, hkv, d, generator=gen) * 0.1
+    v = torch.randn(kv_len, hkv, d, generator=gen)
+    q = torch.randn(1, hq, d, generator=gen) * 0.1
+    direction = torch.randn(d, generator=gen)
+    direction /= direction.norm()
+    q[0, :] += 40.0 * direction
+    k[target, :] += 40.0 * direction
+    k, v, q = k.bfloat16().float(), v.bfloat16().float(), q.bfloat16().float()
+    max_pages = -(-kv_len // page)
+    table = make_tables(1, max_pages, max_pages + 9, seed=2)
+    kc, vc = fill_cache([k], [v], table, max_pages + 9, page, torch.bfloat16)
+    out = run_decode(q.bfloat16().to(DEV), kc, vc, [0], [kv_len - 1], [0], table, 1.0, window,
+                     n_splits=5).double().cpu()
+    want = attention_reference(q, [k], [v], [kv_len - 1], [0], 1.0, window)
+    torch.testing.assert_close(out, want, **tol(torch.bfloat16))
+    hit = torch.stack([v[target, h // (hq // hkv)] for h in range(hq)]).double()
+    if where == "just_outside":
+        assert (out[0] - hit).abs().max() > 0.1
+    else:
+        torch.testing.assert_close(out[0], hit, rtol=5e-2, atol=5e-2)

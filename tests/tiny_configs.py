@@ -37,8 +37,30 @@ TINY_W = {
 TINY_W_INIT = {"seed": 2, "std": 0.04, "norm_std": 0.1}
 TINY_W_PAGE = 16
 
+# Head sizes that the tensor-core attention kernels take (64 and 128), with small and large groups.
+TINY_C = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "num_hidden_layers": 2, "hidden_size": 96, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "head_dim": 64, "intermediate_size": 144, "vocab_size": 211, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 512,
+}
+TINY_C_INIT = {"seed": 3, "std": 0.05, "norm_std": 0.1}
+TINY_C_PAGE = 16
+
+TINY_D = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "num_hidden_layers": 2, "hidden_size": 160, "num_attention_heads": 8, "num_key_value_heads": 1,
+    "head_dim": 128, "intermediate_size": 208, "vocab_size": 300, "rope_theta": 10000.0,
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 512,
+    "use_sliding_window": True, "sliding_window": 40, "max_window_layers": 1,
+}
+TINY_D_INIT = {"seed": 4, "std": 0.04, "norm_std": 0.1}
+TINY_D_PAGE = 32
+
 ALL = {
     "A": (TINY_A, TINY_A_INIT, TINY_A_PAGE),
     "B": (TINY_B, TINY_B_INIT, TINY_B_PAGE),
     "W": (TINY_W, TINY_W_INIT, TINY_W_PAGE),
+    "C": (TINY_C, TINY_C_INIT, TINY_C_PAGE),
+    "D": (TINY_D, TINY_D_INIT, TINY_D_PAGE),
 }

@@ -1,0 +1,338 @@
+// Split-K paged attention for single next tokens (bfloat16, head_dim 64 or 128).
+//
+// One thread block per (key split, kv head, decoded token).  The query heads that
+// share the kv head form the rows of a 16-row tensor-core tile, so keys and values
+// are read once for the whole group.  Each of the four warps walks its own 16-key
+// tiles of the block's key range (one cache page, or a part of a larger page, per
+// tile), copies them into shared memory with cp.async two tiles ahead of use, and
+// keeps its own online-softmax state in registers: scores, running maximum,
+// normaliser and output accumulator are float32
+// (src/tokamak/kernels/paged_attention.py:111-123,139-151).  The warps are merged
+// through shared memory, the block writes an unnormalised partial result with its
+// maximum and normaliser to scratch memory, and a second kernel merges the splits.
+// The reference's kernel has no split and one program per (sequence, kv head)
+// (paged_attention.py:19-20,202).
+//
+// Keys outside [max(0, pos - window + 1), pos] are never loaded: their rows are
+// zero-filled, so stale or foreign data in a partly filled or given-back page
+// cannot reach the result.
+#include "mma_utils.cuh"
+
+namespace tk {
+
+constexpr int kDecWarps = 4;
+constexpr int kDecTile = 16;      // keys per warp tile
+constexpr int kDecStages = 3;
+
+struct DecodeParams {
+  const __nv_bfloat16* q;       // [n_tokens, n_q_heads, D]
+  const __nv_bfloat16* k_cache; // [num_pages, n_kv_heads, page_size, D]
+  const __nv_bfloat16* v_cache;
+  float* part_o;                // [n_items, n_q_heads, n_splits, D]
+  float* part_ml;               // [n_items, n_q_heads, n_splits, 2]
+  const int* items;             // [n_items] token index of each decoded token
+  const int* positions;
+  const int* tok_req;
+  const int* req_slot;
+  const int* block_table;
+  int* err;
+  int n_items, n_reqs, n_q_heads, n_kv_heads, page_size, max_pages, num_pages, window, n_splits;
+  float scale_log2;             // softmax scale * log2(e)
+};
+
+template <int D>
+__global__ void __launch_bounds__(kDecWarps * 32)
+attn_decode_split_kernel(DecodeParams p) {
+  constexpr int CH = D / 8;                       // 16-byte chunks per row
+  constexpr int TILE_BYTES = kDecTile * D * 2;    // one K or V tile
+  constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+  extern __shared__ __align__(128) unsigned char smem[];
+
+  const int split = blockIdx.x, hkv = blockIdx.y, item = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int group = p.n_q_heads / p.n_kv_heads;
+
+  const int tok = p.items[item];
+  const int pos = p.positions[tok];
+  const int r = p.tok_req[tok];
+  bool bad = (pos < 0 || r < 0 || r >= p.n_reqs);
+  if (bad && threadIdx.x == 0) set_error(p.err, pos < 0 ? kErrPosition : kErrRequest, tok, pos, r);
+  const int* table = p.block_table + (size_t)(bad ? 0 : p.req_slot[r]) * p.max_pages;
+  const int lo = (!bad && p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+
+  // key tiles of this block
+  const int first_tile = lo / kDecTile;
+  const int last_tile = bad ? first_tile - 1 : pos / kDecTile;
+  const int n_tiles = last_tile - first_tile + 1;
+  const int per_split = (n_tiles + p.n_splits - 1) / p.n_splits;
+  const int my_begin = first_tile + split * per_split;
+  const int my_end = min(my_begin + per_split, last_tile + 1);
+
+  unsigned char* my_smem = smem + warp * kDecStages * STAGE_BYTES;
+  const uint32_t my_smem_u32 = smem_u32(my_smem);
+
+  // ---- query fragments: row g of the tile is query head hkv * group + g --------------------
+  uint32_t qa[D / 16][4];
+  {
+    const __nv_bfloat16* qbase = p.q + ((size_t)tok * p.n_q_heads + (size_t)hkv * group) * D;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const int c0 = ks * 16 + 2 * t4;
+      qa[ks][0] = (g < group) ? *reinterpret_cast<const uint32_t*>(qbase + (size_t)g * D + c0) : 0u;
+      qa[ks][2] = (g < group) ? *reinterpret_cast<const uint32_t*>(qbase + (size_t)g * D + c0 + 8) : 0u;
+      qa[ks][1] = (g + 8 < group) ? *reinterpret_cast<const uint32_t*>(qbase + (size_t)(g + 8) * D + c0) : 0u;
+      qa[ks][3] = (g + 8 < group) ? *reinterpret_cast<const uint32_t*>(qbase + (size_t)(g + 8) * D + c0 + 8) : 0u;
+    }
+  }
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.0f, 0.0f};
+
+  // ---- asynchronous load of one 16-key tile of K and V into a stage ------------------------
+  auto issue_load = [&](int tile, int stage) {
+    const int key0 = tile * kDecTile;
+    const int pidx = key0 / p.page_size;
+    int page = (pidx < p.max_pages) ? table[pidx] : -1;
+    if (page < 0 || page >= p.num_pages) {
+      if (lane == 0) set_error(p.err, kErrPage, tok, pidx, page);
+      page = -1;
+    }
+    const size_t row0 = ((size_t)(page < 0 ? 0 : page) * p.n_kv_heads + hkv) * p.page_size +
+                        (key0 % p.page_size);
+    const __nv_bfloat16* ksrc = p.k_cache + row0 * D;
+    const __nv_bfloat16* vsrc = p.v_cache + row0 * D;
+    const uint32_t kdst = my_smem_u32 + stage * STAGE_BYTES;
+    const uint32_t vdst = kdst + TILE_BYTES;
+#pragma unroll
+    for (int i = 0; i < (kDecTile * CH) / 32; ++i) {
+      const int idx = i * 32 + lane;
+      const int row = idx / CH, chunk = idx % CH;
+      const int key = key0 + row;
+      const bool valid = (page >= 0) && key >= lo && key <= pos;
+      const int off = swizzled_offset(row, chunk, CH);
+      cp_async16(kdst + off, ksrc + (size_t)row * D + chunk * 8, valid);
+      cp_async16(vdst + off, vsrc + (size_t)row * D + chunk * 8, valid);
+    }
+  };
+
+  // tiles of this warp: my_begin + warp, + kDecWarps, ...
+  const int n_mine = (my_end - my_begin - warp + kDecWarps - 1) / kDecWarps;
+#pragma unroll
+  for (int s = 0; s < kDecStages - 1; ++s) {
+    if (s < n_mine) issue_load(my_begin + warp + s * kDecWarps, s);
+    cp_async_commit();
+  }
+
+  for (int i = 0; i < n_mine; ++i) {
+    const int tile = my_begin + warp + i * kDecWarps;
+    {
+      const int nxt = i + kDecStages - 1;
+      if (nxt < n_mine) issue_load(my_begin + warp + nxt * kDecWarps, nxt % kDecStages);
+      cp_async_commit();
+    }
+    cp_async_wait<kDecStages - 1>();
+    __syncwarp();
+
+    const uint32_t kbase = my_smem_u32 + (i % kDecStages) * STAGE_BYTES;
+    const uint32_t vbase = kbase + TILE_BYTES;
+
+    // scores of 16 rows x 16 keys
+    float s[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f; }
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const int row = ((lane >> 4) << 3) + (lane & 7);
+      const int chunk = 2 * ks + ((lane >> 3) & 1);
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4(kbase + swizzled_offset(row, chunk, CH), b0, b1, b2, b3);
+      mma_bf16_16816(s[0], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+      mma_bf16_16816(s[1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b2, b3);
+    }
+
+    // mask, running maximum, probabilities
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = tile * kDecTile + nt * 8 + 2 * t4 + (e & 1);
+        const bool valid = key >= lo && key <= pos;
+        s[nt][e] = valid ? s[nt][e] * p.scale_log2 : -INFINITY;
+        mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+      }
+    }
+    float corr[2], m_use[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      const float m_new = fmaxf(m_run[h], mx[h]);
+      m_use[h] = (m_new == -INFINITY) ? 0.0f : m_new;
+      corr[h] = exp2f(m_run[h] - m_use[h]);
+      m_run[h] = m_new;
+    }
+    float psum[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        s[nt][e] = exp2f(s[nt][e] - m_use[e >> 1]);
+        psum[e >> 1] += s[nt][e];
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) l_run[h] = l_run[h] * corr[h] + psum[h];
+#pragma unroll
+    for (int i2 = 0; i2 < D / 8; ++i2) {
+      o[i2][0] *= corr[0]; o[i2][1] *= corr[0];
+      o[i2][2] *= corr[1]; o[i2][3] *= corr[1];
+    }
+
+    // output += P * V
+    const uint32_t pa0 = pack_bf16(s[0][0], s[0][1]);
+    const uint32_t pa1 = pack_bf16(s[0][2], s[0][3]);
+    const uint32_t pa2 = pack_bf16(s[1][0], s[1][1]);
+    const uint32_t pa3 = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+    for (int c = 0; c < D / 8; c += 2) {
+      const int row = (((lane >> 3) & 1) << 3) + (lane & 7);
+      const int chunk = c + (lane >> 4);
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4_trans(vbase + swizzled_offset(row, chunk, CH), b0, b1, b2, b3);
+      mma_bf16_16816(o[c], pa0, pa1, pa2, pa3, b0, b1);
+      mma_bf16_16816(o[c + 1], pa0, pa1, pa2, pa3, b2, b3);
+    }
+    __syncwarp();
+  }
+  cp_async_wait<0>();
+
+  // ---- merge the warps --------------------------------------------------------------------
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+  __syncthreads();   // every warp is done with its stages; the memory is reused below
+  float* so = reinterpret_cast<float*>(smem);                  // [warps][16][D]
+  float* sml = so + kDecWarps * 16 * D;                        // [warps][16][2]
+#pragma unroll
+  for (int i2 = 0; i2 < D / 8; ++i2) {
+    const int col = i2 * 8 + 2 * t4;
+    float* row0 = so + ((size_t)warp * 16 + g) * D + col;
+    float* row1 = so + ((size_t)warp * 16 + g + 8) * D + col;
+    row0[0] = o[i2][0]; row0[1] = o[i2][1];
+    row1[0] = o[i2][2]; row1[1] = o[i2][3];
+  }
+  if (t4 == 0) {
+    sml[(warp * 16 + g) * 2 + 0] = m_run[0];     sml[(warp * 16 + g) * 2 + 1] = l_run[0];
+    sml[(warp * 16 + g + 8) * 2 + 0] = m_run[1]; sml[(warp * 16 + g + 8) * 2 + 1] = l_run[1];
+  }
+  __syncthreads();
+
+  for (int idx = threadIdx.x; idx < group * D; idx += kDecWarps * 32) {
+    const int row = idx / D, col = idx % D;
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kDecWarps; ++w) m_all = fmaxf(m_all, sml[(w * 16 + row) * 2]);
+    float acc = 0.0f, l_all = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kDecWarps; ++w) {
+      const float mw = sml[(w * 16 + row) * 2];
+      const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - m_all);
+      acc += so[((size_t)w * 16 + row) * D + col] * f;
+      l_all += sml[(w * 16 + row) * 2 + 1] * f;
+    }
+    const size_t pidx = ((size_t)item * p.n_q_heads + (size_t)hkv * group + row) * p.n_splits + split;
+    p.part_o[pidx * D + col] = acc;
+    if (col == 0) { p.part_ml[pidx * 2] = m_all; p.part_ml[pidx * 2 + 1] = l_all; }
+  }
+}
+
+// out[tok, head, :] = sum_s o_s * 2^(m_s - m) / sum_s l_s * 2^(m_s - m)
+__global__ void attn_decode_merge_kernel(const float* __restrict__ part_o,
+                                         const float* __restrict__ part_ml,
+                                         const int* __restrict__ items, __nv_bfloat16* __restrict__ out,
+                                         int n_q_heads, int n_splits, int D) {
+  const int item = blockIdx.x, head = blockIdx.y;
+  const size_t base = ((size_t)item * n_q_heads + head) * n_splits;
+  float m_all = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) m_all = fmaxf(m_all, part_ml[(base + s) * 2]);
+  float l_all = 0.0f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float ms = part_ml[(base + s) * 2];
+    if (ms != -INFINITY) l_all += part_ml[(base + s) * 2 + 1] * exp2f(ms - m_all);
+  }
+  const float inv = 1.0f / l_all;
+  __nv_bfloat16* orow = out + ((size_t)items[item] * n_q_heads + head) * D;
+  for (int col = threadIdx.x; col < D; col += blockDim.x) {
+    float acc = 0.0f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float ms = part_ml[(base + s) * 2];
+      if (ms != -INFINITY) acc += part_o[(base + s) * D + col] * exp2f(ms - m_all);
+    }
+    orow[col] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+template <int D>
+static int launch_decode(const DecodeParams& p, void* out, cudaStream_t stream) {
+  constexpr int smem_bytes = kDecWarps * kDecStages * 2 * kDecTile * D * 2;
+  static_assert(kDecWarps * 16 * D * 4 + kDecWarps * 16 * 2 * 4 <= smem_bytes, "merge area too small");
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_split_kernel<D>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(p.n_splits, p.n_kv_heads, p.n_items);
+  attn_decode_split_kernel<D><<<grid, kDecWarps * 32, smem_bytes, stream>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  dim3 mgrid(p.n_items, p.n_q_heads);
+  attn_decode_merge_kernel<<<mgrid, D >= 128 ? 128 : 64, 0, stream>>>(
+      p.part_o, p.part_ml, p.items, (__nv_bfloat16*)out, p.n_q_heads, p.n_splits, D);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace tk
+
+// Floats of scratch that tk_attention_decode needs: partial outputs, then (max, sum) pairs.
+TK_API long long tk_attention_decode_scratch_floats(int n_items, int n_q_heads, int head_dim,
+                                                    int n_splits) {
+  return (long long)n_items * n_q_heads * n_splits * (head_dim + 2);
+}
+
+TK_API int tk_attention_decode(const void* q, void* out, const void* k_cache, const void* v_cache,
+                               float* scratch, const int* items, const int* positions,
+                               const int* tok_req, const int* req_slot, const int* block_table,
+                               int* err, int n_items, int n_reqs, int n_q_heads, int n_kv_heads,
+                               int head_dim, int page_size, int max_pages, int num_pages, int window,
+                               int n_splits, float scale, cudaStream_t stream) {
+  if (n_items <= 0) return 0;
+  const int group = n_kv_heads > 0 ? n_q_heads / n_kv_heads : 0;
+  if (n_kv_heads < 1 || n_q_heads % n_kv_heads != 0 || group > 16 || page_size % 16 != 0 ||
+      n_splits < 1 || n_splits > 65535 || n_items > 65535 || n_kv_heads > 65535 ||
+      (head_dim != 64 && head_dim != 128)) {
+    return (int)cudaErrorInvalidValue;
+  }
+  tk::DecodeParams p;
+  p.q = (const __nv_bfloat16*)q;
+  p.k_cache = (const __nv_bfloat16*)k_cache;
+  p.v_cache = (const __nv_bfloat16*)v_cache;
+  p.part_o = scratch;
+  p.part_ml = scratch + (size_t)n_items * n_q_heads * n_splits * head_dim;
+  p.items = items; p.positions = positions; p.tok_req = tok_req; p.req_slot = req_slot;
+  p.block_table = block_table; p.err = err;
+  p.n_items = n_items; p.n_reqs = n_reqs; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
+  p.page_size = page_size; p.max_pages = max_pages; p.num_pages = num_pages; p.window = window;
+  p.n_splits = n_splits;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  if (head_dim == 128) return tk::launch_decode<128>(p, out, stream);
+  return tk::launch_decode<64>(p, out, stream);
+}

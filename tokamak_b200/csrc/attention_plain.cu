@@ -25,6 +25,7 @@ struct AttnParams {
   const int* tok_req;       // [n_tokens]
   const int* req_slot;      // [n_reqs]
   const int* block_table;   // [n_slots, max_pages]
+  const int* items;         // [n_items] token indices to process, or null for all tokens
   int* err;
   int n_tokens, n_reqs, n_q_heads, n_kv_heads, head_dim;
   int page_size, max_pages, num_pages, window;
@@ -37,7 +38,7 @@ __global__ void attention_plain_kernel(AttnParams p) {
   __shared__ float s_l[kPlainWarps];
   __shared__ float s_acc[kPlainWarps][kPlainMaxPerLane * 32];
 
-  const int t = blockIdx.x;
+  const int t = p.items ? p.items[blockIdx.x] : blockIdx.x;
   const int hq = blockIdx.y;
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -128,7 +129,7 @@ __global__ void attention_plain_kernel(AttnParams p) {
 
 TK_API int tk_attention_plain(const void* q, void* out, const void* k_cache, const void* v_cache,
                               const int* positions, const int* tok_req, const int* req_slot,
-                              const int* block_table, int* err, int n_tokens, int n_reqs,
+                              const int* block_table, const int* items, int* err, int n_tokens, int n_reqs,
                               int n_q_heads, int n_kv_heads, int head_dim, int page_size,
                               int max_pages, int num_pages, int window, float scale, int dtype,
                               cudaStream_t stream) {
@@ -140,7 +141,7 @@ TK_API int tk_attention_plain(const void* q, void* out, const void* k_cache, con
   tk::AttnParams p;
   p.q = q; p.out = out; p.k_cache = k_cache; p.v_cache = v_cache;
   p.positions = positions; p.tok_req = tok_req; p.req_slot = req_slot; p.block_table = block_table;
-  p.err = err; p.n_tokens = n_tokens; p.n_reqs = n_reqs; p.n_q_heads = n_q_heads;
+  p.items = items; p.err = err; p.n_tokens = n_tokens; p.n_reqs = n_reqs; p.n_q_heads = n_q_heads;
   p.n_kv_heads = n_kv_heads; p.head_dim = head_dim; p.page_size = page_size;
   p.max_pages = max_pages; p.num_pages = num_pages; p.window = window; p.scale = scale;
   dim3 grid(n_tokens, n_q_heads);

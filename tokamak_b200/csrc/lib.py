@@ -22,9 +22,12 @@ _SIGNATURES: dict[str, list] = {
     "tk_rope_kv": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                    c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                    c_float, c_int, _P],
-    "tk_attention_plain": [_P, _P, _P, _P, _P, _P, _P, _P, _P,
+    "tk_attention_plain": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                            c_float, c_int, _P],
+    "tk_attention_decode": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
+                            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                            c_float, _P],
     "tk_gemm_f32": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "tk_sample": [_P, c_longlong, _P, _P, _P, _P, _P, _P, c_int, c_int, _P],
 }

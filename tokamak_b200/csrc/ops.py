@@ -141,8 +141,10 @@ def rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | None
 def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     positions: torch.Tensor, tok_req: torch.Tensor, req_slot: torch.Tensor,
                     block_table: torch.Tensor, err: torch.Tensor, *, scale: float,
-                    window: int | None = None) -> None:
-    """Paged attention of a mixed batch; q and out are [N, Hq, d]."""
+                    window: int | None = None, items: torch.Tensor | None = None) -> None:
+    """Paged attention of a mixed batch; q and out are [N, Hq, d].
+
+    ``items`` restricts the work to the listed token indices (rows of q and out)."""
     _want(q, None, "q"); _want(out, q.dtype, "out")
     _want(k_cache, q.dtype, "k_cache"); _want(v_cache, q.dtype, "v_cache")
     n, hq, d = q.shape
@@ -155,11 +157,58 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
         raise KernelError(f"head_dim {d} is beyond the kernels' limit of 256")
     _check(library().tk_attention_plain(q.data_ptr(), out.data_ptr(), k_cache.data_ptr(),
                                         v_cache.data_ptr(), positions.data_ptr(), tok_req.data_ptr(),
-                                        req_slot.data_ptr(), block_table.data_ptr(), err.data_ptr(),
-                                        n, req_slot.numel(), hq, hkv, d, page_size,
+                                        req_slot.data_ptr(), block_table.data_ptr(), _ptr(items),
+                                        err.data_ptr(), n if items is None else items.numel(),
+                                        req_slot.numel(), hq, hkv, d, page_size,
                                         block_table.shape[1], num_pages, int(window or 0),
                                         float(scale), dtype_code(q.dtype), _stream()),
            "attention_plain")
+
+
+def decode_splits(n_items: int, n_kv_heads: int, max_kv_len: int) -> int:
+    """How many key splits give the decode kernel enough blocks to fill the GPU."""
+    tiles = max(1, -(-max_kv_len // 16))
+    want = -(-592 // max(1, n_items * n_kv_heads))          # 148 SMs x 2 blocks x 2 waves
+    return max(1, min(want, -(-tiles // 8)))
+
+
+def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                     items: torch.Tensor, positions: torch.Tensor, tok_req: torch.Tensor,
+                     req_slot: torch.Tensor, block_table: torch.Tensor, err: torch.Tensor, *,
+                     scale: float, window: int | None, n_splits: int,
+                     scratch: torch.Tensor | None = None) -> None:
+    """Split-K paged attention for the single next tokens listed in ``items`` (bfloat16 only)."""
+    _want(q, torch.bfloat16, "q"); _want(out, torch.bfloat16, "out")
+    _want(k_cache, torch.bfloat16, "k_cache"); _want(v_cache, torch.bfloat16, "v_cache")
+    _want(items, torch.int32, "items")
+    n, hq, d = q.shape
+    num_pages, hkv, page_size, dk = k_cache.shape
+    if not decode_kernel_takes(hq, hkv, d, page_size):
+        raise KernelError(f"the split-K decode kernel does not take heads {hq}/{hkv}, head_dim {d}, "
+                          f"page size {page_size}")
+    n_items = items.numel()
+    need = n_items * hq * n_splits * (d + 2)
+    if scratch is None:
+        scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+    else:
+        _want(scratch, torch.float32, "scratch")
+        if scratch.numel() < need:
+            raise KernelError(f"scratch holds {scratch.numel()} floats, {need} needed")
+    _check(library().tk_attention_decode(q.data_ptr(), out.data_ptr(), k_cache.data_ptr(),
+                                         v_cache.data_ptr(), scratch.data_ptr(), items.data_ptr(),
+                                         positions.data_ptr(), tok_req.data_ptr(), req_slot.data_ptr(),
+                                         block_table.data_ptr(), err.data_ptr(), n_items,
+                                         req_slot.numel(), hq, hkv, d, page_size, block_table.shape[1],
+                                         num_pages, int(window or 0), n_splits, float(scale), _stream()),
+           "attention_decode")
+    global LAUNCHES
+    LAUNCHES += 1      # the merge kernel
+
+
+def decode_kernel_takes(n_q_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    """Shapes of the tensor-core decode kernel; everything else goes to the general kernel."""
+    return (head_dim in (64, 128) and page_size % 16 == 0 and n_q_heads % n_kv_heads == 0
+            and n_q_heads // n_kv_heads <= 16)
 
 
 def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:

@@ -100,8 +100,22 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
                     window: int | None) -> None:
     """Attention of every token of the step over the pages of its own request.
 
-    Chooses the kernel: the general one for float32 and for shapes the tiled
-    kernels do not take.
+    Chooses the kernels.  bfloat16 with a head_dim and page size the tiled kernels take:
+    single next tokens go to the split-K decode kernel, portions of prompts to the
+    general kernel.  float32, and every other shape, runs on the general kernel alone.
     """
-    ops.attention_plain(q, out, cache_view.k, cache_view.v, step.positions, step.tok_req,
-                        step.req_slot, cache_view.table, step.err, scale=scale, window=window)
+    n, hq, d = q.shape
+    hkv, page = cache_view.k.shape[1], cache_view.k.shape[2]
+    tiled = q.dtype == torch.bfloat16 and ops.decode_kernel_takes(hq, hkv, d, page)
+    n_dec = step.decode_items.numel()
+    if not tiled or n_dec == 0:
+        ops.attention_plain(q, out, cache_view.k, cache_view.v, step.positions, step.tok_req,
+                            step.req_slot, cache_view.table, step.err, scale=scale, window=window)
+        return
+    ops.attention_decode(q, out, cache_view.k, cache_view.v, step.decode_items, step.positions,
+                         step.tok_req, step.req_slot, cache_view.table, step.err, scale=scale,
+                         window=window, n_splits=ops.decode_splits(n_dec, hkv, step.max_kv_len))
+    if step.prefill_items.numel():
+        ops.attention_plain(q, out, cache_view.k, cache_view.v, step.positions, step.tok_req,
+                            step.req_slot, cache_view.table, step.err, scale=scale, window=window,
+                            items=step.prefill_items)
