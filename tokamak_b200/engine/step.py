@@ -132,8 +132,13 @@ class StepBuffers:
 class StepFunction:
     """Builds the batch description, runs the model and keeps the cache's lengths."""
 
-    def __init__(self, model, cache: DeviceCache, max_step_tokens: int, max_seq_len: int):
+    def __init__(self, model, cache: DeviceCache, max_step_tokens: int, max_seq_len: int,
+                 use_graphs: bool = True):
         self.model = model
+        self.use_graphs = use_graphs
+        self._graphs: dict = {}          # (batch, key-length bucket) -> captured decode step
+        self._graph_seen: dict = {}
+        self._graph_pool = None
         self.cache = cache
         self.manager = cache.manager
         self.device = cache.device
@@ -246,20 +251,61 @@ class StepFunction:
 
     @torch.inference_mode()
     def run_and_sample(self, entries: Sequence[StepEntry], sampling: Sequence[SamplingRow]) -> list[int]:
-        """One token per wanted place, sampled on the device; one copy back for tokens and errors."""
+        """One token per wanted place, sampled on the device; one copy back for tokens and errors.
+
+        A step in which every request brings exactly one token and wants it sampled has the
+        same launches every time, so it is captured into a CUDA graph the second time its shape
+        (batch size, bucket of the longest context) is seen and replayed from then on: the
+        description of the step is uploaded outside the graph into buffers at fixed addresses.
+        """
         batch, samp = self.build(entries, sampling)
-        logits = self.model.forward(batch)
         W = batch.n_want
         res = self.buffers.result
-        if W:
-            ops.sample(logits, samp["temperature"], samp["top_k"], samp["top_p"], samp["seed"],
-                       samp["counter"], res[4:4 + W])
+        graphable = (self.use_graphs and batch.max_q_len == 1 and W == batch.n_tokens)
+        if graphable:
+            bucket = 256
+            while bucket < batch.max_kv_len:
+                bucket *= 2
+            batch.max_kv_len = bucket        # kernels size their grids from the bucket
+            key = (batch.n_tokens, bucket)
+            graph = self._graphs.get(key)
+            if graph is None and self._graph_seen.get(key, 0) >= 1:
+                graph = self._capture(key, batch, samp)
+            if graph is not None:
+                graph["graph"].replay()
+                self.graph_launches += graph["kernels"]
+            else:
+                self._graph_seen[key] = self._graph_seen.get(key, 0) + 1
+                graphable = False
+        if not graphable:
+            logits = self.model.forward(batch)
+            if W:
+                ops.sample(logits, samp["temperature"], samp["top_k"], samp["top_p"], samp["seed"],
+                           samp["counter"], res[4:4 + W])
         self.finish(entries)
         host = self.buffers.result_host
         host[:4 + W].copy_(res[:4 + W], non_blocking=True)
         torch.cuda.current_stream().synchronize()
         self._raise_on_error(host[:4].tolist())
         return host[4:4 + W].tolist()
+
+    def _capture(self, key, batch: StepBatch, samp: dict) -> dict:
+        """Record the decode step of this shape; its launches are replayed, not run, here."""
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        W = batch.n_want
+        graph = torch.cuda.CUDAGraph()
+        before = ops.LAUNCHES
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            logits = self.model.forward(batch)
+            ops.sample(logits, samp["temperature"], samp["top_k"], samp["top_p"], samp["seed"],
+                       samp["counter"], self.buffers.result[4:4 + W])
+        kernels = ops.LAUNCHES - before
+        ops.LAUNCHES = before
+        entry = {"graph": graph, "kernels": kernels, "logits": logits}
+        self._graphs[key] = entry
+        return entry
 
     def check_errors(self) -> None:
         self._raise_on_error(self.buffers.result[:4].cpu().tolist())
