@@ -1,0 +1,79 @@
+// Split-K paged decode attention for callers that cannot allocate device memory.
+//
+// No counterpart in WeichunK/tokamak.  See tokamak_b200_noalloc.h for who needs it
+// and for the contract.  The scratch of the decode kernels (unnormalised partial
+// outputs and their (maximum, normaliser) pairs, one set per key split) lives in
+// the file-scope device array below; the kernels themselves are the ones behind
+// tk_attention_decode, reached through that exported function with the array's
+// device address as its scratch argument.
+#include "common.cuh"
+#include "tokamak_b200_noalloc.h"
+
+// The existing entry point (attention_decode.cu); it launches two kernels and allocates nothing.
+extern "C" int tk_attention_decode(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                   float* scratch, const int* items, const int* positions,
+                                   const int* tok_req, const int* req_slot, const int* block_table,
+                                   int* err, int n_items, int n_reqs, int n_q_heads, int n_kv_heads,
+                                   int head_dim, int page_size, int max_pages, int num_pages, int window,
+                                   int n_splits, float scale, cudaStream_t stream);
+
+namespace {
+
+constexpr long long kScratchFloats = 1ll << 20;   // 4 MiB on every GPU that loads the library
+constexpr int kMaxDevices = 64;
+
+// In host code this name is only a handle for the runtime, not a device address:
+// the address comes from cudaGetSymbolAddress, per device.
+static __device__ __align__(256) float g_decode_scratch[kScratchFloats];
+
+float* g_scratch_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the array on the current device, looked up once per device.
+int scratch_for_current_device(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return TK_NOALLOC_BAD_DEVICE;
+  if (g_scratch_ptr[dev] == nullptr) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_decode_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_scratch_ptr[dev] = ptr;
+  }
+  *out = g_scratch_ptr[dev];
+  return 0;
+}
+
+}  // namespace
+
+TK_API long long tk_attention_decode_noalloc_capacity_floats(void) { return kScratchFloats; }
+
+TK_API const char* tk_noalloc_error_string(int code) {
+  switch (code) {
+    case 0: return "success";
+    case TK_NOALLOC_TOO_LARGE:
+      return "the call needs more scratch than the library's static array holds "
+             "(n_items * n_q_heads * n_splits * (head_dim + 2) floats; see "
+             "tk_attention_decode_noalloc_capacity_floats): use fewer splits or fewer items per call";
+    case TK_NOALLOC_BAD_DEVICE: return "the current device's index is beyond the library's table";
+    default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown error";
+  }
+}
+
+TK_API int tk_attention_decode_noalloc(const void* q, void* out, const void* k_cache,
+                                       const void* v_cache, const int* items, const int* positions,
+                                       const int* tok_req, const int* req_slot, const int* block_table,
+                                       int* err, int n_items, int n_reqs, int n_q_heads, int n_kv_heads,
+                                       int head_dim, int page_size, int max_pages, int num_pages,
+                                       int window, int n_splits, float scale, cudaStream_t stream) {
+  if (n_items <= 0) return 0;
+  if (n_q_heads < 1 || head_dim < 1 || n_splits < 1) return (int)cudaErrorInvalidValue;
+  const long long need = (long long)n_items * n_q_heads * n_splits * (head_dim + 2);
+  if (need > kScratchFloats) return TK_NOALLOC_TOO_LARGE;
+  float* scratch = nullptr;
+  const int rc = scratch_for_current_device(&scratch);
+  if (rc != 0) return rc;
+  return tk_attention_decode(q, out, k_cache, v_cache, scratch, items, positions, tok_req, req_slot,
+                             block_table, err, n_items, n_reqs, n_q_heads, n_kv_heads, head_dim,
+                             page_size, max_pages, num_pages, window, n_splits, scale, stream);
+}

@@ -54,7 +54,7 @@ def sources() -> list[Path]:
 
 def _source_stamp() -> str:
     h = hashlib.sha256()
-    for path in sorted(list(SOURCE_DIR.glob("*.cu")) + list(SOURCE_DIR.glob("*.cuh"))):
+    for path in sorted(list(SOURCE_DIR.glob("*.cu")) + list(SOURCE_DIR.glob("*.cuh")) + list(SOURCE_DIR.glob("*.h"))):
         h.update(path.name.encode())
         h.update(path.read_bytes())
     h.update(" ".join(NVCC_FLAGS).encode())
