@@ -426,3 +426,81 @@ def test_attention_decode_finds_the_one_key_that_matters(where):
         assert (out[0] - hit).abs().max() > 0.1
     else:
         torch.testing.assert_close(out[0], hit, rtol=5e-2, atol=5e-2)
+
+
+# ----------------------------------------------------------------------------- flash prefill kernel
+
+@pytest.mark.parametrize("hq,hkv,d,page,window", [(8, 2, 128, 16, None), (4, 4, 64, 16, None),
+                                                    (6, 1, 64, 8, None), (8, 8, 128, 32, 50),
+                                                    (3, 1, 128, 16, 200), (10, 5, 64, 4, 9)])
+def test_attention_prefill_portions(hq, hkv, d, page, window):
+    """Whole prompts and portions that continue a request, with lengths around the 64-token
+    tile and the page edges; unwritten cache slots are NaN."""
+    from tokamak_b200.csrc import ops
+    kv_lens = [2, 64, 65, 300, 129, 1000, 47]
+    q_lens = [2, 64, 65, 37, 128, 130, 3]        # whole, whole, whole, portion, portion, portion, portion
+    n_reqs = len(kv_lens)
+    max_pages = max(-(-l // page) for l in kv_lens)
+    num_pages = n_reqs * max_pages + 5
+    table = make_tables(n_reqs, max_pages, num_pages, seed=d + hq)
+    gen = torch.Generator().manual_seed(5 * hq + d)
+    k_all = [torch.randn(l, hkv, d, generator=gen).bfloat16().float() for l in kv_lens]
+    v_all = [torch.randn(l, hkv, d, generator=gen).bfloat16().float() for l in kv_lens]
+    kc, vc = fill_cache(k_all, v_all, table, num_pages, page, torch.bfloat16)
+    positions, tok_req, q_start = [], [], []
+    for r, (kl, ql) in enumerate(zip(kv_lens, q_lens)):
+        q_start.append(len(positions))
+        positions += list(range(kl - ql, kl)); tok_req += [r] * ql
+    n = len(positions)
+    q = torch.randn(n, hq, d, generator=gen).bfloat16()
+    tiles = [(r, t) for r in range(n_reqs) for t in range(-(-q_lens[r] // 64))]
+    tiles = tiles[::-1]
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    err = err_word()
+    out = torch.full_like(q, float("nan")).to(DEV)
+    scale = d ** -0.5
+    ops.attention_prefill(q.to(DEV), out, kc, vc, i32([x for rt in tiles for x in rt]), i32(q_start),
+                          i32(q_lens), i32(kv_lens), i32(list(range(n_reqs))), table.to(DEV), err,
+                          scale=scale, window=window)
+    assert err.tolist()[0] == 0
+    want = attention_reference(q.float(), k_all, v_all, positions, tok_req, scale, window)
+    torch.testing.assert_close(out.double().cpu(), want, **tol(torch.bfloat16))
+
+
+@pytest.mark.parametrize("where", ["first", "far", "page_edge", "diagonal", "window_edge", "just_outside"])
+def test_attention_prefill_finds_the_one_key_that_matters(where):
+    """The last query of a 100-token portion at the end of 900 tokens must find one key."""
+    from tokamak_b200.csrc import ops
+    hq, hkv, d, page = 4, 2, 128, 16
+    kv_len, q_len, window = 900, 100, None
+    target = {"first": 0, "far": 123, "page_edge": 16 * 30 - 1, "diagonal": kv_len - 1,
+              "window_edge": kv_len - 300, "just_outside": kv_len - 301}[where]
+    if where in ("window_edge", "just_outside"):
+        window = 300
+    gen = torch.Generator().manual_seed(21)
+    k = torch.randn(kv_len, hkv, d, generator=gen) * 0.1
+    v = torch.randn(kv_len, hkv, d, generator=gen)
+    q = torch.randn(q_len, hq, d, generator=gen) * 0.1
+    direction = torch.randn(d, generator=gen)
+    direction /= direction.norm()
+    q[-1, :] += 40.0 * direction
+    k[target, :] += 40.0 * direction
+    k, v, q = k.bfloat16().float(), v.bfloat16().float(), q.bfloat16().float()
+    max_pages = -(-kv_len // page)
+    table = make_tables(1, max_pages, max_pages + 9, seed=4)
+    kc, vc = fill_cache([k], [v], table, max_pages + 9, page, torch.bfloat16)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    err = err_word()
+    out = torch.empty(q_len, hq, d, dtype=torch.bfloat16, device=DEV)
+    ops.attention_prefill(q.bfloat16().to(DEV), out, kc, vc, i32([0, 1, 0, 0]), i32([0]), i32([q_len]),
+                          i32([kv_len]), i32([0]), table.to(DEV), err, scale=1.0, window=window)
+    assert err.tolist()[0] == 0
+    positions = list(range(kv_len - q_len, kv_len))
+    want = attention_reference(q, [k], [v], positions, [0] * q_len, 1.0, window)
+    out = out.double().cpu()
+    torch.testing.assert_close(out, want, **tol(torch.bfloat16))
+    hit = torch.stack([v[target, h // (hq // hkv)] for h in range(hq)]).double()
+    if where == "just_outside":
+        assert (out[-1] - hit).abs().max() > 0.1
+    else:
+        torch.testing.assert_close(out[-1], hit, rtol=5e-2, atol=5e-2)

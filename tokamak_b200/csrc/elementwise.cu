@@ -60,6 +60,81 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TDelta* __re
   }
 }
 
+// Same operation for widths that are a multiple of 8: every thread keeps its values in
+// registers between the sum of squares and the scaling, so the row is read once, with
+// 16- and 32-byte accesses.
+template <typename T> struct Vec8;
+template <> struct Vec8<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+};
+template <> struct Vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = raw;
+  }
+};
+
+template <typename T, int ITERS>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                       const float* __restrict__ weight, T* __restrict__ out,
+                                       const int* __restrict__ rows, int hidden, float eps) {
+  __shared__ float scratch[32];
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  float* x = resid + (size_t)r * hidden;
+  const T* d = delta ? delta + (size_t)r * hidden : nullptr;
+  const bool write_back = (rows == nullptr) && (d != nullptr);
+  float v[ITERS][8];
+  float ss = 0.0f;
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int h = (it * blockDim.x + threadIdx.x) * 8;
+    if (h < hidden) {
+      Vec8<float>::load(x + h, v[it]);
+      if (d) {
+        float dv[8];
+        Vec8<T>::load(d + h, dv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[it][e] += dv[e];
+      }
+      if (write_back) Vec8<float>::store(x + h, v[it]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += v[it][e] * v[it][e];
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd = rsqrtf(ss / (float)hidden + eps);
+  T* o = out + (size_t)i * hidden;
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int h = (it * blockDim.x + threadIdx.x) * 8;
+    if (h < hidden) {
+      float w[8], y[8];
+      Vec8<float>::load(weight + h, w);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y[e] = v[it][e] * rstd * w[e];
+      Vec8<T>::store(o + h, y);
+    }
+  }
+}
+
 // out[t, j] = silu(gu[t, j]) * gu[t, inter + j]           (src/tokamak/model/layers.py:103)
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total) {
@@ -91,6 +166,21 @@ TK_API int tk_add_rmsnorm(float* resid, const void* delta, const float* weight, 
                           const int* rows, int n_rows, int hidden, float eps, int dtype,
                           cudaStream_t stream) {
   if (n_rows <= 0) return 0;
+  if (hidden % 8 == 0 && hidden <= 4 * 512 * 8) {
+    // one pass with the row in registers: threads * 8 * ITERS >= hidden
+    int threads = ((hidden / 8 + 31) / 32) * 32;
+    int iters = 1;
+    if (threads > 512) { iters = (hidden / 8 + 511) / 512; threads = 512; }
+    if (threads > 256 && iters == 1 && n_rows >= 64) { threads = (threads / 2 + 31) / 32 * 32; iters = 2; }
+    if (iters == 3) iters = 4;
+#define TK_LAUNCH_VEC(IT)                                                                       \
+    TK_DISPATCH_DTYPE(dtype, T,                                                                 \
+                      (tk::add_rmsnorm_vec_kernel<T, IT><<<n_rows, threads, 0, stream>>>(        \
+                          resid, (const T*)delta, weight, (T*)out, rows, hidden, eps)))
+    if (iters == 1) { TK_LAUNCH_VEC(1); } else if (iters == 2) { TK_LAUNCH_VEC(2); } else { TK_LAUNCH_VEC(4); }
+#undef TK_LAUNCH_VEC
+    return (int)cudaGetLastError();
+  }
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   TK_DISPATCH_DTYPE(dtype, T,
                     (tk::add_rmsnorm_kernel<T, T><<<n_rows, threads, 0, stream>>>(

@@ -205,6 +205,35 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
     LAUNCHES += 1      # the merge kernel
 
 
+def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                      tiles: torch.Tensor, req_q_start: torch.Tensor, req_q_len: torch.Tensor,
+                      req_kv_len: torch.Tensor, req_slot: torch.Tensor, block_table: torch.Tensor,
+                      err: torch.Tensor, *, scale: float, window: int | None) -> None:
+    """Paged flash attention for the 64-token query tiles listed in ``tiles`` (bfloat16 only).
+
+    ``tiles`` is int32 ``[n_tiles, 2]``: the request's row in the per-request arrays and the
+    index of the tile within the tokens that the request brings to this step."""
+    _want(q, torch.bfloat16, "q"); _want(out, torch.bfloat16, "out")
+    _want(k_cache, torch.bfloat16, "k_cache"); _want(v_cache, torch.bfloat16, "v_cache")
+    _want(tiles, torch.int32, "tiles")
+    n, hq, d = q.shape
+    num_pages, hkv, page_size, dk = k_cache.shape
+    if not prefill_kernel_takes(hq, hkv, d, page_size) or dk != d:
+        raise KernelError(f"the flash prefill kernel does not take heads {hq}/{hkv}, head_dim {d}")
+    _check(library().tk_attention_prefill(q.data_ptr(), out.data_ptr(), k_cache.data_ptr(),
+                                          v_cache.data_ptr(), tiles.data_ptr(), req_q_start.data_ptr(),
+                                          req_q_len.data_ptr(), req_kv_len.data_ptr(),
+                                          req_slot.data_ptr(), block_table.data_ptr(), err.data_ptr(),
+                                          tiles.numel() // 2, req_slot.numel(), hq, hkv, d, page_size,
+                                          block_table.shape[1], num_pages, int(window or 0),
+                                          float(scale), _stream()), "attention_prefill")
+
+
+def prefill_kernel_takes(n_q_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    """Shapes of the tensor-core prefill kernel; everything else goes to the general kernel."""
+    return head_dim in (64, 128) and n_q_heads % n_kv_heads == 0 and page_size >= 1
+
+
 def decode_kernel_takes(n_q_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> bool:
     """Shapes of the tensor-core decode kernel; everything else goes to the general kernel."""
     return (head_dim in (64, 128) and page_size % 16 == 0 and n_q_heads % n_kv_heads == 0

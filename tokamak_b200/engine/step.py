@@ -73,6 +73,7 @@ class StepBatch:
     logits_rows: torch.Tensor
     decode_items: torch.Tensor      # token indices of requests that bring one token
     prefill_items: torch.Tensor     # token indices of requests that bring more than one
+    prefill_tiles: torch.Tensor     # [n_tiles, 2] (request row, 64-token tile) of those requests, longest first
     cache: DeviceCache
     err: torch.Tensor
     host_q_start: list[int] = field(default_factory=list)
@@ -95,7 +96,7 @@ class StepBuffers:
 
     def __init__(self, device: torch.device, max_tokens: int, max_reqs: int):
         self.device = device
-        self.capacity = 6 * max_reqs + 4 * max_tokens + 5 * max_tokens + 64
+        self.capacity = 8 * max_reqs + 10 * max_tokens + 64
         self.hosts = [torch.zeros(self.capacity, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
         self.events: list = [None] * self.RING
         self.turn = 0
@@ -215,8 +216,12 @@ class StepFunction:
                        i32([s.top_k for s in sampling]), i32([s.counter for s in sampling])]
         dec_items = [q_start[r] for r in range(len(entries)) if q_len[r] == 1]
         pf_items = [q_start[r] + j for r in range(len(entries)) if q_len[r] > 1 for j in range(q_len[r])]
+        pf_tiles = [(kv_len[r] - q_len[r] + 64 * (t + 1), r, t) for r in range(len(entries))
+                    if q_len[r] > 1 for t in range(-(-q_len[r] // 64))]
+        pf_tiles.sort(reverse=True)       # tiles with the most keys to visit start first
+        pf_flat = [x for _, r, t in pf_tiles for x in (r, t)]
         arrays += [i32(tokens), i32(positions), i32(tok_req), i32(q_start), i32(q_len), i32(kv_len),
-                   i32(slots), i32(rows), i32(dec_items), i32(pf_items)]
+                   i32(slots), i32(rows), i32(dec_items), i32(pf_items), i32(pf_flat)]
         views = self.buffers.upload(arrays)
         samp = {}
         if sampling is not None:
@@ -228,7 +233,7 @@ class StepFunction:
             n_tokens=len(tokens), n_reqs=len(entries), n_want=W,
             token_ids=views[0], positions=views[1], tok_req=views[2], req_q_start=views[3],
             req_q_len=views[4], req_kv_len=views[5], req_slot=views[6], logits_rows=views[7],
-            decode_items=views[8], prefill_items=views[9], cache=self.cache, err=self.buffers.result[:4],
+            decode_items=views[8], prefill_items=views[9], prefill_tiles=views[10], cache=self.cache, err=self.buffers.result[:4],
             host_q_start=q_start, host_q_len=q_len, host_kv_len=kv_len, host_slot=slots,
             max_q_len=max(q_len), max_kv_len=max(kv_len))
         return batch, samp

@@ -100,22 +100,29 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
                     window: int | None) -> None:
     """Attention of every token of the step over the pages of its own request.
 
-    Chooses the kernels.  bfloat16 with a head_dim and page size the tiled kernels take:
-    single next tokens go to the split-K decode kernel, portions of prompts to the
-    general kernel.  float32, and every other shape, runs on the general kernel alone.
+    Chooses the kernels.  bfloat16 with a head_dim the tiled kernels take: single next
+    tokens go to the split-K decode kernel, portions of prompts to the flash prefill
+    kernel.  float32, and every other shape, runs on the general kernel.
     """
     n, hq, d = q.shape
     hkv, page = cache_view.k.shape[1], cache_view.k.shape[2]
-    tiled = q.dtype == torch.bfloat16 and ops.decode_kernel_takes(hq, hkv, d, page)
+    bf16 = q.dtype == torch.bfloat16
     n_dec = step.decode_items.numel()
-    if not tiled or n_dec == 0:
-        ops.attention_plain(q, out, cache_view.k, cache_view.v, step.positions, step.tok_req,
-                            step.req_slot, cache_view.table, step.err, scale=scale, window=window)
-        return
-    ops.attention_decode(q, out, cache_view.k, cache_view.v, step.decode_items, step.positions,
-                         step.tok_req, step.req_slot, cache_view.table, step.err, scale=scale,
-                         window=window, n_splits=ops.decode_splits(n_dec, hkv, step.max_kv_len))
-    if step.prefill_items.numel():
+    n_pf = step.prefill_items.numel()
+    dec_tiled = bf16 and n_dec > 0 and ops.decode_kernel_takes(hq, hkv, d, page)
+    pf_tiled = bf16 and n_pf > 0 and ops.prefill_kernel_takes(hq, hkv, d, page)
+    if dec_tiled:
+        ops.attention_decode(q, out, cache_view.k, cache_view.v, step.decode_items, step.positions,
+                             step.tok_req, step.req_slot, cache_view.table, step.err, scale=scale,
+                             window=window, n_splits=ops.decode_splits(n_dec, hkv, step.max_kv_len))
+    if pf_tiled:
+        ops.attention_prefill(q, out, cache_view.k, cache_view.v, step.prefill_tiles,
+                              step.req_q_start, step.req_q_len, step.req_kv_len, step.req_slot,
+                              cache_view.table, step.err, scale=scale, window=window)
+    dec_rest = n_dec > 0 and not dec_tiled
+    pf_rest = n_pf > 0 and not pf_tiled
+    if dec_rest or pf_rest:
+        items = None if (dec_rest and pf_rest) else (step.decode_items if dec_rest else step.prefill_items)
         ops.attention_plain(q, out, cache_view.k, cache_view.v, step.positions, step.tok_req,
                             step.req_slot, cache_view.table, step.err, scale=scale, window=window,
-                            items=step.prefill_items)
+                            items=items)
