@@ -205,7 +205,8 @@ def time_e2e(core, batch: int, steps: int, warmup: int, ctx_end: int, vocab: int
     """Decode tokens per second through ``LLM.generate``: host token ids in and out."""
     import torch
     from tokamak_b200 import LLM, SamplingParams
-    llm = LLM("<random>", _core=core, max_batch_size=batch, max_num_batched_tokens=PREFILL_TOKENS,
+    # a budget that takes every prompt in one step, so that all requests decode together
+    llm = LLM("<random>", _core=core, max_batch_size=batch, max_num_batched_tokens=batch * ctx_end,
               block_size=core.page_size)
     gen = torch.Generator().manual_seed(7)
     new_tokens = steps + warmup + 1
@@ -215,7 +216,8 @@ def time_e2e(core, batch: int, steps: int, warmup: int, ctx_end: int, vocab: int
     outs = llm.generate(prompt_token_ids=prompts, sampling_params=params)
     assert all(len(o.output_token_ids) == new_tokens for o in outs)
     times = llm.last_stats["decode_step_times"]
-    full = [t for t in times][-steps:]            # the last K decode steps, all at full batch
+    assert len(times) >= steps + warmup, "the requests did not decode together"
+    full = times[-steps:]                         # the last K decode steps, all at full batch
     tok_s = batch * len(full) / sum(full)
     h2d = 4 * (8 * batch + 5 * batch)             # step description + sampling rows, int32 words
     d2h = 4 * (4 + batch)
@@ -256,7 +258,7 @@ def main() -> int:
     max_batch = 64 if not args.skip_points else max(args.batch, 1)
     core = random_core(raw, seed=0, std=0.02, dtype="bfloat16", max_seq_len=CONTEXT, page_size=16,
                        pool_tokens=max_batch * CONTEXT, max_slots=max_batch,
-                       max_step_tokens=PREFILL_TOKENS)
+                       max_step_tokens=max(PREFILL_TOKENS, args.batch * CONTEXT))
     wbytes = weight_bytes(core)
 
     sampler = ClockSampler(torch.cuda.current_device())

@@ -1,0 +1,337 @@
+"""Each part of a layer alone against the plain functions, the schedule as data, and a toy
+mixer with state of its own that is registered, built and stepped from the test alone."""
+
+from __future__ import annotations
+
+import json
+from dataclasses import dataclass
+
+import numpy as np
+import pytest
+import torch
+
+import traces
+from helpers import assert_logits_close, random_tokens
+from plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def runtime(dtype):
+    from tokamak_b200.parts.base import Runtime
+    return Runtime(device=torch.device("cuda", 0), dtype=dtype)
+
+
+def tol(dtype):
+    return dict(rtol=3e-5, atol=3e-5) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)
+
+
+# ----------------------------------------------------------------------------- single parts
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_part(dtype):
+    from tokamak_b200.parts.norm import RMSNorm, RMSNormSpec
+    spec = RMSNormSpec(dim=200, eps=1e-5)
+    assert RMSNorm.expected_tensors(spec, "n.weight")["n.weight"].shape == (200,)
+    w = 1 + 0.1 * torch.randn(200, device=DEV)
+    part = RMSNorm(spec, "n.weight", {"n.weight": w}, runtime(dtype))
+    resid = torch.randn(9, 200, device=DEV)
+    delta = torch.randn(9, 200, device=DEV).to(dtype)
+    want_sum = resid.double() + delta.double()
+    out = part.add_norm(resid, delta)
+    assert out.dtype == dtype
+    torch.testing.assert_close(resid.double(), want_sum, rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(out.double(), plain.rms_norm(want_sum, w.double(), 1e-5), **tol(dtype))
+
+
+def test_position_parts():
+    from tokamak_b200.parts.position import NoPosition, NoPositionSpec, RopeNeox, RopeSpec
+    rope = RopeNeox(RopeSpec(head_dim=48, theta=50000.0), runtime(torch.float32))
+    inv_freq, rotary_dim = rope.rotary_table()
+    want = 1.0 / (50000.0 ** (torch.arange(0, 48, 2, dtype=torch.float32) / 48))
+    assert rotary_dim == 48 and torch.equal(inv_freq.cpu(), want)
+    assert NoPosition(NoPositionSpec(), runtime(torch.float32)).rotary_table() == (None, 0)
+    with pytest.raises(ValueError):
+        RopeNeox(RopeSpec(head_dim=15, theta=1e4), runtime(torch.float32))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_part(dtype):
+    from tokamak_b200.parts.feedforward import SwiGLU, SwiGLUSpec
+    spec = SwiGLUSpec(hidden_size=72, intermediate_size=136)
+    names = SwiGLU.expected_tensors(spec, "mlp.")
+    assert names["mlp.down_proj.weight"].shape == (72, 136)
+    tensors = {n: (0.1 * torch.randn(r.shape, device=DEV)).to(dtype) for n, r in names.items()}
+    part = SwiGLU(spec, "mlp.", tensors, runtime(dtype))
+    x = torch.randn(11, 72, device=DEV).to(dtype)
+    got = part.forward(x, None)
+    want = plain.swiglu_mlp(x.double(), tensors["mlp.gate_proj.weight"].double(),
+                            tensors["mlp.up_proj.weight"].double(), tensors["mlp.down_proj.weight"].double())
+    torch.testing.assert_close(got.double(), want, **tol(dtype))
+
+
+class _Harness:
+    """A cache and a step function around one part, so that the part can be stepped alone."""
+
+    def __init__(self, need, dtype, page=8, pool_tokens=256, max_seq_len=256):
+        from tokamak_b200.cache.device import DeviceCache, plan_groups
+        from tokamak_b200.cache.manager import CacheManager
+        from tokamak_b200.engine.step import StepFunction
+        kv, st = plan_groups({"c": need}, pool_tokens, page)
+        self.manager = CacheManager(kv, st, 4)
+        self.cache = DeviceCache(self.manager, dtype, torch.device("cuda", 0), max_seq_len)
+        self.step = StepFunction(None, self.cache, 256, max_seq_len)
+
+    def batch(self, entries):
+        from tokamak_b200.engine.step import StepEntry
+        b, _ = self.step.build([StepEntry(r, [0] * n, []) for r, n in entries])
+        return b
+
+    def done(self, entries):
+        from tokamak_b200.engine.step import StepEntry
+        self.step.finish([StepEntry(r, [0] * n, []) for r, n in entries])
+        self.step.check_errors()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hq,hkv,d,window", [(6, 2, 32, None), (4, 1, 64, 9), (3, 3, 16, None)])
+def test_attention_part_alone_in_portions(dtype, hq, hkv, d, window):
+    """The attention mixer stepped in portions equals the plain attention block on the whole input."""
+    from tokamak_b200.parts.attention import Attention, AttentionSpec
+    from tokamak_b200.parts.position import RopeSpec
+    hidden, T = 40, 37
+    spec = AttentionSpec(hidden_size=hidden, num_heads=hq, num_kv_heads=hkv, head_dim=d,
+                         position=RopeSpec(d, 1e4), qk_norm_eps=1e-6, window=window)
+    names = Attention.expected_tensors(spec, "a.")
+    tensors = {}
+    for n, r in names.items():
+        t = torch.randn(r.shape, device=DEV)
+        tensors[n] = (1 + 0.1 * t) if r.role == "vector" else (0.15 * t).to(dtype)
+    part = Attention(spec, "a.", tensors, runtime(dtype))
+    x = torch.randn(T, hidden, device=DEV).to(dtype)
+    cfg = {"num_attention_heads": hq, "num_key_value_heads": hkv, "head_dim": d, "hidden_size": hidden,
+           "rms_norm_eps": 1e-6, "rope_theta": 1e4}
+    w64 = {k: v.double().cpu() for k, v in tensors.items()}
+    want = plain.attention_block(x.double().cpu(), torch.arange(T), w64, "a.", cfg, torch.float64,
+                                 window=window)
+    h = _Harness(part.cache_need(), dtype)
+    got, pos = [], 0
+    for n in (5, 1, 16, 2, 13):
+        b = h.batch([("r", n)])
+        got.append(part.forward(x[pos:pos + n].contiguous(), b, h.cache.view("c")))
+        h.done([("r", n)])
+        pos += n
+    torch.testing.assert_close(torch.cat(got).double().cpu(), want, **tol(dtype))
+
+
+def test_schedule_names_a_block_twice_and_shares_a_cache():
+    """The order of layers is data: block b0 runs twice with caches of its own, and block b1,
+    built without key and value projections, reads the cache that the first call wrote."""
+    from tokamak_b200.cache.device import DeviceCache, plan_groups
+    from tokamak_b200.cache.manager import CacheManager
+    from tokamak_b200.engine.step import StepEntry, StepFunction
+    from tokamak_b200.models.decoder import DecoderModel, LayerCall, ModelSpec
+    from tokamak_b200.parts.attention import AttentionSpec
+    from tokamak_b200.parts.block import PreNormBlockSpec
+    from tokamak_b200.parts.embedding import EmbeddingSpec, HeadSpec
+    from tokamak_b200.parts.feedforward import SwiGLUSpec
+    from tokamak_b200.parts.norm import RMSNormSpec
+    from tokamak_b200.parts.position import RopeSpec
+    from tokamak_b200.weights import random_tensors
+
+    H, V, d, hq, hkv, inter, eps = 48, 97, 16, 4, 2, 80, 1e-6
+    norm = RMSNormSpec(H, eps)
+
+    def block(name, own_kv):
+        return PreNormBlockSpec(
+            name=name, norm1=norm, norm2=norm,
+            mixer=AttentionSpec(H, hq, hkv, d, RopeSpec(d, 1e4), qk_norm_eps=eps, own_kv=own_kv),
+            feed_forward=SwiGLUSpec(H, inter), norm1_name=f"{name}.n1", mixer_prefix=f"{name}.attn.",
+            norm2_name=f"{name}.n2", ffn_prefix=f"{name}.mlp.")
+
+    spec = ModelSpec(embedding=EmbeddingSpec(V, H, "embed"), blocks=(block("b0", True), block("b1", False)),
+                     schedule=(LayerCall("b0", "first"), LayerCall("b1", "first"), LayerCall("b0", "second")),
+                     final_norm=norm, final_norm_name="final", head=HeadSpec(V, H, tied=True))
+    expected = DecoderModel.expected_tensors(spec)
+    assert "b1.attn.k_proj.weight" not in expected and "b0.attn.k_proj.weight" in expected
+    tensors = random_tensors(expected, seed=9, std=0.08, dtype=torch.float32, device="cuda")
+    model = DecoderModel(spec, tensors, runtime(torch.float32))
+    needs = model.cache_needs()
+    assert set(needs) == {"first", "second"}
+    kv, st = plan_groups(needs, 128, 8)
+    assert len(kv) == 1 and sorted(kv[0].cache_keys) == ["first", "second"]      # one group, two slabs
+    cache = DeviceCache(CacheManager(kv, st, 2), torch.float32, torch.device("cuda", 0), 128)
+    step = StepFunction(model, cache, 128, 128)
+    ids = random_tokens(V, 30, seed=1)
+    got = torch.cat([step.run([StepEntry("r", ids[:11], list(range(11)))]),
+                     step.run([StepEntry("r", ids[11:], list(range(19)))])]).double().cpu()
+
+    # the same computation with the plain functions
+    w = {k: v.double().cpu() for k, v in tensors.items()}
+    cfg = {"num_attention_heads": hq, "num_key_value_heads": hkv, "head_dim": d, "hidden_size": H,
+           "rms_norm_eps": eps, "rope_theta": 1e4}
+    pos = torch.arange(30)
+    x = w["embed"][torch.tensor(ids)]
+    cos, sin = plain.rope_tables(pos, d, 1e4, torch.float64)
+
+    def mlp(x, name):
+        h = plain.rms_norm(x, w[f"{name}.n2"], eps)
+        return x + plain.swiglu_mlp(h, w[f"{name}.mlp.gate_proj.weight"], w[f"{name}.mlp.up_proj.weight"],
+                                    w[f"{name}.mlp.down_proj.weight"])
+
+    def b0(x):
+        h = plain.rms_norm(x, w["b0.n1"], eps)
+        return mlp(x + plain.attention_block(h, pos, w, "b0.attn.", cfg, torch.float64), "b0")
+
+    # first call of b0: remember its keys and values for b1
+    h0 = plain.rms_norm(x, w["b0.n1"], eps)
+    k0 = plain.apply_rope(plain.rms_norm((h0 @ w["b0.attn.k_proj.weight"].T).view(30, hkv, d),
+                                         w["b0.attn.k_norm.weight"], eps), cos, sin)
+    v0 = (h0 @ w["b0.attn.v_proj.weight"].T).view(30, hkv, d)
+    x = b0(x)
+    h1 = plain.rms_norm(x, w["b1.n1"], eps)
+    q1 = plain.apply_rope(plain.rms_norm((h1 @ w["b1.attn.q_proj.weight"].T).view(30, hq, d),
+                                         w["b1.attn.q_norm.weight"], eps), cos, sin)
+    a1 = plain.causal_attention(q1, k0, v0).reshape(30, hq * d) @ w["b1.attn.o_proj.weight"].T
+    x = mlp(x + a1, "b1")
+    x = b0(x)
+    want = plain.rms_norm(x, w["final"], eps) @ w["embed"].T
+    torch.testing.assert_close(got, want, rtol=2e-4, atol=2e-4)
+
+
+# ----------------------------------------------------------------------------- a toy architecture
+
+@dataclass(frozen=True)
+class DecaySumSpec:
+    """A mixer with state of its own: s_t = decay * s_{t-1} + x_t, y_t = s_t W^T."""
+    hidden_size: int
+    decay: float
+    kind: str = "toy_decay_sum"
+
+
+class DecaySum:
+    def __init__(self, spec, prefix, tensors, rt):
+        self.spec, self.rt = spec, rt
+        self.w = tensors[prefix + "mix.weight"]
+
+    @staticmethod
+    def expected_tensors(spec, prefix):
+        from tokamak_b200.parts.base import TensorReq
+        return {prefix + "mix.weight": TensorReq((spec.hidden_size, spec.hidden_size))}
+
+    def cache_need(self):
+        from tokamak_b200.cache.manager import StateNeed
+        return StateNeed((self.spec.hidden_size,), "float32")
+
+    def forward(self, h, step, cache_view):
+        from tokamak_b200.parts.base import linear
+        records = cache_view.records                       # [max_slots, hidden] float32
+        out = torch.empty_like(h, dtype=torch.float32)
+        for start, n, slot in zip(step.host_q_start, step.host_q_len, step.host_slot):
+            s = records[slot]
+            for t in range(start, start + n):              # a toy: one token at a time
+                s = self.spec.decay * s + h[t].float()
+                out[t] = s
+            records[slot] = s
+        return linear(out.to(h.dtype), self.w)
+
+
+TOY_CONFIG = {"architectures": ["ToyDecayForCausalLM"], "vocab_size": 131, "hidden_size": 56,
+              "heads": 2, "head_dim": 16, "inter": 72, "eps": 1e-6, "theta": 10000.0, "decay": 0.8,
+              "max_position_embeddings": 256}
+
+
+def _toy_architecture():
+    """An architecture of one attention block and one decay-sum block, described from outside."""
+    from tokamak_b200.config import Architecture
+    from tokamak_b200.models.decoder import LayerCall, ModelSpec
+    from tokamak_b200.parts.attention import AttentionSpec
+    from tokamak_b200.parts.block import PreNormBlockSpec
+    from tokamak_b200.parts.embedding import EmbeddingSpec, HeadSpec
+    from tokamak_b200.parts.feedforward import SwiGLUSpec
+    from tokamak_b200.parts.norm import RMSNormSpec
+    from tokamak_b200.parts.position import RopeSpec
+
+    @dataclass(frozen=True)
+    class ToyConfig:
+        raw: tuple
+        architecture: str = "ToyDecayForCausalLM"
+        eos_token_ids: tuple = ()
+
+        def __getattr__(self, name):
+            return dict(self.raw)[name]
+
+    def parse_config(raw, eos_token_ids=None):
+        return ToyConfig(tuple((k, v) for k, v in raw.items() if k != "architectures"))
+
+    def model_spec(cfg):
+        H, norm = cfg.hidden_size, RMSNormSpec(cfg.hidden_size, cfg.eps)
+        ffn = SwiGLUSpec(H, cfg.inter)
+        attn = AttentionSpec(H, cfg.heads, cfg.heads, cfg.head_dim, RopeSpec(cfg.head_dim, cfg.theta),
+                             qk_norm_eps=cfg.eps)
+        blocks = (
+            PreNormBlockSpec("l0", norm, attn, norm, ffn, "l0.n1", "l0.attn.", "l0.n2", "l0.mlp."),
+            PreNormBlockSpec("l1", norm, DecaySumSpec(H, cfg.decay), norm, ffn, "l1.n1", "l1.", "l1.n2",
+                             "l1.mlp."),
+        )
+        return ModelSpec(EmbeddingSpec(cfg.vocab_size, H, "embed"), blocks,
+                         (LayerCall("l0", "l0"), LayerCall("l1", "l1")), norm, "final",
+                         HeadSpec(cfg.vocab_size, H, tied=False, name="head"))
+
+    return Architecture("ToyDecayForCausalLM", parse_config, model_spec)
+
+
+def _toy_plain_logits(folder, ids):
+    cfg, w = plain.load_folder(folder)
+    w = {k: v.double() for k, v in w.items()}
+    c = {"num_attention_heads": cfg["heads"], "num_key_value_heads": cfg["heads"], "head_dim": cfg["head_dim"],
+         "hidden_size": cfg["hidden_size"], "rms_norm_eps": cfg["eps"], "rope_theta": cfg["theta"]}
+    T, eps = len(ids), cfg["eps"]
+    x = w["embed"][torch.tensor(ids)]
+    mlp = lambda x, n: x + plain.swiglu_mlp(plain.rms_norm(x, w[f"{n}.n2"], eps), w[f"{n}.mlp.gate_proj.weight"],
+                                            w[f"{n}.mlp.up_proj.weight"], w[f"{n}.mlp.down_proj.weight"])
+    x = x + plain.attention_block(plain.rms_norm(x, w["l0.n1"], eps), torch.arange(T), w, "l0.attn.", c,
+                                  torch.float64)
+    x = mlp(x, "l0")
+    h = plain.rms_norm(x, w["l1.n1"], eps)
+    s = torch.zeros(cfg["hidden_size"], dtype=torch.float64)
+    states = []
+    for t in range(T):
+        s = cfg["decay"] * s + h[t]
+        states.append(s)
+    x = mlp(x + torch.stack(states) @ w["l1.mix.weight"].T, "l1")
+    return plain.rms_norm(x, w["final"], eps) @ w["head"].T
+
+
+def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
+    """Nothing in the framework's files knows this mixer or this architecture: the test registers
+    both, writes a model folder with the framework's writer, and replays it whole, in portions
+    and mixed with other requests through the ordinary engine; slots of ended requests are
+    handed to new ones, whose state must start from zero."""
+    from tokamak_b200.config import register_architecture
+    from tokamak_b200.engine.replay import build_core, run_step
+    from tokamak_b200.parts.base import MIXERS
+    from tokamak_b200.weights import write_random_model
+
+    MIXERS.register("toy_decay_sum")(DecaySum)
+    register_architecture(_toy_architecture())
+    try:
+        folder = write_random_model(tmp_path / "toy", TOY_CONFIG, seed=3, std=0.08, dtype="float32")
+        assert json.loads((folder / "config.json").read_text())["architectures"] == ["ToyDecayForCausalLM"]
+        reqs = {f"t{i}": random_tokens(131, n, seed=50 + i) for i, n in enumerate([9, 40, 23, 64, 31, 17])}
+        truth = {rid: _toy_plain_logits(folder, ids) for rid, ids in reqs.items()}
+        for builder, kw in ((traces.whole, {}), (traces.portions, {}),
+                            (traces.mixed, {"max_tokens": 192, "max_live": 3, "seed": 2})):
+            core = build_core(folder, "float32", 192, page_size=16, max_live=3)
+            assert len(core.manager.state_groups) == 1 and len(core.manager.kv_groups) == 1
+            records, rows = builder(reqs, **kw)
+            for rec in records:
+                out = run_step(core, rec)
+                got = torch.from_numpy(out)
+                want = torch.stack([truth[rid][p] for rid, p in rows[rec["step"]]])
+                assert_logits_close(got, want, "float32", f"toy {builder.__name__} step {rec['step']}")
+            assert not core.manager.live_requests()
+    finally:
+        MIXERS.unregister("toy_decay_sum")
