@@ -225,6 +225,85 @@ def time_e2e(core, batch: int, steps: int, warmup: int, ctx_end: int, vocab: int
             "ms_per_step": 1e3 * sum(full) / len(full)}
 
 
+def kernel_case(name: str, batch: int, ctx: int, iters: int, peaks: dict) -> dict:
+    """One kernel alone on inputs larger than L2, timed with CUDA events: achieved bytes or flops
+    per second against the peak.  Also the small case that ncu captures are made on."""
+    import torch
+    from tokamak_b200.csrc import ops
+    dev = "cuda"
+    cfg = QWEN3_8B
+    hq, hkv, d, page = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], 16
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    err = torch.zeros(4, dtype=torch.int32, device=dev)
+    gen = torch.Generator(device=dev).manual_seed(0)
+    flops = 0.0
+    if name in ("attention_decode", "attention_prefill"):
+        pages_per_req = -(-ctx // page)
+        num_pages = batch * pages_per_req
+        kc = torch.randn((num_pages, hkv, page, d), device=dev, generator=gen).bfloat16()
+        vc = torch.randn((num_pages, hkv, page, d), device=dev, generator=gen).bfloat16()
+        table = torch.randperm(num_pages, device=dev, generator=gen).to(torch.int32).view(batch, pages_per_req)
+        slots = i32(list(range(batch)))
+        if name == "attention_decode":
+            q = torch.randn((batch, hq, d), device=dev, generator=gen).bfloat16()
+            out = torch.empty_like(q)
+            items, tok_req = i32(list(range(batch))), i32(list(range(batch)))
+            positions = i32([ctx - 1] * batch)
+            n_splits = ops.decode_splits(batch, hkv, ctx)
+            scratch = torch.empty(batch * hq * n_splits * (d + 2), dtype=torch.float32, device=dev)
+            run = lambda: ops.attention_decode(q, out, kc, vc, items, positions, tok_req, slots, table, err,
+                                               scale=d ** -0.5, window=None, n_splits=n_splits, scratch=scratch)
+            nbytes = 2 * kc.numel() * 2 + 2 * q.numel() * 2
+        else:
+            q = torch.randn((batch * ctx, hq, d), device=dev, generator=gen).bfloat16()
+            out = torch.empty_like(q)
+            tiles = [(r, t) for t in reversed(range(-(-ctx // 64))) for r in range(batch)]
+            tiles_t = i32([x for rt in tiles for x in rt])
+            q_start, q_len = i32([r * ctx for r in range(batch)]), i32([ctx] * batch)
+            run = lambda: ops.attention_prefill(q, out, kc, vc, tiles_t, q_start, q_len, q_len, slots, table,
+                                                err, scale=d ** -0.5, window=None)
+            nbytes = 2 * kc.numel() * 2 + 2 * q.numel() * 2
+            flops = batch * 2.0 * 2.0 * (ctx * (ctx + 1) / 2) * hq * d
+    elif name == "rmsnorm":
+        n, h = batch, cfg["hidden_size"]
+        resid = torch.randn((n, h), device=dev, generator=gen)
+        delta = torch.randn((n, h), device=dev, generator=gen).bfloat16()
+        w = torch.ones(h, device=dev)
+        out = torch.empty((n, h), dtype=torch.bfloat16, device=dev)
+        run = lambda: ops.add_rmsnorm(resid, delta, w, out, 1e-6)
+        nbytes = n * h * (4 + 2 + 4 + 2)
+    elif name == "gemm_decode":
+        # the library product the decode step uses, for comparison: gate_up of one layer
+        w = torch.randn((2 * cfg["intermediate_size"], cfg["hidden_size"]), device=dev, generator=gen).bfloat16()
+        ws = [w.clone() for _ in range(4)]          # rotate over copies so that L2 holds none of them
+        x = torch.randn((batch, cfg["hidden_size"]), device=dev, generator=gen).bfloat16()
+        turn = [0]
+        def run():
+            turn[0] = (turn[0] + 1) % len(ws)
+            torch.mm(x, ws[turn[0]].t())
+        nbytes = w.numel() * 2
+    else:
+        raise SystemExit(f"unknown kernel case {name!r}")
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(iters):
+        run()
+    end.record()
+    torch.cuda.synchronize()
+    us = begin.elapsed_time(end) * 1e3 / iters
+    gbs = nbytes / (us * 1e-6) / 1e9
+    res = {"kernel": name, "batch": batch, "ctx": ctx, "us": round(us, 2), "bytes": nbytes,
+           "GB/s": round(gbs, 1), "hbm_frac": round(gbs / peaks["hbm_gbs"], 4), "peaks": peaks["source"]}
+    if flops:
+        tf = flops / (us * 1e-6) / 1e12
+        res.update({"TFLOP/s": round(tf, 1), "bf16_frac": round(tf / peaks["bf16_tflops"], 4)})
+    assert err.tolist()[0] == 0
+    return res
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -234,6 +313,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the 36 of Qwen3-8B")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
+    ap.add_argument("--kernel", default=None, help="time one kernel alone instead: attention_decode, "
+                    "attention_prefill, rmsnorm, gemm_decode")
+    ap.add_argument("--ctx", type=int, default=CONTEXT, help="context length of a --kernel case")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -246,6 +328,9 @@ def main() -> int:
         return 2
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
+    if args.kernel:
+        print(json.dumps(kernel_case(args.kernel, args.batch, args.ctx, steps, load_peaks())))
+        return 0
 
     import torch
     from tokamak_b200.engine.core import random_core

@@ -504,3 +504,42 @@ def test_attention_prefill_finds_the_one_key_that_matters(where):
         assert (out[-1] - hit).abs().max() > 0.1
     else:
         torch.testing.assert_close(out[-1], hit, rtol=5e-2, atol=5e-2)
+
+
+# ----------------------------------------------------------------------------- tcgen05 matrix product
+
+@pytest.mark.parametrize("tokens,n_out,k,splits", [(8, 300, 512, 1), (8, 256, 4096, 4), (1, 128, 64, 1),
+                                                    (64, 1000, 1536, 3), (16, 384, 96, 2), (33, 130, 200, 5)])
+def test_gemm_tcgen05_swapped_partials(tokens, n_out, k, splits):
+    """The weight as the 128-row operand: partials over K splits sum to x @ W^T."""
+    from tokamak_b200.csrc import ops
+    gen = torch.Generator().manual_seed(tokens + n_out)
+    x = torch.randn(tokens, k, generator=gen).bfloat16()
+    w = torch.randn(n_out, k, generator=gen).bfloat16()
+    err = err_word()
+    parts = ops.gemm_tc_swapped(w.to(DEV), x.to(DEV), err, splits)
+    torch.cuda.synchronize()
+    assert err.tolist()[0] == 0, err.tolist()
+    want = x.double() @ w.double().T
+    got = parts.double().sum(0).cpu()
+    torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-3 * (k ** 0.5) / 8)
+
+
+@pytest.mark.parametrize("tokens,n_out,k,bn,out_dtype", [(200, 384, 320, 128, torch.bfloat16),
+                                                          (128, 256, 64, 256, torch.float32),
+                                                          (2048, 512, 1024, 256, torch.bfloat16),
+                                                          (77, 317, 96, 64, torch.float32)])
+def test_gemm_tcgen05_tokens_as_rows(tokens, n_out, k, bn, out_dtype):
+    from tokamak_b200.csrc import ops
+    gen = torch.Generator().manual_seed(tokens + n_out)
+    x = torch.randn(tokens, k, generator=gen).bfloat16()
+    w = torch.randn(n_out, k, generator=gen).bfloat16()
+    err = err_word()
+    got = ops.gemm_tc(x.to(DEV), w.to(DEV), err, out_dtype=out_dtype, bn=bn)
+    torch.cuda.synchronize()
+    assert err.tolist()[0] == 0, err.tolist()
+    want = x.double() @ w.double().T
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(got.double().cpu(), want, rtol=1e-4, atol=1e-3 * (k ** 0.5) / 8)
+    else:
+        torch.testing.assert_close(got.double().cpu(), want, rtol=1e-2, atol=1e-2 * (k ** 0.5))

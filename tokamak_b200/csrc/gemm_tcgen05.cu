@@ -1,0 +1,357 @@
+// bfloat16 matrix product on the 5th-generation tensor cores:
+//   D[i, j] = sum_k R[i, k] * C[j, k]      (both operands K-major, float32 accumulation)
+//
+// One thread block per (128-row tile of R, BN-column tile of C, K split).  Operand
+// tiles of 64 k-elements travel global -> shared memory by TMA (cp.async.bulk.tensor,
+// 128-byte swizzle, no multicast) into a ring of stages guarded by mbarriers; one
+// elected thread issues tcgen05.mma (M = 128, N = BN, K = 16) with the accumulator in
+// tensor memory; four epilogue warps read the accumulator with tcgen05.ld and store it.
+//
+// Two uses:
+//  * decode ("swapped"): R = weight [N_out, K], C = activations [tokens <= 64, K].  The
+//    weights are the 128-row operand, so every byte of them is streamed exactly once
+//    through a deep TMA pipeline; the K range is split over blocks to fill the GPU, and
+//    each split stores a float32 partial [split, token, N_out] that the consuming kernel
+//    sums (norm, rotation, activation): no atomics, the sum order is fixed.
+//  * prefill: R = activations [tokens, K], C = weight [N_out, K], BN = 128 or 256,
+//    output rounded to bfloat16 (or kept float32) directly.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out records kErrWait, raises a
+// block-wide abort flag and the block leaves through the common exit that frees its
+// tensor memory.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace tk {
+
+constexpr int kGtBM = 128;        // rows of R per block = UMMA M
+constexpr int kGtBK = 64;         // k-elements per stage = one 128-byte swizzle span of bf16
+constexpr int kGtThreads = 192;   // warp 0: TMA, warp 1: MMA, warps 2..5: epilogue
+constexpr unsigned kGtSpinLimit = 1u << 22;
+
+struct GemmTcParams {
+  void* out;                // swapped: float [n_splits, cols_total, rows_total]; else [rows_total, cols_total]
+  int* err;
+  int rows_total;           // rows of R
+  int cols_total;           // rows of C (columns of D)
+  int k_total;
+  int bn;                   // UMMA N: 16..256, multiple of 16
+  int n_stages;
+  int n_splits;
+  int swapped;              // 1: store D transposed as float32 partials
+  int out_f32;              // non-swapped: 1 = float32 output, 0 = bfloat16
+  long long ld_out;         // non-swapped: elements between output rows
+};
+
+__device__ __forceinline__ uint32_t gt_smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity; false when the limit ran out or the block aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (unsigned spin = 0; spin < kGtSpinLimit; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((spin & 1023u) == 1023u && *abort_flag) return false;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
+// groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+  uint64_t desc = 0;
+  desc |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);          // start address, 16-byte units
+  desc |= (uint64_t)1 << 16;                                 // leading byte offset (unused for this layout)
+  desc |= (uint64_t)(1024 >> 4) << 32;                       // stride byte offset: 8 rows * 128 B
+  desc |= (uint64_t)1 << 46;                                 // descriptor version of sm_100
+  desc |= (uint64_t)2 << 61;                                 // layout: 128-byte swizzle
+  return desc;
+}
+
+// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = bn.
+__device__ __forceinline__ uint32_t umma_idesc_bf16(int bn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kGtBM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(kGtThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_c,
+                    GemmTcParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // the dynamic window is only guaranteed 16-byte aligned: round up to 1024 for the swizzle
+  const uint32_t raw = gt_smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* smem = smem_raw + (base - raw);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_r = blockIdx.x, tile_c = blockIdx.y, split = blockIdx.z;
+  const uint32_t r_bytes = kGtBM * kGtBK * 2;
+  const uint32_t c_bytes = (uint32_t)p.bn * kGtBK * 2;
+  const uint32_t stage_bytes = r_bytes + ((c_bytes + 1023u) & ~1023u);
+
+  // barriers and bookkeeping live behind the stages
+  unsigned char* ctrl = smem + (size_t)p.n_stages * stage_bytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
+  uint64_t* empty_bar = full_bar + p.n_stages;
+  uint64_t* accum_bar = empty_bar + p.n_stages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int kb_total = (p.k_total + kGtBK - 1) / kGtBK;
+  const int kb_per = (kb_total + p.n_splits - 1) / p.n_splits;
+  const int kb_begin = split * kb_per;
+  const int kb_end = min(kb_begin + kb_per, kb_total);
+  const int n_kb = max(kb_end - kb_begin, 0);
+  const uint32_t tmem_cols = p.bn < 32 ? 32u : (uint32_t)p.bn;   // bn is 16, 32, 64, 128 or 256
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.n_stages; ++s) {
+      mbar_init(gt_smem_u32(&full_bar[s]), 1);
+      mbar_init(gt_smem_u32(&empty_bar[s]), 1);
+    }
+    mbar_init(gt_smem_u32(accum_bar), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                 ::"r"(gt_smem_u32(tmem_slot)), "r"(tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---- TMA producer ---------------------------------------------------------------------
+    if (lane == 0) {
+      for (int i = 0; i < n_kb; ++i) {
+        const int s = i % p.n_stages;
+        const uint32_t round = (uint32_t)(i / p.n_stages);
+        if (round > 0 && !mbar_wait(gt_smem_u32(&empty_bar[s]), (round - 1) & 1u, abort_flag)) {
+          set_error(p.err, kErrWait, 0, i, s);
+          *abort_flag = 1;
+          break;
+        }
+        const uint32_t full = gt_smem_u32(&full_bar[s]);
+        const uint32_t dst = base + (uint32_t)s * stage_bytes;
+        mbar_expect_tx(full, r_bytes + c_bytes);
+        const int k0 = (kb_begin + i) * kGtBK;
+        tma_load_2d(dst, &map_r, k0, tile_r * kGtBM, full);
+        tma_load_2d(dst + r_bytes, &map_c, k0, tile_c * p.bn, full);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer -----------------------------------------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16(p.bn);
+      bool ok = true;
+      for (int i = 0; i < n_kb && ok; ++i) {
+        const int s = i % p.n_stages;
+        const uint32_t round = (uint32_t)(i / p.n_stages);
+        if (!mbar_wait(gt_smem_u32(&full_bar[s]), round & 1u, abort_flag)) {
+          set_error(p.err, kErrWait, 1, i, s);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const uint32_t a_addr = base + (uint32_t)s * stage_bytes;
+        const uint64_t desc_a = umma_desc_sw128(a_addr);
+        const uint64_t desc_b = umma_desc_sw128(a_addr + r_bytes);
+#pragma unroll
+        for (int k = 0; k < kGtBK / 16; ++k) {
+          // 16 k-elements = 32 bytes further inside the swizzle span: +2 in 16-byte units
+          umma_bf16(tmem_base, desc_a + (uint64_t)(2 * k), desc_b + (uint64_t)(2 * k), idesc,
+                    (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(gt_smem_u32(&empty_bar[s]));     // the stage may be refilled once these MMAs are done
+      }
+      if (ok) umma_commit(gt_smem_u32(accum_bar));  // the accumulator is complete
+    }
+  } else {
+    // ---- epilogue: warps 2..5, each owns the 32 accumulator lanes of its quarter --------------
+    const int quarter = warp & 3;
+    bool ok = true;
+    if (n_kb > 0) {
+      ok = mbar_wait(gt_smem_u32(accum_bar), 0u, abort_flag);
+      if (!ok && lane == 0) { set_error(p.err, kErrWait, 2, 0, 0); *abort_flag = 1; }
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const int row = tile_r * kGtBM + quarter * 32 + lane;      // row of R = lane of the accumulator
+    for (int c0 = 0; c0 < p.bn; c0 += 16) {
+      uint32_t v[16];
+      if (ok && n_kb > 0) {
+        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+      } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) v[e] = 0u;
+      }
+      if (row >= p.rows_total) continue;
+      if (p.swapped) {
+        float* part = reinterpret_cast<float*>(p.out) + (size_t)split * p.cols_total * p.rows_total;
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const int col = tile_c * p.bn + c0 + e;              // token
+          if (col < p.cols_total) part[(size_t)col * p.rows_total + row] = __uint_as_float(v[e]);
+        }
+      } else if (p.out_f32) {
+        float* orow = reinterpret_cast<float*>(p.out) + (size_t)row * p.ld_out;
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const int col = tile_c * p.bn + c0 + e;
+          if (col < p.cols_total) orow[col] = __uint_as_float(v[e]);
+        }
+      } else {
+        __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.ld_out;
+        const int col0 = tile_c * p.bn + c0;
+        if (col0 + 16 <= p.cols_total && (p.ld_out % 8) == 0) {
+          uint4 lo, hi;
+          __nv_bfloat162* l2 = reinterpret_cast<__nv_bfloat162*>(&lo);
+          __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&hi);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            l2[e] = __floats2bfloat162_rn(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1]));
+            h2[e] = __floats2bfloat162_rn(__uint_as_float(v[8 + 2 * e]), __uint_as_float(v[8 + 2 * e + 1]));
+          }
+          *reinterpret_cast<uint4*>(orow + col0) = lo;
+          *reinterpret_cast<uint4*>(orow + col0 + 8) = hi;
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            if (col0 + e < p.cols_total) orow[col0 + e] = __float2bfloat16_rn(__uint_as_float(v[e]));
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 2) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(tmem_cols)
+                 : "memory");
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+  }
+  return fn;
+}
+
+// Map of a row-major bf16 matrix [rows, k] (row stride ld elements) with boxes of box_rows x 64.
+static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long k, long long ld, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return (int)cudaErrorNotSupported;
+  if (((uintptr_t)ptr & 15u) != 0 || (ld * 2) % 16 != 0) return (int)cudaErrorInvalidValue;
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kGtBK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+}  // namespace tk
+
+// D = R * C^T on tcgen05.  r: [rows, k] bf16 (row stride ld_r), c: [cols, k] bf16 (row stride ld_c).
+// swapped = 1: out is float32 [n_splits, cols, rows] (partials, to be summed by the consumer).
+// swapped = 0: out is [rows, cols] with row stride ld_out, float32 if out_f32 else bfloat16; n_splits must be 1.
+TK_API int tk_gemm_bf16_tcgen05(const void* r, const void* c, void* out, int* err, int rows, int cols, int k,
+                                long long ld_r, long long ld_c, long long ld_out, int bn, int n_splits,
+                                int swapped, int out_f32, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (k <= 0 || k % 8 != 0 || (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) || n_splits < 1 ||
+      (!swapped && n_splits != 1)) {
+    return (int)cudaErrorInvalidValue;
+  }
+  CUtensorMap map_r, map_c;
+  int rc = tk::make_map(&map_r, r, rows, k, ld_r, tk::kGtBM);
+  if (rc != 0) return rc;
+  rc = tk::make_map(&map_c, c, cols, k, ld_c, bn);
+  if (rc != 0) return rc;
+
+  const unsigned r_bytes = tk::kGtBM * tk::kGtBK * 2;
+  const unsigned c_bytes = ((unsigned)bn * tk::kGtBK * 2 + 1023u) & ~1023u;
+  const unsigned stage_bytes = r_bytes + c_bytes;
+  const int kb_total = (k + tk::kGtBK - 1) / tk::kGtBK;
+  const int kb_per = (kb_total + n_splits - 1) / n_splits;
+  int n_stages = (int)((200u * 1024u) / stage_bytes);
+  if (n_stages > 8) n_stages = 8;
+  if (n_stages > kb_per) n_stages = kb_per < 2 ? 2 : kb_per;
+  const size_t smem_bytes = (size_t)n_stages * stage_bytes + 1024 /* alignment slack */ + 256 /* barriers */;
+
+  static size_t configured = 0;
+  if (smem_bytes > configured) {
+    cudaError_t e = cudaFuncSetAttribute(tk::gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)(220 * 1024));
+    if (e != cudaSuccess) return (int)e;
+    configured = 220 * 1024;
+  }
+  tk::GemmTcParams p;
+  p.out = out; p.err = err; p.rows_total = rows; p.cols_total = cols; p.k_total = k; p.bn = bn;
+  p.n_stages = n_stages; p.n_splits = n_splits; p.swapped = swapped; p.out_f32 = out_f32; p.ld_out = ld_out;
+  dim3 grid((rows + tk::kGtBM - 1) / tk::kGtBM, (cols + bn - 1) / bn, n_splits);
+  tk::gemm_tcgen05_kernel<<<grid, tk::kGtThreads, smem_bytes, stream>>>(map_r, map_c, p);
+  return (int)cudaGetLastError();
+}

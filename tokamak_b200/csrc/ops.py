@@ -258,6 +258,44 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
     return out
 
 
+def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_splits: int,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+    """Float32 partials ``[n_splits, tokens, N_out]`` of ``x @ weight^T`` on tcgen05, the weight
+    being the 128-row operand (for few tokens: every weight byte is streamed once by TMA).
+    The caller sums the partials."""
+    _want(weight, torch.bfloat16, "weight"); _want(x, torch.bfloat16, "x")
+    n_out, k = weight.shape
+    tokens, kx = x.shape
+    if k != kx or k % 8:
+        raise KernelError(f"inner sizes {k} and {kx} must agree and be a multiple of 8")
+    if tokens > 256:
+        raise KernelError("the swapped product takes at most 256 tokens")
+    bn = 16
+    while bn < tokens:
+        bn *= 2
+    if out is None:
+        out = torch.empty((n_splits, tokens, n_out), dtype=torch.float32, device=x.device)
+    _check(library().tk_gemm_bf16_tcgen05(weight.data_ptr(), x.data_ptr(), out.data_ptr(), err.data_ptr(),
+                                          n_out, tokens, k, k, k, 0, bn, n_splits, 1, 1, _stream()),
+           "gemm_tc_swapped")
+    return out
+
+
+def gemm_tc(x: torch.Tensor, weight: torch.Tensor, err: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+            bn: int = 128) -> torch.Tensor:
+    """``x @ weight^T`` on tcgen05 with the tokens as the 128-row operand; output ``[tokens, N_out]``."""
+    _want(weight, torch.bfloat16, "weight"); _want(x, torch.bfloat16, "x")
+    n_out, k = weight.shape
+    tokens, kx = x.shape
+    if k != kx or k % 8:
+        raise KernelError(f"inner sizes {k} and {kx} must agree and be a multiple of 8")
+    out = torch.empty((tokens, n_out), dtype=out_dtype, device=x.device)
+    _check(library().tk_gemm_bf16_tcgen05(x.data_ptr(), weight.data_ptr(), out.data_ptr(), err.data_ptr(),
+                                          tokens, n_out, k, k, k, n_out, bn, 1, 0,
+                                          1 if out_dtype == torch.float32 else 0, _stream()), "gemm_tc")
+    return out
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
            seed: torch.Tensor, counter: torch.Tensor, out_tokens: torch.Tensor) -> None:
     """One token per row of float32 logits; see sampling.cu for the exact rule."""
