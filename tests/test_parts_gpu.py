@@ -100,6 +100,7 @@ class _Harness:
 def test_attention_part_alone_in_portions(dtype, hq, hkv, d, window):
     """The attention mixer stepped in portions equals the plain attention block on the whole input."""
     from tokamak_b200.parts.attention import Attention, AttentionSpec
+    from tokamak_b200.parts.base import sum_parts
     from tokamak_b200.parts.position import RopeSpec
     hidden, T = 40, 37
     spec = AttentionSpec(hidden_size=hidden, num_heads=hq, num_kv_heads=hkv, head_dim=d,
@@ -120,7 +121,7 @@ def test_attention_part_alone_in_portions(dtype, hq, hkv, d, window):
     got, pos = [], 0
     for n in (5, 1, 16, 2, 13):
         b = h.batch([("r", n)])
-        got.append(part.forward(x[pos:pos + n].contiguous(), b, h.cache.view("c")))
+        got.append(sum_parts(part.forward(x[pos:pos + n].contiguous(), b, h.cache.view("c"))).to(dtype))
         h.done([("r", n)])
         pos += n
     torch.testing.assert_close(torch.cat(got).double().cpu(), want, **tol(dtype))

@@ -31,6 +31,7 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
 // over the positions whose logits are wanted).
 template <typename TOut, typename TDelta>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TDelta* __restrict__ delta,
+                                   const float* __restrict__ parts, int n_parts, size_t part_stride,
                                    const float* __restrict__ weight, TOut* __restrict__ out,
                                    const int* __restrict__ rows, int hidden, float eps) {
   __shared__ float scratch[32];
@@ -38,11 +39,19 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TDelta* __re
   const int r = rows ? rows[i] : i;
   float* x = resid + (size_t)r * hidden;
   const TDelta* d = delta ? delta + (size_t)r * hidden : nullptr;
-  const bool write_back = (rows == nullptr) && (d != nullptr);
+  const float* ps = parts ? parts + (size_t)r * hidden : nullptr;
+  const bool has_delta = (d != nullptr) || (ps != nullptr);
+  const bool write_back = (rows == nullptr) && has_delta;
+  auto branch = [&](int h) -> float {
+    if (d) return to_f32<TDelta>(d[h]);
+    float acc = 0.0f;
+    for (int s = 0; s < n_parts; ++s) acc += ps[(size_t)s * part_stride + h];
+    return acc;
+  };
   float ss = 0.0f;
   for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
     float v = x[h];
-    if (d) v += to_f32<TDelta>(d[h]);
+    if (has_delta) v += branch(h);
     if (write_back) x[h] = v;
     ss += v * v;
   }
@@ -51,10 +60,10 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TDelta* __re
   TOut* o = out + (size_t)i * hidden;
   for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
     float v;
-    if (write_back || d == nullptr) {
+    if (write_back || !has_delta) {
       v = x[h];
     } else {
-      v = x[h] + to_f32<TDelta>(d[h]);
+      v = x[h] + branch(h);
     }
     o[h] = from_f32<TOut>(v * rstd * weight[h]);
   }
@@ -93,6 +102,7 @@ template <> struct Vec8<__nv_bfloat16> {
 
 template <typename T, int ITERS>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                       const float* __restrict__ parts, int n_parts, size_t part_stride,
                                        const float* __restrict__ weight, T* __restrict__ out,
                                        const int* __restrict__ rows, int hidden, float eps) {
   __shared__ float scratch[32];
@@ -100,7 +110,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
   const int r = rows ? rows[i] : i;
   float* x = resid + (size_t)r * hidden;
   const T* d = delta ? delta + (size_t)r * hidden : nullptr;
-  const bool write_back = (rows == nullptr) && (d != nullptr);
+  const float* ps = parts ? parts + (size_t)r * hidden : nullptr;
+  const bool write_back = (rows == nullptr) && (d != nullptr || ps != nullptr);
   float v[ITERS][8];
   float ss = 0.0f;
 #pragma unroll
@@ -113,6 +124,13 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
         Vec8<T>::load(d + h, dv);
 #pragma unroll
         for (int e = 0; e < 8; ++e) v[it][e] += dv[e];
+      } else if (ps) {
+        for (int s = 0; s < n_parts; ++s) {
+          float dv[8];
+          Vec8<float>::load(ps + (size_t)s * part_stride + h, dv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[it][e] += dv[e];
+        }
       }
       if (write_back) Vec8<float>::store(x + h, v[it]);
 #pragma unroll
@@ -137,14 +155,24 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
 
 // out[t, j] = silu(gu[t, j]) * gu[t, inter + j]           (src/tokamak/model/layers.py:103)
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, const float* __restrict__ parts, int n_parts,
+                              size_t part_stride, T* __restrict__ out, int inter, size_t total) {
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (; idx < total; idx += stride) {
     const size_t t = idx / inter;
     const int j = (int)(idx - t * inter);
-    const float g = to_f32<T>(gu[t * 2 * inter + j]);
-    const float u = to_f32<T>(gu[t * 2 * inter + inter + j]);
+    float g, u;
+    if (parts == nullptr) {
+      g = to_f32<T>(gu[t * 2 * inter + j]);
+      u = to_f32<T>(gu[t * 2 * inter + inter + j]);
+    } else {
+      g = 0.0f; u = 0.0f;
+      for (int s = 0; s < n_parts; ++s) {
+        g += parts[s * part_stride + t * 2 * inter + j];
+        u += parts[s * part_stride + t * 2 * inter + inter + j];
+      }
+    }
     const float s = g / (1.0f + expf(-g));
     out[idx] = from_f32<T>(s * u);
   }
@@ -162,10 +190,13 @@ TK_API int tk_embed_gather(const void* table, int dtype, const int* ids, float* 
   return (int)cudaGetLastError();
 }
 
-TK_API int tk_add_rmsnorm(float* resid, const void* delta, const float* weight, void* out,
-                          const int* rows, int n_rows, int hidden, float eps, int dtype,
-                          cudaStream_t stream) {
+// delta: branch output in the activation type, or null.  parts: float32 partial sums of the
+// branch output [n_parts, rows of resid, hidden] (part_stride elements apart), or null.
+TK_API int tk_add_rmsnorm(float* resid, const void* delta, const float* parts, int n_parts,
+                          long long part_stride, const float* weight, void* out, const int* rows,
+                          int n_rows, int hidden, float eps, int dtype, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
+  if (parts != nullptr && (delta != nullptr || n_parts < 1)) return (int)cudaErrorInvalidValue;
   if (hidden % 8 == 0 && hidden <= 4 * 512 * 8) {
     // one pass with the row in registers: threads * 8 * ITERS >= hidden
     int threads = ((hidden / 8 + 31) / 32) * 32;
@@ -176,7 +207,8 @@ TK_API int tk_add_rmsnorm(float* resid, const void* delta, const float* weight, 
 #define TK_LAUNCH_VEC(IT)                                                                       \
     TK_DISPATCH_DTYPE(dtype, T,                                                                 \
                       (tk::add_rmsnorm_vec_kernel<T, IT><<<n_rows, threads, 0, stream>>>(        \
-                          resid, (const T*)delta, weight, (T*)out, rows, hidden, eps)))
+                          resid, (const T*)delta, parts, n_parts, (size_t)part_stride, weight,  \
+                          (T*)out, rows, hidden, eps)))
     if (iters == 1) { TK_LAUNCH_VEC(1); } else if (iters == 2) { TK_LAUNCH_VEC(2); } else { TK_LAUNCH_VEC(4); }
 #undef TK_LAUNCH_VEC
     return (int)cudaGetLastError();
@@ -184,12 +216,13 @@ TK_API int tk_add_rmsnorm(float* resid, const void* delta, const float* weight, 
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   TK_DISPATCH_DTYPE(dtype, T,
                     (tk::add_rmsnorm_kernel<T, T><<<n_rows, threads, 0, stream>>>(
-                        resid, (const T*)delta, weight, (T*)out, rows, hidden, eps)));
+                        resid, (const T*)delta, parts, n_parts, (size_t)part_stride, weight, (T*)out,
+                        rows, hidden, eps)));
   return (int)cudaGetLastError();
 }
 
-TK_API int tk_swiglu(const void* gate_up, void* out, int n_tokens, int inter, int dtype,
-                     cudaStream_t stream) {
+TK_API int tk_swiglu(const void* gate_up, const float* parts, int n_parts, long long part_stride,
+                     void* out, int n_tokens, int inter, int dtype, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   const size_t total = (size_t)n_tokens * inter;
   const int threads = 256;
@@ -197,6 +230,6 @@ TK_API int tk_swiglu(const void* gate_up, void* out, int n_tokens, int inter, in
   if (blocks > 148 * 16) blocks = 148 * 16;
   TK_DISPATCH_DTYPE(dtype, T,
                     tk::swiglu_kernel<T><<<(int)blocks, threads, 0, stream>>>(
-                        (const T*)gate_up, (T*)out, inter, total));
+                        (const T*)gate_up, parts, n_parts, (size_t)part_stride, (T*)out, inter, total));
   return (int)cudaGetLastError();
 }

@@ -319,7 +319,7 @@ static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long
 // swapped = 0: out is [rows, cols] with row stride ld_out, float32 if out_f32 else bfloat16; n_splits must be 1.
 TK_API int tk_gemm_bf16_tcgen05(const void* r, const void* c, void* out, int* err, int rows, int cols, int k,
                                 long long ld_r, long long ld_c, long long ld_out, int bn, int n_splits,
-                                int swapped, int out_f32, cudaStream_t stream) {
+                                int swapped, int out_f32, int max_stages, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;
   if (k <= 0 || k % 8 != 0 || (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) || n_splits < 1 ||
       (!swapped && n_splits != 1)) {
@@ -338,6 +338,7 @@ TK_API int tk_gemm_bf16_tcgen05(const void* r, const void* c, void* out, int* er
   const int kb_per = (kb_total + n_splits - 1) / n_splits;
   int n_stages = (int)((200u * 1024u) / stage_bytes);
   if (n_stages > 8) n_stages = 8;
+  if (max_stages > 0 && n_stages > max_stages) n_stages = max_stages;
   if (n_stages > kb_per) n_stages = kb_per < 2 ? 2 : kb_per;
   const size_t smem_bytes = (size_t)n_stages * stage_bytes + 1024 /* alignment slack */ + 256 /* barriers */;
 

@@ -66,12 +66,21 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, resid: torch.Tensor, er
 
 def add_rmsnorm(resid: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor,
                 out: torch.Tensor, eps: float, rows: torch.Tensor | None = None) -> None:
-    """x = resid (+ delta), written back unless ``rows`` is given; out = weight * x * rsqrt(mean x^2 + eps)."""
+    """x = resid (+ delta), written back unless ``rows`` is given; out = weight * x * rsqrt(mean x^2 + eps).
+
+    ``delta`` is the branch output in the activation type, or a 3-D float32 tensor of partial
+    sums ``[parts, tokens, hidden]`` (from a split-K product) that the kernel adds up."""
     _want(resid, torch.float32, "resid"); _want(weight, torch.float32, "weight"); _want(out, None, "out")
     hidden = resid.shape[-1]
     if weight.numel() != hidden or out.shape[-1] != hidden:
         raise KernelError("norm width mismatch")
-    if delta is not None:
+    parts, n_parts, part_stride = None, 0, 0
+    if delta is not None and delta.dim() == 3:
+        _want(delta, torch.float32, "delta partial sums")
+        if delta.shape[1:] != resid.shape:
+            raise KernelError("partial sums and resid differ in shape")
+        parts, n_parts, part_stride, delta = delta, delta.shape[0], delta.stride(0), None
+    elif delta is not None:
         _want(delta, out.dtype, "delta")
         if delta.shape != resid.shape:
             raise KernelError("delta and resid differ in shape")
@@ -82,19 +91,29 @@ def add_rmsnorm(resid: torch.Tensor, delta: torch.Tensor | None, weight: torch.T
         n_rows = resid.numel() // hidden
     if out.numel() < n_rows * hidden:
         raise KernelError("out is too small")
-    _check(library().tk_add_rmsnorm(resid.data_ptr(), _ptr(delta), weight.data_ptr(), out.data_ptr(),
-                                    _ptr(rows), n_rows, hidden, float(eps), dtype_code(out.dtype),
-                                    _stream()), "add_rmsnorm")
+    _check(library().tk_add_rmsnorm(resid.data_ptr(), _ptr(delta), _ptr(parts), n_parts, part_stride,
+                                    weight.data_ptr(), out.data_ptr(), _ptr(rows), n_rows, hidden,
+                                    float(eps), dtype_code(out.dtype), _stream()), "add_rmsnorm")
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, j] = silu(gate_up[t, j]) * gate_up[t, I + j]."""
-    _want(gate_up, None, "gate_up"); _want(out, gate_up.dtype, "out")
-    n, two_i = gate_up.shape
+    """out[t, j] = silu(gate_up[t, j]) * gate_up[t, I + j]; ``gate_up`` may be float32 partial
+    sums ``[parts, tokens, 2I]`` that the kernel adds up first."""
+    _want(gate_up, None, "gate_up"); _want(out, None, "out")
+    parts, n_parts, part_stride = None, 0, 0
+    if gate_up.dim() == 3:
+        _want(gate_up, torch.float32, "gate_up partial sums")
+        parts, n_parts, part_stride = gate_up, gate_up.shape[0], gate_up.stride(0)
+        n, two_i = gate_up.shape[1:]
+        gate_up = None
+    else:
+        if gate_up.dtype != out.dtype:
+            raise KernelError("gate_up and out differ in element type")
+        n, two_i = gate_up.shape
     if two_i % 2 or out.shape != (n, two_i // 2):
         raise KernelError("swiglu shape mismatch")
-    _check(library().tk_swiglu(gate_up.data_ptr(), out.data_ptr(), n, two_i // 2,
-                               dtype_code(out.dtype), _stream()), "swiglu")
+    _check(library().tk_swiglu(_ptr(gate_up), _ptr(parts), n_parts, part_stride, out.data_ptr(), n,
+                               two_i // 2, dtype_code(out.dtype), _stream()), "swiglu")
 
 
 def rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | None,
@@ -103,10 +122,21 @@ def rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | None
             k_norm_w: torch.Tensor | None, inv_freq: torch.Tensor | None, err: torch.Tensor, *,
             n_q_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int, eps: float,
             write_kv: bool = True) -> None:
-    """Per-head norm of q and k, rotation, and the write of k and v into their pages."""
-    _want(qkv, None, "qkv"); _want(q_out, qkv.dtype, "q_out")
-    n = qkv.shape[0]
-    row = qkv.shape[1]
+    """Per-head norm of q and k, rotation, and the write of k and v into their pages.
+
+    ``qkv`` is ``[tokens, (Hq + 2 Hkv) d]`` in the activation type, or float32 partial sums
+    ``[parts, tokens, (Hq + 2 Hkv) d]`` that the kernel adds up."""
+    _want(qkv, None, "qkv"); _want(q_out, None, "q_out")
+    parts, n_parts = None, 0
+    if qkv.dim() == 3:
+        _want(qkv, torch.float32, "qkv partial sums")
+        parts, n_parts = qkv, qkv.shape[0]
+        n, row = qkv.shape[1:]
+        qkv = None
+    else:
+        if qkv.dtype != q_out.dtype:
+            raise KernelError("qkv and q_out differ in element type")
+        n, row = qkv.shape
     need = (n_q_heads + (2 * n_kv_heads if write_kv else 0)) * head_dim
     if row < need:
         raise KernelError(f"qkv rows hold {row} values, {need} needed")
@@ -123,18 +153,18 @@ def rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | None
     if inv_freq is not None and inv_freq.numel() * 2 != rotary_dim:
         raise KernelError("inv_freq does not match rotary_dim")
     if write_kv:
-        _want(k_cache, qkv.dtype, "k_cache"); _want(v_cache, qkv.dtype, "v_cache")
+        _want(k_cache, q_out.dtype, "k_cache"); _want(v_cache, q_out.dtype, "v_cache")
         num_pages, hkv, page_size, d = k_cache.shape
         if hkv != n_kv_heads or d != head_dim or v_cache.shape != k_cache.shape:
             raise KernelError("cache pages do not match the heads")
     else:
         num_pages, page_size = 0, 1
-    _check(library().tk_rope_kv(qkv.data_ptr(), q_out.data_ptr(), _ptr(k_cache), _ptr(v_cache),
+    _check(library().tk_rope_kv(_ptr(qkv), _ptr(parts), n_parts, q_out.data_ptr(), _ptr(k_cache), _ptr(v_cache),
                                 positions.data_ptr(), tok_req.data_ptr(), req_slot.data_ptr(),
                                 block_table.data_ptr(), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq),
                                 err.data_ptr(), n, req_slot.numel(), n_q_heads, n_kv_heads, head_dim,
                                 rotary_dim, row, page_size, block_table.shape[1], num_pages,
-                                1 if write_kv else 0, float(eps), dtype_code(qkv.dtype), _stream()),
+                                1 if write_kv else 0, float(eps), dtype_code(q_out.dtype), _stream()),
            "rope_kv")
 
 
@@ -259,7 +289,7 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
 
 
 def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_splits: int,
-                    out: torch.Tensor | None = None) -> torch.Tensor:
+                    out: torch.Tensor | None = None, max_stages: int = 0) -> torch.Tensor:
     """Float32 partials ``[n_splits, tokens, N_out]`` of ``x @ weight^T`` on tcgen05, the weight
     being the 128-row operand (for few tokens: every weight byte is streamed once by TMA).
     The caller sums the partials."""
@@ -276,13 +306,24 @@ def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_
     if out is None:
         out = torch.empty((n_splits, tokens, n_out), dtype=torch.float32, device=x.device)
     _check(library().tk_gemm_bf16_tcgen05(weight.data_ptr(), x.data_ptr(), out.data_ptr(), err.data_ptr(),
-                                          n_out, tokens, k, k, k, 0, bn, n_splits, 1, 1, _stream()),
+                                          n_out, tokens, k, k, k, 0, bn, n_splits, 1, 1, max_stages, _stream()),
            "gemm_tc_swapped")
     return out
 
 
+def swapped_gemm_plan(n_out: int, k: int) -> tuple[int, int]:
+    """(K splits, pipeline stages) of the swapped product: about 2.5 blocks per SM, each with at
+    least four 64-wide k blocks; shallow rings so that several blocks share an SM and one block's
+    start-up hides behind another's streaming."""
+    tiles = -(-n_out // 128)
+    k_blocks = -(-k // 64)
+    splits = max(1, min(round(384 / tiles), max(1, k_blocks // 4)))
+    stages = 4 if splits == 1 else 3
+    return splits, stages
+
+
 def gemm_tc(x: torch.Tensor, weight: torch.Tensor, err: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
-            bn: int = 128) -> torch.Tensor:
+            bn: int = 128, max_stages: int = 0) -> torch.Tensor:
     """``x @ weight^T`` on tcgen05 with the tokens as the 128-row operand; output ``[tokens, N_out]``."""
     _want(weight, torch.bfloat16, "weight"); _want(x, torch.bfloat16, "x")
     n_out, k = weight.shape
@@ -292,7 +333,7 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, err: torch.Tensor, out_dtype:
     out = torch.empty((tokens, n_out), dtype=out_dtype, device=x.device)
     _check(library().tk_gemm_bf16_tcgen05(x.data_ptr(), weight.data_ptr(), out.data_ptr(), err.data_ptr(),
                                           tokens, n_out, k, k, k, n_out, bn, 1, 0,
-                                          1 if out_dtype == torch.float32 else 0, _stream()), "gemm_tc")
+                                          1 if out_dtype == torch.float32 else 0, max_stages, _stream()), "gemm_tc")
     return out
 
 

@@ -16,6 +16,8 @@ namespace tk {
 
 struct RopeKvParams {
   const void* qkv;          // [n_tokens, row_stride] : q heads | k heads | v heads
+  const float* qkv_parts;   // or float32 partial sums [n_parts, n_tokens, row_stride] to be added up
+  int n_parts;
   void* q_out;              // [n_tokens, n_q_heads, head_dim]
   void* k_cache;            // [num_pages, n_kv_heads, page_size, head_dim]
   void* v_cache;
@@ -51,10 +53,20 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
   else if (h < p.n_q_heads + p.n_kv_heads) { kind = 1; head = h - p.n_q_heads; }
   else { kind = 2; head = h - p.n_q_heads - p.n_kv_heads; }
 
-  const T* src = (const T*)p.qkv + (size_t)t * p.row_stride +
-                 (size_t)(kind == 0 ? head
-                                    : (kind == 1 ? p.n_q_heads + head
-                                                 : p.n_q_heads + p.n_kv_heads + head)) * d;
+  const size_t src_off = (size_t)t * p.row_stride +
+                         (size_t)(kind == 0 ? head
+                                            : (kind == 1 ? p.n_q_heads + head
+                                                         : p.n_q_heads + p.n_kv_heads + head)) * d;
+  const T* src = (const T*)p.qkv + src_off;
+  const float* parts = p.qkv_parts ? p.qkv_parts + src_off : nullptr;
+  const size_t part_stride = (size_t)p.n_tokens * p.row_stride;
+  // element e of this head's input: the tensor itself, or the sum of the partial products
+  auto in = [&](int e) -> float {
+    if (parts == nullptr) return to_f32<T>(src[e]);
+    float acc = 0.0f;
+    for (int s = 0; s < p.n_parts; ++s) acc += parts[(size_t)s * part_stride + e];
+    return acc;
+  };
 
   T* dst;
   if (kind == 0) {
@@ -73,7 +85,7 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
   }
 
   if (kind == 2) {
-    for (int e = lane; e < d; e += 32) dst[e] = src[e];
+    for (int e = lane; e < d; e += 32) dst[e] = from_f32<T>(in(e));
     return;
   }
 
@@ -81,15 +93,15 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
   float rstd = 1.0f;
   if (w != nullptr) {
     float ss = 0.0f;
-    for (int e = lane; e < d; e += 32) { const float v = to_f32<T>(src[e]); ss += v * v; }
+    for (int e = lane; e < d; e += 32) { const float v = in(e); ss += v * v; }
     ss = warp_sum(ss);
     rstd = rsqrtf(ss / (float)d + p.eps);
   }
   const float fpos = (float)p.positions[t];
   // rotated pairs (i, i + half) for i < half; elements beyond rotary_dim pass through
   for (int i = lane; i < half; i += 32) {
-    float x1 = to_f32<T>(src[i]) * rstd;
-    float x2 = to_f32<T>(src[i + half]) * rstd;
+    float x1 = in(i) * rstd;
+    float x2 = in(i + half) * rstd;
     if (w != nullptr) { x1 *= w[i]; x2 *= w[i + half]; }
     float c = 1.0f, s = 0.0f;
     if (p.inv_freq != nullptr) {
@@ -100,7 +112,7 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
     dst[i + half] = from_f32<T>(x2 * c + x1 * s);
   }
   for (int e = 2 * half + lane; e < d; e += 32) {
-    float x = to_f32<T>(src[e]) * rstd;
+    float x = in(e) * rstd;
     if (w != nullptr) x *= w[e];
     dst[e] = from_f32<T>(x);
   }
@@ -108,7 +120,7 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
 
 }  // namespace tk
 
-TK_API int tk_rope_kv(const void* qkv, void* q_out, void* k_cache, void* v_cache,
+TK_API int tk_rope_kv(const void* qkv, const float* qkv_parts, int n_parts, void* q_out, void* k_cache, void* v_cache,
                       const int* positions, const int* tok_req, const int* req_slot,
                       const int* block_table, const float* q_norm_w, const float* k_norm_w,
                       const float* inv_freq, int* err, int n_tokens, int n_reqs, int n_q_heads,
@@ -120,7 +132,7 @@ TK_API int tk_rope_kv(const void* qkv, void* q_out, void* k_cache, void* v_cache
     return (int)cudaErrorInvalidValue;
   }
   tk::RopeKvParams p;
-  p.qkv = qkv; p.q_out = q_out; p.k_cache = k_cache; p.v_cache = v_cache;
+  p.qkv = qkv; p.qkv_parts = qkv_parts; p.n_parts = n_parts; p.q_out = q_out; p.k_cache = k_cache; p.v_cache = v_cache;
   p.positions = positions; p.tok_req = tok_req; p.req_slot = req_slot; p.block_table = block_table;
   p.q_norm_w = q_norm_w; p.k_norm_w = k_norm_w; p.inv_freq = inv_freq; p.err = err;
   p.n_tokens = n_tokens; p.n_reqs = n_reqs; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;

@@ -92,4 +92,4 @@ class DecoderModel:
         if step.n_want == 0:
             return torch.empty((0, self.spec.head.vocab_size), dtype=torch.float32, device=resid.device)
         h = self.final_norm.add_norm(resid, pending, rows=step.logits_rows)
-        return self.head.forward(h)
+        return self.head.forward(h, step.err)

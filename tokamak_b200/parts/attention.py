@@ -82,7 +82,7 @@ class Attention:
     def forward(self, h: torch.Tensor, step, cache_view) -> torch.Tensor:
         spec = self.spec
         n = h.shape[0]
-        qkv = linear(h, self.w_qkv)
+        qkv = linear(h, self.w_qkv, err=step.err)
         q = torch.empty((n, spec.num_heads, spec.head_dim), dtype=h.dtype, device=h.device)
         inv_freq, rotary_dim = self.position.rotary_table()
         ops.rope_kv(qkv, q, cache_view.k if spec.own_kv else None,
@@ -93,7 +93,7 @@ class Attention:
                     rotary_dim=rotary_dim, eps=spec.qk_norm_eps or 0.0, write_kv=spec.own_kv)
         out = torch.empty_like(q)
         paged_attention(q, out, cache_view, step, scale=self.scale, window=spec.window)
-        return linear(out.view(n, spec.num_heads * spec.head_dim), self.w_o)
+        return linear(out.view(n, spec.num_heads * spec.head_dim), self.w_o, err=step.err)
 
 
 def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, scale: float,

@@ -23,6 +23,11 @@ block          ``expected_tensors(spec)``, ``__init__(spec, tensors, rt)``,
 
 No part knows which model it is in: it sees its spec, its tensors, the step's
 batch description and the view of its own cache.
+
+Where a row says ``[N, hidden]`` a mixer or feed-forward may instead return what
+:func:`linear` gave it: a 3-D float32 tensor of partial sums ``[parts, N, hidden]``
+from a split-K product.  The norm that consumes it adds the parts up (a 32-bit sum);
+:func:`sum_parts` does the same for anyone else.
 """
 
 from __future__ import annotations
@@ -95,18 +100,38 @@ FEED_FORWARDS = Registry("feed_forward")
 BLOCKS = Registry("block")
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+SWAPPED_GEMM_MAX_TOKENS = 64
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
+           err: torch.Tensor | None = None) -> torch.Tensor:
     """``x @ weight^T`` for ``weight`` of shape [out, in].
 
-    float32: the engine's own FFMA kernel (no TF32, no tensor cores).  bfloat16:
-    the library product, as the reference uses the library for its projections
-    (src/tokamak/model/transformer.py:38-41); ``out_dtype=float32`` keeps the
+    float32: the engine's own FFMA kernel (no TF32, no tensor cores).
+
+    bfloat16, few tokens (decoding): the tcgen05 kernel with the weight as the 128-row
+    operand, streamed once by TMA and split over K.  The result is then a 3-D float32
+    tensor of partial sums ``[splits, tokens, out]`` which the consuming kernel (norm,
+    rotation, activation) adds up; ``err`` is the error word its bounded waits report to.
+
+    bfloat16, many tokens: the library product, as the reference uses the library for its
+    projections (src/tokamak/model/transformer.py:38-41); ``out_dtype=float32`` keeps the
     32-bit accumulators instead of rounding them.
     """
     from ..csrc import ops
 
     if x.dtype == torch.float32:
         return ops.gemm_f32(x, weight)
+    if err is not None and x.shape[0] <= SWAPPED_GEMM_MAX_TOKENS and weight.shape[1] % 8 == 0:
+        splits, stages = ops.swapped_gemm_plan(weight.shape[0], weight.shape[1])
+        return ops.gemm_tc_swapped(weight, x, err, splits, max_stages=stages)
     if out_dtype is not None and out_dtype != x.dtype:
         return torch.mm(x, weight.t(), out_dtype=out_dtype)
     return torch.mm(x, weight.t())
+
+
+def sum_parts(t: torch.Tensor, dtype: torch.dtype | None = None) -> torch.Tensor:
+    """A 2-D tensor from the result of :func:`linear`: partial sums are added up."""
+    if t.dim() == 3:
+        t = t[0] if t.shape[0] == 1 else t.sum(0)
+    return t if dtype is None or t.dtype == dtype else t.to(dtype)

@@ -7,7 +7,7 @@ from dataclasses import dataclass
 import torch
 
 from ..csrc import ops
-from .base import Runtime, TensorReq, linear
+from .base import Runtime, TensorReq, linear, sum_parts
 
 
 @dataclass(frozen=True)
@@ -62,5 +62,5 @@ class Head:
         # a tied checkpoint may still carry the head; it is then ignored
         return {spec.name: TensorReq((spec.vocab_size, spec.hidden_size), optional=spec.tied)}
 
-    def forward(self, h: torch.Tensor) -> torch.Tensor:
-        return linear(h, self.weight, out_dtype=torch.float32)
+    def forward(self, h: torch.Tensor, err: torch.Tensor | None = None) -> torch.Tensor:
+        return sum_parts(linear(h, self.weight, out_dtype=torch.float32, err=err), torch.float32)

@@ -42,7 +42,8 @@ class SwiGLU:
         }
 
     def forward(self, h: torch.Tensor, step) -> torch.Tensor:
-        gate_up = linear(h, self.w_gate_up)
+        err = step.err if step is not None else None
+        gate_up = linear(h, self.w_gate_up, err=err)
         act = torch.empty((h.shape[0], self.spec.intermediate_size), dtype=h.dtype, device=h.device)
         ops.swiglu(gate_up, act)
-        return linear(act, self.w_down)
+        return linear(act, self.w_down, err=err)
