@@ -43,6 +43,8 @@ struct DecodeParams {
 template <int D>
 __global__ void __launch_bounds__(kDecWarps * 32)
 attn_decode_split_kernel(DecodeParams p) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int CH = D / 8;                       // 16-byte chunks per row
   constexpr int TILE_BYTES = kDecTile * D * 2;    // one K or V tile
   constexpr int STAGE_BYTES = 2 * TILE_BYTES;
@@ -258,6 +260,8 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o,
                                          const float* __restrict__ part_ml,
                                          const int* __restrict__ items, __nv_bfloat16* __restrict__ out,
                                          int n_q_heads, int n_splits, int D) {
+  pdl_trigger();
+  pdl_wait();
   const int item = blockIdx.x, head = blockIdx.y;
   const size_t base = ((size_t)item * n_q_heads + head) * n_splits;
   float m_all = -INFINITY;
@@ -291,13 +295,11 @@ static int launch_decode(const DecodeParams& p, void* out, cudaStream_t stream) 
     configured = true;
   }
   dim3 grid(p.n_splits, p.n_kv_heads, p.n_items);
-  attn_decode_split_kernel<D><<<grid, kDecWarps * 32, smem_bytes, stream>>>(p);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch(attn_decode_split_kernel<D>, grid, dim3(kDecWarps * 32), smem_bytes, stream, p);
   if (e != cudaSuccess) return (int)e;
   dim3 mgrid(p.n_items, p.n_q_heads);
-  attn_decode_merge_kernel<<<mgrid, D >= 128 ? 128 : 64, 0, stream>>>(
-      p.part_o, p.part_ml, p.items, (__nv_bfloat16*)out, p.n_q_heads, p.n_splits, D);
-  return (int)cudaGetLastError();
+  return (int)launch(attn_decode_merge_kernel, mgrid, dim3(D >= 128 ? 128 : 64), 0, stream, (const float*)p.part_o,
+                     (const float*)p.part_ml, p.items, (__nv_bfloat16*)out, p.n_q_heads, p.n_splits, D);
 }
 
 }  // namespace tk

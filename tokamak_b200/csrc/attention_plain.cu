@@ -34,6 +34,8 @@ struct AttnParams {
 
 template <typename T>
 __global__ void attention_plain_kernel(AttnParams p) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float s_m[kPlainWarps];
   __shared__ float s_l[kPlainWarps];
   __shared__ float s_acc[kPlainWarps][kPlainMaxPerLane * 32];
@@ -145,7 +147,8 @@ TK_API int tk_attention_plain(const void* q, void* out, const void* k_cache, con
   p.n_kv_heads = n_kv_heads; p.head_dim = head_dim; p.page_size = page_size;
   p.max_pages = max_pages; p.num_pages = num_pages; p.window = window; p.scale = scale;
   dim3 grid(n_tokens, n_q_heads);
+  cudaError_t e = cudaSuccess;
   TK_DISPATCH_DTYPE(dtype, T,
-                    tk::attention_plain_kernel<T><<<grid, tk::kPlainWarps * 32, 0, stream>>>(p));
-  return (int)cudaGetLastError();
+                    e = tk::launch(tk::attention_plain_kernel<T>, grid, dim3(tk::kPlainWarps * 32), 0, stream, p));
+  return (int)e;
 }

@@ -40,6 +40,8 @@ struct PrefillParams {
 template <int D>
 __global__ void __launch_bounds__(kPfWarps * 32)
 attn_prefill_kernel(PrefillParams p) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int CH = D / 8;
   constexpr int TILE_BYTES = kPfKeys * D * 2;
   constexpr int STAGE_BYTES = 2 * TILE_BYTES;
@@ -244,8 +246,7 @@ static int launch_prefill(const PrefillParams& p, cudaStream_t stream) {
     configured = true;
   }
   dim3 grid(p.n_tiles, p.n_q_heads);
-  attn_prefill_kernel<D><<<grid, kPfWarps * 32, smem_bytes, stream>>>(p);
-  return (int)cudaGetLastError();
+  return (int)launch(attn_prefill_kernel<D>, grid, dim3(kPfWarps * 32), smem_bytes, stream, p);
 }
 
 }  // namespace tk

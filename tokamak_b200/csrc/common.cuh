@@ -5,6 +5,9 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
+
+#include <utility>
 
 namespace tk {
 
@@ -80,6 +83,41 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   float r = (lane < nwarps) ? scratch[lane] : -INFINITY;
   r = warp_max(r);
   return r;
+}
+
+// Programmatic dependent launch.  Every kernel of this library is launched so that it may
+// start while the kernel before it in the stream is still running, lets the kernel after it
+// start early in turn (pdl_trigger at its top), and calls pdl_wait before it touches anything
+// that an earlier kernel wrote and before it writes anything itself.  What runs before
+// pdl_wait (index arithmetic, barrier set-up, loads of weights, which no kernel writes)
+// overlaps the tail of the previous kernel.  Without the launch attribute both calls do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+// TOKAMAK_B200_PDL=0 in the environment switches the launch attribute off.
+inline bool pdl_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* e = getenv("TOKAMAK_B200_PDL");
+    enabled = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return enabled == 1;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
 }  // namespace tk

@@ -12,6 +12,8 @@ namespace tk {
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ resid, int hidden, int vocab, int* err) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* out = resid + (size_t)t * hidden;
@@ -35,6 +37,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TDelta* __re
                                    const float* __restrict__ weight, TOut* __restrict__ out,
                                    const int* __restrict__ rows, int hidden, float eps) {
   __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
   const int i = blockIdx.x;
   const int r = rows ? rows[i] : i;
   float* x = resid + (size_t)r * hidden;
@@ -106,6 +110,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
                                        const float* __restrict__ weight, T* __restrict__ out,
                                        const int* __restrict__ rows, int hidden, float eps) {
   __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
   const int i = blockIdx.x;
   const int r = rows ? rows[i] : i;
   float* x = resid + (size_t)r * hidden;
@@ -157,6 +163,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, const float* __restrict__ parts, int n_parts,
                               size_t part_stride, T* __restrict__ out, int inter, size_t total) {
+  pdl_trigger();
+  pdl_wait();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (; idx < total; idx += stride) {
@@ -184,10 +192,11 @@ TK_API int tk_embed_gather(const void* table, int dtype, const int* ids, float* 
                            int hidden, int vocab, int* err, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
+  cudaError_t e = cudaSuccess;
   TK_DISPATCH_DTYPE(dtype, T,
-                    tk::embed_gather_kernel<T><<<n_tokens, threads, 0, stream>>>(
-                        (const T*)table, ids, resid, hidden, vocab, err));
-  return (int)cudaGetLastError();
+                    e = tk::launch(tk::embed_gather_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream,
+                                       (const T*)table, ids, resid, hidden, vocab, err));
+  return (int)e;
 }
 
 // delta: branch output in the activation type, or null.  parts: float32 partial sums of the
@@ -197,6 +206,7 @@ TK_API int tk_add_rmsnorm(float* resid, const void* delta, const float* parts, i
                           int n_rows, int hidden, float eps, int dtype, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (parts != nullptr && (delta != nullptr || n_parts < 1)) return (int)cudaErrorInvalidValue;
+  cudaError_t e = cudaSuccess;
   if (hidden % 8 == 0 && hidden <= 4 * 512 * 8) {
     // one pass with the row in registers: threads * 8 * ITERS >= hidden
     int threads = ((hidden / 8 + 31) / 32) * 32;
@@ -206,19 +216,19 @@ TK_API int tk_add_rmsnorm(float* resid, const void* delta, const float* parts, i
     if (iters == 3) iters = 4;
 #define TK_LAUNCH_VEC(IT)                                                                       \
     TK_DISPATCH_DTYPE(dtype, T,                                                                 \
-                      (tk::add_rmsnorm_vec_kernel<T, IT><<<n_rows, threads, 0, stream>>>(        \
-                          resid, (const T*)delta, parts, n_parts, (size_t)part_stride, weight,  \
-                          (T*)out, rows, hidden, eps)))
+                      (e = tk::launch(tk::add_rmsnorm_vec_kernel<T, IT>, dim3(n_rows), dim3(threads), 0, \
+                                      stream, resid, (const T*)delta, parts, n_parts,             \
+                                      (size_t)part_stride, weight, (T*)out, rows, hidden, eps)))
     if (iters == 1) { TK_LAUNCH_VEC(1); } else if (iters == 2) { TK_LAUNCH_VEC(2); } else { TK_LAUNCH_VEC(4); }
 #undef TK_LAUNCH_VEC
-    return (int)cudaGetLastError();
+    return (int)e;
   }
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   TK_DISPATCH_DTYPE(dtype, T,
-                    (tk::add_rmsnorm_kernel<T, T><<<n_rows, threads, 0, stream>>>(
-                        resid, (const T*)delta, parts, n_parts, (size_t)part_stride, weight, (T*)out,
-                        rows, hidden, eps)));
-  return (int)cudaGetLastError();
+                    (e = tk::launch(tk::add_rmsnorm_kernel<T, T>, dim3(n_rows), dim3(threads), 0, stream,
+                                    resid, (const T*)delta, parts, n_parts, (size_t)part_stride, weight,
+                                    (T*)out, rows, hidden, eps)));
+  return (int)e;
 }
 
 TK_API int tk_swiglu(const void* gate_up, const float* parts, int n_parts, long long part_stride,
@@ -228,8 +238,10 @@ TK_API int tk_swiglu(const void* gate_up, const float* parts, int n_parts, long 
   const int threads = 256;
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
+  cudaError_t e = cudaSuccess;
   TK_DISPATCH_DTYPE(dtype, T,
-                    tk::swiglu_kernel<T><<<(int)blocks, threads, 0, stream>>>(
-                        (const T*)gate_up, parts, n_parts, (size_t)part_stride, (T*)out, inter, total));
-  return (int)cudaGetLastError();
+                    e = tk::launch(tk::swiglu_kernel<T>, dim3((unsigned)blocks), dim3(threads), 0, stream,
+                                   (const T*)gate_up, parts, n_parts, (size_t)part_stride, (T*)out, inter,
+                                   total));
+  return (int)e;
 }

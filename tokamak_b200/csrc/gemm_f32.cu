@@ -16,6 +16,8 @@ constexpr int kGemmBK = 16;
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ C,
                 int M, int N, int K, int lda, int ldw, int ldc) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float sA[kGemmBK][kGemmBM + 4];
   __shared__ float sW[kGemmBK][kGemmBN + 4];
 
@@ -80,6 +82,5 @@ TK_API int tk_gemm_f32(const float* A, const float* W, float* C, int M, int N, i
   if (K < 0) return (int)cudaErrorInvalidValue;
   dim3 grid((N + tk::kGemmBN - 1) / tk::kGemmBN, (M + tk::kGemmBM - 1) / tk::kGemmBM);
   if (grid.y > 65535) return (int)cudaErrorInvalidValue;
-  tk::gemm_f32_kernel<<<grid, 256, 0, stream>>>(A, W, C, M, N, K, lda, ldw, ldc);
-  return (int)cudaGetLastError();
+  return (int)tk::launch(tk::gemm_f32_kernel, grid, dim3(256), 0, stream, A, W, C, M, N, K, lda, ldw, ldc);
 }

@@ -145,6 +145,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
   const int n_kb = max(kb_end - kb_begin, 0);
   const uint32_t tmem_cols = p.bn < 32 ? 32u : (uint32_t)p.bn;   // bn is 16, 32, 64, 128 or 256
 
+  pdl_trigger();
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.n_stages; ++s) {
       mbar_init(gt_smem_u32(&full_bar[s]), 1);
@@ -167,10 +168,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
   if (warp == 0) {
     // ---- TMA producer ---------------------------------------------------------------------
     if (lane == 0) {
-      for (int i = 0; i < n_kb; ++i) {
+      // The first ring of stages: with weights as the row operand (which no kernel writes)
+      // their tiles are requested before the wait on the previous kernel, so they stream in
+      // while it finishes; the activation tiles follow after the wait.
+      const int first = min(n_kb, p.n_stages);
+      const bool rows_are_weights = p.swapped != 0;
+      for (int i = 0; i < first; ++i) {
+        const uint32_t full = gt_smem_u32(&full_bar[i]);
+        mbar_expect_tx(full, r_bytes + c_bytes);
+        if (rows_are_weights) {
+          tma_load_2d(base + (uint32_t)i * stage_bytes, &map_r, (kb_begin + i) * kGtBK, tile_r * kGtBM, full);
+        }
+      }
+      pdl_wait();
+      for (int i = 0; i < first; ++i) {
+        const uint32_t full = gt_smem_u32(&full_bar[i]);
+        const uint32_t dst = base + (uint32_t)i * stage_bytes;
+        const int k0 = (kb_begin + i) * kGtBK;
+        if (!rows_are_weights) tma_load_2d(dst, &map_r, k0, tile_r * kGtBM, full);
+        tma_load_2d(dst + r_bytes, &map_c, k0, tile_c * p.bn, full);
+      }
+      for (int i = first; i < n_kb; ++i) {
         const int s = i % p.n_stages;
         const uint32_t round = (uint32_t)(i / p.n_stages);
-        if (round > 0 && !mbar_wait(gt_smem_u32(&empty_bar[s]), (round - 1) & 1u, abort_flag)) {
+        if (!mbar_wait(gt_smem_u32(&empty_bar[s]), (round - 1) & 1u, abort_flag)) {
           set_error(p.err, kErrWait, 0, i, s);
           *abort_flag = 1;
           break;
@@ -215,6 +236,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
     // ---- epilogue: warps 2..5, each owns the 32 accumulator lanes of its quarter --------------
     const int quarter = warp & 3;
     bool ok = true;
+    pdl_wait();   // nothing is stored before the previous kernels are done with the output buffer
     if (n_kb > 0) {
       ok = mbar_wait(gt_smem_u32(accum_bar), 0u, abort_flag);
       if (!ok && lane == 0) { set_error(p.err, kErrWait, 2, 0, 0); *abort_flag = 1; }
@@ -353,6 +375,5 @@ TK_API int tk_gemm_bf16_tcgen05(const void* r, const void* c, void* out, int* er
   p.out = out; p.err = err; p.rows_total = rows; p.cols_total = cols; p.k_total = k; p.bn = bn;
   p.n_stages = n_stages; p.n_splits = n_splits; p.swapped = swapped; p.out_f32 = out_f32; p.ld_out = ld_out;
   dim3 grid((rows + tk::kGtBM - 1) / tk::kGtBM, (cols + bn - 1) / bn, n_splits);
-  tk::gemm_tcgen05_kernel<<<grid, tk::kGtThreads, smem_bytes, stream>>>(map_r, map_c, p);
-  return (int)cudaGetLastError();
+  return (int)tk::launch(tk::gemm_tcgen05_kernel, grid, dim3(tk::kGtThreads), smem_bytes, stream, map_r, map_c, p);
 }

@@ -37,6 +37,8 @@ struct RopeKvParams {
 
 template <typename T>
 __global__ void rope_kv_kernel(RopeKvParams p) {
+  pdl_trigger();
+  pdl_wait();
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int heads_total = p.n_q_heads + (p.write_kv ? 2 * p.n_kv_heads : 0);
@@ -143,7 +145,9 @@ TK_API int tk_rope_kv(const void* qkv, const float* qkv_parts, int n_parts, void
   const int warps_per_block = 4;
   const long long items = (long long)n_tokens * heads_total;
   const long long blocks = (items + warps_per_block - 1) / warps_per_block;
+  cudaError_t e = cudaSuccess;
   TK_DISPATCH_DTYPE(dtype, T,
-                    tk::rope_kv_kernel<T><<<(unsigned)blocks, warps_per_block * 32, 0, stream>>>(p));
-  return (int)cudaGetLastError();
+                    e = tk::launch(tk::rope_kv_kernel<T>, dim3((unsigned)blocks), dim3(warps_per_block * 32), 0,
+                                   stream, p));
+  return (int)e;
 }

@@ -65,6 +65,8 @@ __device__ __forceinline__ unsigned long long warp_incl_scan_u64(unsigned long l
 }
 
 __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleParams p) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
   __shared__ unsigned int s_count[256];
@@ -255,8 +257,7 @@ TK_API int tk_sample(const float* logits, long long ld, const float* temperature
   tk::SampleParams p;
   p.logits = logits; p.temperature = temperature; p.top_k = top_k; p.top_p = top_p;
   p.seed = seed; p.counter = counter; p.out_tokens = out_tokens; p.vocab = vocab; p.ld = ld;
-  tk::sample_kernel<<<n_rows, tk::kSampleThreads, 0, stream>>>(p);
-  return (int)cudaGetLastError();
+  return (int)tk::launch(tk::sample_kernel, dim3(n_rows), dim3(tk::kSampleThreads), 0, stream, p);
 }
 
 // Host copy of the generator, for callers that need the same uniform without a GPU.
