@@ -137,8 +137,9 @@ def test_rope_kv_write(dtype, hq, hkv, d, page):
     q_out = torch.empty(n, hq, d, device=DEV, dtype=dtype)
     err = err_word()
     pos_t = torch.tensor(positions, dtype=torch.int32, device=DEV)
+    rot = ops.rope_table(pos_t, inv_freq)
     ops.rope_kv(qkv, q_out, kc, vc, pos_t, torch.tensor(tok_req, dtype=torch.int32, device=DEV),
-                torch.tensor([0, 1, 2], dtype=torch.int32, device=DEV), table.to(DEV), qw, kw, inv_freq,
+                torch.tensor([0, 1, 2], dtype=torch.int32, device=DEV), table.to(DEV), qw, kw, rot,
                 err, n_q_heads=hq, n_kv_heads=hkv, head_dim=d, rotary_dim=d, eps=eps)
     assert err.tolist()[0] == 0
     x = qkv.double().cpu()

@@ -48,11 +48,17 @@ def test_rmsnorm_part(dtype):
 
 def test_position_parts():
     from tokamak_b200.parts.position import NoPosition, NoPositionSpec, RopeNeox, RopeSpec
+    from types import SimpleNamespace
     rope = RopeNeox(RopeSpec(head_dim=48, theta=50000.0), runtime(torch.float32))
-    inv_freq, rotary_dim = rope.rotary_table()
-    want = 1.0 / (50000.0 ** (torch.arange(0, 48, 2, dtype=torch.float32) / 48))
-    assert rotary_dim == 48 and torch.equal(inv_freq.cpu(), want)
-    assert NoPosition(NoPositionSpec(), runtime(torch.float32)).rotary_table() == (None, 0)
+    positions = [0, 1, 7, 300, 40001]
+    step = SimpleNamespace(positions=torch.tensor(positions, dtype=torch.int32, device=DEV), scratch={})
+    table, rotary_dim = rope.rotary_table(step)
+    assert rotary_dim == 48 and table.shape == (5, 24, 2)
+    assert rope.rotary_table(step)[0] is table                      # made once per step
+    cos, sin = plain.rope_tables(torch.tensor(positions), 48, 50000.0, torch.float64)
+    torch.testing.assert_close(table[..., 0].double().cpu(), cos[:, :24], rtol=0, atol=2e-6)
+    torch.testing.assert_close(table[..., 1].double().cpu(), sin[:, :24], rtol=0, atol=2e-6)
+    assert NoPosition(NoPositionSpec(), runtime(torch.float32)).rotary_table(step) == (None, 0)
     with pytest.raises(ValueError):
         RopeNeox(RopeSpec(head_dim=15, theta=1e4), runtime(torch.float32))
 

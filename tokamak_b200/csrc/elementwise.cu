@@ -186,6 +186,39 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, const float* __restrict_
   }
 }
 
+// The same for an intermediate size that is a multiple of 8: 16-byte loads and stores.
+template <typename T>
+__global__ void swiglu_vec_kernel(const T* __restrict__ gu, const float* __restrict__ parts, int n_parts,
+                                  size_t part_stride, T* __restrict__ out, int inter, size_t total8) {
+  pdl_trigger();
+  pdl_wait();
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const int per_row = inter / 8;
+  for (; idx < total8; idx += stride) {
+    const size_t t = idx / per_row;
+    const int j = (int)(idx - t * per_row) * 8;
+    float g[8], u[8], y[8];
+    if (parts == nullptr) {
+      Vec8<T>::load(gu + t * 2 * inter + j, g);
+      Vec8<T>::load(gu + t * 2 * inter + inter + j, u);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { g[e] = 0.0f; u[e] = 0.0f; }
+      for (int s = 0; s < n_parts; ++s) {
+        float a[8], b[8];
+        Vec8<float>::load(parts + s * part_stride + t * 2 * inter + j, a);
+        Vec8<float>::load(parts + s * part_stride + t * 2 * inter + inter + j, b);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { g[e] += a[e]; u[e] += b[e]; }
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = g[e] / (1.0f + expf(-g[e])) * u[e];
+    Vec8<T>::store(out + t * inter + j, y);
+  }
+}
+
 }  // namespace tk
 
 TK_API int tk_embed_gather(const void* table, int dtype, const int* ids, float* resid, int n_tokens,
@@ -236,9 +269,19 @@ TK_API int tk_swiglu(const void* gate_up, const float* parts, int n_parts, long 
   if (n_tokens <= 0) return 0;
   const size_t total = (size_t)n_tokens * inter;
   const int threads = 256;
+  cudaError_t e = cudaSuccess;
+  if (inter % 8 == 0) {
+    const size_t total8 = total / 8;
+    size_t vblocks = (total8 + threads - 1) / threads;
+    if (vblocks > 148 * 32) vblocks = 148 * 32;
+    TK_DISPATCH_DTYPE(dtype, T,
+                      e = tk::launch(tk::swiglu_vec_kernel<T>, dim3((unsigned)vblocks), dim3(threads), 0, stream,
+                                     (const T*)gate_up, parts, n_parts, (size_t)part_stride, (T*)out, inter,
+                                     total8));
+    return (int)e;
+  }
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  cudaError_t e = cudaSuccess;
   TK_DISPATCH_DTYPE(dtype, T,
                     e = tk::launch(tk::swiglu_kernel<T>, dim3((unsigned)blocks), dim3(threads), 0, stream,
                                    (const T*)gate_up, parts, n_parts, (size_t)part_stride, (T*)out, inter,

@@ -22,6 +22,7 @@ _SIGNATURES: dict[str, list] = {
     "tk_rope_kv": [_P, _P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                    c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                    c_float, c_int, _P],
+    "tk_rope_table": [_P, _P, _P, c_int, c_int, _P],
     "tk_attention_plain": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                            c_float, c_int, _P],

@@ -116,10 +116,20 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
                                two_i // 2, dtype_code(out.dtype), _stream()), "swiglu")
 
 
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """``[tokens, len(inv_freq), 2]`` float32: (cos, sin) of ``float(position) * inv_freq[j]``."""
+    _want(positions, torch.int32, "positions"); _want(inv_freq, torch.float32, "inv_freq")
+    n, half = positions.numel(), inv_freq.numel()
+    table = torch.empty((n, half, 2), dtype=torch.float32, device=positions.device)
+    _check(library().tk_rope_table(positions.data_ptr(), inv_freq.data_ptr(), table.data_ptr(), n, 2 * half,
+                                   _stream()), "rope_table")
+    return table
+
+
 def rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | None,
             v_cache: torch.Tensor | None, positions: torch.Tensor, tok_req: torch.Tensor,
             req_slot: torch.Tensor, block_table: torch.Tensor, q_norm_w: torch.Tensor | None,
-            k_norm_w: torch.Tensor | None, inv_freq: torch.Tensor | None, err: torch.Tensor, *,
+            k_norm_w: torch.Tensor | None, table: torch.Tensor | None, err: torch.Tensor, *,
             n_q_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int, eps: float,
             write_kv: bool = True) -> None:
     """Per-head norm of q and k, rotation, and the write of k and v into their pages.
@@ -143,15 +153,20 @@ def rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | None
     for name, t in (("positions", positions), ("tok_req", tok_req), ("req_slot", req_slot),
                     ("block_table", block_table)):
         _want(t, torch.int32, name)
-    for name, t in (("q_norm_w", q_norm_w), ("k_norm_w", k_norm_w), ("inv_freq", inv_freq)):
+    for name, t in (("q_norm_w", q_norm_w), ("k_norm_w", k_norm_w), ("table", table)):
         if t is not None:
             _want(t, torch.float32, name)
+    if head_dim % 4 or rotary_dim % 4 or rotary_dim > head_dim:
+        raise KernelError(f"head_dim {head_dim} and rotary_dim {rotary_dim} must be multiples of 4 "
+                          f"with rotary_dim <= head_dim")
     if q_norm_w is not None and q_norm_w.numel() != head_dim:
         raise KernelError("q_norm weight does not match head_dim")
     if k_norm_w is not None and k_norm_w.numel() != head_dim:
         raise KernelError("k_norm weight does not match head_dim")
-    if inv_freq is not None and inv_freq.numel() * 2 != rotary_dim:
-        raise KernelError("inv_freq does not match rotary_dim")
+    if table is not None and table.shape != (n, rotary_dim // 2, 2):
+        raise KernelError(f"the rotation table must be [{n}, {rotary_dim // 2}, 2], got {tuple(table.shape)}")
+    if table is None and rotary_dim != 0:
+        raise KernelError("rotary_dim without a rotation table")
     if write_kv:
         _want(k_cache, q_out.dtype, "k_cache"); _want(v_cache, q_out.dtype, "v_cache")
         num_pages, hkv, page_size, d = k_cache.shape
@@ -161,7 +176,7 @@ def rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | None
         num_pages, page_size = 0, 1
     _check(library().tk_rope_kv(_ptr(qkv), _ptr(parts), n_parts, q_out.data_ptr(), _ptr(k_cache), _ptr(v_cache),
                                 positions.data_ptr(), tok_req.data_ptr(), req_slot.data_ptr(),
-                                block_table.data_ptr(), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq),
+                                block_table.data_ptr(), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(table),
                                 err.data_ptr(), n, req_slot.numel(), n_q_heads, n_kv_heads, head_dim,
                                 rotary_dim, row, page_size, block_table.shape[1], num_pages,
                                 1 if write_kv else 0, float(eps), dtype_code(q_out.dtype), _stream()),

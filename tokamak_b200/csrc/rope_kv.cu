@@ -9,10 +9,27 @@
 // Keys are stored after norm and rotation, values raw
 // (src/tokamak/memory/paged_cache.py:72-81).  Everything is computed in float32
 // and rounded once on store.
+//
+// The cosines and sines depend on the token's position only, so they are computed
+// once per step into a float32 table [token, rotary_dim / 2] of (cos, sin) pairs
+// (tk_rope_table) that every layer of the step reads.
 #include "common.cuh"
 
 namespace tk {
 
+// table[t, j] = (cos, sin)(float(positions[t]) * inv_freq[j])
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                  float2* __restrict__ table, int n_tokens, int half) {
+  pdl_trigger();
+  pdl_wait();
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_tokens * half) return;
+  const int t = idx / half, j = idx - t * half;
+  const float ang = (float)positions[t] * inv_freq[j];
+  float s, c;
+  sincosf(ang, &s, &c);
+  table[idx] = make_float2(c, s);
+}
 
 struct RopeKvParams {
   const void* qkv;          // [n_tokens, row_stride] : q heads | k heads | v heads
@@ -27,7 +44,7 @@ struct RopeKvParams {
   const int* block_table;   // [n_slots, max_pages]
   const float* q_norm_w;    // [head_dim] or null
   const float* k_norm_w;    // [head_dim] or null
-  const float* inv_freq;    // [rotary_dim / 2] or null (no rotation)
+  const float2* rope_table; // [n_tokens, rotary_dim / 2] (cos, sin) or null (no rotation)
   int* err;
   int n_tokens, n_reqs, n_q_heads, n_kv_heads, head_dim, rotary_dim;
   int row_stride, page_size, max_pages, num_pages;
@@ -35,6 +52,24 @@ struct RopeKvParams {
   float eps;
 };
 
+template <typename T> struct Pair;
+template <> struct Pair<float> {
+  static __device__ __forceinline__ float2 load(const float* p) { return *reinterpret_cast<const float2*>(p); }
+  static __device__ __forceinline__ void store(float* p, float a, float b) {
+    *reinterpret_cast<float2*>(p) = make_float2(a, b);
+  }
+};
+template <> struct Pair<__nv_bfloat16> {
+  static __device__ __forceinline__ float2 load(const __nv_bfloat16* p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+  }
+};
+
+// One warp per (token, head).  head_dim and rotary_dim are multiples of 4, so every lane
+// works on pairs of neighbouring elements with 4- and 8-byte accesses.
 template <typename T>
 __global__ void rope_kv_kernel(RopeKvParams p) {
   pdl_trigger();
@@ -55,18 +90,18 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
   else if (h < p.n_q_heads + p.n_kv_heads) { kind = 1; head = h - p.n_q_heads; }
   else { kind = 2; head = h - p.n_q_heads - p.n_kv_heads; }
 
-  const size_t src_off = (size_t)t * p.row_stride +
-                         (size_t)(kind == 0 ? head
-                                            : (kind == 1 ? p.n_q_heads + head
-                                                         : p.n_q_heads + p.n_kv_heads + head)) * d;
+  const size_t src_off = (size_t)t * p.row_stride + (size_t)h * d;   // heads lie in the order q | k | v
   const T* src = (const T*)p.qkv + src_off;
   const float* parts = p.qkv_parts ? p.qkv_parts + src_off : nullptr;
   const size_t part_stride = (size_t)p.n_tokens * p.row_stride;
-  // element e of this head's input: the tensor itself, or the sum of the partial products
-  auto in = [&](int e) -> float {
-    if (parts == nullptr) return to_f32<T>(src[e]);
-    float acc = 0.0f;
-    for (int s = 0; s < p.n_parts; ++s) acc += parts[(size_t)s * part_stride + e];
+  // elements e, e + 1 of this head's input: the tensor itself, or the sum of the partial products
+  auto in2 = [&](int e) -> float2 {
+    if (parts == nullptr) return Pair<T>::load(src + e);
+    float2 acc = make_float2(0.0f, 0.0f);
+    for (int s = 0; s < p.n_parts; ++s) {
+      const float2 v = *reinterpret_cast<const float2*>(parts + (size_t)s * part_stride + e);
+      acc.x += v.x; acc.y += v.y;
+    }
     return acc;
   };
 
@@ -87,7 +122,7 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
   }
 
   if (kind == 2) {
-    for (int e = lane; e < d; e += 32) dst[e] = from_f32<T>(in(e));
+    for (int e = 2 * lane; e < d; e += 64) { const float2 v = in2(e); Pair<T>::store(dst + e, v.x, v.y); }
     return;
   }
 
@@ -95,48 +130,63 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
   float rstd = 1.0f;
   if (w != nullptr) {
     float ss = 0.0f;
-    for (int e = lane; e < d; e += 32) { const float v = in(e); ss += v * v; }
+    for (int e = 2 * lane; e < d; e += 64) { const float2 v = in2(e); ss += v.x * v.x + v.y * v.y; }
     ss = warp_sum(ss);
     rstd = rsqrtf(ss / (float)d + p.eps);
   }
-  const float fpos = (float)p.positions[t];
   // rotated pairs (i, i + half) for i < half; elements beyond rotary_dim pass through
-  for (int i = lane; i < half; i += 32) {
-    float x1 = in(i) * rstd;
-    float x2 = in(i + half) * rstd;
-    if (w != nullptr) { x1 *= w[i]; x2 *= w[i + half]; }
-    float c = 1.0f, s = 0.0f;
-    if (p.inv_freq != nullptr) {
-      const float ang = fpos * p.inv_freq[i];
-      sincosf(ang, &s, &c);
+  const float2* tab = p.rope_table ? p.rope_table + (size_t)t * half : nullptr;
+  for (int i = 2 * lane; i < half; i += 64) {
+    float2 x1 = in2(i), x2 = in2(i + half);
+    x1.x *= rstd; x1.y *= rstd; x2.x *= rstd; x2.y *= rstd;
+    if (w != nullptr) {
+      const float2 w1 = *reinterpret_cast<const float2*>(w + i);
+      const float2 w2 = *reinterpret_cast<const float2*>(w + i + half);
+      x1.x *= w1.x; x1.y *= w1.y; x2.x *= w2.x; x2.y *= w2.y;
     }
-    dst[i] = from_f32<T>(x1 * c - x2 * s);
-    dst[i + half] = from_f32<T>(x2 * c + x1 * s);
+    float4 cs = make_float4(1.0f, 0.0f, 1.0f, 0.0f);       // (cos, sin) of i and of i + 1
+    if (tab != nullptr) cs = *reinterpret_cast<const float4*>(tab + i);
+    Pair<T>::store(dst + i, x1.x * cs.x - x2.x * cs.y, x1.y * cs.z - x2.y * cs.w);
+    Pair<T>::store(dst + i + half, x2.x * cs.x + x1.x * cs.y, x2.y * cs.z + x1.y * cs.w);
   }
-  for (int e = 2 * half + lane; e < d; e += 32) {
-    float x = in(e) * rstd;
-    if (w != nullptr) x *= w[e];
-    dst[e] = from_f32<T>(x);
+  for (int e = 2 * half + 2 * lane; e < d; e += 64) {
+    float2 x = in2(e);
+    x.x *= rstd; x.y *= rstd;
+    if (w != nullptr) { x.x *= w[e]; x.y *= w[e + 1]; }
+    Pair<T>::store(dst + e, x.x, x.y);
   }
 }
 
 }  // namespace tk
 
-TK_API int tk_rope_kv(const void* qkv, const float* qkv_parts, int n_parts, void* q_out, void* k_cache, void* v_cache,
-                      const int* positions, const int* tok_req, const int* req_slot,
+TK_API int tk_rope_table(const int* positions, const float* inv_freq, float* table, int n_tokens,
+                         int rotary_dim, cudaStream_t stream) {
+  if (n_tokens <= 0 || rotary_dim <= 0) return 0;
+  if (rotary_dim & 1) return (int)cudaErrorInvalidValue;
+  const int half = rotary_dim / 2;
+  const int total = n_tokens * half;
+  return (int)tk::launch(tk::rope_table_kernel, dim3((total + 255) / 256), dim3(256), 0, stream, positions,
+                         inv_freq, (float2*)table, n_tokens, half);
+}
+
+TK_API int tk_rope_kv(const void* qkv, const float* qkv_parts, int n_parts, void* q_out, void* k_cache,
+                      void* v_cache, const int* positions, const int* tok_req, const int* req_slot,
                       const int* block_table, const float* q_norm_w, const float* k_norm_w,
-                      const float* inv_freq, int* err, int n_tokens, int n_reqs, int n_q_heads,
+                      const float* rope_table, int* err, int n_tokens, int n_reqs, int n_q_heads,
                       int n_kv_heads, int head_dim, int rotary_dim, int row_stride, int page_size,
                       int max_pages, int num_pages, int write_kv, float eps, int dtype,
                       cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (head_dim < 1 || rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) {
+  // pairs of neighbouring elements in both halves of the rotation: multiples of 4
+  if (head_dim < 4 || head_dim % 4 != 0 || rotary_dim < 0 || rotary_dim > head_dim || rotary_dim % 4 != 0 ||
+      row_stride % 2 != 0) {
     return (int)cudaErrorInvalidValue;
   }
   tk::RopeKvParams p;
-  p.qkv = qkv; p.qkv_parts = qkv_parts; p.n_parts = n_parts; p.q_out = q_out; p.k_cache = k_cache; p.v_cache = v_cache;
+  p.qkv = qkv; p.qkv_parts = qkv_parts; p.n_parts = n_parts; p.q_out = q_out; p.k_cache = k_cache;
+  p.v_cache = v_cache;
   p.positions = positions; p.tok_req = tok_req; p.req_slot = req_slot; p.block_table = block_table;
-  p.q_norm_w = q_norm_w; p.k_norm_w = k_norm_w; p.inv_freq = inv_freq; p.err = err;
+  p.q_norm_w = q_norm_w; p.k_norm_w = k_norm_w; p.rope_table = (const float2*)rope_table; p.err = err;
   p.n_tokens = n_tokens; p.n_reqs = n_reqs; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
   p.head_dim = head_dim; p.rotary_dim = rotary_dim; p.row_stride = row_stride;
   p.page_size = page_size; p.max_pages = max_pages; p.num_pages = num_pages;

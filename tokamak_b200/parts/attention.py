@@ -84,11 +84,11 @@ class Attention:
         n = h.shape[0]
         qkv = linear(h, self.w_qkv, err=step.err)
         q = torch.empty((n, spec.num_heads, spec.head_dim), dtype=h.dtype, device=h.device)
-        inv_freq, rotary_dim = self.position.rotary_table()
+        table, rotary_dim = self.position.rotary_table(step)
         ops.rope_kv(qkv, q, cache_view.k if spec.own_kv else None,
                     cache_view.v if spec.own_kv else None,
                     step.positions, step.tok_req, step.req_slot, cache_view.table,
-                    self.q_norm_w, self.k_norm_w, inv_freq, step.err,
+                    self.q_norm_w, self.k_norm_w, table, step.err,
                     n_q_heads=spec.num_heads, n_kv_heads=spec.num_kv_heads, head_dim=spec.head_dim,
                     rotary_dim=rotary_dim, eps=spec.qk_norm_eps or 0.0, write_kv=spec.own_kv)
         out = torch.empty_like(q)

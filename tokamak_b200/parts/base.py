@@ -11,7 +11,8 @@ role           interface of the registered class
 =============  ==========================================================
 norm           ``expected_tensors(spec, name)``, ``__init__(spec, name, tensors, rt)``,
                ``add_norm(resid, delta, rows=None) -> normed``
-position       ``__init__(spec, rt)``, ``rotary_table() -> (inv_freq | None, rotary_dim)``
+position       ``__init__(spec, rt)``, ``rotary_table(step) -> (table | None, rotary_dim)`` with
+               ``table`` float32 ``[tokens, rotary_dim / 2, 2]`` of (cos, sin) per token
 mixer          ``expected_tensors(spec, prefix)``, ``__init__(spec, prefix, tensors, rt)``,
                ``cache_need() -> KVPagesNeed | StateNeed | None``,
                ``forward(h, step, cache_view) -> [N, hidden]``

@@ -1,5 +1,5 @@
-"""Position encodings.  A position part hands the mixer a table of rotation
-frequencies; the rotation itself happens in the mixer's fused kernel."""
+"""Position encodings.  A position part hands the mixer a table of (cos, sin) pairs for the
+tokens of the step; the rotation itself happens in the mixer's fused kernel."""
 
 from __future__ import annotations
 
@@ -7,6 +7,7 @@ from dataclasses import dataclass
 
 import torch
 
+from ..csrc import ops
 from .base import POSITIONS, Runtime
 
 
@@ -28,8 +29,9 @@ class RopeNeox:
     (src/tokamak/model/layers.py:36-89).
 
     ``inv_freq[j] = 1 / theta ** (2j / d)`` is formed in float32 from a float32
-    ``arange`` exactly as the reference does (layers.py:47); the kernel multiplies
-    it by the float32 position and takes sine and cosine in float32.
+    ``arange`` exactly as the reference does (layers.py:47); a kernel multiplies it by
+    the float32 position and takes cosine and sine in float32, once per step: every
+    layer with the same spec reads the same table.
     """
 
     def __init__(self, spec: RopeSpec, rt: Runtime):
@@ -40,8 +42,14 @@ class RopeNeox:
                                          / spec.head_dim))
         self.inv_freq = inv_freq.to(rt.device)
 
-    def rotary_table(self) -> tuple[torch.Tensor | None, int]:
-        return self.inv_freq, self.spec.head_dim
+    def rotary_table(self, step) -> tuple[torch.Tensor | None, int]:
+        """``([tokens, head_dim / 2, 2] float32 of (cos, sin), rotary_dim)`` for the step's tokens."""
+        key = ("rope_table", self.spec)
+        table = step.scratch.get(key)
+        if table is None:
+            table = ops.rope_table(step.positions, self.inv_freq)
+            step.scratch[key] = table
+        return table, self.spec.head_dim
 
 
 @POSITIONS.register("none")
@@ -51,5 +59,5 @@ class NoPosition:
     def __init__(self, spec: NoPositionSpec, rt: Runtime):
         self.spec = spec
 
-    def rotary_table(self) -> tuple[torch.Tensor | None, int]:
+    def rotary_table(self, step) -> tuple[torch.Tensor | None, int]:
         return None, 0
