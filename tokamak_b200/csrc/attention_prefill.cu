@@ -38,7 +38,7 @@ struct PrefillParams {
 };
 
 template <int D>
-__global__ void __launch_bounds__(kPfWarps * 32)
+__global__ void __launch_bounds__(kPfWarps * 32, 3)
 attn_prefill_kernel(PrefillParams p) {
   pdl_trigger();
   pdl_wait();
@@ -160,15 +160,31 @@ attn_prefill_kernel(PrefillParams p) {
     }
 
     float mx[2] = {-INFINITY, -INFINITY};
+    // a tile that lies wholly below the diagonal and inside the window of all 16 rows of this
+    // warp needs no mask
+    const int key_first = kt * kPfKeys, key_last = key_first + kPfKeys - 1;
+    const bool interior = (wr + 15 < rows_here) && key_last <= pos0 + wr &&
+                          (p.window <= 0 || key_first >= pos0 + wr + 15 - p.window + 1);
+    if (interior) {
 #pragma unroll
-    for (int nt = 0; nt < kPfKeys / 8; ++nt) {
+      for (int nt = 0; nt < kPfKeys / 8; ++nt) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = kt * kPfKeys + nt * 8 + 2 * t4 + (e & 1);
-        const bool valid = (e < 2) ? (hasA && key <= posA && key >= loA)
-                                   : (hasB && key <= posB && key >= loB);
-        s[nt][e] = valid ? s[nt][e] * p.scale_log2 : -INFINITY;
-        mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+        for (int e = 0; e < 4; ++e) {
+          s[nt][e] *= p.scale_log2;
+          mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int nt = 0; nt < kPfKeys / 8; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = key_first + nt * 8 + 2 * t4 + (e & 1);
+          const bool valid = (e < 2) ? (hasA && key <= posA && key >= loA)
+                                     : (hasB && key <= posB && key >= loB);
+          s[nt][e] = valid ? s[nt][e] * p.scale_log2 : -INFINITY;
+          mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+        }
       }
     }
     float corr[2], m_use[2];
