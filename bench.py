@@ -237,7 +237,7 @@ def kernel_case(name: str, batch: int, ctx: int, iters: int, peaks: dict) -> dic
     err = torch.zeros(4, dtype=torch.int32, device=dev)
     gen = torch.Generator(device=dev).manual_seed(0)
     flops = 0.0
-    if name in ("attention_decode", "attention_prefill"):
+    if name in ("attention_decode", "attention_prefill", "attention_prefill_mma"):
         pages_per_req = -(-ctx // page)
         num_pages = batch * pages_per_req
         kc = torch.randn((num_pages, hkv, page, d), device=dev, generator=gen).bfloat16()
@@ -257,11 +257,13 @@ def kernel_case(name: str, batch: int, ctx: int, iters: int, peaks: dict) -> dic
         else:
             q = torch.randn((batch * ctx, hq, d), device=dev, generator=gen).bfloat16()
             out = torch.empty_like(q)
-            tiles = [(r, t) for t in reversed(range(-(-ctx // 64))) for r in range(batch)]
+            rows = 64 if name == "attention_prefill_mma" else 128      # tcgen05 kernel: 128-token tiles
+            fn = ops.attention_prefill if name == "attention_prefill_mma" else ops.attention_prefill_tc
+            tiles = [(r, t) for t in reversed(range(-(-ctx // rows))) for r in range(batch)]
             tiles_t = i32([x for rt in tiles for x in rt])
             q_start, q_len = i32([r * ctx for r in range(batch)]), i32([ctx] * batch)
-            run = lambda: ops.attention_prefill(q, out, kc, vc, tiles_t, q_start, q_len, q_len, slots, table,
-                                                err, scale=d ** -0.5, window=None)
+            run = lambda: fn(q, out, kc, vc, tiles_t, q_start, q_len, q_len, slots, table, err,
+                             scale=d ** -0.5, window=None)
             nbytes = 2 * kc.numel() * 2 + 2 * q.numel() * 2
             flops = batch * 2.0 * 2.0 * (ctx * (ctx + 1) / 2) * hq * d
     elif name == "rmsnorm":
@@ -314,7 +316,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
     ap.add_argument("--kernel", default=None, help="time one kernel alone instead: attention_decode, "
-                    "attention_prefill, rmsnorm, gemm_decode")
+                    "attention_prefill (tcgen05), attention_prefill_mma, rmsnorm, gemm_decode")
     ap.add_argument("--ctx", type=int, default=CONTEXT, help="context length of a --kernel case")
     args = ap.parse_args()
 

@@ -429,17 +429,44 @@ def test_attention_decode_finds_the_one_key_that_matters(where):
         torch.testing.assert_close(out[0], hit, rtol=5e-2, atol=5e-2)
 
 
-# ----------------------------------------------------------------------------- flash prefill kernel
+# ----------------------------------------------------------------------------- flash prefill kernels
 
+def zero_rest_of_last_pages(kc, vc, table, kv_lens, page):
+    """What the cache-writing kernel guarantees to kernels that load whole pages: behind a
+    request's last position its page holds zeros, never stale values."""
+    for r, l in enumerate(kv_lens):
+        if l % page:
+            pg = int(table[r, (l - 1) // page])
+            kc[pg, :, l % page:] = 0
+            vc[pg, :, l % page:] = 0
+
+
+def run_prefill(kernel, q, out, kc, vc, q_lens, kv_lens, q_start, table, scale, window):
+    from tokamak_b200.csrc import ops
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    rows = 128 if kernel == "tc" else 64
+    tiles = [(r, t) for r in range(len(q_lens)) for t in range(-(-q_lens[r] // rows))][::-1]
+    fn = ops.attention_prefill_tc if kernel == "tc" else ops.attention_prefill
+    err = err_word()
+    fn(q, out, kc, vc, i32([x for rt in tiles for x in rt]), i32(q_start), i32(q_lens), i32(kv_lens),
+       i32(list(range(len(q_lens)))), table.to(DEV), err, scale=scale, window=window)
+    torch.cuda.synchronize()
+    assert err.tolist()[0] == 0, err.tolist()
+
+
+@pytest.mark.parametrize("kernel", ["mma", "tc"])
 @pytest.mark.parametrize("hq,hkv,d,page,window", [(8, 2, 128, 16, None), (4, 4, 64, 16, None),
                                                     (6, 1, 64, 8, None), (8, 8, 128, 32, 50),
-                                                    (3, 1, 128, 16, 200), (10, 5, 64, 4, 9)])
-def test_attention_prefill_portions(hq, hkv, d, page, window):
-    """Whole prompts and portions that continue a request, with lengths around the 64-token
-    tile and the page edges; unwritten cache slots are NaN."""
+                                                    (3, 1, 128, 16, 200), (10, 5, 64, 4, 9),
+                                                    (4, 2, 128, 64, None), (2, 1, 64, 128, 300)])
+def test_attention_prefill_portions(kernel, hq, hkv, d, page, window):
+    """Whole prompts and portions that continue a request, with lengths around the tile sizes
+    and the page edges; cache slots that no request has written are NaN."""
     from tokamak_b200.csrc import ops
-    kv_lens = [2, 64, 65, 300, 129, 1000, 47]
-    q_lens = [2, 64, 65, 37, 128, 130, 3]        # whole, whole, whole, portion, portion, portion, portion
+    if kernel == "tc" and not ops.prefill_tc_kernel_takes(hq, hkv, d, page):
+        pytest.skip("page size not taken by the tcgen05 kernel")
+    kv_lens = [2, 64, 65, 300, 129, 1000, 47, 256, 385]
+    q_lens = [2, 64, 65, 37, 128, 130, 3, 256, 129]      # whole prompts and portions
     n_reqs = len(kv_lens)
     max_pages = max(-(-l // page) for l in kv_lens)
     num_pages = n_reqs * max_pages + 5
@@ -448,30 +475,25 @@ def test_attention_prefill_portions(hq, hkv, d, page, window):
     k_all = [torch.randn(l, hkv, d, generator=gen).bfloat16().float() for l in kv_lens]
     v_all = [torch.randn(l, hkv, d, generator=gen).bfloat16().float() for l in kv_lens]
     kc, vc = fill_cache(k_all, v_all, table, num_pages, page, torch.bfloat16)
+    if kernel == "tc":
+        zero_rest_of_last_pages(kc, vc, table, kv_lens, page)
     positions, tok_req, q_start = [], [], []
     for r, (kl, ql) in enumerate(zip(kv_lens, q_lens)):
         q_start.append(len(positions))
         positions += list(range(kl - ql, kl)); tok_req += [r] * ql
     n = len(positions)
     q = torch.randn(n, hq, d, generator=gen).bfloat16()
-    tiles = [(r, t) for r in range(n_reqs) for t in range(-(-q_lens[r] // 64))]
-    tiles = tiles[::-1]
-    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
-    err = err_word()
     out = torch.full_like(q, float("nan")).to(DEV)
     scale = d ** -0.5
-    ops.attention_prefill(q.to(DEV), out, kc, vc, i32([x for rt in tiles for x in rt]), i32(q_start),
-                          i32(q_lens), i32(kv_lens), i32(list(range(n_reqs))), table.to(DEV), err,
-                          scale=scale, window=window)
-    assert err.tolist()[0] == 0
+    run_prefill(kernel, q.to(DEV), out, kc, vc, q_lens, kv_lens, q_start, table, scale, window)
     want = attention_reference(q.float(), k_all, v_all, positions, tok_req, scale, window)
     torch.testing.assert_close(out.double().cpu(), want, **tol(torch.bfloat16))
 
 
+@pytest.mark.parametrize("kernel", ["mma", "tc"])
 @pytest.mark.parametrize("where", ["first", "far", "page_edge", "diagonal", "window_edge", "just_outside"])
-def test_attention_prefill_finds_the_one_key_that_matters(where):
+def test_attention_prefill_finds_the_one_key_that_matters(kernel, where):
     """The last query of a 100-token portion at the end of 900 tokens must find one key."""
-    from tokamak_b200.csrc import ops
     hq, hkv, d, page = 4, 2, 128, 16
     kv_len, q_len, window = 900, 100, None
     target = {"first": 0, "far": 123, "page_edge": 16 * 30 - 1, "diagonal": kv_len - 1,
@@ -490,12 +512,10 @@ def test_attention_prefill_finds_the_one_key_that_matters(where):
     max_pages = -(-kv_len // page)
     table = make_tables(1, max_pages, max_pages + 9, seed=4)
     kc, vc = fill_cache([k], [v], table, max_pages + 9, page, torch.bfloat16)
-    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
-    err = err_word()
+    if kernel == "tc":
+        zero_rest_of_last_pages(kc, vc, table, [kv_len], page)
     out = torch.empty(q_len, hq, d, dtype=torch.bfloat16, device=DEV)
-    ops.attention_prefill(q.bfloat16().to(DEV), out, kc, vc, i32([0, 1, 0, 0]), i32([0]), i32([q_len]),
-                          i32([kv_len]), i32([0]), table.to(DEV), err, scale=1.0, window=window)
-    assert err.tolist()[0] == 0
+    run_prefill(kernel, q.bfloat16().to(DEV), out, kc, vc, [q_len], [kv_len], [0], table, 1.0, window)
     positions = list(range(kv_len - q_len, kv_len))
     want = attention_reference(q, [k], [v], positions, [0] * q_len, 1.0, window)
     out = out.double().cpu()
@@ -505,6 +525,29 @@ def test_attention_prefill_finds_the_one_key_that_matters(where):
         assert (out[-1] - hit).abs().max() > 0.1
     else:
         torch.testing.assert_close(out[-1], hit, rtol=5e-2, atol=5e-2)
+
+
+def test_rope_kv_clears_the_rest_of_a_page_begun_in_this_step():
+    from tokamak_b200.csrc import ops
+    hq, hkv, d, page = 2, 2, 16, 8
+    # request 0 brings 11 tokens from position 0 (pages 0 and 1 begun now: slots 3.. of page 1 cleared);
+    # request 1 brings 2 tokens at positions 9, 10 (its page was begun earlier: nothing cleared)
+    q_lens, kv_lens = [11, 2], [11, 11]
+    positions = list(range(11)) + [9, 10]
+    tok_req = [0] * 11 + [1] * 2
+    table = torch.tensor([[3, 1], [0, 2]], dtype=torch.int32)
+    qkv = torch.randn(13, (hq + 2 * hkv) * d, device=DEV)
+    kc = torch.full((4, hkv, page, d), 7.0, device=DEV)
+    vc = torch.full_like(kc, 7.0)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    err = err_word()
+    ops.rope_kv(qkv, torch.empty(13, hq, d, device=DEV), kc, vc, i32(positions), i32(tok_req), i32([0, 1]),
+                table.to(DEV), None, None, None, err, n_q_heads=hq, n_kv_heads=hkv, head_dim=d, rotary_dim=0,
+                eps=0.0, req_q_len=i32(q_lens), req_kv_len=i32(kv_lens))
+    assert err.tolist()[0] == 0
+    assert (vc[1, :, 3:] == 0).all() and (kc[1, :, 3:] == 0).all()        # request 0, page 1, slots 3..7
+    assert (vc[2, :, 3:] == 7).all() and (vc[2, :, :1] == 7).all()        # request 1: untouched around its tokens
+    assert (vc[3] != 7).all() and (vc[0] == 7).all()
 
 
 # ----------------------------------------------------------------------------- tcgen05 matrix product

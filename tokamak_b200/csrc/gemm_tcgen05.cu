@@ -19,16 +19,13 @@
 // Every wait on an mbarrier is bounded; a wait that runs out records kErrWait, raises a
 // block-wide abort flag and the block leaves through the common exit that frees its
 // tensor memory.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05_utils.cuh"
 
 namespace tk {
 
 constexpr int kGtBM = 128;        // rows of R per block = UMMA M
 constexpr int kGtBK = 64;         // k-elements per stage = one 128-byte swizzle span of bf16
 constexpr int kGtThreads = 192;   // warp 0: TMA, warp 1: MMA, warps 2..5: epilogue
-constexpr unsigned kGtSpinLimit = 1u << 22;
 
 struct GemmTcParams {
   void* out;                // swapped: float [n_splits, cols_total, rows_total]; else [rows_total, cols_total]
@@ -43,77 +40,6 @@ struct GemmTcParams {
   int out_f32;              // non-swapped: 1 = float32 output, 0 = bfloat16
   long long ld_out;         // non-swapped: elements between output rows
 };
-
-__device__ __forceinline__ uint32_t gt_smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-// Bounded wait for the phase with the given parity; false when the limit ran out or the block aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (unsigned spin = 0; spin < kGtSpinLimit; ++spin) {
-    uint32_t done;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (done) return true;
-    if ((spin & 1023u) == 1023u && *abort_flag) return false;
-  }
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
-      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
-      : "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
-// groups of 8 rows 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
-  uint64_t desc = 0;
-  desc |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);          // start address, 16-byte units
-  desc |= (uint64_t)1 << 16;                                 // leading byte offset (unused for this layout)
-  desc |= (uint64_t)(1024 >> 4) << 32;                       // stride byte offset: 8 rows * 128 B
-  desc |= (uint64_t)1 << 46;                                 // descriptor version of sm_100
-  desc |= (uint64_t)2 << 61;                                 // layout: 128-byte swizzle
-  return desc;
-}
-
-// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = bn.
-__device__ __forceinline__ uint32_t umma_idesc_bf16(int bn) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kGtBM >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar)
-               : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
 
 __global__ void __launch_bounds__(kGtThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_c,
@@ -300,24 +226,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
 }
 
 // ---- host side ------------------------------------------------------------------------------
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess) {
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
-  }
-  return fn;
-}
 
 // Map of a row-major bf16 matrix [rows, k] (row stride ld elements) with boxes of box_rows x 64.
 static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long k, long long ld, int box_rows) {

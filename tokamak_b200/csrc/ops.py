@@ -131,11 +131,14 @@ def rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | None
             req_slot: torch.Tensor, block_table: torch.Tensor, q_norm_w: torch.Tensor | None,
             k_norm_w: torch.Tensor | None, table: torch.Tensor | None, err: torch.Tensor, *,
             n_q_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int, eps: float,
-            write_kv: bool = True) -> None:
+            write_kv: bool = True, req_q_len: torch.Tensor | None = None,
+            req_kv_len: torch.Tensor | None = None) -> None:
     """Per-head norm of q and k, rotation, and the write of k and v into their pages.
 
     ``qkv`` is ``[tokens, (Hq + 2 Hkv) d]`` in the activation type, or float32 partial sums
-    ``[parts, tokens, (Hq + 2 Hkv) d]`` that the kernel adds up."""
+    ``[parts, tokens, (Hq + 2 Hkv) d]`` that the kernel adds up.  With ``req_q_len`` and
+    ``req_kv_len`` the last token of every request also clears the rest of a page begun in
+    this step (the tcgen05 attention kernel loads whole pages and relies on it)."""
     _want(qkv, None, "qkv"); _want(q_out, None, "q_out")
     parts, n_parts = None, 0
     if qkv.dim() == 3:
@@ -176,7 +179,8 @@ def rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | None
         num_pages, page_size = 0, 1
     _check(library().tk_rope_kv(_ptr(qkv), _ptr(parts), n_parts, q_out.data_ptr(), _ptr(k_cache), _ptr(v_cache),
                                 positions.data_ptr(), tok_req.data_ptr(), req_slot.data_ptr(),
-                                block_table.data_ptr(), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(table),
+                                block_table.data_ptr(), _ptr(req_q_len), _ptr(req_kv_len),
+                                _ptr(q_norm_w), _ptr(k_norm_w), _ptr(table),
                                 err.data_ptr(), n, req_slot.numel(), n_q_heads, n_kv_heads, head_dim,
                                 rotary_dim, row, page_size, block_table.shape[1], num_pages,
                                 1 if write_kv else 0, float(eps), dtype_code(q_out.dtype), _stream()),
@@ -272,6 +276,35 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
                                           tiles.numel() // 2, req_slot.numel(), hq, hkv, d, page_size,
                                           block_table.shape[1], num_pages, int(window or 0),
                                           float(scale), _stream()), "attention_prefill")
+
+
+def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                         tiles: torch.Tensor, req_q_start: torch.Tensor, req_q_len: torch.Tensor,
+                         req_kv_len: torch.Tensor, req_slot: torch.Tensor, block_table: torch.Tensor,
+                         err: torch.Tensor, *, scale: float, window: int | None) -> None:
+    """Paged flash attention on tcgen05 for the 128-token query tiles listed in ``tiles``
+    (int32 ``[n_tiles, 2]``: request row, tile index).  Loads whole pages: the cache must have been
+    written by :func:`rope_kv` with ``req_q_len`` and ``req_kv_len`` given."""
+    _want(q, torch.bfloat16, "q"); _want(out, torch.bfloat16, "out")
+    _want(k_cache, torch.bfloat16, "k_cache"); _want(v_cache, torch.bfloat16, "v_cache")
+    _want(tiles, torch.int32, "tiles")
+    n, hq, d = q.shape
+    num_pages, hkv, page_size, dk = k_cache.shape
+    if not prefill_tc_kernel_takes(hq, hkv, d, page_size) or dk != d:
+        raise KernelError(f"the tcgen05 prefill kernel does not take heads {hq}/{hkv}, head_dim {d}, "
+                          f"page size {page_size}")
+    _check(library().tk_attention_prefill_tc(q.data_ptr(), out.data_ptr(), k_cache.data_ptr(),
+                                             v_cache.data_ptr(), tiles.data_ptr(), req_q_start.data_ptr(),
+                                             req_q_len.data_ptr(), req_kv_len.data_ptr(),
+                                             req_slot.data_ptr(), block_table.data_ptr(), err.data_ptr(),
+                                             n, tiles.numel() // 2, req_slot.numel(), hq, hkv, d, page_size,
+                                             block_table.shape[1], num_pages, int(window or 0),
+                                             float(scale), _stream()), "attention_prefill_tc")
+
+
+def prefill_tc_kernel_takes(n_q_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    """Shapes of the tcgen05 prefill kernel."""
+    return bool(library().tk_attention_prefill_tc_takes(n_q_heads, n_kv_heads, head_dim, page_size))
 
 
 def prefill_kernel_takes(n_q_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> bool:

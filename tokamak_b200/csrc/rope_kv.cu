@@ -42,6 +42,8 @@ struct RopeKvParams {
   const int* tok_req;       // [n_tokens] row of the token's request in this step
   const int* req_slot;      // [n_reqs]   row of the request in block_table
   const int* block_table;   // [n_slots, max_pages]
+  const int* req_q_len;     // [n_reqs] tokens the request brings to this step, or null
+  const int* req_kv_len;    // [n_reqs] positions of the request after this step, or null
   const float* q_norm_w;    // [head_dim] or null
   const float* k_norm_w;    // [head_dim] or null
   const float2* rope_table; // [n_tokens, rotary_dim / 2] (cos, sin) or null (no rotation)
@@ -106,6 +108,7 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
   };
 
   T* dst;
+  int zero_rows = 0;        // rows after this token's slot that are cleared (see below)
   if (kind == 0) {
     dst = (T*)p.q_out + ((size_t)t * p.n_q_heads + head) * d;
   } else {
@@ -119,6 +122,18 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
     if (page < 0 || page >= p.num_pages) { if (lane == 0) set_error(p.err, kErrPage, t, pidx, page); return; }
     T* base = (T*)(kind == 1 ? p.k_cache : p.v_cache);
     dst = base + (((size_t)page * p.n_kv_heads + head) * p.page_size + (pos % p.page_size)) * d;
+    // The request's last token of this step clears the rest of its page if the page was begun
+    // in this step, so that a live page never holds stale values behind the last position:
+    // kernels that load whole pages multiply them by probabilities that are exactly zero.
+    if (p.req_kv_len != nullptr) {
+      const int kv_len = p.req_kv_len[r], q_len = p.req_q_len[r];
+      if (pos == kv_len - 1 && pos - pos % p.page_size >= kv_len - q_len) {
+        zero_rows = p.page_size - 1 - pos % p.page_size;
+      }
+    }
+  }
+  for (int z = 1; z <= zero_rows; ++z) {
+    for (int e = 2 * lane; e < d; e += 64) Pair<T>::store(dst + (size_t)z * d + e, 0.0f, 0.0f);
   }
 
   if (kind == 2) {
@@ -171,7 +186,8 @@ TK_API int tk_rope_table(const int* positions, const float* inv_freq, float* tab
 
 TK_API int tk_rope_kv(const void* qkv, const float* qkv_parts, int n_parts, void* q_out, void* k_cache,
                       void* v_cache, const int* positions, const int* tok_req, const int* req_slot,
-                      const int* block_table, const float* q_norm_w, const float* k_norm_w,
+                      const int* block_table, const int* req_q_len, const int* req_kv_len,
+                      const float* q_norm_w, const float* k_norm_w,
                       const float* rope_table, int* err, int n_tokens, int n_reqs, int n_q_heads,
                       int n_kv_heads, int head_dim, int rotary_dim, int row_stride, int page_size,
                       int max_pages, int num_pages, int write_kv, float eps, int dtype,
@@ -186,6 +202,7 @@ TK_API int tk_rope_kv(const void* qkv, const float* qkv_parts, int n_parts, void
   p.qkv = qkv; p.qkv_parts = qkv_parts; p.n_parts = n_parts; p.q_out = q_out; p.k_cache = k_cache;
   p.v_cache = v_cache;
   p.positions = positions; p.tok_req = tok_req; p.req_slot = req_slot; p.block_table = block_table;
+  p.req_q_len = req_q_len; p.req_kv_len = req_kv_len;
   p.q_norm_w = q_norm_w; p.k_norm_w = k_norm_w; p.rope_table = (const float2*)rope_table; p.err = err;
   p.n_tokens = n_tokens; p.n_reqs = n_reqs; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
   p.head_dim = head_dim; p.rotary_dim = rotary_dim; p.row_stride = row_stride;

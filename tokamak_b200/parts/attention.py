@@ -90,7 +90,8 @@ class Attention:
                     step.positions, step.tok_req, step.req_slot, cache_view.table,
                     self.q_norm_w, self.k_norm_w, table, step.err,
                     n_q_heads=spec.num_heads, n_kv_heads=spec.num_kv_heads, head_dim=spec.head_dim,
-                    rotary_dim=rotary_dim, eps=spec.qk_norm_eps or 0.0, write_kv=spec.own_kv)
+                    rotary_dim=rotary_dim, eps=spec.qk_norm_eps or 0.0, write_kv=spec.own_kv,
+                    req_q_len=step.req_q_len, req_kv_len=step.req_kv_len)
         out = torch.empty_like(q)
         paged_attention(q, out, cache_view, step, scale=self.scale, window=spec.window)
         return linear(out.view(n, spec.num_heads * spec.head_dim), self.w_o, err=step.err)
@@ -101,8 +102,9 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
     """Attention of every token of the step over the pages of its own request.
 
     Chooses the kernels.  bfloat16 with a head_dim the tiled kernels take: single next
-    tokens go to the split-K decode kernel, portions of prompts to the flash prefill
-    kernel.  float32, and every other shape, runs on the general kernel.
+    tokens go to the split-K decode kernel, portions of prompts to the tcgen05 flash
+    prefill kernel (or to the mma.sync one for page sizes it does not take).  float32,
+    and every other shape, runs on the general kernel.
     """
     n, hq, d = q.shape
     hkv, page = cache_view.k.shape[1], cache_view.k.shape[2]
@@ -115,7 +117,11 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
         ops.attention_decode(q, out, cache_view.k, cache_view.v, step.decode_items, step.positions,
                              step.tok_req, step.req_slot, cache_view.table, step.err, scale=scale,
                              window=window, n_splits=ops.decode_splits(n_dec, hkv, step.max_kv_len))
-    if pf_tiled:
+    if pf_tiled and ops.prefill_tc_kernel_takes(hq, hkv, d, page):
+        ops.attention_prefill_tc(q, out, cache_view.k, cache_view.v, step.prefill_tiles128,
+                                 step.req_q_start, step.req_q_len, step.req_kv_len, step.req_slot,
+                                 cache_view.table, step.err, scale=scale, window=window)
+    elif pf_tiled:
         ops.attention_prefill(q, out, cache_view.k, cache_view.v, step.prefill_tiles,
                               step.req_q_start, step.req_q_len, step.req_kv_len, step.req_slot,
                               cache_view.table, step.err, scale=scale, window=window)
