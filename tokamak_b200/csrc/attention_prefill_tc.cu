@@ -237,16 +237,28 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       __syncwarp();
       if (lane == 0) mbar_arrive(gt_smem_u32(&s_empty[j & 1]));
 
+      // Scores stay unscaled in sv; the softmax scale (> 0) is folded into the exponent below.
+      // A tile wholly below this row's diagonal and inside its window needs no mask.
       const int key_first = (first_kt + j) * kAtBN;
+      const bool interior = row_valid && key_first + kAtBN - 1 <= pos_r && key_first >= lo_r;
       float mx = -INFINITY;
       float sv[kAtBN];
+      if (interior) {
 #pragma unroll
-      for (int c = 0; c < kAtBN; ++c) {
-        const int key = key_first + c;
-        const bool valid = row_valid && key <= pos_r && key >= lo_r;
-        sv[c] = valid ? __uint_as_float(sraw[c]) * p.scale_log2 : -INFINITY;
-        mx = fmaxf(mx, sv[c]);
+        for (int c = 0; c < kAtBN; ++c) {
+          sv[c] = __uint_as_float(sraw[c]);
+          mx = fmaxf(mx, sv[c]);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < kAtBN; ++c) {
+          const int key = key_first + c;
+          const bool valid = row_valid && key <= pos_r && key >= lo_r;
+          sv[c] = valid ? __uint_as_float(sraw[c]) : -INFINITY;
+          mx = fmaxf(mx, sv[c]);
+        }
       }
+      mx *= p.scale_log2;       // -inf stays -inf
       const float m_new = fmaxf(m_ref, mx);
       const bool need = m_new > m_ref + kAtRescale;     // also true when the first visible key arrives
       if (__any_sync(0xffffffffu, need)) {
@@ -274,7 +286,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       float psum = 0.0f;
 #pragma unroll
       for (int c = 0; c < kAtBN; ++c) {
-        sv[c] = exp2f(sv[c] - m_use);
+        sv[c] = exp2f(fmaf(sv[c], p.scale_log2, -m_use));
         psum += sv[c];
       }
       l_sum += psum;
