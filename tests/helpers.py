@@ -47,10 +47,17 @@ def plain_logits(folder, tokens) -> torch.Tensor:
 
 
 # Tolerances.  float32: the engine and the float64 truth differ by rounding of 32-bit
-# sums only.  bfloat16: activations are rounded to 8 bits of mantissa between kernels;
-# the error is judged against the spread of the logits of the row.
+# sums only.  bfloat16: activations are rounded to 8 bits of mantissa between kernels; the
+# error of a row of logits is judged against the spread (standard deviation) of that row, as
+# a root mean square over the vocabulary and as a maximum.  The limits are set by what
+# bfloat16 itself costs, measured once at the Qwen3-8B layer sizes (two layers, 150 tokens,
+# vocabulary 2048): a plain PyTorch pipeline that rounds where the reference's bfloat16 model
+# rounds is off by 1.45e-2 (rms) and 7.6e-2 (max) of the row's spread; this engine, which keeps
+# the residual stream and the rotation in float32, by 1.1e-2 and 6.1e-2.  A wrong key, page or
+# mask shows as an error of the order of the spread itself.
 F32_ATOL, F32_RTOL = 2e-4, 2e-4
-BF16_REL_TO_ROW = 4e-2
+BF16_RMS_TO_ROW = 2e-2
+BF16_MAX_TO_ROW = 1e-1
 
 
 def assert_logits_close(got: torch.Tensor, want: torch.Tensor, dtype: str, what: str = "") -> None:
@@ -69,8 +76,14 @@ def assert_logits_close(got: torch.Tensor, want: torch.Tensor, dtype: str, what:
                                  f"max err {err.max():.3e}")
     else:
         spread = want.std(dim=-1, keepdim=True).clamp_min(1e-6)
-        rel = ((got - want).abs() / spread).amax(dim=-1)
-        worst = int(rel.argmax())
-        assert rel[worst] <= BF16_REL_TO_ROW, (
-            f"{what}: row {worst} differs by {rel[worst]:.3e} of the row's spread "
-            f"(limit {BF16_REL_TO_ROW})")
+        rel = (got - want).abs() / spread
+        rms = rel.pow(2).mean(dim=-1).sqrt()
+        worst = int(rms.argmax())
+        assert rms[worst] <= BF16_RMS_TO_ROW, (
+            f"{what}: row {worst} is off by {rms[worst]:.3e} (rms) of the row's spread "
+            f"(limit {BF16_RMS_TO_ROW})")
+        mx = rel.amax(dim=-1)
+        worst = int(mx.argmax())
+        assert mx[worst] <= BF16_MAX_TO_ROW, (
+            f"{what}: row {worst} is off by {mx[worst]:.3e} (max) of the row's spread "
+            f"(limit {BF16_MAX_TO_ROW})")

@@ -64,3 +64,12 @@ ALL = {
     "C": (TINY_C, TINY_C_INIT, TINY_C_PAGE),
     "D": (TINY_D, TINY_D_INIT, TINY_D_PAGE),
 }
+
+# The layer sizes of Qwen3-8B (hidden 4096, 32 query / 8 key-value heads of 128, intermediate 12288)
+# with two layers and a small vocabulary: the shapes the serving kernels are tuned for.
+LAYER_8B = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "num_hidden_layers": 2, "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8,
+    "head_dim": 128, "intermediate_size": 12288, "vocab_size": 2048, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 4096,
+}
