@@ -274,6 +274,18 @@ def kernel_case(name: str, batch: int, ctx: int, iters: int, peaks: dict) -> dic
         out = torch.empty((n, h), dtype=torch.bfloat16, device=dev)
         run = lambda: ops.add_rmsnorm(resid, delta, w, out, 1e-6)
         nbytes = n * h * (4 + 2 + 4 + 2)
+    elif name == "gemm_tc_decode":
+        # the engine's own decode product: gate_up of one layer on tcgen05, weight as the row operand
+        w = torch.randn((2 * cfg["intermediate_size"], cfg["hidden_size"]), device=dev, generator=gen).bfloat16()
+        ws = [w.clone() for _ in range(4)]
+        x = torch.randn((batch, cfg["hidden_size"]), device=dev, generator=gen).bfloat16()
+        splits, stages = ops.swapped_gemm_plan(w.shape[0], w.shape[1])
+        out = torch.empty((splits, batch, w.shape[0]), dtype=torch.float32, device=dev)
+        turn = [0]
+        def run():
+            turn[0] = (turn[0] + 1) % len(ws)
+            ops.gemm_tc_swapped(ws[turn[0]], x, err, splits, out=out, max_stages=stages)
+        nbytes = w.numel() * 2
     elif name == "gemm_decode":
         # the library product the decode step uses, for comparison: gate_up of one layer
         w = torch.randn((2 * cfg["intermediate_size"], cfg["hidden_size"]), device=dev, generator=gen).bfloat16()
@@ -316,7 +328,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
     ap.add_argument("--kernel", default=None, help="time one kernel alone instead: attention_decode, "
-                    "attention_prefill (tcgen05), attention_prefill_mma, rmsnorm, gemm_decode")
+                    "attention_prefill (tcgen05), attention_prefill_mma, rmsnorm, gemm_tc_decode, gemm_decode (library)")
     ap.add_argument("--ctx", type=int, default=CONTEXT, help="context length of a --kernel case")
     args = ap.parse_args()
 
