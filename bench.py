@@ -257,7 +257,7 @@ def kernel_case(name: str, batch: int, ctx: int, iters: int, peaks: dict) -> dic
         else:
             q = torch.randn((batch * ctx, hq, d), device=dev, generator=gen).bfloat16()
             out = torch.empty_like(q)
-            rows = 64 if name == "attention_prefill_mma" else 128      # tcgen05 kernel: 128-token tiles
+            rows = 64 if name == "attention_prefill_mma" else ops.PREFILL_TC_ROWS
             fn = ops.attention_prefill if name == "attention_prefill_mma" else ops.attention_prefill_tc
             tiles = [(r, t) for t in reversed(range(-(-ctx // rows))) for r in range(batch)]
             tiles_t = i32([x for rt in tiles for x in rt])

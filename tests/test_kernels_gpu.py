@@ -444,7 +444,7 @@ def zero_rest_of_last_pages(kc, vc, table, kv_lens, page):
 def run_prefill(kernel, q, out, kc, vc, q_lens, kv_lens, q_start, table, scale, window):
     from tokamak_b200.csrc import ops
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
-    rows = 128 if kernel == "tc" else 64
+    rows = ops.PREFILL_TC_ROWS if kernel == "tc" else 64
     tiles = [(r, t) for r in range(len(q_lens)) for t in range(-(-q_lens[r] // rows))][::-1]
     fn = ops.attention_prefill_tc if kernel == "tc" else ops.attention_prefill
     err = err_word()

@@ -1,39 +1,44 @@
 // Paged flash attention for portions of prompts on the 5th-generation tensor cores
 // (bfloat16, head_dim 64 or 128).
 //
-// One thread block per (tile of 128 query tokens of one request, query head):
-//   warp 0      TMA: the query tile once, then key and value tiles of 64 keys, page by page
-//               (cp.async.bulk.tensor, 128-byte swizzle, no multicast), into a ring of stages;
-//   warp 1      one thread issues tcgen05.mma: S = Q K^T (M 128, N 64) into one of two score
-//               buffers in tensor memory, and O += P V (M 128, N head_dim) with V read straight
-//               from its page layout as an MN-major operand;
-//   warps 2..5  softmax: thread i owns query row i = tensor-memory lane i.  It reads its 64
-//               scores with tcgen05.ld, masks (causal with offset kv_len - q_len, window),
-//               keeps a reference maximum and the normaliser in float32, writes the
-//               probabilities as bfloat16 into a swizzled shared tile for the second product,
-//               and rescales the output accumulator in tensor memory only when the row maximum
-//               has grown by more than 2^8 since the reference was set (the probabilities stay
-//               below 2^8, exact enough in bfloat16; the result is the same softmax).
-// The score buffers and the probability tiles are double-buffered, so the products of one key
-// tile overlap the softmax of the next.
+// One thread block per (256 query tokens of one request, query head), handled as two query
+// tiles of 128 rows that share every key and value tile:
+//   warp 0       TMA: the query tiles once, then key and value tiles of 64 keys, page by page
+//                (cp.async.bulk.tensor, 128-byte swizzle, no multicast), into a ring of stages;
+//   warp 1       one thread issues tcgen05.mma for both query tiles: S = Q K^T (M 128, N 64)
+//                into one of the tile's two score buffers in tensor memory, and O += P V
+//                (M 128, N head_dim) with V read straight from its page layout as an MN-major
+//                operand;
+//   warps 2..5   softmax of query tile 0, warps 6..9 of query tile 1: thread i owns query row
+//                i = tensor-memory lane i.  It reads its 64 scores with tcgen05.ld, masks
+//                (causal with offset kv_len - q_len, window), keeps a reference maximum and
+//                the normaliser in float32, writes the probabilities as bfloat16 into a swizzled
+//                shared tile for the second product, and rescales the output accumulator in
+//                tensor memory only when the row maximum has grown by more than 2^8 since the
+//                reference was set (the probabilities stay below 2^8, exact enough in bfloat16;
+//                the result is the same softmax).
+// Score buffers and probability tiles are double-buffered per query tile, so the tensor cores
+// work for one tile, or on the next key tile, while the other tile's softmax runs; two softmax
+// warps share every scheduler.
 //
-// Pages are loaded whole.  A page that lies outside the tile's visible keys is replaced by the
-// page of the tile's last key (its probabilities are exactly zero), and the kernel that writes
+// Pages are loaded whole.  A page that lies outside the block's visible keys is replaced by the
+// page of the block's last key (its probabilities are exactly zero), and the kernel that writes
 // the cache zero-fills the unwritten rest of a request's last page, so no stale value can turn
 // a zero probability into a NaN.  Every mbarrier wait is bounded and reports kErrWait.
 #include "tcgen05_utils.cuh"
 
 namespace tk {
 
-constexpr int kAtBM = 128;
-constexpr int kAtBN = 64;
+constexpr int kAtBM = 128;            // rows of one query tile
+constexpr int kAtQT = 2;              // query tiles per block
+constexpr int kAtBN = 64;             // keys per tile
 constexpr int kAtStages = 3;
-constexpr int kAtThreads = 192;
+constexpr int kAtThreads = 64 + kAtQT * 128;
 constexpr float kAtRescale = 8.0f;    // log2 units
 
 struct AttnTcParams {
   __nv_bfloat16* out;            // [n_tokens, n_q_heads, D]
-  const int* tiles;              // [n_tiles, 2]: request row, 128-token tile index within its tokens
+  const int* tiles;              // [n_tiles, 2]: request row, index of the 256-token tile within its tokens
   const int* req_q_start;
   const int* req_q_len;
   const int* req_kv_len;
@@ -44,36 +49,43 @@ struct AttnTcParams {
   float scale_log2;
 };
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int D>
 __global__ void __launch_bounds__(kAtThreads, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, AttnTcParams p) {
   constexpr int SUB = D / 64;                          // 64-column sub-tiles per row
-  constexpr uint32_t Q_BYTES = kAtBM * D * 2;
+  constexpr uint32_t Q_BYTES = kAtBM * D * 2;          // one query tile
   constexpr uint32_t KSUB_BYTES = kAtBN * 64 * 2;      // one sub-tile of a key or value tile
   constexpr uint32_t KV_BYTES = kAtBN * D * 2;         // one key tile (or one value tile)
   constexpr uint32_t STAGE_BYTES = 2 * KV_BYTES;
   constexpr uint32_t P_BYTES = kAtBM * kAtBN * 2;
-  constexpr uint32_t TMEM_COLS = 256;                  // S0: 0..63, S1: 64..127, O: 128..128+D-1
+  constexpr uint32_t TMEM_COLS = 512;   // per query tile t: scores at t*128 + {0, 64}; outputs at 256 + t*128
+  constexpr uint32_t DATA_BYTES = kAtQT * Q_BYTES + kAtStages * STAGE_BYTES + kAtQT * 2 * P_BYTES;
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const uint32_t raw = gt_smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char* smem = smem_raw + (base - raw);
   const uint32_t q_smem = base;
-  const uint32_t kv_smem = q_smem + Q_BYTES;
+  const uint32_t kv_smem = q_smem + kAtQT * Q_BYTES;
   const uint32_t p_smem = kv_smem + kAtStages * STAGE_BYTES;
-  unsigned char* ctrl = smem + Q_BYTES + kAtStages * STAGE_BYTES + 2 * P_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + DATA_BYTES);
   uint64_t* q_full = bars;                  // 1
   uint64_t* kv_full = bars + 1;             // kAtStages
   uint64_t* kv_empty = kv_full + kAtStages; // kAtStages
-  uint64_t* s_full = kv_empty + kAtStages;  // 2
-  uint64_t* s_empty = s_full + 2;           // 2
-  uint64_t* p_full = s_empty + 2;           // 2
-  uint64_t* p_empty = p_full + 2;           // 2
-  uint64_t* o_full = p_empty + 2;           // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+  uint64_t* tile_bars = kv_empty + kAtStages;   // per query tile: s_full[2] s_empty[2] p_full[2] p_empty[2] o_full
+  auto s_full = [&](int t, int b) { return gt_smem_u32(tile_bars + t * 9 + b); };
+  auto s_empty = [&](int t, int b) { return gt_smem_u32(tile_bars + t * 9 + 2 + b); };
+  auto p_full = [&](int t, int b) { return gt_smem_u32(tile_bars + t * 9 + 4 + b); };
+  auto p_empty = [&](int t, int b) { return gt_smem_u32(tile_bars + t * 9 + 6 + b); };
+  auto o_full = [&](int t) { return gt_smem_u32(tile_bars + t * 9 + 8); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tile_bars + kAtQT * 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -88,13 +100,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       mbar_init(gt_smem_u32(&kv_full[s]), 1);
       mbar_init(gt_smem_u32(&kv_empty[s]), 1);
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(gt_smem_u32(&s_full[b]), 1);
-      mbar_init(gt_smem_u32(&s_empty[b]), 4);
-      mbar_init(gt_smem_u32(&p_full[b]), 4);
-      mbar_init(gt_smem_u32(&p_empty[b]), 1);
+    for (int t = 0; t < kAtQT; ++t) {
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(s_full(t, b), 1);
+        mbar_init(s_empty(t, b), 4);
+        mbar_init(p_full(t, b), 4);
+        mbar_init(p_empty(t, b), 1);
+      }
+      mbar_init(o_full(t), 1);
     }
-    mbar_init(gt_smem_u32(o_full), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -109,30 +123,43 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const uint32_t tmem_base = *tmem_slot;
   pdl_wait();     // queries, cache pages and the step's tables come from earlier kernels and copies
 
-  // ---- the tile's geometry (identical in every thread) -----------------------------------------
+  // ---- geometry of the block and of its query tiles (identical in every thread) ----------------
   const int r = p.tiles[2 * tile_id];
   const int ti = p.tiles[2 * tile_id + 1];
   bool geometry_ok = (r >= 0 && r < p.n_reqs);
   int q_start = 0, q_len = 0, kv_len = 0;
   if (geometry_ok) { q_start = p.req_q_start[r]; q_len = p.req_q_len[r]; kv_len = p.req_kv_len[r]; }
-  const int row0 = ti * kAtBM;
-  const int rows_here = min(kAtBM, q_len - row0);
-  geometry_ok = geometry_ok && rows_here > 0 && kv_len >= q_len;
+  const int row0 = ti * (kAtQT * kAtBM);
+  const int rows_block = min(kAtQT * kAtBM, q_len - row0);
+  geometry_ok = geometry_ok && rows_block > 0 && kv_len >= q_len;
   if (!geometry_ok && threadIdx.x == 0) set_error(p.err, kErrRequest, tile_id, r, q_len);
-  const int pos0 = kv_len - q_len + row0;
-  const int pos_last = pos0 + rows_here - 1;
-  const int lo_tile = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
-  const int first_kt = lo_tile / kAtBN;
-  const int n_kt = geometry_ok ? (pos_last / kAtBN - first_kt + 1) : 0;
+  const int n_qt = !geometry_ok ? 0 : (rows_block > kAtBM ? 2 : 1);
+  // query tile t: rows [t*128, t*128 + rows_t), positions pos0_t .., key tiles [first_t, last_t]
+  int rows_t[kAtQT], pos0_t[kAtQT], first_t[kAtQT], last_t[kAtQT];
+#pragma unroll
+  for (int t = 0; t < kAtQT; ++t) {
+    rows_t[t] = min(kAtBM, rows_block - t * kAtBM);
+    pos0_t[t] = kv_len - q_len + row0 + t * kAtBM;
+    const int lo = (p.window > 0 && pos0_t[t] - p.window + 1 > 0) ? pos0_t[t] - p.window + 1 : 0;
+    first_t[t] = lo / kAtBN;
+    last_t[t] = (pos0_t[t] + rows_t[t] - 1) / kAtBN;
+  }
+  const int lo_block = (p.window > 0 && pos0_t[0] - p.window + 1 > 0) ? pos0_t[0] - p.window + 1 : 0;
+  const int pos_last = n_qt > 0 ? pos0_t[n_qt - 1] + rows_t[n_qt - 1] - 1 : 0;
+  const int first_kt = first_t[0];
+  const int n_kt = n_qt > 0 ? last_t[n_qt - 1] - first_kt + 1 : 0;
 
   if (warp == 0) {
     // ---- TMA producer ------------------------------------------------------------------------
     if (lane == 0 && n_kt > 0) {
       const int* table = p.block_table + (size_t)p.req_slot[r] * p.max_pages;
-      mbar_expect_tx(gt_smem_u32(q_full), Q_BYTES);
+      mbar_expect_tx(gt_smem_u32(q_full), (uint32_t)n_qt * Q_BYTES);
+      for (int t = 0; t < n_qt; ++t) {
 #pragma unroll
-      for (int c = 0; c < SUB; ++c) {
-        tma_load_3d(q_smem + c * (kAtBM * 128), &map_q, c * 64, head, q_start + row0, gt_smem_u32(q_full));
+        for (int c = 0; c < SUB; ++c) {
+          tma_load_3d(q_smem + t * Q_BYTES + c * (kAtBM * 128), &map_q, c * 64, head,
+                      q_start + row0 + t * kAtBM, gt_smem_u32(q_full));
+        }
       }
       const int kpl = p.page_size < kAtBN ? p.page_size : kAtBN;     // keys per load
       for (int it = 0; it < n_kt; ++it) {
@@ -150,7 +177,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int kt = first_kt + it;
         for (int u = 0; u < kAtBN / kpl; ++u) {
           int key0 = kt * kAtBN + u * kpl;
-          if (key0 + kpl - 1 < lo_tile || key0 > pos_last) key0 = (pos_last / kpl) * kpl;   // nothing visible here
+          if (key0 + kpl - 1 < lo_block || key0 > pos_last) key0 = (pos_last / kpl) * kpl;   // nothing visible here
           const int pidx = key0 / p.page_size;
           int page = (pidx < p.max_pages) ? table[pidx] : -1;
           if (page < 0 || page >= p.num_pages) {
@@ -171,75 +198,94 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (lane == 0 && n_kt > 0) {
       const uint32_t idesc_s = umma_idesc(kAtBN, false);
       const uint32_t idesc_o = umma_idesc(D, true);
-      const uint32_t tmem_o = tmem_base + 128;
       bool ok = mbar_wait(gt_smem_u32(q_full), 0u, abort_flag);
       if (!ok) { set_error(p.err, kErrWait, 11, 0, 0); *abort_flag = 1; }
       for (int j = 0; j <= n_kt && ok; ++j) {
         if (j < n_kt) {
           const int s = j % kAtStages;
+          const int kt = first_kt + j;
           ok = mbar_wait(gt_smem_u32(&kv_full[s]), (uint32_t)(j / kAtStages) & 1u, abort_flag);
-          if (ok && j >= 2) ok = mbar_wait(gt_smem_u32(&s_empty[j & 1]), (uint32_t)((j >> 1) - 1) & 1u, abort_flag);
           if (!ok) { set_error(p.err, kErrWait, 12, j, s); *abort_flag = 1; break; }
-          tc_fence_after();
           const uint32_t k_addr = kv_smem + s * STAGE_BYTES;
+          for (int t = 0; t < n_qt && ok; ++t) {
+            if (kt < first_t[t] || kt > last_t[t]) continue;
+            const int jt = kt - first_t[t], b = jt & 1;
+            if (jt >= 2) ok = mbar_wait(s_empty(t, b), (uint32_t)((jt >> 1) - 1) & 1u, abort_flag);
+            if (!ok) { set_error(p.err, kErrWait, 18, j, t); *abort_flag = 1; break; }
+            tc_fence_after();
 #pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            const uint64_t da = umma_desc_sw128(q_smem + (ks / 4) * (kAtBM * 128)) + (uint64_t)(2 * (ks % 4));
-            const uint64_t db = umma_desc_sw128(k_addr + (ks / 4) * KSUB_BYTES) + (uint64_t)(2 * (ks % 4));
-            umma_bf16(tmem_base + (uint32_t)(j & 1) * kAtBN, da, db, idesc_s, ks > 0 ? 1u : 0u);
+            for (int ks = 0; ks < D / 16; ++ks) {
+              const uint64_t da = umma_desc_sw128(q_smem + t * Q_BYTES + (ks / 4) * (kAtBM * 128)) +
+                                  (uint64_t)(2 * (ks % 4));
+              const uint64_t db = umma_desc_sw128(k_addr + (ks / 4) * KSUB_BYTES) + (uint64_t)(2 * (ks % 4));
+              umma_bf16(tmem_base + (uint32_t)(t * 128 + b * kAtBN), da, db, idesc_s, ks > 0 ? 1u : 0u);
+            }
+            umma_commit(s_full(t, b));
           }
-          umma_commit(gt_smem_u32(&s_full[j & 1]));
+          if (!ok) break;
         }
         if (j >= 1) {
-          const int jj = j - 1;
-          const int s = jj % kAtStages;
-          ok = mbar_wait(gt_smem_u32(&p_full[jj & 1]), (uint32_t)(jj >> 1) & 1u, abort_flag);
-          if (!ok) { set_error(p.err, kErrWait, 13, jj, s); *abort_flag = 1; break; }
-          tc_fence_after();
+          const int s = (j - 1) % kAtStages;
+          const int kt = first_kt + j - 1;
           const uint32_t v_addr = kv_smem + s * STAGE_BYTES + KV_BYTES;
-          const uint32_t p_addr = p_smem + (uint32_t)(jj & 1) * P_BYTES;
+          for (int t = 0; t < n_qt && ok; ++t) {
+            if (kt < first_t[t] || kt > last_t[t]) continue;
+            const int jt = kt - first_t[t], b = jt & 1;
+            ok = mbar_wait(p_full(t, b), (uint32_t)(jt >> 1) & 1u, abort_flag);
+            if (!ok) { set_error(p.err, kErrWait, 13, j, t); *abort_flag = 1; break; }
+            tc_fence_after();
+            const uint32_t p_addr = p_smem + (uint32_t)(t * 2 + b) * P_BYTES;
 #pragma unroll
-          for (int kk = 0; kk < kAtBN / 16; ++kk) {
-            const uint64_t da = umma_desc_sw128(p_addr) + (uint64_t)(2 * kk);
-            const uint64_t db = umma_desc_sw128_mn(v_addr + kk * (16 * 128), KSUB_BYTES);
-            umma_bf16(tmem_o, da, db, idesc_o, (jj > 0 || kk > 0) ? 1u : 0u);
+            for (int kk = 0; kk < kAtBN / 16; ++kk) {
+              const uint64_t da = umma_desc_sw128(p_addr) + (uint64_t)(2 * kk);
+              const uint64_t db = umma_desc_sw128_mn(v_addr + kk * (16 * 128), KSUB_BYTES);
+              umma_bf16(tmem_base + (uint32_t)(256 + t * 128), da, db, idesc_o, (jt > 0 || kk > 0) ? 1u : 0u);
+            }
+            umma_commit(p_empty(t, b));
+            if (kt == last_t[t]) umma_commit(o_full(t));
           }
+          if (!ok) break;
           umma_commit(gt_smem_u32(&kv_empty[s]));
-          umma_commit(gt_smem_u32(&p_empty[jj & 1]));
         }
       }
-      if (ok) umma_commit(gt_smem_u32(o_full));
     }
   } else {
-    // ---- softmax and epilogue: row = tensor-memory lane ---------------------------------------
+    // ---- softmax and epilogue of query tile t: row = tensor-memory lane ---------------------------
+    const int t = (warp - 2) >> 2;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const bool row_valid = row < rows_here;
-    const int pos_r = pos0 + row;
+    const uint32_t tmem_s = tmem_base + lane_addr + (uint32_t)(t * 128);
+    const uint32_t tmem_o = tmem_base + lane_addr + (uint32_t)(256 + t * 128);
+    const bool active = t < n_qt;
+    const int my_rows = active ? rows_t[t] : 0;
+    const bool row_valid = row < my_rows;
+    const int pos_r = pos0_t[t] + row;
     const int lo_r = (p.window > 0 && pos_r - p.window + 1 > 0) ? pos_r - p.window + 1 : 0;
+    const int my_kt = active ? last_t[t] - first_t[t] + 1 : 0;
     float m_ref = -INFINITY, l_sum = 0.0f;
     bool ok = true;
 
-    for (int j = 0; j < n_kt && ok; ++j) {
-      ok = __all_sync(0xffffffffu, mbar_wait(gt_smem_u32(&s_full[j & 1]), (uint32_t)(j >> 1) & 1u, abort_flag));
-      if (!ok) { if (lane == 0) { set_error(p.err, kErrWait, 14, j, 0); *abort_flag = 1; } break; }
+    for (int j = 0; j < my_kt && ok; ++j) {
+      const int b = j & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(s_full(t, b), (uint32_t)(j >> 1) & 1u, abort_flag));
+      if (!ok) { if (lane == 0) { set_error(p.err, kErrWait, 14, j, t); *abort_flag = 1; } break; }
       tc_fence_after();
       uint32_t sraw[kAtBN];
       {
         uint32_t(&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sraw[0]);
         uint32_t(&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sraw[32]);
-        tmem_ld32(tmem_base + lane_addr + (uint32_t)(j & 1) * kAtBN, lo);
-        tmem_ld32(tmem_base + lane_addr + (uint32_t)(j & 1) * kAtBN + 32, hi);
+        tmem_ld32(tmem_s + (uint32_t)(b * kAtBN), lo);
+        tmem_ld32(tmem_s + (uint32_t)(b * kAtBN) + 32, hi);
         tmem_wait_ld();
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(gt_smem_u32(&s_empty[j & 1]));
+      if (lane == 0) mbar_arrive(s_empty(t, b));
 
       // Scores stay unscaled in sv; the softmax scale (> 0) is folded into the exponent below.
       // A tile wholly below this row's diagonal and inside its window needs no mask.
-      const int key_first = (first_kt + j) * kAtBN;
+      const int key_first = (first_t[t] + j) * kAtBN;
       const bool interior = row_valid && key_first + kAtBN - 1 <= pos_r && key_first >= lo_r;
       float mx = -INFINITY;
       float sv[kAtBN];
@@ -265,18 +311,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const float corr = need ? exp2f(m_ref - m_new) : 1.0f;
         if (need) { l_sum *= corr; m_ref = m_new; }
         if (j > 0) {
-          ok = __all_sync(0xffffffffu, mbar_wait(gt_smem_u32(&p_empty[(j - 1) & 1]),
-                                                 (uint32_t)((j - 1) >> 1) & 1u, abort_flag));
-          if (!ok) { if (lane == 0) { set_error(p.err, kErrWait, 15, j, 0); *abort_flag = 1; } break; }
+          ok = __all_sync(0xffffffffu, mbar_wait(p_empty(t, (j - 1) & 1), (uint32_t)((j - 1) >> 1) & 1u,
+                                                 abort_flag));
+          if (!ok) { if (lane == 0) { set_error(p.err, kErrWait, 15, j, t); *abort_flag = 1; } break; }
           tc_fence_after();
 #pragma unroll
           for (int c = 0; c < D / 32; ++c) {
             uint32_t o[32];
-            tmem_ld32(tmem_base + lane_addr + 128 + c * 32, o);
+            tmem_ld32(tmem_o + c * 32, o);
             tmem_wait_ld();
 #pragma unroll
             for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * corr);
-            tmem_st32(tmem_base + lane_addr + 128 + c * 32, o);
+            tmem_st32(tmem_o + c * 32, o);
           }
           tmem_wait_st();
           tc_fence_before();
@@ -286,17 +332,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       float psum = 0.0f;
 #pragma unroll
       for (int c = 0; c < kAtBN; ++c) {
-        sv[c] = exp2f(fmaf(sv[c], p.scale_log2, -m_use));
+        sv[c] = ex2_approx(fmaf(sv[c], p.scale_log2, -m_use));
         psum += sv[c];
       }
       l_sum += psum;
 
-      if (j >= 2) {     // the probability tile is free once the second product of tile j - 2 is done
-        ok = __all_sync(0xffffffffu, mbar_wait(gt_smem_u32(&p_empty[j & 1]), (uint32_t)((j - 2) >> 1) & 1u,
-                                               abort_flag));
-        if (!ok) { if (lane == 0) { set_error(p.err, kErrWait, 16, j, 0); *abort_flag = 1; } break; }
+      if (j >= 2) {     // the probability tile is free once the second product of key tile j - 2 is done
+        ok = __all_sync(0xffffffffu, mbar_wait(p_empty(t, b), (uint32_t)((j - 2) >> 1) & 1u, abort_flag));
+        if (!ok) { if (lane == 0) { set_error(p.err, kErrWait, 16, j, t); *abort_flag = 1; } break; }
       }
-      unsigned char* prow = smem + Q_BYTES + kAtStages * STAGE_BYTES + (size_t)(j & 1) * P_BYTES +
+      unsigned char* prow = smem + kAtQT * Q_BYTES + kAtStages * STAGE_BYTES + (size_t)(t * 2 + b) * P_BYTES +
                             (size_t)(row >> 3) * 1024 + (size_t)(row & 7) * 128;
 #pragma unroll
       for (int ch = 0; ch < kAtBN / 8; ++ch) {
@@ -309,21 +354,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       fence_async_shared();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(gt_smem_u32(&p_full[j & 1]));
+      if (lane == 0) mbar_arrive(p_full(t, b));
     }
 
-    if (ok && n_kt > 0) {
-      ok = __all_sync(0xffffffffu, mbar_wait(gt_smem_u32(o_full), 0u, abort_flag));
-      if (!ok && lane == 0) { set_error(p.err, kErrWait, 17, 0, 0); *abort_flag = 1; }
+    if (ok && my_kt > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait(o_full(t), 0u, abort_flag));
+      if (!ok && lane == 0) { set_error(p.err, kErrWait, 17, 0, t); *abort_flag = 1; }
     }
-    if (ok && n_kt > 0) {
+    if (ok && my_kt > 0) {
       tc_fence_after();
       const float inv = (row_valid && l_sum > 0.0f) ? 1.0f / l_sum : 0.0f;
-      __nv_bfloat16* orow = p.out + ((size_t)(q_start + row0 + row) * p.n_q_heads + head) * D;
+      __nv_bfloat16* orow = p.out + ((size_t)(q_start + row0 + t * kAtBM + row) * p.n_q_heads + head) * D;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t o[32];
-        tmem_ld32(tmem_base + lane_addr + 128 + c * 32, o);
+        tmem_ld32(tmem_o + c * 32, o);
         tmem_wait_ld();
         if (row_valid) {
 #pragma unroll
@@ -353,8 +398,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 template <int D>
 static int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                              const AttnTcParams& p, cudaStream_t stream) {
-  constexpr size_t smem_bytes = (size_t)kAtBM * D * 2 + (size_t)kAtStages * 2 * kAtBN * D * 2 +
-                                2 * (size_t)kAtBM * kAtBN * 2 + 1024 /* alignment */ + 256 /* barriers */;
+  constexpr size_t smem_bytes = (size_t)kAtQT * kAtBM * D * 2 + (size_t)kAtStages * 2 * kAtBN * D * 2 +
+                                (size_t)kAtQT * 2 * kAtBM * kAtBN * 2 + 1024 /* alignment */ + 512 /* barriers */;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -367,6 +412,9 @@ static int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mk, const
 }
 
 }  // namespace tk
+
+// Query tokens that one block of tk_attention_prefill_tc covers (the tile list is cut by this).
+TK_API int tk_attention_prefill_tc_rows(void) { return tk::kAtQT * tk::kAtBM; }
 
 // Whether tk_attention_prefill_tc takes a shape.
 TK_API int tk_attention_prefill_tc_takes(int n_q_heads, int n_kv_heads, int head_dim, int page_size) {

@@ -282,8 +282,8 @@ def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tens
                          tiles: torch.Tensor, req_q_start: torch.Tensor, req_q_len: torch.Tensor,
                          req_kv_len: torch.Tensor, req_slot: torch.Tensor, block_table: torch.Tensor,
                          err: torch.Tensor, *, scale: float, window: int | None) -> None:
-    """Paged flash attention on tcgen05 for the 128-token query tiles listed in ``tiles``
-    (int32 ``[n_tiles, 2]``: request row, tile index).  Loads whole pages: the cache must have been
+    """Paged flash attention on tcgen05 for the query tiles listed in ``tiles`` (int32
+    ``[n_tiles, 2]``: request row, tile index), each of :data:`PREFILL_TC_ROWS` tokens.  Loads whole pages: the cache must have been
     written by :func:`rope_kv` with ``req_q_len`` and ``req_kv_len`` given."""
     _want(q, torch.bfloat16, "q"); _want(out, torch.bfloat16, "out")
     _want(k_cache, torch.bfloat16, "k_cache"); _want(v_cache, torch.bfloat16, "v_cache")
@@ -300,6 +300,9 @@ def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tens
                                              n, tiles.numel() // 2, req_slot.numel(), hq, hkv, d, page_size,
                                              block_table.shape[1], num_pages, int(window or 0),
                                              float(scale), _stream()), "attention_prefill_tc")
+
+
+PREFILL_TC_ROWS = 256     # query tokens per block of the tcgen05 prefill kernel (two tiles of 128)
 
 
 def prefill_tc_kernel_takes(n_q_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> bool:

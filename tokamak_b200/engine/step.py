@@ -74,7 +74,7 @@ class StepBatch:
     decode_items: torch.Tensor      # token indices of requests that bring one token
     prefill_items: torch.Tensor     # token indices of requests that bring more than one
     prefill_tiles: torch.Tensor     # [n_tiles, 2] (request row, 64-token tile) of those requests, longest first
-    prefill_tiles128: torch.Tensor  # the same in tiles of 128 tokens
+    prefill_tiles_tc: torch.Tensor  # the same in the tile size of the tcgen05 kernel (ops.PREFILL_TC_ROWS)
     cache: DeviceCache
     err: torch.Tensor
     host_q_start: list[int] = field(default_factory=list)
@@ -221,10 +221,11 @@ class StepFunction:
                     if q_len[r] > 1 for t in range(-(-q_len[r] // 64))]
         pf_tiles.sort(reverse=True)       # tiles with the most keys to visit start first
         pf_flat = [x for _, r, t in pf_tiles for x in (r, t)]
-        pf_tiles128 = [(kv_len[r] - q_len[r] + 128 * (t + 1), r, t) for r in range(len(entries))
-                       if q_len[r] > 1 for t in range(-(-q_len[r] // 128))]
-        pf_tiles128.sort(reverse=True)
-        pf_flat128 = [x for _, r, t in pf_tiles128 for x in (r, t)]
+        tc_rows = ops.PREFILL_TC_ROWS
+        pf_tiles_tc = [(kv_len[r] - q_len[r] + tc_rows * (t + 1), r, t) for r in range(len(entries))
+                       if q_len[r] > 1 for t in range(-(-q_len[r] // tc_rows))]
+        pf_tiles_tc.sort(reverse=True)
+        pf_flat128 = [x for _, r, t in pf_tiles_tc for x in (r, t)]
         arrays += [i32(tokens), i32(positions), i32(tok_req), i32(q_start), i32(q_len), i32(kv_len),
                    i32(slots), i32(rows), i32(dec_items), i32(pf_items), i32(pf_flat), i32(pf_flat128)]
         views = self.buffers.upload(arrays)
@@ -238,7 +239,7 @@ class StepFunction:
             n_tokens=len(tokens), n_reqs=len(entries), n_want=W,
             token_ids=views[0], positions=views[1], tok_req=views[2], req_q_start=views[3],
             req_q_len=views[4], req_kv_len=views[5], req_slot=views[6], logits_rows=views[7],
-            decode_items=views[8], prefill_items=views[9], prefill_tiles=views[10], prefill_tiles128=views[11],
+            decode_items=views[8], prefill_items=views[9], prefill_tiles=views[10], prefill_tiles_tc=views[11],
             cache=self.cache, err=self.buffers.result[:4],
             host_q_start=q_start, host_q_len=q_len, host_kv_len=kv_len, host_slot=slots,
             max_q_len=max(q_len), max_kv_len=max(kv_len))

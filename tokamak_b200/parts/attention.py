@@ -118,7 +118,7 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
                              step.tok_req, step.req_slot, cache_view.table, step.err, scale=scale,
                              window=window, n_splits=ops.decode_splits(n_dec, hkv, step.max_kv_len))
     if pf_tiled and ops.prefill_tc_kernel_takes(hq, hkv, d, page):
-        ops.attention_prefill_tc(q, out, cache_view.k, cache_view.v, step.prefill_tiles128,
+        ops.attention_prefill_tc(q, out, cache_view.k, cache_view.v, step.prefill_tiles_tc,
                                  step.req_q_start, step.req_q_len, step.req_kv_len, step.req_slot,
                                  cache_view.table, step.err, scale=scale, window=window)
     elif pf_tiled:
