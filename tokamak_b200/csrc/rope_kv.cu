@@ -51,6 +51,7 @@ struct RopeKvParams {
   int n_tokens, n_reqs, n_q_heads, n_kv_heads, head_dim, rotary_dim;
   int row_stride, page_size, max_pages, num_pages;
   int write_kv;             // 0: this layer reads another layer's cache; only q is produced
+  int heads_per_warp;       // consecutive heads of one token that a warp works through
   float eps;
 };
 
@@ -70,22 +71,31 @@ template <> struct Pair<__nv_bfloat16> {
   }
 };
 
-// One warp per (token, head).  head_dim and rotary_dim are multiples of 4, so every lane
-// works on pairs of neighbouring elements with 4- and 8-byte accesses.
+// One thread block per (token, group of heads): each of its four warps works through
+// heads_per_warp consecutive heads of the token, so that with many tokens the lookups of the
+// token's position, request and page are shared by many heads, while with few tokens (decoding)
+// every head still has a warp of its own.  head_dim and rotary_dim are multiples of 4, so every
+// lane works on pairs of neighbouring elements with 4- and 8-byte accesses.
+template <typename T>
+__device__ __forceinline__ void rope_kv_head(const RopeKvParams& p, int t, int h, int lane, int d, int half);
+
 template <typename T>
 __global__ void rope_kv_kernel(RopeKvParams p) {
   pdl_trigger();
   pdl_wait();
-  const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int heads_total = p.n_q_heads + (p.write_kv ? 2 * p.n_kv_heads : 0);
-  const long long item = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
-  if (item >= (long long)p.n_tokens * heads_total) return;
-  const int t = (int)(item / heads_total);
-  const int h = (int)(item - (long long)t * heads_total);
+  const int t = blockIdx.x;
+  const int h_begin = (blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5)) * p.heads_per_warp;
   const int d = p.head_dim;
   const int half = p.rotary_dim >> 1;
+  for (int h = h_begin; h < min(h_begin + p.heads_per_warp, heads_total); ++h) {
+    rope_kv_head<T>(p, t, h, lane, d, half);
+  }
+}
 
+template <typename T>
+__device__ __forceinline__ void rope_kv_head(const RopeKvParams& p, int t, int h, int lane, int d, int half) {
   // kind: 0 = q, 1 = k, 2 = v
   int kind, head;
   if (h < p.n_q_heads) { kind = 0; head = h; }
@@ -142,27 +152,42 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
   }
 
   const float* w = (kind == 0) ? p.q_norm_w : p.k_norm_w;
+  // The rotated pairs (i, i + half) are read once and kept in registers between the sum of
+  // squares and the rotation (half <= 128: two pairs of neighbours per lane).
+  constexpr int kMaxIter = 2;
+  float2 x1[kMaxIter], x2[kMaxIter];
+  float ss = 0.0f;
+#pragma unroll
+  for (int k = 0; k < kMaxIter; ++k) {
+    const int i = 2 * lane + 64 * k;
+    if (i < half) {
+      x1[k] = in2(i); x2[k] = in2(i + half);
+      ss += x1[k].x * x1[k].x + x1[k].y * x1[k].y + x2[k].x * x2[k].x + x2[k].y * x2[k].y;
+    }
+  }
   float rstd = 1.0f;
   if (w != nullptr) {
-    float ss = 0.0f;
-    for (int e = 2 * lane; e < d; e += 64) { const float2 v = in2(e); ss += v.x * v.x + v.y * v.y; }
+    for (int e = 2 * half + 2 * lane; e < d; e += 64) { const float2 v = in2(e); ss += v.x * v.x + v.y * v.y; }
     ss = warp_sum(ss);
     rstd = rsqrtf(ss / (float)d + p.eps);
   }
-  // rotated pairs (i, i + half) for i < half; elements beyond rotary_dim pass through
   const float2* tab = p.rope_table ? p.rope_table + (size_t)t * half : nullptr;
-  for (int i = 2 * lane; i < half; i += 64) {
-    float2 x1 = in2(i), x2 = in2(i + half);
-    x1.x *= rstd; x1.y *= rstd; x2.x *= rstd; x2.y *= rstd;
-    if (w != nullptr) {
-      const float2 w1 = *reinterpret_cast<const float2*>(w + i);
-      const float2 w2 = *reinterpret_cast<const float2*>(w + i + half);
-      x1.x *= w1.x; x1.y *= w1.y; x2.x *= w2.x; x2.y *= w2.y;
+#pragma unroll
+  for (int k = 0; k < kMaxIter; ++k) {
+    const int i = 2 * lane + 64 * k;
+    if (i < half) {
+      float2 a = x1[k], b = x2[k];
+      a.x *= rstd; a.y *= rstd; b.x *= rstd; b.y *= rstd;
+      if (w != nullptr) {
+        const float2 w1 = *reinterpret_cast<const float2*>(w + i);
+        const float2 w2 = *reinterpret_cast<const float2*>(w + i + half);
+        a.x *= w1.x; a.y *= w1.y; b.x *= w2.x; b.y *= w2.y;
+      }
+      float4 cs = make_float4(1.0f, 0.0f, 1.0f, 0.0f);       // (cos, sin) of i and of i + 1
+      if (tab != nullptr) cs = *reinterpret_cast<const float4*>(tab + i);
+      Pair<T>::store(dst + i, a.x * cs.x - b.x * cs.y, a.y * cs.z - b.y * cs.w);
+      Pair<T>::store(dst + i + half, b.x * cs.x + a.x * cs.y, b.y * cs.z + a.y * cs.w);
     }
-    float4 cs = make_float4(1.0f, 0.0f, 1.0f, 0.0f);       // (cos, sin) of i and of i + 1
-    if (tab != nullptr) cs = *reinterpret_cast<const float4*>(tab + i);
-    Pair<T>::store(dst + i, x1.x * cs.x - x2.x * cs.y, x1.y * cs.z - x2.y * cs.w);
-    Pair<T>::store(dst + i + half, x2.x * cs.x + x1.x * cs.y, x2.y * cs.z + x1.y * cs.w);
   }
   for (int e = 2 * half + 2 * lane; e < d; e += 64) {
     float2 x = in2(e);
@@ -195,7 +220,7 @@ TK_API int tk_rope_kv(const void* qkv, const float* qkv_parts, int n_parts, void
   if (n_tokens <= 0) return 0;
   // pairs of neighbouring elements in both halves of the rotation: multiples of 4
   if (head_dim < 4 || head_dim % 4 != 0 || rotary_dim < 0 || rotary_dim > head_dim || rotary_dim % 4 != 0 ||
-      row_stride % 2 != 0) {
+      rotary_dim > 256 || row_stride % 2 != 0) {
     return (int)cudaErrorInvalidValue;
   }
   tk::RopeKvParams p;
@@ -210,11 +235,13 @@ TK_API int tk_rope_kv(const void* qkv, const float* qkv_parts, int n_parts, void
   p.write_kv = write_kv; p.eps = eps;
   const int heads_total = n_q_heads + (write_kv ? 2 * n_kv_heads : 0);
   const int warps_per_block = 4;
-  const long long items = (long long)n_tokens * heads_total;
-  const long long blocks = (items + warps_per_block - 1) / warps_per_block;
+  // many tokens: one block per token, every warp takes a quarter of the heads; few tokens: a warp per head
+  p.heads_per_warp = n_tokens >= 256 ? (heads_total + warps_per_block - 1) / warps_per_block : 1;
+  const int head_groups = (heads_total + warps_per_block * p.heads_per_warp - 1) / (warps_per_block * p.heads_per_warp);
+  if (head_groups > 65535) return (int)cudaErrorInvalidValue;
   cudaError_t e = cudaSuccess;
   TK_DISPATCH_DTYPE(dtype, T,
-                    e = tk::launch(tk::rope_kv_kernel<T>, dim3((unsigned)blocks), dim3(warps_per_block * 32), 0,
-                                   stream, p));
+                    e = tk::launch(tk::rope_kv_kernel<T>, dim3((unsigned)n_tokens, (unsigned)head_groups),
+                                   dim3(warps_per_block * 32), 0, stream, p));
   return (int)e;
 }

@@ -167,14 +167,17 @@ class StepFunction:
         if not entries:
             raise ValueError("a step needs at least one entry")
         seen = set()
-        tokens: list[int] = []
-        positions: list[int] = []
-        tok_req: list[int] = []
+        tok_parts: list[np.ndarray] = []
+        pos_parts: list[np.ndarray] = []
+        req_parts: list[np.ndarray] = []
+        pf_parts: list[np.ndarray] = []
         q_start: list[int] = []
         q_len: list[int] = []
         kv_len: list[int] = []
         slots: list[int] = []
         rows: list[int] = []
+        dec_items: list[int] = []
+        n_tokens = 0
         for r, e in enumerate(entries):
             if e.req_id in seen:
                 raise ValueError(f"request {e.req_id!r} appears twice in one step")
@@ -189,25 +192,30 @@ class StepFunction:
                 raise ValueError(f"request {e.req_id!r} would reach {start + n} tokens, "
                                  f"beyond max_seq_len={self.max_seq_len}")
             self.manager.grow(e.req_id, start + n)
-            q_start.append(len(tokens))
+            q_start.append(n_tokens)
             q_len.append(n)
             kv_len.append(start + n)
             slots.append(self.manager.slot(e.req_id))
             for w in e.want:
                 if not 0 <= w < n:
                     raise ValueError(f"request {e.req_id!r} wants place {w} of {n} tokens")
-                rows.append(len(tokens) + w)
-            tokens.extend(int(t) for t in e.tokens)
-            positions.extend(range(start, start + n))
-            tok_req.extend([r] * n)
-        if len(tokens) > self.max_step_tokens:
-            raise ValueError(f"step of {len(tokens)} tokens exceeds max_step_tokens="
-                             f"{self.max_step_tokens}")
+                rows.append(n_tokens + w)
+            tok_parts.append(np.asarray(e.tokens, dtype=np.int32))
+            pos_parts.append(np.arange(start, start + n, dtype=np.int32))
+            req_parts.append(np.full(n, r, dtype=np.int32))
+            if n == 1:
+                dec_items.append(n_tokens)
+            else:
+                pf_parts.append(np.arange(n_tokens, n_tokens + n, dtype=np.int32))
+            n_tokens += n
+        if n_tokens > self.max_step_tokens:
+            raise ValueError(f"step of {n_tokens} tokens exceeds max_step_tokens={self.max_step_tokens}")
         W = len(rows)
         if sampling is not None and len(sampling) != W:
             raise ValueError(f"{len(sampling)} sampling rows for {W} wanted places")
 
         i32 = lambda x: np.asarray(x, dtype=np.int32)
+        cat = lambda parts: np.concatenate(parts) if parts else np.zeros(0, dtype=np.int32)
         arrays = []
         if sampling is not None:
             seeds = np.asarray([s.seed & 0x7FFFFFFFFFFFFFFF for s in sampling], dtype=np.int64)
@@ -215,19 +223,18 @@ class StepFunction:
                        np.asarray([s.temperature for s in sampling], dtype=np.float32).view(np.int32),
                        np.asarray([s.top_p for s in sampling], dtype=np.float32).view(np.int32),
                        i32([s.top_k for s in sampling]), i32([s.counter for s in sampling])]
-        dec_items = [q_start[r] for r in range(len(entries)) if q_len[r] == 1]
-        pf_items = [q_start[r] + j for r in range(len(entries)) if q_len[r] > 1 for j in range(q_len[r])]
-        pf_tiles = [(kv_len[r] - q_len[r] + 64 * (t + 1), r, t) for r in range(len(entries))
-                    if q_len[r] > 1 for t in range(-(-q_len[r] // 64))]
-        pf_tiles.sort(reverse=True)       # tiles with the most keys to visit start first
-        pf_flat = [x for _, r, t in pf_tiles for x in (r, t)]
-        tc_rows = ops.PREFILL_TC_ROWS
-        pf_tiles_tc = [(kv_len[r] - q_len[r] + tc_rows * (t + 1), r, t) for r in range(len(entries))
-                       if q_len[r] > 1 for t in range(-(-q_len[r] // tc_rows))]
-        pf_tiles_tc.sort(reverse=True)
-        pf_flat128 = [x for _, r, t in pf_tiles_tc for x in (r, t)]
-        arrays += [i32(tokens), i32(positions), i32(tok_req), i32(q_start), i32(q_len), i32(kv_len),
-                   i32(slots), i32(rows), i32(dec_items), i32(pf_items), i32(pf_flat), i32(pf_flat128)]
+
+        def tiles_of(rows_per_tile: int) -> list[int]:
+            # (request row, tile index) of every request that brings more than one token; tiles
+            # with the most keys to visit start first
+            tiles = [(kv_len[r] - q_len[r] + rows_per_tile * (t + 1), r, t) for r in range(len(entries))
+                     if q_len[r] > 1 for t in range(-(-q_len[r] // rows_per_tile))]
+            tiles.sort(reverse=True)
+            return [x for _, r, t in tiles for x in (r, t)]
+
+        arrays += [cat(tok_parts), cat(pos_parts), cat(req_parts), i32(q_start), i32(q_len), i32(kv_len),
+                   i32(slots), i32(rows), i32(dec_items), cat(pf_parts), i32(tiles_of(64)),
+                   i32(tiles_of(ops.PREFILL_TC_ROWS))]
         views = self.buffers.upload(arrays)
         samp = {}
         if sampling is not None:
@@ -236,7 +243,7 @@ class StepFunction:
             views = views[5:]
         self.cache.sync()
         batch = StepBatch(
-            n_tokens=len(tokens), n_reqs=len(entries), n_want=W,
+            n_tokens=n_tokens, n_reqs=len(entries), n_want=W,
             token_ids=views[0], positions=views[1], tok_req=views[2], req_q_start=views[3],
             req_q_len=views[4], req_kv_len=views[5], req_slot=views[6], logits_rows=views[7],
             decode_items=views[8], prefill_items=views[9], prefill_tiles=views[10], prefill_tiles_tc=views[11],
