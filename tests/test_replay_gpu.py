@@ -21,7 +21,8 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 LENGTHS = {"A": [5, 17, 33, 70, 130, 96, 41, 128], "B": [1, 7, 31, 64, 100, 143, 52, 90],
            "W": [3, 40, 77, 150, 64, 110, 25, 95], "C": [2, 19, 64, 129, 80, 47, 111, 96],
-           "D": [4, 33, 65, 140, 90, 128, 31, 70]}
+           "D": [4, 33, 65, 140, 90, 128, 31, 70], "O": [6, 50, 97, 130, 64, 33, 120, 80],
+           "H": [3, 66, 120, 40, 90, 128, 17, 72]}
 DTYPES = ["float32", "bfloat16"]
 
 
@@ -71,13 +72,13 @@ def test_tail_one_by_one(tag, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("tag", ["A", "B", "W", "C", "D"])
+@pytest.mark.parametrize("tag", ["A", "B", "W", "C", "D", "O", "H"])
 def test_portions(tag, dtype):
     replay(tag, dtype, traces.portions, max_tokens=192)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("tag", ["A", "B", "W", "C", "D"])
+@pytest.mark.parametrize("tag", ["A", "B", "W", "C", "D", "O", "H"])
 def test_mixed_with_page_reuse(tag, dtype):
     core = replay(tag, dtype, traces.mixed, max_tokens=384, poison=True, seed=7)
     # the pool is smaller than the sum of all requests, so pages were used again

@@ -57,12 +57,36 @@ TINY_D = {
 TINY_D_INIT = {"seed": 4, "std": 0.04, "norm_std": 0.1}
 TINY_D_PAGE = 32
 
+# Sizes off every fast path: a width and an intermediate size that are no multiple of 8, a head
+# size (80) that only the general attention kernel takes, a group of 5, an odd vocabulary.
+TINY_O = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "num_hidden_layers": 2, "hidden_size": 100, "num_attention_heads": 5, "num_key_value_heads": 1,
+    "head_dim": 80, "intermediate_size": 150, "vocab_size": 333, "rope_theta": 20000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "max_position_embeddings": 320,
+}
+TINY_O_INIT = {"seed": 5, "std": 0.05, "norm_std": 0.1}
+TINY_O_PAGE = 16
+
+# A head size of 256 (the kernels' limit) and more query heads per key/value head (24) than the
+# tensor-core decode kernel packs into one tile.
+TINY_H = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "num_hidden_layers": 1, "hidden_size": 128, "num_attention_heads": 24, "num_key_value_heads": 1,
+    "head_dim": 256, "intermediate_size": 64, "vocab_size": 128, "rope_theta": 10000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 256,
+}
+TINY_H_INIT = {"seed": 6, "std": 0.03, "norm_std": 0.1}
+TINY_H_PAGE = 16
+
 ALL = {
     "A": (TINY_A, TINY_A_INIT, TINY_A_PAGE),
     "B": (TINY_B, TINY_B_INIT, TINY_B_PAGE),
     "W": (TINY_W, TINY_W_INIT, TINY_W_PAGE),
     "C": (TINY_C, TINY_C_INIT, TINY_C_PAGE),
     "D": (TINY_D, TINY_D_INIT, TINY_D_PAGE),
+    "O": (TINY_O, TINY_O_INIT, TINY_O_PAGE),
+    "H": (TINY_H, TINY_H_INIT, TINY_H_PAGE),
 }
 
 # The layer sizes of Qwen3-8B (hidden 4096, 32 query / 8 key-value heads of 128, intermediate 12288)

@@ -46,8 +46,9 @@ class Attention:
         if spec.num_heads % spec.num_kv_heads:
             raise ValueError(f"{spec.num_heads} query heads are not a multiple of "
                              f"{spec.num_kv_heads} key/value heads")
-        if spec.head_dim > 256:
-            raise ValueError(f"head_dim {spec.head_dim} is beyond the attention kernels' limit of 256")
+        if spec.head_dim > 256 or spec.head_dim % 4:
+            raise ValueError(f"head_dim {spec.head_dim} is not taken by the attention kernels: "
+                             f"they need a multiple of 4 up to 256")
         self.spec = spec
         self.rt = rt
         mats = [tensors[prefix + "q_proj.weight"]]
