@@ -8,8 +8,10 @@
 // keeps its own online-softmax state in registers: scores, running maximum,
 // normaliser and output accumulator are float32
 // (src/tokamak/kernels/paged_attention.py:111-123,139-151).  The warps are merged
-// through shared memory, the block writes an unnormalised partial result with its
-// maximum and normaliser to scratch memory, and a second kernel merges the splits.
+// through shared memory and the block writes an unnormalised partial result with its
+// maximum and normaliser to scratch memory; the block that arrives last for a (token,
+// kv head), counted with an atomic in scratch memory, merges the splits and writes
+// the output, and puts the counter back to zero.
 // The reference's kernel has no split and one program per (sequence, kv head)
 // (paged_attention.py:19-20,202).
 //
@@ -23,6 +25,7 @@ namespace tk {
 constexpr int kDecWarps = 4;
 constexpr int kDecTile = 16;      // keys per warp tile
 constexpr int kDecStages = 3;
+constexpr int kDecMaxSplits = 128;
 
 struct DecodeParams {
   const __nv_bfloat16* q;       // [n_tokens, n_q_heads, D]
@@ -30,6 +33,8 @@ struct DecodeParams {
   const __nv_bfloat16* v_cache;
   float* part_o;                // [n_items, n_q_heads, n_splits, D]
   float* part_ml;               // [n_items, n_q_heads, n_splits, 2]
+  int* counters;                // [n_items, n_kv_heads] arrivals of the splits; zero before and after
+  __nv_bfloat16* out;           // [n_tokens, n_q_heads, D]
   const int* items;             // [n_items] token index of each decoded token
   const int* positions;
   const int* tok_req;
@@ -253,38 +258,64 @@ attn_decode_split_kernel(DecodeParams p) {
     p.part_o[pidx * D + col] = acc;
     if (col == 0) { p.part_ml[pidx * 2] = m_all; p.part_ml[pidx * 2 + 1] = l_all; }
   }
-}
 
-// out[tok, head, :] = sum_s o_s * 2^(m_s - m) / sum_s l_s * 2^(m_s - m)
-__global__ void attn_decode_merge_kernel(const float* __restrict__ part_o,
-                                         const float* __restrict__ part_ml,
-                                         const int* __restrict__ items, __nv_bfloat16* __restrict__ out,
-                                         int n_q_heads, int n_splits, int D) {
-  pdl_trigger();
-  pdl_wait();
-  const int item = blockIdx.x, head = blockIdx.y;
-  const size_t base = ((size_t)item * n_q_heads + head) * n_splits;
-  float m_all = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) m_all = fmaxf(m_all, part_ml[(base + s) * 2]);
-  float l_all = 0.0f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float ms = part_ml[(base + s) * 2];
-    if (ms != -INFINITY) l_all += part_ml[(base + s) * 2 + 1] * exp2f(ms - m_all);
+  // ---- the last block of this (token, kv head) merges the splits ------------------------------
+  __shared__ int s_last;
+  __threadfence();                       // this block's partial result is visible before it is counted
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int arrived = atomicAdd(&p.counters[item * p.n_kv_heads + hkv], 1);
+    s_last = (arrived == p.n_splits - 1);
   }
-  const float inv = 1.0f / l_all;
-  __nv_bfloat16* orow = out + ((size_t)items[item] * n_q_heads + head) * D;
-  for (int col = threadIdx.x; col < D; col += blockDim.x) {
-    float acc = 0.0f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float ms = part_ml[(base + s) * 2];
-      if (ms != -INFINITY) acc += part_o[(base + s) * D + col] * exp2f(ms - m_all);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();                       // and the others' partial results before they are read
+  // weights of the splits, row by row: f_s = 2^(m_s - m) / sum_s l_s 2^(m_s - m)
+  float* sf = reinterpret_cast<float*>(smem);            // [group][n_splits]
+  for (int row = warp; row < group; row += kDecWarps) {
+    const size_t base = ((size_t)item * p.n_q_heads + (size_t)hkv * group + row) * p.n_splits;
+    float m_loc[kDecMaxSplits / 32], l_loc[kDecMaxSplits / 32];
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < kDecMaxSplits / 32; ++k) {
+      const int s2 = k * 32 + lane;
+      m_loc[k] = -INFINITY; l_loc[k] = 0.0f;
+      if (s2 < p.n_splits) {
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(&p.part_ml[(base + s2) * 2]));
+        m_loc[k] = ml.x; l_loc[k] = ml.y;
+      }
+      m_all = fmaxf(m_all, m_loc[k]);
     }
-    orow[col] = __float2bfloat16_rn(acc * inv);
+    m_all = warp_max(m_all);
+    float l_all = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kDecMaxSplits / 32; ++k) {
+      m_loc[k] = (m_loc[k] == -INFINITY) ? 0.0f : exp2f(m_loc[k] - m_all);
+      l_all += l_loc[k] * m_loc[k];
+    }
+    l_all = warp_sum(l_all);
+    const float inv = 1.0f / l_all;
+#pragma unroll
+    for (int k = 0; k < kDecMaxSplits / 32; ++k) {
+      const int s2 = k * 32 + lane;
+      if (s2 < p.n_splits) sf[row * p.n_splits + s2] = m_loc[k] * inv;
+    }
   }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < group * D; idx += kDecWarps * 32) {
+    const int row = idx / D, col = idx % D;
+    const size_t base = ((size_t)item * p.n_q_heads + (size_t)hkv * group + row) * p.n_splits;
+    const float* f = sf + row * p.n_splits;
+    float acc = 0.0f;
+#pragma unroll 4
+    for (int s2 = 0; s2 < p.n_splits; ++s2) acc += __ldcg(&p.part_o[(base + s2) * D + col]) * f[s2];
+    p.out[((size_t)tok * p.n_q_heads + (size_t)hkv * group + row) * D + col] = __float2bfloat16_rn(acc);
+  }
+  if (threadIdx.x == 0) p.counters[item * p.n_kv_heads + hkv] = 0;
 }
 
 template <int D>
-static int launch_decode(const DecodeParams& p, void* out, cudaStream_t stream) {
+static int launch_decode(const DecodeParams& p, cudaStream_t stream) {
   constexpr int smem_bytes = kDecWarps * kDecStages * 2 * kDecTile * D * 2;
   static_assert(kDecWarps * 16 * D * 4 + kDecWarps * 16 * 2 * 4 <= smem_bytes, "merge area too small");
   static bool configured = false;
@@ -295,23 +326,21 @@ static int launch_decode(const DecodeParams& p, void* out, cudaStream_t stream) 
     configured = true;
   }
   dim3 grid(p.n_splits, p.n_kv_heads, p.n_items);
-  cudaError_t e = launch(attn_decode_split_kernel<D>, grid, dim3(kDecWarps * 32), smem_bytes, stream, p);
-  if (e != cudaSuccess) return (int)e;
-  dim3 mgrid(p.n_items, p.n_q_heads);
-  return (int)launch(attn_decode_merge_kernel, mgrid, dim3(D >= 128 ? 128 : 64), 0, stream, (const float*)p.part_o,
-                     (const float*)p.part_ml, p.items, (__nv_bfloat16*)out, p.n_q_heads, p.n_splits, D);
+  return (int)launch(attn_decode_split_kernel<D>, grid, dim3(kDecWarps * 32), smem_bytes, stream, p);
 }
 
 }  // namespace tk
 
 // Floats of scratch that tk_attention_decode needs: partial outputs, then (max, sum) pairs.
+// Beside them it needs n_items * n_kv_heads int counters that are zero before the call (the
+// kernel leaves them at zero).
 TK_API long long tk_attention_decode_scratch_floats(int n_items, int n_q_heads, int head_dim,
                                                     int n_splits) {
   return (long long)n_items * n_q_heads * n_splits * (head_dim + 2);
 }
 
 TK_API int tk_attention_decode(const void* q, void* out, const void* k_cache, const void* v_cache,
-                               float* scratch, const int* items, const int* positions,
+                               float* scratch, int* counters, const int* items, const int* positions,
                                const int* tok_req, const int* req_slot, const int* block_table,
                                int* err, int n_items, int n_reqs, int n_q_heads, int n_kv_heads,
                                int head_dim, int page_size, int max_pages, int num_pages, int window,
@@ -319,7 +348,7 @@ TK_API int tk_attention_decode(const void* q, void* out, const void* k_cache, co
   if (n_items <= 0) return 0;
   const int group = n_kv_heads > 0 ? n_q_heads / n_kv_heads : 0;
   if (n_kv_heads < 1 || n_q_heads % n_kv_heads != 0 || group > 16 || page_size % 16 != 0 ||
-      n_splits < 1 || n_splits > 65535 || n_items > 65535 || n_kv_heads > 65535 ||
+      n_splits < 1 || n_splits > tk::kDecMaxSplits || n_items > 65535 || n_kv_heads > 65535 ||
       (head_dim != 64 && head_dim != 128)) {
     return (int)cudaErrorInvalidValue;
   }
@@ -329,12 +358,13 @@ TK_API int tk_attention_decode(const void* q, void* out, const void* k_cache, co
   p.v_cache = (const __nv_bfloat16*)v_cache;
   p.part_o = scratch;
   p.part_ml = scratch + (size_t)n_items * n_q_heads * n_splits * head_dim;
+  p.counters = counters; p.out = (__nv_bfloat16*)out;
   p.items = items; p.positions = positions; p.tok_req = tok_req; p.req_slot = req_slot;
   p.block_table = block_table; p.err = err;
   p.n_items = n_items; p.n_reqs = n_reqs; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
   p.page_size = page_size; p.max_pages = max_pages; p.num_pages = num_pages; p.window = window;
   p.n_splits = n_splits;
   p.scale_log2 = scale * 1.4426950408889634f;
-  if (head_dim == 128) return tk::launch_decode<128>(p, out, stream);
-  return tk::launch_decode<64>(p, out, stream);
+  if (head_dim == 128) return tk::launch_decode<128>(p, stream);
+  return tk::launch_decode<64>(p, stream);
 }

@@ -1,17 +1,18 @@
 // Split-K paged decode attention for callers that cannot allocate device memory.
 //
 // No counterpart in WeichunK/tokamak.  See tokamak_b200_noalloc.h for who needs it
-// and for the contract.  The scratch of the decode kernels (unnormalised partial
-// outputs and their (maximum, normaliser) pairs, one set per key split) lives in
-// the file-scope device array below; the kernels themselves are the ones behind
+// and for the contract.  The scratch of the decode kernel (unnormalised partial
+// outputs and their (maximum, normaliser) pairs, one set per key split, and the
+// counters by which the last split to arrive is found) lives in the file-scope
+// device arrays below; the kernel itself is the one behind
 // tk_attention_decode, reached through that exported function with the array's
 // device address as its scratch argument.
 #include "common.cuh"
 #include "tokamak_b200_noalloc.h"
 
-// The existing entry point (attention_decode.cu); it launches two kernels and allocates nothing.
+// The existing entry point (attention_decode.cu); it launches one kernel and allocates nothing.
 extern "C" int tk_attention_decode(const void* q, void* out, const void* k_cache, const void* v_cache,
-                                   float* scratch, const int* items, const int* positions,
+                                   float* scratch, int* counters, const int* items, const int* positions,
                                    const int* tok_req, const int* req_slot, const int* block_table,
                                    int* err, int n_items, int n_reqs, int n_q_heads, int n_kv_heads,
                                    int head_dim, int page_size, int max_pages, int num_pages, int window,
@@ -20,16 +21,20 @@ extern "C" int tk_attention_decode(const void* q, void* out, const void* k_cache
 namespace {
 
 constexpr long long kScratchFloats = 1ll << 20;   // 4 MiB on every GPU that loads the library
+constexpr int kCounters = 4096;                   // arrival counters, one per (token, kv head)
 constexpr int kMaxDevices = 64;
 
 // In host code this name is only a handle for the runtime, not a device address:
 // the address comes from cudaGetSymbolAddress, per device.
 static __device__ __align__(256) float g_decode_scratch[kScratchFloats];
+// Zero when the library is loaded; every call leaves the counters it used at zero again.
+static __device__ __align__(256) int g_decode_counters[kCounters];
 
 float* g_scratch_ptr[kMaxDevices] = {nullptr};
+int* g_counter_ptr[kMaxDevices] = {nullptr};
 
-// Device address of the array on the current device, looked up once per device.
-int scratch_for_current_device(float** out) {
+// Device addresses of the arrays on the current device, looked up once per device.
+int scratch_for_current_device(float** out, int** counters) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
@@ -38,9 +43,14 @@ int scratch_for_current_device(float** out) {
     float* ptr = nullptr;
     e = cudaGetSymbolAddress((void**)&ptr, g_decode_scratch);
     if (e != cudaSuccess) return (int)e;
+    int* cptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&cptr, g_decode_counters);
+    if (e != cudaSuccess) return (int)e;
+    g_counter_ptr[dev] = cptr;
     g_scratch_ptr[dev] = ptr;
   }
   *out = g_scratch_ptr[dev];
+  *counters = g_counter_ptr[dev];
   return 0;
 }
 
@@ -69,11 +79,12 @@ TK_API int tk_attention_decode_noalloc(const void* q, void* out, const void* k_c
   if (n_items <= 0) return 0;
   if (n_q_heads < 1 || head_dim < 1 || n_splits < 1) return (int)cudaErrorInvalidValue;
   const long long need = (long long)n_items * n_q_heads * n_splits * (head_dim + 2);
-  if (need > kScratchFloats) return TK_NOALLOC_TOO_LARGE;
+  if (need > kScratchFloats || (long long)n_items * n_kv_heads > kCounters) return TK_NOALLOC_TOO_LARGE;
   float* scratch = nullptr;
-  const int rc = scratch_for_current_device(&scratch);
+  int* counters = nullptr;
+  const int rc = scratch_for_current_device(&scratch, &counters);
   if (rc != 0) return rc;
-  return tk_attention_decode(q, out, k_cache, v_cache, scratch, items, positions, tok_req, req_slot,
+  return tk_attention_decode(q, out, k_cache, v_cache, scratch, counters, items, positions, tok_req, req_slot,
                              block_table, err, n_items, n_reqs, n_q_heads, n_kv_heads, head_dim,
                              page_size, max_pages, num_pages, window, n_splits, scale, stream);
 }

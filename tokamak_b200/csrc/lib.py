@@ -26,7 +26,7 @@ _SIGNATURES: dict[str, list] = {
     "tk_attention_plain": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                            c_float, c_int, _P],
-    "tk_attention_decode": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
+    "tk_attention_decode": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                             c_float, _P],
     "tk_attention_prefill": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,

@@ -35,16 +35,20 @@ const char* tk_noalloc_error_string(int code);
  * caller passes no scratch: partial results go to a static array in device memory.
  *
  *  - Calls no cudaMalloc, cudaFree or other allocating routine.
- *  - Needs n_items * n_q_heads * n_splits * (head_dim + 2) floats of scratch; a call that
- *    needs more than the capacity returns TK_NOALLOC_TOO_LARGE and launches nothing
- *    (use fewer splits, or fewer items per call).
+ *  - Needs n_items * n_q_heads * n_splits * (head_dim + 2) floats of scratch and
+ *    n_items * n_kv_heads arrival counters (the library holds 4096); a call that needs more
+ *    than the capacity returns TK_NOALLOC_TOO_LARGE and launches nothing (use fewer splits,
+ *    or fewer items per call).
  *  - The first call on a device looks up the array's device address (once per device,
  *    with that device current).  Make that first call outside any stream capture.
- *  - All calls share the one array, and it keeps what the last call left in it.  Nothing
- *    in it has to start at zero: the first kernel writes every partial result (an empty
- *    split writes a zero sum) before the merge kernel reads any.  Two calls whose
- *    kernels overlap on the GPU (different streams, no ordering between them) race on
- *    the array; order them on one stream or with events.
+ *  - All calls share the arrays, and they keep what the last call left in them.  The
+ *    partial results need no clearing: every split writes its result (an empty split
+ *    writes a zero sum) before the block that merges reads any.  The arrival counters must
+ *    be zero at the start of a call: they are zero when the library is loaded, and the
+ *    merging block puts each counter back to zero, so a call that ran to its end leaves
+ *    them ready for the next.  Two calls whose kernels overlap on the GPU (different
+ *    streams, no ordering between them) race on the arrays; order them on one stream or
+ *    with events.
  */
 int tk_attention_decode_noalloc(const void* q, void* out, const void* k_cache, const void* v_cache,
                                 const int* items, const int* positions, const int* tok_req,
