@@ -153,3 +153,25 @@ def test_window_policy_matches_a_windowed_config():
     assert outs[0].output_token_ids == plain.greedy_generate(cfg, w, prompts[0], 6)
     with pytest.raises(ValueError, match="attention_policy"):
         llm_for("A", "float32", attention_policy="streaming:8+2")
+
+
+def test_many_requests_small_pool_equal_single_request_runs():
+    """Forty requests of mixed lengths and sampling settings through a pool that forces waiting
+    and preemption: every request's tokens equal those of the same request run alone."""
+    from tokamak_b200 import SamplingParams
+    lengths = [3 + (i * 37) % 90 for i in range(40)]
+    prompts = prompts_for("C", lengths)
+    params = [SamplingParams(temperature=0.0 if i % 3 else 0.9, top_k=0 if i % 2 else 12, seed=100 + i,
+                             max_new_tokens=4 + i % 9) for i in range(40)]
+    shared = llm_for("C", "float32", max_seq_len=128, kv_pool_tokens=512, max_batch_size=6,
+                     max_num_batched_tokens=96, prefill_chunk=40)
+    outs = shared.generate(prompt_token_ids=prompts, sampling_params=params)
+    stats = shared.last_stats
+    assert stats["mixed_steps"] > 0 and stats["decode_tokens"] > 0
+    shared.cache_manager.check_invariants()
+    assert all(g.num_free == g.num_pages for g in shared.cache_manager.kv_groups)
+    alone = llm_for("C", "float32", max_seq_len=128, kv_pool_tokens=128, max_batch_size=1)
+    for i in range(0, 40, 3):
+        want = alone.generate(prompt_token_ids=[prompts[i]], sampling_params=params[i])[0]
+        assert outs[i].output_token_ids == want.output_token_ids, i
+        assert len(outs[i].output_token_ids) == params[i].max_new_tokens
