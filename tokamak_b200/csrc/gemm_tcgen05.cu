@@ -10,9 +10,12 @@
 // Two uses:
 //  * decode ("swapped"): R = weight [N_out, K], C = activations [tokens <= 64, K].  The
 //    weights are the 128-row operand, so every byte of them is streamed exactly once
-//    through a deep TMA pipeline; the K range is split over blocks to fill the GPU, and
-//    each split stores a float32 partial [split, token, N_out] that the consuming kernel
-//    sums (norm, rotation, activation): no atomics, the sum order is fixed.
+//    through a deep TMA pipeline; the K range is split over blocks to fill the GPU.  The
+//    blocks of one output tile form a thread-block cluster: each stages its float32
+//    partial accumulator in its own shared memory, and every block adds up its share of
+//    the token columns over distributed shared memory, always in the same order, and
+//    stores the float32 result [1, token, N_out] (no atomics).  Without the cluster every split
+//    stores its partial [split, token, N_out] and the consuming kernel adds them up.
 //  * prefill: R = activations [tokens, K], C = weight [N_out, K], BN = 128 or 256,
 //    output rounded to bfloat16 (or kept float32) directly.
 //
@@ -37,6 +40,7 @@ struct GemmTcParams {
   int n_stages;
   int n_splits;
   int swapped;              // 1: store D transposed as float32 partials
+  int cluster_reduce;       // 1 (swapped only): the splits of a tile are one cluster and store their sum
   int out_f32;              // non-swapped: 1 = float32 output, 0 = bfloat16
   long long ld_out;         // non-swapped: elements between output rows
 };
@@ -178,6 +182,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
 #pragma unroll
         for (int e = 0; e < 16; ++e) v[e] = 0u;
       }
+      if (p.cluster_reduce && p.n_splits > 1) {
+        // stage[column][row of the tile]: consecutive lanes write consecutive words
+        float* stage = reinterpret_cast<float*>(smem);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) stage[(c0 + e) * kGtBM + quarter * 32 + lane] = __uint_as_float(v[e]);
+        continue;
+      }
       if (row >= p.rows_total) continue;
       if (p.swapped) {
         float* part = reinterpret_cast<float*>(p.out) + (size_t)split * p.cols_total * p.rows_total;
@@ -219,6 +230,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
 
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
+  if (p.cluster_reduce && p.n_splits > 1) {
+    cluster_sync_all();                    // every block of the tile has staged its partial
+    if (warp >= 2) {
+      // every block of the cluster adds up its share of the columns (tokens): column c belongs
+      // to rank c mod n_splits; the order of the sum over the ranks is always the same
+      const uint32_t my_rank = cluster_ctarank();
+      const int quarter = warp & 3;
+      const int row = tile_r * kGtBM + quarter * 32 + lane;
+      const uint32_t stage = base;         // the staging area starts where the ring of stages did
+      float* out = reinterpret_cast<float*>(p.out);
+      if (row < p.rows_total) {
+        for (int c = (int)my_rank; c < p.bn; c += p.n_splits) {
+          const int col = tile_c * p.bn + c;
+          if (col >= p.cols_total) break;
+          float sum = 0.0f;
+          for (int rk = 0; rk < p.n_splits; ++rk) {
+            sum += ld_cluster_f32(stage + (uint32_t)((c * kGtBM + quarter * 32 + lane) * 4), (uint32_t)rk);
+          }
+          out[(size_t)col * p.rows_total + row] = sum;
+        }
+      }
+    }
+    cluster_sync_all();                    // nobody's shared memory is read any more
+  }
   if (warp == 2) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(tmem_cols)
                  : "memory");
@@ -249,10 +284,10 @@ static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long
 // swapped = 0: out is [rows, cols] with row stride ld_out, float32 if out_f32 else bfloat16; n_splits must be 1.
 TK_API int tk_gemm_bf16_tcgen05(const void* r, const void* c, void* out, int* err, int rows, int cols, int k,
                                 long long ld_r, long long ld_c, long long ld_out, int bn, int n_splits,
-                                int swapped, int out_f32, int max_stages, cudaStream_t stream) {
+                                int swapped, int out_f32, int max_stages, int cluster_reduce, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;
   if (k <= 0 || k % 8 != 0 || (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) || n_splits < 1 ||
-      (!swapped && n_splits != 1)) {
+      (!swapped && n_splits != 1) || (cluster_reduce && (!swapped || n_splits > 8))) {
     return (int)cudaErrorInvalidValue;
   }
   CUtensorMap map_r, map_c;
@@ -281,7 +316,13 @@ TK_API int tk_gemm_bf16_tcgen05(const void* r, const void* c, void* out, int* er
   }
   tk::GemmTcParams p;
   p.out = out; p.err = err; p.rows_total = rows; p.cols_total = cols; p.k_total = k; p.bn = bn;
-  p.n_stages = n_stages; p.n_splits = n_splits; p.swapped = swapped; p.out_f32 = out_f32; p.ld_out = ld_out;
+  p.n_stages = n_stages; p.n_splits = n_splits; p.swapped = swapped; p.out_f32 = out_f32; p.ld_out = ld_out; p.cluster_reduce = cluster_reduce;
   dim3 grid((rows + tk::kGtBM - 1) / tk::kGtBM, (cols + bn - 1) / bn, n_splits);
+  if (cluster_reduce && n_splits > 1) {
+    // the staging area [bn][128] floats must fit into the ring of stages
+    if ((size_t)bn * tk::kGtBM * 4 > (size_t)n_stages * stage_bytes) return (int)cudaErrorInvalidValue;
+    return (int)tk::launch_cluster_z(tk::gemm_tcgen05_kernel, grid, dim3(tk::kGtThreads), smem_bytes, stream,
+                                     (unsigned)n_splits, map_r, map_c, p);
+  }
   return (int)tk::launch(tk::gemm_tcgen05_kernel, grid, dim3(tk::kGtThreads), smem_bytes, stream, map_r, map_c, p);
 }

@@ -358,10 +358,12 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
 
 
 def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_splits: int,
-                    out: torch.Tensor | None = None, max_stages: int = 0) -> torch.Tensor:
-    """Float32 partials ``[n_splits, tokens, N_out]`` of ``x @ weight^T`` on tcgen05, the weight
-    being the 128-row operand (for few tokens: every weight byte is streamed once by TMA).
-    The caller sums the partials."""
+                    out: torch.Tensor | None = None, max_stages: int = 0,
+                    cluster_reduce: bool = False) -> torch.Tensor:
+    """``x @ weight^T`` on tcgen05, the weight being the 128-row operand (for few tokens: every
+    weight byte is streamed once by TMA), as float32 partial sums ``[parts, tokens, N_out]`` for
+    the caller to add up: ``parts = n_splits``, or 1 with ``cluster_reduce`` (at most 8 splits),
+    where the splits of a tile form a thread-block cluster that adds them up itself."""
     _want(weight, torch.bfloat16, "weight"); _want(x, torch.bfloat16, "x")
     n_out, k = weight.shape
     tokens, kx = x.shape
@@ -372,10 +374,14 @@ def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_
     bn = 16
     while bn < tokens:
         bn *= 2
+    if cluster_reduce and n_splits > 8:
+        raise KernelError("a cluster adds up at most 8 splits")
     if out is None:
-        out = torch.empty((n_splits, tokens, n_out), dtype=torch.float32, device=x.device)
+        out = torch.empty((1 if cluster_reduce else n_splits, tokens, n_out), dtype=torch.float32,
+                          device=x.device)
     _check(library().tk_gemm_bf16_tcgen05(weight.data_ptr(), x.data_ptr(), out.data_ptr(), err.data_ptr(),
-                                          n_out, tokens, k, k, k, 0, bn, n_splits, 1, 1, max_stages, _stream()),
+                                          n_out, tokens, k, k, k, 0, bn, n_splits, 1, 1, max_stages,
+                                          1 if cluster_reduce else 0, _stream()),
            "gemm_tc_swapped")
     return out
 
@@ -386,7 +392,7 @@ def swapped_gemm_plan(n_out: int, k: int) -> tuple[int, int]:
     start-up hides behind another's streaming."""
     tiles = -(-n_out // 128)
     k_blocks = -(-k // 64)
-    splits = max(1, min(round(384 / tiles), max(1, k_blocks // 4)))
+    splits = max(1, min(round(384 / tiles), max(1, k_blocks // 4), 8))    # a cluster holds 8 blocks
     stages = 4 if splits == 1 else 3
     return splits, stages
 
@@ -402,7 +408,7 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, err: torch.Tensor, out_dtype:
     out = torch.empty((tokens, n_out), dtype=out_dtype, device=x.device)
     _check(library().tk_gemm_bf16_tcgen05(x.data_ptr(), weight.data_ptr(), out.data_ptr(), err.data_ptr(),
                                           tokens, n_out, k, k, k, n_out, bn, 1, 0,
-                                          1 if out_dtype == torch.float32 else 0, max_stages, _stream()), "gemm_tc")
+                                          1 if out_dtype == torch.float32 else 0, max_stages, 0, _stream()), "gemm_tc")
     return out
 
 

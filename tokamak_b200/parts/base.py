@@ -111,9 +111,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     float32: the engine's own FFMA kernel (no TF32, no tensor cores).
 
     bfloat16, few tokens (decoding): the tcgen05 kernel with the weight as the 128-row
-    operand, streamed once by TMA and split over K.  The result is then a 3-D float32
-    tensor of partial sums ``[splits, tokens, out]`` which the consuming kernel (norm,
-    rotation, activation) adds up; ``err`` is the error word its bounded waits report to.
+    operand, streamed once by TMA and split over K, the splits of a tile added up inside a
+    thread-block cluster.  The result is a 3-D float32 tensor ``[parts, tokens, out]`` (here
+    one part) which the consuming kernel (norm, rotation, activation) adds up; ``err`` is the
+    error word its bounded waits report to.
 
     bfloat16, many tokens: the library product, as the reference uses the library for its
     projections (src/tokamak/model/transformer.py:38-41); ``out_dtype=float32`` keeps the
@@ -125,7 +126,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
         return ops.gemm_f32(x, weight)
     if err is not None and x.shape[0] <= SWAPPED_GEMM_MAX_TOKENS and weight.shape[1] % 8 == 0:
         splits, stages = ops.swapped_gemm_plan(weight.shape[0], weight.shape[1])
-        return ops.gemm_tc_swapped(weight, x, err, splits, max_stages=stages)
+        return ops.gemm_tc_swapped(weight, x, err, splits, max_stages=stages, cluster_reduce=True)
     if out_dtype is not None and out_dtype != x.dtype:
         return torch.mm(x, weight.t(), out_dtype=out_dtype)
     return torch.mm(x, weight.t())
