@@ -279,12 +279,13 @@ def kernel_case(name: str, batch: int, ctx: int, iters: int, peaks: dict) -> dic
         w = torch.randn((2 * cfg["intermediate_size"], cfg["hidden_size"]), device=dev, generator=gen).bfloat16()
         ws = [w.clone() for _ in range(4)]
         x = torch.randn((batch, cfg["hidden_size"]), device=dev, generator=gen).bfloat16()
-        splits, stages = ops.swapped_gemm_plan(w.shape[0], w.shape[1])
-        out = torch.empty((splits, batch, w.shape[0]), dtype=torch.float32, device=dev)
+        splits, stages, cluster = ops.swapped_gemm_plan(w.shape[0], w.shape[1])
+        out = torch.empty((splits // cluster if cluster > 1 else splits, batch, w.shape[0]),
+                          dtype=torch.float32, device=dev)
         turn = [0]
         def run():
             turn[0] = (turn[0] + 1) % len(ws)
-            ops.gemm_tc_swapped(ws[turn[0]], x, err, splits, out=out, max_stages=stages)
+            ops.gemm_tc_swapped(ws[turn[0]], x, err, splits, out=out, max_stages=stages, cluster=cluster)
         nbytes = w.numel() * 2
     elif name == "gemm_decode":
         # the library product the decode step uses, for comparison: gate_up of one layer

@@ -552,10 +552,10 @@ def test_rope_kv_clears_the_rest_of_a_page_begun_in_this_step():
 
 # ----------------------------------------------------------------------------- tcgen05 matrix product
 
-@pytest.mark.parametrize("cluster", [False, True])
-@pytest.mark.parametrize("tokens,n_out,k,splits", [(8, 300, 512, 1), (8, 256, 4096, 4), (1, 128, 64, 1),
-                                                    (64, 1000, 1536, 3), (16, 384, 96, 2), (33, 130, 200, 5),
-                                                    (8, 4096, 4096, 8), (64, 640, 12288, 8)])
+@pytest.mark.parametrize("tokens,n_out,k,splits,cluster", [
+    (8, 300, 512, 1, 0), (8, 256, 4096, 4, 0), (1, 128, 64, 1, 0), (64, 1000, 1536, 3, 0), (16, 384, 96, 2, 2),
+    (33, 130, 200, 5, 5), (8, 4096, 4096, 8, 8), (64, 640, 12288, 8, 4), (8, 512, 12288, 16, 8),
+    (16, 300, 4096, 6, 3)])
 def test_gemm_tcgen05_swapped_partials(tokens, n_out, k, splits, cluster):
     """The weight as the 128-row operand: partials over K splits sum to x @ W^T, whether the
     caller adds them up or the thread-block cluster does."""
@@ -564,10 +564,10 @@ def test_gemm_tcgen05_swapped_partials(tokens, n_out, k, splits, cluster):
     x = torch.randn(tokens, k, generator=gen).bfloat16()
     w = torch.randn(n_out, k, generator=gen).bfloat16()
     err = err_word()
-    parts = ops.gemm_tc_swapped(w.to(DEV), x.to(DEV), err, splits, cluster_reduce=cluster)
+    parts = ops.gemm_tc_swapped(w.to(DEV), x.to(DEV), err, splits, cluster=cluster)
     torch.cuda.synchronize()
     assert err.tolist()[0] == 0, err.tolist()
-    assert parts.shape[0] == (1 if cluster else splits)
+    assert parts.shape[0] == (splits // cluster if cluster > 1 else splits)
     want = x.double() @ w.double().T
     got = parts.double().sum(0).cpu()
     torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-3 * (k ** 0.5) / 8)

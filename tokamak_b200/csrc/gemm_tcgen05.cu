@@ -40,7 +40,8 @@ struct GemmTcParams {
   int n_stages;
   int n_splits;
   int swapped;              // 1: store D transposed as float32 partials
-  int cluster_reduce;       // 1 (swapped only): the splits of a tile are one cluster and store their sum
+  int cluster_reduce;       // swapped only: 0, or the cluster size: that many consecutive splits of a tile
+                            // form a cluster and store their sum as one part (n_splits / cluster parts)
   int out_f32;              // non-swapped: 1 = float32 output, 0 = bfloat16
   long long ld_out;         // non-swapped: elements between output rows
 };
@@ -182,7 +183,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
 #pragma unroll
         for (int e = 0; e < 16; ++e) v[e] = 0u;
       }
-      if (p.cluster_reduce && p.n_splits > 1) {
+      if (p.cluster_reduce > 1) {
         // stage[column][row of the tile]: consecutive lanes write consecutive words
         float* stage = reinterpret_cast<float*>(smem);
 #pragma unroll
@@ -230,22 +231,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
 
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
-  if (p.cluster_reduce && p.n_splits > 1) {
-    cluster_sync_all();                    // every block of the tile has staged its partial
+  if (p.cluster_reduce > 1) {
+    cluster_sync_all();                    // every block of the cluster has staged its partial
     if (warp >= 2) {
       // every block of the cluster adds up its share of the columns (tokens): column c belongs
-      // to rank c mod n_splits; the order of the sum over the ranks is always the same
+      // to rank c mod cluster size; the order of the sum over the ranks is always the same
       const uint32_t my_rank = cluster_ctarank();
       const int quarter = warp & 3;
       const int row = tile_r * kGtBM + quarter * 32 + lane;
       const uint32_t stage = base;         // the staging area starts where the ring of stages did
-      float* out = reinterpret_cast<float*>(p.out);
+      float* out = reinterpret_cast<float*>(p.out) +
+                   (size_t)(split / p.cluster_reduce) * p.cols_total * p.rows_total;
       if (row < p.rows_total) {
-        for (int c = (int)my_rank; c < p.bn; c += p.n_splits) {
+        for (int c = (int)my_rank; c < p.bn; c += p.cluster_reduce) {
           const int col = tile_c * p.bn + c;
           if (col >= p.cols_total) break;
           float sum = 0.0f;
-          for (int rk = 0; rk < p.n_splits; ++rk) {
+          for (int rk = 0; rk < p.cluster_reduce; ++rk) {
             sum += ld_cluster_f32(stage + (uint32_t)((c * kGtBM + quarter * 32 + lane) * 4), (uint32_t)rk);
           }
           out[(size_t)col * p.rows_total + row] = sum;
@@ -280,14 +282,17 @@ static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long
 }  // namespace tk
 
 // D = R * C^T on tcgen05.  r: [rows, k] bf16 (row stride ld_r), c: [cols, k] bf16 (row stride ld_c).
-// swapped = 1: out is float32 [n_splits, cols, rows] (partials, to be summed by the consumer).
+// swapped = 1: out is float32 [parts, cols, rows] (partials, to be summed by the consumer);
+// parts = n_splits, or n_splits / cluster_reduce when cluster_reduce > 1 (2..8, a divisor of
+// n_splits): that many consecutive splits form a thread-block cluster and store their sum.
 // swapped = 0: out is [rows, cols] with row stride ld_out, float32 if out_f32 else bfloat16; n_splits must be 1.
 TK_API int tk_gemm_bf16_tcgen05(const void* r, const void* c, void* out, int* err, int rows, int cols, int k,
                                 long long ld_r, long long ld_c, long long ld_out, int bn, int n_splits,
                                 int swapped, int out_f32, int max_stages, int cluster_reduce, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;
   if (k <= 0 || k % 8 != 0 || (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) || n_splits < 1 ||
-      (!swapped && n_splits != 1) || (cluster_reduce && (!swapped || n_splits > 8))) {
+      (!swapped && n_splits != 1) ||
+      (cluster_reduce > 1 && (!swapped || cluster_reduce > 8 || n_splits % cluster_reduce != 0)) || cluster_reduce < 0) {
     return (int)cudaErrorInvalidValue;
   }
   CUtensorMap map_r, map_c;
@@ -318,11 +323,11 @@ TK_API int tk_gemm_bf16_tcgen05(const void* r, const void* c, void* out, int* er
   p.out = out; p.err = err; p.rows_total = rows; p.cols_total = cols; p.k_total = k; p.bn = bn;
   p.n_stages = n_stages; p.n_splits = n_splits; p.swapped = swapped; p.out_f32 = out_f32; p.ld_out = ld_out; p.cluster_reduce = cluster_reduce;
   dim3 grid((rows + tk::kGtBM - 1) / tk::kGtBM, (cols + bn - 1) / bn, n_splits);
-  if (cluster_reduce && n_splits > 1) {
+  if (cluster_reduce > 1) {
     // the staging area [bn][128] floats must fit into the ring of stages
     if ((size_t)bn * tk::kGtBM * 4 > (size_t)n_stages * stage_bytes) return (int)cudaErrorInvalidValue;
     return (int)tk::launch_cluster_z(tk::gemm_tcgen05_kernel, grid, dim3(tk::kGtThreads), smem_bytes, stream,
-                                     (unsigned)n_splits, map_r, map_c, p);
+                                     (unsigned)cluster_reduce, map_r, map_c, p);
   }
   return (int)tk::launch(tk::gemm_tcgen05_kernel, grid, dim3(tk::kGtThreads), smem_bytes, stream, map_r, map_c, p);
 }

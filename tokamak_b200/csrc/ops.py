@@ -358,12 +358,12 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
 
 
 def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_splits: int,
-                    out: torch.Tensor | None = None, max_stages: int = 0,
-                    cluster_reduce: bool = False) -> torch.Tensor:
+                    out: torch.Tensor | None = None, max_stages: int = 0, cluster: int = 0) -> torch.Tensor:
     """``x @ weight^T`` on tcgen05, the weight being the 128-row operand (for few tokens: every
     weight byte is streamed once by TMA), as float32 partial sums ``[parts, tokens, N_out]`` for
-    the caller to add up: ``parts = n_splits``, or 1 with ``cluster_reduce`` (at most 8 splits),
-    where the splits of a tile form a thread-block cluster that adds them up itself."""
+    the caller to add up.  ``parts = n_splits``, or ``n_splits / cluster`` with ``cluster`` in
+    2..8 (a divisor of ``n_splits``): that many consecutive splits of a tile form a thread-block
+    cluster that adds its partials up itself."""
     _want(weight, torch.bfloat16, "weight"); _want(x, torch.bfloat16, "x")
     n_out, k = weight.shape
     tokens, kx = x.shape
@@ -371,30 +371,34 @@ def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_
         raise KernelError(f"inner sizes {k} and {kx} must agree and be a multiple of 8")
     if tokens > 256:
         raise KernelError("the swapped product takes at most 256 tokens")
+    if cluster > 1 and (cluster > 8 or n_splits % cluster):
+        raise KernelError("a cluster holds 2..8 splits and must divide their count")
     bn = 16
     while bn < tokens:
         bn *= 2
-    if cluster_reduce and n_splits > 8:
-        raise KernelError("a cluster adds up at most 8 splits")
+    parts = n_splits // cluster if cluster > 1 else n_splits
     if out is None:
-        out = torch.empty((1 if cluster_reduce else n_splits, tokens, n_out), dtype=torch.float32,
-                          device=x.device)
+        out = torch.empty((parts, tokens, n_out), dtype=torch.float32, device=x.device)
     _check(library().tk_gemm_bf16_tcgen05(weight.data_ptr(), x.data_ptr(), out.data_ptr(), err.data_ptr(),
                                           n_out, tokens, k, k, k, 0, bn, n_splits, 1, 1, max_stages,
-                                          1 if cluster_reduce else 0, _stream()),
+                                          cluster if cluster > 1 else 0, _stream()),
            "gemm_tc_swapped")
     return out
 
 
-def swapped_gemm_plan(n_out: int, k: int) -> tuple[int, int]:
-    """(K splits, pipeline stages) of the swapped product: about 2.5 blocks per SM, each with at
-    least four 64-wide k blocks; shallow rings so that several blocks share an SM and one block's
-    start-up hides behind another's streaming."""
+def swapped_gemm_plan(n_out: int, k: int) -> tuple[int, int, int]:
+    """(K splits, pipeline stages, cluster size) of the swapped product.
+
+    About 2.5 to 3 blocks per SM, each with at least four 64-wide k blocks; three-stage rings so
+    that several blocks share an SM and one block's start-up hides behind another's streaming;
+    the splits of a tile (at most 8) form one cluster that adds its partials up, so the consumer
+    sees a single part.  Measured on the Qwen3-8B decode step: 16 splits in two clusters, deeper
+    rings and other block counts were all slower."""
     tiles = -(-n_out // 128)
     k_blocks = -(-k // 64)
-    splits = max(1, min(round(384 / tiles), max(1, k_blocks // 4), 8))    # a cluster holds 8 blocks
+    splits = max(1, min(round(448 / tiles), max(1, k_blocks // 4), 8))
     stages = 4 if splits == 1 else 3
-    return splits, stages
+    return splits, stages, splits
 
 
 def gemm_tc(x: torch.Tensor, weight: torch.Tensor, err: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,

@@ -112,8 +112,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
 
     bfloat16, few tokens (decoding): the tcgen05 kernel with the weight as the 128-row
     operand, streamed once by TMA and split over K, the splits of a tile added up inside a
-    thread-block cluster.  The result is a 3-D float32 tensor ``[parts, tokens, out]`` (here
-    one part) which the consuming kernel (norm, rotation, activation) adds up; ``err`` is the
+    thread-block cluster.  The result is a 3-D float32 tensor ``[parts, tokens, out]`` (one
+    or two parts) which the consuming kernel (norm, rotation, activation) adds up; ``err`` is the
     error word its bounded waits report to.
 
     bfloat16, many tokens: the library product, as the reference uses the library for its
@@ -125,8 +125,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     if x.dtype == torch.float32:
         return ops.gemm_f32(x, weight)
     if err is not None and x.shape[0] <= SWAPPED_GEMM_MAX_TOKENS and weight.shape[1] % 8 == 0:
-        splits, stages = ops.swapped_gemm_plan(weight.shape[0], weight.shape[1])
-        return ops.gemm_tc_swapped(weight, x, err, splits, max_stages=stages, cluster_reduce=True)
+        splits, stages, cluster = ops.swapped_gemm_plan(weight.shape[0], weight.shape[1])
+        return ops.gemm_tc_swapped(weight, x, err, splits, max_stages=stages, cluster=cluster)
     if out_dtype is not None and out_dtype != x.dtype:
         return torch.mm(x, weight.t(), out_dtype=out_dtype)
     return torch.mm(x, weight.t())
