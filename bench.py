@@ -266,6 +266,24 @@ def kernel_case(name: str, batch: int, ctx: int, iters: int, peaks: dict) -> dic
                              scale=d ** -0.5, window=None)
             nbytes = 2 * kc.numel() * 2 + 2 * q.numel() * 2
             flops = batch * 2.0 * 2.0 * (ctx * (ctx + 1) / 2) * hq * d
+    elif name == "rope_kv":
+        # q/k norm + rotation + cache write for `batch` tokens of one request (prefill shape)
+        n = batch
+        pages = -(-n // page)
+        kc = torch.zeros((pages, hkv, page, d), dtype=torch.bfloat16, device=dev)
+        vc = torch.zeros_like(kc)
+        qkv = torch.randn((n, (hq + 2 * hkv) * d), device=dev, generator=gen).bfloat16()
+        q_out = torch.empty((n, hq, d), dtype=torch.bfloat16, device=dev)
+        positions = torch.arange(n, dtype=torch.int32, device=dev)
+        tok_req = torch.zeros(n, dtype=torch.int32, device=dev)
+        table = torch.arange(pages, dtype=torch.int32, device=dev).view(1, pages)
+        wq, wk = torch.ones(d, device=dev), torch.ones(d, device=dev)
+        inv_freq = (1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(dev)
+        rot = ops.rope_table(positions, inv_freq)
+        run = lambda: ops.rope_kv(qkv, q_out, kc, vc, positions, tok_req, i32([0]), table, wq, wk, rot, err,
+                                  n_q_heads=hq, n_kv_heads=hkv, head_dim=d, rotary_dim=d, eps=1e-6,
+                                  req_q_len=i32([n]), req_kv_len=i32([n]))
+        nbytes = qkv.numel() * 2 + q_out.numel() * 2 + 2 * n * hkv * d * 2
     elif name == "rmsnorm":
         n, h = batch, cfg["hidden_size"]
         resid = torch.randn((n, h), device=dev, generator=gen)
