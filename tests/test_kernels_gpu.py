@@ -79,6 +79,24 @@ def test_swiglu(dtype):
     torch.testing.assert_close(out.double(), g * torch.sigmoid(g) * u, **tol(dtype))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("inter,block", [(192, 64), (320, 64), (45, 9), (96, 24)])
+def test_swiglu_gate_and_up_in_blocks(dtype, inter, block):
+    """Rows that hold ``block`` gate values, then the ``block`` up values of the same outputs."""
+    from tokamak_b200.csrc import ops
+    n = 7
+    g = (torch.randn(n, inter, device=DEV) * 3).to(dtype)
+    u = torch.randn(n, inter, device=DEV).to(dtype)
+    gu = torch.stack((g.view(n, inter // block, block), u.view(n, inter // block, block)), dim=2).reshape(n, 2 * inter)
+    out = torch.empty(n, inter, device=DEV, dtype=dtype)
+    ops.swiglu(gu.contiguous(), out, block=block)
+    torch.testing.assert_close(out.double(), g.double() * torch.sigmoid(g.double()) * u.double(), **tol(dtype))
+    parts = torch.stack((0.25 * gu.float(), 0.75 * gu.float()))
+    out2 = torch.empty_like(out)
+    ops.swiglu(parts, out2, block=block)
+    torch.testing.assert_close(out2.double(), out.double(), **tol(dtype))
+
+
 @pytest.mark.parametrize("shape", [(3, 317, 96), (130, 70, 33), (1, 1, 1), (64, 64, 16), (65, 129, 1000)])
 def test_gemm_f32_is_true_float32_and_row_independent(shape):
     from tokamak_b200.csrc import ops
@@ -571,6 +589,33 @@ def test_gemm_tcgen05_swapped_partials(tokens, n_out, k, splits, cluster):
     want = x.double() @ w.double().T
     got = parts.double().sum(0).cpu()
     torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-3 * (k ** 0.5) / 8)
+
+
+@pytest.mark.parametrize("tokens,inter,k,splits", [(8, 192, 512, 2), (1, 64, 64, 1), (64, 640, 1536, 6),
+                                                    (33, 128, 200, 1), (16, 12288, 4096, 8), (5, 320, 4096, 8)])
+def test_gemm_tcgen05_swapped_with_gated_activation(tokens, inter, k, splits):
+    """The decode product of a stacked gate/up weight (rows alternating in blocks of 64) whose
+    cluster stores silu(gate) * up itself, against the separate product and formula."""
+    from tokamak_b200.csrc import ops
+    gen = torch.Generator().manual_seed(tokens + inter)
+    x = torch.randn(tokens, k, generator=gen).bfloat16()
+    wg = (torch.randn(inter, k, generator=gen) * (2.0 / k ** 0.5)).bfloat16()
+    wu = (torch.randn(inter, k, generator=gen) / k ** 0.5).bfloat16()
+    b = ops.SWIGLU_TILE_BLOCK
+    w = torch.stack((wg.view(inter // b, b, k), wu.view(inter // b, b, k)), dim=1).reshape(2 * inter, k).contiguous()
+    err = err_word()
+    got = ops.gemm_tc_swapped(w.to(DEV), x.to(DEV), err, splits, cluster=splits, swiglu=True)
+    torch.cuda.synchronize()
+    assert err.tolist()[0] == 0, err.tolist()
+    assert got.shape == (tokens, inter) and got.dtype == torch.bfloat16
+    g, u = x.double() @ wg.double().T, x.double() @ wu.double().T
+    want = g * torch.sigmoid(g) * u
+    torch.testing.assert_close(got.double().cpu(), want, rtol=1e-2, atol=1e-2)
+    # the same sums through the float32 partials and the separate activation kernel: bit-equal
+    sums = ops.gemm_tc_swapped(w.to(DEV), x.to(DEV), err, splits, cluster=splits)
+    two = torch.empty(tokens, inter, device=DEV, dtype=torch.bfloat16)
+    ops.swiglu(sums, two, block=b)
+    assert torch.equal(two, got)
 
 
 @pytest.mark.parametrize("tokens,n_out,k,bn,out_dtype", [(200, 384, 320, 128, torch.bfloat16),

@@ -64,17 +64,24 @@ def test_position_parts():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_swiglu_part(dtype):
+@pytest.mark.parametrize("inter", [136, 192])       # stacked gate/up as two halves, and in blocks of 64
+def test_swiglu_part(dtype, inter):
+    from types import SimpleNamespace
+    from tokamak_b200.parts.base import sum_parts
     from tokamak_b200.parts.feedforward import SwiGLU, SwiGLUSpec
-    spec = SwiGLUSpec(hidden_size=72, intermediate_size=136)
+    spec = SwiGLUSpec(hidden_size=72, intermediate_size=inter)
     names = SwiGLU.expected_tensors(spec, "mlp.")
-    assert names["mlp.down_proj.weight"].shape == (72, 136)
+    assert names["mlp.down_proj.weight"].shape == (72, inter)
     tensors = {n: (0.1 * torch.randn(r.shape, device=DEV)).to(dtype) for n, r in names.items()}
     part = SwiGLU(spec, "mlp.", tensors, runtime(dtype))
     x = torch.randn(11, 72, device=DEV).to(dtype)
-    got = part.forward(x, None)
     want = plain.swiglu_mlp(x.double(), tensors["mlp.gate_proj.weight"].double(),
                             tensors["mlp.up_proj.weight"].double(), tensors["mlp.down_proj.weight"].double())
+    got = part.forward(x, None)                      # the path of many tokens
+    torch.testing.assert_close(got.double(), want, **tol(dtype))
+    step = SimpleNamespace(err=torch.zeros(4, dtype=torch.int32, device=DEV))
+    got = sum_parts(part.forward(x, step))           # the path of few tokens (the decode products in bfloat16)
+    assert step.err.tolist()[0] == 0
     torch.testing.assert_close(got.double(), want, **tol(dtype))
 
 

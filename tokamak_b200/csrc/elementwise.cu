@@ -159,10 +159,12 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
   }
 }
 
-// out[t, j] = silu(gu[t, j]) * gu[t, inter + j]           (src/tokamak/model/layers.py:103)
+// out[t, j] = silu(gate[t, j]) * up[t, j]           (src/tokamak/model/layers.py:103)
+// A row of gu holds gate and up alternating in blocks: `block` gate values, then the `block` up
+// values of the same outputs (block = inter: all gate values, then all up values).
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, const float* __restrict__ parts, int n_parts,
-                              size_t part_stride, T* __restrict__ out, int inter, size_t total) {
+                              size_t part_stride, T* __restrict__ out, int inter, int block, size_t total) {
   pdl_trigger();
   pdl_wait();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -170,15 +172,16 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, const float* __restrict_
   for (; idx < total; idx += stride) {
     const size_t t = idx / inter;
     const int j = (int)(idx - t * inter);
+    const size_t at = t * 2 * inter + (size_t)(j / block) * 2 * block + (j % block);
     float g, u;
     if (parts == nullptr) {
-      g = to_f32<T>(gu[t * 2 * inter + j]);
-      u = to_f32<T>(gu[t * 2 * inter + inter + j]);
+      g = to_f32<T>(gu[at]);
+      u = to_f32<T>(gu[at + block]);
     } else {
       g = 0.0f; u = 0.0f;
       for (int s = 0; s < n_parts; ++s) {
-        g += parts[s * part_stride + t * 2 * inter + j];
-        u += parts[s * part_stride + t * 2 * inter + inter + j];
+        g += parts[s * part_stride + at];
+        u += parts[s * part_stride + at + block];
       }
     }
     const float s = g / (1.0f + expf(-g));
@@ -186,10 +189,10 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, const float* __restrict_
   }
 }
 
-// The same for an intermediate size that is a multiple of 8: 16-byte loads and stores.
+// The same for an intermediate size and a block that are multiples of 8: 16-byte loads and stores.
 template <typename T>
 __global__ void swiglu_vec_kernel(const T* __restrict__ gu, const float* __restrict__ parts, int n_parts,
-                                  size_t part_stride, T* __restrict__ out, int inter, size_t total8) {
+                                  size_t part_stride, T* __restrict__ out, int inter, int block, size_t total8) {
   pdl_trigger();
   pdl_wait();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -198,17 +201,18 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ gu, const float* __restr
   for (; idx < total8; idx += stride) {
     const size_t t = idx / per_row;
     const int j = (int)(idx - t * per_row) * 8;
+    const size_t at = t * 2 * inter + (size_t)(j / block) * 2 * block + (j % block);
     float g[8], u[8], y[8];
     if (parts == nullptr) {
-      Vec8<T>::load(gu + t * 2 * inter + j, g);
-      Vec8<T>::load(gu + t * 2 * inter + inter + j, u);
+      Vec8<T>::load(gu + at, g);
+      Vec8<T>::load(gu + at + block, u);
     } else {
 #pragma unroll
       for (int e = 0; e < 8; ++e) { g[e] = 0.0f; u[e] = 0.0f; }
       for (int s = 0; s < n_parts; ++s) {
         float a[8], b[8];
-        Vec8<float>::load(parts + s * part_stride + t * 2 * inter + j, a);
-        Vec8<float>::load(parts + s * part_stride + t * 2 * inter + inter + j, b);
+        Vec8<float>::load(parts + s * part_stride + at, a);
+        Vec8<float>::load(parts + s * part_stride + at + block, b);
 #pragma unroll
         for (int e = 0; e < 8; ++e) { g[e] += a[e]; u[e] += b[e]; }
       }
@@ -265,19 +269,20 @@ TK_API int tk_add_rmsnorm(float* resid, const void* delta, const float* parts, i
 }
 
 TK_API int tk_swiglu(const void* gate_up, const float* parts, int n_parts, long long part_stride,
-                     void* out, int n_tokens, int inter, int dtype, cudaStream_t stream) {
+                     void* out, int n_tokens, int inter, int block, int dtype, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
+  if (block <= 0 || inter % block != 0) return (int)cudaErrorInvalidValue;
   const size_t total = (size_t)n_tokens * inter;
   const int threads = 256;
   cudaError_t e = cudaSuccess;
-  if (inter % 8 == 0) {
+  if (inter % 8 == 0 && block % 8 == 0) {
     const size_t total8 = total / 8;
     size_t vblocks = (total8 + threads - 1) / threads;
     if (vblocks > 148 * 32) vblocks = 148 * 32;
     TK_DISPATCH_DTYPE(dtype, T,
                       e = tk::launch(tk::swiglu_vec_kernel<T>, dim3((unsigned)vblocks), dim3(threads), 0, stream,
                                      (const T*)gate_up, parts, n_parts, (size_t)part_stride, (T*)out, inter,
-                                     total8));
+                                     block, total8));
     return (int)e;
   }
   size_t blocks = (total + threads - 1) / threads;
@@ -285,6 +290,6 @@ TK_API int tk_swiglu(const void* gate_up, const float* parts, int n_parts, long 
   TK_DISPATCH_DTYPE(dtype, T,
                     e = tk::launch(tk::swiglu_kernel<T>, dim3((unsigned)blocks), dim3(threads), 0, stream,
                                    (const T*)gate_up, parts, n_parts, (size_t)part_stride, (T*)out, inter,
-                                   total));
+                                   block, total));
   return (int)e;
 }

@@ -29,6 +29,11 @@ namespace tk {
 constexpr int kGtBM = 128;        // rows of R per block = UMMA M
 constexpr int kGtBK = 64;         // k-elements per stage = one 128-byte swizzle span of bf16
 constexpr int kGtThreads = 192;   // warp 0: TMA, warp 1: MMA, warps 2..5: epilogue
+// Epilogue of the swapped form for a stacked gate/up weight whose rows alternate in blocks of
+// 64 (64 gate rows, then the 64 up rows of the same outputs): a 128-row tile then holds both
+// halves of 64 outputs, and the block that adds the splits up stores
+// bf16(silu(gate) * up) as [token, rows / 2] instead of the float32 sums.
+constexpr int kGtEpiSwiglu = 1;
 
 struct GemmTcParams {
   void* out;                // swapped: float [n_splits, cols_total, rows_total]; else [rows_total, cols_total]
@@ -43,6 +48,7 @@ struct GemmTcParams {
   int cluster_reduce;       // swapped only: 0, or the cluster size: that many consecutive splits of a tile
                             // form a cluster and store their sum as one part (n_splits / cluster parts)
   int out_f32;              // non-swapped: 1 = float32 output, 0 = bfloat16
+  int epilogue;             // swapped only: 0 = float32 sums; 1 = gated activation, see kGtEpiSwiglu
   long long ld_out;         // non-swapped: elements between output rows
 };
 
@@ -183,7 +189,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
 #pragma unroll
         for (int e = 0; e < 16; ++e) v[e] = 0u;
       }
-      if (p.cluster_reduce > 1) {
+      if (p.cluster_reduce > 1 || p.epilogue == kGtEpiSwiglu) {
         // stage[column][row of the tile]: consecutive lanes write consecutive words
         float* stage = reinterpret_cast<float*>(smem);
 #pragma unroll
@@ -231,7 +237,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
 
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
-  if (p.cluster_reduce > 1) {
+  if (p.epilogue == kGtEpiSwiglu) {
+    cluster_sync_all();                    // every block of the cluster has staged its partial
+    if (warp >= 2) {
+      // thread -> output j of the tile's 64 and one of two column phases; gate in tile row j,
+      // up in tile row 64 + j; the sum over the ranks runs in the same order as without the
+      // activation, and the activation is the formula of the separate kernel
+      const int csize = p.cluster_reduce > 1 ? p.cluster_reduce : 1;
+      const uint32_t my_rank = p.cluster_reduce > 1 ? cluster_ctarank() : 0u;
+      const int t = (warp - 2) * 32 + lane;
+      const int j = t & 63, phase = t >> 6;
+      const int inter = p.rows_total >> 1;
+      const int oc = tile_r * 64 + j;
+      __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out);
+      if (oc < inter) {
+        for (int c = (int)my_rank + csize * phase; c < p.bn; c += 2 * csize) {
+          const int col = tile_c * p.bn + c;
+          if (col >= p.cols_total) break;
+          float g = 0.0f, u = 0.0f;
+          for (int rk = 0; rk < csize; ++rk) {
+            g += ld_cluster_f32(base + (uint32_t)((c * kGtBM + j) * 4), (uint32_t)rk);
+            u += ld_cluster_f32(base + (uint32_t)((c * kGtBM + 64 + j) * 4), (uint32_t)rk);
+          }
+          out[(size_t)col * inter + oc] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+        }
+      }
+    }
+    cluster_sync_all();                    // nobody's shared memory is read any more
+  } else if (p.cluster_reduce > 1) {
     cluster_sync_all();                    // every block of the cluster has staged its partial
     if (warp >= 2) {
       // every block of the cluster adds up its share of the columns (tokens): column c belongs
@@ -286,13 +319,20 @@ static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long
 // parts = n_splits, or n_splits / cluster_reduce when cluster_reduce > 1 (2..8, a divisor of
 // n_splits): that many consecutive splits form a thread-block cluster and store their sum.
 // swapped = 0: out is [rows, cols] with row stride ld_out, float32 if out_f32 else bfloat16; n_splits must be 1.
+// epilogue = 1 (swapped, rows a multiple of 128 whose gate and up rows alternate in blocks of 64, all
+// splits in one cluster): out is bfloat16 [cols, rows / 2] = silu(gate) * up.
 TK_API int tk_gemm_bf16_tcgen05(const void* r, const void* c, void* out, int* err, int rows, int cols, int k,
                                 long long ld_r, long long ld_c, long long ld_out, int bn, int n_splits,
-                                int swapped, int out_f32, int max_stages, int cluster_reduce, cudaStream_t stream) {
+                                int swapped, int out_f32, int max_stages, int cluster_reduce, int epilogue,
+                                cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;
   if (k <= 0 || k % 8 != 0 || (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) || n_splits < 1 ||
       (!swapped && n_splits != 1) ||
       (cluster_reduce > 1 && (!swapped || cluster_reduce > 8 || n_splits % cluster_reduce != 0)) || cluster_reduce < 0) {
+    return (int)cudaErrorInvalidValue;
+  }
+  if (epilogue != 0 && (epilogue != tk::kGtEpiSwiglu || !swapped || rows % 128 != 0 ||
+                        n_splits != (cluster_reduce > 1 ? cluster_reduce : 1))) {
     return (int)cudaErrorInvalidValue;
   }
   CUtensorMap map_r, map_c;
@@ -321,13 +361,13 @@ TK_API int tk_gemm_bf16_tcgen05(const void* r, const void* c, void* out, int* er
   }
   tk::GemmTcParams p;
   p.out = out; p.err = err; p.rows_total = rows; p.cols_total = cols; p.k_total = k; p.bn = bn;
-  p.n_stages = n_stages; p.n_splits = n_splits; p.swapped = swapped; p.out_f32 = out_f32; p.ld_out = ld_out; p.cluster_reduce = cluster_reduce;
+  p.n_stages = n_stages; p.n_splits = n_splits; p.swapped = swapped; p.out_f32 = out_f32; p.ld_out = ld_out; p.cluster_reduce = cluster_reduce; p.epilogue = epilogue;
   dim3 grid((rows + tk::kGtBM - 1) / tk::kGtBM, (cols + bn - 1) / bn, n_splits);
-  if (cluster_reduce > 1) {
+  if (cluster_reduce > 1 || epilogue != 0) {
     // the staging area [bn][128] floats must fit into the ring of stages
     if ((size_t)bn * tk::kGtBM * 4 > (size_t)n_stages * stage_bytes) return (int)cudaErrorInvalidValue;
     return (int)tk::launch_cluster_z(tk::gemm_tcgen05_kernel, grid, dim3(tk::kGtThreads), smem_bytes, stream,
-                                     (unsigned)cluster_reduce, map_r, map_c, p);
+                                     (unsigned)(cluster_reduce > 1 ? cluster_reduce : 1), map_r, map_c, p);
   }
   return (int)tk::launch(tk::gemm_tcgen05_kernel, grid, dim3(tk::kGtThreads), smem_bytes, stream, map_r, map_c, p);
 }

@@ -18,7 +18,7 @@ _P = c_void_p
 _SIGNATURES: dict[str, list] = {
     "tk_embed_gather": [_P, c_int, _P, _P, c_int, c_int, c_int, _P, _P],
     "tk_add_rmsnorm": [_P, _P, _P, c_int, c_longlong, _P, _P, _P, c_int, c_int, c_float, c_int, _P],
-    "tk_swiglu": [_P, _P, c_int, c_longlong, _P, c_int, c_int, c_int, _P],
+    "tk_swiglu": [_P, _P, c_int, c_longlong, _P, c_int, c_int, c_int, c_int, _P],
     "tk_rope_kv": [_P, _P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                    c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                    c_float, c_int, _P],
@@ -38,7 +38,7 @@ _SIGNATURES: dict[str, list] = {
     "tk_attention_prefill_tc_takes": [c_int, c_int, c_int, c_int],
     "tk_attention_prefill_tc_rows": [],
     "tk_gemm_bf16_tcgen05": [_P, _P, _P, _P, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
-                             c_int, c_int, c_int, c_int, c_int, c_int, _P],
+                             c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "tk_gemm_f32": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "tk_sample": [_P, c_longlong, _P, _P, _P, _P, _P, _P, c_int, c_int, _P],
 }

@@ -96,9 +96,11 @@ def add_rmsnorm(resid: torch.Tensor, delta: torch.Tensor | None, weight: torch.T
                                     float(eps), dtype_code(out.dtype), _stream()), "add_rmsnorm")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, j] = silu(gate_up[t, j]) * gate_up[t, I + j]; ``gate_up`` may be float32 partial
-    sums ``[parts, tokens, 2I]`` that the kernel adds up first."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
+    """out[t, j] = silu(gate[t, j]) * up[t, j]; a row of ``gate_up`` holds ``block`` gate values,
+    then the ``block`` up values of the same outputs, and so on (``block = 0``: all I gate values,
+    then all up values).  ``gate_up`` may be float32 partial sums ``[parts, tokens, 2I]`` that the
+    kernel adds up first."""
     _want(gate_up, None, "gate_up"); _want(out, None, "out")
     parts, n_parts, part_stride = None, 0, 0
     if gate_up.dim() == 3:
@@ -112,8 +114,11 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
         n, two_i = gate_up.shape
     if two_i % 2 or out.shape != (n, two_i // 2):
         raise KernelError("swiglu shape mismatch")
+    block = block or two_i // 2
+    if (two_i // 2) % block:
+        raise KernelError("the gate/up block must divide the intermediate size")
     _check(library().tk_swiglu(_ptr(gate_up), _ptr(parts), n_parts, part_stride, out.data_ptr(), n,
-                               two_i // 2, dtype_code(out.dtype), _stream()), "swiglu")
+                               two_i // 2, block, dtype_code(out.dtype), _stream()), "swiglu")
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
@@ -357,13 +362,21 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
     return out
 
 
+SWIGLU_TILE_BLOCK = 64     # gate/up rows alternate in blocks of this many for the fused activation
+
+
 def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_splits: int,
-                    out: torch.Tensor | None = None, max_stages: int = 0, cluster: int = 0) -> torch.Tensor:
+                    out: torch.Tensor | None = None, max_stages: int = 0, cluster: int = 0,
+                    swiglu: bool = False) -> torch.Tensor:
     """``x @ weight^T`` on tcgen05, the weight being the 128-row operand (for few tokens: every
     weight byte is streamed once by TMA), as float32 partial sums ``[parts, tokens, N_out]`` for
     the caller to add up.  ``parts = n_splits``, or ``n_splits / cluster`` with ``cluster`` in
     2..8 (a divisor of ``n_splits``): that many consecutive splits of a tile form a thread-block
-    cluster that adds its partials up itself."""
+    cluster that adds its partials up itself.
+
+    ``swiglu=True``: the weight is a stacked gate/up matrix whose rows alternate in blocks of
+    ``SWIGLU_TILE_BLOCK`` (gate rows, then the up rows of the same outputs); all splits form one
+    cluster and the result is bfloat16 ``[tokens, N_out / 2] = silu(gate) * up``."""
     _want(weight, torch.bfloat16, "weight"); _want(x, torch.bfloat16, "x")
     n_out, k = weight.shape
     tokens, kx = x.shape
@@ -377,11 +390,16 @@ def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_
     while bn < tokens:
         bn *= 2
     parts = n_splits // cluster if cluster > 1 else n_splits
-    if out is None:
+    if swiglu:
+        if n_out % (2 * SWIGLU_TILE_BLOCK) or parts != 1:
+            raise KernelError("the fused activation wants rows in blocks of 64 gate + 64 up and one cluster")
+        if out is None:
+            out = torch.empty((tokens, n_out // 2), dtype=torch.bfloat16, device=x.device)
+    elif out is None:
         out = torch.empty((parts, tokens, n_out), dtype=torch.float32, device=x.device)
     _check(library().tk_gemm_bf16_tcgen05(weight.data_ptr(), x.data_ptr(), out.data_ptr(), err.data_ptr(),
                                           n_out, tokens, k, k, k, 0, bn, n_splits, 1, 1, max_stages,
-                                          cluster if cluster > 1 else 0, _stream()),
+                                          cluster if cluster > 1 else 0, 1 if swiglu else 0, _stream()),
            "gemm_tc_swapped")
     return out
 
@@ -412,7 +430,8 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, err: torch.Tensor, out_dtype:
     out = torch.empty((tokens, n_out), dtype=out_dtype, device=x.device)
     _check(library().tk_gemm_bf16_tcgen05(x.data_ptr(), weight.data_ptr(), out.data_ptr(), err.data_ptr(),
                                           tokens, n_out, k, k, k, n_out, bn, 1, 0,
-                                          1 if out_dtype == torch.float32 else 0, max_stages, 0, _stream()), "gemm_tc")
+                                          1 if out_dtype == torch.float32 else 0, max_stages, 0, 0, _stream()),
+           "gemm_tc")
     return out
 
 

@@ -7,7 +7,7 @@ from dataclasses import dataclass
 import torch
 
 from ..csrc import ops
-from .base import FEED_FORWARDS, Runtime, TensorReq, linear
+from .base import FEED_FORWARDS, SWAPPED_GEMM_MAX_TOKENS, Runtime, TensorReq, linear
 
 
 @dataclass(frozen=True)
@@ -22,14 +22,26 @@ class SwiGLU:
     """``down(silu(gate(x)) * up(x))`` without biases (src/tokamak/model/layers.py:92-104).
 
     The gate and up matrices are stacked into one ``[2I, H]`` operand so that one
-    product feeds the activation kernel.
+    product feeds the activation.  Where the intermediate size allows it, their rows
+    alternate in blocks of 64 (64 gate rows, then the 64 up rows of the same outputs): a
+    128-row tile of the decode product then holds both halves of 64 outputs, and the block
+    that adds its K splits up applies the activation itself, so that decoding needs no
+    activation kernel and no float32 round trip of the ``[tokens, 2I]`` sums.
     """
 
     def __init__(self, spec: SwiGLUSpec, prefix: str, tensors: dict[str, torch.Tensor], rt: Runtime):
         self.spec = spec
         self.rt = rt
-        self.w_gate_up = torch.cat((tensors[prefix + "gate_proj.weight"],
-                                    tensors[prefix + "up_proj.weight"]), dim=0).contiguous()
+        gate, up = tensors[prefix + "gate_proj.weight"], tensors[prefix + "up_proj.weight"]
+        i, h = spec.intermediate_size, spec.hidden_size
+        b = ops.SWIGLU_TILE_BLOCK
+        if i % b == 0:
+            self.block = b
+            self.w_gate_up = torch.stack((gate.view(i // b, b, h), up.view(i // b, b, h)), dim=1).reshape(2 * i, h)
+        else:
+            self.block = i
+            self.w_gate_up = torch.cat((gate, up), dim=0)
+        self.w_gate_up = self.w_gate_up.contiguous()
         self.w_down = tensors[prefix + "down_proj.weight"]
 
     @staticmethod
@@ -43,7 +55,13 @@ class SwiGLU:
 
     def forward(self, h: torch.Tensor, step) -> torch.Tensor:
         err = step.err if step is not None else None
-        gate_up = linear(h, self.w_gate_up, err=err)
-        act = torch.empty((h.shape[0], self.spec.intermediate_size), dtype=h.dtype, device=h.device)
-        ops.swiglu(gate_up, act)
+        if (h.dtype == torch.bfloat16 and err is not None and h.shape[0] <= SWAPPED_GEMM_MAX_TOKENS
+                and self.block == ops.SWIGLU_TILE_BLOCK and self.spec.hidden_size % 8 == 0):
+            splits, stages, cluster = ops.swapped_gemm_plan(2 * self.spec.intermediate_size, self.spec.hidden_size)
+            act = ops.gemm_tc_swapped(self.w_gate_up, h, err, splits, max_stages=stages, cluster=cluster,
+                                      swiglu=True)
+        else:
+            gate_up = linear(h, self.w_gate_up, err=err)
+            act = torch.empty((h.shape[0], self.spec.intermediate_size), dtype=h.dtype, device=h.device)
+            ops.swiglu(gate_up, act, block=self.block)
         return linear(act, self.w_down, err=err)
