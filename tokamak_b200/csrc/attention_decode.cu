@@ -15,6 +15,10 @@
 // The reference's kernel has no split and one program per (sequence, kv head)
 // (paged_attention.py:19-20,202).
 //
+// Programmatic dependent launch: key and value tiles that lie wholly below the token's own
+// position are requested before the wait on the preceding kernel (which writes the cache only
+// at the new tokens' places); the queries and the tile of the new token come after it.
+//
 // Keys outside [max(0, pos - window + 1), pos] are never loaded: their rows are
 // zero-filled, so stale or foreign data in a partly filled or given-back page
 // cannot reach the result.
@@ -49,7 +53,6 @@ template <int D>
 __global__ void __launch_bounds__(kDecWarps * 32)
 attn_decode_split_kernel(DecodeParams p) {
   pdl_trigger();
-  pdl_wait();
   constexpr int CH = D / 8;                       // 16-byte chunks per row
   constexpr int TILE_BYTES = kDecTile * D * 2;    // one K or V tile
   constexpr int STAGE_BYTES = 2 * TILE_BYTES;
@@ -78,20 +81,6 @@ attn_decode_split_kernel(DecodeParams p) {
 
   unsigned char* my_smem = smem + warp * kDecStages * STAGE_BYTES;
   const uint32_t my_smem_u32 = smem_u32(my_smem);
-
-  // ---- query fragments: row g of the tile is query head hkv * group + g --------------------
-  uint32_t qa[D / 16][4];
-  {
-    const __nv_bfloat16* qbase = p.q + ((size_t)tok * p.n_q_heads + (size_t)hkv * group) * D;
-#pragma unroll
-    for (int ks = 0; ks < D / 16; ++ks) {
-      const int c0 = ks * 16 + 2 * t4;
-      qa[ks][0] = (g < group) ? *reinterpret_cast<const uint32_t*>(qbase + (size_t)g * D + c0) : 0u;
-      qa[ks][2] = (g < group) ? *reinterpret_cast<const uint32_t*>(qbase + (size_t)g * D + c0 + 8) : 0u;
-      qa[ks][1] = (g + 8 < group) ? *reinterpret_cast<const uint32_t*>(qbase + (size_t)(g + 8) * D + c0) : 0u;
-      qa[ks][3] = (g + 8 < group) ? *reinterpret_cast<const uint32_t*>(qbase + (size_t)(g + 8) * D + c0 + 8) : 0u;
-    }
-  }
 
   float o[D / 8][4];
 #pragma unroll
@@ -128,8 +117,34 @@ attn_decode_split_kernel(DecodeParams p) {
 
   // tiles of this warp: my_begin + warp, + kDecWarps, ...
   const int n_mine = (my_end - my_begin - warp + kDecWarps - 1) / kDecWarps;
+  // Warm start.  The batch description and the block tables were written before the chain of
+  // kernels of this step began, and the kernel before this one writes the cache only at the
+  // new tokens' places, for this token at `pos`.  Tiles that end below `pos` are therefore
+  // requested before the wait on that kernel; the tile that holds `pos`, and the queries, after.
+  int warm = 0;
 #pragma unroll
-  for (int s = 0; s < kDecStages - 1; ++s) {
+  for (; warm < kDecStages - 1; ++warm) {
+    const int tile = my_begin + warp + warm * kDecWarps;
+    if (warm >= n_mine || tile >= last_tile) break;
+    issue_load(tile, warm);
+    cp_async_commit();
+  }
+  pdl_wait();
+  // ---- query fragments: row g of the tile is query head hkv * group + g --------------------
+  uint32_t qa[D / 16][4];
+  {
+    const __nv_bfloat16* qbase = p.q + ((size_t)tok * p.n_q_heads + (size_t)hkv * group) * D;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const int c0 = ks * 16 + 2 * t4;
+      qa[ks][0] = (g < group) ? *reinterpret_cast<const uint32_t*>(qbase + (size_t)g * D + c0) : 0u;
+      qa[ks][2] = (g < group) ? *reinterpret_cast<const uint32_t*>(qbase + (size_t)g * D + c0 + 8) : 0u;
+      qa[ks][1] = (g + 8 < group) ? *reinterpret_cast<const uint32_t*>(qbase + (size_t)(g + 8) * D + c0) : 0u;
+      qa[ks][3] = (g + 8 < group) ? *reinterpret_cast<const uint32_t*>(qbase + (size_t)(g + 8) * D + c0 + 8) : 0u;
+    }
+  }
+
+  for (int s = warm; s < kDecStages - 1; ++s) {
     if (s < n_mine) issue_load(my_begin + warp + s * kDecWarps, s);
     cp_async_commit();
   }
