@@ -297,7 +297,7 @@ def kernel_case(name: str, batch: int, ctx: int, iters: int, peaks: dict) -> dic
         w = torch.randn((2 * cfg["intermediate_size"], cfg["hidden_size"]), device=dev, generator=gen).bfloat16()
         ws = [w.clone() for _ in range(4)]
         x = torch.randn((batch, cfg["hidden_size"]), device=dev, generator=gen).bfloat16()
-        splits, stages, cluster = ops.swapped_gemm_plan(w.shape[0], w.shape[1])
+        splits, stages, cluster = ops.swapped_gemm_plan(w.shape[0], w.shape[1], batch)
         out = torch.empty((splits // cluster if cluster > 1 else splits, batch, w.shape[0]),
                           dtype=torch.float32, device=dev)
         turn = [0]

@@ -404,18 +404,20 @@ def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_
     return out
 
 
-def swapped_gemm_plan(n_out: int, k: int) -> tuple[int, int, int]:
+def swapped_gemm_plan(n_out: int, k: int, tokens: int = 8) -> tuple[int, int, int]:
     """(K splits, pipeline stages, cluster size) of the swapped product.
 
-    About 2.5 to 3 blocks per SM, each with at least four 64-wide k blocks; three-stage rings so
-    that several blocks share an SM and one block's start-up hides behind another's streaming;
-    the splits of a tile (at most 8) form one cluster that adds its partials up, so the consumer
-    sees a single part.  Measured on the Qwen3-8B decode step: 16 splits in two clusters, deeper
-    rings and other block counts were all slower."""
+    About 2.5 to 3 blocks per SM, each with at least four 64-wide k blocks, so that several
+    blocks share an SM and one block's start-up hides behind another's streaming; the splits of
+    a tile (at most 8) form one cluster that adds its partials up, so the consumer sees a single
+    part.  Rings of three stages; four where the grid is short (at most about 2.7 blocks per SM)
+    and the token tile is small, so that three blocks still fit an SM.  Measured on the
+    Qwen3-8B decode step: 16 splits in two clusters, deeper rings and other block counts were
+    all slower, and so were four stages for the long gate/up grid or for 64-token tiles."""
     tiles = -(-n_out // 128)
     k_blocks = -(-k // 64)
     splits = max(1, min(round(448 / tiles), max(1, k_blocks // 4), 8))
-    stages = 4 if splits == 1 else 3
+    stages = 4 if splits == 1 or (tiles * splits <= 400 and tokens <= 16) else 3
     return splits, stages, splits
 
 

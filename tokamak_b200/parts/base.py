@@ -125,7 +125,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     if x.dtype == torch.float32:
         return ops.gemm_f32(x, weight)
     if err is not None and x.shape[0] <= SWAPPED_GEMM_MAX_TOKENS and weight.shape[1] % 8 == 0:
-        splits, stages, cluster = ops.swapped_gemm_plan(weight.shape[0], weight.shape[1])
+        splits, stages, cluster = ops.swapped_gemm_plan(weight.shape[0], weight.shape[1], x.shape[0])
         return ops.gemm_tc_swapped(weight, x, err, splits, max_stages=stages, cluster=cluster)
     if out_dtype is not None and out_dtype != x.dtype:
         return torch.mm(x, weight.t(), out_dtype=out_dtype)

@@ -57,7 +57,8 @@ class SwiGLU:
         err = step.err if step is not None else None
         if (h.dtype == torch.bfloat16 and err is not None and h.shape[0] <= SWAPPED_GEMM_MAX_TOKENS
                 and self.block == ops.SWIGLU_TILE_BLOCK and self.spec.hidden_size % 8 == 0):
-            splits, stages, cluster = ops.swapped_gemm_plan(2 * self.spec.intermediate_size, self.spec.hidden_size)
+            splits, stages, cluster = ops.swapped_gemm_plan(2 * self.spec.intermediate_size, self.spec.hidden_size,
+                                                            h.shape[0])
             act = ops.gemm_tc_swapped(self.w_gate_up, h, err, splits, max_stages=stages, cluster=cluster,
                                       swiglu=True)
         else:
