@@ -150,14 +150,23 @@ def time_decode(core, batch: int, steps: int, warmup: int, ctx_end: int, vocab: 
     from tokamak_b200.csrc import ops
     from tokamak_b200.engine.step import SamplingRow, StepEntry
     req_ids = [f"b{batch}_{i}" for i in range(batch)]
-    start_len = ctx_end - (steps + warmup)
+    start_len = ctx_end - (steps + warmup + 1)
     fill_context(core, req_ids, start_len, vocab, seed=batch)
     greedy = [SamplingRow(0.0, 0, 1.0, 0, 0) for _ in range(batch)]
     tokens = [1 + i for i in range(batch)]
 
+    # Steps are launched one ahead: the token that a step samples stays on the device and feeds
+    # the next step, which is launched before the host has read the step before it, so the
+    # device does not wait for the host.  Every step's tokens still come back to the host.
+    fed_entries = [StepEntry(r, [0], [0]) for r in req_ids]
+    feed = list(range(batch))
+    flight = core.step.launch_and_sample([StepEntry(r, [t], [0]) for r, t in zip(req_ids, tokens)], greedy)
+
     def one_step():
-        nonlocal tokens
-        tokens = core.step.run_and_sample([StepEntry(r, [t], [0]) for r, t in zip(req_ids, tokens)], greedy)
+        nonlocal tokens, flight
+        ahead = core.step.launch_and_sample(fed_entries, greedy, feed)
+        tokens = core.step.collect(flight)
+        flight = ahead
 
     for _ in range(warmup):
         one_step()
@@ -170,6 +179,7 @@ def time_decode(core, batch: int, steps: int, warmup: int, ctx_end: int, vocab: 
         one_step()
     end.record()
     torch.cuda.synchronize()
+    tokens = core.step.collect(flight)
     ms = begin.elapsed_time(end)
     wall = time.perf_counter() - t_host
     launches = ops.LAUNCHES + core.step.graph_launches - launches0
@@ -219,7 +229,9 @@ def time_e2e(core, batch: int, steps: int, warmup: int, ctx_end: int, vocab: int
     assert len(times) >= steps + warmup, "the requests did not decode together"
     full = times[-steps:]                         # the last K decode steps, all at full batch
     tok_s = batch * len(full) / sum(full)
-    h2d = 4 * (8 * batch + 5 * batch)             # step description + sampling rows, int32 words
+    # int32 words of a decode step's description: 9 per request for the batch layout, 7 for sampling
+    # (feed place, 64-bit seed, temperature, top-p, top-k, counter)
+    h2d = 4 * 16 * batch
     d2h = 4 * (4 + batch)
     return {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
             "ms_per_step": 1e3 * sum(full) / len(full)}

@@ -175,3 +175,79 @@ def test_many_requests_small_pool_equal_single_request_runs():
         want = alone.generate(prompt_token_ids=[prompts[i]], sampling_params=params[i])[0]
         assert outs[i].output_token_ids == want.output_token_ids, i
         assert len(outs[i].output_token_ids) == params[i].max_new_tokens
+
+
+def test_steps_launched_ahead_end_where_the_requests_end_alone():
+    """Decode steps are launched before the step before them has been read.  Requests that stop
+    on an end-of-sequence token, or at different lengths, while such a step is already running
+    end exactly where they end alone, and every page and slot comes back."""
+    from tokamak_b200 import SamplingParams
+    llm = llm_for("A", "float32", max_batch_size=4)
+    prompts = prompts_for("A", [6, 11, 19, 8])
+    free_run = SamplingParams(temperature=0.0, max_new_tokens=20)
+    alone = [llm.generate(prompt_token_ids=[p], sampling_params=free_run)[0].output_token_ids for p in prompts]
+    eos = alone[1][7]
+    limits = [20, 20, 13, 5]
+    want = []
+    for toks, limit in zip(alone, limits):
+        toks = toks[:limit]
+        want.append(toks[:toks.index(eos) + 1] if eos in toks else toks)
+    llm.model_config = dataclasses.replace(llm.model_config, eos_token_ids=(eos,))
+    params = [SamplingParams(temperature=0.0, max_new_tokens=n) for n in limits]
+    outs = llm.generate(prompt_token_ids=prompts, sampling_params=params)
+    assert [o.output_token_ids for o in outs] == want
+    assert outs[1].finish_reason.value == "stop" and len(outs[1].output_token_ids) <= 8
+    assert outs[3].finish_reason.value in ("length", "stop")
+    assert llm.last_stats["decode_steps"] >= 10
+    llm.cache_manager.check_invariants()
+    assert all(g.num_free == g.num_pages for g in llm.cache_manager.kv_groups)
+    assert llm.cache_manager.num_free_slots == llm.cache_manager.max_slots
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_step_fed_on_the_device_equals_one_fed_by_the_host(dtype):
+    """launch_and_sample with a feed, two steps in flight, against run_and_sample step by step:
+    the same tokens, with and without CUDA graphs (seeded temperature sampling, so the counters
+    of the random generator have to be right as well)."""
+    from tokamak_b200.engine.replay import build_core
+    from tokamak_b200.engine.step import SamplingRow, StepEntry
+    tag = "C" if dtype == "bfloat16" else "B"
+    cfg, _, page = tiny_configs.ALL[tag][:3]
+    core = build_core(model_folder(tag, dtype), dtype, max_tokens=512, page_size=page)
+    prompts = [random_tokens(cfg["vocab_size"], n, seed=n) for n in (9, 4, 17)]
+    rows = lambda k: [SamplingRow(0.7, 0, 1.0, seed=100 + i, counter=k) for i in range(3)]
+    steps = 12
+
+    def by_host(ids):
+        toks = core.step.run_and_sample([StepEntry(r, p, [len(p) - 1]) for r, p in zip(ids, prompts)], rows(0))
+        out = [toks]
+        for k in range(1, steps):
+            toks = core.step.run_and_sample([StepEntry(r, [t], [0]) for r, t in zip(ids, toks)], rows(k))
+            out.append(toks)
+        for r in ids:
+            core.step.free(r)
+        return out
+
+    def by_device(ids):
+        flight = core.step.launch_and_sample([StepEntry(r, p, [len(p) - 1]) for r, p in zip(ids, prompts)], rows(0))
+        out = []
+        for k in range(1, steps):
+            # entries in another order than the step before: the feed names the places
+            order = [2, 0, 1] if k % 2 else [0, 1, 2]
+            prev = order_before if k > 1 else [0, 1, 2]
+            ahead = core.step.launch_and_sample([StepEntry(ids[i], [0], [0]) for i in order],
+                                                [rows(k)[i] for i in order],
+                                                feed=[prev.index(i) for i in order])
+            toks = core.step.collect(flight)
+            out.append([toks[prev.index(i)] for i in range(3)])
+            flight, order_before = ahead, order
+        toks = core.step.collect(flight)
+        out.append([toks[order_before.index(i)] for i in range(3)])
+        for r in ids:
+            core.step.free(r)
+        return out
+
+    want = by_host(["h0", "h1", "h2"])
+    assert by_device(["d0", "d1", "d2"]) == want          # decode steps seen once or twice: mostly eager
+    assert by_device(["e0", "e1", "e2"]) == want          # replayed from the captured graph
+    assert core.step.graph_launches > 0

@@ -64,6 +64,15 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, resid: torch.Tensor, er
            "embed_gather")
 
 
+def feed_tokens(ids: torch.Tensor, feed: torch.Tensor, sampled: torch.Tensor, err: torch.Tensor) -> None:
+    """ids[t] = sampled[feed[t]] wherever feed[t] >= 0 (all int32, on the device)."""
+    _want(ids, torch.int32, "ids"); _want(feed, torch.int32, "feed"); _want(sampled, torch.int32, "sampled")
+    if feed.numel() < ids.numel():
+        raise KernelError("feed is shorter than ids")
+    _check(library().tk_feed_tokens(ids.data_ptr(), feed.data_ptr(), sampled.data_ptr(), ids.numel(),
+                                    sampled.numel(), err.data_ptr(), _stream()), "feed_tokens")
+
+
 def add_rmsnorm(resid: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor,
                 out: torch.Tensor, eps: float, rows: torch.Tensor | None = None) -> None:
     """x = resid (+ delta), written back unless ``rows`` is given; out = weight * x * rsqrt(mean x^2 + eps).

@@ -20,11 +20,23 @@ import torch
 from ..sampling.params import SamplingParams
 from .core import EngineCore
 from .outputs import RequestOutput
-from .scheduler import Scheduler, StepPlan
+from dataclasses import dataclass
+
+from ..cache.manager import OutOfPagesError
+from .scheduler import PlannedEntry, Scheduler, StepPlan
 from .sequence import Sequence
-from .step import SamplingRow, StepEntry
+from .step import PendingStep, SamplingRow, StepEntry
 
 logger = logging.getLogger(__name__)
+
+
+@dataclass
+class _Flight:
+    """A step that has been launched and not read yet."""
+
+    plan: StepPlan
+    pending: PendingStep
+    samplers: list          # the sequences that sample in it, in the order of its sampled tokens
 
 
 def parse_attention_policy(spec: str) -> int | None:
@@ -149,27 +161,42 @@ class LLM:
                  "mixed_steps": 0, "decode_steps": 0, "decode_step_time_s": 0.0,
                  "decode_step_tokens": 0, "decode_step_times": []}
         try:
-            while scheduler.has_unfinished():
-                t_step = time.perf_counter()
-                plan = scheduler.schedule()
-                if plan is None:
-                    raise RuntimeError("scheduler returned no work but is unfinished")
-                done = self._step(plan)
+            flight = None                    # the launched step whose tokens have not been read
+            mark = time.perf_counter()       # when the device last became free for a new step
+            while flight is not None or scheduler.has_unfinished():
+                if flight is None:
+                    mark = time.perf_counter()
+                    plan = scheduler.schedule()
+                    if plan is None:
+                        raise RuntimeError("scheduler returned no work but is unfinished")
+                    flight = self._launch(plan, None)
+                # the step after a step of single next tokens is known but for the tokens, which
+                # stay on the device: it is launched before this step's tokens are read
+                ahead = None
+                plan_ahead = self._plan_ahead(scheduler, flight)
+                if plan_ahead is not None:
+                    ahead = self._launch(plan_ahead, flight)
+                done = self._complete(flight, ahead)
+                plan = flight.plan
                 stats["steps"] += 1
                 stats["tokens_run"] += plan.num_tokens
                 n_dec = sum(1 for e in plan.entries if e.count == 1 and e.start > 0)
                 stats["decode_tokens"] += n_dec
                 stats["prefill_tokens"] += plan.num_tokens - n_dec
                 stats["mixed_steps"] += int(0 < n_dec < len(plan.entries))
+                now = time.perf_counter()
                 if n_dec == len(plan.entries):
-                    # a step of single next tokens only, timed from planning to tokens on the host
-                    dt = time.perf_counter() - t_step
+                    # a step of single next tokens only, timed from the moment the device was free
+                    # for it (planning, or the end of the step before it) to its tokens on the host
+                    dt = now - mark
                     stats["decode_steps"] += 1
                     stats["decode_step_time_s"] += dt
                     stats["decode_step_tokens"] += n_dec
                     stats["decode_step_times"].append(dt)
+                mark = now
                 if bar is not None:
                     bar.update(done)
+                flight = ahead
         finally:
             for seq in sequences:
                 self.cache_manager.free(seq.seq_id)
@@ -180,31 +207,79 @@ class LLM:
         return [self._to_output(seq, prompt_texts[seq.seq_id] if prompt_texts else None)
                 for seq in sequences]
 
-    def _step(self, plan: StepPlan) -> int:
-        """Run one planned step, append the sampled tokens and free what finished."""
-        entries, rows, samplers = [], [], []
+    def _launch(self, plan: StepPlan, fed_by: "_Flight | None") -> "_Flight":
+        """Start one planned step.  With ``fed_by`` (the step before it, not yet read) every
+        entry is the next single token of a sequence that sampled in that step."""
+        entries, rows, samplers, feed = [], [], [], []
+        place = {id(seq): i for i, seq in enumerate(fed_by.samplers)} if fed_by is not None else {}
         for e in plan.entries:
-            toks = e.seq.tokens_from(e.start, e.count)
-            entries.append(StepEntry(e.seq.seq_id, toks, [e.count - 1] if e.samples else []))
-            if e.samples:
-                p = e.seq.sampling_params
+            p = e.seq.sampling_params
+            if fed_by is not None:
+                # the token is still on the device: a placeholder here, its place in the feed
+                entries.append(StepEntry(e.seq.seq_id, [0], [0]))
+                feed.append(place[id(e.seq)])
                 rows.append(SamplingRow(p.temperature, p.top_k, p.top_p, e.seq.seed,
-                                        e.seq.num_output_tokens))
+                                        e.seq.num_output_tokens + 1))
                 samplers.append(e.seq)
-        tokens = self.core.step.run_and_sample(entries, rows)
-        now = time.perf_counter()
-        for e in plan.entries:
+            else:
+                toks = e.seq.tokens_from(e.start, e.count)
+                entries.append(StepEntry(e.seq.seq_id, toks, [e.count - 1] if e.samples else []))
+                if e.samples:
+                    rows.append(SamplingRow(p.temperature, p.top_k, p.top_p, e.seq.seed,
+                                            e.seq.num_output_tokens))
+                    samplers.append(e.seq)
             e.seq.num_computed = e.start + e.count
+        pending = self.core.step.launch_and_sample(entries, rows, feed if fed_by is not None else None)
+        return _Flight(plan, pending, samplers)
+
+    def _plan_ahead(self, scheduler: Scheduler, flight: "_Flight") -> StepPlan | None:
+        """The step after ``flight`` if it is certain but for the token values: ``flight`` is a
+        step of single next tokens of every running sequence, nothing waits for admission, and
+        the pages for one more token are there.  Sequences that reach their length limit in
+        ``flight`` drop out; one that turns out to have stopped on an end-of-sequence token is
+        in the step for nothing, and its token is thrown away."""
+        plan = flight.plan
+        if any(e.count != 1 or not e.samples for e in plan.entries):
+            return None
+        going = [e for e in plan.entries if not e.seq.is_finished]
+        if scheduler.waiting or len(going) != sum(1 for s in scheduler.running if not s.is_finished):
+            return None
+        entries = []
+        for e in going:
+            seq = e.seq
+            if (seq.num_output_tokens + 1 >= seq.sampling_params.max_new_tokens
+                    or seq.num_tokens + 1 >= self._max_total_tokens(seq)):
+                continue
+            entries.append(PlannedEntry(seq, e.start + 1, 1, samples=True))
+        if not entries:
+            return None
+        try:
+            for e in entries:
+                self.cache_manager.grow(e.seq.seq_id, e.start + 1)
+        except OutOfPagesError:
+            return None         # the scheduler decides who gives way, once this step has been read
+        return StepPlan(entries)
+
+    def _complete(self, flight: "_Flight", ahead: "_Flight | None") -> int:
+        """Read a step's tokens, append them and free what finished."""
+        tokens = self.core.step.collect(flight.pending)
+        now = time.perf_counter()
+        in_ahead = {id(s) for s in ahead.samplers} if ahead is not None else set()
         finished = 0
-        for seq, token in zip(samplers, tokens):
+        for seq, token in zip(flight.samplers, tokens):
+            if seq.is_finished:
+                # it stopped in the step before, while this one was already running
+                self.cache_manager.free(seq.seq_id)
+                continue
             done = seq.append_checked(int(token), eos_token_ids=self.model_config.eos_token_ids,
                                       max_total_tokens=self._max_total_tokens(seq))
             if seq.first_token_time is None:
                 seq.first_token_time = now
             if done:
                 seq.finish_time = now
-                self.cache_manager.free(seq.seq_id)
                 finished += 1
+                if id(seq) not in in_ahead:
+                    self.cache_manager.free(seq.seq_id)
         return finished
 
     # ---- helpers ------------------------------------------------------------------------------

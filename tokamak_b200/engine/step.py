@@ -86,6 +86,15 @@ class StepBatch:
     scratch: dict = field(default_factory=dict)     # per-step values that parts share (e.g. plans)
 
 
+@dataclass
+class PendingStep:
+    """A launched step whose sampled tokens have not been read yet (see ``StepFunction.collect``)."""
+
+    n_want: int
+    host: torch.Tensor          # pinned: error word, then the sampled tokens
+    done: torch.cuda.Event
+
+
 class StepBuffers:
     """Pinned host staging and its device twin for the integers that describe a step.
 
@@ -97,14 +106,16 @@ class StepBuffers:
 
     def __init__(self, device: torch.device, max_tokens: int, max_reqs: int):
         self.device = device
-        self.capacity = 8 * max_reqs + 11 * max_tokens + 64
+        self.capacity = 8 * max_reqs + 12 * max_tokens + 64
         self.hosts = [torch.zeros(self.capacity, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
         self.events: list = [None] * self.RING
         self.turn = 0
         self.dev = torch.zeros(self.capacity, dtype=torch.int32, device=device)
         # error word and sampled tokens travel back together
         self.result = torch.zeros(4 + max_tokens, dtype=torch.int32, device=device)
-        self.result_host = torch.zeros(4 + max_tokens, dtype=torch.int32).pin_memory()
+        self.result_hosts = [torch.zeros(4 + max_tokens, dtype=torch.int32).pin_memory()
+                             for _ in range(self.RING)]
+        self.result_turn = 0
 
     def upload(self, arrays: list[np.ndarray]) -> list[torch.Tensor]:
         """Copy the arrays (int32 views) to the device in one transfer; returns device views."""
@@ -161,9 +172,13 @@ class StepFunction:
         return self.manager.length(req_id)
 
     # ---- the step ----------------------------------------------------------------------
-    def build(self, entries: Sequence[StepEntry],
-              sampling: Sequence[SamplingRow] | None = None) -> tuple[StepBatch, dict]:
-        """Reserve pages, lay the batch out and upload its description."""
+    def build(self, entries: Sequence[StepEntry], sampling: Sequence[SamplingRow] | None = None,
+              feed: Sequence[int] | None = None) -> tuple[StepBatch, dict]:
+        """Reserve pages, lay the batch out and upload its description.
+
+        ``feed`` (with ``sampling`` only) has one number per entry: the place among the previous
+        step's sampled tokens whose token is this entry's single token, or -1 for an entry that
+        brings its tokens itself."""
         if not entries:
             raise ValueError("a step needs at least one entry")
         seen = set()
@@ -218,8 +233,17 @@ class StepFunction:
         cat = lambda parts: np.concatenate(parts) if parts else np.zeros(0, dtype=np.int32)
         arrays = []
         if sampling is not None:
+            feed_tok = np.full(n_tokens, -1, dtype=np.int32)
+            if feed is not None:
+                if len(feed) != len(entries):
+                    raise ValueError(f"{len(feed)} feed places for {len(entries)} entries")
+                for r, f in enumerate(feed):
+                    if f >= 0:
+                        if q_len[r] != 1:
+                            raise ValueError("only an entry of one token can take it from the previous step")
+                        feed_tok[q_start[r]] = f
             seeds = np.asarray([s.seed & 0x7FFFFFFFFFFFFFFF for s in sampling], dtype=np.int64)
-            arrays += [seeds.view(np.int32),
+            arrays += [seeds.view(np.int32), feed_tok,     # the 64-bit seeds first: they need an even offset
                        np.asarray([s.temperature for s in sampling], dtype=np.float32).view(np.int32),
                        np.asarray([s.top_p for s in sampling], dtype=np.float32).view(np.int32),
                        i32([s.top_k for s in sampling]), i32([s.counter for s in sampling])]
@@ -238,9 +262,10 @@ class StepFunction:
         views = self.buffers.upload(arrays)
         samp = {}
         if sampling is not None:
-            samp = {"seed": views[0].view(torch.int64), "temperature": views[1].view(torch.float32),
-                    "top_p": views[2].view(torch.float32), "top_k": views[3], "counter": views[4]}
-            views = views[5:]
+            samp = {"feed": views[1], "fed": feed is not None,
+                    "seed": views[0].view(torch.int64), "temperature": views[2].view(torch.float32),
+                    "top_p": views[3].view(torch.float32), "top_k": views[4], "counter": views[5]}
+            views = views[6:]
         self.cache.sync()
         batch = StepBatch(
             n_tokens=n_tokens, n_reqs=len(entries), n_want=W,
@@ -268,16 +293,26 @@ class StepFunction:
             self.check_errors()
         return logits
 
-    @torch.inference_mode()
     def run_and_sample(self, entries: Sequence[StepEntry], sampling: Sequence[SamplingRow]) -> list[int]:
-        """One token per wanted place, sampled on the device; one copy back for tokens and errors.
+        """One token per wanted place, sampled on the device; one copy back for tokens and errors."""
+        return self.collect(self.launch_and_sample(entries, sampling))
+
+    @torch.inference_mode()
+    def launch_and_sample(self, entries: Sequence[StepEntry], sampling: Sequence[SamplingRow],
+                          feed: Sequence[int] | None = None) -> PendingStep:
+        """Start a step that samples one token per wanted place on the device; ``collect`` reads them.
 
         A step in which every request brings exactly one token and wants it sampled has the
         same launches every time, so it is captured into a CUDA graph the second time its shape
         (batch size, bucket of the longest context) is seen and replayed from then on: the
         description of the step is uploaded outside the graph into buffers at fixed addresses.
+
+        With ``feed`` (see ``build``) single tokens come from the previous step's sampled tokens
+        on the device, so the step can be launched before that step has been collected: the
+        device then never waits for the host between two steps.  At most two launched steps may
+        be waiting to be collected, and they are collected in the order of their launch.
         """
-        batch, samp = self.build(entries, sampling)
+        batch, samp = self.build(entries, sampling, feed)
         W = batch.n_want
         res = self.buffers.result
         graphable = (self.use_graphs and batch.max_q_len == 1 and W == batch.n_tokens)
@@ -297,16 +332,26 @@ class StepFunction:
                 self._graph_seen[key] = self._graph_seen.get(key, 0) + 1
                 graphable = False
         if not graphable:
+            if samp["fed"]:
+                ops.feed_tokens(batch.token_ids, samp["feed"], res[4:], batch.err)
             logits = self.model.forward(batch)
             if W:
                 ops.sample(logits, samp["temperature"], samp["top_k"], samp["top_p"], samp["seed"],
                            samp["counter"], res[4:4 + W])
         self.finish(entries)
-        host = self.buffers.result_host
+        bufs = self.buffers
+        host = bufs.result_hosts[bufs.result_turn]
+        bufs.result_turn = (bufs.result_turn + 1) % bufs.RING
         host[:4 + W].copy_(res[:4 + W], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        self._raise_on_error(host[:4].tolist())
-        return host[4:4 + W].tolist()
+        done = torch.cuda.Event()
+        done.record()
+        return PendingStep(W, host, done)
+
+    def collect(self, pending: PendingStep) -> list[int]:
+        """Wait for a launched step and return its sampled tokens; raises on a kernel error."""
+        pending.done.synchronize()
+        self._raise_on_error(pending.host[:4].tolist())
+        return pending.host[4:4 + pending.n_want].tolist()
 
     def _capture(self, key, batch: StepBatch, samp: dict) -> dict:
         """Record the decode step of this shape; its launches are replayed, not run, here."""
@@ -317,6 +362,8 @@ class StepFunction:
         before = ops.LAUNCHES
         torch.cuda.synchronize()
         with torch.cuda.graph(graph, pool=self._graph_pool):
+            # tokens that the previous step sampled (feed >= 0) take their places first
+            ops.feed_tokens(batch.token_ids, samp["feed"], self.buffers.result[4:], batch.err)
             logits = self.model.forward(batch)
             ops.sample(logits, samp["temperature"], samp["top_k"], samp["top_p"], samp["seed"],
                        samp["counter"], self.buffers.result[4:4 + W])
