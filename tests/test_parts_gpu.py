@@ -1,5 +1,6 @@
-"""Each part of a layer alone against the plain functions, the schedule as data, and a toy
-mixer with state of its own that is registered, built and stepped from the test alone."""
+"""Each part of a layer alone against the plain functions, the schedule as data, and toy parts
+that are registered, built and stepped from the test alone: a mixer with state of its own, a
+feed-forward with routing and another position encoding."""
 
 from __future__ import annotations
 
@@ -349,3 +350,189 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
             assert not core.manager.live_requests()
     finally:
         MIXERS.unregister("toy_decay_sum")
+
+
+# ----------------------------------------------------------------------------- more toy parts
+
+@dataclass(frozen=True)
+class ScaledPartialRopeSpec:
+    """A position encoding of the test's own: only the first ``rotary_dim`` elements of a head
+    are rotated, at angle (position / factor) * theta ** (-2j / rotary_dim)."""
+    rotary_dim: int
+    theta: float
+    factor: float
+    kind: str = "toy_scaled_partial_rope"
+
+
+class ScaledPartialRope:
+    def __init__(self, spec, rt):
+        self.spec = spec
+        j = torch.arange(0, spec.rotary_dim, 2, dtype=torch.float32, device=rt.device)
+        self.inv_freq = 1.0 / (spec.theta ** (j / spec.rotary_dim))
+
+    def rotary_table(self, step):
+        key = ("toy_rope", self.spec)
+        if key not in step.scratch:
+            ang = (step.positions.float() / self.spec.factor)[:, None] * self.inv_freq[None, :]
+            step.scratch[key] = torch.stack((ang.cos(), ang.sin()), dim=-1).contiguous()
+        return step.scratch[key], self.spec.rotary_dim
+
+
+@dataclass(frozen=True)
+class Top1ExpertsSpec:
+    """A feed-forward with routing: float32 router logits, the best expert of every token runs
+    (a SwiGLU of its own), scaled by the router's softmax probability of that expert."""
+    hidden_size: int
+    intermediate_size: int
+    num_experts: int
+    kind: str = "toy_top1_experts"
+
+
+class Top1Experts:
+    def __init__(self, spec, prefix, tensors, rt):
+        self.spec = spec
+        self.router = tensors[prefix + "router.weight"]                 # float32 (role "vector")
+        self.w = [{n: tensors[f"{prefix}experts.{e}.{n}.weight"] for n in ("gate", "up", "down")}
+                  for e in range(spec.num_experts)]
+
+    @staticmethod
+    def expected_tensors(spec, prefix):
+        from tokamak_b200.parts.base import TensorReq
+        h, i = spec.hidden_size, spec.intermediate_size
+        out = {prefix + "router.weight": TensorReq((spec.num_experts, h), role="vector")}
+        for e in range(spec.num_experts):
+            out[f"{prefix}experts.{e}.gate.weight"] = TensorReq((i, h))
+            out[f"{prefix}experts.{e}.up.weight"] = TensorReq((i, h))
+            out[f"{prefix}experts.{e}.down.weight"] = TensorReq((h, i))
+        return out
+
+    def forward(self, h, step):
+        from tokamak_b200.parts.base import linear
+        logits = h.float() @ self.router.t()                            # router logits in 32-bit
+        prob, choice = torch.softmax(logits, dim=-1).max(dim=-1)
+        out = torch.zeros_like(h, dtype=torch.float32)
+        for e, w in enumerate(self.w):
+            rows = (choice == e).nonzero().flatten()
+            if rows.numel() == 0:
+                continue
+            x = h[rows]
+            g, u = linear(x, w["gate"]).float(), linear(x, w["up"]).float()
+            y = linear((g * torch.sigmoid(g) * u).to(h.dtype), w["down"]).float()
+            out[rows] = y * prob[rows, None]
+        return out.to(h.dtype)
+
+
+ROUTED_CONFIG = {"architectures": ["ToyRoutedForCausalLM"], "vocab_size": 97, "hidden_size": 40,
+                 "heads": 4, "kv_heads": 2, "head_dim": 24, "rotary_dim": 12, "factor": 4.0, "inter": 48,
+                 "experts": 3, "eps": 1e-5, "theta": 500.0, "max_position_embeddings": 256}
+
+
+def _routed_architecture():
+    from tokamak_b200.config import Architecture
+    from tokamak_b200.models.decoder import LayerCall, ModelSpec
+    from tokamak_b200.parts.attention import AttentionSpec
+    from tokamak_b200.parts.block import PreNormBlockSpec
+    from tokamak_b200.parts.embedding import EmbeddingSpec, HeadSpec
+    from tokamak_b200.parts.feedforward import SwiGLUSpec
+    from tokamak_b200.parts.norm import RMSNormSpec
+
+    @dataclass(frozen=True)
+    class Config:
+        raw: tuple
+        architecture: str = "ToyRoutedForCausalLM"
+        eos_token_ids: tuple = ()
+
+        def __getattr__(self, name):
+            return dict(self.raw)[name]
+
+    def parse_config(raw, eos_token_ids=None):
+        return Config(tuple((k, v) for k, v in raw.items() if k != "architectures"))
+
+    def model_spec(cfg):
+        H, norm = cfg.hidden_size, RMSNormSpec(cfg.hidden_size, cfg.eps)
+        pos = ScaledPartialRopeSpec(cfg.rotary_dim, cfg.theta, cfg.factor)
+        attn = AttentionSpec(H, cfg.heads, cfg.kv_heads, cfg.head_dim, pos, qk_norm_eps=cfg.eps)
+        blocks = (
+            PreNormBlockSpec("l0", norm, attn, norm, Top1ExpertsSpec(H, cfg.inter, cfg.experts),
+                             "l0.n1", "l0.attn.", "l0.n2", "l0.moe."),
+            PreNormBlockSpec("l1", norm, attn, norm, SwiGLUSpec(H, cfg.inter), "l1.n1", "l1.attn.", "l1.n2",
+                             "l1.mlp."),
+        )
+        return ModelSpec(EmbeddingSpec(cfg.vocab_size, H, "embed"), blocks,
+                         (LayerCall("l0", "l0"), LayerCall("l1", "l1")), norm, "final",
+                         HeadSpec(cfg.vocab_size, H, tied=True, name="head"))
+
+    return Architecture("ToyRoutedForCausalLM", parse_config, model_spec)
+
+
+def _routed_plain_logits(folder, ids):
+    cfg, w = plain.load_folder(folder)
+    w = {k: v.double() for k, v in w.items()}
+    T, eps, d, rot = len(ids), cfg["eps"], cfg["head_dim"], cfg["rotary_dim"]
+    ang = (torch.arange(T, dtype=torch.float64) / cfg["factor"])[:, None] * \
+        (1.0 / cfg["theta"] ** (torch.arange(0, rot, 2, dtype=torch.float64) / rot))[None, :]
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+
+    def rope(x):                                    # [T, heads, d]: the first `rot` elements rotate by halves
+        a, b, rest = x[..., :rot // 2], x[..., rot // 2:rot], x[..., rot:]
+        return torch.cat((a * cos - b * sin, b * cos + a * sin, rest), dim=-1)
+
+    def attn(x, n):
+        q = (x @ w[f"{n}.attn.q_proj.weight"].T).view(T, cfg["heads"], d)
+        k = (x @ w[f"{n}.attn.k_proj.weight"].T).view(T, cfg["kv_heads"], d)
+        v = (x @ w[f"{n}.attn.v_proj.weight"].T).view(T, cfg["kv_heads"], d)
+        q = rope(plain.rms_norm(q, w[f"{n}.attn.q_norm.weight"], eps))
+        k = rope(plain.rms_norm(k, w[f"{n}.attn.k_norm.weight"], eps))
+        return plain.causal_attention(q, k, v).reshape(T, -1) @ w[f"{n}.attn.o_proj.weight"].T
+
+    x = w["embed"][torch.tensor(ids)]
+    x = x + attn(plain.rms_norm(x, w["l0.n1"], eps), "l0")
+    h = plain.rms_norm(x, w["l0.n2"], eps)
+    prob, choice = torch.softmax(h @ w["l0.moe.router.weight"].T, dim=-1).max(dim=-1)
+    y = torch.stack([plain.swiglu_mlp(h[t:t + 1], w[f"l0.moe.experts.{int(e)}.gate.weight"],
+                                      w[f"l0.moe.experts.{int(e)}.up.weight"],
+                                      w[f"l0.moe.experts.{int(e)}.down.weight"])[0] * prob[t]
+                     for t, e in enumerate(choice)])
+    x = x + y
+    x = x + attn(plain.rms_norm(x, w["l1.n1"], eps), "l1")
+    x = x + plain.swiglu_mlp(plain.rms_norm(x, w["l1.n2"], eps), w["l1.mlp.gate_proj.weight"],
+                             w["l1.mlp.up_proj.weight"], w["l1.mlp.down_proj.weight"])
+    return plain.rms_norm(x, w["final"], eps) @ w["embed"].T, choice
+
+
+def test_toy_routed_feed_forward_and_toy_position_encoding(tmp_path):
+    """A feed-forward with routing and a position encoding that rotates a part of the head at
+    scaled positions, both defined here, are registered, chosen layer by layer by a toy
+    architecture, built from a folder that the framework's writer made, and replayed whole, in
+    portions and mixed through the ordinary engine.  No file of the framework knows them."""
+    from tokamak_b200.config import register_architecture
+    from tokamak_b200.engine.replay import build_core, run_step
+    from tokamak_b200.parts.base import FEED_FORWARDS, POSITIONS
+    from tokamak_b200.weights import write_random_model
+
+    FEED_FORWARDS.register("toy_top1_experts")(Top1Experts)
+    POSITIONS.register("toy_scaled_partial_rope")(ScaledPartialRope)
+    register_architecture(_routed_architecture())
+    try:
+        folder = write_random_model(tmp_path / "routed", ROUTED_CONFIG, seed=11, std=0.3, dtype="float32")
+        reqs = {f"m{i}": random_tokens(97, n, seed=70 + i) for i, n in enumerate([12, 33, 64, 21, 47])}
+        truth, used = {}, set()
+        for rid, ids in reqs.items():
+            truth[rid], choice = _routed_plain_logits(folder, ids)
+            used |= set(choice.tolist())
+        assert used == {0, 1, 2}, "the workload should reach every expert"
+        for builder, kw in ((traces.whole, {}), (traces.tail_one_by_one, {}), (traces.portions, {}),
+                            (traces.mixed, {"max_tokens": 192, "max_live": 3, "seed": 5})):
+            core = build_core(folder, "float32", 192, page_size=16, max_live=3)
+            records, rows = builder(reqs, **kw)
+            for rec in records:
+                out = run_step(core, rec)
+                if out is None:
+                    continue
+                got = torch.from_numpy(out)
+                want = torch.stack([truth[rid][p] for rid, p in rows[rec["step"]]])
+                assert_logits_close(got, want, "float32", f"routed {builder.__name__} step {rec['step']}")
+            assert not core.manager.live_requests()
+    finally:
+        FEED_FORWARDS.unregister("toy_top1_experts")
+        POSITIONS.unregister("toy_scaled_partial_rope")
