@@ -240,26 +240,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
   if (p.epilogue == kGtEpiSwiglu) {
     cluster_sync_all();                    // every block of the cluster has staged its partial
     if (warp >= 2) {
-      // thread -> output j of the tile's 64 and one of two column phases; gate in tile row j,
-      // up in tile row 64 + j; the sum over the ranks runs in the same order as without the
-      // activation, and the activation is the formula of the separate kernel
+      // thread -> four neighbouring outputs of the tile's 64 and one of eight column phases; gate
+      // in tile rows j.., up in tile rows 64 + j..; the sum over the ranks runs in the same order
+      // as without the activation, and the activation is the formula of the separate kernel
       const int csize = p.cluster_reduce > 1 ? p.cluster_reduce : 1;
       const uint32_t my_rank = p.cluster_reduce > 1 ? cluster_ctarank() : 0u;
       const int t = (warp - 2) * 32 + lane;
-      const int j = t & 63, phase = t >> 6;
+      const int j4 = (t & 15) * 4, phase = t >> 4;
       const int inter = p.rows_total >> 1;
-      const int oc = tile_r * 64 + j;
+      const int oc = tile_r * 64 + j4;
       __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out);
-      if (oc < inter) {
-        for (int c = (int)my_rank + csize * phase; c < p.bn; c += 2 * csize) {
+      if (oc < inter) {                    // inter is a multiple of 64: all four outputs exist
+        for (int c = (int)my_rank + csize * phase; c < p.bn; c += 8 * csize) {
           const int col = tile_c * p.bn + c;
           if (col >= p.cols_total) break;
-          float g = 0.0f, u = 0.0f;
+          float4 g = make_float4(0.0f, 0.0f, 0.0f, 0.0f), u = g;
           for (int rk = 0; rk < csize; ++rk) {
-            g += ld_cluster_f32(base + (uint32_t)((c * kGtBM + j) * 4), (uint32_t)rk);
-            u += ld_cluster_f32(base + (uint32_t)((c * kGtBM + 64 + j) * 4), (uint32_t)rk);
+            const float4 a = ld_cluster_f32x4(base + (uint32_t)((c * kGtBM + j4) * 4), (uint32_t)rk);
+            const float4 b = ld_cluster_f32x4(base + (uint32_t)((c * kGtBM + 64 + j4) * 4), (uint32_t)rk);
+            g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
+            u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
           }
-          out[(size_t)col * inter + oc] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+          uint2 packed;
+          *reinterpret_cast<__nv_bfloat162*>(&packed.x) =
+              __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+          *reinterpret_cast<__nv_bfloat162*>(&packed.y) =
+              __floats2bfloat162_rn(g.z / (1.0f + expf(-g.z)) * u.z, g.w / (1.0f + expf(-g.w)) * u.w);
+          *reinterpret_cast<uint2*>(out + (size_t)col * inter + oc) = packed;
         }
       }
     }
@@ -268,22 +275,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
     cluster_sync_all();                    // every block of the cluster has staged its partial
     if (warp >= 2) {
       // every block of the cluster adds up its share of the columns (tokens): column c belongs
-      // to rank c mod cluster size; the order of the sum over the ranks is always the same
+      // to rank c mod cluster size; a thread takes four neighbouring rows of one column; the
+      // order of the sum over the ranks is always the same
       const uint32_t my_rank = cluster_ctarank();
-      const int quarter = warp & 3;
-      const int row = tile_r * kGtBM + quarter * 32 + lane;
-      const uint32_t stage = base;         // the staging area starts where the ring of stages did
+      const int t = (warp - 2) * 32 + lane;
+      const int r4 = (t & 31) * 4, phase = t >> 5;
+      const int row = tile_r * kGtBM + r4;
+      const bool vec = (p.rows_total & 3) == 0;
       float* out = reinterpret_cast<float*>(p.out) +
                    (size_t)(split / p.cluster_reduce) * p.cols_total * p.rows_total;
       if (row < p.rows_total) {
-        for (int c = (int)my_rank; c < p.bn; c += p.cluster_reduce) {
+        for (int c = (int)my_rank + p.cluster_reduce * phase; c < p.bn; c += 4 * p.cluster_reduce) {
           const int col = tile_c * p.bn + c;
           if (col >= p.cols_total) break;
-          float sum = 0.0f;
+          float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
           for (int rk = 0; rk < p.cluster_reduce; ++rk) {
-            sum += ld_cluster_f32(stage + (uint32_t)((c * kGtBM + quarter * 32 + lane) * 4), (uint32_t)rk);
+            const float4 v = ld_cluster_f32x4(base + (uint32_t)((c * kGtBM + r4) * 4), (uint32_t)rk);
+            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
           }
-          out[(size_t)col * p.rows_total + row] = sum;
+          float* dst = out + (size_t)col * p.rows_total + row;
+          if (vec && row + 3 < p.rows_total) {
+            *reinterpret_cast<float4*>(dst) = sum;
+          } else {
+            dst[0] = sum.x;
+            if (row + 1 < p.rows_total) dst[1] = sum.y;
+            if (row + 2 < p.rows_total) dst[2] = sum.z;
+            if (row + 3 < p.rows_total) dst[3] = sum.w;
+          }
         }
       }
     }

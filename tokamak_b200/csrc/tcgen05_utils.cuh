@@ -167,6 +167,15 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t local_smem_addr, uint32
   return v;
 }
 
+__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t local_smem_addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(local_smem_addr), "r"(rank));
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];\n"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+  return v;
+}
+
 // ---- host side: the driver's tensor-map encoder, found through the runtime (no link to libcuda) ----
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
