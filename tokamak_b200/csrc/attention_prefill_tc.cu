@@ -5,10 +5,12 @@
 // tiles of 128 rows that share every key and value tile:
 //   warp 0       TMA: the query tiles once, then key and value tiles of 64 keys, page by page
 //                (cp.async.bulk.tensor, 128-byte swizzle, no multicast), into a ring of stages;
-//   warp 1       one thread issues tcgen05.mma for both query tiles: S = Q K^T (M 128, N 64)
+//                every lane looks one page up and issues one copy, so the look-ups of a stage
+//                cost one memory latency, and the next stage's are under way while it waits;
+//   warps 1, 10  one thread each issues tcgen05.mma for one query tile: S = Q K^T (M 128, N 64)
 //                into one of the tile's two score buffers in tensor memory, and O += P V
 //                (M 128, N head_dim) with V read straight from its page layout as an MN-major
-//                operand;
+//                operand (issuing is what a single thread is slow at, hence one per tile);
 //   warps 2..5   softmax of query tile 0, warps 6..9 of query tile 1: thread i owns query row
 //                i = tensor-memory lane i.  It reads its 64 scores with tcgen05.ld, masks
 //                (causal with offset kv_len - q_len, window), keeps a reference maximum and
@@ -33,7 +35,8 @@ constexpr int kAtBM = 128;            // rows of one query tile
 constexpr int kAtQT = 2;              // query tiles per block
 constexpr int kAtBN = 64;             // keys per tile
 constexpr int kAtStages = 3;
-constexpr int kAtThreads = 64 + kAtQT * 128;
+constexpr int kAtThreads = 64 + kAtQT * 128 + 32;   // TMA, MMA of tile 0, softmax warps, MMA of tile 1
+constexpr int kAtMmaWarp1 = 2 + kAtQT * 4;           // the warp that issues for query tile 1
 constexpr float kAtRescale = 8.0f;    // log2 units
 
 struct AttnTcParams {
@@ -98,7 +101,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     mbar_init(gt_smem_u32(q_full), 1);
     for (int s = 0; s < kAtStages; ++s) {
       mbar_init(gt_smem_u32(&kv_full[s]), 1);
-      mbar_init(gt_smem_u32(&kv_empty[s]), 1);
+      mbar_init(gt_smem_u32(&kv_empty[s]), kAtQT);      // one arrival per issuing warp
     }
     for (int t = 0; t < kAtQT; ++t) {
       for (int b = 0; b < 2; ++b) {
@@ -151,64 +154,77 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
   if (warp == 0) {
     // ---- TMA producer ------------------------------------------------------------------------
-    if (lane == 0 && n_kt > 0) {
+    if (n_kt > 0) {
       const int* table = p.block_table + (size_t)p.req_slot[r] * p.max_pages;
-      mbar_expect_tx(gt_smem_u32(q_full), (uint32_t)n_qt * Q_BYTES);
-      for (int t = 0; t < n_qt; ++t) {
+      if (lane == 0) {
+        mbar_expect_tx(gt_smem_u32(q_full), (uint32_t)n_qt * Q_BYTES);
+        for (int t = 0; t < n_qt; ++t) {
 #pragma unroll
-        for (int c = 0; c < SUB; ++c) {
-          tma_load_3d(q_smem + t * Q_BYTES + c * (kAtBM * 128), &map_q, c * 64, head,
-                      q_start + row0 + t * kAtBM, gt_smem_u32(q_full));
+          for (int c = 0; c < SUB; ++c) {
+            tma_load_3d(q_smem + t * Q_BYTES + c * (kAtBM * 128), &map_q, c * 64, head,
+                        q_start + row0 + t * kAtBM, gt_smem_u32(q_full));
+          }
         }
       }
+      // a stage is (64 / kpl) page parts x SUB column halves x {key, value}: one copy per lane
       const int kpl = p.page_size < kAtBN ? p.page_size : kAtBN;     // keys per load
+      const int n_loads = (kAtBN / kpl) * SUB * 2;                   // at most 32: page sizes from 8
+      const bool loader = lane < n_loads;
+      const int is_v = lane & 1, c = (lane >> 1) % SUB, u = lane / (2 * SUB);
+      auto key0_of = [&](int it) {
+        int key0 = (first_kt + it) * kAtBN + u * kpl;
+        if (key0 + kpl - 1 < lo_block || key0 > pos_last) key0 = (pos_last / kpl) * kpl;   // nothing visible here
+        return key0;
+      };
+      auto lookup = [&](int it) {
+        const int pidx = key0_of(it) / p.page_size;
+        return (loader && it < n_kt && pidx < p.max_pages) ? table[pidx] : -1;
+      };
+      int page = lookup(0);
+      bool ok = true;
       for (int it = 0; it < n_kt; ++it) {
         const int s = it % kAtStages;
         const uint32_t round = (uint32_t)(it / kAtStages);
-        if (round > 0 && !mbar_wait(gt_smem_u32(&kv_empty[s]), (round - 1) & 1u, abort_flag)) {
-          set_error(p.err, kErrWait, 10, it, s);
-          *abort_flag = 1;
-          break;
+        const int page_next = lookup(it + 1);          // under way while this stage waits and is issued
+        if (round > 0) {
+          ok = __all_sync(0xffffffffu, mbar_wait(gt_smem_u32(&kv_empty[s]), (round - 1) & 1u, abort_flag));
+          if (!ok) { if (lane == 0) { set_error(p.err, kErrWait, 10, it, s); *abort_flag = 1; } break; }
         }
         const uint32_t full = gt_smem_u32(&kv_full[s]);
-        mbar_expect_tx(full, STAGE_BYTES);
-        const uint32_t kdst = kv_smem + s * STAGE_BYTES;
-        const uint32_t vdst = kdst + KV_BYTES;
-        const int kt = first_kt + it;
-        for (int u = 0; u < kAtBN / kpl; ++u) {
-          int key0 = kt * kAtBN + u * kpl;
-          if (key0 + kpl - 1 < lo_block || key0 > pos_last) key0 = (pos_last / kpl) * kpl;   // nothing visible here
-          const int pidx = key0 / p.page_size;
-          int page = (pidx < p.max_pages) ? table[pidx] : -1;
+        if (lane == 0) mbar_expect_tx(full, STAGE_BYTES);
+        __syncwarp();
+        if (loader) {
+          const int key0 = key0_of(it);
           if (page < 0 || page >= p.num_pages) {
-            set_error(p.err, kErrPage, tile_id, pidx, page);
+            set_error(p.err, kErrPage, tile_id, key0 / p.page_size, page);
             page = 0;
           }
           const int row = (page * p.n_kv_heads + hkv) * p.page_size + (key0 % p.page_size);
-#pragma unroll
-          for (int c = 0; c < SUB; ++c) {
-            tma_load_2d(kdst + c * KSUB_BYTES + u * kpl * 128, &map_k, c * 64, row, full);
-            tma_load_2d(vdst + c * KSUB_BYTES + u * kpl * 128, &map_v, c * 64, row, full);
-          }
+          const uint32_t dst = kv_smem + s * STAGE_BYTES + (is_v ? KV_BYTES : 0u) + c * KSUB_BYTES + u * kpl * 128;
+          tma_load_2d(dst, is_v ? &map_v : &map_k, c * 64, row, full);
         }
+        page = page_next;
       }
     }
-  } else if (warp == 1) {
-    // ---- MMA issuer --------------------------------------------------------------------------
+  } else if (warp == 1 || warp == kAtMmaWarp1) {
+    // ---- MMA issuer of query tile t ------------------------------------------------------------
+    // Both issuers walk all key tiles of the block, so that each gives every stage back exactly
+    // once; a tile outside the query tile's own range gets no products.
+    const int t = warp == 1 ? 0 : 1;
     if (lane == 0 && n_kt > 0) {
       const uint32_t idesc_s = umma_idesc(kAtBN, false);
       const uint32_t idesc_o = umma_idesc(D, true);
+      const bool mine = t < n_qt;
       bool ok = mbar_wait(gt_smem_u32(q_full), 0u, abort_flag);
-      if (!ok) { set_error(p.err, kErrWait, 11, 0, 0); *abort_flag = 1; }
+      if (!ok) { set_error(p.err, kErrWait, 11, 0, t); *abort_flag = 1; }
       for (int j = 0; j <= n_kt && ok; ++j) {
         if (j < n_kt) {
           const int s = j % kAtStages;
           const int kt = first_kt + j;
           ok = mbar_wait(gt_smem_u32(&kv_full[s]), (uint32_t)(j / kAtStages) & 1u, abort_flag);
           if (!ok) { set_error(p.err, kErrWait, 12, j, s); *abort_flag = 1; break; }
-          const uint32_t k_addr = kv_smem + s * STAGE_BYTES;
-          for (int t = 0; t < n_qt && ok; ++t) {
-            if (kt < first_t[t] || kt > last_t[t]) continue;
+          if (mine && kt >= first_t[t] && kt <= last_t[t]) {
+            const uint32_t k_addr = kv_smem + s * STAGE_BYTES;
             const int jt = kt - first_t[t], b = jt & 1;
             if (jt >= 2) ok = mbar_wait(s_empty(t, b), (uint32_t)((jt >> 1) - 1) & 1u, abort_flag);
             if (!ok) { set_error(p.err, kErrWait, 18, j, t); *abort_flag = 1; break; }
@@ -222,14 +238,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             umma_commit(s_full(t, b));
           }
-          if (!ok) break;
         }
         if (j >= 1) {
           const int s = (j - 1) % kAtStages;
           const int kt = first_kt + j - 1;
-          const uint32_t v_addr = kv_smem + s * STAGE_BYTES + KV_BYTES;
-          for (int t = 0; t < n_qt && ok; ++t) {
-            if (kt < first_t[t] || kt > last_t[t]) continue;
+          if (mine && kt >= first_t[t] && kt <= last_t[t]) {
+            const uint32_t v_addr = kv_smem + s * STAGE_BYTES + KV_BYTES;
             const int jt = kt - first_t[t], b = jt & 1;
             ok = mbar_wait(p_full(t, b), (uint32_t)(jt >> 1) & 1u, abort_flag);
             if (!ok) { set_error(p.err, kErrWait, 13, j, t); *abort_flag = 1; break; }
@@ -244,8 +258,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             umma_commit(p_empty(t, b));
             if (kt == last_t[t]) umma_commit(o_full(t));
           }
-          if (!ok) break;
-          umma_commit(gt_smem_u32(&kv_empty[s]));
+          umma_commit(gt_smem_u32(&kv_empty[s]));    // this issuer is done with the stage
         }
       }
     }
