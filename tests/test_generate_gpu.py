@@ -251,3 +251,26 @@ def test_a_step_fed_on_the_device_equals_one_fed_by_the_host(dtype):
     assert by_device(["d0", "d1", "d2"]) == want          # decode steps seen once or twice: mostly eager
     assert by_device(["e0", "e1", "e2"]) == want          # replayed from the captured graph
     assert core.step.graph_launches > 0
+
+
+def test_pool_sized_from_free_memory():
+    """kv_pool_tokens="auto": the pool fills a share of the free device memory after a probe
+    step has measured what a step needs, holds whole pages, never less than one request's
+    maximum, and generation is what it is with the default pool."""
+    from tokamak_b200 import SamplingParams
+    prompts = prompts_for("A", [9, 21])
+    params = SamplingParams(temperature=0.0, max_new_tokens=6)
+    want = [o.output_token_ids for o in llm_for("A", "float32").generate(prompt_token_ids=prompts,
+                                                                         sampling_params=params)]
+    free, _ = torch.cuda.mem_get_info()
+    share = 256e6 / free                                     # about 256 MB of pages
+    llm = llm_for("A", "float32", kv_pool_tokens="auto", gpu_memory_utilization=share, max_seq_len=128)
+    group = llm.cache_manager.kv_groups[0]
+    per_token = llm.core.cache.bytes_per_token()
+    assert group.num_pages * group.page_size >= 128
+    assert 0.5 * 256e6 < group.num_pages * group.page_size * per_token <= 256e6
+    assert [o.output_token_ids for o in llm.generate(prompt_token_ids=prompts, sampling_params=params)] == want
+    tiny = llm_for("A", "float32", kv_pool_tokens="auto", gpu_memory_utilization=1e-9, max_seq_len=128)
+    assert tiny.cache_manager.kv_groups[0].num_pages * tiny.cache_manager.kv_groups[0].page_size >= 128
+    with pytest.raises(ValueError, match="'auto'"):
+        llm_for("A", "float32", kv_pool_tokens="most")

@@ -56,3 +56,41 @@ def test_8b_layer_sizes_under_every_cut(model_8b_sizes, dtype):
             want = torch.stack([truth[rid][p] for rid, p in rows[rec["step"]]])
             assert_logits_close(got, want, dtype, f"8B sizes {builder.__name__} step {rec['step']}")
         assert not core.manager.live_requests()
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_pages_beyond_four_gib_are_addressed_right(model_8b_sizes, dtype):
+    """A pool whose per-layer key view alone is larger than 4 GiB, with every low page taken
+    away first: the requests live in the last pages, more than 2^32 bytes and 2^31 elements into
+    the view, and prefill, portions and decoding give the logits of the plain implementation."""
+    from tokamak_b200.engine.core import EngineCore
+    from tokamak_b200.engine.replay import run_step
+    raw, tensors, cpu = model_8b_sizes
+    elem = 2 if dtype == "bfloat16" else 4
+    pool_tokens = 2_359_296 * 2 // elem           # 1024 key elements per token and layer: 4.5 GiB per view
+    need = 4 * pool_tokens * 1024 * elem + (8 << 30)
+    if torch.cuda.mem_get_info()[0] < need:
+        pytest.skip("not enough free device memory for a pool beyond 4 GiB per view")
+    dt = torch.float32 if dtype == "float32" else torch.bfloat16
+    mine = {k: (v.float() if v.dim() == 1 else v.to(dt)) for k, v in tensors.items()}
+    core = EngineCore("<random>", dtype=dtype, tensors=mine, raw_config=raw, max_seq_len=512,
+                      page_size=16, pool_tokens=pool_tokens, max_slots=4, max_step_tokens=512)
+    view = core.cache.view(next(iter(core.model.cache_needs())))
+    assert view.k.numel() * view.k.element_size() > (1 << 32)
+    assert dtype == "float32" or view.k.numel() > (1 << 31)
+    for g in core.manager.kv_groups:
+        g.allocator.take(g.num_free - 64)         # held by nobody's table: only the last 64 pages are left
+    reqs = {"a": random_tokens(raw["vocab_size"], 300, seed=5), "b": random_tokens(raw["vocab_size"], 90, seed=6)}
+    truth = {rid: plain.forward_logits(raw, cpu, ids, torch.float64) for rid, ids in reqs.items()}
+    for builder, kw in ((traces.whole, {}), (traces.tail_one_by_one, {"tail": 8}),
+                        (traces.mixed, {"max_tokens": 512, "max_live": 2, "seed": 3})):
+        records, rows = builder(reqs, **kw)
+        for rec in records:
+            out = run_step(core, rec)
+            if out is None:
+                continue
+            want = torch.stack([truth[rid][p] for rid, p in rows[rec["step"]]])
+            assert_logits_close(torch.from_numpy(out), want, dtype, f"high pages {builder.__name__} {rec['step']}")
+        assert not core.manager.live_requests()
+    del core
+    torch.cuda.empty_cache()

@@ -33,7 +33,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--dtype", default="auto", choices=["auto", "bfloat16", "float32"])
     ap.add_argument("--max-seq-len", type=int, default=None)
     ap.add_argument("--block-size", type=int, default=16)
-    ap.add_argument("--kv-pool-tokens", type=int, default=None)
+    ap.add_argument("--kv-pool-tokens", type=lambda v: v if v == "auto" else int(v), default=None,
+                    help="tokens the page pool holds (default: max-seq-len), or 'auto' to fill the free memory")
+    ap.add_argument("--gpu-memory-utilization", type=float, default=0.9)
     ap.add_argument("--max-batch-size", type=int, default=16)
     ap.add_argument("--max-num-batched-tokens", type=int, default=2048)
     ap.add_argument("--prefill-chunk", type=int, default=None)
@@ -65,6 +67,7 @@ def main(argv: list[str] | None = None) -> int:
 
     llm = LLM(args.model, dtype=args.dtype, max_seq_len=args.max_seq_len, block_size=args.block_size,
               kv_pool_tokens=args.kv_pool_tokens, max_batch_size=args.max_batch_size,
+              gpu_memory_utilization=args.gpu_memory_utilization,
               max_num_batched_tokens=args.max_num_batched_tokens, prefill_chunk=args.prefill_chunk,
               attention_policy=args.attention_policy)
     params = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,

@@ -56,7 +56,10 @@ class EngineCore:
         page_size: positions per cache page (``block_size`` of the reference).
         pool_tokens: positions the page pool of every layer group holds; at least
             ``max_seq_len`` so that any single request can finish alone
-            (src/tokamak/engine/llm.py:157-163).
+            (src/tokamak/engine/llm.py:157-163), which is also the default.  ``"auto"`` sizes
+            the pool from the device memory that is free once the weights are loaded:
+            ``memory_utilization`` of it, less room for the activations of the largest step.
+        memory_utilization: share of the free device memory that ``pool_tokens="auto"`` may use.
         max_slots: most requests that are live at a time.
         max_step_tokens: most tokens of one step.
         tensors, raw_config: weights and configuration given directly instead of read from
@@ -66,9 +69,10 @@ class EngineCore:
 
     def __init__(self, model: str | Path, *, dtype: str | torch.dtype = "bfloat16",
                  device: str | torch.device = "cuda", max_seq_len: int | None = None,
-                 page_size: int = 16, pool_tokens: int | None = None, max_slots: int = 16,
+                 page_size: int = 16, pool_tokens: int | str | None = None, max_slots: int = 16,
                  max_step_tokens: int | None = None, tensors: dict | None = None,
-                 raw_config: dict | None = None, config_overrides: dict | None = None):
+                 raw_config: dict | None = None, config_overrides: dict | None = None,
+                 memory_utilization: float = 0.9):
         self.device = require_cuda(device)
         self.dtype = resolve_dtype(dtype)
         torch.cuda.set_device(self.device)
@@ -92,21 +96,64 @@ class EngineCore:
 
         model_max = int(getattr(self.config, "max_position_embeddings", max_seq_len or 0))
         self.max_seq_len = min(max_seq_len or model_max, model_max)
+        if page_size < 1:
+            raise ValueError(f"block_size must be >= 1, got {page_size}")
+        self.max_step_tokens = max_step_tokens or max(self.max_seq_len, max_slots)
+        if pool_tokens == "auto":
+            pool_tokens = self._pool_tokens_from_free_memory(page_size, max_slots, memory_utilization)
+        elif isinstance(pool_tokens, str):
+            raise ValueError(f"kv_pool_tokens must be a number of tokens or 'auto', got {pool_tokens!r}")
         pool_tokens = pool_tokens or self.max_seq_len
         if pool_tokens < self.max_seq_len:
             raise ValueError(f"kv_pool_tokens ({pool_tokens}) must be >= max_seq_len "
                              f"({self.max_seq_len}) so any single request can complete alone")
-        if page_size < 1:
-            raise ValueError(f"block_size must be >= 1, got {page_size}")
         kv_groups, state_groups = plan_groups(self.model.cache_needs(), pool_tokens, page_size)
         self.manager = CacheManager(kv_groups, state_groups, max_slots)
         self.cache = DeviceCache(self.manager, self.dtype, self.device, self.max_seq_len)
         self.page_size = page_size
-        self.max_step_tokens = max_step_tokens or max(self.max_seq_len, max_slots)
         self.step = StepFunction(self.model, self.cache, self.max_step_tokens, self.max_seq_len)
         logger.info("Loaded %s (%s) on %s as %s: %d pages of %d tokens per layer group",
                     model, self.config.architecture, self.device, self.dtype,
                     kv_groups[0].num_pages if kv_groups else 0, page_size)
+
+
+    def _pool_tokens_from_free_memory(self, page_size: int, max_slots: int, utilization: float) -> int:
+        """Positions that fit into the free device memory beside the activations of one step.
+
+        The activations are measured, not estimated: a throw-away cache of the smallest allowed
+        size carries one step of the largest allowed size, and the allocator's peak during that
+        step is what the real pool leaves free (whatever parts the model is made of)."""
+        from ..cache.manager import KVPagesNeed
+        from .step import StepEntry
+        if not 0.0 < utilization <= 1.0:
+            raise ValueError(f"memory_utilization must be in (0, 1], got {utilization}")
+        elem = 4 if self.dtype == torch.float32 else 2
+        per_token = sum(2 * need.n_kv_heads * need.head_dim * elem
+                        for need in self.model.cache_needs().values() if isinstance(need, KVPagesNeed))
+        smallest = -(-self.max_seq_len // page_size) * page_size
+        if per_token == 0:
+            return smallest
+        kv_groups, state_groups = plan_groups(self.model.cache_needs(), smallest, page_size)
+        manager = CacheManager(kv_groups, state_groups, max_slots)
+        cache = DeviceCache(manager, self.dtype, self.device, self.max_seq_len)
+        step = StepFunction(self.model, cache, self.max_step_tokens, self.max_seq_len, use_graphs=False)
+        n = min(self.max_step_tokens, self.max_seq_len)
+        torch.cuda.synchronize(self.device)
+        torch.cuda.reset_peak_memory_stats(self.device)
+        before = torch.cuda.memory_allocated(self.device)
+        step.run([StepEntry("probe", [0] * n, [n - 1])])
+        torch.cuda.synchronize(self.device)
+        peak = torch.cuda.max_memory_allocated(self.device) - before
+        del step, cache, manager, kv_groups, state_groups
+        torch.cuda.empty_cache()
+        # the float32 logits of a full decode batch come on top of what one wanted row needed
+        workspace = int(1.25 * peak) + 8 * max_slots * self.spec.embedding.vocab_size
+        free, _ = torch.cuda.mem_get_info(self.device)
+        budget = int(free * utilization) - workspace
+        tokens = max(budget, 0) // per_token // page_size * page_size
+        logger.info("free device memory %.1f GB, step workspace %.2f GB: pool of %d tokens",
+                    free / 1e9, workspace / 1e9, max(tokens, smallest))
+        return max(tokens, smallest)
 
 
 def random_core(raw_config: dict, *, seed: int = 0, std: float = 0.02, norm_std: float = 0.1,

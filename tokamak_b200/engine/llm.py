@@ -67,7 +67,10 @@ class LLM:
             the model's trained maximum.
         block_size: tokens per cache page.
         kv_pool_tokens: token capacity of the page pool; defaults to ``max_seq_len`` and
-            must be at least that, so that any single request can finish alone.
+            must be at least that, so that any single request can finish alone.  ``"auto"``
+            (not in the reference) fills ``gpu_memory_utilization`` of the device memory that is
+            free after loading, less the measured activations of the largest step.
+        gpu_memory_utilization: see ``kv_pool_tokens="auto"``.
         max_batch_size: upper bound on concurrently running sequences.
         max_num_batched_tokens: most tokens of one step (decode tokens plus prompt portions).
         prefill_chunk: most tokens of one prompt portion; ``None`` leaves it to the budget.
@@ -76,9 +79,10 @@ class LLM:
 
     def __init__(self, model: str | Path, *, device: str | torch.device = "auto",
                  dtype: str | torch.dtype = "auto", max_seq_len: int | None = None,
-                 block_size: int = 16, kv_pool_tokens: int | None = None, max_batch_size: int = 16,
+                 block_size: int = 16, kv_pool_tokens: int | str | None = None, max_batch_size: int = 16,
                  max_num_batched_tokens: int = 2048, prefill_chunk: int | None = None,
-                 attention_policy: str = "full", _core: EngineCore | None = None) -> None:
+                 attention_policy: str = "full", gpu_memory_utilization: float = 0.9,
+                 _core: EngineCore | None = None) -> None:
         if block_size < 1:
             raise ValueError(f"block_size must be >= 1, got {block_size}")
         if max_batch_size < 1:
@@ -95,7 +99,8 @@ class LLM:
                                    page_size=block_size, pool_tokens=kv_pool_tokens,
                                    max_slots=max_batch_size,
                                    max_step_tokens=max(max_num_batched_tokens, max_batch_size),
-                                   config_overrides=overrides)
+                                   config_overrides=overrides,
+                                   memory_utilization=gpu_memory_utilization)
         self.model_path = Path(model)
         self.model_config = self.core.config
         self.max_seq_len = self.core.max_seq_len
