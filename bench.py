@@ -237,6 +237,61 @@ def time_e2e(core, batch: int, steps: int, warmup: int, ctx_end: int, vocab: int
             "ms_per_step": 1e3 * sum(full) / len(full)}
 
 
+QWEN3_0_6B = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "num_hidden_layers": 28, "hidden_size": 1024, "num_attention_heads": 16,
+    "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 3072, "vocab_size": 151936,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
+    "max_position_embeddings": 40960,
+}
+
+
+def throughput_requests(num_requests: int, max_new_cap: int, seed: int, vocab: int):
+    """The requests of the reference's throughput benchmark (benchmarks/workload.py:23-48): prompt
+    lengths log-normal(5.0, 0.7) clipped to 16..512, new tokens 8 + exponential(mean 120) capped,
+    random token ids folded below the first special token.  The draws are made in the
+    reference's order, so that the default arguments give its 4,915 prompt and 2,901 output tokens."""
+    import random
+    rng = random.Random(seed)
+    prompts, new_tokens = [], []
+    for _ in range(num_requests):
+        length = int(min(max(rng.lognormvariate(5.0, 0.7), 16), 512))
+        new_tokens.append(min(int(rng.expovariate(1 / 120)) + 8, max_new_cap))
+        prompts.append([rng.randrange(vocab) % 151_643 for _ in range(length)])
+    return prompts, new_tokens
+
+
+def throughput_workload(sizes: str, num_requests: int, max_new_cap: int, batch: int, pool_tokens: int,
+                        seed: int) -> dict:
+    """Output tokens per second of ``LLM.generate`` over the reference's 32-request workload
+    (benchmarks/benchmark_throughput.py:31-68: continuous batching, EOS ignored, greedy)."""
+    import torch
+    from tokamak_b200 import LLM, SamplingParams
+    from tokamak_b200.engine.core import random_core
+    raw = dict(QWEN3_0_6B if sizes == "0.6b" else QWEN3_8B)
+    core = random_core(raw, seed=0, std=0.02, dtype="bfloat16", max_seq_len=1024, page_size=16,
+                       pool_tokens=pool_tokens, max_slots=batch, max_step_tokens=2048)
+    llm = LLM("<random>", _core=core, max_batch_size=batch, max_num_batched_tokens=2048, block_size=16)
+    prompts, new_tokens = throughput_requests(num_requests, max_new_cap, seed, raw["vocab_size"])
+    params = [SamplingParams(temperature=0.0, max_new_tokens=n, ignore_eos=True) for n in new_tokens]
+    llm.generate(prompt_token_ids=prompts, sampling_params=params)          # warm-up: graphs, allocator
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outs = llm.generate(prompt_token_ids=prompts, sampling_params=params)
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    n_out = sum(len(o.output_token_ids) for o in outs)
+    ttft = sorted(o.ttft_s for o in outs)
+    lat = sorted(o.latency_s for o in outs)
+    return {"workload": "throughput (reference's 32 seeded requests)", "sizes": f"Qwen3-{sizes.upper()} layer sizes",
+            "requests": num_requests, "prompt_tokens": sum(len(p) for p in prompts), "output_tokens": n_out,
+            "max_batch_size": batch, "kv_pool_tokens": pool_tokens, "output_tok_s": round(n_out / wall, 1),
+            "wall_s": round(wall, 3), "ttft_mean_s": round(sum(ttft) / len(ttft), 4),
+            "ttft_p99_s": round(ttft[-1], 4), "latency_mean_s": round(sum(lat) / len(lat), 4),
+            "steps": llm.last_stats["steps"], "mixed_steps": llm.last_stats["mixed_steps"],
+            "preemptions": llm.last_stats["preemptions"], "dtype": "bf16", "data": "synthetic"}
+
+
 def kernel_case(name: str, batch: int, ctx: int, iters: int, peaks: dict) -> dict:
     """One kernel alone on inputs larger than L2, timed with CUDA events: achieved bytes or flops
     per second against the peak.  Also the small case that ncu captures are made on."""
@@ -361,6 +416,13 @@ def main() -> int:
     ap.add_argument("--kernel", default=None, help="time one kernel alone instead: attention_decode, "
                     "attention_prefill (tcgen05), attention_prefill_mma, rmsnorm, gemm_tc_decode, gemm_decode (library)")
     ap.add_argument("--ctx", type=int, default=CONTEXT, help="context length of a --kernel case")
+    ap.add_argument("--workload", default=None, choices=["throughput"],
+                    help="run the reference's throughput workload through LLM.generate instead")
+    ap.add_argument("--sizes", default="8b", choices=["0.6b", "8b"], help="layer sizes of --workload")
+    ap.add_argument("--num-requests", type=int, default=32)
+    ap.add_argument("--max-new-cap", type=int, default=256)
+    ap.add_argument("--kv-pool-tokens", type=int, default=16384)
+    ap.add_argument("--seed", type=int, default=0)
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -375,6 +437,10 @@ def main() -> int:
     steps = max(1, args.steps)
     if args.kernel:
         print(json.dumps(kernel_case(args.kernel, args.batch, args.ctx, steps, load_peaks())))
+        return 0
+    if args.workload == "throughput":
+        print(json.dumps(throughput_workload(args.sizes, args.num_requests, args.max_new_cap, args.batch,
+                                             args.kv_pool_tokens, args.seed)))
         return 0
 
     import torch
