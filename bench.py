@@ -382,6 +382,21 @@ def kernel_case(name: str, batch: int, ctx: int, iters: int, peaks: dict) -> dic
             turn[0] = (turn[0] + 1) % len(ws)
             torch.mm(x, ws[turn[0]].t())
         nbytes = w.numel() * 2
+    elif name in ("gemm_pair_swiglu", "gemm_prefill_library"):
+        # the prefill gate/up product of one layer over ctx tokens with the activation: the engine's
+        # kernel on pairs of SMs with the activation in its epilogue, or the library product followed
+        # by the activation kernel
+        inter, hidden = cfg["intermediate_size"], cfg["hidden_size"]
+        w = (torch.randn((2 * inter, hidden), device=dev, generator=gen) * 0.02).bfloat16()
+        x = torch.randn((ctx, hidden), device=dev, generator=gen).bfloat16()
+        act = torch.empty((ctx, inter), device=dev, dtype=torch.bfloat16)
+        if name == "gemm_pair_swiglu":
+            run = lambda: ops.gemm_pair(x, w, err, swiglu=True)
+        else:
+            def run():
+                ops.swiglu(torch.mm(x, w.t()), act, block=ops.SWIGLU_TILE_BLOCK)
+        nbytes = (w.numel() + x.numel() + act.numel()) * 2
+        flops = 2.0 * ctx * 2 * inter * hidden
     else:
         raise SystemExit(f"unknown kernel case {name!r}")
     for _ in range(3):
@@ -414,7 +429,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
     ap.add_argument("--kernel", default=None, help="time one kernel alone instead: attention_decode, "
-                    "attention_prefill (tcgen05), attention_prefill_mma, rmsnorm, gemm_tc_decode, gemm_decode (library)")
+                    "attention_prefill (tcgen05), attention_prefill_mma, rope_kv, rmsnorm, gemm_tc_decode, gemm_decode (library), "
+                    "gemm_pair_swiglu, gemm_prefill_library (--ctx tokens)")
     ap.add_argument("--ctx", type=int, default=CONTEXT, help="context length of a --kernel case")
     ap.add_argument("--workload", default=None, choices=["throughput"],
                     help="run the reference's throughput workload through LLM.generate instead")

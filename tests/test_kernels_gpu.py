@@ -636,3 +636,39 @@ def test_gemm_tcgen05_tokens_as_rows(tokens, n_out, k, bn, out_dtype):
         torch.testing.assert_close(got.double().cpu(), want, rtol=1e-4, atol=1e-3 * (k ** 0.5) / 8)
     else:
         torch.testing.assert_close(got.double().cpu(), want, rtol=1e-2, atol=1e-2 * (k ** 0.5))
+
+
+@pytest.mark.parametrize("tokens,n_out,k", [(256, 256, 64), (300, 384, 320), (77, 200, 96), (1000, 1304, 1032),
+                                            (2048, 512, 4096), (513, 256, 12288)])
+def test_gemm_tcgen05_pairs_of_sms(tokens, n_out, k):
+    """The persistent product on pairs of SMs (cta_group::2): ragged token, output and inner sizes,
+    several tiles per pair (both accumulators in turn) and more pairs than tiles."""
+    from tokamak_b200.csrc import ops
+    gen = torch.Generator().manual_seed(tokens + n_out + k)
+    x = torch.randn(tokens, k, generator=gen).bfloat16()
+    w = (torch.randn(n_out, k, generator=gen) / k ** 0.5).bfloat16()
+    err = err_word()
+    got = ops.gemm_pair(x.to(DEV), w.to(DEV), err)
+    torch.cuda.synchronize()
+    assert err.tolist()[0] == 0, err.tolist()
+    want = x.double() @ w.double().T
+    torch.testing.assert_close(got.double().cpu(), want, rtol=1e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("tokens,inter,k", [(256, 128, 256), (700, 320, 1536), (2048, 1024, 4096), (65, 64, 72)])
+def test_gemm_tcgen05_pairs_with_gated_activation(tokens, inter, k):
+    """The same product storing silu(gate) * up of a stacked gate/up weight in blocks of 64."""
+    from tokamak_b200.csrc import ops
+    gen = torch.Generator().manual_seed(tokens + inter)
+    x = torch.randn(tokens, k, generator=gen).bfloat16()
+    wg = (torch.randn(inter, k, generator=gen) * (2.0 / k ** 0.5)).bfloat16()
+    wu = (torch.randn(inter, k, generator=gen) / k ** 0.5).bfloat16()
+    b = ops.SWIGLU_TILE_BLOCK
+    w = torch.stack((wg.view(inter // b, b, k), wu.view(inter // b, b, k)), dim=1).reshape(2 * inter, k).contiguous()
+    err = err_word()
+    got = ops.gemm_pair(x.to(DEV), w.to(DEV), err, swiglu=True)
+    torch.cuda.synchronize()
+    assert err.tolist()[0] == 0, err.tolist()
+    assert got.shape == (tokens, inter)
+    g, u = x.double() @ wg.double().T, x.double() @ wu.double().T
+    torch.testing.assert_close(got.double().cpu(), g * torch.sigmoid(g) * u, rtol=1e-2, atol=2e-2)

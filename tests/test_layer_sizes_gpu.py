@@ -94,3 +94,23 @@ def test_pages_beyond_four_gib_are_addressed_right(model_8b_sizes, dtype):
         assert not core.manager.live_requests()
     del core
     torch.cuda.empty_cache()
+
+
+def test_a_long_prompt_through_the_products_for_many_tokens(model_8b_sizes):
+    """A prompt of 1,024 tokens in one step: the projections with enough tiles run on pairs of SMs,
+    the gate/up product with the activation in its epilogue; then eight tokens one by one."""
+    from tokamak_b200.engine.core import EngineCore
+    from tokamak_b200.engine.replay import run_step
+    from tokamak_b200.csrc import ops
+    raw, tensors, cpu = model_8b_sizes
+    assert ops.pair_gemm_takes(1016, 2 * raw["intermediate_size"], raw["hidden_size"], fused=True)
+    mine = {k: (v.float() if v.dim() == 1 else v) for k, v in tensors.items()}
+    core = EngineCore("<random>", dtype="bfloat16", tensors=mine, raw_config=raw, max_seq_len=1024, page_size=16,
+                      pool_tokens=1024, max_slots=2, max_step_tokens=1024)
+    reqs = {"long": random_tokens(raw["vocab_size"], 1024, seed=9)}
+    truth = plain.forward_logits(raw, cpu, reqs["long"], torch.float64)
+    records, rows = traces.tail_one_by_one(reqs, tail=8)
+    for rec in records:
+        out = run_step(core, rec)
+        want = torch.stack([truth[p] for _, p in rows[rec["step"]]])
+        assert_logits_close(torch.from_numpy(out), want, "bfloat16", f"long prompt step {rec['step']}")

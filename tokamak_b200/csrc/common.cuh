@@ -120,10 +120,10 @@ inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
-// The same with the blocks of every grid.z column forming one thread-block cluster.
+// The same with thread-block clusters of the given shape.
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_cluster_z(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                                    cudaStream_t stream, unsigned cluster_z, Args&&... args) {
+inline cudaError_t launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                  cudaStream_t stream, dim3 cluster, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -131,14 +131,21 @@ inline cudaError_t launch_cluster_z(void (*kernel)(KArgs...), dim3 grid, dim3 bl
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = cluster_z;
+  attr[0].val.clusterDim.x = cluster.x;
+  attr[0].val.clusterDim.y = cluster.y;
+  attr[0].val.clusterDim.z = cluster.z;
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 2 : 1;
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+// Clusters of the blocks of every grid.z column.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_cluster_z(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, unsigned cluster_z, Args&&... args) {
+  return launch_cluster(kernel, grid, block, smem, stream, dim3(1, 1, cluster_z), std::forward<Args>(args)...);
 }
 
 }  // namespace tk

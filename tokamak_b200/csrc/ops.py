@@ -7,6 +7,8 @@ is no CPU path: a tensor that is not on a CUDA device is an error.
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .lib import library
@@ -443,6 +445,42 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, err: torch.Tensor, out_dtype:
                                           tokens, n_out, k, k, k, n_out, bn, 1, 0,
                                           1 if out_dtype == torch.float32 else 0, max_stages, 0, 0, _stream()),
            "gemm_tc")
+    return out
+
+
+# Which products of many tokens run on the engine's own kernel for pairs of SMs: "all" of them,
+# only the gate/up product with the "fused" activation, or none ("off": the library everywhere).
+PAIR_GEMM_POLICY = os.environ.get("TOKAMAK_B200_PAIR_GEMM", "all")
+PAIR_GEMM_MIN_TILES = 96     # below this the grid of SM pairs is too empty and the library is faster
+
+
+def pair_gemm_takes(tokens: int, n_out: int, k: int, fused: bool = False) -> bool:
+    """Whether :func:`gemm_pair` is the product to use: the policy allows it, there are enough
+    256 x 256 tiles to keep the 74 pairs of SMs busy, and its TMA maps and 16-byte stores can
+    address the sizes."""
+    if PAIR_GEMM_POLICY == "off" or (PAIR_GEMM_POLICY == "fused" and not fused):
+        return False
+    tiles = -(-tokens // 256) * -(-n_out // 256)
+    return tiles >= PAIR_GEMM_MIN_TILES and k % 8 == 0 and n_out % 8 == 0
+
+
+def gemm_pair(x: torch.Tensor, weight: torch.Tensor, err: torch.Tensor, swiglu: bool = False) -> torch.Tensor:
+    """``x @ weight^T`` for many tokens on pairs of SMs (tcgen05.mma.cta_group::2, persistent grid);
+    bfloat16 ``[tokens, N_out]``.  ``swiglu=True``: the weight is a stacked gate/up matrix whose rows
+    alternate in blocks of ``SWIGLU_TILE_BLOCK``; the result is ``[tokens, N_out / 2] = silu(gate) * up``."""
+    _want(weight, torch.bfloat16, "weight"); _want(x, torch.bfloat16, "x")
+    n_out, k = weight.shape
+    tokens, kx = x.shape
+    if k != kx or k % 8:
+        raise KernelError(f"inner sizes {k} and {kx} must agree and be a multiple of 8")
+    if swiglu and n_out % (2 * SWIGLU_TILE_BLOCK):
+        raise KernelError("the fused activation wants rows in blocks of 64 gate + 64 up")
+    width = n_out // 2 if swiglu else n_out
+    if width % 8:
+        raise KernelError("the output width must be a multiple of 8")
+    out = torch.empty((tokens, width), dtype=torch.bfloat16, device=x.device)
+    _check(library().tk_gemm_bf16_pair(x.data_ptr(), weight.data_ptr(), out.data_ptr(), err.data_ptr(), tokens,
+                                       n_out, k, k, k, width, 1 if swiglu else 0, _stream()), "gemm_pair")
     return out
 
 

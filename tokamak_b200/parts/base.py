@@ -116,9 +116,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     or two parts) which the consuming kernel (norm, rotation, activation) adds up; ``err`` is the
     error word its bounded waits report to.
 
-    bfloat16, many tokens: the library product, as the reference uses the library for its
-    projections (src/tokamak/model/transformer.py:38-41); ``out_dtype=float32`` keeps the
-    32-bit accumulators instead of rounding them.
+    bfloat16, many tokens: the persistent tcgen05 kernel on pairs of SMs (``ops.gemm_pair``)
+    where its grid fills the GPU; otherwise the library product, as the reference uses the
+    library for its projections (src/tokamak/model/transformer.py:38-41); ``out_dtype=float32``
+    keeps the 32-bit accumulators instead of rounding them (library only).
     """
     from ..csrc import ops
 
@@ -129,6 +130,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
         return ops.gemm_tc_swapped(weight, x, err, splits, max_stages=stages, cluster=cluster)
     if out_dtype is not None and out_dtype != x.dtype:
         return torch.mm(x, weight.t(), out_dtype=out_dtype)
+    if err is not None and ops.pair_gemm_takes(x.shape[0], weight.shape[0], weight.shape[1]):
+        return ops.gemm_pair(x, weight, err)
     return torch.mm(x, weight.t())
 
 

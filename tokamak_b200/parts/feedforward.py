@@ -61,6 +61,10 @@ class SwiGLU:
                                                             h.shape[0])
             act = ops.gemm_tc_swapped(self.w_gate_up, h, err, splits, max_stages=stages, cluster=cluster,
                                       swiglu=True)
+        elif (h.dtype == torch.bfloat16 and err is not None and self.block == ops.SWIGLU_TILE_BLOCK
+              and ops.pair_gemm_takes(h.shape[0], 2 * self.spec.intermediate_size, self.spec.hidden_size, fused=True)):
+            # many tokens: the product on pairs of SMs applies the activation to its accumulators
+            act = ops.gemm_pair(h, self.w_gate_up, err, swiglu=True)
         else:
             gate_up = linear(h, self.w_gate_up, err=err)
             act = torch.empty((h.shape[0], self.spec.intermediate_size), dtype=h.dtype, device=h.device)
