@@ -114,3 +114,33 @@ def test_a_long_prompt_through_the_products_for_many_tokens(model_8b_sizes):
         out = run_step(core, rec)
         want = torch.stack([truth[p] for _, p in rows[rec["step"]]])
         assert_logits_close(torch.from_numpy(out), want, "bfloat16", f"long prompt step {rec['step']}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("sizes", ["LAYER_14B", "LAYER_32B"])
+def test_14b_and_32b_layer_sizes(sizes, dtype):
+    """One layer of the widths, head counts and intermediate sizes of Qwen3-14B and Qwen3-32B (one
+    layer keeps the float64 oracle on the CPU within seconds): a prompt whole with its tail token by
+    token, and two requests mixed, one of them long enough for the products of many tokens."""
+    from tokamak_b200.config import architecture_of
+    from tokamak_b200.engine.replay import run_step
+    from tokamak_b200.models.decoder import DecoderModel
+    from tokamak_b200.weights import random_tensors
+    raw = getattr(tiny_configs, sizes)
+    arch = architecture_of(raw)
+    expected = DecoderModel.expected_tensors(arch.model_spec(arch.parse_config(raw)))
+    tensors = random_tensors(expected, seed=5, std=0.02, norm_std=0.1, dtype=torch.bfloat16, device="cuda")
+    cpu = {k: v.float().cpu() for k, v in tensors.items()}
+    reqs = {"a": random_tokens(raw["vocab_size"], 300, seed=3), "b": random_tokens(raw["vocab_size"], 45, seed=4)}
+    truth = {rid: plain.forward_logits(raw, cpu, ids, torch.float64) for rid, ids in reqs.items()}
+    del cpu
+    core = make_core(raw, tensors, dtype)
+    for builder, kw in ((traces.tail_one_by_one, {"tail": 6}), (traces.mixed, {"max_tokens": 512, "max_live": 2, "seed": 2})):
+        records, rows = builder(reqs, **kw)
+        for rec in records:
+            out = run_step(core, rec)
+            if out is None:
+                continue
+            want = torch.stack([truth[rid][p] for rid, p in rows[rec["step"]]])
+            assert_logits_close(torch.from_numpy(out), want, dtype, f"{sizes} {builder.__name__} step {rec['step']}")
+        assert not core.manager.live_requests()

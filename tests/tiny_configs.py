@@ -97,3 +97,18 @@ LAYER_8B = {
     "head_dim": 128, "intermediate_size": 12288, "vocab_size": 2048, "rope_theta": 1000000.0,
     "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 4096,
 }
+
+# The layer sizes of Qwen3-14B and Qwen3-32B with one layer and a small vocabulary: a width of
+# 5120 (no power of two), groups of 5 and of 8 query heads, intermediate sizes 17408 and 25600.
+LAYER_14B = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "num_hidden_layers": 1, "hidden_size": 5120, "num_attention_heads": 40, "num_key_value_heads": 8,
+    "head_dim": 128, "intermediate_size": 17408, "vocab_size": 1000, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 4096,
+}
+LAYER_32B = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "num_hidden_layers": 1, "hidden_size": 5120, "num_attention_heads": 64, "num_key_value_heads": 8,
+    "head_dim": 128, "intermediate_size": 25600, "vocab_size": 1000, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 4096,
+}
