@@ -20,7 +20,14 @@ class KernelError(RuntimeError):
     """A kernel launch failed or refused its arguments."""
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current stream's handle.  Every launch asks for it, so the fast accessor is used where
+    this torch has it (no Stream object is built)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
