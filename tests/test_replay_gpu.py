@@ -85,6 +85,14 @@ def test_mixed_with_page_reuse(tag, dtype):
     assert sum(LENGTHS[tag]) > 384
 
 
+@pytest.mark.parametrize("seed", [1, 2, 3])
+@pytest.mark.parametrize("tag,dtype", [("W", "float32"), ("D", "bfloat16"), ("C", "bfloat16"), ("B", "float32")])
+def test_mixed_in_other_orders(tag, dtype, seed):
+    """The mixed replay again with other random orders, portion sizes and pauses, and a smaller
+    pool: windows that give pages back while other requests take them, poisoned free pages."""
+    replay(tag, dtype, traces.mixed, max_tokens=320, poison=True, seed=seed)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_first_tokens_and_long_decode(dtype):
     """Positions 0, 1, 2 one by one, then 220 more decoded one by one across many pages."""
