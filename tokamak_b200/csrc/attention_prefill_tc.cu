@@ -4,7 +4,7 @@
 // One thread block per (256 query tokens of one request, query head), handled as two query
 // tiles of 128 rows that share every key and value tile:
 //   warp 0       TMA: the query tiles once, then key and value tiles of 64 keys, page by page
-//                (cp.async.bulk.tensor, 128-byte swizzle, no multicast), into a ring of stages;
+//                (cp.async.bulk.tensor, 128-byte swizzle, every block for itself), into a ring of stages;
 //                every lane looks one page up and issues one copy, so the look-ups of a stage
 //                cost one memory latency, and the next stage's are under way while it waits;
 //   warps 1, 10  one thread each issues tcgen05.mma for one query tile: S = Q K^T (M 128, N 64)

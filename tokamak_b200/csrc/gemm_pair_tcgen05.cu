@@ -4,7 +4,7 @@
 // The grid is persistent: thread-block clusters of two blocks walk the 256 x 256 output tiles,
 // token tiles fastest, so that the pairs that run at the same time share weight tiles in L2.
 // Of a tile's operands each block of the pair loads its own half by TMA (128 token rows and
-// 128 weight rows of 64 k-elements per stage, 128-byte swizzle, no multicast) into its own
+// 128 weight rows of 64 k-elements per stage, 128-byte swizzle, every block for itself) into its own
 // shared memory; both halves complete on the full-barrier of the pair's first block, whose
 // single issuing thread runs tcgen05.mma with M = 256, N = 256 over both blocks' shared memory.
 // Each block ends up with the 128 x 256 float32 accumulator of its own token rows in its own

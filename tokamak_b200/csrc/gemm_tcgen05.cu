@@ -3,7 +3,7 @@
 //
 // One thread block per (128-row tile of R, BN-column tile of C, K split).  Operand
 // tiles of 64 k-elements travel global -> shared memory by TMA (cp.async.bulk.tensor,
-// 128-byte swizzle, no multicast) into a ring of stages guarded by mbarriers; one
+// 128-byte swizzle, every block for itself) into a ring of stages guarded by mbarriers; one
 // elected thread issues tcgen05.mma (M = 128, N = BN, K = 16) with the accumulator in
 // tensor memory; four epilogue warps read the accumulator with tcgen05.ld and store it.
 //

@@ -1,5 +1,5 @@
 // Inline PTX for the Blackwell data path shared by the tcgen05 kernels: mbarriers with
-// bounded waits, TMA tile loads (no multicast), shared-memory matrix descriptors, tcgen05.mma /
+// bounded waits, TMA tile loads (each block loads for itself), shared-memory matrix descriptors, tcgen05.mma /
 // commit / ld / st, and the host-side lookup of cuTensorMapEncodeTiled.
 #pragma once
 
