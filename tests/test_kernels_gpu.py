@@ -672,3 +672,46 @@ def test_gemm_tcgen05_pairs_with_gated_activation(tokens, inter, k):
     assert got.shape == (tokens, inter)
     g, u = x.double() @ wg.double().T, x.double() @ wu.double().T
     torch.testing.assert_close(got.double().cpu(), g * torch.sigmoid(g) * u, rtol=1e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("tokens,hidden,k,splits", [(8, 256, 512, 4), (1, 128, 64, 1), (33, 640, 1536, 8), (64, 4096, 4096, 8)])
+def test_gemm_tcgen05_swapped_residual_and_owed_norm(tokens, hidden, k, splits):
+    """A product that ends a residual branch adds its sums to the residual stream itself and hands
+    on bf16(residual * norm weight) with the tiles' sums of squares; the product after it (plain,
+    and with the gated activation) multiplies its sums by the owed rsqrt(mean square + eps).  Both
+    against the formulas: x + delta, then weight * x * rsqrt(mean(x^2) + eps), then the product."""
+    from tokamak_b200.csrc import ops
+    eps = 1e-5
+    gen = torch.Generator().manual_seed(tokens + hidden)
+    a = torch.randn(tokens, k, generator=gen).bfloat16()
+    w1 = (torch.randn(hidden, k, generator=gen) / k ** 0.5).bfloat16()
+    resid = torch.randn(tokens, hidden, generator=gen)
+    norm_w = 1 + 0.1 * torch.randn(hidden, generator=gen)
+    err = err_word()
+    r_dev = resid.to(DEV)
+    xb, sums = ops.gemm_tc_swapped(w1.to(DEV), a.to(DEV), err, splits, cluster=splits,
+                                   residual_norm=(r_dev, norm_w.to(DEV)))
+    torch.cuda.synchronize()
+    assert err.tolist()[0] == 0, err.tolist()
+    r_want = resid.double() + a.double() @ w1.double().T
+    torch.testing.assert_close(r_dev.double().cpu(), r_want, rtol=1e-5, atol=1e-4 * k ** 0.5)
+    torch.testing.assert_close(xb.double().cpu(), r_want * norm_w.double(), rtol=1e-2, atol=1e-2)
+    assert sums.shape == (hidden // 128, tokens)
+    torch.testing.assert_close(sums.double().sum(0).cpu(), (r_want ** 2).sum(1), rtol=1e-4, atol=1e-4)
+    normed = plain.rms_norm(r_want, norm_w.double(), eps)
+    # the product after the norm: plain sums ...
+    w2 = (torch.randn(384, hidden, generator=gen) / hidden ** 0.5).bfloat16()
+    y = ops.gemm_tc_swapped(w2.to(DEV), xb, err, 2, cluster=2, colscale=(sums, hidden, eps))
+    torch.testing.assert_close(y[0].double().cpu(), normed @ w2.double().T, rtol=2e-2, atol=2e-2)
+    y1 = ops.gemm_tc_swapped(w2.to(DEV), xb, err, 1, colscale=(sums, hidden, eps))      # a single block per tile
+    torch.testing.assert_close(y1[0].double().cpu(), normed @ w2.double().T, rtol=2e-2, atol=2e-2)
+    # ... and with the gated activation
+    b = ops.SWIGLU_TILE_BLOCK
+    wg = (torch.randn(128, hidden, generator=gen) * (2.0 / hidden ** 0.5)).bfloat16()
+    wu = (torch.randn(128, hidden, generator=gen) / hidden ** 0.5).bfloat16()
+    wgu = torch.stack((wg.view(-1, b, hidden), wu.view(-1, b, hidden)), dim=1).reshape(256, hidden).contiguous()
+    act = ops.gemm_tc_swapped(wgu.to(DEV), xb, err, 2, cluster=2, swiglu=True, colscale=(sums, hidden, eps))
+    g, u = normed @ wg.double().T, normed @ wu.double().T
+    torch.testing.assert_close(act.double().cpu(), g * torch.sigmoid(g) * u, rtol=3e-2, atol=3e-2)
+    torch.cuda.synchronize()
+    assert err.tolist()[0] == 0, err.tolist()

@@ -34,6 +34,14 @@ constexpr int kGtThreads = 192;   // warp 0: TMA, warp 1: MMA, warps 2..5: epilo
 // halves of 64 outputs, and the block that adds the splits up stores
 // bf16(silu(gate) * up) as [token, rows / 2] instead of the float32 sums.
 constexpr int kGtEpiSwiglu = 1;
+// Epilogue of the swapped form for a product that ends a residual branch: the block that adds the
+// splits up adds the sums to the float32 residual stream in place, stores
+// bf16(residual * norm weight) for the product that follows the next RMSNorm, and the tile's
+// share of every token's sum of squares.  The consumer of these (see colscale below) multiplies
+// its own sums by rsqrt(mean square + eps): the norm between two products needs no kernel of its
+// own (src/tokamak/model/layers.py:28-33, transformer.py:107-108; the 32-bit statistics are the
+// same, the rounding to bfloat16 happens before instead of after the scaling by the statistic).
+constexpr int kGtEpiResidualNorm = 2;
 
 struct GemmTcParams {
   void* out;                // swapped: float [n_splits, cols_total, rows_total]; else [rows_total, cols_total]
@@ -48,7 +56,19 @@ struct GemmTcParams {
   int cluster_reduce;       // swapped only: 0, or the cluster size: that many consecutive splits of a tile
                             // form a cluster and store their sum as one part (n_splits / cluster parts)
   int out_f32;              // non-swapped: 1 = float32 output, 0 = bfloat16
-  int epilogue;             // swapped only: 0 = float32 sums; 1 = gated activation, see kGtEpiSwiglu
+  int epilogue;             // swapped only: 0 = float32 sums; 1 = gated activation, see kGtEpiSwiglu;
+                            // 2 = residual sum and preparation of the next norm, see kGtEpiResidualNorm
+  // swapped only: every column (token) of the sums is multiplied by
+  // rsqrt(sum_i colscale_parts[i, token] * colscale_inv_dim + colscale_eps) before it is stored
+  const float* colscale_parts;
+  int n_colscale_parts;
+  float colscale_inv_dim, colscale_eps;
+  // epilogue 2: the residual stream [tokens, rows] (float32, updated in place), the norm weight [rows],
+  // the prepared activations [tokens, rows] and the sums of squares [row tiles, tokens]
+  float* resid;
+  const float* norm_w;
+  __nv_bfloat16* xb_out;
+  float* sumsq_out;
   long long ld_out;         // non-swapped: elements between output rows
 };
 
@@ -81,6 +101,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
   const int kb_end = min(kb_begin + kb_per, kb_total);
   const int n_kb = max(kb_end - kb_begin, 0);
   const uint32_t tmem_cols = p.bn < 32 ? 32u : (uint32_t)p.bn;   // bn is 16, 32, 64, 128 or 256
+
+  // the sums pass through shared memory (and the cluster) whenever anything is done to them
+  const bool staged = p.cluster_reduce > 1 || p.epilogue != 0 || p.colscale_parts != nullptr;
 
   pdl_trigger();
   if (threadIdx.x == 0) {
@@ -174,12 +197,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
     const int quarter = warp & 3;
     bool ok = true;
     pdl_wait();   // nothing is stored before the previous kernels are done with the output buffer
+    // the scale of this thread's column (token), while the products still run
+    float my_scale = 1.0f;
+    const int my_col = (warp - 2) * 32 + lane;
+    if (p.colscale_parts != nullptr && my_col < p.bn && tile_c * p.bn + my_col < p.cols_total) {
+      float ss = 0.0f;
+      for (int i = 0; i < p.n_colscale_parts; ++i) {
+        ss += p.colscale_parts[(size_t)i * p.cols_total + tile_c * p.bn + my_col];
+      }
+      my_scale = rsqrtf(ss * p.colscale_inv_dim + p.colscale_eps);
+    }
     if (n_kb > 0) {
       ok = mbar_wait(gt_smem_u32(accum_bar), 0u, abort_flag);
       if (!ok && lane == 0) { set_error(p.err, kErrWait, 2, 0, 0); *abort_flag = 1; }
     }
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const int row = tile_r * kGtBM + quarter * 32 + lane;      // row of R = lane of the accumulator
+    if (staged && my_col < p.bn) {
+      // behind the staging area, in the ring of stages that the products are done with
+      reinterpret_cast<float*>(smem)[p.bn * kGtBM + my_col] = my_scale;
+    }
     for (int c0 = 0; c0 < p.bn; c0 += 16) {
       uint32_t v[16];
       if (ok && n_kb > 0) {
@@ -189,7 +226,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
 #pragma unroll
         for (int e = 0; e < 16; ++e) v[e] = 0u;
       }
-      if (p.cluster_reduce > 1 || p.epilogue == kGtEpiSwiglu) {
+      if (staged) {
         // stage[column][row of the tile]: consecutive lanes write consecutive words
         float* stage = reinterpret_cast<float*>(smem);
 #pragma unroll
@@ -237,14 +274,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
 
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
-  if (p.epilogue == kGtEpiSwiglu) {
+  if (staged) {
     cluster_sync_all();                    // every block of the cluster has staged its partial
-    if (warp >= 2) {
+    const int csize = p.cluster_reduce > 1 ? p.cluster_reduce : 1;
+    const uint32_t my_rank = p.cluster_reduce > 1 ? cluster_ctarank() : 0u;
+    const float* s_scale = reinterpret_cast<const float*>(smem) + p.bn * kGtBM;   // this block's own copy
+    if (warp >= 2 && p.epilogue == kGtEpiSwiglu) {
       // thread -> four neighbouring outputs of the tile's 64 and one of eight column phases; gate
       // in tile rows j.., up in tile rows 64 + j..; the sum over the ranks runs in the same order
       // as without the activation, and the activation is the formula of the separate kernel
-      const int csize = p.cluster_reduce > 1 ? p.cluster_reduce : 1;
-      const uint32_t my_rank = p.cluster_reduce > 1 ? cluster_ctarank() : 0u;
       const int t = (warp - 2) * 32 + lane;
       const int j4 = (t & 15) * 4, phase = t >> 4;
       const int inter = p.rows_total >> 1;
@@ -261,6 +299,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
             g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
             u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
           }
+          if (p.colscale_parts != nullptr) {
+            const float sc = s_scale[c];
+            g.x *= sc; g.y *= sc; g.z *= sc; g.w *= sc;
+            u.x *= sc; u.y *= sc; u.z *= sc; u.w *= sc;
+          }
           uint2 packed;
           *reinterpret_cast<__nv_bfloat162*>(&packed.x) =
               __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
@@ -269,29 +312,43 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
           *reinterpret_cast<uint2*>(out + (size_t)col * inter + oc) = packed;
         }
       }
-    }
-    cluster_sync_all();                    // nobody's shared memory is read any more
-  } else if (p.cluster_reduce > 1) {
-    cluster_sync_all();                    // every block of the cluster has staged its partial
-    if (warp >= 2) {
+    } else if (warp >= 2) {
       // every block of the cluster adds up its share of the columns (tokens): column c belongs
-      // to rank c mod cluster size; a thread takes four neighbouring rows of one column; the
-      // order of the sum over the ranks is always the same
-      const uint32_t my_rank = cluster_ctarank();
+      // to rank c mod cluster size; a warp takes one column at a time, its lanes four neighbouring
+      // rows each; the order of the sum over the ranks is always the same
       const int t = (warp - 2) * 32 + lane;
       const int r4 = (t & 31) * 4, phase = t >> 5;
       const int row = tile_r * kGtBM + r4;
       const bool vec = (p.rows_total & 3) == 0;
       float* out = reinterpret_cast<float*>(p.out) +
-                   (size_t)(split / p.cluster_reduce) * p.cols_total * p.rows_total;
+                   (size_t)(split / csize) * p.cols_total * p.rows_total;
+      // with the residual epilogue the rows are a multiple of 128: every lane has its four rows
       if (row < p.rows_total) {
-        for (int c = (int)my_rank + p.cluster_reduce * phase; c < p.bn; c += 4 * p.cluster_reduce) {
+        for (int c = (int)my_rank + csize * phase; c < p.bn; c += 4 * csize) {
           const int col = tile_c * p.bn + c;
           if (col >= p.cols_total) break;
           float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-          for (int rk = 0; rk < p.cluster_reduce; ++rk) {
+          for (int rk = 0; rk < csize; ++rk) {
             const float4 v = ld_cluster_f32x4(base + (uint32_t)((c * kGtBM + r4) * 4), (uint32_t)rk);
             sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+          }
+          if (p.colscale_parts != nullptr) {
+            const float sc = s_scale[c];
+            sum.x *= sc; sum.y *= sc; sum.z *= sc; sum.w *= sc;
+          }
+          if (p.epilogue == kGtEpiResidualNorm) {
+            float* rp = p.resid + (size_t)col * p.rows_total + row;
+            float4 r = *reinterpret_cast<const float4*>(rp);
+            r.x += sum.x; r.y += sum.y; r.z += sum.z; r.w += sum.w;
+            *reinterpret_cast<float4*>(rp) = r;
+            const float4 w = *reinterpret_cast<const float4*>(p.norm_w + row);
+            uint2 packed;
+            *reinterpret_cast<__nv_bfloat162*>(&packed.x) = __floats2bfloat162_rn(r.x * w.x, r.y * w.y);
+            *reinterpret_cast<__nv_bfloat162*>(&packed.y) = __floats2bfloat162_rn(r.z * w.z, r.w * w.w);
+            *reinterpret_cast<uint2*>(p.xb_out + (size_t)col * p.rows_total + row) = packed;
+            const float ss = warp_sum(r.x * r.x + r.y * r.y + r.z * r.z + r.w * r.w);
+            if (lane == 0) p.sumsq_out[(size_t)tile_r * p.cols_total + col] = ss;
+            continue;
           }
           float* dst = out + (size_t)col * p.rows_total + row;
           if (vec && row + 3 < p.rows_total) {
@@ -339,18 +396,33 @@ static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long
 // swapped = 0: out is [rows, cols] with row stride ld_out, float32 if out_f32 else bfloat16; n_splits must be 1.
 // epilogue = 1 (swapped, rows a multiple of 128 whose gate and up rows alternate in blocks of 64, all
 // splits in one cluster): out is bfloat16 [cols, rows / 2] = silu(gate) * up.
+// epilogue = 2 (swapped, rows a multiple of 128, all splits in one cluster): nothing goes to out; the
+// sums are added to resid [cols, rows] (float32) in place, xb_out [cols, rows] receives
+// bf16(resid * norm_w) and sumsq_out [rows / 128, cols] the tiles' sums of squares of resid.
+// colscale_parts (swapped, or null): [n_colscale_parts, cols] float32; the sums of column c are
+// multiplied by rsqrt(sum_i colscale_parts[i, c] * colscale_inv_dim + colscale_eps).
 TK_API int tk_gemm_bf16_tcgen05(const void* r, const void* c, void* out, int* err, int rows, int cols, int k,
                                 long long ld_r, long long ld_c, long long ld_out, int bn, int n_splits,
                                 int swapped, int out_f32, int max_stages, int cluster_reduce, int epilogue,
-                                cudaStream_t stream) {
+                                const float* colscale_parts, int n_colscale_parts, float colscale_inv_dim,
+                                float colscale_eps, float* resid, const float* norm_w, void* xb_out,
+                                float* sumsq_out, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;
   if (k <= 0 || k % 8 != 0 || (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) || n_splits < 1 ||
       (!swapped && n_splits != 1) ||
       (cluster_reduce > 1 && (!swapped || cluster_reduce > 8 || n_splits % cluster_reduce != 0)) || cluster_reduce < 0) {
     return (int)cudaErrorInvalidValue;
   }
-  if (epilogue != 0 && (epilogue != tk::kGtEpiSwiglu || !swapped || rows % 128 != 0 ||
-                        n_splits != (cluster_reduce > 1 ? cluster_reduce : 1))) {
+  if (epilogue != 0 && ((epilogue != tk::kGtEpiSwiglu && epilogue != tk::kGtEpiResidualNorm) || !swapped ||
+                        rows % 128 != 0 || n_splits != (cluster_reduce > 1 ? cluster_reduce : 1))) {
+    return (int)cudaErrorInvalidValue;
+  }
+  if (epilogue == tk::kGtEpiResidualNorm &&
+      (resid == nullptr || norm_w == nullptr || xb_out == nullptr || sumsq_out == nullptr)) {
+    return (int)cudaErrorInvalidValue;
+  }
+  if (colscale_parts != nullptr && (!swapped || n_colscale_parts < 1 ||
+                                    n_splits != (cluster_reduce > 1 ? cluster_reduce : 1))) {
     return (int)cudaErrorInvalidValue;
   }
   CUtensorMap map_r, map_c;
@@ -380,10 +452,12 @@ TK_API int tk_gemm_bf16_tcgen05(const void* r, const void* c, void* out, int* er
   tk::GemmTcParams p;
   p.out = out; p.err = err; p.rows_total = rows; p.cols_total = cols; p.k_total = k; p.bn = bn;
   p.n_stages = n_stages; p.n_splits = n_splits; p.swapped = swapped; p.out_f32 = out_f32; p.ld_out = ld_out; p.cluster_reduce = cluster_reduce; p.epilogue = epilogue;
+  p.colscale_parts = colscale_parts; p.n_colscale_parts = n_colscale_parts; p.colscale_inv_dim = colscale_inv_dim;
+  p.colscale_eps = colscale_eps; p.resid = resid; p.norm_w = norm_w; p.xb_out = (__nv_bfloat16*)xb_out; p.sumsq_out = sumsq_out;
   dim3 grid((rows + tk::kGtBM - 1) / tk::kGtBM, (cols + bn - 1) / bn, n_splits);
-  if (cluster_reduce > 1 || epilogue != 0) {
-    // the staging area [bn][128] floats must fit into the ring of stages
-    if ((size_t)bn * tk::kGtBM * 4 > (size_t)n_stages * stage_bytes) return (int)cudaErrorInvalidValue;
+  if (cluster_reduce > 1 || epilogue != 0 || colscale_parts != nullptr) {
+    // the staging area [bn][128] floats and the column scales must fit into the ring of stages
+    if ((size_t)bn * tk::kGtBM * 4 + (size_t)bn * 4 > (size_t)n_stages * stage_bytes) return (int)cudaErrorInvalidValue;
     return (int)tk::launch_cluster_z(tk::gemm_tcgen05_kernel, grid, dim3(tk::kGtThreads), smem_bytes, stream,
                                      (unsigned)(cluster_reduce > 1 ? cluster_reduce : 1), map_r, map_c, p);
   }

@@ -385,7 +385,8 @@ SWIGLU_TILE_BLOCK = 64     # gate/up rows alternate in blocks of this many for t
 
 def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_splits: int,
                     out: torch.Tensor | None = None, max_stages: int = 0, cluster: int = 0,
-                    swiglu: bool = False) -> torch.Tensor:
+                    swiglu: bool = False, colscale: tuple | None = None,
+                    residual_norm: tuple | None = None):
     """``x @ weight^T`` on tcgen05, the weight being the 128-row operand (for few tokens: every
     weight byte is streamed once by TMA), as float32 partial sums ``[parts, tokens, N_out]`` for
     the caller to add up.  ``parts = n_splits``, or ``n_splits / cluster`` with ``cluster`` in
@@ -394,7 +395,16 @@ def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_
 
     ``swiglu=True``: the weight is a stacked gate/up matrix whose rows alternate in blocks of
     ``SWIGLU_TILE_BLOCK`` (gate rows, then the up rows of the same outputs); all splits form one
-    cluster and the result is bfloat16 ``[tokens, N_out / 2] = silu(gate) * up``."""
+    cluster and the result is bfloat16 ``[tokens, N_out / 2] = silu(gate) * up``.
+
+    ``colscale=(sumsq, dim, eps)`` with ``sumsq`` float32 ``[tiles, tokens]``: every token's sums
+    are multiplied by ``rsqrt(sum over tiles / dim + eps)`` (all splits in one cluster): ``x``
+    then holds activations whose RMS scale is still owed.
+
+    ``residual_norm=(resid, norm_weight)`` (all splits in one cluster, ``N_out`` a multiple of
+    128): the sums are added to the float32 residual stream ``resid [tokens, N_out]`` in place and
+    ``(xb, sumsq)`` is returned: ``xb = bf16(resid * norm_weight)`` and the tiles' sums of squares
+    ``[N_out / 128, tokens]``, ready to be the ``x`` and ``colscale`` of the next product."""
     _want(weight, torch.bfloat16, "weight"); _want(x, torch.bfloat16, "x")
     n_out, k = weight.shape
     tokens, kx = x.shape
@@ -408,18 +418,39 @@ def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_
     while bn < tokens:
         bn *= 2
     parts = n_splits // cluster if cluster > 1 else n_splits
-    if swiglu:
+    cs_ptr, cs_n, cs_inv, cs_eps = None, 0, 0.0, 0.0
+    if colscale is not None:
+        sumsq, dim, eps = colscale
+        _want(sumsq, torch.float32, "colscale sums")
+        if parts != 1 or sumsq.dim() != 2 or sumsq.shape[1] != tokens:
+            raise KernelError("colscale wants one cluster and sums of squares [tiles, tokens]")
+        cs_ptr, cs_n, cs_inv, cs_eps = sumsq.data_ptr(), sumsq.shape[0], 1.0 / dim, float(eps)
+    epilogue, resid_ptr, w_ptr, xb, sums_out, result = 0, None, None, None, None, None
+    if residual_norm is not None:
+        resid, norm_w = residual_norm
+        _want(resid, torch.float32, "resid"); _want(norm_w, torch.float32, "norm weight")
+        if swiglu or parts != 1 or n_out % 128 or resid.shape != (tokens, n_out) or norm_w.numel() != n_out:
+            raise KernelError("residual_norm wants one cluster, N_out a multiple of 128 and resid [tokens, N_out]")
+        xb = torch.empty((tokens, n_out), dtype=torch.bfloat16, device=x.device)
+        sums_out = torch.empty((n_out // 128, tokens), dtype=torch.float32, device=x.device)
+        epilogue, resid_ptr, w_ptr, result = 2, resid.data_ptr(), norm_w.data_ptr(), (xb, sums_out)
+        out_ptr = None
+    elif swiglu:
         if n_out % (2 * SWIGLU_TILE_BLOCK) or parts != 1:
             raise KernelError("the fused activation wants rows in blocks of 64 gate + 64 up and one cluster")
         if out is None:
             out = torch.empty((tokens, n_out // 2), dtype=torch.bfloat16, device=x.device)
-    elif out is None:
-        out = torch.empty((parts, tokens, n_out), dtype=torch.float32, device=x.device)
-    _check(library().tk_gemm_bf16_tcgen05(weight.data_ptr(), x.data_ptr(), out.data_ptr(), err.data_ptr(),
+        epilogue, out_ptr, result = 1, out.data_ptr(), out
+    else:
+        if out is None:
+            out = torch.empty((parts, tokens, n_out), dtype=torch.float32, device=x.device)
+        out_ptr, result = out.data_ptr(), out
+    _check(library().tk_gemm_bf16_tcgen05(weight.data_ptr(), x.data_ptr(), out_ptr, err.data_ptr(),
                                           n_out, tokens, k, k, k, 0, bn, n_splits, 1, 1, max_stages,
-                                          cluster if cluster > 1 else 0, 1 if swiglu else 0, _stream()),
+                                          cluster if cluster > 1 else 0, epilogue, cs_ptr, cs_n, cs_inv, cs_eps,
+                                          resid_ptr, w_ptr, _ptr(xb), _ptr(sums_out), _stream()),
            "gemm_tc_swapped")
-    return out
+    return result
 
 
 def swapped_gemm_plan(n_out: int, k: int, tokens: int = 8) -> tuple[int, int, int]:
@@ -450,7 +481,8 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, err: torch.Tensor, out_dtype:
     out = torch.empty((tokens, n_out), dtype=out_dtype, device=x.device)
     _check(library().tk_gemm_bf16_tcgen05(x.data_ptr(), weight.data_ptr(), out.data_ptr(), err.data_ptr(),
                                           tokens, n_out, k, k, k, n_out, bn, 1, 0,
-                                          1 if out_dtype == torch.float32 else 0, max_stages, 0, 0, _stream()),
+                                          1 if out_dtype == torch.float32 else 0, max_stages, 0, 0,
+                                          None, 0, 0.0, 0.0, None, None, None, None, _stream()),
            "gemm_tc")
     return out
 

@@ -6,7 +6,7 @@ from dataclasses import dataclass
 
 import torch
 
-from ..parts.base import BLOCKS, NORMS, Runtime, TensorReq
+from ..parts.base import BLOCKS, NORMS, OwedNorm, Runtime, TensorReq
 from ..parts.embedding import Embedding, EmbeddingSpec, Head, HeadSpec
 
 
@@ -86,10 +86,20 @@ class DecoderModel:
         """Float32 logits ``[len(step.logits_rows), vocab]`` for the rows asked for."""
         resid = self.embedding.forward(step)
         pending = None
-        for call in self.spec.schedule:
+        schedule = self.spec.schedule
+        for i, call in enumerate(schedule):
             view = step.cache.view(call.cache) if call.cache is not None else None
-            resid, pending = self.blocks[call.block].forward(resid, pending, step, view)
+            block = self.blocks[call.block]
+            if getattr(block, "TAKES_NEXT_NORM", False):
+                # the norm that will consume what the block leaves pending: the next block's, or the last
+                after = self.blocks[schedule[i + 1].block] if i + 1 < len(schedule) else None
+                next_norm = getattr(after, "entry_norm", None) if after is not None else self.final_norm
+                resid, pending = block.forward(resid, pending, step, view, next_norm=next_norm)
+            else:
+                resid, pending = block.forward(resid, pending, step, view)
         if step.n_want == 0:
             return torch.empty((0, self.spec.head.vocab_size), dtype=torch.float32, device=resid.device)
-        h = self.final_norm.add_norm(resid, pending, rows=step.logits_rows)
+        # every request brings one token and wants it: the wanted rows are all rows, in order
+        all_rows = step.n_want == step.n_tokens and step.max_q_len == 1
+        h = self.final_norm.add_norm(resid, pending, rows=None if all_rows and isinstance(pending, OwedNorm) else step.logits_rows)
         return self.head.forward(h, step.err)

@@ -80,7 +80,10 @@ class Attention:
     def cache_need(self) -> KVPagesNeed:
         return KVPagesNeed(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
 
-    def forward(self, h: torch.Tensor, step, cache_view) -> torch.Tensor:
+    TAKES_OWED_NORM = True     # the q|k|v product pays an owed norm scale in its epilogue
+    TAKES_THEN_NORM = True     # the output product can add itself to the residual stream
+
+    def forward(self, h, step, cache_view, then_norm=None):
         spec = self.spec
         n = h.shape[0]
         qkv = linear(h, self.w_qkv, err=step.err)
@@ -95,7 +98,7 @@ class Attention:
                     req_q_len=step.req_q_len, req_kv_len=step.req_kv_len)
         out = torch.empty_like(q)
         paged_attention(q, out, cache_view, step, scale=self.scale, window=spec.window)
-        return linear(out.view(n, spec.num_heads * spec.head_dim), self.w_o, err=step.err)
+        return linear(out.view(n, spec.num_heads * spec.head_dim), self.w_o, err=step.err, then_norm=then_norm)
 
 
 def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, scale: float,

@@ -25,6 +25,17 @@ block          ``expected_tensors(spec)``, ``__init__(spec, tensors, rt)``,
 No part knows which model it is in: it sees its spec, its tensors, the step's
 batch description and the view of its own cache.
 
+**Owed norms.**  In bfloat16 steps of few tokens the kernel of a product that ends a branch can
+add its sums to the residual stream itself and hand on the input of the *next* norm with the
+scaling by the statistic still owed (:class:`OwedNorm`); the product after that norm pays it in
+its epilogue, and the norm between them needs no kernel.  This is opt-in: a mixer or
+feed-forward with ``TAKES_THEN_NORM = True`` is called with ``then_norm=(resid, norm part)`` and
+may return an :class:`OwedNorm` prepared for that norm instead of its output; one with
+``TAKES_OWED_NORM = True`` may be handed an :class:`OwedNorm` as ``h`` (others get a tensor); a
+block with ``TAKES_NEXT_NORM = True`` is told which norm will consume what it leaves pending and
+names the norm that consumes its own input as ``entry_norm``.  Parts without these attributes
+never see any of it.
+
 Where a row says ``[N, hidden]`` a mixer or feed-forward may instead return what
 :func:`linear` gave it: a 3-D float32 tensor of partial sums ``[parts, N, hidden]``
 from a split-K product.  The norm that consumes it adds the parts up (a 32-bit sum);
@@ -104,8 +115,46 @@ BLOCKS = Registry("block")
 SWAPPED_GEMM_MAX_TOKENS = 64
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
-           err: torch.Tensor | None = None) -> torch.Tensor:
+@dataclass
+class OwedNorm:
+    """Input of a norm whose scaling by the statistic is still owed.
+
+    ``xb`` is ``bf16(residual * norm weight)`` (the residual stream already holds the sum),
+    ``sumsq`` the sums of squares of the residual rows in tiles ``[tiles, N]``: the normalised
+    rows are ``xb * rsqrt(sumsq.sum(0) / dim + eps)``.  ``norm`` is the norm part it was prepared
+    for.  :func:`linear` takes it in place of a tensor.
+    """
+
+    xb: torch.Tensor
+    sumsq: torch.Tensor
+    dim: int
+    eps: float
+    norm: Any
+
+    @property
+    def shape(self):
+        return self.xb.shape
+
+    @property
+    def dtype(self):
+        return self.xb.dtype
+
+    @property
+    def device(self):
+        return self.xb.device
+
+    def materialize(self) -> torch.Tensor:
+        """The normalised rows as an ordinary tensor (for a consumer that cannot pay the scale)."""
+        rstd = torch.rsqrt(self.sumsq.sum(0) / self.dim + self.eps)
+        return (self.xb.float() * rstd[:, None]).to(self.xb.dtype)
+
+    def rows(self, index: torch.Tensor) -> "OwedNorm":
+        return OwedNorm(self.xb.index_select(0, index.long()).contiguous(),
+                        self.sumsq.index_select(1, index.long()).contiguous(), self.dim, self.eps, self.norm)
+
+
+def linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
+           err: torch.Tensor | None = None, then_norm: tuple | None = None):
     """``x @ weight^T`` for ``weight`` of shape [out, in].
 
     float32: the engine's own FFMA kernel (no TF32, no tensor cores).
@@ -114,7 +163,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     operand, streamed once by TMA and split over K, the splits of a tile added up inside a
     thread-block cluster.  The result is a 3-D float32 tensor ``[parts, tokens, out]`` (one
     or two parts) which the consuming kernel (norm, rotation, activation) adds up; ``err`` is the
-    error word its bounded waits report to.
+    error word its bounded waits report to.  On this path ``x`` may be an :class:`OwedNorm` (the
+    kernel multiplies its sums by the owed scale), and with ``then_norm=(resid, norm part)`` the
+    kernel adds its sums to the float32 residual stream ``resid`` itself and an :class:`OwedNorm`
+    for that norm is returned instead of the product (where the sizes allow it; otherwise the
+    product is returned as usual).
 
     bfloat16, many tokens: the persistent tcgen05 kernel on pairs of SMs (``ops.gemm_pair``)
     where its grid fills the GPU; otherwise the library product, as the reference uses the
@@ -127,7 +180,21 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
         return ops.gemm_f32(x, weight)
     if err is not None and x.shape[0] <= SWAPPED_GEMM_MAX_TOKENS and weight.shape[1] % 8 == 0:
         splits, stages, cluster = ops.swapped_gemm_plan(weight.shape[0], weight.shape[1], x.shape[0])
-        return ops.gemm_tc_swapped(weight, x, err, splits, max_stages=stages, cluster=cluster)
+        colscale = None
+        if isinstance(x, OwedNorm):
+            colscale, x = (x.sumsq, x.dim, x.eps), x.xb
+        if then_norm is not None:
+            resid, norm = then_norm
+            params = norm.owed_norm_params() if hasattr(norm, "owed_norm_params") else None
+            if (params is not None and weight.shape[0] % 128 == 0 and resid.dtype == torch.float32
+                    and resid.shape == (x.shape[0], weight.shape[0])):
+                norm_weight, eps = params
+                xb, sumsq = ops.gemm_tc_swapped(weight, x, err, splits, max_stages=stages, cluster=cluster,
+                                                colscale=colscale, residual_norm=(resid, norm_weight))
+                return OwedNorm(xb, sumsq, weight.shape[0], eps, norm)
+        return ops.gemm_tc_swapped(weight, x, err, splits, max_stages=stages, cluster=cluster, colscale=colscale)
+    if isinstance(x, OwedNorm):
+        x = x.materialize()
     if out_dtype is not None and out_dtype != x.dtype:
         return torch.mm(x, weight.t(), out_dtype=out_dtype)
     if err is not None and ops.pair_gemm_takes(x.shape[0], weight.shape[0], weight.shape[1]):

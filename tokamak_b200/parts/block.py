@@ -6,7 +6,7 @@ from dataclasses import dataclass
 
 import torch
 
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Runtime, TensorReq
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, OwedNorm, Runtime, TensorReq
 
 
 @dataclass(frozen=True)
@@ -38,7 +38,14 @@ class PreNormBlock:
     has not been added to it yet; each norm call adds the pending branch and
     normalises the sum in one kernel.  The second branch's output is returned as
     the new pending value, to be added by whoever normalises next.
+
+    Where a branch can, its last product adds itself to the residual stream and prepares
+    the input of the norm after it (see ``parts/base.py``, owed norms): the mixer for
+    ``norm2``, the feed-forward for ``next_norm``, the norm that will consume what this
+    block leaves pending.
     """
+
+    TAKES_NEXT_NORM = True
 
     def __init__(self, spec: PreNormBlockSpec, tensors: dict[str, torch.Tensor], rt: Runtime):
         self.spec = spec
@@ -61,8 +68,21 @@ class PreNormBlock:
     def cache_need(self):
         return self.mixer.cache_need()
 
-    def forward(self, resid: torch.Tensor, pending: torch.Tensor | None, step, cache_view):
+    @property
+    def entry_norm(self):
+        return self.norm1
+
+    @staticmethod
+    def _branch(part, h, args: tuple, then_norm):
+        if isinstance(h, OwedNorm) and not getattr(part, "TAKES_OWED_NORM", False):
+            h = h.materialize()
+        if then_norm is not None and getattr(part, "TAKES_THEN_NORM", False):
+            return part.forward(h, *args, then_norm=then_norm)
+        return part.forward(h, *args)
+
+    def forward(self, resid: torch.Tensor, pending, step, cache_view, next_norm=None):
         h = self.norm1.add_norm(resid, pending)
-        a = self.mixer.forward(h, step, cache_view)
+        a = self._branch(self.mixer, h, (step, cache_view), (resid, self.norm2))
         h = self.norm2.add_norm(resid, a)
-        return resid, self.feed_forward.forward(h, step)
+        out = self._branch(self.feed_forward, h, (step,), (resid, next_norm) if next_norm is not None else None)
+        return resid, out

@@ -7,7 +7,7 @@ from dataclasses import dataclass
 import torch
 
 from ..csrc import ops
-from .base import FEED_FORWARDS, SWAPPED_GEMM_MAX_TOKENS, Runtime, TensorReq, linear
+from .base import FEED_FORWARDS, SWAPPED_GEMM_MAX_TOKENS, OwedNorm, Runtime, TensorReq, linear
 
 
 @dataclass(frozen=True)
@@ -53,20 +53,29 @@ class SwiGLU:
             prefix + "down_proj.weight": TensorReq((h, i)),
         }
 
-    def forward(self, h: torch.Tensor, step) -> torch.Tensor:
+    TAKES_OWED_NORM = True     # the gate/up product pays an owed norm scale in its epilogue
+    TAKES_THEN_NORM = True     # the down product can add itself to the residual stream
+
+    def forward(self, h, step, then_norm=None):
         err = step.err if step is not None else None
-        if (h.dtype == torch.bfloat16 and err is not None and h.shape[0] <= SWAPPED_GEMM_MAX_TOKENS
+        n = h.shape[0]
+        if (h.dtype == torch.bfloat16 and err is not None and n <= SWAPPED_GEMM_MAX_TOKENS
                 and self.block == ops.SWIGLU_TILE_BLOCK and self.spec.hidden_size % 8 == 0):
-            splits, stages, cluster = ops.swapped_gemm_plan(2 * self.spec.intermediate_size, self.spec.hidden_size,
-                                                            h.shape[0])
+            splits, stages, cluster = ops.swapped_gemm_plan(2 * self.spec.intermediate_size, self.spec.hidden_size, n)
+            colscale = None
+            if isinstance(h, OwedNorm):
+                colscale, h = (h.sumsq, h.dim, h.eps), h.xb
             act = ops.gemm_tc_swapped(self.w_gate_up, h, err, splits, max_stages=stages, cluster=cluster,
-                                      swiglu=True)
-        elif (h.dtype == torch.bfloat16 and err is not None and self.block == ops.SWIGLU_TILE_BLOCK
-              and ops.pair_gemm_takes(h.shape[0], 2 * self.spec.intermediate_size, self.spec.hidden_size, fused=True)):
-            # many tokens: the product on pairs of SMs applies the activation to its accumulators
-            act = ops.gemm_pair(h, self.w_gate_up, err, swiglu=True)
+                                      swiglu=True, colscale=colscale)
         else:
-            gate_up = linear(h, self.w_gate_up, err=err)
-            act = torch.empty((h.shape[0], self.spec.intermediate_size), dtype=h.dtype, device=h.device)
-            ops.swiglu(gate_up, act, block=self.block)
-        return linear(act, self.w_down, err=err)
+            if isinstance(h, OwedNorm):
+                h = h.materialize()
+            if (h.dtype == torch.bfloat16 and err is not None and self.block == ops.SWIGLU_TILE_BLOCK
+                    and ops.pair_gemm_takes(n, 2 * self.spec.intermediate_size, self.spec.hidden_size, fused=True)):
+                # many tokens: the product on pairs of SMs applies the activation to its accumulators
+                act = ops.gemm_pair(h, self.w_gate_up, err, swiglu=True)
+            else:
+                gate_up = linear(h, self.w_gate_up, err=err)
+                act = torch.empty((n, self.spec.intermediate_size), dtype=h.dtype, device=h.device)
+                ops.swiglu(gate_up, act, block=self.block)
+        return linear(act, self.w_down, err=err, then_norm=then_norm)

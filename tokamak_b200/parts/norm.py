@@ -7,7 +7,7 @@ from dataclasses import dataclass
 import torch
 
 from ..csrc import ops
-from .base import NORMS, Runtime, TensorReq
+from .base import NORMS, OwedNorm, Runtime, TensorReq
 
 
 @dataclass(frozen=True)
@@ -35,14 +35,23 @@ class RMSNorm:
     def expected_tensors(spec: RMSNormSpec, name: str) -> dict[str, TensorReq]:
         return {name: TensorReq((spec.dim,), role="vector")}
 
-    def add_norm(self, resid: torch.Tensor, delta: torch.Tensor | None,
-                 rows: torch.Tensor | None = None) -> torch.Tensor:
+    def owed_norm_params(self) -> tuple[torch.Tensor, float] | None:
+        """Weight and eps for a product kernel that prepares this norm's input itself."""
+        return self.weight, self.spec.eps
+
+    def add_norm(self, resid: torch.Tensor, delta, rows: torch.Tensor | None = None):
         """Normalised rows in the engine's dtype.
 
         Without ``rows`` the sum ``resid + delta`` is written back to ``resid`` and
         every row is normalised.  With ``rows`` only those rows are summed and
-        normalised and ``resid`` is left as it is.
+        normalised and ``resid`` is left as it is.  ``delta`` may be an
+        :class:`OwedNorm`: the branch has been added to ``resid`` already; if it was
+        prepared for this norm it is handed on as it is (its consumer pays the scale).
         """
+        if isinstance(delta, OwedNorm):
+            if delta.norm is self:
+                return delta if rows is None else delta.rows(rows)
+            delta = None
         n = rows.numel() if rows is not None else resid.shape[0]
         out = torch.empty((n, self.spec.dim), dtype=self.rt.dtype, device=resid.device)
         ops.add_rmsnorm(resid, delta, self.weight, out, self.spec.eps, rows)
