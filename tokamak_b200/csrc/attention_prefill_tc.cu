@@ -52,6 +52,33 @@ struct AttnTcParams {
   float scale_log2;
 };
 
+// Two float32 operations in one instruction (sm_100): the softmax warps are bound by the
+// instructions they issue, so halving the multiply-adds and additions shows.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  uint64_t ra, rb, rc, rd;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+  float2 d;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+  return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  uint64_t ra, rb, rd;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+  float2 d;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
@@ -304,9 +331,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       float sv[kAtBN];
       if (interior) {
 #pragma unroll
-        for (int c = 0; c < kAtBN; ++c) {
+        for (int c = 0; c < kAtBN; c += 2) {
           sv[c] = __uint_as_float(sraw[c]);
-          mx = fmaxf(mx, sv[c]);
+          sv[c + 1] = __uint_as_float(sraw[c + 1]);
+          mx = max3(mx, sv[c], sv[c + 1]);
         }
       } else {
 #pragma unroll
@@ -342,13 +370,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
       }
       const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
-      float psum = 0.0f;
+      float2 psum = make_float2(0.0f, 0.0f);
+      const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), shift2 = make_float2(-m_use, -m_use);
 #pragma unroll
-      for (int c = 0; c < kAtBN; ++c) {
-        sv[c] = ex2_approx(fmaf(sv[c], p.scale_log2, -m_use));
-        psum += sv[c];
+      for (int c = 0; c < kAtBN; c += 2) {
+        const float2 x = fma2(make_float2(sv[c], sv[c + 1]), scale2, shift2);
+        sv[c] = ex2_approx(x.x);
+        sv[c + 1] = ex2_approx(x.y);
+        psum = add2(psum, make_float2(sv[c], sv[c + 1]));
       }
-      l_sum += psum;
+      l_sum += psum.x + psum.y;
 
       if (j >= 2) {     // the probability tile is free once the second product of key tile j - 2 is done
         ok = __all_sync(0xffffffffu, mbar_wait(p_empty(t, b), (uint32_t)((j - 2) >> 1) & 1u, abort_flag));
