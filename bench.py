@@ -40,6 +40,11 @@ QWEN3_8B = {
     "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
     "max_position_embeddings": 40960,
 }
+QWEN3_14B = dict(QWEN3_8B, num_hidden_layers=40, hidden_size=5120, num_attention_heads=40,
+                 intermediate_size=17408)
+QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64,
+                 intermediate_size=25600)
+SIZES = {"8b": ("Qwen3-8B", QWEN3_8B), "14b": ("Qwen3-14B", QWEN3_14B), "32b": ("Qwen3-32B", QWEN3_32B)}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
@@ -434,7 +439,9 @@ def main() -> int:
     ap.add_argument("--ctx", type=int, default=CONTEXT, help="context length of a --kernel case")
     ap.add_argument("--workload", default=None, choices=["throughput"],
                     help="run the reference's throughput workload through LLM.generate instead")
-    ap.add_argument("--sizes", default="8b", choices=["0.6b", "8b"], help="layer sizes of --workload")
+    ap.add_argument("--sizes", default="8b", choices=["0.6b", "8b", "14b", "32b"],
+                    help="layer sizes: of --workload (0.6b, 8b), or of the decode/prefill run (8b, the metric's "
+                         "own, 14b, 32b)")
     ap.add_argument("--num-requests", type=int, default=32)
     ap.add_argument("--max-new-cap", type=int, default=256)
     ap.add_argument("--kv-pool-tokens", type=int, default=16384)
@@ -462,7 +469,10 @@ def main() -> int:
     import torch
     from tokamak_b200.engine.core import random_core
 
-    raw = dict(QWEN3_8B)
+    if args.sizes not in SIZES:
+        raise SystemExit("--sizes 0.6b is for --workload throughput only")
+    model_name, sizes = SIZES[args.sizes]
+    raw = dict(sizes)
     n_layers = args.layers or raw["num_hidden_layers"]
     raw["num_hidden_layers"] = n_layers
     vocab = raw["vocab_size"]
@@ -489,13 +499,13 @@ def main() -> int:
     pf_flops = step_flops(raw, n_layers, PREFILL_TOKENS)
     pf_frac = pf_flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12)
     line = {
-        "metric": "decode tok/s at batch 8 (Qwen3-8B layer sizes, context 4096)",
+        "metric": f"decode tok/s at batch {args.batch} ({model_name} layer sizes, context {CONTEXT})",
         "value": round(main_run["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
         "warmup": warmup, "ms_per_step": round(main_run["ms_per_step"], 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded random weights N(0, 0.02), uniform random token ids",
         "config": {
-            "model": "Qwen3-8B layer sizes", "layers": n_layers, "layers_of_model": 36,
+            "model": f"{model_name} layer sizes", "layers": n_layers, "layers_of_model": sizes["num_hidden_layers"],
             "hidden": raw["hidden_size"], "q_heads": raw["num_attention_heads"],
             "kv_heads": raw["num_key_value_heads"], "head_dim": raw["head_dim"],
             "intermediate": raw["intermediate_size"], "vocab": vocab, "rope_theta": raw["rope_theta"],
