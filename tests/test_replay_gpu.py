@@ -138,3 +138,53 @@ def test_trace_run_program(tmp_path):
     vocab = tiny_configs.ALL[tag][0]["vocab_size"]
     results = {s: np.fromfile(out / f"{s}.f32", dtype="<f4").reshape(-1, vocab) for s in rows}
     traces.check(results, rows, reqs, folder, dtype, "trace_run")
+
+
+def _random_config(seed: int) -> tuple[dict, int]:
+    """A Qwen3 configuration drawn at random from what the configuration allows: head sizes in
+    steps of 16, any number of heads and groups, widths and vocabularies that are no powers of two,
+    one to three layers, with or without a window, tied or untied head."""
+    import random
+    rng = random.Random(seed)
+    kv = rng.choice([1, 2, 3, 4])
+    heads = kv * rng.choice([1, 2, 3, 5])
+    cfg = {
+        "architectures": ["Qwen3ForCausalLM"],
+        "num_hidden_layers": rng.choice([1, 2, 3]),
+        "hidden_size": 8 * rng.randrange(4, 30),
+        "num_attention_heads": heads, "num_key_value_heads": kv,
+        "head_dim": 16 * rng.randrange(1, 9),
+        "intermediate_size": 8 * rng.randrange(5, 40),
+        "vocab_size": rng.randrange(90, 400),
+        "rope_theta": rng.choice([1e4, 5e4, 1e6]),
+        "rms_norm_eps": rng.choice([1e-6, 1e-5]),
+        "tie_word_embeddings": rng.random() < 0.5,
+        "max_position_embeddings": 256,
+    }
+    if rng.random() < 0.4:
+        cfg.update({"use_sliding_window": True, "sliding_window": rng.randrange(5, 60),
+                    "max_window_layers": rng.randrange(0, cfg["num_hidden_layers"])})
+    return cfg, rng.choice([8, 16, 32])
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_configurations_drawn_at_random(seed, tmp_path):
+    """Mixed replay with page reuse, in float32 and in bfloat16, for configurations drawn at random."""
+    from tokamak_b200.engine.replay import build_core, run_step
+    from tokamak_b200.weights import write_random_model
+    cfg, page = _random_config(seed)
+    lengths = [3, 47, 130, 64, 21, 90]
+    reqs = {f"q{i}": random_tokens(cfg["vocab_size"], n, seed=31 * i + seed) for i, n in enumerate(lengths)}
+    for dtype in DTYPES:
+        folder = write_random_model(tmp_path / dtype, cfg, seed=seed, std=0.08, dtype=dtype)
+        records, rows = traces.mixed(reqs, max_tokens=256, max_live=3, seed=seed)
+        core = build_core(folder, dtype, 256, page_size=page, max_live=3)
+        results = {}
+        for rec in records:
+            core.cache.poison_free_pages()
+            out = run_step(core, rec)
+            if out is not None:
+                results[rec["step"]] = out
+            core.manager.check_invariants()
+        assert not core.manager.live_requests()
+        traces.check(results, rows, reqs, folder, dtype, f"random configuration {seed} ({cfg}) in {dtype}")
