@@ -297,6 +297,44 @@ def throughput_workload(sizes: str, num_requests: int, max_new_cap: int, batch: 
             "preemptions": llm.last_stats["preemptions"], "dtype": "bf16", "data": "synthetic"}
 
 
+def latency_workload(sizes: str, prompt_tokens: int, new_tokens: int, iters: int, seed: int) -> dict:
+    """Single-sequence latency as the reference measures it (benchmarks/benchmark_latency.py:63-97,
+    119-133): one seeded random prompt, time to the first token (prefill, argmax on the host side
+    of a sync), then greedy steps one by one with the token read back every step; medians of
+    ``iters`` runs after a warm-up."""
+    import torch
+    from tokamak_b200.engine.core import random_core
+    from tokamak_b200.engine.step import SamplingRow, StepEntry
+    raw = dict(QWEN3_0_6B if sizes == "0.6b" else SIZES[sizes][1])
+    total = prompt_tokens + new_tokens
+    core = random_core(raw, seed=0, std=0.02, dtype="bfloat16", max_seq_len=total, page_size=16,
+                       pool_tokens=2 * total, max_slots=2, max_step_tokens=max(prompt_tokens, 64))
+    gen = torch.Generator().manual_seed(seed)
+    prompt = torch.randint(0, raw["vocab_size"], (prompt_tokens,), generator=gen).tolist()
+    greedy = [SamplingRow()]
+
+    def run_once(i: int) -> tuple[float, float]:
+        rid = f"lat{i}"
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        token = core.step.run_and_sample([StepEntry(rid, prompt, [prompt_tokens - 1])], greedy)[0]
+        t1 = time.perf_counter()
+        for _ in range(new_tokens):
+            token = core.step.run_and_sample([StepEntry(rid, [token], [0])], greedy)[0]
+        t2 = time.perf_counter()
+        core.step.free(rid)
+        return (t1 - t0) * 1e3, new_tokens / (t2 - t1)
+
+    run_once(-1)
+    runs = [run_once(i) for i in range(iters)]
+    prefill_ms = statistics.median(r[0] for r in runs)
+    tok_s = statistics.median(r[1] for r in runs)
+    return {"workload": "latency (reference's single-sequence measurement)", "sizes": f"Qwen3-{sizes.upper()} layer sizes",
+            "prompt_tokens": prompt_tokens, "new_tokens": new_tokens, "prefill_ms": round(prefill_ms, 3),
+            "prefill_tok_s": round(prompt_tokens / (prefill_ms / 1e3), 1), "decode_tok_s": round(tok_s, 1),
+            "inter_token_ms": round(1e3 / tok_s, 3), "iters": iters, "dtype": "bf16", "data": "synthetic"}
+
+
 def kernel_case(name: str, batch: int, ctx: int, iters: int, peaks: dict) -> dict:
     """One kernel alone on inputs larger than L2, timed with CUDA events: achieved bytes or flops
     per second against the peak.  Also the small case that ncu captures are made on."""
@@ -437,8 +475,9 @@ def main() -> int:
                     "attention_prefill (tcgen05), attention_prefill_mma, rope_kv, rmsnorm, gemm_tc_decode, gemm_decode (library), "
                     "gemm_pair_swiglu, gemm_prefill_library (--ctx tokens)")
     ap.add_argument("--ctx", type=int, default=CONTEXT, help="context length of a --kernel case")
-    ap.add_argument("--workload", default=None, choices=["throughput"],
-                    help="run the reference's throughput workload through LLM.generate instead")
+    ap.add_argument("--workload", default=None, choices=["throughput", "latency"],
+                    help="run the reference's throughput workload through LLM.generate, or its single-sequence "
+                         "latency measurement (512 prompt tokens, 128 greedy steps), instead")
     ap.add_argument("--sizes", default="8b", choices=["0.6b", "8b", "14b", "32b"],
                     help="layer sizes: of --workload (0.6b, 8b), or of the decode/prefill run (8b, the metric's "
                          "own, 14b, 32b)")
@@ -460,6 +499,9 @@ def main() -> int:
     steps = max(1, args.steps)
     if args.kernel:
         print(json.dumps(kernel_case(args.kernel, args.batch, args.ctx, steps, load_peaks())))
+        return 0
+    if args.workload == "latency":
+        print(json.dumps(latency_workload(args.sizes, 512, 128, 3, args.seed)))
         return 0
     if args.workload == "throughput":
         print(json.dumps(throughput_workload(args.sizes, args.num_requests, args.max_new_cap, args.batch,
