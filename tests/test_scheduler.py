@@ -155,3 +155,51 @@ def test_stop_rules_in_the_reference_order():
         c.append_output_token(1)
     with pytest.raises(ValueError):
         Sequence(3, [], SamplingParams())
+
+
+def test_plan_ahead_only_when_the_next_step_is_certain():
+    """The step after a decode step may be planned before its tokens are known: same sequences,
+    one position on; not while a prompt portion runs, somebody waits, or pages are short; and
+    sequences that reach their length limit in the running step drop out."""
+    m, s = make(num_pages=8, page=4, budget=64)
+    a, b = seq(0, 5, max_new=3), seq(1, 6, max_new=8)
+    s.add(a); s.add(b)
+    limit = lambda q: 10 ** 6
+    first = s.schedule()                                # both prompts whole
+    assert s.plan_ahead(first, limit) is None           # prompt portions: the next step depends on nothing certain
+    run_plan(m, first)
+    dec = s.schedule()
+    assert describe(dec) == [(0, 5, 1, True), (1, 6, 1, True)]
+    for e in dec.entries:                               # what the engine does at launch
+        m.advance(e.seq.seq_id, e.count)
+        e.seq.num_computed = e.start + e.count
+    ahead = s.plan_ahead(dec, limit)
+    assert describe(ahead) == [(0, 6, 1, True), (1, 7, 1, True)]
+    assert m.length(0) == 6 and m.length(1) == 7        # lengths advance at launch, not at planning
+    for e in dec.entries:                               # the tokens of the running step arrive
+        e.seq.append_checked(9, eos_token_ids=(), max_total_tokens=10 ** 6)
+    for e in ahead.entries:
+        m.advance(e.seq.seq_id, e.count)
+        e.seq.num_computed = e.start + e.count
+    # sequence 0 has two of its three tokens: the step in flight gives the third, so it drops out
+    nxt = s.plan_ahead(ahead, limit)
+    assert describe(nxt) == [(1, 8, 1, True)]
+    # a context limit does the same
+    assert s.plan_ahead(ahead, lambda q: q.num_tokens + 1) is None
+    # somebody waiting: the scheduler has to look at admissions first
+    s.add(seq(2, 3))
+    assert s.plan_ahead(ahead, limit) is None
+
+
+def test_plan_ahead_gives_up_when_pages_are_short():
+    m2, s2 = make(num_pages=2, page=4, budget=64)
+    c = seq(1, 7, max_new=8)
+    s2.add(c)
+    run_plan(m2, s2.schedule())                         # 7 computed, token 8 sampled
+    dec = s2.schedule()                                 # position 7: still inside page 2
+    assert describe(dec) == [(1, 7, 1, True)]
+    for e in dec.entries:
+        m2.advance(e.seq.seq_id, e.count)
+        e.seq.num_computed = e.start + e.count
+    assert s2.plan_ahead(dec, lambda q: 10 ** 6) is None    # position 8 would need a third page
+    m2.check_invariants()

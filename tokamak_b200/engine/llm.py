@@ -22,8 +22,7 @@ from .core import EngineCore
 from .outputs import RequestOutput
 from dataclasses import dataclass
 
-from ..cache.manager import OutOfPagesError
-from .scheduler import PlannedEntry, Scheduler, StepPlan
+from .scheduler import Scheduler, StepPlan
 from .sequence import Sequence
 from .step import PendingStep, SamplingRow, StepEntry
 
@@ -178,7 +177,7 @@ class LLM:
                 # the step after a step of single next tokens is known but for the tokens, which
                 # stay on the device: it is launched before this step's tokens are read
                 ahead = None
-                plan_ahead = self._plan_ahead(scheduler, flight)
+                plan_ahead = scheduler.plan_ahead(flight.plan, self._max_total_tokens)
                 if plan_ahead is not None:
                     ahead = self._launch(plan_ahead, flight)
                 done = self._complete(flight, ahead)
@@ -236,34 +235,6 @@ class LLM:
             e.seq.num_computed = e.start + e.count
         pending = self.core.step.launch_and_sample(entries, rows, feed if fed_by is not None else None)
         return _Flight(plan, pending, samplers)
-
-    def _plan_ahead(self, scheduler: Scheduler, flight: "_Flight") -> StepPlan | None:
-        """The step after ``flight`` if it is certain but for the token values: ``flight`` is a
-        step of single next tokens of every running sequence, nothing waits for admission, and
-        the pages for one more token are there.  Sequences that reach their length limit in
-        ``flight`` drop out; one that turns out to have stopped on an end-of-sequence token is
-        in the step for nothing, and its token is thrown away."""
-        plan = flight.plan
-        if any(e.count != 1 or not e.samples for e in plan.entries):
-            return None
-        going = [e for e in plan.entries if not e.seq.is_finished]
-        if scheduler.waiting or len(going) != sum(1 for s in scheduler.running if not s.is_finished):
-            return None
-        entries = []
-        for e in going:
-            seq = e.seq
-            if (seq.num_output_tokens + 1 >= seq.sampling_params.max_new_tokens
-                    or seq.num_tokens + 1 >= self._max_total_tokens(seq)):
-                continue
-            entries.append(PlannedEntry(seq, e.start + 1, 1, samples=True))
-        if not entries:
-            return None
-        try:
-            for e in entries:
-                self.cache_manager.grow(e.seq.seq_id, e.start + 1)
-        except OutOfPagesError:
-            return None         # the scheduler decides who gives way, once this step has been read
-        return StepPlan(entries)
 
     def _complete(self, flight: "_Flight", ahead: "_Flight | None") -> int:
         """Read a step's tokens, append them and free what finished."""

@@ -142,6 +142,38 @@ class Scheduler:
                 continue
             return None
 
+    def plan_ahead(self, plan: StepPlan, max_total_tokens) -> StepPlan | None:
+        """The step after ``plan``, decided before ``plan``'s tokens are known, or ``None``.
+
+        It exists when it is certain but for the token values: ``plan`` is a step of single
+        next tokens of every running sequence, every one of them sampling, nothing waits for
+        admission, and the pages for one more token are there.  Sequences that reach a length
+        limit in ``plan`` (``max_new_tokens``, or ``max_total_tokens(seq)``) drop out.  A
+        sequence that turns out to have stopped on an end-of-sequence token in ``plan`` is in
+        the step for nothing; the engine throws its token away.  When pages are short the answer
+        is ``None``: who gives way is decided by ``schedule`` once ``plan`` has been read.
+        """
+        if any(e.count != 1 or not e.samples for e in plan.entries):
+            return None
+        going = [e for e in plan.entries if not e.seq.is_finished]
+        if self.waiting or len(going) != sum(1 for s in self.running if not s.is_finished):
+            return None
+        entries = []
+        for e in going:
+            seq = e.seq
+            if (seq.num_output_tokens + 1 >= seq.sampling_params.max_new_tokens
+                    or seq.num_tokens + 1 >= max_total_tokens(seq)):
+                continue
+            entries.append(PlannedEntry(seq, e.start + 1, 1, samples=True))
+        if not entries:
+            return None
+        try:
+            for e in entries:
+                self._manager.grow(e.seq.seq_id, e.start + 1)
+        except OutOfPagesError:
+            return None
+        return StepPlan(entries)
+
     # ------------------------------------------------------------------------------
     def _fits_new(self, seq: Sequence) -> bool:
         return all(g.pages_for(seq.num_tokens) <= g.num_free for g in self._manager.kv_groups)
