@@ -1,23 +1,20 @@
-// bfloat16 matrix product on the 5th-generation tensor cores:
-//   D[i, j] = sum_k R[i, k] * C[j, k]      (both operands K-major, float32 accumulation)
+// bfloat16 matrix product for few tokens (decoding) on the 5th-generation tensor cores:
+//   D[t, n] = sum_k X[t, k] * W[n, k]      (both operands K-major, float32 accumulation)
 //
-// One thread block per (128-row tile of R, BN-column tile of C, K split).  Operand
-// tiles of 64 k-elements travel global -> shared memory by TMA (cp.async.bulk.tensor,
-// 128-byte swizzle, every block for itself) into a ring of stages guarded by mbarriers; one
-// elected thread issues tcgen05.mma (M = 128, N = BN, K = 16) with the accumulator in
-// tensor memory; four epilogue warps read the accumulator with tcgen05.ld and store it.
+// The weight is the 128-row operand of the MMA and the tokens (at most 256, usually 1 to 64) its
+// N side, so every byte of the weights is streamed exactly once.  One thread block per (128-row
+// tile of W, token tile, K split).  Operand tiles of 64 k-elements travel global -> shared memory
+// by TMA (cp.async.bulk.tensor, 128-byte swizzle, every block for itself) into a ring of stages
+// guarded by mbarriers; one elected thread issues tcgen05.mma (M = 128, N = token tile, K = 16)
+// with the accumulator in tensor memory; four epilogue warps read it with tcgen05.ld.
 //
-// Two uses:
-//  * decode ("swapped"): R = weight [N_out, K], C = activations [tokens <= 64, K].  The
-//    weights are the 128-row operand, so every byte of them is streamed exactly once
-//    through a deep TMA pipeline; the K range is split over blocks to fill the GPU.  The
-//    blocks of one output tile form a thread-block cluster: each stages its float32
-//    partial accumulator in its own shared memory, and every block adds up its share of
-//    the token columns over distributed shared memory, always in the same order, and
-//    stores the float32 result [1, token, N_out] (no atomics).  Without the cluster every split
-//    stores its partial [split, token, N_out] and the consuming kernel adds them up.
-//  * prefill: R = activations [tokens, K], C = weight [N_out, K], BN = 128 or 256,
-//    output rounded to bfloat16 (or kept float32) directly.
+// The K range is split over blocks to fill the GPU.  The blocks of one output tile form a
+// thread-block cluster: each stages its float32 partial accumulator in its own shared memory, and
+// every block adds up its share of the token columns over distributed shared memory, always in
+// the same order, and stores the float32 result [1, token, N_out] (no atomics).  Without the
+// cluster every split stores its partial [split, token, N_out] and the consuming kernel adds
+// them up.  The library's product takes the place of this kernel in the reference
+// (src/tokamak/model/transformer.py:38-41).
 //
 // Every wait on an mbarrier is bounded; a wait that runs out records kErrWait, raises a
 // block-wide abort flag and the block leaves through the common exit that frees its
@@ -29,12 +26,12 @@ namespace tk {
 constexpr int kGtBM = 128;        // rows of R per block = UMMA M
 constexpr int kGtBK = 64;         // k-elements per stage = one 128-byte swizzle span of bf16
 constexpr int kGtThreads = 192;   // warp 0: TMA, warp 1: MMA, warps 2..5: epilogue
-// Epilogue of the swapped form for a stacked gate/up weight whose rows alternate in blocks of
+// Epilogue for a stacked gate/up weight whose rows alternate in blocks of
 // 64 (64 gate rows, then the 64 up rows of the same outputs): a 128-row tile then holds both
 // halves of 64 outputs, and the block that adds the splits up stores
 // bf16(silu(gate) * up) as [token, rows / 2] instead of the float32 sums.
 constexpr int kGtEpiSwiglu = 1;
-// Epilogue of the swapped form for a product that ends a residual branch: the block that adds the
+// Epilogue for a product that ends a residual branch: the block that adds the
 // splits up adds the sums to the float32 residual stream in place, stores
 // bf16(residual * norm weight) for the product that follows the next RMSNorm, and the tile's
 // share of every token's sum of squares.  The consumer of these (see colscale below) multiplies
@@ -44,7 +41,7 @@ constexpr int kGtEpiSwiglu = 1;
 constexpr int kGtEpiResidualNorm = 2;
 
 struct GemmTcParams {
-  void* out;                // swapped: float [n_splits, cols_total, rows_total]; else [rows_total, cols_total]
+  void* out;                // float [parts, cols_total, rows_total], or what the epilogue stores
   int* err;
   int rows_total;           // rows of R
   int cols_total;           // rows of C (columns of D)
@@ -52,13 +49,11 @@ struct GemmTcParams {
   int bn;                   // UMMA N: 16..256, multiple of 16
   int n_stages;
   int n_splits;
-  int swapped;              // 1: store D transposed as float32 partials
-  int cluster_reduce;       // swapped only: 0, or the cluster size: that many consecutive splits of a tile
+  int cluster_reduce;       // 0, or the cluster size: that many consecutive splits of a tile
                             // form a cluster and store their sum as one part (n_splits / cluster parts)
-  int out_f32;              // non-swapped: 1 = float32 output, 0 = bfloat16
-  int epilogue;             // swapped only: 0 = float32 sums; 1 = gated activation, see kGtEpiSwiglu;
+  int epilogue;             // 0 = float32 sums; 1 = gated activation, see kGtEpiSwiglu;
                             // 2 = residual sum and preparation of the next norm, see kGtEpiResidualNorm
-  // swapped only: every column (token) of the sums is multiplied by
+  // every column (token) of the sums is multiplied by
   // rsqrt(sum_i colscale_parts[i, token] * colscale_inv_dim + colscale_eps) before it is stored
   const float* colscale_parts;
   int n_colscale_parts;
@@ -69,7 +64,6 @@ struct GemmTcParams {
   const float* norm_w;
   __nv_bfloat16* xb_out;
   float* sumsq_out;
-  long long ld_out;         // non-swapped: elements between output rows
 };
 
 __global__ void __launch_bounds__(kGtThreads, 1)
@@ -128,24 +122,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
   if (warp == 0) {
     // ---- TMA producer ---------------------------------------------------------------------
     if (lane == 0) {
-      // The first ring of stages: with weights as the row operand (which no kernel writes)
-      // their tiles are requested before the wait on the previous kernel, so they stream in
-      // while it finishes; the activation tiles follow after the wait.
+      // The first ring of stages: the weight tiles (which no kernel writes) are requested
+      // before the wait on the previous kernel, so they stream in while it finishes; the
+      // activation tiles follow after the wait.
       const int first = min(n_kb, p.n_stages);
-      const bool rows_are_weights = p.swapped != 0;
       for (int i = 0; i < first; ++i) {
         const uint32_t full = gt_smem_u32(&full_bar[i]);
         mbar_expect_tx(full, r_bytes + c_bytes);
-        if (rows_are_weights) {
-          tma_load_2d(base + (uint32_t)i * stage_bytes, &map_r, (kb_begin + i) * kGtBK, tile_r * kGtBM, full);
-        }
+        tma_load_2d(base + (uint32_t)i * stage_bytes, &map_r, (kb_begin + i) * kGtBK, tile_r * kGtBM, full);
       }
       pdl_wait();
       for (int i = 0; i < first; ++i) {
         const uint32_t full = gt_smem_u32(&full_bar[i]);
         const uint32_t dst = base + (uint32_t)i * stage_bytes;
         const int k0 = (kb_begin + i) * kGtBK;
-        if (!rows_are_weights) tma_load_2d(dst, &map_r, k0, tile_r * kGtBM, full);
         tma_load_2d(dst + r_bytes, &map_c, k0, tile_c * p.bn, full);
       }
       for (int i = first; i < n_kb; ++i) {
@@ -234,40 +224,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
         continue;
       }
       if (row >= p.rows_total) continue;
-      if (p.swapped) {
-        float* part = reinterpret_cast<float*>(p.out) + (size_t)split * p.cols_total * p.rows_total;
+      float* part = reinterpret_cast<float*>(p.out) + (size_t)split * p.cols_total * p.rows_total;
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const int col = tile_c * p.bn + c0 + e;              // token
-          if (col < p.cols_total) part[(size_t)col * p.rows_total + row] = __uint_as_float(v[e]);
-        }
-      } else if (p.out_f32) {
-        float* orow = reinterpret_cast<float*>(p.out) + (size_t)row * p.ld_out;
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const int col = tile_c * p.bn + c0 + e;
-          if (col < p.cols_total) orow[col] = __uint_as_float(v[e]);
-        }
-      } else {
-        __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.ld_out;
-        const int col0 = tile_c * p.bn + c0;
-        if (col0 + 16 <= p.cols_total && (p.ld_out % 8) == 0) {
-          uint4 lo, hi;
-          __nv_bfloat162* l2 = reinterpret_cast<__nv_bfloat162*>(&lo);
-          __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&hi);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            l2[e] = __floats2bfloat162_rn(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1]));
-            h2[e] = __floats2bfloat162_rn(__uint_as_float(v[8 + 2 * e]), __uint_as_float(v[8 + 2 * e + 1]));
-          }
-          *reinterpret_cast<uint4*>(orow + col0) = lo;
-          *reinterpret_cast<uint4*>(orow + col0 + 8) = hi;
-        } else {
-#pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            if (col0 + e < p.cols_total) orow[col0 + e] = __float2bfloat16_rn(__uint_as_float(v[e]));
-          }
-        }
+      for (int e = 0; e < 16; ++e) {
+        const int col = tile_c * p.bn + c0 + e;              // token
+        if (col < p.cols_total) part[(size_t)col * p.rows_total + row] = __uint_as_float(v[e]);
       }
     }
   }
@@ -389,31 +350,29 @@ static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long
 
 }  // namespace tk
 
-// D = R * C^T on tcgen05.  r: [rows, k] bf16 (row stride ld_r), c: [cols, k] bf16 (row stride ld_c).
-// swapped = 1: out is float32 [parts, cols, rows] (partials, to be summed by the consumer);
-// parts = n_splits, or n_splits / cluster_reduce when cluster_reduce > 1 (2..8, a divisor of
-// n_splits): that many consecutive splits form a thread-block cluster and store their sum.
-// swapped = 0: out is [rows, cols] with row stride ld_out, float32 if out_f32 else bfloat16; n_splits must be 1.
-// epilogue = 1 (swapped, rows a multiple of 128 whose gate and up rows alternate in blocks of 64, all
+// D^T = (R * C^T)^T on tcgen05.  r: [rows, k] bf16 (the weight, row stride ld_r), c: [cols, k] bf16
+// (the tokens, row stride ld_c).  out is float32 [parts, cols, rows] (partials, to be summed by the
+// consumer); parts = n_splits, or n_splits / cluster_reduce when cluster_reduce > 1 (2..8, a divisor
+// of n_splits): that many consecutive splits form a thread-block cluster and store their sum.
+// epilogue = 1 (rows a multiple of 128 whose gate and up rows alternate in blocks of 64, all
 // splits in one cluster): out is bfloat16 [cols, rows / 2] = silu(gate) * up.
-// epilogue = 2 (swapped, rows a multiple of 128, all splits in one cluster): nothing goes to out; the
+// epilogue = 2 (rows a multiple of 128, all splits in one cluster): nothing goes to out; the
 // sums are added to resid [cols, rows] (float32) in place, xb_out [cols, rows] receives
 // bf16(resid * norm_w) and sumsq_out [rows / 128, cols] the tiles' sums of squares of resid.
-// colscale_parts (swapped, or null): [n_colscale_parts, cols] float32; the sums of column c are
+// colscale_parts (or null): [n_colscale_parts, cols] float32; the sums of column c are
 // multiplied by rsqrt(sum_i colscale_parts[i, c] * colscale_inv_dim + colscale_eps).
 TK_API int tk_gemm_bf16_tcgen05(const void* r, const void* c, void* out, int* err, int rows, int cols, int k,
-                                long long ld_r, long long ld_c, long long ld_out, int bn, int n_splits,
-                                int swapped, int out_f32, int max_stages, int cluster_reduce, int epilogue,
+                                long long ld_r, long long ld_c, int bn, int n_splits,
+                                int max_stages, int cluster_reduce, int epilogue,
                                 const float* colscale_parts, int n_colscale_parts, float colscale_inv_dim,
                                 float colscale_eps, float* resid, const float* norm_w, void* xb_out,
                                 float* sumsq_out, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;
   if (k <= 0 || k % 8 != 0 || (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) || n_splits < 1 ||
-      (!swapped && n_splits != 1) ||
-      (cluster_reduce > 1 && (!swapped || cluster_reduce > 8 || n_splits % cluster_reduce != 0)) || cluster_reduce < 0) {
+      (cluster_reduce > 1 && (cluster_reduce > 8 || n_splits % cluster_reduce != 0)) || cluster_reduce < 0) {
     return (int)cudaErrorInvalidValue;
   }
-  if (epilogue != 0 && ((epilogue != tk::kGtEpiSwiglu && epilogue != tk::kGtEpiResidualNorm) || !swapped ||
+  if (epilogue != 0 && ((epilogue != tk::kGtEpiSwiglu && epilogue != tk::kGtEpiResidualNorm) ||
                         rows % 128 != 0 || n_splits != (cluster_reduce > 1 ? cluster_reduce : 1))) {
     return (int)cudaErrorInvalidValue;
   }
@@ -421,7 +380,7 @@ TK_API int tk_gemm_bf16_tcgen05(const void* r, const void* c, void* out, int* er
       (resid == nullptr || norm_w == nullptr || xb_out == nullptr || sumsq_out == nullptr)) {
     return (int)cudaErrorInvalidValue;
   }
-  if (colscale_parts != nullptr && (!swapped || n_colscale_parts < 1 ||
+  if (colscale_parts != nullptr && (n_colscale_parts < 1 ||
                                     n_splits != (cluster_reduce > 1 ? cluster_reduce : 1))) {
     return (int)cudaErrorInvalidValue;
   }
@@ -451,7 +410,7 @@ TK_API int tk_gemm_bf16_tcgen05(const void* r, const void* c, void* out, int* er
   }
   tk::GemmTcParams p;
   p.out = out; p.err = err; p.rows_total = rows; p.cols_total = cols; p.k_total = k; p.bn = bn;
-  p.n_stages = n_stages; p.n_splits = n_splits; p.swapped = swapped; p.out_f32 = out_f32; p.ld_out = ld_out; p.cluster_reduce = cluster_reduce; p.epilogue = epilogue;
+  p.n_stages = n_stages; p.n_splits = n_splits; p.cluster_reduce = cluster_reduce; p.epilogue = epilogue;
   p.colscale_parts = colscale_parts; p.n_colscale_parts = n_colscale_parts; p.colscale_inv_dim = colscale_inv_dim;
   p.colscale_eps = colscale_eps; p.resid = resid; p.norm_w = norm_w; p.xb_out = (__nv_bfloat16*)xb_out; p.sumsq_out = sumsq_out;
   dim3 grid((rows + tk::kGtBM - 1) / tk::kGtBM, (cols + bn - 1) / bn, n_splits);

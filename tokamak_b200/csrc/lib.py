@@ -38,8 +38,8 @@ _SIGNATURES: dict[str, list] = {
                                 c_float, _P],
     "tk_attention_prefill_tc_takes": [c_int, c_int, c_int, c_int],
     "tk_attention_prefill_tc_rows": [],
-    "tk_gemm_bf16_tcgen05": [_P, _P, _P, _P, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
-                             c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+    "tk_gemm_bf16_tcgen05": [_P, _P, _P, _P, c_int, c_int, c_int, c_longlong, c_longlong,
+                             c_int, c_int, c_int, c_int, c_int,
                              _P, c_int, c_float, c_float, _P, _P, _P, _P, _P],
     "tk_gemm_bf16_pair": [_P, _P, _P, _P, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, _P],
     "tk_gemm_f32": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],

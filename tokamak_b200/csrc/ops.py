@@ -446,7 +446,7 @@ def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_
             out = torch.empty((parts, tokens, n_out), dtype=torch.float32, device=x.device)
         out_ptr, result = out.data_ptr(), out
     _check(library().tk_gemm_bf16_tcgen05(weight.data_ptr(), x.data_ptr(), out_ptr, err.data_ptr(),
-                                          n_out, tokens, k, k, k, 0, bn, n_splits, 1, 1, max_stages,
+                                          n_out, tokens, k, k, k, bn, n_splits, max_stages,
                                           cluster if cluster > 1 else 0, epilogue, cs_ptr, cs_n, cs_inv, cs_eps,
                                           resid_ptr, w_ptr, _ptr(xb), _ptr(sums_out), _stream()),
            "gemm_tc_swapped")
@@ -468,23 +468,6 @@ def swapped_gemm_plan(n_out: int, k: int, tokens: int = 8) -> tuple[int, int, in
     splits = max(1, min(round(448 / tiles), max(1, k_blocks // 4), 8))
     stages = 4 if splits == 1 or (tiles * splits <= 400 and tokens <= 16) else 3
     return splits, stages, splits
-
-
-def gemm_tc(x: torch.Tensor, weight: torch.Tensor, err: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
-            bn: int = 128, max_stages: int = 0) -> torch.Tensor:
-    """``x @ weight^T`` on tcgen05 with the tokens as the 128-row operand; output ``[tokens, N_out]``."""
-    _want(weight, torch.bfloat16, "weight"); _want(x, torch.bfloat16, "x")
-    n_out, k = weight.shape
-    tokens, kx = x.shape
-    if k != kx or k % 8:
-        raise KernelError(f"inner sizes {k} and {kx} must agree and be a multiple of 8")
-    out = torch.empty((tokens, n_out), dtype=out_dtype, device=x.device)
-    _check(library().tk_gemm_bf16_tcgen05(x.data_ptr(), weight.data_ptr(), out.data_ptr(), err.data_ptr(),
-                                          tokens, n_out, k, k, k, n_out, bn, 1, 0,
-                                          1 if out_dtype == torch.float32 else 0, max_stages, 0, 0,
-                                          None, 0, 0.0, 0.0, None, None, None, None, _stream()),
-           "gemm_tc")
-    return out
 
 
 # Which products of many tokens run on the engine's own kernel for pairs of SMs: "all" of them,
