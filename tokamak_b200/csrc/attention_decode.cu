@@ -285,6 +285,23 @@ attn_decode_split_kernel(DecodeParams p) {
   __syncthreads();
   if (!s_last) return;
   __threadfence();                       // and the others' partial results before they are read
+  // A thread adds up four neighbouring columns of one row over the splits, always in the order of
+  // the splits, sixteen independent 16-byte loads at a time so that their latencies overlap; the
+  // first sixteen are requested before the weights are worked out.
+  constexpr int kMergeChunk = 16;
+  constexpr int V4 = D / 4;
+  const int n_vec = group * V4;
+  auto load_chunk = [&](int idx, int s0, float4 (&v)[kMergeChunk]) {
+    const int row = idx / V4, c4 = idx % V4;
+    const size_t base = ((size_t)item * p.n_q_heads + (size_t)hkv * group + row) * p.n_splits;
+    const float4* src = reinterpret_cast<const float4*>(p.part_o + base * D) + c4;
+#pragma unroll
+    for (int u = 0; u < kMergeChunk; ++u) {
+      v[u] = (s0 + u < p.n_splits) ? __ldcg(src + (size_t)(s0 + u) * V4) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+  };
+  float4 first[kMergeChunk];
+  if ((int)threadIdx.x < n_vec) load_chunk(threadIdx.x, 0, first);
   // weights of the splits, row by row: f_s = 2^(m_s - m) / sum_s l_s 2^(m_s - m)
   float* sf = reinterpret_cast<float*>(smem);            // [group][n_splits]
   for (int row = warp; row < group; row += kDecWarps) {
@@ -317,14 +334,28 @@ attn_decode_split_kernel(DecodeParams p) {
     }
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < group * D; idx += kDecWarps * 32) {
-    const int row = idx / D, col = idx % D;
-    const size_t base = ((size_t)item * p.n_q_heads + (size_t)hkv * group + row) * p.n_splits;
+  for (int idx = threadIdx.x; idx < n_vec; idx += kDecWarps * 32) {
+    const int row = idx / V4, c4 = idx % V4;
     const float* f = sf + row * p.n_splits;
-    float acc = 0.0f;
-#pragma unroll 4
-    for (int s2 = 0; s2 < p.n_splits; ++s2) acc += __ldcg(&p.part_o[(base + s2) * D + col]) * f[s2];
-    p.out[((size_t)tok * p.n_q_heads + (size_t)hkv * group + row) * D + col] = __float2bfloat16_rn(acc);
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int s0 = 0; s0 < p.n_splits; s0 += kMergeChunk) {
+      float4 v[kMergeChunk];
+      if (s0 == 0 && idx == (int)threadIdx.x) {
+#pragma unroll
+        for (int u = 0; u < kMergeChunk; ++u) v[u] = first[u];
+      } else {
+        load_chunk(idx, s0, v);
+      }
+#pragma unroll
+      for (int u = 0; u < kMergeChunk; ++u) {
+        const float w = (s0 + u < p.n_splits) ? f[s0 + u] : 0.0f;
+        acc.x += v[u].x * w; acc.y += v[u].y * w; acc.z += v[u].z * w; acc.w += v[u].w * w;
+      }
+    }
+    uint2 packed;
+    packed.x = pack_bf16(acc.x, acc.y);
+    packed.y = pack_bf16(acc.z, acc.w);
+    *reinterpret_cast<uint2*>(p.out + ((size_t)tok * p.n_q_heads + (size_t)hkv * group + row) * D + c4 * 4) = packed;
   }
   if (threadIdx.x == 0) p.counters[item * p.n_kv_heads + hkv] = 0;
 }
