@@ -253,13 +253,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
         for (int c = (int)my_rank + csize * phase; c < p.bn; c += 8 * csize) {
           const int col = tile_c * p.bn + c;
           if (col >= p.cols_total) break;
-          float4 g = make_float4(0.0f, 0.0f, 0.0f, 0.0f), u = g;
-          for (int rk = 0; rk < csize; ++rk) {
-            const float4 a = ld_cluster_f32x4(base + (uint32_t)((c * kGtBM + j4) * 4), (uint32_t)rk);
-            const float4 b = ld_cluster_f32x4(base + (uint32_t)((c * kGtBM + 64 + j4) * 4), (uint32_t)rk);
-            g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
-            u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
-          }
+          float4 g = cluster_sum_f32x4(base + (uint32_t)((c * kGtBM + j4) * 4), csize);
+          float4 u = cluster_sum_f32x4(base + (uint32_t)((c * kGtBM + 64 + j4) * 4), csize);
           if (p.colscale_parts != nullptr) {
             const float sc = s_scale[c];
             g.x *= sc; g.y *= sc; g.z *= sc; g.w *= sc;
@@ -288,21 +283,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
         for (int c = (int)my_rank + csize * phase; c < p.bn; c += 4 * csize) {
           const int col = tile_c * p.bn + c;
           if (col >= p.cols_total) break;
-          float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-          for (int rk = 0; rk < csize; ++rk) {
-            const float4 v = ld_cluster_f32x4(base + (uint32_t)((c * kGtBM + r4) * 4), (uint32_t)rk);
-            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+          // the residual and the norm weight are on their way while the partials are added up
+          float4 r = make_float4(0.0f, 0.0f, 0.0f, 0.0f), w = r;
+          if (p.epilogue == kGtEpiResidualNorm) {
+            r = *reinterpret_cast<const float4*>(p.resid + (size_t)col * p.rows_total + row);
+            w = *reinterpret_cast<const float4*>(p.norm_w + row);
           }
+          float4 sum = cluster_sum_f32x4(base + (uint32_t)((c * kGtBM + r4) * 4), csize);
           if (p.colscale_parts != nullptr) {
             const float sc = s_scale[c];
             sum.x *= sc; sum.y *= sc; sum.z *= sc; sum.w *= sc;
           }
           if (p.epilogue == kGtEpiResidualNorm) {
-            float* rp = p.resid + (size_t)col * p.rows_total + row;
-            float4 r = *reinterpret_cast<const float4*>(rp);
             r.x += sum.x; r.y += sum.y; r.z += sum.z; r.w += sum.w;
-            *reinterpret_cast<float4*>(rp) = r;
-            const float4 w = *reinterpret_cast<const float4*>(p.norm_w + row);
+            *reinterpret_cast<float4*>(p.resid + (size_t)col * p.rows_total + row) = r;
             uint2 packed;
             *reinterpret_cast<__nv_bfloat162*>(&packed.x) = __floats2bfloat162_rn(r.x * w.x, r.y * w.y);
             *reinterpret_cast<__nv_bfloat162*>(&packed.y) = __floats2bfloat162_rn(r.z * w.z, r.w * w.w);

@@ -176,6 +176,23 @@ __device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t local_smem_addr, uin
   return v;
 }
 
+// Sum over the blocks 0 .. csize-1 (at most 8) of a cluster of the four floats at the same
+// shared-memory address of each, added in the order of the ranks.  All loads are requested before
+// the first sum, so that their latencies over the cluster's network overlap.
+__device__ __forceinline__ float4 cluster_sum_f32x4(uint32_t local_smem_addr, int csize) {
+  float4 v[8];
+#pragma unroll
+  for (int rk = 0; rk < 8; ++rk) {
+    if (rk < csize) v[rk] = ld_cluster_f32x4(local_smem_addr, (uint32_t)rk);
+  }
+  float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+  for (int rk = 0; rk < 8; ++rk) {
+    if (rk < csize) { sum.x += v[rk].x; sum.y += v[rk].y; sum.z += v[rk].z; sum.w += v[rk].w; }
+  }
+  return sum;
+}
+
 // ---- host side: the driver's tensor-map encoder, found through the runtime (no link to libcuda) ----
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
