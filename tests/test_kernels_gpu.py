@@ -695,3 +695,87 @@ def test_gemm_tcgen05_swapped_residual_and_owed_norm(tokens, hidden, k, splits):
     torch.testing.assert_close(act.double().cpu(), g * torch.sigmoid(g) * u, rtol=3e-2, atol=3e-2)
     torch.cuda.synchronize()
     assert err.tolist()[0] == 0, err.tolist()
+
+
+@pytest.mark.parametrize("tokens,hq,hkv,k,splits,page,owed", [(8, 4, 2, 512, 4, 16, False), (1, 2, 1, 64, 1, 8, True),
+                                                              (33, 5, 1, 1536, 6, 16, True), (64, 8, 8, 320, 5, 4, False)])
+def test_gemm_tcgen05_swapped_with_norm_rotation_and_page_write(tokens, hq, hkv, k, splits, page, owed):
+    """The q|k|v product of few tokens whose epilogue does the per-head norm, the rotation and the
+    page write (heads of 128): against the formulas, and the cache against the separate kernel's
+    rules: values raw, nothing else touched except the cleared rest of a page begun in this step."""
+    from tokamak_b200.csrc import ops
+    d, eps, theta = 128, 1e-6, 1e6
+    gen = torch.Generator().manual_seed(tokens + k)
+    # every token its own request: request r has start[r] earlier positions; some begin a page now
+    starts = [(7 * r * r + (0 if r % 3 else page * r)) % 5000 for r in range(tokens)]
+    starts[0] = 40000                                              # far out: the angle's accuracy
+    max_pages = max(s // page for s in starts) + 1
+    num_pages = tokens + 3
+    pages = torch.randperm(num_pages, generator=gen).tolist()
+    table = torch.full((tokens, max_pages), -1, dtype=torch.int32)
+    for r, s in enumerate(starts):
+        table[r, s // page] = pages[r]
+    x = torch.randn(tokens, k, generator=gen).bfloat16()
+    w = (torch.randn((hq + 2 * hkv) * d, k, generator=gen) / k ** 0.5).bfloat16()
+    qw = 1 + 0.1 * torch.randn(d, generator=gen)
+    kw = 1 + 0.1 * torch.randn(d, generator=gen)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    pos_t = i32(starts)
+    inv_freq = (1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(DEV)
+    rot = ops.rope_table(pos_t, inv_freq)
+    kc = torch.full((num_pages, hkv, page, d), 7.0, device=DEV, dtype=torch.bfloat16)
+    vc = torch.full_like(kc, 7.0)
+    q_out = torch.empty(tokens, hq, d, device=DEV, dtype=torch.bfloat16)
+    err = err_word()
+    colscale, scale = None, torch.ones(tokens, dtype=torch.float64)
+    if owed:       # the input's norm scale is still owed: sums of squares in three tiles
+        sums = torch.rand(3, tokens, generator=gen) * k
+        colscale = (sums.to(DEV), k, 1e-5)
+        scale = torch.rsqrt(sums.double().sum(0) / k + 1e-5)
+    ops.gemm_qkv_rope(w.to(DEV), x.to(DEV), err, splits, q_out, kc, vc, pos_t, i32(list(range(tokens))),
+                      i32(list(range(tokens))), table.to(DEV), qw.to(DEV), kw.to(DEV), rot, n_q_heads=hq,
+                      n_kv_heads=hkv, eps=eps, colscale=colscale, req_q_len=i32([1] * tokens),
+                      req_kv_len=i32([s + 1 for s in starts]))
+    torch.cuda.synchronize()
+    assert err.tolist()[0] == 0, err.tolist()
+    y = (x.double() @ w.double().T) * scale[:, None]
+    q = y[:, : hq * d].view(tokens, hq, d)
+    kk = y[:, hq * d:(hq + hkv) * d].view(tokens, hkv, d)
+    v = y[:, (hq + hkv) * d:].view(tokens, hkv, d)
+    cos, sin = plain.rope_tables(torch.tensor(starts), d, theta, torch.float64)
+    q_want = plain.apply_rope(plain.rms_norm(q, qw.double(), eps), cos, sin)
+    k_want = plain.apply_rope(plain.rms_norm(kk, kw.double(), eps), cos, sin)
+    t = dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(q_out.double().cpu(), q_want, **t)
+    kc_h, vc_h = kc.double().cpu(), vc.double().cpu()
+    for r, s in enumerate(starts):
+        pg, slot = pages[r], s % page
+        torch.testing.assert_close(kc_h[pg, :, slot], k_want[r], **t)
+        torch.testing.assert_close(vc_h[pg, :, slot], v[r], **t)
+        assert (kc_h[pg, :, :slot] == 7).all() and (vc_h[pg, :, :slot] == 7).all()      # earlier tokens stay
+        rest = 0.0 if slot == 0 else 7.0               # a page begun by this token is cleared behind it
+        assert (kc_h[pg, :, slot + 1:] == rest).all() and (vc_h[pg, :, slot + 1:] == rest).all()
+    for pg in pages[tokens:]:
+        assert (kc_h[pg] == 7).all() and (vc_h[pg] == 7).all()
+    # the same through the product and the separate kernel: the same cache and queries up to rounding
+    kc2 = torch.full_like(kc, 7.0); vc2 = torch.full_like(kc, 7.0); q2 = torch.empty_like(q_out)
+    sums2 = ops.gemm_tc_swapped(w.to(DEV), x.to(DEV), err, splits, cluster=splits, colscale=colscale)
+    ops.rope_kv(sums2, q2, kc2, vc2, pos_t, i32(list(range(tokens))), i32(list(range(tokens))), table.to(DEV),
+                qw.to(DEV), kw.to(DEV), rot, err, n_q_heads=hq, n_kv_heads=hkv, head_dim=d, rotary_dim=d, eps=eps,
+                req_q_len=i32([1] * tokens), req_kv_len=i32([s + 1 for s in starts]))
+    assert torch.equal(vc2, vc)
+    torch.testing.assert_close(q2.float(), q_out.float(), rtol=8e-3, atol=1e-5)       # one bfloat16 step
+    torch.testing.assert_close(kc2.float(), kc.float(), rtol=8e-3, atol=1e-5)
+    # without norms and rotation the sums pass through
+    ops.gemm_qkv_rope(w.to(DEV), x.to(DEV), err, splits, q_out, kc, vc, pos_t, i32(list(range(tokens))),
+                      i32(list(range(tokens))), table.to(DEV), None, None, None, n_q_heads=hq, n_kv_heads=hkv,
+                      eps=0.0, colscale=colscale)
+    torch.cuda.synchronize()
+    assert err.tolist()[0] == 0, err.tolist()
+    torch.testing.assert_close(q_out.double().cpu(), q, **t)
+    # a page outside the pool is reported, not written
+    bad = table.clone(); bad[0, starts[0] // page] = num_pages
+    ops.gemm_qkv_rope(w.to(DEV), x.to(DEV), err, splits, q_out, kc, vc, pos_t, i32(list(range(tokens))),
+                      i32(list(range(tokens))), bad.to(DEV), None, None, None, n_q_heads=hq, n_kv_heads=hkv, eps=0.0)
+    torch.cuda.synchronize()
+    assert err.tolist()[0] == 2, err.tolist()

@@ -39,6 +39,31 @@ constexpr int kGtEpiSwiglu = 1;
 // own (src/tokamak/model/layers.py:28-33, transformer.py:107-108; the 32-bit statistics are the
 // same, the rounding to bfloat16 happens before instead of after the scaling by the statistic).
 constexpr int kGtEpiResidualNorm = 2;
+// Epilogue for the stacked q|k|v projection of heads of 128 elements, where a 128-row tile is one
+// head of one token per column: the warp that adds the splits up holds the whole head, so it
+// applies the per-head RMSNorm of q and k and the half rotation, stores q as bfloat16
+// [token, head, 128] and writes k (normed and rotated) and v (as it is) into the token's place in
+// its cache page.  Formulas and page addressing are those of the separate kernel in rope_kv.cu
+// (src/tokamak/model/transformer.py:71-73, layers.py:56-89, memory/paged_cache.py:72-81).
+constexpr int kGtEpiQkvRope = 3;
+constexpr int kGtHeadDim = 128;   // the only head size of that epilogue
+
+struct GemmQkvRope {
+  __nv_bfloat16* q_out;     // [tokens, n_q_heads, 128]
+  __nv_bfloat16* k_cache;   // [num_pages, n_kv_heads, page_size, 128]
+  __nv_bfloat16* v_cache;
+  const int* positions;     // [tokens]
+  const int* tok_req;       // [tokens] row of the token's request in this step
+  const int* req_slot;      // [n_reqs] row of the request in block_table
+  const int* block_table;   // [n_slots, max_pages]
+  const int* req_q_len;     // [n_reqs] tokens the request brings to this step, or null
+  const int* req_kv_len;    // [n_reqs] positions of the request after this step, or null
+  const float* q_norm_w;    // [128] or null
+  const float* k_norm_w;    // [128] or null
+  const float2* rope_table; // [tokens, 64] (cos, sin), or null: no rotation
+  int n_reqs, n_q_heads, n_kv_heads, page_size, max_pages, num_pages;
+  float eps;
+};
 
 struct GemmTcParams {
   void* out;                // float [parts, cols_total, rows_total], or what the epilogue stores
@@ -64,6 +89,7 @@ struct GemmTcParams {
   const float* norm_w;
   __nv_bfloat16* xb_out;
   float* sumsq_out;
+  GemmQkvRope qkv;          // epilogue 3
 };
 
 __global__ void __launch_bounds__(kGtThreads, 1)
@@ -197,6 +223,37 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
       }
       my_scale = rsqrtf(ss * p.colscale_inv_dim + p.colscale_eps);
     }
+    // the cache row of this thread's column (token), for the tiles that hold keys or values:
+    // ((page * kv heads + 0) * page_size + slot), or -1; and how many rows behind it to clear
+    long long my_cache_row = -1;
+    int my_zero_rows = 0;
+    if (p.epilogue == kGtEpiQkvRope && tile_r >= p.qkv.n_q_heads && my_col < p.bn &&
+        tile_c * p.bn + my_col < p.cols_total) {
+      const GemmQkvRope& e = p.qkv;
+      const int t = tile_c * p.bn + my_col;
+      const int pos = e.positions[t];
+      const int r = e.tok_req[t];
+      if (pos < 0) {
+        set_error(p.err, kErrPosition, t, pos, 0);
+      } else if (r < 0 || r >= e.n_reqs) {
+        set_error(p.err, kErrRequest, t, r, e.n_reqs);
+      } else {
+        const int pidx = pos / e.page_size;
+        const int page = (pidx < e.max_pages) ? e.block_table[(size_t)e.req_slot[r] * e.max_pages + pidx] : -1;
+        if (page < 0 || page >= e.num_pages) {
+          set_error(p.err, kErrPage, t, pidx, page);
+        } else {
+          my_cache_row = (long long)page * e.n_kv_heads * e.page_size + (pos % e.page_size);
+          // the request's last token of this step clears the rest of a page begun in this step
+          if (e.req_kv_len != nullptr) {
+            const int kv_len = e.req_kv_len[r], q_len = e.req_q_len[r];
+            if (pos == kv_len - 1 && pos - pos % e.page_size >= kv_len - q_len) {
+              my_zero_rows = e.page_size - 1 - pos % e.page_size;
+            }
+          }
+        }
+      }
+    }
     if (n_kb > 0) {
       ok = mbar_wait(gt_smem_u32(accum_bar), 0u, abort_flag);
       if (!ok && lane == 0) { set_error(p.err, kErrWait, 2, 0, 0); *abort_flag = 1; }
@@ -206,6 +263,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
     if (staged && my_col < p.bn) {
       // behind the staging area, in the ring of stages that the products are done with
       reinterpret_cast<float*>(smem)[p.bn * kGtBM + my_col] = my_scale;
+      if (p.epilogue == kGtEpiQkvRope) {
+        unsigned char* behind = smem + (size_t)p.bn * kGtBM * 4 + (size_t)p.bn * 4;   // 8-byte aligned: bn is even
+        reinterpret_cast<long long*>(behind)[my_col] = my_cache_row;
+        reinterpret_cast<int*>(behind + (size_t)p.bn * 8)[my_col] = my_zero_rows;
+      }
     }
     for (int c0 = 0; c0 < p.bn; c0 += 16) {
       uint32_t v[16];
@@ -294,6 +356,55 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
             const float sc = s_scale[c];
             sum.x *= sc; sum.y *= sc; sum.z *= sc; sum.w *= sc;
           }
+          if (p.epilogue == kGtEpiQkvRope) {
+            // this warp holds head `tile_r` of token `col`: lane l the elements 4 l .. 4 l + 3
+            const GemmQkvRope& e = p.qkv;
+            const int kind = tile_r < e.n_q_heads ? 0 : (tile_r < e.n_q_heads + e.n_kv_heads ? 1 : 2);
+            const float* nw = kind == 0 ? e.q_norm_w : (kind == 1 ? e.k_norm_w : nullptr);
+            if (nw != nullptr) {
+              const float4 w4 = *reinterpret_cast<const float4*>(nw + r4);
+              const float ss = warp_sum(sum.x * sum.x + sum.y * sum.y + sum.z * sum.z + sum.w * sum.w);
+              const float rstd = rsqrtf(ss / (float)kGtHeadDim + e.eps);
+              sum.x = sum.x * rstd * w4.x; sum.y = sum.y * rstd * w4.y;
+              sum.z = sum.z * rstd * w4.z; sum.w = sum.w * rstd * w4.w;
+            }
+            if (kind != 2 && e.rope_table != nullptr) {
+              // element i < 64 turns with element i + 64, which lane l ^ 16 holds
+              const float4* cs = reinterpret_cast<const float4*>(e.rope_table + (size_t)col * (kGtHeadDim / 2) +
+                                                                  4 * (lane & 15));
+              const float4 cs01 = cs[0], cs23 = cs[1];        // (cos, sin) of two elements each
+              float4 other;
+              other.x = __shfl_xor_sync(0xffffffffu, sum.x, 16); other.y = __shfl_xor_sync(0xffffffffu, sum.y, 16);
+              other.z = __shfl_xor_sync(0xffffffffu, sum.z, 16); other.w = __shfl_xor_sync(0xffffffffu, sum.w, 16);
+              if (lane < 16) {
+                sum.x = sum.x * cs01.x - other.x * cs01.y; sum.y = sum.y * cs01.z - other.y * cs01.w;
+                sum.z = sum.z * cs23.x - other.z * cs23.y; sum.w = sum.w * cs23.z - other.w * cs23.w;
+              } else {
+                sum.x = sum.x * cs01.x + other.x * cs01.y; sum.y = sum.y * cs01.z + other.y * cs01.w;
+                sum.z = sum.z * cs23.x + other.z * cs23.y; sum.w = sum.w * cs23.z + other.w * cs23.w;
+              }
+            }
+            uint2 packed;
+            *reinterpret_cast<__nv_bfloat162*>(&packed.x) = __floats2bfloat162_rn(sum.x, sum.y);
+            *reinterpret_cast<__nv_bfloat162*>(&packed.y) = __floats2bfloat162_rn(sum.z, sum.w);
+            if (kind == 0) {
+              *reinterpret_cast<uint2*>(e.q_out + ((size_t)col * e.n_q_heads + tile_r) * kGtHeadDim + r4) = packed;
+            } else {
+              const unsigned char* behind = smem + (size_t)p.bn * kGtBM * 4 + (size_t)p.bn * 4;
+              const long long cache_row = reinterpret_cast<const long long*>(behind)[c];
+              const int zero_rows = reinterpret_cast<const int*>(behind + (size_t)p.bn * 8)[c];
+              if (cache_row >= 0) {
+                const int head = tile_r - e.n_q_heads - (kind == 2 ? e.n_kv_heads : 0);
+                __nv_bfloat16* dst = (kind == 1 ? e.k_cache : e.v_cache) +
+                                     ((size_t)cache_row + (size_t)head * e.page_size) * kGtHeadDim + r4;
+                *reinterpret_cast<uint2*>(dst) = packed;
+                for (int z = 1; z <= zero_rows; ++z) {
+                  *reinterpret_cast<uint2*>(dst + (size_t)z * kGtHeadDim) = make_uint2(0u, 0u);
+                }
+              }
+            }
+            continue;
+          }
           if (p.epilogue == kGtEpiResidualNorm) {
             r.x += sum.x; r.y += sum.y; r.z += sum.z; r.w += sum.w;
             *reinterpret_cast<float4*>(p.resid + (size_t)col * p.rows_total + row) = r;
@@ -342,6 +453,57 @@ static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
+// Checks the sizes, makes the maps and launches; `p` comes with its epilogue's fields filled in.
+static int launch_gemm(const void* r, const void* c, int rows, int cols, int k, long long ld_r, long long ld_c,
+                       int bn, int n_splits, int max_stages, int cluster_reduce, GemmTcParams p,
+                       cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (k <= 0 || k % 8 != 0 || (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) || n_splits < 1 ||
+      (cluster_reduce > 1 && (cluster_reduce > 8 || n_splits % cluster_reduce != 0)) || cluster_reduce < 0) {
+    return (int)cudaErrorInvalidValue;
+  }
+  const bool one_part = n_splits == (cluster_reduce > 1 ? cluster_reduce : 1);
+  if (p.epilogue != 0 && (p.epilogue < kGtEpiSwiglu || p.epilogue > kGtEpiQkvRope || rows % 128 != 0 || !one_part)) {
+    return (int)cudaErrorInvalidValue;
+  }
+  if (p.colscale_parts != nullptr && (p.n_colscale_parts < 1 || !one_part)) return (int)cudaErrorInvalidValue;
+  CUtensorMap map_r, map_c;
+  int rc = make_map(&map_r, r, rows, k, ld_r, kGtBM);
+  if (rc != 0) return rc;
+  rc = make_map(&map_c, c, cols, k, ld_c, bn);
+  if (rc != 0) return rc;
+
+  const unsigned r_bytes = kGtBM * kGtBK * 2;
+  const unsigned c_bytes = ((unsigned)bn * kGtBK * 2 + 1023u) & ~1023u;
+  const unsigned stage_bytes = r_bytes + c_bytes;
+  const int kb_total = (k + kGtBK - 1) / kGtBK;
+  const int kb_per = (kb_total + n_splits - 1) / n_splits;
+  int n_stages = (int)((200u * 1024u) / stage_bytes);
+  if (n_stages > 8) n_stages = 8;
+  if (max_stages > 0 && n_stages > max_stages) n_stages = max_stages;
+  if (n_stages > kb_per) n_stages = kb_per < 2 ? 2 : kb_per;
+  const size_t smem_bytes = (size_t)n_stages * stage_bytes + 1024 /* alignment slack */ + 256 /* barriers */;
+
+  static size_t configured = 0;
+  if (smem_bytes > configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)(220 * 1024));
+    if (e != cudaSuccess) return (int)e;
+    configured = 220 * 1024;
+  }
+  p.rows_total = rows; p.cols_total = cols; p.k_total = k; p.bn = bn;
+  p.n_stages = n_stages; p.n_splits = n_splits; p.cluster_reduce = cluster_reduce;
+  dim3 grid((rows + kGtBM - 1) / kGtBM, (cols + bn - 1) / bn, n_splits);
+  if (cluster_reduce > 1 || p.epilogue != 0 || p.colscale_parts != nullptr) {
+    // the staging area [bn][128] floats, the column scales and (q|k|v epilogue) the cache rows
+    // must fit into the ring of stages
+    if ((size_t)bn * kGtBM * 4 + (size_t)bn * 16 > (size_t)n_stages * stage_bytes) return (int)cudaErrorInvalidValue;
+    return (int)launch_cluster_z(gemm_tcgen05_kernel, grid, dim3(kGtThreads), smem_bytes, stream,
+                                 (unsigned)(cluster_reduce > 1 ? cluster_reduce : 1), map_r, map_c, p);
+  }
+  return (int)launch(gemm_tcgen05_kernel, grid, dim3(kGtThreads), smem_bytes, stream, map_r, map_c, p);
+}
+
 }  // namespace tk
 
 // D^T = (R * C^T)^T on tcgen05.  r: [rows, k] bf16 (the weight, row stride ld_r), c: [cols, k] bf16
@@ -361,58 +523,47 @@ TK_API int tk_gemm_bf16_tcgen05(const void* r, const void* c, void* out, int* er
                                 const float* colscale_parts, int n_colscale_parts, float colscale_inv_dim,
                                 float colscale_eps, float* resid, const float* norm_w, void* xb_out,
                                 float* sumsq_out, cudaStream_t stream) {
-  if (rows <= 0 || cols <= 0) return 0;
-  if (k <= 0 || k % 8 != 0 || (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) || n_splits < 1 ||
-      (cluster_reduce > 1 && (cluster_reduce > 8 || n_splits % cluster_reduce != 0)) || cluster_reduce < 0) {
-    return (int)cudaErrorInvalidValue;
-  }
-  if (epilogue != 0 && ((epilogue != tk::kGtEpiSwiglu && epilogue != tk::kGtEpiResidualNorm) ||
-                        rows % 128 != 0 || n_splits != (cluster_reduce > 1 ? cluster_reduce : 1))) {
-    return (int)cudaErrorInvalidValue;
-  }
+  if (epilogue < 0 || epilogue > tk::kGtEpiResidualNorm) return (int)cudaErrorInvalidValue;
   if (epilogue == tk::kGtEpiResidualNorm &&
       (resid == nullptr || norm_w == nullptr || xb_out == nullptr || sumsq_out == nullptr)) {
     return (int)cudaErrorInvalidValue;
   }
-  if (colscale_parts != nullptr && (n_colscale_parts < 1 ||
-                                    n_splits != (cluster_reduce > 1 ? cluster_reduce : 1))) {
-    return (int)cudaErrorInvalidValue;
-  }
-  CUtensorMap map_r, map_c;
-  int rc = tk::make_map(&map_r, r, rows, k, ld_r, tk::kGtBM);
-  if (rc != 0) return rc;
-  rc = tk::make_map(&map_c, c, cols, k, ld_c, bn);
-  if (rc != 0) return rc;
-
-  const unsigned r_bytes = tk::kGtBM * tk::kGtBK * 2;
-  const unsigned c_bytes = ((unsigned)bn * tk::kGtBK * 2 + 1023u) & ~1023u;
-  const unsigned stage_bytes = r_bytes + c_bytes;
-  const int kb_total = (k + tk::kGtBK - 1) / tk::kGtBK;
-  const int kb_per = (kb_total + n_splits - 1) / n_splits;
-  int n_stages = (int)((200u * 1024u) / stage_bytes);
-  if (n_stages > 8) n_stages = 8;
-  if (max_stages > 0 && n_stages > max_stages) n_stages = max_stages;
-  if (n_stages > kb_per) n_stages = kb_per < 2 ? 2 : kb_per;
-  const size_t smem_bytes = (size_t)n_stages * stage_bytes + 1024 /* alignment slack */ + 256 /* barriers */;
-
-  static size_t configured = 0;
-  if (smem_bytes > configured) {
-    cudaError_t e = cudaFuncSetAttribute(tk::gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)(220 * 1024));
-    if (e != cudaSuccess) return (int)e;
-    configured = 220 * 1024;
-  }
-  tk::GemmTcParams p;
-  p.out = out; p.err = err; p.rows_total = rows; p.cols_total = cols; p.k_total = k; p.bn = bn;
-  p.n_stages = n_stages; p.n_splits = n_splits; p.cluster_reduce = cluster_reduce; p.epilogue = epilogue;
+  tk::GemmTcParams p = {};
+  p.out = out; p.err = err; p.epilogue = epilogue;
   p.colscale_parts = colscale_parts; p.n_colscale_parts = n_colscale_parts; p.colscale_inv_dim = colscale_inv_dim;
   p.colscale_eps = colscale_eps; p.resid = resid; p.norm_w = norm_w; p.xb_out = (__nv_bfloat16*)xb_out; p.sumsq_out = sumsq_out;
-  dim3 grid((rows + tk::kGtBM - 1) / tk::kGtBM, (cols + bn - 1) / bn, n_splits);
-  if (cluster_reduce > 1 || epilogue != 0 || colscale_parts != nullptr) {
-    // the staging area [bn][128] floats and the column scales must fit into the ring of stages
-    if ((size_t)bn * tk::kGtBM * 4 + (size_t)bn * 4 > (size_t)n_stages * stage_bytes) return (int)cudaErrorInvalidValue;
-    return (int)tk::launch_cluster_z(tk::gemm_tcgen05_kernel, grid, dim3(tk::kGtThreads), smem_bytes, stream,
-                                     (unsigned)(cluster_reduce > 1 ? cluster_reduce : 1), map_r, map_c, p);
+  return tk::launch_gemm(r, c, rows, cols, k, ld_r, ld_c, bn, n_splits, max_stages, cluster_reduce, p, stream);
+}
+
+// The stacked q|k|v projection of heads of 128 elements with the per-head norms, the rotation and
+// the cache write in its epilogue (see kGtEpiQkvRope): w is [(n_q_heads + 2 n_kv_heads) * 128, k],
+// x is [tokens, k]; all n_splits blocks of a tile form one cluster.  q_out receives
+// [tokens, n_q_heads, 128]; keys and values go to their pages as in tk_rope_kv.
+TK_API int tk_gemm_qkv_rope(const void* w, const void* x, int* err, int tokens, int k, long long ld_w, long long ld_x,
+                            int bn, int n_splits, int max_stages,
+                            const float* colscale_parts, int n_colscale_parts, float colscale_inv_dim,
+                            float colscale_eps,
+                            void* q_out, void* k_cache, void* v_cache, const int* positions, const int* tok_req,
+                            const int* req_slot, const int* block_table, const int* req_q_len,
+                            const int* req_kv_len, const float* q_norm_w, const float* k_norm_w,
+                            const void* rope_table, int n_reqs, int n_q_heads, int n_kv_heads, int page_size,
+                            int max_pages, int num_pages, float eps, cudaStream_t stream) {
+  if (n_q_heads < 1 || n_kv_heads < 1 || page_size < 1 || n_splits > 8 ||
+      (req_kv_len != nullptr && req_q_len == nullptr)) {
+    return (int)cudaErrorInvalidValue;
   }
-  return (int)tk::launch(tk::gemm_tcgen05_kernel, grid, dim3(tk::kGtThreads), smem_bytes, stream, map_r, map_c, p);
+  tk::GemmTcParams p = {};
+  p.err = err; p.epilogue = tk::kGtEpiQkvRope;
+  p.colscale_parts = colscale_parts; p.n_colscale_parts = n_colscale_parts; p.colscale_inv_dim = colscale_inv_dim;
+  p.colscale_eps = colscale_eps;
+  tk::GemmQkvRope& e = p.qkv;
+  e.q_out = (__nv_bfloat16*)q_out; e.k_cache = (__nv_bfloat16*)k_cache; e.v_cache = (__nv_bfloat16*)v_cache;
+  e.positions = positions; e.tok_req = tok_req; e.req_slot = req_slot; e.block_table = block_table;
+  e.req_q_len = req_q_len; e.req_kv_len = req_kv_len; e.q_norm_w = q_norm_w; e.k_norm_w = k_norm_w;
+  e.rope_table = (const float2*)rope_table;
+  e.n_reqs = n_reqs; e.n_q_heads = n_q_heads; e.n_kv_heads = n_kv_heads; e.page_size = page_size;
+  e.max_pages = max_pages; e.num_pages = num_pages; e.eps = eps;
+  const int rows = (n_q_heads + 2 * n_kv_heads) * tk::kGtHeadDim;
+  return tk::launch_gemm(w, x, rows, tokens, k, ld_w, ld_x, bn, n_splits, max_stages, n_splits > 1 ? n_splits : 0,
+                         p, stream);
 }

@@ -41,6 +41,10 @@ _SIGNATURES: dict[str, list] = {
     "tk_gemm_bf16_tcgen05": [_P, _P, _P, _P, c_int, c_int, c_int, c_longlong, c_longlong,
                              c_int, c_int, c_int, c_int, c_int,
                              _P, c_int, c_float, c_float, _P, _P, _P, _P, _P],
+    "tk_gemm_qkv_rope": [_P, _P, _P, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_int,
+                         _P, c_int, c_float, c_float,
+                         _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
+                         c_int, c_int, c_int, c_int, c_int, c_int, c_float, _P],
     "tk_gemm_bf16_pair": [_P, _P, _P, _P, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, _P],
     "tk_gemm_f32": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "tk_sample": [_P, c_longlong, _P, _P, _P, _P, _P, _P, c_int, c_int, _P],

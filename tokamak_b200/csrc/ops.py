@@ -455,6 +455,69 @@ def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_
     return result
 
 
+QKV_ROPE_HEAD_DIM = 128    # the head size whose heads are whole 128-row tiles of the swapped product
+
+
+def gemm_qkv_rope(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_splits: int, q_out: torch.Tensor,
+                  k_cache: torch.Tensor, v_cache: torch.Tensor, positions: torch.Tensor, tok_req: torch.Tensor,
+                  req_slot: torch.Tensor, block_table: torch.Tensor, q_norm_w: torch.Tensor | None,
+                  k_norm_w: torch.Tensor | None, table: torch.Tensor | None, *, n_q_heads: int, n_kv_heads: int,
+                  eps: float, max_stages: int = 0, colscale: tuple | None = None,
+                  req_q_len: torch.Tensor | None = None, req_kv_len: torch.Tensor | None = None) -> None:
+    """The stacked q|k|v projection of few tokens with :func:`rope_kv`'s work in its epilogue, for
+    heads of 128 elements: ``weight`` is ``[(Hq + 2 Hkv) 128, K]``, ``x`` ``[tokens, K]``; ``q_out``
+    receives the normed and rotated queries, the keys and values go to their pages.  All
+    ``n_splits`` (at most 8) blocks of a head form one cluster.  ``colscale`` as in
+    :func:`gemm_tc_swapped`; ``table`` is the rotation table ``[tokens, 64, 2]`` or None."""
+    _want(weight, torch.bfloat16, "weight"); _want(x, torch.bfloat16, "x"); _want(q_out, torch.bfloat16, "q_out")
+    _want(k_cache, torch.bfloat16, "k_cache"); _want(v_cache, torch.bfloat16, "v_cache")
+    d = QKV_ROPE_HEAD_DIM
+    n_out, k = weight.shape
+    tokens, kx = x.shape
+    if k != kx or k % 8:
+        raise KernelError(f"inner sizes {k} and {kx} must agree and be a multiple of 8")
+    if n_out != (n_q_heads + 2 * n_kv_heads) * d:
+        raise KernelError(f"the weight has {n_out} rows, {(n_q_heads + 2 * n_kv_heads) * d} needed for heads of {d}")
+    if tokens > 256 or not 1 <= n_splits <= 8:
+        raise KernelError("the swapped product takes at most 256 tokens and 8 splits in a cluster")
+    if q_out.shape != (tokens, n_q_heads, d):
+        raise KernelError(f"q_out must be [{tokens}, {n_q_heads}, {d}]")
+    num_pages, hkv, page_size, dk = k_cache.shape
+    if hkv != n_kv_heads or dk != d or v_cache.shape != k_cache.shape:
+        raise KernelError("cache pages do not match the heads")
+    for name, t in (("positions", positions), ("tok_req", tok_req), ("req_slot", req_slot),
+                    ("block_table", block_table)):
+        _want(t, torch.int32, name)
+    for name, t in (("q_norm_w", q_norm_w), ("k_norm_w", k_norm_w), ("table", table)):
+        if t is not None:
+            _want(t, torch.float32, name)
+    for name, t in (("q_norm_w", q_norm_w), ("k_norm_w", k_norm_w)):
+        if t is not None and t.numel() != d:
+            raise KernelError(f"{name} does not match head_dim {d}")
+    if table is not None and table.shape != (tokens, d // 2, 2):
+        raise KernelError(f"the rotation table must be [{tokens}, {d // 2}, 2], got {tuple(table.shape)}")
+    if (req_q_len is None) != (req_kv_len is None):
+        raise KernelError("req_q_len and req_kv_len come together")
+    cs_ptr, cs_n, cs_inv, cs_eps = None, 0, 0.0, 0.0
+    if colscale is not None:
+        sumsq, dim, cs_eps = colscale
+        _want(sumsq, torch.float32, "colscale sums")
+        if sumsq.dim() != 2 or sumsq.shape[1] != tokens:
+            raise KernelError("colscale wants sums of squares [tiles, tokens]")
+        cs_ptr, cs_n, cs_inv, cs_eps = sumsq.data_ptr(), sumsq.shape[0], 1.0 / dim, float(cs_eps)
+    bn = 16
+    while bn < tokens:
+        bn *= 2
+    _check(library().tk_gemm_qkv_rope(weight.data_ptr(), x.data_ptr(), err.data_ptr(), tokens, k, k, k, bn,
+                                      n_splits, max_stages, cs_ptr, cs_n, cs_inv, cs_eps,
+                                      q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                      positions.data_ptr(), tok_req.data_ptr(), req_slot.data_ptr(),
+                                      block_table.data_ptr(), _ptr(req_q_len), _ptr(req_kv_len),
+                                      _ptr(q_norm_w), _ptr(k_norm_w), _ptr(table), req_slot.numel(),
+                                      n_q_heads, n_kv_heads, page_size, block_table.shape[1], num_pages,
+                                      float(eps), _stream()), "gemm_qkv_rope")
+
+
 def swapped_gemm_plan(n_out: int, k: int, tokens: int = 8) -> tuple[int, int, int]:
     """(K splits, pipeline stages, cluster size) of the swapped product.
 

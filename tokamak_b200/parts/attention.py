@@ -8,7 +8,7 @@ import torch
 
 from ..cache.manager import KVPagesNeed
 from ..csrc import ops
-from .base import MIXERS, POSITIONS, Runtime, TensorReq, linear
+from .base import MIXERS, POSITIONS, SWAPPED_GEMM_MAX_TOKENS, OwedNorm, Runtime, TensorReq, linear
 
 
 @dataclass(frozen=True)
@@ -86,9 +86,30 @@ class Attention:
     def forward(self, h, step, cache_view, then_norm=None):
         spec = self.spec
         n = h.shape[0]
-        qkv = linear(h, self.w_qkv, err=step.err)
         q = torch.empty((n, spec.num_heads, spec.head_dim), dtype=h.dtype, device=h.device)
         table, rotary_dim = self.position.rotary_table(step)
+        if (h.dtype == torch.bfloat16 and n <= SWAPPED_GEMM_MAX_TOKENS and spec.own_kv
+                and spec.head_dim == ops.QKV_ROPE_HEAD_DIM and rotary_dim in (0, spec.head_dim)
+                and spec.hidden_size % 8 == 0 and cache_view.k.dtype == torch.bfloat16):
+            # few tokens and heads that are whole tiles: norm, rotation and page write ride in
+            # the product's epilogue
+            splits, stages, _ = ops.swapped_gemm_plan(self.w_qkv.shape[0], spec.hidden_size, n)
+            colscale, x = ((h.sumsq, h.dim, h.eps), h.xb) if isinstance(h, OwedNorm) else (None, h)
+            ops.gemm_qkv_rope(self.w_qkv, x, step.err, splits, q, cache_view.k, cache_view.v, step.positions,
+                              step.tok_req, step.req_slot, cache_view.table, self.q_norm_w, self.k_norm_w,
+                              table, n_q_heads=spec.num_heads, n_kv_heads=spec.num_kv_heads,
+                              eps=spec.qk_norm_eps or 0.0, max_stages=stages, colscale=colscale,
+                              req_q_len=step.req_q_len, req_kv_len=step.req_kv_len)
+        else:
+            self._project_and_rotate(h, q, table, rotary_dim, step, cache_view)
+        out = torch.empty_like(q)
+        paged_attention(q, out, cache_view, step, scale=self.scale, window=spec.window)
+        return linear(out.view(n, spec.num_heads * spec.head_dim), self.w_o, err=step.err, then_norm=then_norm)
+
+    def _project_and_rotate(self, h, q, table, rotary_dim, step, cache_view) -> None:
+        """The q|k|v product, then norm, rotation and page write in a kernel of their own."""
+        spec = self.spec
+        qkv = linear(h, self.w_qkv, err=step.err)
         ops.rope_kv(qkv, q, cache_view.k if spec.own_kv else None,
                     cache_view.v if spec.own_kv else None,
                     step.positions, step.tok_req, step.req_slot, cache_view.table,
@@ -96,9 +117,6 @@ class Attention:
                     n_q_heads=spec.num_heads, n_kv_heads=spec.num_kv_heads, head_dim=spec.head_dim,
                     rotary_dim=rotary_dim, eps=spec.qk_norm_eps or 0.0, write_kv=spec.own_kv,
                     req_q_len=step.req_q_len, req_kv_len=step.req_kv_len)
-        out = torch.empty_like(q)
-        paged_attention(q, out, cache_view, step, scale=self.scale, window=spec.window)
-        return linear(out.view(n, spec.num_heads * spec.head_dim), self.w_o, err=step.err, then_norm=then_norm)
 
 
 def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, scale: float,
