@@ -92,7 +92,9 @@ struct GemmTcParams {
   GemmQkvRope qkv;          // epilogue 3
 };
 
-__global__ void __launch_bounds__(kGtThreads, 1)
+// Four blocks with rings of three stages fit an SM's shared memory; the register bound keeps it so
+// (grids of up to four blocks per SM then run as one wave).
+__global__ void __launch_bounds__(kGtThreads, 4)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_c,
                     GemmTcParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
