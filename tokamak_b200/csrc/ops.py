@@ -524,14 +524,19 @@ def swapped_gemm_plan(n_out: int, k: int, tokens: int = 8) -> tuple[int, int, in
     About 2.5 to 3 blocks per SM, each with at least four 64-wide k blocks, so that several
     blocks share an SM and one block's start-up hides behind another's streaming; the splits of
     a tile (at most 8) form one cluster that adds its partials up, so the consumer sees a single
-    part.  Rings of three stages; four where the grid is short (at most about 2.7 blocks per SM)
-    and the token tile is small, so that three blocks still fit an SM.  Measured on the
-    Qwen3-8B decode step: 16 splits in two clusters, deeper rings and other block counts were
-    all slower, and so were four stages for the long gate/up grid or for 64-token tiles."""
+    part.  Rings of three stages; four where the grid is short enough that its blocks still all
+    fit: with at most 16 tokens a single split or up to about 2.7 blocks per SM (three such
+    blocks fit an SM), with more tokens (larger stages) up to two blocks per SM.  Measured on
+    the Qwen3-8B decode step: 16 splits in two clusters, deeper rings and other block counts were
+    all slower, and so were four stages for the long gate/up grid, and for the q|k|v and head
+    products at 32 and 64 tokens (head at 64 tokens: 195 us with three stages, 212 with four)."""
     tiles = -(-n_out // 128)
     k_blocks = -(-k // 64)
     splits = max(1, min(round(448 / tiles), max(1, k_blocks // 4), 8))
-    stages = 4 if splits == 1 or (tiles * splits <= 400 and tokens <= 16) else 3
+    if tokens <= 16:
+        stages = 4 if splits == 1 or tiles * splits <= 400 else 3
+    else:
+        stages = 4 if tiles * splits <= 296 else 3
     return splits, stages, splits
 
 
