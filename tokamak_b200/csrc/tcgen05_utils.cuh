@@ -148,51 +148,6 @@ __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 
-// Thread-block clusters: rank, barrier over all threads of the cluster, and reads of another
-// block's shared memory.
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ float ld_cluster_f32(uint32_t local_smem_addr, uint32_t rank) {
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(local_smem_addr), "r"(rank));
-  float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(remote) : "memory");
-  return v;
-}
-
-__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t local_smem_addr, uint32_t rank) {
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(local_smem_addr), "r"(rank));
-  float4 v;
-  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];\n"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
-  return v;
-}
-
-// Sum over the blocks 0 .. csize-1 (at most 8) of a cluster of the four floats at the same
-// shared-memory address of each, added in the order of the ranks.  All loads are requested before
-// the first sum, so that their latencies over the cluster's network overlap.
-__device__ __forceinline__ float4 cluster_sum_f32x4(uint32_t local_smem_addr, int csize) {
-  float4 v[8];
-#pragma unroll
-  for (int rk = 0; rk < 8; ++rk) {
-    if (rk < csize) v[rk] = ld_cluster_f32x4(local_smem_addr, (uint32_t)rk);
-  }
-  float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-#pragma unroll
-  for (int rk = 0; rk < 8; ++rk) {
-    if (rk < csize) { sum.x += v[rk].x; sum.y += v[rk].y; sum.z += v[rk].z; sum.w += v[rk].w; }
-  }
-  return sum;
-}
-
 // ---- host side: the driver's tensor-map encoder, found through the runtime (no link to libcuda) ----
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
