@@ -195,18 +195,18 @@ def time_decode(core, batch: int, steps: int, warmup: int, ctx_end: int, vocab: 
             "kv_bytes": kv_bytes, "wall_ms_per_step": wall * 1e3 / steps}
 
 
-def time_prefill(core, vocab: int, repeats: int = 3):
+def time_prefill(core, vocab: int, tokens: int = PREFILL_TOKENS, repeats: int = 3):
     import torch
     from tokamak_b200.engine.step import StepEntry
     gen = torch.Generator().manual_seed(99)
     times = []
     for i in range(repeats + 1):
-        toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
+        toks = torch.randint(0, vocab, (tokens,), generator=gen).tolist()
         rid = f"prefill{i}"
         torch.cuda.synchronize()
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         begin.record()
-        core.step.run([StepEntry(rid, toks, [PREFILL_TOKENS - 1])], check=False)
+        core.step.run([StepEntry(rid, toks, [tokens - 1])], check=False)
         end.record()
         torch.cuda.synchronize()
         core.step.free(rid)
@@ -493,6 +493,8 @@ def main() -> int:
     ap.add_argument("--max-new-cap", type=int, default=256)
     ap.add_argument("--kv-pool-tokens", type=int, default=16384)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--seq-len", type=int, default=CONTEXT, help="context length at which the decode steps run")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="length of the timed prompt")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -527,29 +529,30 @@ def main() -> int:
     raw["num_hidden_layers"] = n_layers
     vocab = raw["vocab_size"]
     peaks = load_peaks()
+    ctx, pf_tokens = args.seq_len, args.prefill_tokens      # the defaults unless asked otherwise
     max_batch = 64 if not args.skip_points else max(args.batch, 1)
-    core = random_core(raw, seed=0, std=0.02, dtype="bfloat16", max_seq_len=CONTEXT, page_size=16,
-                       pool_tokens=max_batch * CONTEXT, max_slots=max_batch,
-                       max_step_tokens=max(PREFILL_TOKENS, args.batch * CONTEXT))
+    core = random_core(raw, seed=0, std=0.02, dtype="bfloat16", max_seq_len=max(ctx, pf_tokens), page_size=16,
+                       pool_tokens=max(max_batch * ctx, pf_tokens + 64), max_slots=max_batch,
+                       max_step_tokens=max(pf_tokens, args.batch * ctx))
     wbytes = weight_bytes(core)
 
     sampler = ClockSampler(torch.cuda.current_device())
     sampler.start()
-    main_run = time_decode(core, args.batch, steps, warmup, CONTEXT, vocab)
-    prefill_ms = time_prefill(core, vocab)
+    main_run = time_decode(core, args.batch, steps, warmup, ctx, vocab)
+    prefill_ms = time_prefill(core, vocab, pf_tokens)
     points = {}
     if not args.skip_points:
         for b in (1, 64):
-            points[f"decode_b{b}"] = round(time_decode(core, b, steps, warmup, CONTEXT, vocab)["tok_s"], 1)
-    e2e = time_e2e(core, args.batch, steps, warmup, CONTEXT, vocab)
+            points[f"decode_b{b}"] = round(time_decode(core, b, steps, warmup, ctx, vocab)["tok_s"], 1)
+    e2e = time_e2e(core, args.batch, steps, warmup, ctx, vocab)
     clocks = sampler.stop()
 
     step_bytes = wbytes + main_run["kv_bytes"]
     achieved = step_bytes / (main_run["ms_per_step"] / 1e3) / 1e9
-    pf_flops = step_flops(raw, n_layers, PREFILL_TOKENS)
+    pf_flops = step_flops(raw, n_layers, pf_tokens)
     pf_frac = pf_flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12)
     line = {
-        "metric": f"decode tok/s at batch {args.batch} ({model_name} layer sizes, context {CONTEXT})",
+        "metric": f"decode tok/s at batch {args.batch} ({model_name} layer sizes, context {ctx})",
         "value": round(main_run["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
         "warmup": warmup, "ms_per_step": round(main_run["ms_per_step"], 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
@@ -560,13 +563,13 @@ def main() -> int:
             "kv_heads": raw["num_key_value_heads"], "head_dim": raw["head_dim"],
             "intermediate": raw["intermediate_size"], "vocab": vocab, "rope_theta": raw["rope_theta"],
             "rms_norm_eps": raw["rms_norm_eps"], "tied_head": False, "global_batch": args.batch,
-            "seq_len": CONTEXT, "prefill_tokens": PREFILL_TOKENS, "kv_block": 16,
+            "seq_len": ctx, "prefill_tokens": pf_tokens, "kv_block": 16,
             "parallelism": "single GPU", "l2": "inputs larger than L2 (weights read every step)",
             "peaks": peaks["source"],
         },
         "e2e": {k: (round(v, 2) if isinstance(v, float) else v) for k, v in e2e.items()},
         "gpu_launches": main_run["launches"],
-        "prefill": {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
+        "prefill": {"value": round(pf_tokens / (prefill_ms / 1e3), 1), "tokens": pf_tokens,
                     "ms": round(prefill_ms, 3), "frac": round(pf_frac, 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4)},
