@@ -9,19 +9,22 @@
 //                cost one memory latency, and the next stage's are under way while it waits;
 //   warps 1, 10  one thread each issues tcgen05.mma for one query tile: S = Q K^T (M 128, N 64)
 //                into one of the tile's two score buffers in tensor memory, and O += P V
-//                (M 128, N head_dim) with V read straight from its page layout as an MN-major
-//                operand (issuing is what a single thread is slow at, hence one per tile);
+//                (M 128, N head_dim) with P read from tensor memory and V straight from its page
+//                layout as an MN-major operand (issuing is what a single thread is slow at,
+//                hence one per tile);
 //   warps 2..5   softmax of query tile 0, warps 6..9 of query tile 1: thread i owns query row
 //                i = tensor-memory lane i.  It reads its 64 scores with tcgen05.ld, masks
 //                (causal with offset kv_len - q_len, window), keeps a reference maximum and
-//                the normaliser in float32, writes the probabilities as bfloat16 into a swizzled
-//                shared tile for the second product, and rescales the output accumulator in
+//                the normaliser in float32, writes the probabilities as bfloat16 pairs over the
+//                scores they came from (tcgen05.st), where the second product takes them as its
+//                A operand straight from tensor memory, and rescales the output accumulator in
 //                tensor memory only when the row maximum has grown by more than 2^8 since the
 //                reference was set (the probabilities stay below 2^8, exact enough in bfloat16;
 //                the result is the same softmax).
-// Score buffers and probability tiles are double-buffered per query tile, so the tensor cores
-// work for one tile, or on the next key tile, while the other tile's softmax runs; two softmax
-// warps share every scheduler.
+// Every query tile has two score buffers, so the tensor cores work for one tile, or on the next
+// key tile, while the other tile's softmax runs; a buffer is written again only by a product that
+// the same thread issues after the one that read the probabilities in it, and the tensor cores
+// run a thread's products in order.  Two softmax warps share every scheduler.
 //
 // Pages are loaded whole.  A page that lies outside the block's visible keys is replaced by the
 // page of the block's last key (its probabilities are exactly zero), and the kernel that writes
@@ -94,9 +97,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   constexpr uint32_t KSUB_BYTES = kAtBN * 64 * 2;      // one sub-tile of a key or value tile
   constexpr uint32_t KV_BYTES = kAtBN * D * 2;         // one key tile (or one value tile)
   constexpr uint32_t STAGE_BYTES = 2 * KV_BYTES;
-  constexpr uint32_t P_BYTES = kAtBM * kAtBN * 2;
   constexpr uint32_t TMEM_COLS = 512;   // per query tile t: scores at t*128 + {0, 64}; outputs at 256 + t*128
-  constexpr uint32_t DATA_BYTES = kAtQT * Q_BYTES + kAtStages * STAGE_BYTES + kAtQT * 2 * P_BYTES;
+  constexpr uint32_t DATA_BYTES = kAtQT * Q_BYTES + kAtStages * STAGE_BYTES;
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const uint32_t raw = gt_smem_u32(smem_raw);
@@ -104,18 +106,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   unsigned char* smem = smem_raw + (base - raw);
   const uint32_t q_smem = base;
   const uint32_t kv_smem = q_smem + kAtQT * Q_BYTES;
-  const uint32_t p_smem = kv_smem + kAtStages * STAGE_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + DATA_BYTES);
   uint64_t* q_full = bars;                  // 1
   uint64_t* kv_full = bars + 1;             // kAtStages
   uint64_t* kv_empty = kv_full + kAtStages; // kAtStages
-  uint64_t* tile_bars = kv_empty + kAtStages;   // per query tile: s_full[2] s_empty[2] p_full[2] p_empty[2] o_full
-  auto s_full = [&](int t, int b) { return gt_smem_u32(tile_bars + t * 9 + b); };
-  auto s_empty = [&](int t, int b) { return gt_smem_u32(tile_bars + t * 9 + 2 + b); };
-  auto p_full = [&](int t, int b) { return gt_smem_u32(tile_bars + t * 9 + 4 + b); };
-  auto p_empty = [&](int t, int b) { return gt_smem_u32(tile_bars + t * 9 + 6 + b); };
-  auto o_full = [&](int t) { return gt_smem_u32(tile_bars + t * 9 + 8); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tile_bars + kAtQT * 9);
+  uint64_t* tile_bars = kv_empty + kAtStages;   // per query tile: s_full[2] p_full[2] p_empty[2] o_full
+  auto s_full = [&](int t, int b) { return gt_smem_u32(tile_bars + t * 7 + b); };
+  auto p_full = [&](int t, int b) { return gt_smem_u32(tile_bars + t * 7 + 2 + b); };
+  auto p_empty = [&](int t, int b) { return gt_smem_u32(tile_bars + t * 7 + 4 + b); };
+  auto o_full = [&](int t) { return gt_smem_u32(tile_bars + t * 7 + 6); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tile_bars + kAtQT * 7);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -133,7 +133,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     for (int t = 0; t < kAtQT; ++t) {
       for (int b = 0; b < 2; ++b) {
         mbar_init(s_full(t, b), 1);
-        mbar_init(s_empty(t, b), 4);
         mbar_init(p_full(t, b), 4);
         mbar_init(p_empty(t, b), 1);
       }
@@ -253,8 +252,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           if (mine && kt >= first_t[t] && kt <= last_t[t]) {
             const uint32_t k_addr = kv_smem + s * STAGE_BYTES;
             const int jt = kt - first_t[t], b = jt & 1;
-            if (jt >= 2) ok = mbar_wait(s_empty(t, b), (uint32_t)((jt >> 1) - 1) & 1u, abort_flag);
-            if (!ok) { set_error(p.err, kErrWait, 18, j, t); *abort_flag = 1; break; }
+            // the score buffer also held the probabilities of key tile jt - 2: the second product
+            // that read them was issued by this thread before, and the products run in order
             tc_fence_after();
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
@@ -275,12 +274,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             ok = mbar_wait(p_full(t, b), (uint32_t)(jt >> 1) & 1u, abort_flag);
             if (!ok) { set_error(p.err, kErrWait, 13, j, t); *abort_flag = 1; break; }
             tc_fence_after();
-            const uint32_t p_addr = p_smem + (uint32_t)(t * 2 + b) * P_BYTES;
+            const uint32_t p_tmem = tmem_base + (uint32_t)(t * 128 + b * kAtBN);   // 16 keys = 8 columns
 #pragma unroll
             for (int kk = 0; kk < kAtBN / 16; ++kk) {
-              const uint64_t da = umma_desc_sw128(p_addr) + (uint64_t)(2 * kk);
               const uint64_t db = umma_desc_sw128_mn(v_addr + kk * (16 * 128), KSUB_BYTES);
-              umma_bf16(tmem_base + (uint32_t)(256 + t * 128), da, db, idesc_o, (jt > 0 || kk > 0) ? 1u : 0u);
+              umma_bf16_ts(tmem_base + (uint32_t)(256 + t * 128), p_tmem + (uint32_t)(8 * kk), db, idesc_o,
+                           (jt > 0 || kk > 0) ? 1u : 0u);
             }
             umma_commit(p_empty(t, b));
             if (kt == last_t[t]) umma_commit(o_full(t));
@@ -319,9 +318,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         tmem_ld32(tmem_s + (uint32_t)(b * kAtBN) + 32, hi);
         tmem_wait_ld();
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_empty(t, b));
 
       // Scores stay unscaled in sv; the softmax scale (> 0) is folded into the exponent below.
       // A tile wholly below this row's diagonal and inside its window needs no mask.
@@ -381,21 +377,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       l_sum += psum.x + psum.y;
 
-      if (j >= 2) {     // the probability tile is free once the second product of key tile j - 2 is done
-        ok = __all_sync(0xffffffffu, mbar_wait(p_empty(t, b), (uint32_t)((j - 2) >> 1) & 1u, abort_flag));
-        if (!ok) { if (lane == 0) { set_error(p.err, kErrWait, 16, j, t); *abort_flag = 1; } break; }
-      }
-      unsigned char* prow = smem + kAtQT * Q_BYTES + kAtStages * STAGE_BYTES + (size_t)(t * 2 + b) * P_BYTES +
-                            (size_t)(row >> 3) * 1024 + (size_t)(row & 7) * 128;
+      // the probabilities take the place of the scores they came from: bfloat16 pairs in the
+      // first half of the score buffer, where the second product reads its A operand
+      {
+        uint32_t packed[kAtBN / 2];
 #pragma unroll
-      for (int ch = 0; ch < kAtBN / 8; ++ch) {
-        uint4 v;
-        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&v);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(sv[ch * 8 + 2 * e], sv[ch * 8 + 2 * e + 1]);
-        *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = v;
+        for (int c = 0; c < kAtBN / 2; ++c) {
+          const __nv_bfloat162 h2 = __floats2bfloat162_rn(sv[2 * c], sv[2 * c + 1]);
+          packed[c] = *reinterpret_cast<const uint32_t*>(&h2);
+        }
+        tmem_st32(tmem_s + (uint32_t)(b * kAtBN), packed);
+        tmem_wait_st();
       }
-      fence_async_shared();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full(t, b));
@@ -443,7 +436,7 @@ template <int D>
 static int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                              const AttnTcParams& p, cudaStream_t stream) {
   constexpr size_t smem_bytes = (size_t)kAtQT * kAtBM * D * 2 + (size_t)kAtStages * 2 * kAtBN * D * 2 +
-                                (size_t)kAtQT * 2 * kAtBM * kAtBN * 2 + 1024 /* alignment */ + 512 /* barriers */;
+                                1024 /* alignment */ + 512 /* barriers */;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
