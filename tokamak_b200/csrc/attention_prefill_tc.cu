@@ -241,6 +241,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const uint32_t idesc_s = umma_idesc(kAtBN, false);
       const uint32_t idesc_o = umma_idesc(D, true);
       const bool mine = t < n_qt;
+      // The descriptors are made once; a product adds what changes (16-byte units in the low bits):
+      // issuing is a chain of dependent instructions in one thread, and every one of them counts.
+      const uint64_t desc_q = umma_desc_sw128(q_smem + t * Q_BYTES);
+      const uint64_t desc_k = umma_desc_sw128(kv_smem);
+      const uint64_t desc_v = umma_desc_sw128_mn(kv_smem + KV_BYTES, KSUB_BYTES);
+      const uint32_t tmem_o_t = tmem_base + (uint32_t)(256 + t * 128);
       bool ok = mbar_wait(gt_smem_u32(q_full), 0u, abort_flag);
       if (!ok) { set_error(p.err, kErrWait, 11, 0, t); *abort_flag = 1; }
       for (int j = 0; j <= n_kt && ok; ++j) {
@@ -250,17 +256,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           ok = mbar_wait(gt_smem_u32(&kv_full[s]), (uint32_t)(j / kAtStages) & 1u, abort_flag);
           if (!ok) { set_error(p.err, kErrWait, 12, j, s); *abort_flag = 1; break; }
           if (mine && kt >= first_t[t] && kt <= last_t[t]) {
-            const uint32_t k_addr = kv_smem + s * STAGE_BYTES;
+            const uint64_t desc_ks = desc_k + (uint64_t)((uint32_t)s * (STAGE_BYTES >> 4));
             const int jt = kt - first_t[t], b = jt & 1;
+            const uint32_t tmem_sb = tmem_base + (uint32_t)(t * 128 + b * kAtBN);
             // the score buffer also held the probabilities of key tile jt - 2: the second product
             // that read them was issued by this thread before, and the products run in order
             tc_fence_after();
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
-              const uint64_t da = umma_desc_sw128(q_smem + t * Q_BYTES + (ks / 4) * (kAtBM * 128)) +
-                                  (uint64_t)(2 * (ks % 4));
-              const uint64_t db = umma_desc_sw128(k_addr + (ks / 4) * KSUB_BYTES) + (uint64_t)(2 * (ks % 4));
-              umma_bf16(tmem_base + (uint32_t)(t * 128 + b * kAtBN), da, db, idesc_s, ks > 0 ? 1u : 0u);
+              const uint64_t da = desc_q + (uint64_t)((ks / 4) * ((kAtBM * 128) >> 4) + 2 * (ks % 4));
+              const uint64_t db = desc_ks + (uint64_t)((ks / 4) * (KSUB_BYTES >> 4) + 2 * (ks % 4));
+              umma_bf16(tmem_sb, da, db, idesc_s, ks > 0 ? 1u : 0u);
             }
             umma_commit(s_full(t, b));
           }
@@ -269,7 +275,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           const int s = (j - 1) % kAtStages;
           const int kt = first_kt + j - 1;
           if (mine && kt >= first_t[t] && kt <= last_t[t]) {
-            const uint32_t v_addr = kv_smem + s * STAGE_BYTES + KV_BYTES;
+            const uint64_t desc_vs = desc_v + (uint64_t)((uint32_t)s * (STAGE_BYTES >> 4));
             const int jt = kt - first_t[t], b = jt & 1;
             ok = mbar_wait(p_full(t, b), (uint32_t)(jt >> 1) & 1u, abort_flag);
             if (!ok) { set_error(p.err, kErrWait, 13, j, t); *abort_flag = 1; break; }
@@ -277,9 +283,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const uint32_t p_tmem = tmem_base + (uint32_t)(t * 128 + b * kAtBN);   // 16 keys = 8 columns
 #pragma unroll
             for (int kk = 0; kk < kAtBN / 16; ++kk) {
-              const uint64_t db = umma_desc_sw128_mn(v_addr + kk * (16 * 128), KSUB_BYTES);
-              umma_bf16_ts(tmem_base + (uint32_t)(256 + t * 128), p_tmem + (uint32_t)(8 * kk), db, idesc_o,
-                           (jt > 0 || kk > 0) ? 1u : 0u);
+              const uint64_t db = desc_vs + (uint64_t)(kk * ((16 * 128) >> 4));
+              umma_bf16_ts(tmem_o_t, p_tmem + (uint32_t)(8 * kk), db, idesc_o, (jt > 0 || kk > 0) ? 1u : 0u);
             }
             umma_commit(p_empty(t, b));
             if (kt == last_t[t]) umma_commit(o_full(t));
