@@ -48,7 +48,10 @@ attn_prefill_kernel(PrefillParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t smem_base = smem_u32(smem);
 
-  const int tile_id = blockIdx.x, head = blockIdx.y;
+  // heads vary fastest: the tiles are listed with the most keys first, so the blocks start in
+  // that order over all heads (the short ones fill the end), and the query heads that share a
+  // kv head run at the same time and find its keys and values in L2
+  const int head = blockIdx.x, tile_id = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t4 = lane & 3;
   const int group = p.n_q_heads / p.n_kv_heads;
@@ -261,7 +264,8 @@ static int launch_prefill(const PrefillParams& p, cudaStream_t stream) {
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid(p.n_tiles, p.n_q_heads);
+  if (p.n_tiles > 65535) return (int)cudaErrorInvalidValue;
+  dim3 grid(p.n_q_heads, p.n_tiles);
   return (int)launch(attn_prefill_kernel<D>, grid, dim3(kPfWarps * 32), smem_bytes, stream, p);
 }
 

@@ -119,7 +119,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile_id = blockIdx.x, head = blockIdx.y;
+  // heads vary fastest: the tiles are listed with the most keys first, so the blocks start in
+  // that order over all heads (the short ones fill the end), and the query heads that share a
+  // kv head run at the same time and find its keys and values in L2
+  const int head = blockIdx.x, tile_id = blockIdx.y;
   const int group = p.n_q_heads / p.n_kv_heads;
   const int hkv = head / group;
 
@@ -449,7 +452,8 @@ static int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mk, const
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid(p.n_tiles, p.n_q_heads);
+  if (p.n_tiles > 65535) return (int)cudaErrorInvalidValue;
+  dim3 grid(p.n_q_heads, p.n_tiles);
   return (int)launch(attn_prefill_tc_kernel<D>, grid, dim3(kAtThreads), smem_bytes, stream, mq, mk, mv, p);
 }
 
