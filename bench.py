@@ -470,6 +470,35 @@ def kernel_case(name: str, batch: int, ctx: int, iters: int, peaks: dict) -> dic
     return res
 
 
+def reference_main(args) -> int:
+    """``--impl reference``: the unmodified reference from ``baseline/_ref`` on the same metric, or
+    one line that says why it cannot run.  Everything it does is in ``baseline/reference_arm.py``."""
+    sys.path.insert(0, str(ROOT / "baseline"))
+    import reference_arm
+    why = reference_arm.available()
+    if why is None and args.gpus != 1:
+        why = "the reference runs on one GPU only"
+    if why is None and args.sizes not in SIZES:
+        why = "--sizes 0.6b is for --workload throughput only"
+    if why is not None:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    model_name, sizes = SIZES[args.sizes]
+    raw = dict(sizes)
+    if args.layers:
+        raw["num_hidden_layers"] = args.layers
+    try:
+        line = reference_arm.run(raw, model_name, args.batch, args.seq_len, args.prefill_tokens, max(1, args.steps),
+                                 max(3, args.warmup), points=() if args.skip_points else (1, 64),
+                                 clock_sampler=ClockSampler(0))
+    except Exception as err:    # the reference's failure is reported, never hidden behind our numbers
+        print(json.dumps({"impl": "reference", "unavailable": f"{type(err).__name__}: {str(err)[:300]}"}))
+        return 0
+    line["config"]["layers_of_model"] = sizes["num_hidden_layers"]
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -498,10 +527,7 @@ def main() -> int:
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "pip install --no-index of WeichunK/tokamak fails offline: its build backend "
-                          "hatchling is neither installed nor in the wheelhouse"}))
-        return 0
+        return reference_main(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
