@@ -305,6 +305,49 @@ def throughput_workload(sizes: str, num_requests: int, max_new_cap: int, batch: 
             "preemptions": stats["preemptions"], "dtype": "bf16", "data": "synthetic"}
 
 
+def mixed_workload(sizes: str, num_requests: int, new_tokens: int, chunk: int, seed: int) -> dict:
+    """A mixed batch through ``LLM.generate``: ``num_requests`` requests with prompt lengths uniform
+    in 128..4,096, all submitted at once, prompts computed in portions of ``chunk`` tokens beside the
+    decode tokens of the requests that already run, ``new_tokens`` greedy tokens each, context limit
+    8,192.  Every request runs from the start (a pool for all of them), so all but the first steps
+    are mixed steps until the last prompt is done."""
+    import random
+    import torch
+    from tokamak_b200 import LLM, SamplingParams
+    from tokamak_b200.engine.core import random_core
+    raw = dict(QWEN3_0_6B if sizes == "0.6b" else SIZES[sizes][1])
+    rng = random.Random(seed)
+    lengths = [rng.randint(128, 4096) for _ in range(num_requests)]
+    prompts = [[rng.randrange(raw["vocab_size"]) for _ in range(n)] for n in lengths]
+    pool = sum(-(-(n + new_tokens) // 16) * 16 for n in lengths)
+    core = random_core(raw, seed=0, std=0.02, dtype="bfloat16", max_seq_len=8192, page_size=16,
+                       pool_tokens=max(pool, 8192), max_slots=num_requests,
+                       max_step_tokens=chunk + num_requests)
+    llm = LLM("<random>", _core=core, max_batch_size=num_requests, max_num_batched_tokens=chunk + num_requests,
+              prefill_chunk=chunk, block_size=16)
+    params = SamplingParams(temperature=0.0, max_new_tokens=new_tokens, ignore_eos=True)
+    llm.generate(prompt_token_ids=prompts, sampling_params=params)          # warm-up
+    runs = []
+    for _ in range(3):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        outs = llm.generate(prompt_token_ids=prompts, sampling_params=params)
+        torch.cuda.synchronize()
+        runs.append((time.perf_counter() - t0, outs, dict(llm.last_stats)))
+    runs.sort(key=lambda r: r[0])
+    wall, outs, stats = runs[1]
+    n_out = sum(len(o.output_token_ids) for o in outs)
+    ttft = sorted(o.ttft_s for o in outs)
+    return {"workload": "mixed batch (prompt portions beside decode tokens)", "sizes": f"Qwen3-{sizes.upper()} layer sizes",
+            "requests": num_requests, "prompt_tokens": sum(lengths), "output_tokens": n_out,
+            "prefill_chunk": chunk, "max_seq_len": 8192, "kv_pool_tokens": max(pool, 8192),
+            "total_tok_s": round((sum(lengths) + n_out) / wall, 1), "output_tok_s": round(n_out / wall, 1),
+            "wall_s": round(wall, 3), "wall_s_runs": [round(r[0], 3) for r in runs],
+            "ttft_mean_s": round(sum(ttft) / len(ttft), 4), "ttft_max_s": round(ttft[-1], 4),
+            "steps": stats["steps"], "mixed_steps": stats["mixed_steps"], "preemptions": stats["preemptions"],
+            "dtype": "bf16", "data": "synthetic"}
+
+
 def latency_workload(sizes: str, prompt_tokens: int, new_tokens: int, iters: int, seed: int) -> dict:
     """Single-sequence latency as the reference measures it (benchmarks/benchmark_latency.py:63-97,
     119-133): one seeded random prompt, time to the first token (prefill, argmax on the host side
@@ -512,9 +555,12 @@ def main() -> int:
                     "attention_prefill (tcgen05), attention_prefill_mma, rope_kv, rmsnorm, gemm_tc_decode, gemm_decode (library), "
                     "gemm_pair_swiglu, gemm_prefill_library (--ctx tokens)")
     ap.add_argument("--ctx", type=int, default=CONTEXT, help="context length of a --kernel case")
-    ap.add_argument("--workload", default=None, choices=["throughput", "latency"],
+    ap.add_argument("--workload", default=None, choices=["throughput", "latency", "mixed"],
                     help="run the reference's throughput workload through LLM.generate, or its single-sequence "
-                         "latency measurement (512 prompt tokens, 128 greedy steps), instead")
+                         "latency measurement (512 prompt tokens, 128 greedy steps), or a mixed batch of 32 "
+                         "requests (prompts of 128 to 4,096 tokens in portions of 512 beside decode tokens, 256 "
+                         "new tokens each; --sizes 14b is the configuration it is named for), instead")
+    ap.add_argument("--prefill-chunk", type=int, default=512, help="portion size of --workload mixed")
     ap.add_argument("--sizes", default="8b", choices=["0.6b", "8b", "14b", "32b"],
                     help="layer sizes: of --workload (0.6b, 8b), or of the decode/prefill run (8b, the metric's "
                          "own, 14b, 32b)")
@@ -538,6 +584,10 @@ def main() -> int:
         return 0
     if args.workload == "latency":
         print(json.dumps(latency_workload(args.sizes, 512, 128, 3, args.seed)))
+        return 0
+    if args.workload == "mixed":
+        print(json.dumps(mixed_workload(args.sizes, args.num_requests, args.max_new_cap, args.prefill_chunk,
+                                        args.seed)))
         return 0
     if args.workload == "throughput":
         print(json.dumps(throughput_workload(args.sizes, args.num_requests, args.max_new_cap, args.batch,
