@@ -2,6 +2,7 @@
 
 from __future__ import annotations
 
+import contextlib
 from dataclasses import dataclass
 
 import torch
@@ -119,6 +120,18 @@ class Attention:
                     req_q_len=step.req_q_len, req_kv_len=step.req_kv_len)
 
 
+_SIDE: dict = {}
+
+
+def _side_stream(device: torch.device):
+    """A second stream of the device and the two events that fork to it and join from it."""
+    entry = _SIDE.get(device)
+    if entry is None:
+        entry = (torch.cuda.Stream(device), torch.cuda.Event(), torch.cuda.Event())
+        _SIDE[device] = entry
+    return entry
+
+
 def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, scale: float,
                     window: int | None) -> None:
     """Attention of every token of the step over the pages of its own request.
@@ -135,10 +148,21 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
     n_pf = step.prefill_items.numel()
     dec_tiled = bf16 and n_dec > 0 and ops.decode_kernel_takes(hq, hkv, d, page)
     pf_tiled = bf16 and n_pf > 0 and ops.prefill_kernel_takes(hq, hkv, d, page)
+    # In a mixed step the two kernels touch different tokens.  One portion against a long context
+    # is few blocks (one per pair of 128-row query tiles and head), so the decode kernel runs
+    # beside it on a second stream instead of after it.
+    beside = dec_tiled and pf_tiled and not torch.cuda.is_current_stream_capturing()
+    if beside:
+        side, fork, join = _side_stream(q.device)
+        fork.record()
+        side.wait_event(fork)
     if dec_tiled:
-        ops.attention_decode(q, out, cache_view.k, cache_view.v, step.decode_items, step.positions,
-                             step.tok_req, step.req_slot, cache_view.table, step.err, scale=scale,
-                             window=window, n_splits=ops.decode_splits(n_dec, hkv, step.max_kv_len))
+        with torch.cuda.stream(side) if beside else contextlib.nullcontext():
+            ops.attention_decode(q, out, cache_view.k, cache_view.v, step.decode_items, step.positions,
+                                 step.tok_req, step.req_slot, cache_view.table, step.err, scale=scale,
+                                 window=window, n_splits=ops.decode_splits(n_dec, hkv, step.max_kv_len))
+            if beside:
+                join.record()
     if pf_tiled and ops.prefill_tc_kernel_takes(hq, hkv, d, page):
         ops.attention_prefill_tc(q, out, cache_view.k, cache_view.v, step.prefill_tiles_tc,
                                  step.req_q_start, step.req_q_len, step.req_kv_len, step.req_slot,
@@ -147,6 +171,8 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
         ops.attention_prefill(q, out, cache_view.k, cache_view.v, step.prefill_tiles,
                               step.req_q_start, step.req_q_len, step.req_kv_len, step.req_slot,
                               cache_view.table, step.err, scale=scale, window=window)
+    if beside:
+        torch.cuda.current_stream().wait_event(join)
     dec_rest = n_dec > 0 and not dec_tiled
     pf_rest = n_pf > 0 and not pf_tiled
     if dec_rest or pf_rest:
