@@ -441,9 +441,10 @@ def kernel_case(name: str, batch: int, ctx: int, iters: int, peaks: dict) -> dic
         wq, wk = torch.ones(d, device=dev), torch.ones(d, device=dev)
         inv_freq = (1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(dev)
         rot = ops.rope_table(positions, inv_freq)
-        run = lambda: ops.rope_kv(qkv, q_out, kc, vc, positions, tok_req, i32([0]), table, wq, wk, rot, err,
+        slot0, len_n = i32([0]), i32([n])      # made once: a tensor from a host list is a blocking copy
+        run = lambda: ops.rope_kv(qkv, q_out, kc, vc, positions, tok_req, slot0, table, wq, wk, rot, err,
                                   n_q_heads=hq, n_kv_heads=hkv, head_dim=d, rotary_dim=d, eps=1e-6,
-                                  req_q_len=i32([n]), req_kv_len=i32([n]))
+                                  req_q_len=len_n, req_kv_len=len_n)
         nbytes = qkv.numel() * 2 + q_out.numel() * 2 + 2 * n * hkv * d * 2
     elif name == "rmsnorm":
         n, h = batch, cfg["hidden_size"]
