@@ -27,3 +27,24 @@ def test_write_random_from_the_command_line(tmp_path, capsys):
     assert main(["--write-random", str(out), "--config", str(cfg), "--seed", "3", "--weights-dtype", "float32"]) == 0
     assert (out / "config.json").is_file() and (out / "model.safetensors").is_file()
     assert "wrote" in capsys.readouterr().out
+
+
+def test_llm_accepts_the_reference_options_at_their_defaults_and_refuses_the_rest():
+    """A call written for the reference (src/tokamak/engine/llm.py:64-122) still works: the options
+    that name parts this engine does not have are taken at their defaults and refused otherwise.
+    The checks come before anything touches the device, so they run without one."""
+    import types
+
+    import pytest
+
+    from tokamak_b200.engine.llm import LLM
+
+    for bad in ({"kv_backend": "contiguous"}, {"scheduling": "static"}, {"attention_backend": "sdpa"},
+                {"draft_model": "some/folder"}, {"attention_policy": "streaming:64+4"}, {"block_size": 0},
+                {"max_batch_size": 0}):
+        with pytest.raises(ValueError):
+            LLM("nowhere", **bad)
+    core = types.SimpleNamespace(config=None, max_seq_len=64, device="cuda:0", dtype=None, manager=None, model=None)
+    llm = LLM("nowhere", kv_backend="paged", scheduling="continuous", attention_backend="auto", draft_model=None,
+              num_speculative_tokens=4, _core=core)
+    assert llm.max_seq_len == 64 and llm.max_batch_size == 16

@@ -55,6 +55,11 @@ def parse_attention_policy(spec: str) -> int | None:
     raise ValueError(f"Unknown attention_policy: {spec!r} (expected 'full' or 'window:W')")
 
 
+def _only(name: str, value, allowed: tuple, why: str) -> None:
+    if value not in allowed:
+        raise ValueError(f"{name}={value!r} is not available: {why} (allowed: {', '.join(map(repr, allowed))})")
+
+
 class LLM:
     """Loads a model once and serves batch generation requests.
 
@@ -74,6 +79,9 @@ class LLM:
         max_num_batched_tokens: most tokens of one step (decode tokens plus prompt portions).
         prefill_chunk: most tokens of one prompt portion; ``None`` leaves it to the budget.
         attention_policy: ``"full"`` or ``"window:W"``, a window applied to every layer.
+        kv_backend, scheduling, attention_backend, draft_model, num_speculative_tokens: accepted
+            with the reference's defaults (``"paged"``, ``"continuous"``, ``"auto"``, ``None``), so
+            that a call written for it still works; any other value is refused with the reason.
     """
 
     def __init__(self, model: str | Path, *, device: str | torch.device = "auto",
@@ -81,7 +89,15 @@ class LLM:
                  block_size: int = 16, kv_pool_tokens: int | str | None = None, max_batch_size: int = 16,
                  max_num_batched_tokens: int = 2048, prefill_chunk: int | None = None,
                  attention_policy: str = "full", gpu_memory_utilization: float = 0.9,
-                 _core: EngineCore | None = None) -> None:
+                 kv_backend: str = "paged", scheduling: str = "continuous",
+                 attention_backend: str = "auto", draft_model: str | None = None,
+                 num_speculative_tokens: int = 4, _core: EngineCore | None = None) -> None:
+        # options of the reference whose other values name parts that this engine does not have
+        _only("kv_backend", kv_backend, ("paged",), "the cache is always paged")
+        _only("scheduling", scheduling, ("continuous",), "requests always join and leave step by step")
+        _only("attention_backend", attention_backend, ("auto",), "attention always runs on this engine's kernels")
+        if draft_model is not None:
+            raise ValueError("draft_model: speculative decoding is not part of this engine")
         if block_size < 1:
             raise ValueError(f"block_size must be >= 1, got {block_size}")
         if max_batch_size < 1:
