@@ -203,3 +203,32 @@ def test_plan_ahead_gives_up_when_pages_are_short():
         e.seq.num_computed = e.start + e.count
     assert s2.plan_ahead(dec, lambda q: 10 ** 6) is None    # position 8 would need a third page
     m2.check_invariants()
+
+
+def test_watermark_keeps_room_for_the_running_and_never_blocks_a_lone_request():
+    # 16 pages of 4 positions; a quarter of them (4 pages) stays free while anything runs
+    m = CacheManager([KVGroup(KVPagesNeed(1, 16), 16, 4, ["l0"])], [], 4)
+    s = Scheduler(m, 4, 256, None, watermark=0.25)
+    a, b, c = seq(0, 24), seq(1, 24), seq(2, 8)         # 6 + 6 + 2 pages
+    for x in (a, b, c):
+        s.add(x)
+    p = s.schedule()
+    # a is alone when it is admitted (no margin asked); b would leave 4 free: just allowed;
+    # c would leave 2: it waits although its pages are free, and nobody overtakes
+    assert [e.seq.seq_id for e in p.entries] == [0, 1]
+    run_plan(m, p)
+    assert [e.seq.seq_id for e in s.schedule().entries] == [0, 1]
+    assert m.kv_groups[0].num_free >= 2 and c.status is SequenceStatus.WAITING
+    # without the margin all three start at once
+    m2 = CacheManager([KVGroup(KVPagesNeed(1, 16), 16, 4, ["l0"])], [], 4)
+    s2 = Scheduler(m2, 4, 256, None)
+    for x in (seq(0, 24), seq(1, 24), seq(2, 8)):
+        s2.add(x)
+    assert [e.seq.seq_id for e in s2.schedule().entries] == [0, 1, 2]
+    # a request that is alone is admitted whenever it fits, whatever the margin
+    m3 = CacheManager([KVGroup(KVPagesNeed(1, 16), 16, 4, ["l0"])], [], 4)
+    s3 = Scheduler(m3, 4, 256, None, watermark=0.9)
+    s3.add(seq(0, 60))
+    assert [e.seq.seq_id for e in s3.schedule().entries] == [0]
+    with pytest.raises(ValueError):
+        Scheduler(m3, 4, 256, None, watermark=1.0)

@@ -61,16 +61,22 @@ class Scheduler:
         max_num_batched_tokens: most tokens of one step.
         prefill_chunk: most tokens of one sequence's prompt portion in a step
             (``None``: limited by the budget only).
+        watermark: share of every pool that an admission must leave free while other sequences
+            run, as room for their growth (fewer preemptions at the price of later admissions).
+            The reference has none (docs/design/003-continuous-batching.md:59-62), which is the
+            default; a request that is alone is admitted whenever it fits.
     """
 
     def __init__(self, manager: CacheManager, max_batch_size: int, max_num_batched_tokens: int,
-                 prefill_chunk: int | None = None):
+                 prefill_chunk: int | None = None, watermark: float = 0.0):
         if max_batch_size < 1:
             raise ValueError(f"max_batch_size must be >= 1, got {max_batch_size}")
         if max_num_batched_tokens < 1:
             raise ValueError(f"max_num_batched_tokens must be >= 1, got {max_num_batched_tokens}")
         if prefill_chunk is not None and prefill_chunk < 1:
             raise ValueError(f"prefill_chunk must be >= 1, got {prefill_chunk}")
+        if not 0.0 <= watermark < 1.0:
+            raise ValueError(f"watermark must be in [0, 1), got {watermark}")
         if max_batch_size > manager.max_slots:
             raise ValueError(f"max_batch_size ({max_batch_size}) exceeds the cache's request "
                              f"slots ({manager.max_slots})")
@@ -78,6 +84,7 @@ class Scheduler:
         self._max_batch_size = max_batch_size
         self._budget = max_num_batched_tokens
         self._chunk = prefill_chunk
+        self._watermark = watermark
         self.waiting: deque[Sequence] = deque()
         self.running: list[Sequence] = []
         self.num_preemptions = 0
@@ -176,7 +183,9 @@ class Scheduler:
 
     # ------------------------------------------------------------------------------
     def _fits_new(self, seq: Sequence) -> bool:
-        return all(g.pages_for(seq.num_tokens) <= g.num_free for g in self._manager.kv_groups)
+        keep = self._watermark if self.running else 0.0
+        return all(g.pages_for(seq.num_tokens) + int(keep * g.num_pages) <= g.num_free
+                   for g in self._manager.kv_groups)
 
     def _reserve(self, seq: Sequence, num_tokens: int, preempted: list[Sequence],
                  entries: list[PlannedEntry]) -> bool:
