@@ -232,3 +232,60 @@ def test_watermark_keeps_room_for_the_running_and_never_blocks_a_lone_request():
     assert [e.seq.seq_id for e in s3.schedule().entries] == [0]
     with pytest.raises(ValueError):
         Scheduler(m3, 4, 256, None, watermark=1.0)
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_workloads_finish_in_arrival_order_with_every_page_accounted_for(seed):
+    """Random requests through small pools (a full and a windowed group), with random budgets,
+    portion sizes and margins: every step keeps the cache's invariants, plans only what the pages
+    cover, never lets a later arrival start before an earlier one has, and every request ends with
+    exactly its tokens, preempted or not."""
+    import random
+    rng = random.Random(seed)
+    page = rng.choice((2, 4, 8))
+    window = rng.choice((None, 3 * page, 5 * page + 1))
+    n_pages = rng.randint(12, 40)
+    groups = [KVGroup(KVPagesNeed(1, 16), n_pages, page, ["full"])]
+    if window is not None:
+        groups.append(KVGroup(KVPagesNeed(1, 16, window=window), n_pages, page, ["windowed"]))
+    slots = rng.randint(2, 6)
+    m = CacheManager(groups, [], slots)
+    budget = rng.randint(max(slots, 4), 48)
+    chunk = rng.choice((None, 2, 5, 16))
+    s = Scheduler(m, slots, budget, chunk, watermark=rng.choice((0.0, 0.0, 0.2)))
+    most = (n_pages - 1) * page                        # every request fits the empty pool alone
+    seqs = []
+    for i in range(rng.randint(5, 14)):
+        n_prompt = rng.randint(1, max(1, most // 2))
+        max_new = rng.randint(1, max(1, min(20, most - n_prompt)))
+        q = seq(i, n_prompt, max_new)
+        seqs.append(q)
+        s.add(q)
+    started: list[int] = []
+    steps = 0
+    while s.has_unfinished():
+        plan = s.schedule()
+        assert plan is not None and plan.entries
+        steps += 1
+        assert steps < 20000, "the scheduler makes no progress"
+        assert plan.num_tokens <= budget
+        ids = [e.seq.seq_id for e in plan.entries]
+        assert len(set(ids)) == len(ids) and len(s.running) <= slots
+        for e in plan.entries:
+            assert e.seq.status is SequenceStatus.RUNNING and e.count >= 1
+            assert e.start == e.seq.num_computed == m.length(e.seq.seq_id)
+            assert chunk is None or e.count <= chunk or e.count == 1
+            assert e.samples == (e.start + e.count == e.seq.num_tokens)
+            for g in m.kv_groups:                      # the pages of the planned positions are there
+                assert len(g.table(e.seq.seq_id)) >= g.pages_for(e.start + e.count)
+            if e.start == 0 and e.seq.seq_id not in started:
+                started.append(e.seq.seq_id)
+        for v in plan.preempted:
+            assert v.status is SequenceStatus.WAITING and v.num_computed == 0 and not m.has(v.seq_id)
+        run_plan(m, plan, token=rng.randrange(1, 50))
+        m.check_invariants()
+    assert started == sorted(started)                  # first starts happen in arrival order
+    for q in seqs:
+        assert q.is_finished and q.num_output_tokens == q.sampling_params.max_new_tokens
+    assert not m.live_requests()
+    assert all(g.num_free == g.num_pages for g in m.kv_groups)
