@@ -115,15 +115,9 @@ class ClockSampler:
 
 
 def weight_bytes(core) -> int:
-    """Bytes of every weight a decode step reads once (the embedding table is read by row only)."""
-    import torch
-    m = core.model
-    total = 0
-    for blk in m.blocks.values():
-        for t in (blk.mixer.w_qkv, blk.mixer.w_o, blk.feed_forward.w_gate_up, blk.feed_forward.w_down):
-            total += t.numel() * t.element_size()
-    total += m.head.weight.numel() * m.head.weight.element_size()
-    return total
+    """Bytes of every weight a decode step reads once, as the model's parts report them (the
+    embedding table is read by row only and reports nothing)."""
+    return core.model.step_weight_bytes()
 
 
 def step_flops(cfg, n_layers: int, tokens: int, ctx_start: int = 0) -> float:
@@ -150,33 +144,42 @@ def fill_context(core, req_ids, length: int, vocab: int, seed: int) -> None:
 
 
 def time_decode(core, batch: int, steps: int, warmup: int, ctx_end: int, vocab: int):
-    """Device time of ``steps`` decode steps of ``batch`` requests whose context ends at ``ctx_end``."""
+    """Device time of ``steps`` decode steps of ``batch`` requests whose context ends at ``ctx_end``.
+
+    The steps run as generation runs them: each request's token, position and sampling state
+    are in its slot record on the device, the step is replayed from a CUDA graph, and it is
+    launched one ahead, before the host has read the step before it; every step's tokens still
+    come back to the host.  Afterwards the same requests are rewound and the same steps run
+    again kernel by kernel, without graphs and without launching ahead: the tokens must be the
+    same, or the timed path computed something else than the plain path."""
     import torch
     from tokamak_b200.csrc import ops
     from tokamak_b200.engine.step import SamplingRow, StepEntry
+    step = core.step
     req_ids = [f"b{batch}_{i}" for i in range(batch)]
     start_len = ctx_end - (steps + warmup + 1)
-    fill_context(core, req_ids, start_len, vocab, seed=batch)
-    greedy = [SamplingRow(0.0, 0, 1.0, 0, 0) for _ in range(batch)]
-    tokens = [1 + i for i in range(batch)]
+    for rid in req_ids:
+        step.admit(rid, SamplingRow())                 # greedy
+    fill_context(core, req_ids, start_len - 1, vocab, seed=batch)
+    last = [1 + i for i in range(batch)]
+    # the last prompt token of every request, sampled: from here on the records carry the requests
+    first = step.run_and_sample([StepEntry(r, [t], [0]) for r, t in zip(req_ids, last)])
+    entries = [StepEntry(r, None, [0]) for r in req_ids]
+    produced = [first]
 
-    # Steps are launched one ahead: the token that a step samples stays on the device and feeds
-    # the next step, which is launched before the host has read the step before it, so the
-    # device does not wait for the host.  Every step's tokens still come back to the host.
-    fed_entries = [StepEntry(r, [0], [0]) for r in req_ids]
-    feed = list(range(batch))
-    flight = core.step.launch_and_sample([StepEntry(r, [t], [0]) for r, t in zip(req_ids, tokens)], greedy)
+    flight = step.launch_and_sample(entries)
 
     def one_step():
-        nonlocal tokens, flight
-        ahead = core.step.launch_and_sample(fed_entries, greedy, feed)
-        tokens = core.step.collect(flight)
+        nonlocal flight
+        ahead = step.launch_and_sample(entries)
+        produced.append(step.collect(flight))
         flight = ahead
 
     for _ in range(warmup):
         one_step()
     torch.cuda.synchronize()
-    launches0 = ops.LAUNCHES + core.step.graph_launches
+    launches0 = ops.LAUNCHES + step.graph_launches
+    h2d0, d2h0 = step.buffers.h2d_bytes, step.buffers.d2h_bytes
     t_host = time.perf_counter()
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     begin.record()
@@ -184,15 +187,31 @@ def time_decode(core, batch: int, steps: int, warmup: int, ctx_end: int, vocab: 
         one_step()
     end.record()
     torch.cuda.synchronize()
-    tokens = core.step.collect(flight)
+    produced.append(step.collect(flight))
     ms = begin.elapsed_time(end)
     wall = time.perf_counter() - t_host
-    launches = ops.LAUNCHES + core.step.graph_launches - launches0
+    launches = ops.LAUNCHES + step.graph_launches - launches0
+    h2d, d2h = step.buffers.h2d_bytes - h2d0, step.buffers.d2h_bytes - d2h0
     kv_bytes = batch * (ctx_end - steps / 2.0) * core.cache.bytes_per_token()
+
+    # the check: rewind every request to where the records took over and decode again, plainly
+    replays = step.graph_replays
+    for rid in req_ids:
+        step.restart(rid)
+    fill_context(core, req_ids, start_len - 1, vocab, seed=batch)
+    graphs, step.use_graphs = step.use_graphs, False
+    toks = step.run_and_sample([StepEntry(r, [t], [0]) for r, t in zip(req_ids, last)])
+    checked = toks == produced[0]
+    for want in produced[1:]:
+        toks = step.run_and_sample([StepEntry(r, [t], [0]) for r, t in zip(req_ids, toks)])
+        checked = checked and toks == want
+    step.use_graphs = graphs
+    assert step.graph_replays == replays
     for r in req_ids:
-        core.step.free(r)
+        step.free(r)
     return {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3), "launches": launches,
-            "kv_bytes": kv_bytes, "wall_ms_per_step": wall * 1e3 / steps}
+            "kv_bytes": kv_bytes, "wall_ms_per_step": wall * 1e3 / steps, "checked": checked,
+            "graph_replays": replays, "h2d_bytes_per_step": h2d / steps, "d2h_bytes_per_step": d2h / steps}
 
 
 def time_prefill(core, vocab: int, tokens: int = PREFILL_TOKENS, repeats: int = 3):
@@ -238,11 +257,13 @@ def time_e2e(core, batch: int, steps: int, warmup: int, ctx_end: int, vocab: int
     assert len(times) >= steps + warmup, "the requests did not decode together"
     full = times[-steps:]                         # the last K decode steps, all at full batch
     tok_s = batch * len(full) / sum(full)
-    # int32 words of a decode step's description: 9 per request for the batch layout, 7 for sampling
-    # (feed place, 64-bit seed, temperature, top-p, top-k, counter)
-    h2d = 4 * 16 * batch
+    # bytes copied to the device in those steps, counted from the copies the step function made: a
+    # decode step's description lives in the slot records on the device, so what is copied is the
+    # block-table entries of new pages (a new page every 16 tokens of a request) and, when the set
+    # of running requests changes, the list of their slots
+    h2d = sum(llm.last_stats["decode_step_h2d_bytes"][-steps:]) / len(full)
     d2h = 4 * (4 + batch)
-    return {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+    return {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": round(h2d, 1), "d2h_bytes_per_step": d2h,
             "ms_per_step": 1e3 * sum(full) / len(full), "warmup_steps": warmup}
 
 
@@ -362,16 +383,16 @@ def latency_workload(sizes: str, prompt_tokens: int, new_tokens: int, iters: int
                        pool_tokens=2 * total, max_slots=2, max_step_tokens=max(prompt_tokens, 64))
     gen = torch.Generator().manual_seed(seed)
     prompt = torch.randint(0, raw["vocab_size"], (prompt_tokens,), generator=gen).tolist()
-    greedy = [SamplingRow()]
 
     def run_once(i: int) -> tuple[float, float]:
         rid = f"lat{i}"
+        core.step.admit(rid, SamplingRow())
         torch.cuda.synchronize()
         t0 = time.perf_counter()
-        token = core.step.run_and_sample([StepEntry(rid, prompt, [prompt_tokens - 1])], greedy)[0]
+        token = core.step.run_and_sample([StepEntry(rid, prompt, [prompt_tokens - 1])])[0]
         t1 = time.perf_counter()
         for _ in range(new_tokens):
-            token = core.step.run_and_sample([StepEntry(rid, [token], [0])], greedy)[0]
+            token = core.step.run_and_sample([StepEntry(rid, None, [0])])[0]
         t2 = time.perf_counter()
         core.step.free(rid)
         return (t1 - t0) * 1e3, new_tokens / (t2 - t1)
@@ -551,7 +572,9 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the 36 of Qwen3-8B")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
+    ap.add_argument("--skip-points", action="store_true", help="leave out the further batch sizes")
+    ap.add_argument("--points", type=lambda v: [int(x) for x in v.split(",") if x], default=[1, 64],
+                    help="further decode batch sizes to time, comma-separated (default 1,64)")
     ap.add_argument("--kernel", default=None, help="time one kernel alone instead: attention_decode, "
                     "attention_prefill (tcgen05), attention_prefill_mma, rope_kv, rmsnorm, gemm_tc_decode, gemm_decode (library), "
                     "gemm_pair_swiglu, gemm_prefill_library (--ctx tokens)")
@@ -607,7 +630,7 @@ def main() -> int:
     vocab = raw["vocab_size"]
     peaks = load_peaks()
     ctx, pf_tokens = args.seq_len, args.prefill_tokens      # the defaults unless asked otherwise
-    max_batch = 64 if not args.skip_points else max(args.batch, 1)
+    max_batch = max([args.batch, 1] + ([] if args.skip_points else list(args.points)))
     core = random_core(raw, seed=0, std=0.02, dtype="bfloat16", max_seq_len=max(ctx, pf_tokens), page_size=16,
                        pool_tokens=max(max_batch * ctx, pf_tokens + 64), max_slots=max_batch,
                        max_step_tokens=max(pf_tokens, args.batch * ctx))
@@ -618,9 +641,12 @@ def main() -> int:
     main_run = time_decode(core, args.batch, steps, warmup, ctx, vocab)
     prefill_ms = time_prefill(core, vocab, pf_tokens)
     points = {}
+    checked = main_run["checked"]
     if not args.skip_points:
-        for b in (1, 64):
-            points[f"decode_b{b}"] = round(time_decode(core, b, steps, warmup, ctx, vocab)["tok_s"], 1)
+        for b in args.points:
+            run = time_decode(core, b, steps, warmup, ctx, vocab)
+            points[f"decode_b{b}"] = round(run["tok_s"], 1)
+            checked = checked and run["checked"]
     e2e = time_e2e(core, args.batch, steps, warmup, ctx, vocab)
     clocks = sampler.stop()
 
@@ -653,8 +679,16 @@ def main() -> int:
         "points": points,
         "clocks": clocks,
         "host_ms_per_step": round(main_run["wall_ms_per_step"], 4),
+        # every timed decode step's tokens equal those of the same steps run again kernel by kernel
+        # (no CUDA graph, no step launched ahead, tokens fed by the host)
+        "checked": checked,
+        "device_step_h2d_bytes": round(main_run["h2d_bytes_per_step"], 1),
     }
     print(json.dumps(line))
+    if not checked:
+        print("bench.py: the timed decode steps produced other tokens than the same steps run "
+              "kernel by kernel", file=sys.stderr)
+        return 1
     return 0
 
 

@@ -142,3 +142,35 @@ def test_random_orders_keep_every_page_accounted_for(seed):
     for rid in list(lengths):
         m.free(rid)
     assert all(g.num_free == g.num_pages for g in m.kv_groups) and m.num_free_slots == 5
+
+
+def test_table_writes_follow_every_change_and_restart_keeps_the_slot():
+    """The device learns of block tables write by write: new pages as (group, slot, index, page),
+    entries of a request that ended or was restarted as -1.  A restart (preemption) gives the
+    pages back, keeps the slot and marks the mixers' state in it for clearing."""
+    from tokamak_b200.cache.manager import CacheManager, KVGroup, KVPagesNeed
+    m = CacheManager([KVGroup(KVPagesNeed(1, 8), 6, 4, ["full"]),
+                      KVGroup(KVPagesNeed(1, 8, window=5), 6, 4, ["win"])], [], 3)
+    slot = m.admit("a")
+    m.fresh_slots.clear()
+    m.grow("a", 9)                                            # three pages in both groups
+    assert sorted(m.table_writes) == sorted((g, slot, i, p) for g in (0, 1)
+                                            for i, p in enumerate(m.kv_groups[g].table("a")))
+    m.table_writes.clear()
+    m.grow("a", 9)                                            # nothing new: nothing to write
+    assert m.table_writes == []
+    m.advance("a", 9)                                         # the window passed page 0 of group 1
+    assert m.kv_groups[1].released("a") == 1 and m.table_writes == []    # the stale id stays, unread
+    m.restart("a")
+    assert m.has("a") and m.slot("a") == slot and m.length("a") == 0 and slot in m.fresh_slots
+    assert sorted(m.table_writes) == [(g, slot, i, -1) for g in (0, 1) for i in range(3)]
+    assert all(g.num_free == g.num_pages and g.table("a") == [] for g in m.kv_groups)
+    m.check_invariants()
+    m.table_writes.clear()
+    m.grow("a", 4)
+    m.free("a")
+    assert m.table_writes[-2:] == [(0, slot, 0, -1), (1, slot, 0, -1)] and not m.has("a")
+    assert m.num_free_slots == 3
+    with pytest.raises(KeyError):
+        m.restart("a")
+    m.check_invariants()

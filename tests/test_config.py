@@ -103,3 +103,60 @@ def test_model_spec_is_data():
     assert [b.mixer.window for b in spec.blocks] == [None, 24, 24]
     assert spec.blocks[0].mixer.position.theta == 50000.0
     assert spec.blocks[0].mixer.qk_norm_eps == cfg.rms_norm_eps
+
+
+def test_the_engine_protocol_of_a_configuration_is_checked_and_options_are_refused_by_name():
+    """What the engine reads from a typed configuration is a written protocol that every parsed
+    configuration is checked against; engine-wide options reach ``model_spec`` as arguments, and an
+    architecture that does not list one refuses it with the reason."""
+    from dataclasses import dataclass
+    from tokamak_b200.config import (Architecture, ConfigError, architecture_of, register_architecture,
+                                     unregister_architecture)
+
+    @dataclass(frozen=True)
+    class Good:
+        vocab_size: int = 10
+        max_position_embeddings: int = 32
+        eos_token_ids: tuple = ()
+        architecture: str = "ToyProtocol"
+
+    @dataclass(frozen=True)
+    class Bad:
+        vocab_size: float = 10.0
+        eos_token_ids: tuple = ()
+        architecture: str = "ToyProtocol"
+
+    seen = {}
+
+    def model_spec(cfg, **options):
+        seen.update(options)
+        return "spec"
+
+    try:
+        register_architecture(Architecture("ToyProtocol", lambda raw, eos=None: Good(), model_spec))
+        arch = architecture_of({"architectures": ["ToyProtocol"]})
+        cfg = arch.parse({})
+        assert arch.build_spec(cfg, window=None) == "spec" and seen == {}
+        with pytest.raises(ConfigError, match="does not take the engine option 'window'"):
+            arch.build_spec(cfg, window=16)
+        register_architecture(Architecture("ToyProtocol", lambda raw, eos=None: Good(), model_spec,
+                                           options=frozenset({"window"})))
+        assert architecture_of({"architectures": ["ToyProtocol"]}).build_spec(cfg, window=16) == "spec"
+        assert seen == {"window": 16}
+        register_architecture(Architecture("ToyProtocol", lambda raw, eos=None: Bad(), model_spec))
+        with pytest.raises(ConfigError, match="max_position_embeddings is missing") as info:
+            architecture_of({"architectures": ["ToyProtocol"]}).parse({})
+        assert "vocab_size must be int" in str(info.value)
+        with pytest.raises(ConfigError, match="options that do not exist"):
+            register_architecture(Architecture("ToyProtocol", Good, model_spec, options=frozenset({"turbo"})))
+        with pytest.raises(ConfigError, match="callable"):
+            register_architecture(Architecture("ToyProtocol", None, model_spec))
+    finally:
+        unregister_architecture("ToyProtocol")
+    # the built-in architecture takes the window as an argument and windows every layer with it
+    from tokamak_b200.models import qwen3
+    import tiny_configs
+    qcfg = architecture_of(tiny_configs.TINY_A).parse(tiny_configs.TINY_A)
+    spec = architecture_of(tiny_configs.TINY_A).build_spec(qcfg, window=12)
+    assert all(b.mixer.window == 12 for b in spec.blocks)
+    assert all(b.mixer.window is None for b in qwen3.model_spec(qcfg).blocks)

@@ -74,6 +74,11 @@ def test_preemption_is_invisible_in_greedy_tokens():
     assert small.last_stats["preemptions"] > 0
     assert [o.output_token_ids for o in outs] == want
     assert sum(o.num_preemptions for o in outs) == small.last_stats["preemptions"]
+    # four requests in four slots: every record holds, after all the evictions, as many draws as
+    # its request sampled tokens, and the position its request reached
+    records = small.core.cache.slot_records[:4].cpu()         # the first four slots are handed out first
+    assert records[:, 1].tolist() == [24] * 4
+    assert sorted(records[:, 0].tolist()) == sorted(len(p) + 23 for p in prompts)
     small.cache_manager.check_invariants()
     assert all(g.num_free == g.num_pages for g in small.cache_manager.kv_groups)
 
@@ -205,52 +210,106 @@ def test_steps_launched_ahead_end_where_the_requests_end_alone():
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_a_step_fed_on_the_device_equals_one_fed_by_the_host(dtype):
-    """launch_and_sample with a feed, two steps in flight, against run_and_sample step by step:
-    the same tokens, with and without CUDA graphs (seeded temperature sampling, so the counters
-    of the random generator have to be right as well)."""
+def test_steps_driven_by_the_slot_records_equal_steps_laid_out_by_the_host(dtype):
+    """Steps of single next tokens whose tokens, positions, sampling parameters and generator
+    counters come from the slot records on the device (two steps in flight, requests in a
+    changing order, with and without CUDA graphs, also mixed with a request that brings its
+    tokens itself) against steps in which the host brings every token and every counter:
+    the same tokens, and records that hold what happened."""
     from tokamak_b200.engine.replay import build_core
     from tokamak_b200.engine.step import SamplingRow, StepEntry
     tag = "C" if dtype == "bfloat16" else "B"
     cfg, _, page = tiny_configs.ALL[tag][:3]
     core = build_core(model_folder(tag, dtype), dtype, max_tokens=512, page_size=page)
+    step = core.step
     prompts = [random_tokens(cfg["vocab_size"], n, seed=n) for n in (9, 4, 17)]
     rows = lambda k: [SamplingRow(0.7, 0, 1.0, seed=100 + i, counter=k) for i in range(3)]
     steps = 12
 
     def by_host(ids):
-        toks = core.step.run_and_sample([StepEntry(r, p, [len(p) - 1]) for r, p in zip(ids, prompts)], rows(0))
+        toks = step.run_and_sample([StepEntry(r, p, [len(p) - 1]) for r, p in zip(ids, prompts)], rows(0))
         out = [toks]
         for k in range(1, steps):
-            toks = core.step.run_and_sample([StepEntry(r, [t], [0]) for r, t in zip(ids, toks)], rows(k))
+            toks = step.run_and_sample([StepEntry(r, [t], [0]) for r, t in zip(ids, toks)], rows(k))
             out.append(toks)
         for r in ids:
-            core.step.free(r)
+            step.free(r)
         return out
 
-    def by_device(ids):
-        flight = core.step.launch_and_sample([StepEntry(r, p, [len(p) - 1]) for r, p in zip(ids, prompts)], rows(0))
-        out = []
+    def by_device(ids, extra=None):
+        for r, row in zip(ids, rows(0)):
+            step.admit(r, row)                         # the records are written once, here
+        flight = step.launch_and_sample([StepEntry(r, p, [len(p) - 1]) for r, p in zip(ids, prompts)])
+        out, order_before = [], [0, 1, 2]
         for k in range(1, steps):
-            # entries in another order than the step before: the feed names the places
-            order = [2, 0, 1] if k % 2 else [0, 1, 2]
-            prev = order_before if k > 1 else [0, 1, 2]
-            ahead = core.step.launch_and_sample([StepEntry(ids[i], [0], [0]) for i in order],
-                                                [rows(k)[i] for i in order],
-                                                feed=[prev.index(i) for i in order])
-            toks = core.step.collect(flight)
-            out.append([toks[prev.index(i)] for i in range(3)])
+            order = [2, 0, 1] if k % 2 else [0, 1, 2]  # the list of slots changes from step to step
+            entries = [StepEntry(ids[i], None, [0]) for i in order]
+            if extra is not None and k == 5:           # a prompt portion rides along: a laid-out step
+                entries.append(StepEntry(extra, prompts[1], []))
+            ahead = step.launch_and_sample(entries)
+            toks = step.collect(flight)
+            out.append([toks[order_before.index(i)] for i in range(3)])
             flight, order_before = ahead, order
-        toks = core.step.collect(flight)
+        toks = step.collect(flight)
         out.append([toks[order_before.index(i)] for i in range(3)])
-        for r in ids:
-            core.step.free(r)
+        for i, r in enumerate(ids):
+            rec = step.record(r)
+            assert rec["counter"] == steps and rec["last_token"] == out[-1][i]
+            assert rec["num_computed"] == len(prompts[i]) + steps - 1 == step.length(r)
+            assert rec["seed"] == 100 + i and abs(rec["temperature"] - 0.7) < 1e-6
+        for r in ids + ([extra] if extra else []):
+            step.free(r)
         return out
 
     want = by_host(["h0", "h1", "h2"])
-    assert by_device(["d0", "d1", "d2"]) == want          # decode steps seen once or twice: mostly eager
+    replays = step.graph_replays
+    assert by_device(["d0", "d1", "d2"]) == want          # shapes seen once or twice: mostly kernel by kernel
     assert by_device(["e0", "e1", "e2"]) == want          # replayed from the captured graph
-    assert core.step.graph_launches > 0
+    assert step.graph_replays > replays
+    assert by_device(["f0", "f1", "f2"], extra="x") == want
+    # a steady step copies nothing to the device but new pages: far less than a laid-out step would
+    step.admit("s", SamplingRow())
+    step.run_and_sample([StepEntry("s", prompts[0], [len(prompts[0]) - 1])])
+    step.run_and_sample([StepEntry("s", None, [0])])
+    before = step.buffers.h2d_bytes
+    for _ in range(6):
+        step.run_and_sample([StepEntry("s", None, [0])])
+    assert step.buffers.h2d_bytes - before <= 6 * 4 * (2 + 2)     # at most a (count, count, index, page) a step
+    step.free("s")
+
+
+def test_records_outlive_preemption_at_the_step_function():
+    """A request that is restarted (its pages given back, as the scheduler does on preemption)
+    keeps its slot and its record: after recomputing prompt and generated tokens it goes on with
+    the same generator counter, so its tokens are those of an undisturbed run."""
+    from tokamak_b200.engine.replay import build_core
+    from tokamak_b200.engine.step import SamplingRow, StepEntry
+    cfg, _, page = tiny_configs.ALL["B"][:3]
+    core = build_core(model_folder("B", "float32"), "float32", max_tokens=256, page_size=page)
+    step = core.step
+    prompt = random_tokens(cfg["vocab_size"], 13, seed=3)
+    row = SamplingRow(0.9, 30, 0.95, seed=77)
+
+    def run(rid, restart_at=None):
+        step.admit(rid, row)
+        toks = step.run_and_sample([StepEntry(rid, prompt, [len(prompt) - 1])])
+        for k in range(1, 14):
+            if k == restart_at:
+                slot = core.manager.slot(rid)
+                step.restart(rid)
+                assert core.manager.slot(rid) == slot and step.length(rid) == 0
+                assert all(g.num_free == g.num_pages for g in core.manager.kv_groups)
+                # everything so far is recomputed in two portions; the second samples the next token
+                known = prompt + toks
+                step.run([StepEntry(rid, known[:7], [])])
+                toks += step.run_and_sample([StepEntry(rid, known[7:], [len(known) - 8])])
+            else:
+                toks += step.run_and_sample([StepEntry(rid, None, [0])])
+        assert step.record(rid)["counter"] == len(toks) == 14
+        step.free(rid)
+        return toks
+
+    assert run("calm") == run("shaken", restart_at=6)
 
 
 def test_pool_sized_from_free_memory():

@@ -779,3 +779,111 @@ def test_gemm_tcgen05_swapped_with_norm_rotation_and_page_write(tokens, hq, hkv,
                       i32(list(range(tokens))), bad.to(DEV), None, None, None, n_q_heads=hq, n_kv_heads=hkv, eps=0.0)
     torch.cuda.synchronize()
     assert err.tolist()[0] == 2, err.tolist()
+
+
+@pytest.mark.parametrize("tokens", [1, 8, 64])
+def test_gemm_tcgen05_swapped_at_the_real_vocabulary(tokens):
+    """The head product of Qwen3: 151,936 rows (1,187 row tiles) over 4,096, planned as the engine
+    plans it, against a float64 product computed on the device in slices."""
+    from tokamak_b200.csrc import ops
+    n_out, k = 151936, 4096
+    gen = torch.Generator(device=DEV).manual_seed(tokens)
+    x = torch.randn(tokens, k, generator=gen, device=DEV).bfloat16()
+    w = (torch.randn(n_out, k, generator=gen, device=DEV) * 0.02).bfloat16()
+    splits, stages, cluster = ops.swapped_gemm_plan(n_out, k, tokens)
+    err = err_word()
+    parts = ops.gemm_tc_swapped(w, x, err, splits, max_stages=stages, cluster=cluster)
+    torch.cuda.synchronize()
+    assert err.tolist()[0] == 0, err.tolist()
+    got = parts.double().sum(0)
+    for lo in range(0, n_out, 16384):
+        want = x.double() @ w[lo:lo + 16384].double().T
+        torch.testing.assert_close(got[:, lo:lo + 16384], want, rtol=1e-4, atol=2e-3)
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_leaves_the_engine_usable():
+    """No correct launch makes a barrier wait of the tcgen05 kernels run out, so a kernel made for
+    this test does: one block waits, with the kernels' own bounded wait and a limit of 1,024
+    polls, for a barrier that nobody arrives at, and reports as they would.  The step function
+    raises the error once, with its code, and the next step is clean."""
+    import tiny_configs
+    from helpers import model_folder, random_tokens
+    from tokamak_b200.csrc import ops
+    from tokamak_b200.engine.replay import build_core
+    from tokamak_b200.engine.step import StepEntry, StepError
+    err = err_word()
+    ops.wait_probe(1024, err)
+    torch.cuda.synchronize()
+    word = err.tolist()
+    assert word[0] == 5 and word[3] == 1024, word
+    with pytest.raises(ops.KernelError):
+        ops.wait_probe(1 << 20, err)                       # a probe stays short
+    core = build_core(model_folder("A", "float32"), "float32", max_tokens=128, page_size=16)
+    toks = random_tokens(tiny_configs.TINY_A["vocab_size"], 20, seed=3)
+    clean = core.step.run([StepEntry("a", toks, [19])]).cpu()
+    core.step.free("a")
+    ops.wait_probe(1024, core.step.buffers.result[:4])     # as if a kernel of the next step had given up
+    with pytest.raises(StepError, match="kernel error 5 .*bounded wait"):
+        core.step.run([StepEntry("b", toks, [19])])
+    core.step.free("b")
+    again = core.step.run([StepEntry("c", toks, [19])]).cpu()
+    assert torch.equal(again, clean)
+
+
+def test_step_state_kernels_alone():
+    """The kernels that open a step and the sampler that reads the slot records, on hand-made
+    buffers: updates are applied under their masks and cleared, fed tokens and positions come
+    from the records, bad slots and missing tokens are reported, and the sampler draws what the
+    array-driven sampler draws and moves the record on."""
+    from tokamak_b200.csrc import ops
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    bits = lambda f: torch.tensor([f], dtype=torch.float32).view(torch.int32).item()
+    max_slots, max_tab = 6, 40
+    records = torch.zeros(max_slots, 8, dtype=torch.int32, device=DEV)
+    records[:, 7] = -1
+    tables = torch.full((2, max_slots, 5), -1, dtype=torch.int32, device=DEV)
+    ctl = torch.zeros(2 + 9 * max_slots + 2 * max_tab, dtype=torch.int32, device=DEV)
+    upd = ops.UpdateBuffers(ctl, max_slots, max_tab, records, tables)
+    err = err_word()
+    # two record writes (slot 4 in full, slot 1 sampling words only) and three table writes
+    rec = [4 | (0xFF << 16), 0, 0, 11, 22, bits(0.5), 7, bits(0.9), -1,
+           1 | (0x7E << 16), 99, 3, 33, 44, bits(1.5), 0, bits(1.0), 99]
+    tab = [0 * 30 + 4 * 5 + 0, 17, 1 * 30 + 4 * 5 + 2, 9, 0 * 30 + 1 * 5 + 1, -1]
+    records[1] = i32([40, 0, 0, 0, 0, 0, 0, 123])
+    ctl[:2 + len(rec) + len(tab)] = i32([2, 3] + rec + tab)
+    token_ids = i32([50, 51, 52, 53])
+    ops.step_begin(upd, token_ids, i32([0, 3]), i32([3, 41]), i32([4, 1]), i32([0, 1]), err)
+    torch.cuda.synchronize()
+    assert err.tolist()[0] == 0 and ctl[:2].tolist() == [0, 0]
+    assert records[4].tolist() == [3, 0, 11, 22, bits(0.5), 7, bits(0.9), -1]
+    assert records[1].tolist() == [41, 3, 33, 44, bits(1.5), 0, bits(1.0), 123]     # position, last token kept
+    assert token_ids.tolist() == [50, 51, 52, 123]                                   # request 1 was fed
+    assert tables[0, 4, 0] == 17 and tables[1, 4, 2] == 9 and tables[0, 1, 1] == -1
+    assert int((tables != -1).sum()) == 2
+    # a step described by the records alone
+    records[4, 7] = 77
+    tok, pos, kvl = (torch.zeros(3, dtype=torch.int32, device=DEV) for _ in range(3))
+    ops.decode_begin(upd, i32([1, 4]), 2, 64, tok, pos, kvl, err)
+    torch.cuda.synchronize()
+    assert err.tolist()[0] == 0
+    assert tok.tolist()[:2] == [123, 77] and pos.tolist()[:2] == [41, 3] and kvl.tolist()[:2] == [42, 4]
+    assert records[1, 0] == 42 and records[4, 0] == 4
+    # faults: a slot outside the records, a request that has sampled nothing yet, a position at the limit
+    for slots, limit, code in (([9], 64, 4), ([0], 64, 1), ([1], 42, 3)):
+        e = err_word()
+        ops.decode_begin(upd, i32(slots), 1, limit, tok, pos, kvl, e)
+        torch.cuda.synchronize()
+        assert e.tolist()[0] == code, (slots, e.tolist())
+    # the sampler with records against the sampler with arrays
+    gen = torch.Generator().manual_seed(5)
+    logits = (torch.randn(2, 317, generator=gen) * 3).to(DEV)
+    records[1] = i32([0, 3, 33, 44, bits(1.5), 0, bits(1.0), -1])
+    records[4] = i32([0, 9, 11, 22, bits(0.5), 7, bits(0.9), -1])
+    out_a, out_b = torch.zeros(2, dtype=torch.int32, device=DEV), torch.zeros(2, dtype=torch.int32, device=DEV)
+    ops.sample_slots(logits, records, i32([1, 4]), out_a, err)
+    seeds = torch.tensor([33 | (44 << 32), 11 | (22 << 32)], dtype=torch.int64, device=DEV)
+    ops.sample(logits, torch.tensor([1.5, 0.5], device=DEV), i32([0, 7]), torch.tensor([1.0, 0.9], device=DEV),
+               seeds, i32([3, 9]), out_b)
+    torch.cuda.synchronize()
+    assert out_a.tolist() == out_b.tolist()
+    assert records[1, 1] == 4 and records[4, 1] == 10 and records[1, 7] == out_a[0] and records[4, 7] == out_a[1]

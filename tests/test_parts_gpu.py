@@ -50,7 +50,7 @@ def test_rmsnorm_part(dtype):
 def test_position_parts():
     from tokamak_b200.parts.position import NoPosition, NoPositionSpec, RopeNeox, RopeSpec
     from types import SimpleNamespace
-    rope = RopeNeox(RopeSpec(head_dim=48, theta=50000.0), runtime(torch.float32))
+    rope = RopeNeox(RopeSpec(head_dim=48, theta=50000.0), {}, runtime(torch.float32))
     positions = [0, 1, 7, 300, 40001]
     step = SimpleNamespace(positions=torch.tensor(positions, dtype=torch.int32, device=DEV), scratch={})
     table, rotary_dim = rope.rotary_table(step)
@@ -59,9 +59,9 @@ def test_position_parts():
     cos, sin = plain.rope_tables(torch.tensor(positions), 48, 50000.0, torch.float64)
     torch.testing.assert_close(table[..., 0].double().cpu(), cos[:, :24], rtol=0, atol=2e-6)
     torch.testing.assert_close(table[..., 1].double().cpu(), sin[:, :24], rtol=0, atol=2e-6)
-    assert NoPosition(NoPositionSpec(), runtime(torch.float32)).rotary_table(step) == (None, 0)
+    assert NoPosition(NoPositionSpec(), {}, runtime(torch.float32)).rotary_table(step) == (None, 0)
     with pytest.raises(ValueError):
-        RopeNeox(RopeSpec(head_dim=15, theta=1e4), runtime(torch.float32))
+        RopeNeox(RopeSpec(head_dim=15, theta=1e4), {}, runtime(torch.float32))
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -100,8 +100,7 @@ class _Harness:
 
     def batch(self, entries):
         from tokamak_b200.engine.step import StepEntry
-        b, _ = self.step.build([StepEntry(r, [0] * n, []) for r, n in entries])
-        return b
+        return self.step.build([StepEntry(r, [0] * n, []) for r, n in entries])
 
     def done(self, entries):
         from tokamak_b200.engine.step import StepEntry
@@ -271,15 +270,21 @@ def _toy_architecture():
 
     @dataclass(frozen=True)
     class ToyConfig:
-        raw: tuple
+        vocab_size: int
+        hidden_size: int
+        heads: int
+        head_dim: int
+        inter: int
+        eps: float
+        theta: float
+        decay: float
+        max_position_embeddings: int
         architecture: str = "ToyDecayForCausalLM"
         eos_token_ids: tuple = ()
 
-        def __getattr__(self, name):
-            return dict(self.raw)[name]
-
     def parse_config(raw, eos_token_ids=None):
-        return ToyConfig(tuple((k, v) for k, v in raw.items() if k != "architectures"))
+        return ToyConfig(**{k: v for k, v in raw.items() if k != "architectures"},
+                         eos_token_ids=tuple(eos_token_ids or ()))
 
     def model_spec(cfg):
         H, norm = cfg.hidden_size, RMSNormSpec(cfg.hidden_size, cfg.eps)
@@ -365,10 +370,16 @@ class ScaledPartialRopeSpec:
 
 
 class ScaledPartialRope:
-    def __init__(self, spec, rt):
+    GRAPH_SAFE = True          # tensor operations on the step's device tensors only
+
+    def __init__(self, spec, tensors, rt):
         self.spec = spec
         j = torch.arange(0, spec.rotary_dim, 2, dtype=torch.float32, device=rt.device)
         self.inv_freq = 1.0 / (spec.theta ** (j / spec.rotary_dim))
+
+    @staticmethod
+    def expected_tensors(spec):
+        return {}
 
     def rotary_table(self, step):
         key = ("toy_rope", self.spec)
@@ -438,23 +449,33 @@ def _routed_architecture():
 
     @dataclass(frozen=True)
     class Config:
-        raw: tuple
+        vocab_size: int
+        hidden_size: int
+        heads: int
+        kv_heads: int
+        head_dim: int
+        rotary_dim: int
+        factor: float
+        inter: int
+        experts: int
+        eps: float
+        theta: float
+        max_position_embeddings: int
         architecture: str = "ToyRoutedForCausalLM"
         eos_token_ids: tuple = ()
 
-        def __getattr__(self, name):
-            return dict(self.raw)[name]
-
     def parse_config(raw, eos_token_ids=None):
-        return Config(tuple((k, v) for k, v in raw.items() if k != "architectures"))
+        return Config(**{k: v for k, v in raw.items() if k != "architectures"},
+                      eos_token_ids=tuple(eos_token_ids or ()))
 
     def model_spec(cfg):
         H, norm = cfg.hidden_size, RMSNormSpec(cfg.hidden_size, cfg.eps)
         pos = ScaledPartialRopeSpec(cfg.rotary_dim, cfg.theta, cfg.factor)
         attn = AttentionSpec(H, cfg.heads, cfg.kv_heads, cfg.head_dim, pos, qk_norm_eps=cfg.eps)
+        ffn0 = Top1ExpertsSpec(H, cfg.inter, cfg.experts) if cfg.experts else SwiGLUSpec(H, cfg.inter)
         blocks = (
-            PreNormBlockSpec("l0", norm, attn, norm, Top1ExpertsSpec(H, cfg.inter, cfg.experts),
-                             "l0.n1", "l0.attn.", "l0.n2", "l0.moe."),
+            PreNormBlockSpec("l0", norm, attn, norm, ffn0, "l0.n1", "l0.attn.", "l0.n2",
+                             "l0.moe." if cfg.experts else "l0.mlp."),
             PreNormBlockSpec("l1", norm, attn, norm, SwiGLUSpec(H, cfg.inter), "l1.n1", "l1.attn.", "l1.n2",
                              "l1.mlp."),
         )
@@ -488,11 +509,16 @@ def _routed_plain_logits(folder, ids):
     x = w["embed"][torch.tensor(ids)]
     x = x + attn(plain.rms_norm(x, w["l0.n1"], eps), "l0")
     h = plain.rms_norm(x, w["l0.n2"], eps)
-    prob, choice = torch.softmax(h @ w["l0.moe.router.weight"].T, dim=-1).max(dim=-1)
-    y = torch.stack([plain.swiglu_mlp(h[t:t + 1], w[f"l0.moe.experts.{int(e)}.gate.weight"],
-                                      w[f"l0.moe.experts.{int(e)}.up.weight"],
-                                      w[f"l0.moe.experts.{int(e)}.down.weight"])[0] * prob[t]
-                     for t, e in enumerate(choice)])
+    if cfg["experts"]:
+        prob, choice = torch.softmax(h @ w["l0.moe.router.weight"].T, dim=-1).max(dim=-1)
+        y = torch.stack([plain.swiglu_mlp(h[t:t + 1], w[f"l0.moe.experts.{int(e)}.gate.weight"],
+                                          w[f"l0.moe.experts.{int(e)}.up.weight"],
+                                          w[f"l0.moe.experts.{int(e)}.down.weight"])[0] * prob[t]
+                         for t, e in enumerate(choice)])
+    else:
+        choice = torch.zeros(T, dtype=torch.long)
+        y = plain.swiglu_mlp(h, w["l0.mlp.gate_proj.weight"], w["l0.mlp.up_proj.weight"],
+                             w["l0.mlp.down_proj.weight"])
     x = x + y
     x = x + attn(plain.rms_norm(x, w["l1.n1"], eps), "l1")
     x = x + plain.swiglu_mlp(plain.rms_norm(x, w["l1.n2"], eps), w["l1.mlp.gate_proj.weight"],
@@ -536,3 +562,244 @@ def test_toy_routed_feed_forward_and_toy_position_encoding(tmp_path):
     finally:
         FEED_FORWARDS.unregister("toy_top1_experts")
         POSITIONS.unregister("toy_scaled_partial_rope")
+
+
+# ----------------------------------------------------------------------------- toys through generate
+
+def _plain_greedy(logits_fn, prompt, n_new):
+    """Greedy continuation under a plain logits function of whole sequences."""
+    seq = list(prompt)
+    for _ in range(n_new):
+        out = logits_fn(seq)
+        logits = out[0] if isinstance(out, tuple) else out
+        seq.append(int(logits[-1].argmax()))
+    return seq[len(prompt):]
+
+
+def test_toy_stateful_mixer_and_routed_feed_forward_through_generate(tmp_path):
+    """The toys meet the whole engine: several requests through ``LLM.generate`` with launch-ahead,
+    portions, more requests than slots (slots are handed on) and a pool small enough to preempt.
+
+    The decay-sum mixer plans on the host (``step.host_*``) and the routed feed-forward reads a
+    routing decision back, so neither declares ``GRAPH_SAFE``: their models must run every step
+    kernel by kernel, and the tokens must be the plain implementation's.  A model whose parts all
+    declare it (the toy rotation is plain tensor arithmetic on device tensors) is replayed from
+    CUDA graphs by the same engine and must be right as well."""
+    from tokamak_b200 import LLM, SamplingParams
+    from tokamak_b200.config import register_architecture, unregister_architecture
+    from tokamak_b200.parts.base import FEED_FORWARDS, MIXERS, POSITIONS
+    from tokamak_b200.weights import write_random_model
+
+    MIXERS.register("toy_decay_sum")(DecaySum)
+    FEED_FORWARDS.register("toy_top1_experts")(Top1Experts)
+    POSITIONS.register("toy_scaled_partial_rope")(ScaledPartialRope)
+    register_architecture(_toy_architecture())
+    register_architecture(_routed_architecture())
+    try:
+        cases = [
+            ("toy", TOY_CONFIG, 131, lambda f: (lambda ids: _toy_plain_logits(f, ids)), False),
+            ("routed", ROUTED_CONFIG, 97, lambda f: (lambda ids: _routed_plain_logits(f, ids)), False),
+            ("rope_only", dict(ROUTED_CONFIG, experts=0), 97,
+             lambda f: (lambda ids: _routed_plain_logits(f, ids)), True),
+        ]
+        for name, raw, vocab, plain_of, safe in cases:
+            folder = write_random_model(tmp_path / name, raw, seed=21, std=0.3 if name != "toy" else 0.08,
+                                        dtype="float32")
+            llm = LLM(folder, dtype="float32", max_seq_len=64, block_size=8, kv_pool_tokens=112,
+                      max_batch_size=3, max_num_batched_tokens=40, prefill_chunk=16)
+            assert llm.core.step.graph_safe is safe
+            prompts = [random_tokens(vocab, n, seed=90 + n) for n in (21, 9, 30, 14, 26)]
+            outs = llm.generate(prompt_token_ids=prompts,
+                                sampling_params=SamplingParams(temperature=0.0, max_new_tokens=22))
+            stats = llm.last_stats
+            assert stats["preemptions"] > 0 and stats["mixed_steps"] > 0 and stats["decode_steps"] > 5, stats
+            logits_fn = plain_of(folder)
+            for prompt, out in zip(prompts, outs):
+                assert out.output_token_ids == _plain_greedy(logits_fn, prompt, 22), (name, len(prompt))
+            assert (llm.core.step.graph_replays > 0) is safe, name
+            llm.cache_manager.check_invariants()
+            assert llm.cache_manager.num_free_slots == 3
+    finally:
+        MIXERS.unregister("toy_decay_sum")
+        FEED_FORWARDS.unregister("toy_top1_experts")
+        POSITIONS.unregister("toy_scaled_partial_rope")
+        unregister_architecture("ToyDecayForCausalLM")
+        unregister_architecture("ToyRoutedForCausalLM")
+
+
+# ---- an embedding, a head and an absolute position encoding of the test's own ---------------
+
+@dataclass(frozen=True)
+class ScaledEmbeddingSpec:
+    vocab_size: int
+    hidden_size: int
+    scale: float
+    name: str = "tok.weight"
+    kind: str = "toy_scaled_embedding"
+
+
+class ScaledEmbedding:
+    GRAPH_SAFE = True
+
+    def __init__(self, spec, tensors, rt):
+        self.spec, self.weight = spec, tensors[spec.name]
+
+    @staticmethod
+    def expected_tensors(spec):
+        from tokamak_b200.parts.base import TensorReq
+        return {spec.name: TensorReq((spec.vocab_size, spec.hidden_size))}
+
+    def forward(self, step):
+        return self.weight[step.token_ids.long()].float() * self.spec.scale
+
+
+@dataclass(frozen=True)
+class CappedHeadSpec:
+    """logits = cap * tanh((h W^T + b) / cap)."""
+    vocab_size: int
+    hidden_size: int
+    cap: float
+    kind: str = "toy_capped_head"
+
+
+class CappedHead:
+    GRAPH_SAFE = True
+
+    def __init__(self, spec, embedding, tensors, rt):
+        self.spec, self.weight, self.bias = spec, tensors["out.weight"], tensors["out.bias"]
+
+    @staticmethod
+    def expected_tensors(spec):
+        from tokamak_b200.parts.base import TensorReq
+        return {"out.weight": TensorReq((spec.vocab_size, spec.hidden_size)),
+                "out.bias": TensorReq((spec.vocab_size,), role="vector")}
+
+    def forward(self, h, err=None):
+        from tokamak_b200.parts.base import linear, sum_parts
+        logits = sum_parts(linear(h, self.weight, out_dtype=torch.float32), torch.float32) + self.bias
+        return self.spec.cap * torch.tanh(logits / self.spec.cap)
+
+
+@dataclass(frozen=True)
+class LearnedPositionsSpec:
+    """An absolute encoding: row ``position`` of a learned table is added to the embedded token."""
+    max_positions: int
+    hidden_size: int
+    kind: str = "toy_learned_positions"
+
+
+class LearnedPositions:
+    GRAPH_SAFE = True
+
+    def __init__(self, spec, tensors, rt):
+        self.table = tensors["pos.weight"]
+
+    @staticmethod
+    def expected_tensors(spec):
+        from tokamak_b200.parts.base import TensorReq
+        return {"pos.weight": TensorReq((spec.max_positions, spec.hidden_size))}
+
+    def add_to_embedding(self, resid, step):
+        resid += self.table[step.positions.long()].float()
+
+
+ABS_CONFIG = {"architectures": ["ToyAbsoluteForCausalLM"], "vocab_size": 83, "hidden_size": 48, "heads": 3,
+              "head_dim": 16, "inter": 56, "eps": 1e-6, "cap": 6.0, "max_position_embeddings": 96}
+
+
+def _absolute_architecture():
+    from tokamak_b200.config import Architecture
+    from tokamak_b200.models.decoder import LayerCall, ModelSpec
+    from tokamak_b200.parts.attention import AttentionSpec
+    from tokamak_b200.parts.block import PreNormBlockSpec
+    from tokamak_b200.parts.feedforward import SwiGLUSpec
+    from tokamak_b200.parts.norm import RMSNormSpec
+    from tokamak_b200.parts.position import NoPositionSpec
+
+    @dataclass(frozen=True)
+    class Config:
+        vocab_size: int
+        hidden_size: int
+        heads: int
+        head_dim: int
+        inter: int
+        eps: float
+        cap: float
+        max_position_embeddings: int
+        architecture: str = "ToyAbsoluteForCausalLM"
+        eos_token_ids: tuple = ()
+
+    def parse_config(raw, eos_token_ids=None):
+        return Config(**{k: v for k, v in raw.items() if k != "architectures"})
+
+    def model_spec(cfg):
+        H, norm = cfg.hidden_size, RMSNormSpec(cfg.hidden_size, cfg.eps)
+        attn = AttentionSpec(H, cfg.heads, cfg.heads, cfg.head_dim, NoPositionSpec(), qk_norm_eps=None)
+        blocks = (PreNormBlockSpec("l0", norm, attn, norm, SwiGLUSpec(H, cfg.inter), "l0.n1", "l0.attn.",
+                                   "l0.n2", "l0.mlp."),)
+        return ModelSpec(ScaledEmbeddingSpec(cfg.vocab_size, H, H ** 0.5), blocks, (LayerCall("l0", "l0"),),
+                         norm, "final", CappedHeadSpec(cfg.vocab_size, H, cfg.cap),
+                         embedding_position=LearnedPositionsSpec(cfg.max_position_embeddings, H))
+
+    return Architecture("ToyAbsoluteForCausalLM", parse_config, model_spec)
+
+
+def _absolute_plain_logits(folder, ids):
+    cfg, w = plain.load_folder(folder)
+    w = {k: v.double() for k, v in w.items()}
+    T, H, d, heads, eps = len(ids), cfg["hidden_size"], cfg["head_dim"], cfg["heads"], cfg["eps"]
+    x = w["tok.weight"][torch.tensor(ids)] * H ** 0.5 + w["pos.weight"][:T]
+    h = plain.rms_norm(x, w["l0.n1"], eps)
+    q = (h @ w["l0.attn.q_proj.weight"].T).view(T, heads, d)
+    k = (h @ w["l0.attn.k_proj.weight"].T).view(T, heads, d)
+    v = (h @ w["l0.attn.v_proj.weight"].T).view(T, heads, d)
+    x = x + plain.causal_attention(q, k, v).reshape(T, -1) @ w["l0.attn.o_proj.weight"].T
+    x = x + plain.swiglu_mlp(plain.rms_norm(x, w["l0.n2"], eps), w["l0.mlp.gate_proj.weight"],
+                             w["l0.mlp.up_proj.weight"], w["l0.mlp.down_proj.weight"])
+    logits = plain.rms_norm(x, w["final"], eps) @ w["out.weight"].T + w["out.bias"]
+    return cfg["cap"] * torch.tanh(logits / cfg["cap"])
+
+
+def test_toy_embedding_head_and_absolute_positions(tmp_path):
+    """Embedding and head are registry roles like the other parts, and a position encoding may
+    sit at the embedding instead of inside the mixers: an architecture with a scaled embedding, a
+    learned absolute position table and a biased, soft-capped head is described by the test
+    alone, replayed in portions and mixed, and generated from with CUDA graphs."""
+    from tokamak_b200 import LLM, SamplingParams
+    from tokamak_b200.config import ConfigError, register_architecture, unregister_architecture
+    from tokamak_b200.engine.replay import build_core, run_step
+    from tokamak_b200.parts.base import EMBEDDINGS, HEADS, POSITIONS
+    from tokamak_b200.weights import write_random_model
+
+    EMBEDDINGS.register("toy_scaled_embedding")(ScaledEmbedding)
+    HEADS.register("toy_capped_head")(CappedHead)
+    POSITIONS.register("toy_learned_positions")(LearnedPositions)
+    register_architecture(_absolute_architecture())
+    try:
+        folder = write_random_model(tmp_path / "abs", ABS_CONFIG, seed=5, std=0.2, dtype="float32")
+        reqs = {f"a{i}": random_tokens(83, n, seed=30 + i) for i, n in enumerate([11, 40, 64, 25])}
+        truth = {rid: _absolute_plain_logits(folder, ids) for rid, ids in reqs.items()}
+        for builder, kw in ((traces.portions, {}), (traces.mixed, {"max_tokens": 192, "max_live": 3, "seed": 8})):
+            core = build_core(folder, "float32", 192, page_size=16, max_live=3)
+            records, rows = builder(reqs, **kw)
+            for rec in records:
+                out = run_step(core, rec)
+                if out is None:
+                    continue
+                want = torch.stack([truth[rid][p] for rid, p in rows[rec["step"]]])
+                assert_logits_close(torch.from_numpy(out), want, "float32", f"absolute {builder.__name__}")
+        llm = LLM(folder, dtype="float32", block_size=16, max_batch_size=4)
+        assert llm.core.step.graph_safe
+        prompts = [random_tokens(83, n, seed=60 + n) for n in (7, 19, 33)]
+        outs = llm.generate(prompt_token_ids=prompts, sampling_params=SamplingParams(temperature=0.0, max_new_tokens=20))
+        for prompt, out in zip(prompts, outs):
+            assert out.output_token_ids == _plain_greedy(lambda ids: _absolute_plain_logits(folder, ids), prompt, 20)
+        assert llm.core.step.graph_replays > 0
+        # the architecture lists no engine options: a window is refused with the reason
+        with pytest.raises(ConfigError, match="does not take the engine option 'window'"):
+            LLM(folder, dtype="float32", attention_policy="window:8")
+    finally:
+        EMBEDDINGS.unregister("toy_scaled_embedding")
+        HEADS.unregister("toy_capped_head")
+        POSITIONS.unregister("toy_learned_positions")
+        unregister_architecture("ToyAbsoluteForCausalLM")

@@ -103,13 +103,17 @@ def test_preemption_evicts_the_newest_and_requeues_at_the_front():
     assert [e.seq.seq_id for e in p.entries] == [0]
     assert b.status is SequenceStatus.WAITING and b.num_computed == 0 and b.num_output_tokens == 2
     assert list(s.waiting) == [b, waiting_late]                     # ahead of what arrived later
-    assert m.kv_groups[0].table(1) == [] and not m.has(1)
+    # the pages are back, the slot (with the record of its random generator) is kept
+    assert m.kv_groups[0].table(1) == [] and m.has(1) and m.length(1) == 0
+    slot_of_b = m.slot(1)
+    assert p.admitted == []
     run_plan(m, p)
     while not a.is_finished:
         run_plan(m, s.schedule())
     p = s.schedule()                     # b resumes over prompt + generated, then samples the next
     assert describe(p)[0] == (1, 0, 9, True)
     assert b.num_preemptions == 1 and s.num_preemptions == 1
+    assert m.slot(1) == slot_of_b and b not in p.admitted           # resumed, not admitted anew
 
 
 def test_a_starving_sequence_may_evict_itself():
@@ -262,6 +266,7 @@ def test_random_workloads_finish_in_arrival_order_with_every_page_accounted_for(
         seqs.append(q)
         s.add(q)
     started: list[int] = []
+    given_slots: set[int] = set()
     steps = 0
     while s.has_unfinished():
         plan = s.schedule()
@@ -281,7 +286,13 @@ def test_random_workloads_finish_in_arrival_order_with_every_page_accounted_for(
             if e.start == 0 and e.seq.seq_id not in started:
                 started.append(e.seq.seq_id)
         for v in plan.preempted:
-            assert v.status is SequenceStatus.WAITING and v.num_computed == 0 and not m.has(v.seq_id)
+            assert v.status is SequenceStatus.WAITING and v.num_computed == 0
+            assert m.has(v.seq_id) and m.length(v.seq_id) == 0
+            assert all(g.table(v.seq_id) == [] for g in m.kv_groups)
+        for q in plan.admitted:                        # a slot for the first time: exactly once each
+            assert q.seq_id not in given_slots
+            given_slots.add(q.seq_id)
+        assert all(e.seq.seq_id in given_slots for e in plan.entries)
         run_plan(m, plan, token=rng.randrange(1, 50))
         m.check_invariants()
     assert started == sorted(started)                  # first starts happen in arrival order

@@ -52,7 +52,16 @@ def _case(seed: int, kv_lens, hq=8, hkv=2, d=128, page=16):
             vc[pg, :, p % page] = torch.randn(hkv, d, generator=gen).bfloat16()
     q = torch.randn(n, hq, d, generator=gen).bfloat16()
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
-    return dict(q=q.to(DEV), kc=kc.to(DEV), vc=vc.to(DEV), table=table.to(DEV), items=i32(list(range(n))),
+    # float64 attention written out here, so that the check leans on no other path of the engine
+    truth = torch.zeros(n, hq, d, dtype=torch.float64)
+    for r, l in enumerate(kv_lens):
+        rows = [(int(table[r, p // page]), p % page) for p in range(l)]
+        keys = torch.stack([kc[pg, :, o] for pg, o in rows]).double()       # [l, hkv, d]
+        vals = torch.stack([vc[pg, :, o] for pg, o in rows]).double()
+        for h in range(hq):
+            scores = (keys[:, h // (hq // hkv)] @ q[r, h].double()) * d ** -0.5
+            truth[r, h] = torch.softmax(scores, 0) @ vals[:, h // (hq // hkv)]
+    return dict(truth=truth, q=q.to(DEV), kc=kc.to(DEV), vc=vc.to(DEV), table=table.to(DEV), items=i32(list(range(n))),
                 positions=i32([l - 1 for l in kv_lens]), tok_req=i32(list(range(n))),
                 req_slot=i32(list(range(n))), hq=hq, hkv=hkv, d=d, page=page, n=n,
                 max_pages=max_pages, num_pages=num_pages)
@@ -82,8 +91,9 @@ def test_noalloc_decode_matches_the_ordinary_entry_point_twice_in_a_row():
     lib = _load()
     assert lib.tk_attention_decode_noalloc_capacity_floats() == 1 << 20
     # first call: many splits, long contexts; second call: other shapes, fewer splits, so that
-    # it reads a region of the array which the first call filled with other values
-    for seed, kv_lens, n_splits in ((1, [700, 1, 33, 2048], 9), (2, [90, 515, 16], 2)):
+    # it reads a region of the array which the first call filled with other values; third call:
+    # one split, which stores its result itself and uses neither array
+    for seed, kv_lens, n_splits in ((1, [700, 1, 33, 2048], 9), (2, [90, 515, 16], 2), (4, [300, 40], 1)):
         c = _case(seed, kv_lens)
         scale = c["d"] ** -0.5
         rc, got, err = _call_noalloc(lib, c, n_splits, scale)
@@ -92,8 +102,10 @@ def test_noalloc_decode_matches_the_ordinary_entry_point_twice_in_a_row():
         torch.cuda.synchronize()
         assert err.tolist()[0] == 0 and err2.tolist()[0] == 0
         assert torch.isfinite(got.float()).all()
-        # same kernels, same order of sums: within the tolerance of the other bfloat16 kernel tests
-        torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+        # the same kernel with the same order of sums: every bit agrees
+        assert torch.equal(got, want)
+        # and both are right: against float64 attention, within what bfloat16 outputs allow
+        torch.testing.assert_close(got.double().cpu(), c["truth"], rtol=2e-2, atol=2e-2)
 
 
 def test_noalloc_decode_rejects_what_does_not_fit():
@@ -105,3 +117,15 @@ def test_noalloc_decode_rejects_what_does_not_fit():
     assert b"more scratch" in lib.tk_noalloc_error_string(rc)
     torch.cuda.synchronize()
     assert torch.isnan(out.float()).all()          # nothing was launched
+    # more (token, kv head) pairs than the library holds arrival counters for (4,096)
+    # (2,100 tokens x 2 heads = 4,200), while the scratch would fit (2,100 * 2 * 2 * 66 floats)
+    many = _case(5, [3] * 2100, hq=2, hkv=2, d=64)
+    rc, out, _ = _call_noalloc(lib, many, 2, 1.0)
+    assert rc == -2
+    torch.cuda.synchronize()
+    assert torch.isnan(out.float()).all()
+    # with one split neither limit applies: the kernel needs no scratch and no counters
+    rc, out, err = _call_noalloc(lib, many, 1, many["d"] ** -0.5)
+    torch.cuda.synchronize()
+    assert rc == 0 and err.tolist()[0] == 0
+    torch.testing.assert_close(out.double().cpu(), many["truth"], rtol=2e-2, atol=2e-2)

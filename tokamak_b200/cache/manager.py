@@ -14,8 +14,16 @@ leaves the state intact when it fails (block_manager.py:74-93), and freeing is
 idempotent (block_manager.py:131-140).
 
 Beside the pages every live request owns one *slot*, an index below
-``max_slots`` that addresses its row in the device block tables and its record
-in every group of fixed-size state.
+``max_slots`` that addresses its row in the device block tables, its record in
+every group of fixed-size state, and the engine's own record (position, sampling
+parameters, generator counter, last token).  A request that is preempted gives
+its pages back and keeps its slot (:meth:`CacheManager.restart`), as the reference
+keeps a preempted request's generator (src/tokamak/engine/llm.py:339-340,441-445):
+what can be recomputed from the tokens is dropped, what cannot stays.
+
+Every change of a block table is also queued as a *table write* ``(group, slot,
+logical index, page id)``, with ``-1`` for an entry whose page went back to the pool when
+its request ended, so the device side applies the differences instead of copying rows.
 """
 
 from __future__ import annotations
@@ -204,10 +212,10 @@ class CacheManager:
         self._free_slots = list(range(max_slots - 1, -1, -1))
         self._slot_of: dict[Hashable, int] = {}
         self._length: dict[Hashable, int] = {}     # positions of each live request already in the cache
-        # slots whose state records must be cleared before their next use
+        # slots whose mixer state records must be cleared before their next use
         self.fresh_slots: set[int] = set()
-        # (group index, slot) rows of the device tables that differ from the host's
-        self.dirty_rows: set[tuple[int, int]] = set()
+        # block-table entries that the device has not seen yet: (group, slot, logical index, page id)
+        self.table_writes: list[tuple[int, int, int, int]] = []
 
     # ---- slots ---------------------------------------------------------------------
     @property
@@ -262,22 +270,37 @@ class CacheManager:
                     f"but only {g.num_free} of {g.num_pages} are free")
         slot = self._slot_of[req_id]
         for gi, g in enumerate(self.kv_groups):
-            if g.grow(req_id, num_tokens):
-                self.dirty_rows.add((gi, slot))
+            for index, page in g.grow(req_id, num_tokens):
+                self.table_writes.append((gi, slot, index, page))
 
     def release_passed(self, req_id: Hashable, next_position: int) -> int:
         """Give back, in every windowed group, the pages that the window has passed."""
         return sum(g.release_passed(req_id, next_position) for g in self.kv_groups)
 
+    def _drop_pages(self, req_id: Hashable, slot: int) -> None:
+        for gi, g in enumerate(self.kv_groups):
+            # the row is void from now on: a stale id that a kernel followed would be a live
+            # page of someone else, so the device's copy is overwritten with -1
+            self.table_writes.extend((gi, slot, index, -1) for index in range(len(g.table(req_id))))
+            g.free(req_id)
+
     def free(self, req_id: Hashable) -> None:
         """Give back the pages and the slot of a request; unknown ids are ignored."""
         slot = self._slot_of.pop(req_id, None)
         self._length.pop(req_id, None)
-        for g in self.kv_groups:
-            g.free(req_id)
         if slot is not None:
+            self._drop_pages(req_id, slot)
             self._free_slots.append(slot)
             self.fresh_slots.discard(slot)
+
+    def restart(self, req_id: Hashable) -> None:
+        """Preemption: the pages go back and the request starts over from position 0, in the
+        slot it has.  State that mixers keep in the slot cannot be recomputed from pages and is
+        cleared before the slot's next use; the engine's own record is left as it is."""
+        slot = self._slot_of[req_id]
+        self._drop_pages(req_id, slot)
+        self._length[req_id] = 0
+        self.fresh_slots.add(slot)
 
     def fits_empty_pool(self, num_tokens: int, max_portion: int) -> bool:
         """Whether one request of ``num_tokens`` tokens fits when it has the pools to itself."""

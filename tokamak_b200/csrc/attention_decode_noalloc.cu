@@ -7,6 +7,8 @@
 // device arrays below; the kernel itself is the one behind
 // tk_attention_decode, reached through that exported function with the array's
 // device address as its scratch argument.
+#include <mutex>
+
 #include "common.cuh"
 #include "tokamak_b200_noalloc.h"
 
@@ -32,13 +34,16 @@ static __device__ __align__(256) int g_decode_counters[kCounters];
 
 float* g_scratch_ptr[kMaxDevices] = {nullptr};
 int* g_counter_ptr[kMaxDevices] = {nullptr};
+std::mutex g_lookup_mutex;
 
-// Device addresses of the arrays on the current device, looked up once per device.
+// Device addresses of the arrays on the current device, looked up once per device.  The table
+// is read and filled under a mutex, so host threads may make their first calls at the same time.
 int scratch_for_current_device(float** out, int** counters) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= kMaxDevices) return TK_NOALLOC_BAD_DEVICE;
+  std::lock_guard<std::mutex> lock(g_lookup_mutex);
   if (g_scratch_ptr[dev] == nullptr) {
     float* ptr = nullptr;
     e = cudaGetSymbolAddress((void**)&ptr, g_decode_scratch);
@@ -78,8 +83,10 @@ TK_API int tk_attention_decode_noalloc(const void* q, void* out, const void* k_c
                                        int window, int n_splits, float scale, cudaStream_t stream) {
   if (n_items <= 0) return 0;
   if (n_q_heads < 1 || head_dim < 1 || n_splits < 1) return (int)cudaErrorInvalidValue;
+  // a call with one split stores its result itself and touches neither array
   const long long need = (long long)n_items * n_q_heads * n_splits * (head_dim + 2);
-  if (need > kScratchFloats || (long long)n_items * n_kv_heads > kCounters) return TK_NOALLOC_TOO_LARGE;
+  if (n_splits > 1 && (need > kScratchFloats || (long long)n_items * n_kv_heads > kCounters))
+    return TK_NOALLOC_TOO_LARGE;
   float* scratch = nullptr;
   int* counters = nullptr;
   const int rc = scratch_for_current_device(&scratch, &counters);

@@ -69,7 +69,7 @@ __global__ void attention_plain_kernel(AttnParams p) {
 
   for (int j = lo + warp; j <= pos; j += kPlainWarps) {
     const int pidx = j / p.page_size;
-    const int page = table[pidx];
+    const int page = (pidx < p.max_pages) ? table[pidx] : -1;   // beyond the row: reported, not read
     if (page < 0 || page >= p.num_pages) {
       if (lane == 0) set_error(p.err, kErrPage, t, pidx, page);
       break;

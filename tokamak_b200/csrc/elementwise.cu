@@ -26,20 +26,6 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
   for (int h = threadIdx.x; h < hidden; h += blockDim.x) out[h] = to_f32<T>(row[h]);
 }
 
-// ids[t] = sampled[feed[t]] where feed[t] >= 0: the token that the previous step sampled on the
-// device becomes this step's input without a round trip through the host.
-__global__ void feed_tokens_kernel(int* __restrict__ ids, const int* __restrict__ feed,
-                                   const int* __restrict__ sampled, int n_tokens, int n_sampled, int* err) {
-  pdl_trigger();
-  pdl_wait();
-  const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= n_tokens) return;
-  const int f = feed[t];
-  if (f < 0) return;
-  if (f >= n_sampled) { set_error(err, kErrTokenId, t, f, n_sampled); return; }
-  ids[t] = sampled[f];
-}
-
 // x = resid[r] (+ delta[r]);  resid[r] = x (when written back);
 // out[i] = weight * x * rsqrt(mean(x^2) + eps)
 // rows == nullptr: r = i = blockIdx.x and the sum is written back to resid.
@@ -248,13 +234,6 @@ TK_API int tk_embed_gather(const void* table, int dtype, const int* ids, float* 
                     e = tk::launch(tk::embed_gather_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream,
                                        (const T*)table, ids, resid, hidden, vocab, err));
   return (int)e;
-}
-
-TK_API int tk_feed_tokens(int* ids, const int* feed, const int* sampled, int n_tokens, int n_sampled,
-                          int* err, cudaStream_t stream) {
-  if (n_tokens <= 0) return 0;
-  return (int)tk::launch(tk::feed_tokens_kernel, dim3((n_tokens + 127) / 128), dim3(128), 0, stream, ids,
-                         feed, sampled, n_tokens, n_sampled, err);
 }
 
 // delta: branch output in the activation type, or null.  parts: float32 partial sums of the

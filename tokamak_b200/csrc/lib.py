@@ -17,7 +17,11 @@ _P = c_void_p
 # name -> argument types (every function returns a cudaError_t as int unless noted)
 _SIGNATURES: dict[str, list] = {
     "tk_embed_gather": [_P, c_int, _P, _P, c_int, c_int, c_int, _P, _P],
-    "tk_feed_tokens": [_P, _P, _P, c_int, c_int, _P, _P],
+    "tk_step_begin": [_P, c_int, c_int, _P, c_int, _P, c_longlong, _P, _P, _P, _P, _P, c_int, c_int, _P, _P],
+    "tk_decode_begin": [_P, c_int, c_int, _P, c_int, _P, c_longlong, _P, c_int, c_int, _P, _P, _P, _P, _P],
+    "tk_sample_slots": [_P, c_longlong, _P, _P, c_int, _P, c_int, c_int, _P, _P],
+    "tk_wait_probe": [c_uint, _P, _P],
+    "tk_slot_words": [],
     "tk_add_rmsnorm": [_P, _P, _P, c_int, c_longlong, _P, _P, _P, c_int, c_int, c_float, c_int, _P],
     "tk_swiglu": [_P, _P, c_int, c_longlong, _P, c_int, c_int, c_int, c_int, _P],
     "tk_rope_kv": [_P, _P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,

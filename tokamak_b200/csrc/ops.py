@@ -73,13 +73,76 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, resid: torch.Tensor, er
            "embed_gather")
 
 
-def feed_tokens(ids: torch.Tensor, feed: torch.Tensor, sampled: torch.Tensor, err: torch.Tensor) -> None:
-    """ids[t] = sampled[feed[t]] wherever feed[t] >= 0 (all int32, on the device)."""
-    _want(ids, torch.int32, "ids"); _want(feed, torch.int32, "feed"); _want(sampled, torch.int32, "sampled")
-    if feed.numel() < ids.numel():
-        raise KernelError("feed is shorter than ids")
-    _check(library().tk_feed_tokens(ids.data_ptr(), feed.data_ptr(), sampled.data_ptr(), ids.numel(),
-                                    sampled.numel(), err.data_ptr(), _stream()), "feed_tokens")
+class UpdateBuffers:
+    """Device side of the update list that the kernels opening a step apply (``step_state.cu``):
+    the list itself, the engine's slot records and the flat block tables it writes into."""
+
+    def __init__(self, ctl: torch.Tensor, max_rec: int, max_tab: int, records: torch.Tensor,
+                 tables: torch.Tensor):
+        _want(ctl, torch.int32, "ctl"); _want(records, torch.int32, "records"); _want(tables, torch.int32, "tables")
+        if ctl.numel() < 2 + 9 * max_rec + 2 * max_tab:
+            raise KernelError("the update list is too small for its limits")
+        if records.dim() != 2 or records.shape[1] != library().tk_slot_words():
+            raise KernelError(f"slot records must be [slots, {library().tk_slot_words()}]")
+        self.ctl, self.max_rec, self.max_tab, self.records, self.tables = ctl, max_rec, max_tab, records, tables
+
+    def args(self) -> tuple:
+        return (self.ctl.data_ptr(), self.max_rec, self.max_tab, self.records.data_ptr(),
+                self.records.shape[0], self.tables.data_ptr(), self.tables.numel())
+
+
+def step_begin(upd: UpdateBuffers, token_ids: torch.Tensor, req_q_start: torch.Tensor,
+               req_kv_len: torch.Tensor, req_slot: torch.Tensor, req_fed: torch.Tensor | None,
+               err: torch.Tensor) -> None:
+    """Open a step laid out by the host: apply the pending updates, put the last sampled token of
+    every request marked in ``req_fed`` at its place in ``token_ids``, and note in each request's
+    record that the cache will hold ``req_kv_len`` positions."""
+    for name, t in (("token_ids", token_ids), ("req_q_start", req_q_start), ("req_kv_len", req_kv_len),
+                    ("req_slot", req_slot)):
+        _want(t, torch.int32, name)
+    n = req_slot.numel()
+    if req_q_start.numel() < n or req_kv_len.numel() < n or (req_fed is not None and req_fed.numel() < n):
+        raise KernelError("a per-request array is shorter than the batch")
+    _check(library().tk_step_begin(*upd.args(), token_ids.data_ptr(), req_q_start.data_ptr(),
+                                   req_kv_len.data_ptr(), req_slot.data_ptr(), _ptr(req_fed), n,
+                                   token_ids.numel(), err.data_ptr(), _stream()), "step_begin")
+
+
+def decode_begin(upd: UpdateBuffers, dec_slots: torch.Tensor, n_reqs: int, max_positions: int,
+                 token_ids: torch.Tensor, positions: torch.Tensor, req_kv_len: torch.Tensor,
+                 err: torch.Tensor) -> None:
+    """Open a step of single next tokens from the slot records alone: token, position and cache
+    length of the request in slot ``dec_slots[r]`` go to row ``r`` and its record moves on."""
+    for name, t in (("dec_slots", dec_slots), ("token_ids", token_ids), ("positions", positions),
+                    ("req_kv_len", req_kv_len)):
+        _want(t, torch.int32, name)
+        if t.numel() < n_reqs:
+            raise KernelError(f"{name} is shorter than the batch")
+    _check(library().tk_decode_begin(*upd.args(), dec_slots.data_ptr(), n_reqs, max_positions,
+                                     token_ids.data_ptr(), positions.data_ptr(), req_kv_len.data_ptr(),
+                                     err.data_ptr(), _stream()), "decode_begin")
+
+
+def sample_slots(logits: torch.Tensor, records: torch.Tensor, row_slot: torch.Tensor,
+                 out_tokens: torch.Tensor, err: torch.Tensor) -> None:
+    """One token per row of float32 logits, with the parameters, seed and counter of the slot
+    record ``records[row_slot[r]]``; the token is also written into the record and its counter
+    advanced (see sampling.cu)."""
+    _want(logits, torch.float32, "logits"); _want(records, torch.int32, "records")
+    _want(row_slot, torch.int32, "row_slot"); _want(out_tokens, torch.int32, "out_tokens")
+    rows, vocab = logits.shape
+    if row_slot.numel() < rows or out_tokens.numel() < rows:
+        raise KernelError("a per-row sampling tensor is shorter than the batch")
+    _check(library().tk_sample_slots(logits.data_ptr(), logits.stride(0), records.data_ptr(),
+                                     row_slot.data_ptr(), records.shape[0], out_tokens.data_ptr(), rows, vocab,
+                                     err.data_ptr(), _stream()), "sample_slots")
+
+
+def wait_probe(limit: int, err: torch.Tensor) -> None:
+    """Test aid: one block waits on a barrier that nobody arrives at, gives up after ``limit``
+    polls and reports it through the error word exactly as the tcgen05 kernels would."""
+    _want(err, torch.int32, "err")
+    _check(library().tk_wait_probe(int(limit), err.data_ptr(), _stream()), "wait_probe")
 
 
 def add_rmsnorm(resid: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor,
@@ -347,12 +410,17 @@ def prefill_kernel_takes(n_q_heads: int, n_kv_heads: int, head_dim: int, page_si
 
 
 _DECODE_COUNTERS: dict = {}
+_RETIRED_COUNTERS: list = []
 
 
 def _decode_counters(device: torch.device, n: int) -> torch.Tensor:
-    """Arrival counters of the decode kernel: zero between calls, one buffer per device."""
+    """Arrival counters of the decode kernel: zero between calls, one buffer per device.  A call
+    that needs more than the buffer holds gets a larger one; the smaller one is kept alive for
+    good, because CUDA graphs captured earlier still hold its address."""
     buf = _DECODE_COUNTERS.get(device)
     if buf is None or buf.numel() < n:
+        if buf is not None:
+            _RETIRED_COUNTERS.append(buf)
         buf = torch.zeros(max(65536, n), dtype=torch.int32, device=device)
         _DECODE_COUNTERS[device] = buf
     return buf

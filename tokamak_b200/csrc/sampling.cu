@@ -53,7 +53,16 @@ struct SampleParams {
   int* out_tokens;            // [n_rows]
   int vocab;
   long long ld;
+  // With `records` the parameters of row r come from the state record of slot row_slot[r]
+  // (layout in step_state.cu) instead of the arrays above, and the kernel writes the token
+  // back into the record and advances its counter.
+  int* records;
+  const int* row_slot;
+  int max_slots;
+  int* err;
 };
+
+constexpr int kSlotWords = 8;
 
 __device__ __forceinline__ unsigned long long warp_incl_scan_u64(unsigned long long v, int lane) {
 #pragma unroll
@@ -82,7 +91,16 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleParams p) 
   const int warp = tid >> 5;
   const int V = p.vocab;
   const float* lg = p.logits + (size_t)row * p.ld;
-  const float T = p.temperature[row];
+  int* rec = nullptr;
+  if (p.records != nullptr) {
+    const int slot = p.row_slot[row];
+    if (slot < 0 || slot >= p.max_slots) {
+      if (tid == 0) { set_error(p.err, kErrRequest, row, slot, p.max_slots); p.out_tokens[row] = 0; }
+      return;
+    }
+    rec = p.records + (size_t)slot * kSlotWords;
+  }
+  const float T = rec ? __int_as_float(rec[4]) : p.temperature[row];
 
   // ---- pass 1: maximum and its lowest index ------------------------------------------
   float best = -INFINITY;
@@ -113,15 +131,18 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleParams p) 
   __syncthreads();
   const float max_logit = s_val[0];
   if (T == 0.0f) {
-    if (tid == 0) p.out_tokens[row] = s_idx[0];
+    if (tid == 0) {
+      p.out_tokens[row] = s_idx[0];
+      if (rec) { rec[7] = s_idx[0]; rec[1] += 1; }
+    }
     return;
   }
   const float zmax = max_logit / T;
 
   // ---- thresholds: radix descent over the order-preserving key of z = logit / T -------
   unsigned int thr_key = 0u;   // keep keys >= thr_key
-  const int k = p.top_k[row];
-  const float top_p = p.top_p[row];
+  const int k = rec ? rec[5] : p.top_k[row];
+  const float top_p = rec ? __int_as_float(rec[6]) : p.top_p[row];
   const bool use_k = (k > 0 && k < V);
   const bool use_p = (top_p < 1.0f);
 
@@ -196,8 +217,10 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleParams p) 
 
   // ---- the draw: first index whose inclusive prefix exceeds u * total -------------------
   unsigned int rnd[4];
-  const unsigned long long seed = p.seed[row];
-  philox4x32_10(p.counter[row], 0u, 0u, 0u, (unsigned int)seed, (unsigned int)(seed >> 32), rnd);
+  const unsigned long long seed =
+      rec ? ((unsigned long long)(unsigned int)rec[3] << 32) | (unsigned int)rec[2] : p.seed[row];
+  const unsigned int counter = rec ? (unsigned int)rec[1] : p.counter[row];
+  philox4x32_10(counter, 0u, 0u, 0u, (unsigned int)seed, (unsigned int)(seed >> 32), rnd);
   // target = floor(rnd / 2^32 * total) < total
   const unsigned long long target = __umul64hi(total, (unsigned long long)rnd[0] << 32);
 
@@ -244,7 +267,10 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleParams p) 
     base += chunk_total;
   }
   __syncthreads();
-  if (tid == 0) p.out_tokens[row] = s_result;
+  if (tid == 0) {
+    p.out_tokens[row] = s_result;
+    if (rec) { rec[7] = s_result; rec[1] += 1; }
+  }
 }
 
 }  // namespace tk
@@ -257,6 +283,19 @@ TK_API int tk_sample(const float* logits, long long ld, const float* temperature
   tk::SampleParams p;
   p.logits = logits; p.temperature = temperature; p.top_k = top_k; p.top_p = top_p;
   p.seed = seed; p.counter = counter; p.out_tokens = out_tokens; p.vocab = vocab; p.ld = ld;
+  p.records = nullptr; p.row_slot = nullptr; p.max_slots = 0; p.err = nullptr;
+  return (int)tk::launch(tk::sample_kernel, dim3(n_rows), dim3(tk::kSampleThreads), 0, stream, p);
+}
+
+// The same with every row's parameters in the state record of its request's slot; the sampled
+// token goes to out_tokens[row] and into the record, whose counter moves on by one.
+TK_API int tk_sample_slots(const float* logits, long long ld, int* records, const int* row_slot, int max_slots,
+                           int* out_tokens, int n_rows, int vocab, int* err, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (vocab < 1 || records == nullptr || row_slot == nullptr) return (int)cudaErrorInvalidValue;
+  tk::SampleParams p = {};
+  p.logits = logits; p.out_tokens = out_tokens; p.vocab = vocab; p.ld = ld;
+  p.records = records; p.row_slot = row_slot; p.max_slots = max_slots; p.err = err;
   return (int)tk::launch(tk::sample_kernel, dim3(n_rows), dim3(tk::kSampleThreads), 0, stream, p);
 }
 

@@ -38,7 +38,9 @@ const char* tk_noalloc_error_string(int code);
  *  - Needs n_items * n_q_heads * n_splits * (head_dim + 2) floats of scratch and
  *    n_items * n_kv_heads arrival counters (the library holds 4096); a call that needs more
  *    than the capacity returns TK_NOALLOC_TOO_LARGE and launches nothing (use fewer splits,
- *    or fewer items per call).
+ *    or fewer items per call).  A call with n_splits == 1 uses neither array and has no limit.
+ *  - Host threads: the one-time lookup is guarded by a mutex, so threads may call at the same
+ *    time as far as the host is concerned; what the next point says about the GPU still holds.
  *  - The first call on a device looks up the array's device address (once per device,
  *    with that device current).  Make that first call outside any stream capture.
  *  - All calls share the arrays, and they keep what the last call left in them.  The

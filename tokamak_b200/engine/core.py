@@ -64,14 +64,15 @@ class EngineCore:
         max_step_tokens: most tokens of one step.
         tensors, raw_config: weights and configuration given directly instead of read from
             the folder (random weights made on the device, for measurements).
-        config_overrides: keys that replace those of ``config.json`` (an engine-wide window).
+        window: the engine-wide attention window (``None``: what the configuration says); an
+            architecture that does not take the option refuses it.
     """
 
     def __init__(self, model: str | Path, *, dtype: str | torch.dtype = "bfloat16",
                  device: str | torch.device = "cuda", max_seq_len: int | None = None,
                  page_size: int = 16, pool_tokens: int | str | None = None, max_slots: int = 16,
                  max_step_tokens: int | None = None, tensors: dict | None = None,
-                 raw_config: dict | None = None, config_overrides: dict | None = None,
+                 raw_config: dict | None = None, window: int | None = None,
                  memory_utilization: float = 0.9):
         self.device = require_cuda(device)
         self.dtype = resolve_dtype(dtype)
@@ -81,12 +82,10 @@ class EngineCore:
             eos = read_eos_token_ids(model, raw_config)
         else:
             eos = None
-        if config_overrides:
-            raw_config = {**raw_config, **config_overrides}
         self.raw_config = raw_config
         self.architecture = architecture_of(raw_config)
-        self.config = self.architecture.parse_config(raw_config, eos)
-        self.spec = self.architecture.model_spec(self.config)
+        self.config = self.architecture.parse(raw_config, eos)
+        self.spec = self.architecture.build_spec(self.config, window=window)
         rt = Runtime(device=self.device, dtype=self.dtype)
         if tensors is None:
             expected = DecoderModel.expected_tensors(self.spec)
@@ -94,7 +93,7 @@ class EngineCore:
         self.model = DecoderModel(self.spec, tensors, rt)
         del tensors
 
-        model_max = int(getattr(self.config, "max_position_embeddings", max_seq_len or 0))
+        model_max = self.config.max_position_embeddings
         self.max_seq_len = min(max_seq_len or model_max, model_max)
         if page_size < 1:
             raise ValueError(f"block_size must be >= 1, got {page_size}")
@@ -147,7 +146,7 @@ class EngineCore:
         del step, cache, manager, kv_groups, state_groups
         torch.cuda.empty_cache()
         # the float32 logits of a full decode batch come on top of what one wanted row needed
-        workspace = int(1.25 * peak) + 8 * max_slots * self.spec.embedding.vocab_size
+        workspace = int(1.25 * peak) + 8 * max_slots * self.config.vocab_size
         free, _ = torch.cuda.mem_get_info(self.device)
         budget = int(free * utilization) - workspace
         tokens = max(budget, 0) // per_token // page_size * page_size
@@ -170,7 +169,7 @@ def random_core(raw_config: dict, *, seed: int = 0, std: float = 0.02, norm_std:
     dev = require_cuda(device)
     dt = resolve_dtype(dtype)
     arch = architecture_of(raw_config)
-    spec = arch.model_spec(arch.parse_config(raw_config))
+    spec = arch.build_spec(arch.parse(raw_config), window=kwargs.get("window"))
     expected = DecoderModel.expected_tensors(spec)
     tensors = random_tensors(expected, seed, std, norm_std, dt, device=dev)
     for name, req in expected.items():

@@ -108,16 +108,11 @@ class LLM:
         if _core is not None:
             self.core = _core
         else:
-            overrides = None
-            if window is not None:
-                overrides = {"use_sliding_window": True, "sliding_window": window,
-                             "max_window_layers": 0}
             self.core = EngineCore(model, dtype=dtype, device=device, max_seq_len=max_seq_len,
                                    page_size=block_size, pool_tokens=kv_pool_tokens,
                                    max_slots=max_batch_size,
                                    max_step_tokens=max(max_num_batched_tokens, max_batch_size),
-                                   config_overrides=overrides,
-                                   memory_utilization=gpu_memory_utilization)
+                                   window=window, memory_utilization=gpu_memory_utilization)
         self.model_path = Path(model)
         self.model_config = self.core.config
         self.max_seq_len = self.core.max_seq_len
@@ -134,6 +129,10 @@ class LLM:
         self.model = self.core.model
         self._tokenizer = None
         self.last_stats: dict = {}
+        # A debugging aid: with plain_steps every step is laid out by the host (tokens included),
+        # none is launched ahead of the one before it and none is replayed from a CUDA graph.  The
+        # tokens must not depend on it.
+        self.plain_steps = False
 
     # ---- tokenizer (text in and out only; the engine itself works on token ids) ---------
     @property
@@ -162,15 +161,15 @@ class LLM:
         Exactly one of ``prompts`` and ``prompt_token_ids`` is given.  ``sampling_params`` is one
         object for all prompts, a sequence matching them one to one, or ``None`` for defaults.
         """
-        prompt_texts, token_lists = self._resolve_prompts(prompts, prompt_token_ids)
-        params_list = self._broadcast_params(sampling_params, len(token_lists))
+        texts, token_lists = self._token_lists(prompts, prompt_token_ids)
+        per_prompt = self._params_per_prompt(sampling_params, len(token_lists))
 
         arrival = time.perf_counter()
         sequences = []
-        for i, (ids, params) in enumerate(zip(token_lists, params_list, strict=True)):
-            seq = Sequence(seq_id=i, prompt_token_ids=list(ids), sampling_params=params)
+        for i, (ids, params) in enumerate(zip(token_lists, per_prompt, strict=True)):
+            seq = Sequence(seq_id=i, prompt_token_ids=ids, sampling_params=params)
             seq.arrival_time = arrival
-            self._validate_fits(seq)
+            self._check_request(seq)
             sequences.append(seq)
 
         scheduler = Scheduler(self.cache_manager, self.max_batch_size, self.max_num_batched_tokens,
@@ -182,25 +181,28 @@ class LLM:
         if use_tqdm:
             from tqdm.auto import tqdm
             bar = tqdm(total=len(sequences), desc="Generating")
+        buffers = self.core.step.buffers
         stats = {"steps": 0, "tokens_run": 0, "prefill_tokens": 0, "decode_tokens": 0,
                  "mixed_steps": 0, "decode_steps": 0, "decode_step_time_s": 0.0,
-                 "decode_step_tokens": 0, "decode_step_times": []}
+                 "decode_step_tokens": 0, "decode_step_times": [], "decode_step_h2d_bytes": [],
+                 "pages_free_min": min((g.num_free for g in self.cache_manager.kv_groups), default=0)}
         try:
             flight = None                    # the launched step whose tokens have not been read
             mark = time.perf_counter()       # when the device last became free for a new step
+            h2d_mark = buffers.h2d_bytes
             while flight is not None or scheduler.has_unfinished():
                 if flight is None:
                     mark = time.perf_counter()
                     plan = scheduler.schedule()
                     if plan is None:
                         raise RuntimeError("scheduler returned no work but is unfinished")
-                    flight = self._launch(plan, None)
+                    flight = self._launch(plan)
                 # the step after a step of single next tokens is known but for the tokens, which
                 # stay on the device: it is launched before this step's tokens are read
                 ahead = None
-                plan_ahead = scheduler.plan_ahead(flight.plan, self._max_total_tokens)
+                plan_ahead = None if self.plain_steps else scheduler.plan_ahead(flight.plan, self._context_budget)
                 if plan_ahead is not None:
-                    ahead = self._launch(plan_ahead, flight)
+                    ahead = self._launch(plan_ahead)
                 done = self._complete(flight, ahead)
                 plan = flight.plan
                 stats["steps"] += 1
@@ -209,6 +211,8 @@ class LLM:
                 stats["decode_tokens"] += n_dec
                 stats["prefill_tokens"] += plan.num_tokens - n_dec
                 stats["mixed_steps"] += int(0 < n_dec < len(plan.entries))
+                stats["pages_free_min"] = min([stats["pages_free_min"]]
+                                              + [g.num_free for g in self.cache_manager.kv_groups])
                 now = time.perf_counter()
                 if n_dec == len(plan.entries):
                     # a step of single next tokens only, timed from the moment the device was free
@@ -218,6 +222,9 @@ class LLM:
                     stats["decode_step_time_s"] += dt
                     stats["decode_step_tokens"] += n_dec
                     stats["decode_step_times"].append(dt)
+                    # bytes copied to the device since the step before was accounted for
+                    stats["decode_step_h2d_bytes"].append(buffers.h2d_bytes - h2d_mark)
+                h2d_mark = buffers.h2d_bytes
                 mark = now
                 if bar is not None:
                     bar.update(done)
@@ -228,33 +235,36 @@ class LLM:
             if bar is not None:
                 bar.close()
         stats["preemptions"] = scheduler.num_preemptions
+        stats["pages_free"] = [g.num_free for g in self.cache_manager.kv_groups]
         self.last_stats = stats
-        return [self._to_output(seq, prompt_texts[seq.seq_id] if prompt_texts else None)
-                for seq in sequences]
+        return [self._result_of(seq, texts[seq.seq_id] if texts else None) for seq in sequences]
 
-    def _launch(self, plan: StepPlan, fed_by: "_Flight | None") -> "_Flight":
-        """Start one planned step.  With ``fed_by`` (the step before it, not yet read) every
-        entry is the next single token of a sequence that sampled in that step."""
-        entries, rows, samplers, feed = [], [], [], []
-        place = {id(seq): i for i, seq in enumerate(fed_by.samplers)} if fed_by is not None else {}
+    def _launch(self, plan: StepPlan) -> "_Flight":
+        """Start one planned step.
+
+        A request that was given a slot in this plan gets its record written: how it samples, its
+        seed, a counter of zero.  A request that only needs its next token does not bring it: the
+        device sampled it and holds it in the request's record, whether or not the host has read
+        it yet."""
+        entries, samplers = [], []
+        for seq in plan.admitted:
+            p = seq.sampling_params
+            self.core.step.set_record(seq.seq_id, SamplingRow(p.temperature, p.top_k, p.top_p, seq.seed, 0),
+                                      fresh=True)
         for e in plan.entries:
-            p = e.seq.sampling_params
-            if fed_by is not None:
-                # the token is still on the device: a placeholder here, its place in the feed
-                entries.append(StepEntry(e.seq.seq_id, [0], [0]))
-                feed.append(place[id(e.seq)])
-                rows.append(SamplingRow(p.temperature, p.top_k, p.top_p, e.seq.seed,
-                                        e.seq.num_output_tokens + 1))
-                samplers.append(e.seq)
-            else:
-                toks = e.seq.tokens_from(e.start, e.count)
-                entries.append(StepEntry(e.seq.seq_id, toks, [e.count - 1] if e.samples else []))
-                if e.samples:
-                    rows.append(SamplingRow(p.temperature, p.top_k, p.top_p, e.seq.seed,
-                                            e.seq.num_output_tokens))
-                    samplers.append(e.seq)
-            e.seq.num_computed = e.start + e.count
-        pending = self.core.step.launch_and_sample(entries, rows, feed if fed_by is not None else None)
+            seq = e.seq
+            on_device = e.count == 1 and e.samples and seq.num_output_tokens > 0 and not self.plain_steps
+            tokens = None if on_device else seq.tokens_from(e.start, e.count)
+            entries.append(StepEntry(seq.seq_id, tokens, [e.count - 1] if e.samples else []))
+            if e.samples:
+                samplers.append(seq)
+            seq.num_computed = e.start + e.count
+        step = self.core.step
+        graphs, step.use_graphs = step.use_graphs, step.use_graphs and not self.plain_steps
+        try:
+            pending = step.launch_and_sample(entries)
+        finally:
+            step.use_graphs = graphs
         return _Flight(plan, pending, samplers)
 
     def _complete(self, flight: "_Flight", ahead: "_Flight | None") -> int:
@@ -269,7 +279,7 @@ class LLM:
                 self.cache_manager.free(seq.seq_id)
                 continue
             done = seq.append_checked(int(token), eos_token_ids=self.model_config.eos_token_ids,
-                                      max_total_tokens=self._max_total_tokens(seq))
+                                      max_total_tokens=self._context_budget(seq))
             if seq.first_token_time is None:
                 seq.first_token_time = now
             if done:
@@ -279,61 +289,61 @@ class LLM:
                     self.cache_manager.free(seq.seq_id)
         return finished
 
-    # ---- helpers ------------------------------------------------------------------------------
-    def _max_total_tokens(self, seq: Sequence) -> int:
-        """A request's context budget (src/tokamak/engine/llm.py:483-485)."""
-        return min(self.max_seq_len, seq.num_prompt_tokens + seq.sampling_params.max_new_tokens)
+    # ---- what a request may ask for --------------------------------------------------------------
+    def _context_budget(self, seq: Sequence) -> int:
+        """Tokens the request's stream may reach: its own limit or the engine's, whichever is less."""
+        return min(seq.num_prompt_tokens + seq.sampling_params.max_new_tokens, self.max_seq_len)
 
-    def _validate_fits(self, seq: Sequence) -> None:
-        if seq.num_prompt_tokens >= self.max_seq_len:
-            raise ValueError(f"Prompt of {seq.num_prompt_tokens} tokens does not fit in "
-                             f"max_seq_len={self.max_seq_len} (room for generation is required)")
-        vocab = self.model_config.vocab_size
-        bad = [t for t in seq.prompt_token_ids if not 0 <= t < vocab]
-        if bad:
-            raise ValueError(f"prompt token id {bad[0]} is outside the vocabulary of {vocab}")
-        total = self._max_total_tokens(seq)
+    def _check_request(self, seq: Sequence) -> None:
+        """Refuse at submission what could never run: a prompt that leaves no room to generate,
+        token ids the embedding does not have, more pages than the whole pool."""
+        n, vocab = seq.num_prompt_tokens, self.model_config.vocab_size
+        if n >= self.max_seq_len:
+            raise ValueError(f"a prompt of {n} tokens does not fit: max_seq_len={self.max_seq_len} must "
+                             f"leave room for at least one generated token")
+        for t in seq.prompt_token_ids:
+            if not 0 <= t < vocab:
+                raise ValueError(f"prompt token id {t} is outside the vocabulary of {vocab}")
+        budget = self._context_budget(seq)
         for g in self.cache_manager.kv_groups:
-            if g.pages_for(total) > g.num_pages:
-                raise ValueError(f"Request needs {g.pages_for(total)} KV blocks but the pool has "
-                                 f"{g.num_pages}; raise kv_pool_tokens")
+            need = g.pages_for(budget)
+            if need > g.num_pages:
+                raise ValueError(f"the request needs {need} cache pages at its longest and the pool has "
+                                 f"{g.num_pages}: raise kv_pool_tokens")
 
-    def _resolve_prompts(self, prompts, prompt_token_ids):
-        if (prompts is None) == (prompt_token_ids is None):
-            raise ValueError("provide exactly one of `prompts` or `prompt_token_ids`")
+    def _token_lists(self, prompts, prompt_token_ids) -> tuple[list[str] | None, list[list[int]]]:
+        """Texts (if prompts came as text) and the token ids of every prompt."""
+        given = [x is not None for x in (prompts, prompt_token_ids)]
+        if sum(given) != 1:
+            raise ValueError("give exactly one of `prompts` (text) and `prompt_token_ids`")
         if prompt_token_ids is not None:
-            return None, [list(ids) for ids in prompt_token_ids]
-        if isinstance(prompts, str):
-            prompts = [prompts]
-        texts = list(prompts)
-        return texts, [self.tokenizer.encode(text) for text in texts]
+            return None, [[int(t) for t in ids] for ids in prompt_token_ids]
+        texts = [prompts] if isinstance(prompts, str) else list(prompts)
+        encode = self.tokenizer.encode
+        return texts, [encode(text) for text in texts]
 
-    def _to_output(self, seq: Sequence, prompt_text: str | None) -> RequestOutput:
-        if seq.finish_reason is None:
-            raise RuntimeError(f"Sequence {seq.seq_id} completed without a finish reason")
-        ttft = latency = None
-        if seq.arrival_time is not None:
-            if seq.first_token_time is not None:
-                ttft = seq.first_token_time - seq.arrival_time
-            if seq.finish_time is not None:
-                latency = seq.finish_time - seq.arrival_time
+    def _result_of(self, seq: Sequence, prompt_text: str | None) -> RequestOutput:
+        if not seq.is_finished:
+            raise RuntimeError(f"request {seq.seq_id} left the step loop unfinished")
+        since = lambda t: None if t is None or seq.arrival_time is None else t - seq.arrival_time
+        generated = seq.output_token_ids
         text = ""
         if self._has_tokenizer():
-            text = self.tokenizer.decode(seq.output_token_ids, skip_special_tokens=True)
+            decode = self.tokenizer.decode
+            text = decode(generated, skip_special_tokens=True)
             if prompt_text is None:
-                prompt_text = self.tokenizer.decode(seq.prompt_token_ids, skip_special_tokens=True)
+                prompt_text = decode(seq.prompt_token_ids, skip_special_tokens=True)
         return RequestOutput(request_id=seq.seq_id, prompt=prompt_text,
                              prompt_token_ids=seq.prompt_token_ids, output_text=text,
-                             output_token_ids=seq.output_token_ids, finish_reason=seq.finish_reason,
-                             ttft_s=ttft, latency_s=latency, num_preemptions=seq.num_preemptions)
+                             output_token_ids=generated, finish_reason=seq.finish_reason,
+                             ttft_s=since(seq.first_token_time), latency_s=since(seq.finish_time),
+                             num_preemptions=seq.num_preemptions)
 
     @staticmethod
-    def _broadcast_params(sampling_params, num_prompts: int) -> list[SamplingParams]:
-        if sampling_params is None:
-            return [SamplingParams()] * num_prompts
-        if isinstance(sampling_params, SamplingParams):
-            return [sampling_params] * num_prompts
-        params_list = list(sampling_params)
-        if len(params_list) != num_prompts:
-            raise ValueError(f"Got {len(params_list)} SamplingParams for {num_prompts} prompts")
-        return params_list
+    def _params_per_prompt(sampling_params, n: int) -> list[SamplingParams]:
+        if isinstance(sampling_params, SamplingParams) or sampling_params is None:
+            return [sampling_params or SamplingParams()] * n
+        per_prompt = list(sampling_params)
+        if len(per_prompt) != n:
+            raise ValueError(f"{len(per_prompt)} SamplingParams for {n} prompts: give one, or one each")
+        return per_prompt

@@ -3,8 +3,11 @@
 Policy of the reference (src/tokamak/engine/scheduler.py:1-188): first come first
 served, requests join and leave at token granularity, and when the page pool
 cannot cover a running sequence's next tokens the newest running sequence is
-preempted: its pages and slot are given back and it returns to the *front* of
-the waiting queue with its generated tokens kept, to be recomputed later.
+preempted: its pages are given back and it returns to the *front* of the waiting
+queue with its generated tokens kept, to be recomputed later.  It keeps its request
+slot meanwhile, and with it the record of its random generator, as the reference keeps
+a preempted request's generator (src/tokamak/engine/llm.py:339-340,441-445); since
+nobody is admitted ahead of it, the slot would have no other taker.
 
 What is added here is the token budget.  The reference computes a whole prompt
 in one step and lets the decodes wait meanwhile (scheduler.py:114-117); this
@@ -12,6 +15,12 @@ scheduler plans one mixed batch per step: every running sequence that only needs
 its next token gets one token, and what is left of ``max_num_batched_tokens``
 goes to prompt portions, running prefills first, then new admissions, each
 portion at most ``prefill_chunk`` tokens.
+
+Order within a plan: the running sequences reserve the pages of their next tokens first, and
+admissions take what is left.  The reference asks the admission question first and finds the
+running sequences' pages afterwards (scheduler.py:113-131), so it can admit a request whose
+pages the next step takes away again; here a request is admitted only into room that the
+running sequences leave in this very step.
 
 When pages run out:
   * a waiting request is admitted only if the pages for all its current tokens
@@ -46,6 +55,7 @@ class PlannedEntry:
 class StepPlan:
     entries: list[PlannedEntry]
     preempted: list[Sequence] = field(default_factory=list)
+    admitted: list[Sequence] = field(default_factory=list)    # given a slot for the first time in this plan
 
     @property
     def num_tokens(self) -> int:
@@ -101,19 +111,20 @@ class Scheduler:
         """Plan the next step; ``None`` when everything is finished."""
         self.running = [s for s in self.running if not s.is_finished]
         preempted: list[Sequence] = []
+        admitted: list[Sequence] = []
         while True:
             entries: list[PlannedEntry] = []
             budget = self._budget
 
             # 1. running sequences: single next tokens first, then prompt portions
-            decoding = [s for s in self.running if s.num_tokens - s.num_computed == 1]
-            prefilling = [s for s in self.running if s.num_tokens - s.num_computed > 1]
+            decoding = [s for s in self.running if s.num_pending == 1]
+            prefilling = [s for s in self.running if s.num_pending > 1]
             for seq in decoding + prefilling:
                 if seq not in self.running:
                     continue    # preempted while an earlier sequence was served
                 if budget == 0:
                     break
-                want = seq.num_tokens - seq.num_computed
+                want = seq.num_pending
                 count = min(want, budget, self._chunk or want)
                 if self._reserve(seq, seq.num_computed + count, preempted, entries):
                     entries.append(PlannedEntry(seq, seq.num_computed, count,
@@ -125,13 +136,16 @@ class Scheduler:
             # 2. admissions, strictly in arrival order
             while self.waiting and len(self.running) < self._max_batch_size and budget > 0:
                 seq = self.waiting[0]
-                if self._manager.num_free_slots == 0 or not self._fits_new(seq):
+                resumed = self._manager.has(seq.seq_id)     # preempted earlier: it kept its slot
+                if (not resumed and self._manager.num_free_slots == 0) or not self._fits_new(seq):
                     if not self.running:
                         raise OutOfPagesError(
                             f"sequence {seq.seq_id} needs more pages than the pool can ever provide")
                     break   # pages are busy; decode until some come free
                 self.waiting.popleft()
-                self._manager.admit(seq.seq_id)
+                if not resumed:
+                    self._manager.admit(seq.seq_id)
+                    admitted.append(seq)
                 self._manager.grow(seq.seq_id, seq.num_tokens)
                 seq.status = SequenceStatus.RUNNING
                 seq.num_computed = 0
@@ -141,7 +155,7 @@ class Scheduler:
                 budget -= count
 
             if entries:
-                return StepPlan(entries, preempted)
+                return StepPlan(entries, preempted, admitted)
             if self.running:
                 # unreachable: a running sequence is either planned or preempted above
                 raise RuntimeError("scheduler stalled with running sequences")
@@ -202,11 +216,9 @@ class Scheduler:
                     return False
 
     def _preempt(self, victim: Sequence) -> None:
-        """Evict by recomputation: give back pages and slot, requeue at the front."""
-        self._manager.free(victim.seq_id)
+        """Evict by recomputation: give back the pages, keep the slot, requeue at the front."""
+        self._manager.restart(victim.seq_id)
         self.running.remove(victim)
-        victim.status = SequenceStatus.WAITING
-        victim.num_computed = 0
-        victim.num_preemptions += 1
+        victim.rewind()
         self.num_preemptions += 1
         self.waiting.appendleft(victim)

@@ -1,5 +1,17 @@
-"""Per-request token state (src/tokamak/engine/sequence.py:17-138), with the count of
-tokens that the cache already holds, which chunked prefill needs."""
+"""One generation request as the engine tracks it.
+
+The engine sees a request as one growing token stream (prompt, then what was
+generated) with a *cursor*: ``num_computed`` tokens of the stream are in the cache.
+Whatever lies between the cursor and the end of the stream is still to be run, in
+portions of any size; a step that reaches the end samples the next token.  Preemption
+moves the cursor back to 0 and changes nothing else, which is all that recomputation
+needs.  The request's random stream is its seed plus the number of tokens generated so
+far (the device keeps that count in the request's slot record).
+
+The stop rules and their order are the reference's
+(src/tokamak/engine/sequence.py:109-127): an end-of-sequence token unless ignored, then
+``max_new_tokens``, then the context budget.
+"""
 
 from __future__ import annotations
 
@@ -10,71 +22,69 @@ from ..sampling.params import SamplingParams
 
 
 class SequenceStatus(enum.Enum):
-    WAITING = enum.auto()
-    RUNNING = enum.auto()
-    FINISHED = enum.auto()
+    WAITING = "waiting"
+    RUNNING = "running"
+    FINISHED = "finished"
 
 
 class FinishReason(enum.Enum):
-    STOP = "stop"        # an EOS token was generated
-    LENGTH = "length"    # max_new_tokens or the context limit was reached
+    STOP = "stop"
+    LENGTH = "length"
 
 
 class Sequence:
-    """Tokens and lifecycle of one generation request.
+    """Token stream, cursor and lifecycle of one request."""
 
-    A preempted sequence goes back to WAITING with its generated tokens intact
-    and ``num_computed`` reset; resuming recomputes the cache over prompt plus
-    generated tokens, in portions, and then samples the next token.
-    """
+    __slots__ = ("seq_id", "sampling_params", "seed", "status", "finish_reason", "num_computed",
+                 "num_preemptions", "arrival_time", "first_token_time", "finish_time",
+                 "_stream", "_n_prompt")
 
     def __init__(self, seq_id: int, prompt_token_ids: list[int], sampling_params: SamplingParams):
-        if not prompt_token_ids:
+        if len(prompt_token_ids) == 0:
             raise ValueError("prompt_token_ids must not be empty")
         self.seq_id = seq_id
-        self.prompt_token_ids = list(prompt_token_ids)
-        self.output_token_ids: list[int] = []
         self.sampling_params = sampling_params
+        # an unseeded request draws a seed once, so that recomputation after preemption repeats it
+        self.seed = sampling_params.seed if sampling_params.seed is not None else random.getrandbits(62)
+        self._stream: list[int] = [int(t) for t in prompt_token_ids]
+        self._n_prompt = len(self._stream)
+        self.num_computed = 0           # the cursor: tokens of the stream that the cache holds
+        self.num_preemptions = 0
         self.status = SequenceStatus.WAITING
         self.finish_reason: FinishReason | None = None
-        self.arrival_time: float | None = None
-        self.first_token_time: float | None = None
-        self.finish_time: float | None = None
-        self.num_computed = 0
-        self.num_preemptions = 0
-        seed = sampling_params.seed
-        self.seed = seed if seed is not None else random.getrandbits(62)
+        self.arrival_time = self.first_token_time = self.finish_time = None
+
+    # ---- the stream ---------------------------------------------------------------------
+    @property
+    def num_tokens(self) -> int:
+        return len(self._stream)
 
     @property
     def num_prompt_tokens(self) -> int:
-        return len(self.prompt_token_ids)
+        return self._n_prompt
 
     @property
     def num_output_tokens(self) -> int:
-        return len(self.output_token_ids)
+        return len(self._stream) - self._n_prompt
 
     @property
-    def num_tokens(self) -> int:
-        return len(self.prompt_token_ids) + len(self.output_token_ids)
+    def prompt_token_ids(self) -> list[int]:
+        return self._stream[:self._n_prompt]
 
     @property
-    def all_token_ids(self) -> list[int]:
-        return self.prompt_token_ids + self.output_token_ids
+    def output_token_ids(self) -> list[int]:
+        return self._stream[self._n_prompt:]
+
+    @property
+    def num_pending(self) -> int:
+        """Tokens between the cursor and the end of the stream."""
+        return len(self._stream) - self.num_computed
 
     def tokens_from(self, start: int, count: int) -> list[int]:
-        """``count`` tokens of prompt + generated, beginning at index ``start``."""
-        n_prompt = len(self.prompt_token_ids)
-        end = start + count
-        if end <= n_prompt:
-            return self.prompt_token_ids[start:end]
-        if start >= n_prompt:
-            return self.output_token_ids[start - n_prompt:end - n_prompt]
-        return self.prompt_token_ids[start:] + self.output_token_ids[:end - n_prompt]
+        """``count`` tokens of the stream from index ``start``."""
+        return self._stream[start:start + count]
 
-    @property
-    def last_token_id(self) -> int:
-        return self.output_token_ids[-1] if self.output_token_ids else self.prompt_token_ids[-1]
-
+    # ---- lifecycle ----------------------------------------------------------------------
     @property
     def is_finished(self) -> bool:
         return self.status is SequenceStatus.FINISHED
@@ -82,25 +92,31 @@ class Sequence:
     def append_output_token(self, token_id: int) -> None:
         if self.is_finished:
             raise RuntimeError(f"Sequence {self.seq_id} is already finished")
-        self.output_token_ids.append(token_id)
+        self._stream.append(int(token_id))
 
     def append_checked(self, token_id: int, *, eos_token_ids: tuple[int, ...],
                        max_total_tokens: int) -> bool:
-        """Append one token and apply the stop rules in the reference's order: EOS unless
-        ignored, then ``max_new_tokens``, then the context budget (sequence.py:109-127)."""
+        """Append a generated token; ``True`` if it ended the request."""
         self.append_output_token(token_id)
         params = self.sampling_params
-        if not params.ignore_eos and token_id in eos_token_ids:
-            self.finish(FinishReason.STOP)
-        elif self.num_output_tokens >= params.max_new_tokens or self.num_tokens >= max_total_tokens:
-            self.finish(FinishReason.LENGTH)
-        return self.is_finished
+        reason = None
+        if token_id in eos_token_ids and not params.ignore_eos:
+            reason = FinishReason.STOP
+        elif self.num_output_tokens >= params.max_new_tokens or len(self._stream) >= max_total_tokens:
+            reason = FinishReason.LENGTH
+        if reason is not None:
+            self.finish(reason)
+        return reason is not None
 
     def finish(self, reason: FinishReason) -> None:
-        self.status = SequenceStatus.FINISHED
-        self.finish_reason = reason
+        self.status, self.finish_reason = SequenceStatus.FINISHED, reason
+
+    def rewind(self) -> None:
+        """Preemption: nothing of the stream is in the cache any more."""
+        self.num_computed = 0
+        self.num_preemptions += 1
+        self.status = SequenceStatus.WAITING
 
     def __repr__(self) -> str:
-        return (f"Sequence(id={self.seq_id}, prompt={self.num_prompt_tokens} tok, "
-                f"output={self.num_output_tokens} tok, computed={self.num_computed}, "
-                f"status={self.status.name})")
+        return (f"Sequence({self.seq_id}: {self._n_prompt}+{self.num_output_tokens} tokens, "
+                f"cursor {self.num_computed}, {self.status.value})")

@@ -29,18 +29,32 @@ class StepError(RuntimeError):
     """A kernel reported bad input through the error word."""
 
 
+def _bucket(length: int) -> int:
+    bucket = 256
+    while bucket < length:
+        bucket *= 2
+    return bucket
+
+
 @dataclass
 class StepEntry:
-    """Next tokens of one request and the places among them whose logits are wanted."""
+    """Next tokens of one request and the places among them whose logits are wanted.
+
+    ``tokens=None`` stands for one token: the one that the request sampled last, which is still
+    on the device (in the request's slot record) and may not have been read by the host yet."""
 
     req_id: Hashable
-    tokens: Sequence[int]
+    tokens: Sequence[int] | None
     want: Sequence[int] = ()
+
+    @property
+    def count(self) -> int:
+        return 1 if self.tokens is None else len(self.tokens)
 
 
 @dataclass
 class SamplingRow:
-    """How to sample at one wanted place (see tokamak_b200.sampling)."""
+    """How a request samples (see tokamak_b200.sampling); ``counter`` is the index of its next draw."""
 
     temperature: float = 0.0
     top_k: int = 0
@@ -57,7 +71,8 @@ class StepBatch:
     request in the per-request arrays; ``req_slot[r]`` is that request's row in the
     block tables and state records; ``req_kv_len[r]`` counts the positions of the
     request after this step, so its tokens sit at ``req_kv_len - req_q_len ...``.
-    The ``host_*`` lists repeat the per-request numbers for parts that plan on the host.
+    The ``host_*`` lists repeat the per-request numbers for parts that plan on the host;
+    a part that reads them must not declare itself ``GRAPH_SAFE`` (``parts/base.py``).
     """
 
     n_tokens: int
@@ -82,8 +97,10 @@ class StepBatch:
     host_kv_len: list[int] = field(default_factory=list)
     host_slot: list[int] = field(default_factory=list)
     max_q_len: int = 0
-    max_kv_len: int = 0
+    max_kv_len: int = 0     # a bound on the longest context: the next power of two, at least 256, so
+                            # that what kernels plan from it (grids, key splits) changes rarely
     scratch: dict = field(default_factory=dict)     # per-step values that parts share (e.g. plans)
+    row_slot: torch.Tensor | None = None            # slot of the request of every wanted row
 
 
 @dataclass
@@ -95,38 +112,82 @@ class PendingStep:
     done: torch.cuda.Event
 
 
-class StepBuffers:
-    """Pinned host staging and its device twin for the integers that describe a step.
+class _PinnedRing:
+    """A few pinned host buffers used in turn as the source of asynchronous copies: a buffer is
+    written again only after the copy that read it has completed."""
 
-    The host side is a small ring: a copy to the device is asynchronous, so a staging
-    buffer is written again only after the copy that read it has completed.
+    def __init__(self, words: int, ring: int = 3):
+        self.hosts = [torch.zeros(max(1, words), dtype=torch.int32).pin_memory() for _ in range(ring)]
+        self.events: list = [None] * ring
+        self.turn = 0
+
+    def next(self) -> tuple[torch.Tensor, int]:
+        i = self.turn
+        self.turn = (i + 1) % len(self.hosts)
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        return self.hosts[i], i
+
+    def copied(self, i: int) -> None:
+        if self.events[i] is None:
+            self.events[i] = torch.cuda.Event()
+        self.events[i].record()
+
+
+class StepBuffers:
+    """Everything at a fixed device address that describes steps, and the pinned staging behind it.
+
+    * ``dev``: the integers of a step that the host lays out (token ids, positions, the
+      per-request arrays, ...), one copy per such step.
+    * ``updates``: the list of record and table writes that the kernel opening the next step
+      applies; copied only when something changed.
+    * ``dec_*``: the description of a step of single next tokens, which the device derives from
+      the slot records; only the list of slots comes from the host, and only when it changed.
+    * ``result``: error word and sampled tokens, which travel back together.
     """
 
     RING = 3
 
-    def __init__(self, device: torch.device, max_tokens: int, max_reqs: int):
+    def __init__(self, cache: DeviceCache, max_tokens: int):
+        device, max_reqs = cache.device, cache.manager.max_slots
         self.device = device
-        self.capacity = 8 * max_reqs + 12 * max_tokens + 64
-        self.hosts = [torch.zeros(self.capacity, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
-        self.events: list = [None] * self.RING
-        self.turn = 0
+        self.capacity = 10 * max_reqs + 12 * max_tokens + 64
+        self.staging = _PinnedRing(self.capacity, self.RING)
         self.dev = torch.zeros(self.capacity, dtype=torch.int32, device=device)
-        # error word and sampled tokens travel back together
+        max_tab = cache.tables.numel()
+        self.ctl_words = 2 + 9 * max_reqs + 2 * max_tab
+        self.ctl_ring = _PinnedRing(self.ctl_words, self.RING)
+        ctl = torch.zeros(self.ctl_words, dtype=torch.int32, device=device)
+        self.updates = ops.UpdateBuffers(ctl, max_reqs, max_tab, cache.slot_records, cache.tables)
+        self.dec_ring = _PinnedRing(max_reqs, self.RING)
+        self.dec_slots = torch.zeros(max_reqs, dtype=torch.int32, device=device)
+        self.dec_slots_host: list[int] | None = None       # what the device holds in dec_slots
+        self.dec_token_ids = torch.zeros(max_reqs, dtype=torch.int32, device=device)
+        self.dec_positions = torch.zeros(max_reqs, dtype=torch.int32, device=device)
+        self.dec_kv_len = torch.zeros(max_reqs, dtype=torch.int32, device=device)
+        self.iota = torch.arange(max_reqs, dtype=torch.int32, device=device)
+        self.ones = torch.ones(max_reqs, dtype=torch.int32, device=device)
+        self.empty = torch.zeros(0, dtype=torch.int32, device=device)
         self.result = torch.zeros(4 + max_tokens, dtype=torch.int32, device=device)
         self.result_hosts = [torch.zeros(4 + max_tokens, dtype=torch.int32).pin_memory()
                              for _ in range(self.RING)]
         self.result_turn = 0
+        self.h2d_bytes = 0          # bytes copied to the device so far, counted from the copies made
+        self.h2d_copies = 0
+        self.d2h_bytes = 0
+
+    def _copy(self, dst: torch.Tensor, ring: _PinnedRing, host: torch.Tensor, i: int, words: int) -> None:
+        dst[:words].copy_(host[:words], non_blocking=True)
+        ring.copied(i)
+        self.h2d_bytes += 4 * words
+        self.h2d_copies += 1
 
     def upload(self, arrays: list[np.ndarray]) -> list[torch.Tensor]:
         """Copy the arrays (int32 views) to the device in one transfer; returns device views."""
         total = sum(a.size for a in arrays)
         if total > self.capacity:
             raise ValueError(f"step needs {total} staging words, capacity is {self.capacity}")
-        i = self.turn
-        self.turn = (i + 1) % self.RING
-        if self.events[i] is not None:
-            self.events[i].synchronize()
-        host = self.hosts[i]
+        host, i = self.staging.next()
         host_np = host.numpy()
         views = []
         off = 0
@@ -135,15 +196,42 @@ class StepBuffers:
             views.append(self.dev[off:off + a.size])
             off += a.size
         if total:
-            self.dev[:total].copy_(host[:total], non_blocking=True)
-            if self.events[i] is None:
-                self.events[i] = torch.cuda.Event()
-            self.events[i].record()
+            self._copy(self.dev, self.staging, host, i, total)
         return views
+
+    def upload_updates(self, rec: list[int], tab: list[int]) -> None:
+        """Send the update list (record writes, table writes) for the next opening kernel."""
+        n_rec, n_tab = len(rec) // 9, len(tab) // 2
+        if n_rec > self.updates.max_rec or n_tab > self.updates.max_tab:
+            raise ValueError(f"{n_rec} record and {n_tab} table writes exceed the update list")
+        host, i = self.ctl_ring.next()
+        words = 2 + len(rec) + len(tab)
+        host_np = host.numpy()
+        host_np[0], host_np[1] = n_rec, n_tab
+        host_np[2:2 + len(rec)] = rec
+        host_np[2 + len(rec):words] = tab
+        self._copy(self.updates.ctl, self.ctl_ring, host, i, words)
+
+    def upload_dec_slots(self, slots: list[int]) -> None:
+        if slots == self.dec_slots_host:
+            return
+        host, i = self.dec_ring.next()
+        host.numpy()[:len(slots)] = slots
+        self._copy(self.dec_slots, self.dec_ring, host, i, len(slots))
+        self.dec_slots_host = list(slots)
 
 
 class StepFunction:
-    """Builds the batch description, runs the model and keeps the cache's lengths."""
+    """Builds the batch description, runs the model and keeps the cache's lengths.
+
+    Two kinds of step.  A *laid-out* step is described by the host: any mix of prompt portions
+    and single tokens; its description is uploaded and ``step_begin`` opens it.  A *state-driven*
+    step is one in which every request brings the token it sampled last and wants the next one
+    sampled: the device derives tokens, positions and lengths from the slot records
+    (``decode_begin``), the host uploads only what changed (the list of slots, new pages), and
+    because its launches are the same every time it is replayed from a CUDA graph where every
+    part of the model allows that (``GRAPH_SAFE``, see ``parts/base.py``).
+    """
 
     def __init__(self, model, cache: DeviceCache, max_step_tokens: int, max_seq_len: int,
                  use_graphs: bool = True):
@@ -157,49 +245,55 @@ class StepFunction:
         self.device = cache.device
         self.max_step_tokens = max_step_tokens
         self.max_seq_len = max_seq_len
-        self.buffers = StepBuffers(self.device, max_step_tokens, self.manager.max_slots)
+        self.buffers = StepBuffers(cache, max_step_tokens)
+        self.graph_safe = bool(model is not None and getattr(model, "graph_safe", lambda: False)())
         self.steps_run = 0
         self.graph_launches = 0      # kernels replayed from CUDA graphs (not counted by ops.LAUNCHES)
+        self.graph_replays = 0
 
     # ---- request lifetime ------------------------------------------------------------
-    def admit(self, req_id: Hashable) -> None:
+    def admit(self, req_id: Hashable, sampling: SamplingRow | None = None) -> None:
+        """Give the request a slot and start its record (greedy unless ``sampling`` says otherwise)."""
         self.manager.admit(req_id)
+        self.set_record(req_id, sampling or SamplingRow(), fresh=True)
+
+    def set_record(self, req_id: Hashable, sampling: SamplingRow, fresh: bool = False) -> None:
+        """Queue the request's record for the device: how it samples, its seed and the index of its
+        next draw; ``fresh`` also starts position and last token anew (a newly admitted request)."""
+        self.cache.write_record(self.manager.slot(req_id), temperature=sampling.temperature,
+                                top_k=sampling.top_k, top_p=sampling.top_p, seed=sampling.seed,
+                                counter=sampling.counter, fresh=fresh)
 
     def free(self, req_id: Hashable) -> None:
         self.manager.free(req_id)
 
+    def restart(self, req_id: Hashable) -> None:
+        """Preemption: pages back, position 0, slot and record kept."""
+        self.manager.restart(req_id)
+
     def length(self, req_id: Hashable) -> int:
         return self.manager.length(req_id)
 
-    # ---- the step ----------------------------------------------------------------------
-    def build(self, entries: Sequence[StepEntry], sampling: Sequence[SamplingRow] | None = None,
-              feed: Sequence[int] | None = None) -> tuple[StepBatch, dict]:
-        """Reserve pages, lay the batch out and upload its description.
+    def record(self, req_id: Hashable) -> dict:
+        """The request's slot record as the device holds it (synchronises)."""
+        return self.cache.read_record(self.manager.slot(req_id))
 
-        ``feed`` (with ``sampling`` only) has one number per entry: the place among the previous
-        step's sampled tokens whose token is this entry's single token, or -1 for an entry that
-        brings its tokens itself."""
+    # ---- the step ----------------------------------------------------------------------
+    def _reserve(self, entries: Sequence[StepEntry]) -> tuple[list[int], list[int], list[int]]:
+        """Slots, pages and the per-request numbers (tokens brought, start, slot) of a step."""
         if not entries:
             raise ValueError("a step needs at least one entry")
         seen = set()
-        tok_parts: list[np.ndarray] = []
-        pos_parts: list[np.ndarray] = []
-        req_parts: list[np.ndarray] = []
-        pf_parts: list[np.ndarray] = []
-        q_start: list[int] = []
-        q_len: list[int] = []
-        kv_len: list[int] = []
-        slots: list[int] = []
-        rows: list[int] = []
-        dec_items: list[int] = []
-        n_tokens = 0
-        for r, e in enumerate(entries):
+        counts, starts, slots = [], [], []
+        for e in entries:
             if e.req_id in seen:
                 raise ValueError(f"request {e.req_id!r} appears twice in one step")
             seen.add(e.req_id)
             if not self.manager.has(e.req_id):
+                if e.tokens is None:
+                    raise ValueError(f"request {e.req_id!r} is not live: it has no sampled token to go on from")
                 self.admit(e.req_id)
-            n = len(e.tokens)
+            n = e.count
             if n < 1:
                 raise ValueError(f"request {e.req_id!r} brings no tokens")
             start = self.manager.length(e.req_id)
@@ -207,145 +301,185 @@ class StepFunction:
                 raise ValueError(f"request {e.req_id!r} would reach {start + n} tokens, "
                                  f"beyond max_seq_len={self.max_seq_len}")
             self.manager.grow(e.req_id, start + n)
-            q_start.append(n_tokens)
-            q_len.append(n)
-            kv_len.append(start + n)
-            slots.append(self.manager.slot(e.req_id))
             for w in e.want:
                 if not 0 <= w < n:
                     raise ValueError(f"request {e.req_id!r} wants place {w} of {n} tokens")
-                rows.append(n_tokens + w)
-            tok_parts.append(np.asarray(e.tokens, dtype=np.int32))
-            pos_parts.append(np.arange(start, start + n, dtype=np.int32))
+            counts.append(n)
+            starts.append(start)
+            slots.append(self.manager.slot(e.req_id))
+        if sum(counts) > self.max_step_tokens:
+            raise ValueError(f"step of {sum(counts)} tokens exceeds max_step_tokens={self.max_step_tokens}")
+        return counts, starts, slots
+
+    def _send_updates(self) -> None:
+        self.cache.clear_fresh_state()
+        if self.cache.updates_pending:
+            self.buffers.upload_updates(*self.cache.take_updates())
+
+    def build(self, entries: Sequence[StepEntry]) -> StepBatch:
+        """Reserve pages, lay the batch out, upload its description and open the step on the device."""
+        q_len, starts, slots = self._reserve(entries)
+        n_reqs = len(entries)
+        q_start = [0] * n_reqs
+        n_tokens = 0
+        for r in range(n_reqs):
+            q_start[r] = n_tokens
+            n_tokens += q_len[r]
+        kv_len = [s + n for s, n in zip(starts, q_len)]
+        tok_parts, pos_parts, req_parts, pf_parts = [], [], [], []
+        rows, row_slot, dec_items, fed = [], [], [], []
+        for r, e in enumerate(entries):
+            n = q_len[r]
+            rows.extend(q_start[r] + w for w in e.want)
+            row_slot.extend(slots[r] for _ in e.want)
+            tok_parts.append(np.zeros(1, dtype=np.int32) if e.tokens is None
+                             else np.asarray(e.tokens, dtype=np.int32))
+            fed.append(1 if e.tokens is None else 0)
+            pos_parts.append(np.arange(starts[r], starts[r] + n, dtype=np.int32))
             req_parts.append(np.full(n, r, dtype=np.int32))
             if n == 1:
-                dec_items.append(n_tokens)
+                dec_items.append(q_start[r])
             else:
-                pf_parts.append(np.arange(n_tokens, n_tokens + n, dtype=np.int32))
-            n_tokens += n
-        if n_tokens > self.max_step_tokens:
-            raise ValueError(f"step of {n_tokens} tokens exceeds max_step_tokens={self.max_step_tokens}")
-        W = len(rows)
-        if sampling is not None and len(sampling) != W:
-            raise ValueError(f"{len(sampling)} sampling rows for {W} wanted places")
+                pf_parts.append(np.arange(q_start[r], q_start[r] + n, dtype=np.int32))
 
         i32 = lambda x: np.asarray(x, dtype=np.int32)
         cat = lambda parts: np.concatenate(parts) if parts else np.zeros(0, dtype=np.int32)
-        arrays = []
-        if sampling is not None:
-            feed_tok = np.full(n_tokens, -1, dtype=np.int32)
-            if feed is not None:
-                if len(feed) != len(entries):
-                    raise ValueError(f"{len(feed)} feed places for {len(entries)} entries")
-                for r, f in enumerate(feed):
-                    if f >= 0:
-                        if q_len[r] != 1:
-                            raise ValueError("only an entry of one token can take it from the previous step")
-                        feed_tok[q_start[r]] = f
-            seeds = np.asarray([s.seed & 0x7FFFFFFFFFFFFFFF for s in sampling], dtype=np.int64)
-            arrays += [seeds.view(np.int32), feed_tok,     # the 64-bit seeds first: they need an even offset
-                       np.asarray([s.temperature for s in sampling], dtype=np.float32).view(np.int32),
-                       np.asarray([s.top_p for s in sampling], dtype=np.float32).view(np.int32),
-                       i32([s.top_k for s in sampling]), i32([s.counter for s in sampling])]
 
         def tiles_of(rows_per_tile: int) -> list[int]:
             # (request row, tile index) of every request that brings more than one token; tiles
             # with the most keys to visit start first
-            tiles = [(kv_len[r] - q_len[r] + rows_per_tile * (t + 1), r, t) for r in range(len(entries))
+            tiles = [(kv_len[r] - q_len[r] + rows_per_tile * (t + 1), r, t) for r in range(n_reqs)
                      if q_len[r] > 1 for t in range(-(-q_len[r] // rows_per_tile))]
             tiles.sort(reverse=True)
             return [x for _, r, t in tiles for x in (r, t)]
 
-        arrays += [cat(tok_parts), cat(pos_parts), cat(req_parts), i32(q_start), i32(q_len), i32(kv_len),
-                   i32(slots), i32(rows), i32(dec_items), cat(pf_parts), i32(tiles_of(64)),
-                   i32(tiles_of(ops.PREFILL_TC_ROWS))]
+        arrays = [cat(tok_parts), cat(pos_parts), cat(req_parts), i32(q_start), i32(q_len), i32(kv_len),
+                  i32(slots), i32(rows), i32(dec_items), cat(pf_parts), i32(tiles_of(64)),
+                  i32(tiles_of(ops.PREFILL_TC_ROWS)), i32(fed), i32(row_slot)]
         views = self.buffers.upload(arrays)
-        samp = {}
-        if sampling is not None:
-            samp = {"feed": views[1], "fed": feed is not None,
-                    "seed": views[0].view(torch.int64), "temperature": views[2].view(torch.float32),
-                    "top_p": views[3].view(torch.float32), "top_k": views[4], "counter": views[5]}
-            views = views[6:]
-        self.cache.sync()
+        self._send_updates()
         batch = StepBatch(
-            n_tokens=n_tokens, n_reqs=len(entries), n_want=W,
+            n_tokens=n_tokens, n_reqs=n_reqs, n_want=len(rows),
             token_ids=views[0], positions=views[1], tok_req=views[2], req_q_start=views[3],
             req_q_len=views[4], req_kv_len=views[5], req_slot=views[6], logits_rows=views[7],
             decode_items=views[8], prefill_items=views[9], prefill_tiles=views[10], prefill_tiles_tc=views[11],
             cache=self.cache, err=self.buffers.result[:4],
             host_q_start=q_start, host_q_len=q_len, host_kv_len=kv_len, host_slot=slots,
-            max_q_len=max(q_len), max_kv_len=max(kv_len))
-        return batch, samp
+            max_q_len=max(q_len), max_kv_len=_bucket(max(kv_len)), row_slot=views[13])
+        ops.step_begin(self.buffers.updates, batch.token_ids, batch.req_q_start, batch.req_kv_len,
+                       batch.req_slot, views[12] if any(fed) else None, batch.err)
+        return batch
+
+    def _build_from_state(self, entries: Sequence[StepEntry]) -> StepBatch:
+        """The description of a state-driven step: tensors at fixed addresses that ``decode_begin``
+        fills on the device.  Uploads the list of slots if it differs from the device's, and the
+        pending updates if there are any."""
+        _, starts, slots = self._reserve(entries)
+        b, n = self.buffers, len(entries)
+        b.upload_dec_slots(slots)
+        self._send_updates()
+        return StepBatch(
+            n_tokens=n, n_reqs=n, n_want=n,
+            token_ids=b.dec_token_ids[:n], positions=b.dec_positions[:n], tok_req=b.iota[:n],
+            req_q_start=b.iota[:n], req_q_len=b.ones[:n], req_kv_len=b.dec_kv_len[:n],
+            req_slot=b.dec_slots[:n], logits_rows=b.iota[:n], decode_items=b.iota[:n],
+            prefill_items=b.empty, prefill_tiles=b.empty, prefill_tiles_tc=b.empty,
+            cache=self.cache, err=b.result[:4],
+            host_q_start=list(range(n)), host_q_len=[1] * n, host_kv_len=[s + 1 for s in starts],
+            host_slot=slots, max_q_len=1, max_kv_len=_bucket(max(starts) + 1), row_slot=b.dec_slots[:n])
 
     def finish(self, entries: Sequence[StepEntry]) -> None:
         """Advance the lengths and give back the pages that a window has passed."""
         for e in entries:
-            self.manager.advance(e.req_id, len(e.tokens))
+            self.manager.advance(e.req_id, e.count)
         self.steps_run += 1
 
     @torch.inference_mode()
     def run(self, entries: Sequence[StepEntry], check: bool = True) -> torch.Tensor:
         """Float32 logits ``[wanted, vocab]`` on the device, in the order of entries and ``want``."""
-        batch, _ = self.build(entries)
+        batch = self.build(entries)
         logits = self.model.forward(batch)
         self.finish(entries)
         if check:
             self.check_errors()
         return logits
 
-    def run_and_sample(self, entries: Sequence[StepEntry], sampling: Sequence[SamplingRow]) -> list[int]:
+    def run_and_sample(self, entries: Sequence[StepEntry],
+                       sampling: Sequence[SamplingRow] | None = None) -> list[int]:
         """One token per wanted place, sampled on the device; one copy back for tokens and errors."""
         return self.collect(self.launch_and_sample(entries, sampling))
 
     @torch.inference_mode()
-    def launch_and_sample(self, entries: Sequence[StepEntry], sampling: Sequence[SamplingRow],
-                          feed: Sequence[int] | None = None) -> PendingStep:
-        """Start a step that samples one token per wanted place on the device; ``collect`` reads them.
+    def launch_and_sample(self, entries: Sequence[StepEntry],
+                          sampling: Sequence[SamplingRow] | None = None) -> PendingStep:
+        """Start a step that samples one token at every wanted place (at most one per entry) with
+        the parameters, seed and counter of the request's slot record; ``collect`` reads them.
 
-        A step in which every request brings exactly one token and wants it sampled has the
-        same launches every time, so it is captured into a CUDA graph the second time its shape
-        (batch size, bucket of the longest context) is seen and replayed from then on: the
-        description of the step is uploaded outside the graph into buffers at fixed addresses.
+        ``sampling`` is a shorthand for callers that keep the parameters themselves: one row per
+        wanted place, written into those requests' records before the step (their counters
+        included).  The engine instead writes a record once, when a request is admitted.
 
-        With ``feed`` (see ``build``) single tokens come from the previous step's sampled tokens
-        on the device, so the step can be launched before that step has been collected: the
-        device then never waits for the host between two steps.  At most two launched steps may
-        be waiting to be collected, and they are collected in the order of their launch.
+        The step may be launched before the step before it has been collected: an entry with
+        ``tokens=None`` takes the token it sampled there from its record, so the device never
+        waits for the host between two steps.  At most two launched steps may be waiting to be
+        collected, and they are collected in the order of their launch.
         """
-        batch, samp = self.build(entries, sampling, feed)
-        W = batch.n_want
+        if any(len(e.want) > 1 for e in entries):
+            raise ValueError("a sampling step takes at most one wanted place per request")
+        if sampling is not None:
+            wanting = [e for e in entries if e.want]
+            if len(sampling) != len(wanting):
+                raise ValueError(f"{len(sampling)} sampling rows for {len(wanting)} wanted places")
+            for e, row in zip(wanting, sampling):
+                if not self.manager.has(e.req_id):
+                    self.admit(e.req_id, row)
+                else:
+                    self.set_record(e.req_id, row)
         res = self.buffers.result
-        graphable = (self.use_graphs and batch.max_q_len == 1 and W == batch.n_tokens)
-        if graphable:
-            bucket = 256
-            while bucket < batch.max_kv_len:
-                bucket *= 2
-            batch.max_kv_len = bucket        # kernels size their grids from the bucket
-            key = (batch.n_tokens, bucket)
-            graph = self._graphs.get(key)
-            if graph is None and self._graph_seen.get(key, 0) >= 1:
-                graph = self._capture(key, batch, samp)
-            if graph is not None:
-                graph["graph"].replay()
-                self.graph_launches += graph["kernels"]
-            else:
-                self._graph_seen[key] = self._graph_seen.get(key, 0) + 1
-                graphable = False
-        if not graphable:
-            if samp["fed"]:
-                ops.feed_tokens(batch.token_ids, samp["feed"], res[4:], batch.err)
+        if all(e.tokens is None and len(e.want) == 1 for e in entries):
+            batch = self._build_from_state(entries)
+            self._run_from_state(batch)
+        else:
+            batch = self.build(entries)
             logits = self.model.forward(batch)
-            if W:
-                ops.sample(logits, samp["temperature"], samp["top_k"], samp["top_p"], samp["seed"],
-                           samp["counter"], res[4:4 + W])
+            if batch.n_want:
+                ops.sample_slots(logits, self.cache.slot_records, batch.row_slot, res[4:4 + batch.n_want],
+                                 batch.err)
+        W = batch.n_want
         self.finish(entries)
         bufs = self.buffers
         host = bufs.result_hosts[bufs.result_turn]
         bufs.result_turn = (bufs.result_turn + 1) % bufs.RING
         host[:4 + W].copy_(res[:4 + W], non_blocking=True)
+        bufs.d2h_bytes += 4 * (4 + W)
         done = torch.cuda.Event()
         done.record()
         return PendingStep(W, host, done)
+
+    def _from_state_launches(self, batch: StepBatch) -> torch.Tensor:
+        b, n = self.buffers, batch.n_reqs
+        ops.decode_begin(b.updates, b.dec_slots, n, self.max_seq_len, b.dec_token_ids, b.dec_positions,
+                         b.dec_kv_len, batch.err)
+        logits = self.model.forward(batch)
+        ops.sample_slots(logits, self.cache.slot_records, batch.row_slot, b.result[4:4 + n], batch.err)
+        return logits
+
+    def _run_from_state(self, batch: StepBatch) -> None:
+        """A state-driven step: replayed from its CUDA graph where the model allows it (captured
+        the second time a shape, batch size and bucket of the longest context, is seen), else
+        launched kernel by kernel."""
+        if self.use_graphs and self.graph_safe:
+            key = (batch.n_tokens, batch.max_kv_len)     # kernels size their grids from the bucket
+            graph = self._graphs.get(key)
+            if graph is None and self._graph_seen.get(key, 0) >= 1:
+                graph = self._capture(key, batch)
+            if graph is not None:
+                graph["graph"].replay()
+                self.graph_launches += graph["kernels"]
+                self.graph_replays += 1
+                return
+            self._graph_seen[key] = self._graph_seen.get(key, 0) + 1
+        self._from_state_launches(batch)
 
     def collect(self, pending: PendingStep) -> list[int]:
         """Wait for a launched step and return its sampled tokens; raises on a kernel error."""
@@ -353,20 +487,15 @@ class StepFunction:
         self._raise_on_error(pending.host[:4].tolist())
         return pending.host[4:4 + pending.n_want].tolist()
 
-    def _capture(self, key, batch: StepBatch, samp: dict) -> dict:
-        """Record the decode step of this shape; its launches are replayed, not run, here."""
+    def _capture(self, key, batch: StepBatch) -> dict:
+        """Record the state-driven step of this shape; its launches are replayed, not run, here."""
         if self._graph_pool is None:
             self._graph_pool = torch.cuda.graph_pool_handle()
-        W = batch.n_want
         graph = torch.cuda.CUDAGraph()
         before = ops.LAUNCHES
         torch.cuda.synchronize()
         with torch.cuda.graph(graph, pool=self._graph_pool):
-            # tokens that the previous step sampled (feed >= 0) take their places first
-            ops.feed_tokens(batch.token_ids, samp["feed"], self.buffers.result[4:], batch.err)
-            logits = self.model.forward(batch)
-            ops.sample(logits, samp["temperature"], samp["top_k"], samp["top_p"], samp["seed"],
-                       samp["counter"], self.buffers.result[4:4 + W])
+            logits = self._from_state_launches(batch)
         kernels = ops.LAUNCHES - before
         ops.LAUNCHES = before
         entry = {"graph": graph, "kernels": kernels, "logits": logits}

@@ -6,8 +6,9 @@ from dataclasses import dataclass
 
 import torch
 
-from ..parts.base import BLOCKS, NORMS, OwedNorm, Runtime, TensorReq
-from ..parts.embedding import Embedding, EmbeddingSpec, Head, HeadSpec
+from ..parts import embedding as _builtin_embedding   # registers the built-in embedding and head
+from ..parts.base import (BLOCKS, EMBEDDINGS, HEADS, NORMS, POSITIONS, OwedNorm, Runtime, TensorReq, graph_safe,
+                          weight_bytes)
 
 
 @dataclass(frozen=True)
@@ -26,12 +27,17 @@ class LayerCall:
 
 @dataclass(frozen=True)
 class ModelSpec:
-    embedding: EmbeddingSpec
+    """A model as data.  Every field but the schedule is a spec with a ``kind`` that one of the
+    registries of ``parts/base.py`` resolves; ``embedding_position`` is the seat of a position
+    encoding that is added to the embedded rows (``None``: the mixers carry the positions)."""
+
+    embedding: object                  # an embedding spec (vocab_size, hidden_size, kind, ...)
     blocks: tuple                      # block specs, each with a unique ``name``
     schedule: tuple                    # LayerCall entries, in execution order
     final_norm: object
     final_norm_name: str
-    head: HeadSpec
+    head: object                       # a head spec (vocab_size, kind, ...)
+    embedding_position: object = None
 
     def __post_init__(self) -> None:
         names = [b.name for b in self.blocks]
@@ -49,22 +55,48 @@ class DecoderModel:
     def __init__(self, spec: ModelSpec, tensors: dict[str, torch.Tensor], rt: Runtime):
         self.spec = spec
         self.rt = rt
-        self.embedding = Embedding(spec.embedding, tensors, rt)
+        self.embedding = EMBEDDINGS.get(spec.embedding.kind)(spec.embedding, tensors, rt)
+        self.embedding_position = None
+        if spec.embedding_position is not None:
+            pos = spec.embedding_position
+            self.embedding_position = POSITIONS.get(pos.kind)(pos, tensors, rt)
+            if not hasattr(self.embedding_position, "add_to_embedding"):
+                raise ValueError(f"position encoding {pos.kind!r} cannot sit at the embedding: "
+                                 f"it has no add_to_embedding")
         self.blocks = {b.name: BLOCKS.get(b.kind)(b, tensors, rt) for b in spec.blocks}
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, spec.final_norm_name,
                                                           tensors, rt)
-        self.head = Head(spec.head, self.embedding, tensors, rt)
+        self.head = HEADS.get(spec.head.kind)(spec.head, self.embedding, tensors, rt)
 
     @staticmethod
     def expected_tensors(spec: ModelSpec) -> dict[str, TensorReq]:
         out: dict[str, TensorReq] = {}
-        out.update(Embedding.expected_tensors(spec.embedding))
+        out.update(EMBEDDINGS.get(spec.embedding.kind).expected_tensors(spec.embedding))
+        if spec.embedding_position is not None:
+            pos = spec.embedding_position
+            out.update(POSITIONS.get(pos.kind).expected_tensors(pos))
         for b in spec.blocks:
             out.update(BLOCKS.get(b.kind).expected_tensors(b))
         out.update(NORMS.get(spec.final_norm.kind).expected_tensors(spec.final_norm,
                                                                     spec.final_norm_name))
-        out.update(Head.expected_tensors(spec.head))
+        out.update(HEADS.get(spec.head.kind).expected_tensors(spec.head))
         return out
+
+    def parts(self) -> list:
+        """Every part a step runs, a block once per call of the schedule."""
+        out = [self.embedding] + ([self.embedding_position] if self.embedding_position is not None else [])
+        out += [self.blocks[call.block] for call in self.spec.schedule]
+        return out + [self.final_norm, self.head]
+
+    def graph_safe(self) -> bool:
+        """Whether a step of single next tokens may be replayed from a CUDA graph: every part
+        has to declare it (``GRAPH_SAFE`` in ``parts/base.py``)."""
+        return graph_safe(*self.parts())
+
+    def step_weight_bytes(self) -> int:
+        """Bytes of weights that one step reads in full: every scheduled call's, the final norm's
+        and the head's (what the parts report through ``weight_bytes``)."""
+        return weight_bytes(*self.parts())
 
     def cache_needs(self) -> dict[str, object]:
         """Cache key -> need, checked for agreement between calls that share a key."""
@@ -85,6 +117,8 @@ class DecoderModel:
     def forward(self, step) -> torch.Tensor:
         """Float32 logits ``[len(step.logits_rows), vocab]`` for the rows asked for."""
         resid = self.embedding.forward(step)
+        if self.embedding_position is not None:
+            self.embedding_position.add_to_embedding(resid, step)
         pending = None
         schedule = self.spec.schedule
         for i, call in enumerate(schedule):
@@ -102,4 +136,6 @@ class DecoderModel:
         # every request brings one token and wants it: the wanted rows are all rows, in order
         all_rows = step.n_want == step.n_tokens and step.max_q_len == 1
         h = self.final_norm.add_norm(resid, pending, rows=None if all_rows and isinstance(pending, OwedNorm) else step.logits_rows)
+        if isinstance(h, OwedNorm) and not getattr(self.head, "TAKES_OWED_NORM", False):
+            h = h.materialize()
         return self.head.forward(h, step.err)

@@ -30,8 +30,11 @@ def parse_config(raw: Mapping[str, Any], eos_token_ids=None) -> ModelConfig:
     return cfg
 
 
-def model_spec(cfg: ModelConfig) -> ModelSpec:
-    """Blocks and schedule of a configuration: every layer once, each with a cache of its own."""
+def model_spec(cfg: ModelConfig, window: int | None = None) -> ModelSpec:
+    """Blocks and schedule of a configuration: every layer once, each with a cache of its own.
+
+    ``window`` is the engine-wide option (``attention_policy="window:W"``): every layer sees
+    the last ``W`` positions only, whatever the configuration says about windows."""
     blocks = []
     schedule = []
     for i in range(cfg.num_layers):
@@ -44,7 +47,7 @@ def model_spec(cfg: ModelConfig) -> ModelSpec:
             head_dim=cfg.head_dim,
             position=RopeSpec(cfg.head_dim, cfg.rope_theta),
             qk_norm_eps=cfg.rms_norm_eps if cfg.use_qk_norm else None,
-            window=cfg.layer_window(i),
+            window=window if window is not None else cfg.layer_window(i),
         )
         blocks.append(PreNormBlockSpec(
             name=f"layers.{i}",

@@ -9,7 +9,8 @@ import torch
 
 from ..cache.manager import KVPagesNeed
 from ..csrc import ops
-from .base import MIXERS, POSITIONS, SWAPPED_GEMM_MAX_TOKENS, OwedNorm, Runtime, TensorReq, linear
+from .base import (MIXERS, POSITIONS, SWAPPED_GEMM_MAX_TOKENS, OwedNorm, Runtime, TensorReq, graph_safe,
+                   linear, tensor_bytes)
 
 
 @dataclass(frozen=True)
@@ -59,7 +60,10 @@ class Attention:
         self.w_o = tensors[prefix + "o_proj.weight"]
         self.q_norm_w = tensors.get(prefix + "q_norm.weight") if spec.qk_norm_eps is not None else None
         self.k_norm_w = tensors.get(prefix + "k_norm.weight") if spec.qk_norm_eps is not None else None
-        self.position = POSITIONS.get(spec.position.kind)(spec.position, rt)
+        self.position = POSITIONS.get(spec.position.kind)(spec.position, tensors, rt)
+        if not hasattr(self.position, "rotary_table"):
+            raise ValueError(f"position encoding {spec.position.kind!r} does not rotate queries and keys "
+                             f"(no rotary_table); give it the model's embedding_position seat instead")
         self.scale = spec.softmax_scale if spec.softmax_scale is not None else spec.head_dim ** -0.5
 
     @staticmethod
@@ -76,10 +80,17 @@ class Attention:
             out[prefix + "q_norm.weight"] = TensorReq((d,), role="vector")
             if spec.own_kv:
                 out[prefix + "k_norm.weight"] = TensorReq((d,), role="vector")
+        out.update(POSITIONS.get(spec.position.kind).expected_tensors(spec.position))
         return out
 
     def cache_need(self) -> KVPagesNeed:
         return KVPagesNeed(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
+
+    def GRAPH_SAFE(self) -> bool:
+        return graph_safe(self.position)
+
+    def weight_bytes(self) -> int:
+        return tensor_bytes(self.w_qkv, self.w_o, self.q_norm_w, self.k_norm_w)
 
     TAKES_OWED_NORM = True     # the q|k|v product pays an owed norm scale in its epilogue
     TAKES_THEN_NORM = True     # the output product can add itself to the residual stream

@@ -11,8 +11,12 @@ role           interface of the registered class
 =============  ==========================================================
 norm           ``expected_tensors(spec, name)``, ``__init__(spec, name, tensors, rt)``,
                ``add_norm(resid, delta, rows=None) -> normed``
-position       ``__init__(spec, rt)``, ``rotary_table(step) -> (table | None, rotary_dim)`` with
-               ``table`` float32 ``[tokens, rotary_dim / 2, 2]`` of (cos, sin) per token
+position       ``expected_tensors(spec)``, ``__init__(spec, tensors, rt)`` and one or both of:
+               ``rotary_table(step) -> (table | None, rotary_dim)`` with ``table`` float32
+               ``[tokens, rotary_dim / 2, 2]`` of (cos, sin) per token, for mixers that rotate
+               queries and keys; ``add_to_embedding(resid, step)``, which adds an encoding of
+               ``step.positions`` to the float32 residual rows in place (absolute encodings:
+               a learned table, sinusoids), for the model's ``embedding_position`` seat
 mixer          ``expected_tensors(spec, prefix)``, ``__init__(spec, prefix, tensors, rt)``,
                ``cache_need() -> KVPagesNeed | StateNeed | None``,
                ``forward(h, step, cache_view) -> [N, hidden]``
@@ -20,10 +24,27 @@ feed_forward   ``expected_tensors(spec, prefix)``, ``__init__(spec, prefix, tens
                ``forward(h, step) -> [N, hidden]``
 block          ``expected_tensors(spec)``, ``__init__(spec, tensors, rt)``,
                ``cache_need()``, ``forward(resid, pending, step, cache_view) -> (resid, pending)``
+embedding      ``expected_tensors(spec)``, ``__init__(spec, tensors, rt)``,
+               ``forward(step) -> float32 residual rows [N, hidden]``, attribute ``weight``
+head           ``expected_tensors(spec)``, ``__init__(spec, embedding part, tensors, rt)``,
+               ``forward(h, err) -> float32 logits [rows, vocab]``
 =============  ==========================================================
 
 No part knows which model it is in: it sees its spec, its tensors, the step's
 batch description and the view of its own cache.
+
+**Two declarations every part may make** (both optional, both read with ``getattr``):
+
+``GRAPH_SAFE = True`` says that the part's ``forward`` launches the same kernels with the same
+arguments whatever the step's numbers are: it reads the step through the device tensors of the
+batch description only, never through ``step.host_*``, ``step.max_kv_len`` apart (a bucket under
+replay), takes no decision on values it would have to read back from the device, and keeps no
+host-side state that changes from step to step.  A step of single next tokens is replayed from a
+CUDA graph only if every part of the model says so; a model with one part that does not
+(the default) runs such steps kernel by kernel, with fresh host values every time.
+
+``weight_bytes()`` returns the bytes of the tensors that one call of the part reads in full
+(an embedding table, read by row, reports 0); measurements sum it over the schedule.
 
 **Owed norms.**  In bfloat16 steps of few tokens the kernel of a product that ends a branch can
 add its sums to the residual stream itself and hand on the input of the *next* norm with the
@@ -110,6 +131,29 @@ POSITIONS = Registry("position")
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed_forward")
 BLOCKS = Registry("block")
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("head")
+
+
+def graph_safe(*parts: Any) -> bool:
+    """Whether every given part declares ``GRAPH_SAFE`` (an attribute, or a method for a part
+    made of parts)."""
+    for part in parts:
+        flag = getattr(part, "GRAPH_SAFE", False)
+        if callable(flag):
+            flag = flag()
+        if not flag:
+            return False
+    return True
+
+
+def weight_bytes(*parts: Any) -> int:
+    """Sum of ``weight_bytes()`` over the parts that report it."""
+    return sum(int(part.weight_bytes()) for part in parts if hasattr(part, "weight_bytes"))
+
+
+def tensor_bytes(*tensors: Any) -> int:
+    return sum(t.numel() * t.element_size() for t in tensors if t is not None)
 
 
 SWAPPED_GEMM_MAX_TOKENS = 64

@@ -6,7 +6,7 @@ from dataclasses import dataclass
 
 import torch
 
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, OwedNorm, Runtime, TensorReq
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, OwedNorm, Runtime, TensorReq, graph_safe, weight_bytes
 
 
 @dataclass(frozen=True)
@@ -67,6 +67,12 @@ class PreNormBlock:
 
     def cache_need(self):
         return self.mixer.cache_need()
+
+    def GRAPH_SAFE(self) -> bool:
+        return graph_safe(self.norm1, self.mixer, self.norm2, self.feed_forward)
+
+    def weight_bytes(self) -> int:
+        return weight_bytes(self.norm1, self.mixer, self.norm2, self.feed_forward)
 
     @property
     def entry_norm(self):

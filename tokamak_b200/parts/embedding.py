@@ -7,7 +7,7 @@ from dataclasses import dataclass
 import torch
 
 from ..csrc import ops
-from .base import Runtime, TensorReq, linear, sum_parts
+from .base import EMBEDDINGS, HEADS, Runtime, TensorReq, linear, sum_parts, tensor_bytes
 
 
 @dataclass(frozen=True)
@@ -15,6 +15,7 @@ class EmbeddingSpec:
     vocab_size: int
     hidden_size: int
     name: str = "model.embed_tokens.weight"
+    kind: str = "embedding"
 
 
 @dataclass(frozen=True)
@@ -26,11 +27,18 @@ class HeadSpec:
     hidden_size: int
     tied: bool
     name: str = "lm_head.weight"
+    kind: str = "linear_head"
 
 
+@EMBEDDINGS.register("embedding")
 class Embedding:
     """Row lookup without scaling (src/tokamak/model/transformer.py:140); the rows
     are widened into the float32 residual stream."""
+
+    GRAPH_SAFE = True
+
+    def weight_bytes(self) -> int:
+        return 0          # read by row: a step touches one row per token
 
     def __init__(self, spec: EmbeddingSpec, tensors: dict[str, torch.Tensor], rt: Runtime):
         self.spec = spec
@@ -47,13 +55,19 @@ class Embedding:
         return resid
 
 
+@HEADS.register("linear_head")
 class Head:
     """Logits in float32 for the rows that were asked for
     (src/tokamak/model/transformer.py:173-176).  In bfloat16 the product keeps its
     32-bit accumulators rather than rounding them to bfloat16 first."""
 
-    def __init__(self, spec: HeadSpec, embedding: Embedding, tensors: dict[str, torch.Tensor],
-                 rt: Runtime):
+    GRAPH_SAFE = True
+    TAKES_OWED_NORM = True     # the product pays an owed norm scale in its epilogue
+
+    def weight_bytes(self) -> int:
+        return tensor_bytes(self.weight)
+
+    def __init__(self, spec: HeadSpec, embedding, tensors: dict[str, torch.Tensor], rt: Runtime):
         self.spec = spec
         self.weight = embedding.weight if spec.tied else tensors[spec.name]
 

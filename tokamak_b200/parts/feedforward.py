@@ -7,7 +7,7 @@ from dataclasses import dataclass
 import torch
 
 from ..csrc import ops
-from .base import FEED_FORWARDS, SWAPPED_GEMM_MAX_TOKENS, OwedNorm, Runtime, TensorReq, linear
+from .base import FEED_FORWARDS, SWAPPED_GEMM_MAX_TOKENS, OwedNorm, Runtime, TensorReq, linear, tensor_bytes
 
 
 @dataclass(frozen=True)
@@ -52,6 +52,11 @@ class SwiGLU:
             prefix + "up_proj.weight": TensorReq((i, h)),
             prefix + "down_proj.weight": TensorReq((h, i)),
         }
+
+    GRAPH_SAFE = True
+
+    def weight_bytes(self) -> int:
+        return tensor_bytes(self.w_gate_up, self.w_down)
 
     TAKES_OWED_NORM = True     # the gate/up product pays an owed norm scale in its epilogue
     TAKES_THEN_NORM = True     # the down product can add itself to the residual stream

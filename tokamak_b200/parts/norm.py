@@ -26,6 +26,8 @@ class RMSNorm:
     output to it (a 32-bit sum) and then normalises the sum, in one kernel.
     """
 
+    GRAPH_SAFE = True
+
     def __init__(self, spec: RMSNormSpec, name: str, tensors: dict[str, torch.Tensor], rt: Runtime):
         self.spec = spec
         self.rt = rt
@@ -34,6 +36,9 @@ class RMSNorm:
     @staticmethod
     def expected_tensors(spec: RMSNormSpec, name: str) -> dict[str, TensorReq]:
         return {name: TensorReq((spec.dim,), role="vector")}
+
+    def weight_bytes(self) -> int:
+        return self.weight.numel() * self.weight.element_size()
 
     def owed_norm_params(self) -> tuple[torch.Tensor, float] | None:
         """Weight and eps for a product kernel that prepares this norm's input itself."""

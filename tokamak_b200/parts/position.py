@@ -1,5 +1,6 @@
-"""Position encodings.  A position part hands the mixer a table of (cos, sin) pairs for the
-tokens of the step; the rotation itself happens in the mixer's fused kernel."""
+"""Position encodings.  A rotary position part hands the mixer a table of (cos, sin) pairs for
+the tokens of the step; the rotation itself happens in the mixer's fused kernel.  An absolute
+encoding would instead implement ``add_to_embedding`` (see ``parts/base.py``)."""
 
 from __future__ import annotations
 
@@ -34,13 +35,19 @@ class RopeNeox:
     layer with the same spec reads the same table.
     """
 
-    def __init__(self, spec: RopeSpec, rt: Runtime):
+    GRAPH_SAFE = True
+
+    def __init__(self, spec: RopeSpec, tensors: dict, rt: Runtime):
         if spec.head_dim % 2:
             raise ValueError(f"rotary embedding needs an even head_dim, got {spec.head_dim}")
         self.spec = spec
         inv_freq = 1.0 / (spec.theta ** (torch.arange(0, spec.head_dim, 2, dtype=torch.float32)
                                          / spec.head_dim))
         self.inv_freq = inv_freq.to(rt.device)
+
+    @staticmethod
+    def expected_tensors(spec: RopeSpec) -> dict:
+        return {}
 
     def rotary_table(self, step) -> tuple[torch.Tensor | None, int]:
         """``([tokens, head_dim / 2, 2] float32 of (cos, sin), rotary_dim)`` for the step's tokens."""
@@ -56,8 +63,14 @@ class RopeNeox:
 class NoPosition:
     """No position encoding: queries and keys pass unrotated."""
 
-    def __init__(self, spec: NoPositionSpec, rt: Runtime):
+    GRAPH_SAFE = True
+
+    def __init__(self, spec: NoPositionSpec, tensors: dict, rt: Runtime):
         self.spec = spec
+
+    @staticmethod
+    def expected_tensors(spec: NoPositionSpec) -> dict:
+        return {}
 
     def rotary_table(self, step) -> tuple[torch.Tensor | None, int]:
         return None, 0

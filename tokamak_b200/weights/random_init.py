@@ -52,8 +52,7 @@ def write_random_model(folder: str | Path, config_json: Mapping, seed: int, std:
     folder = Path(folder)
     folder.mkdir(parents=True, exist_ok=True)
     arch = architecture_of(config_json)
-    cfg = arch.parse_config(config_json)
-    expected = DecoderModel.expected_tensors(arch.model_spec(cfg))
+    expected = DecoderModel.expected_tensors(arch.build_spec(arch.parse(config_json)))
     tensors = random_tensors(expected, seed, std, norm_std, dtype)
     raw = dict(config_json)
     raw.setdefault("torch_dtype", "bfloat16" if dtype == torch.bfloat16 else "float32")
