@@ -283,7 +283,7 @@ def _toy_architecture():
         eos_token_ids: tuple = ()
 
     def parse_config(raw, eos_token_ids=None):
-        return ToyConfig(**{k: v for k, v in raw.items() if k != "architectures"},
+        return ToyConfig(**{k: raw[k] for k in TOY_CONFIG if k != "architectures"},
                          eos_token_ids=tuple(eos_token_ids or ()))
 
     def model_spec(cfg):
@@ -465,7 +465,7 @@ def _routed_architecture():
         eos_token_ids: tuple = ()
 
     def parse_config(raw, eos_token_ids=None):
-        return Config(**{k: v for k, v in raw.items() if k != "architectures"},
+        return Config(**{k: raw[k] for k in ROUTED_CONFIG if k != "architectures"},
                       eos_token_ids=tuple(eos_token_ids or ()))
 
     def model_spec(cfg):
@@ -730,7 +730,7 @@ def _absolute_architecture():
         eos_token_ids: tuple = ()
 
     def parse_config(raw, eos_token_ids=None):
-        return Config(**{k: v for k, v in raw.items() if k != "architectures"})
+        return Config(**{k: raw[k] for k in ABS_CONFIG if k != "architectures"})
 
     def model_spec(cfg):
         H, norm = cfg.hidden_size, RMSNormSpec(cfg.hidden_size, cfg.eps)
