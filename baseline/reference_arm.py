@@ -136,8 +136,9 @@ def _decode_run(llm, SamplingParams, batch: int, ctx: int, steps: int, vocab: in
 
 def run(cfg: dict, model_name: str, batch: int, ctx: int, prefill_tokens: int, steps: int, warmup: int,
         points: tuple[int, ...] = (1, 64), device: str = "cuda", dtype: str = "bfloat16",
-        clock_sampler=None, keep_folder: Path | None = None) -> dict:
-    """Measure the reference and return the bench line (``impl: reference``)."""
+        clock_sampler=None, keep_folder: Path | None = None, config: dict | None = None) -> dict:
+    """Measure the reference and return the bench line (``impl: reference``).  ``config`` is the
+    record of sizes that the caller prints for the same run of its own arm."""
     sys.path.insert(0, str(REF_DIR))
     import torch
     from tokamak import LLM, SamplingParams
@@ -190,15 +191,16 @@ def run(cfg: dict, model_name: str, batch: int, ctx: int, prefill_tokens: int, s
         "warmup": max(3, warmup), "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if dtype == "bfloat16" else dtype,
         "data": "synthetic: seeded random weights N(0, 0.02), uniform random token ids",
-        "config": {
+        "config": dict(config) if config is not None else {
             "model": f"{model_name} layer sizes", "layers": cfg["num_hidden_layers"],
             "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
             "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
             "intermediate": cfg["intermediate_size"], "vocab": vocab, "global_batch": batch, "seq_len": ctx,
             "prefill_tokens": prefill_tokens, "kv_block": 16, "parallelism": "single GPU",
-            "attention_backend": str(llm.attention_backend),
-            "timing": "the reference's own timestamps around its decode steps (tokens on the host)",
         },
+        "prompt_tokens": main["prompt_len"],
+        "attention_backend": str(llm.attention_backend),
+        "timing": "the reference's own timestamps around its decode steps (tokens on the host)",
         # the reference has one way in and out: token ids from the host, sampled tokens read back every step
         "e2e": {"value": round(main["tok_s"], 2), "unit": "tokens/s", "ms_per_step": round(main["ms_per_step"], 2)},
         "prefill": {"value": round(prefill_tokens / prefill_s, 1), "tokens": prefill_tokens,

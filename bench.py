@@ -47,6 +47,7 @@ QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention
 SIZES = {"8b": ("Qwen3-8B", QWEN3_8B), "14b": ("Qwen3-14B", QWEN3_14B), "32b": ("Qwen3-32B", QWEN3_32B)}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
+PROMPT_PORTION = PREFILL_TOKENS
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -114,6 +115,22 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+def bench_config(model_name: str, raw: dict, layers_of_model: int, batch: int, ctx: int, pf_tokens: int,
+                 peaks_source: str) -> dict:
+    """The ``config`` record of the bench line: every size, flat.  Both arms (this engine and the
+    reference) print the same record for the same run."""
+    return {
+        "model": f"{model_name} layer sizes", "layers": raw["num_hidden_layers"], "layers_of_model": layers_of_model,
+        "hidden": raw["hidden_size"], "q_heads": raw["num_attention_heads"],
+        "kv_heads": raw["num_key_value_heads"], "head_dim": raw["head_dim"],
+        "intermediate": raw["intermediate_size"], "vocab": raw["vocab_size"], "rope_theta": raw["rope_theta"],
+        "rms_norm_eps": raw["rms_norm_eps"], "tied_head": bool(raw.get("tie_word_embeddings", False)),
+        "global_batch": batch, "seq_len": ctx, "prefill_tokens": pf_tokens, "kv_block": 16,
+        "parallelism": "single GPU", "l2": "inputs larger than L2 (weights read every step)",
+        "peaks": peaks_source,
+    }
+
+
 def weight_bytes(core) -> int:
     """Bytes of every weight a decode step reads once, as the model's parts report them (the
     embedding table is read by row only and reports nothing)."""
@@ -132,14 +149,15 @@ def step_flops(cfg, n_layers: int, tokens: int, ctx_start: int = 0) -> float:
 
 
 def fill_context(core, req_ids, length: int, vocab: int, seed: int) -> None:
-    """Put ``length`` random tokens of every request into the cache, 2,048 tokens a step."""
+    """Put ``length`` random tokens of every request into the cache, in prompts and prompt
+    portions of ``PROMPT_PORTION`` tokens a step (2,048 unless ``--prompt-tokens`` says otherwise)."""
     import torch
     from tokamak_b200.engine.step import StepEntry
     gen = torch.Generator().manual_seed(seed)
     for rid in req_ids:
         toks = torch.randint(0, vocab, (length,), generator=gen).tolist()
-        for s in range(0, length, PREFILL_TOKENS):
-            core.step.run([StepEntry(rid, toks[s:s + PREFILL_TOKENS], [])], check=False)
+        for s in range(0, length, PROMPT_PORTION):
+            core.step.run([StepEntry(rid, toks[s:s + PROMPT_PORTION], [])], check=False)
     core.step.check_errors()
 
 
@@ -553,13 +571,14 @@ def reference_main(args) -> int:
     if args.layers:
         raw["num_hidden_layers"] = args.layers
     try:
+        config = bench_config(model_name, raw, sizes["num_hidden_layers"], args.batch, args.seq_len,
+                              args.prefill_tokens, load_peaks()["source"])
         line = reference_arm.run(raw, model_name, args.batch, args.seq_len, args.prefill_tokens, max(1, args.steps),
-                                 max(3, args.warmup), points=() if args.skip_points else (1, 64),
-                                 clock_sampler=ClockSampler(0))
+                                 max(3, args.warmup), points=() if args.skip_points else tuple(args.points),
+                                 clock_sampler=ClockSampler(0), config=config)
     except Exception as err:    # the reference's failure is reported, never hidden behind our numbers
         print(json.dumps({"impl": "reference", "unavailable": f"{type(err).__name__}: {str(err)[:300]}"}))
         return 0
-    line["config"]["layers_of_model"] = sizes["num_hidden_layers"]
     print(json.dumps(line))
     return 0
 
@@ -594,6 +613,9 @@ def main() -> int:
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--seq-len", type=int, default=CONTEXT, help="context length at which the decode steps run")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="length of the timed prompt")
+    ap.add_argument("--prompt-tokens", type=int, default=None,
+                    help="length of the random prompts (and prompt portions) that fill the contexts before the "
+                         "decode steps are timed (default: --prefill-tokens)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -630,6 +652,8 @@ def main() -> int:
     vocab = raw["vocab_size"]
     peaks = load_peaks()
     ctx, pf_tokens = args.seq_len, args.prefill_tokens      # the defaults unless asked otherwise
+    global PROMPT_PORTION
+    PROMPT_PORTION = args.prompt_tokens or pf_tokens
     max_batch = max([args.batch, 1] + ([] if args.skip_points else list(args.points)))
     core = random_core(raw, seed=0, std=0.02, dtype="bfloat16", max_seq_len=max(ctx, pf_tokens), page_size=16,
                        pool_tokens=max(max_batch * ctx, pf_tokens + 64), max_slots=max_batch,
@@ -660,16 +684,9 @@ def main() -> int:
         "warmup": warmup, "ms_per_step": round(main_run["ms_per_step"], 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded random weights N(0, 0.02), uniform random token ids",
-        "config": {
-            "model": f"{model_name} layer sizes", "layers": n_layers, "layers_of_model": sizes["num_hidden_layers"],
-            "hidden": raw["hidden_size"], "q_heads": raw["num_attention_heads"],
-            "kv_heads": raw["num_key_value_heads"], "head_dim": raw["head_dim"],
-            "intermediate": raw["intermediate_size"], "vocab": vocab, "rope_theta": raw["rope_theta"],
-            "rms_norm_eps": raw["rms_norm_eps"], "tied_head": False, "global_batch": args.batch,
-            "seq_len": ctx, "prefill_tokens": pf_tokens, "kv_block": 16,
-            "parallelism": "single GPU", "l2": "inputs larger than L2 (weights read every step)",
-            "peaks": peaks["source"],
-        },
+        "config": bench_config(model_name, raw, sizes["num_hidden_layers"], args.batch, ctx, pf_tokens,
+                               peaks["source"]),
+        "prompt_tokens": PROMPT_PORTION,
         "e2e": {k: (round(v, 2) if isinstance(v, float) else v) for k, v in e2e.items()},
         "gpu_launches": main_run["launches"],
         "prefill": {"value": round(pf_tokens / (prefill_ms / 1e3), 1), "tokens": pf_tokens,

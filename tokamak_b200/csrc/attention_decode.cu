@@ -25,6 +25,7 @@
 // zero-filled, so stale or foreign data in a partly filled or given-back page
 // cannot reach the result.
 #include "mma_utils.cuh"
+#include "timeline.cuh"
 
 namespace tk {
 
@@ -131,7 +132,9 @@ attn_decode_split_kernel(DecodeParams p) {
     issue_load(tile, warm);
     cp_async_commit();
   }
+  if (threadIdx.x == 0) tl_mark(2, 0);
   pdl_wait();
+  if (threadIdx.x == 0) tl_mark(2, 1);
   // ---- query fragments: row g of the tile is query head hkv * group + g --------------------
   uint32_t qa[D / 16][4];
   {
@@ -234,6 +237,7 @@ attn_decode_split_kernel(DecodeParams p) {
     __syncwarp();
   }
   cp_async_wait<0>();
+  if (threadIdx.x == 0) tl_mark(2, 2);
 
   // ---- merge the warps --------------------------------------------------------------------
 #pragma unroll
@@ -292,6 +296,7 @@ attn_decode_split_kernel(DecodeParams p) {
     s_last = (arrived == p.n_splits - 1);
   }
   __syncthreads();
+  if (threadIdx.x == 0) tl_mark(2, s_last ? 3 : 4);
   if (!s_last) return;
   __threadfence();                       // and the others' partial results before they are read
   // A thread adds up four neighbouring columns of one row over the splits, always in the order of
@@ -366,7 +371,7 @@ attn_decode_split_kernel(DecodeParams p) {
     packed.y = pack_bf16(acc.z, acc.w);
     *reinterpret_cast<uint2*>(p.out + ((size_t)tok * p.n_q_heads + (size_t)hkv * group + row) * D + c4 * 4) = packed;
   }
-  if (threadIdx.x == 0) p.counters[item * p.n_kv_heads + hkv] = 0;
+  if (threadIdx.x == 0) { p.counters[item * p.n_kv_heads + hkv] = 0; tl_mark(2, 4); }
 }
 
 template <int D>
@@ -385,6 +390,8 @@ static int launch_decode(const DecodeParams& p, cudaStream_t stream) {
 }
 
 }  // namespace tk
+
+TK_TIMELINE_SETTER(attention_decode)
 
 // Floats of scratch that tk_attention_decode needs: partial outputs, then (max, sum) pairs.
 // Beside them it needs n_items * n_kv_heads int counters that are zero before the call (the

@@ -31,6 +31,10 @@ NVCC_FLAGS = [
 ]
 
 
+# extra compiler flags, e.g. -DTK_TIMELINE (see timeline.cuh); they are part of the stamp
+EXTRA_FLAGS = os.environ.get("TOKAMAK_B200_NVCC_FLAGS", "").split()
+
+
 class BuildError(RuntimeError):
     """The CUDA extension could not be compiled."""
 
@@ -57,7 +61,7 @@ def _source_stamp() -> str:
     for path in sorted(list(SOURCE_DIR.glob("*.cu")) + list(SOURCE_DIR.glob("*.cuh")) + list(SOURCE_DIR.glob("*.h"))):
         h.update(path.name.encode())
         h.update(path.read_bytes())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(NVCC_FLAGS + EXTRA_FLAGS).encode())
     return h.hexdigest()
 
 
@@ -95,7 +99,7 @@ def _up_to_date(folder: Path, stamp: str) -> bool:
 
 
 def _compile_one(nvcc: str, src: Path, obj: Path, verbose_ptxas: bool) -> str:
-    cmd = [nvcc, *NVCC_FLAGS, "-I", str(SOURCE_DIR), "-c", str(src), "-o", str(obj)]
+    cmd = [nvcc, *NVCC_FLAGS, *EXTRA_FLAGS, "-I", str(SOURCE_DIR), "-c", str(src), "-o", str(obj)]
     if verbose_ptxas:
         cmd[1:1] = ["-Xptxas", "-v"]
     proc = subprocess.run(cmd, capture_output=True, text=True)

@@ -5,6 +5,7 @@
 // type.  RMSNorm statistics are 32-bit as in the reference
 // (src/tokamak/model/layers.py:28-33).
 #include "common.cuh"
+#include "timeline.cuh"
 
 namespace tk {
 
@@ -13,7 +14,9 @@ template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ resid, int hidden, int vocab, int* err) {
   pdl_trigger();
+  if (threadIdx.x == 0) tl_mark(4, 0);
   pdl_wait();
+  if (threadIdx.x == 0) tl_mark(4, 1);
   const int t = blockIdx.x;
   const int id = ids[t];
   float* out = resid + (size_t)t * hidden;
@@ -224,6 +227,8 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ gu, const float* __restr
 }
 
 }  // namespace tk
+
+TK_TIMELINE_SETTER(elementwise)
 
 TK_API int tk_embed_gather(const void* table, int dtype, const int* ids, float* resid, int n_tokens,
                            int hidden, int vocab, int* err, cudaStream_t stream) {

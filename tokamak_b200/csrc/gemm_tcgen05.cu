@@ -20,6 +20,7 @@
 // block-wide abort flag and the block leaves through the common exit that frees its
 // tensor memory.
 #include "tcgen05_utils.cuh"
+#include "timeline.cuh"
 
 namespace tk {
 
@@ -150,6 +151,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
   if (warp == 0) {
     // ---- TMA producer ---------------------------------------------------------------------
     if (lane == 0) {
+      tl_mark(10 + p.epilogue, 0);
       // The first ring of stages: the weight tiles (which no kernel writes) are requested
       // before the wait on the previous kernel, so they stream in while it finishes; the
       // activation tiles follow after the wait.
@@ -160,6 +162,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
         tma_load_2d(base + (uint32_t)i * stage_bytes, &map_r, (kb_begin + i) * kGtBK, tile_r * kGtBM, full);
       }
       pdl_wait();
+      tl_mark(10 + p.epilogue, 1);
       for (int i = 0; i < first; ++i) {
         const uint32_t full = gt_smem_u32(&full_bar[i]);
         const uint32_t dst = base + (uint32_t)i * stage_bytes;
@@ -209,6 +212,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
         umma_commit(gt_smem_u32(&empty_bar[s]));     // the stage may be refilled once these MMAs are done
       }
       if (ok) umma_commit(gt_smem_u32(accum_bar));  // the accumulator is complete
+      tl_mark(10 + p.epilogue, 2);
     }
   } else {
     // ---- epilogue: warps 2..5, each owns the 32 accumulator lanes of its quarter --------------
@@ -260,6 +264,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
       ok = mbar_wait(gt_smem_u32(accum_bar), 0u, abort_flag);
       if (!ok && lane == 0) { set_error(p.err, kErrWait, 2, 0, 0); *abort_flag = 1; }
     }
+    if (warp == 2 && lane == 0) tl_mark(10 + p.epilogue, 3);
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const int row = tile_r * kGtBM + quarter * 32 + lane;      // row of R = lane of the accumulator
     if (staged && my_col < p.bn) {
@@ -435,6 +440,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
   if (warp == 2) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(tmem_cols)
                  : "memory");
+    if (lane == 0) tl_mark(10 + p.epilogue, 4);
   }
 }
 
@@ -519,6 +525,8 @@ static int launch_gemm(const void* r, const void* c, int rows, int cols, int k, 
 // bf16(resid * norm_w) and sumsq_out [rows / 128, cols] the tiles' sums of squares of resid.
 // colscale_parts (or null): [n_colscale_parts, cols] float32; the sums of column c are
 // multiplied by rsqrt(sum_i colscale_parts[i, c] * colscale_inv_dim + colscale_eps).
+TK_TIMELINE_SETTER(gemm_tcgen05)
+
 TK_API int tk_gemm_bf16_tcgen05(const void* r, const void* c, void* out, int* err, int rows, int cols, int k,
                                 long long ld_r, long long ld_c, int bn, int n_splits,
                                 int max_stages, int cluster_reduce, int epilogue,

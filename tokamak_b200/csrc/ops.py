@@ -660,6 +660,40 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
                                out_tokens.data_ptr(), rows, vocab, _stream()), "sample")
 
 
+_TIMELINE_FILES = ("gemm_tcgen05", "attention_decode", "sampling", "step_state", "elementwise")
+
+
+def timeline_start(capacity: int = 1 << 20) -> torch.Tensor:
+    """Hand the kernels a buffer for their time stamps (a library built with -DTK_TIMELINE only,
+    see timeline.cuh) and return it; :func:`timeline_read` decodes it."""
+    import ctypes
+    lib = library()
+    if not hasattr(lib, "tk_timeline_set_gemm_tcgen05"):
+        raise KernelError("the library was built without -DTK_TIMELINE (set TOKAMAK_B200_NVCC_FLAGS)")
+    buf = torch.zeros(1 + 2 * capacity, dtype=torch.int64, device="cuda")
+    for name in _TIMELINE_FILES:
+        fn = getattr(lib, "tk_timeline_set_" + name)
+        fn.argtypes = [ctypes.c_void_p, ctypes.c_uint]
+        fn.restype = ctypes.c_int
+        code = fn(buf.data_ptr(), capacity)
+        if code != 0:
+            raise KernelError(f"timeline_set_{name}: CUDA error {code}")
+    return buf
+
+
+def timeline_read(buf: torch.Tensor) -> list[tuple[int, int, int, int, int]]:
+    """(time in ns, kernel, phase, SM, block) records in the order of time; clears the buffer."""
+    torch.cuda.synchronize()
+    host = buf.cpu()
+    n = min(int(host[0]), (host.numel() - 1) // 2)
+    out = []
+    for i in range(n):
+        t, rec = int(host[1 + 2 * i]), int(host[2 + 2 * i]) & 0xFFFFFFFFFFFFFFFF
+        out.append((t, (rec >> 56) & 0xFF, (rec >> 48) & 0xFF, (rec >> 32) & 0xFFFF, rec & 0xFFFFFFFF))
+    buf.zero_()
+    return sorted(out)
+
+
 def philox_u32(seed: int, counter: int) -> int:
     """First word of the generator's block for (seed, counter), computed on the host."""
     import ctypes

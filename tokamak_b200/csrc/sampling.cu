@@ -13,6 +13,7 @@
 // sums do not depend on the order of the additions, so thresholds and draws are
 // reproducible bit for bit.
 #include "common.cuh"
+#include "timeline.cuh"
 
 namespace tk {
 
@@ -75,7 +76,9 @@ __device__ __forceinline__ unsigned long long warp_incl_scan_u64(unsigned long l
 
 __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleParams p) {
   pdl_trigger();
+  if (threadIdx.x == 0) tl_mark(3, 0);
   pdl_wait();
+  if (threadIdx.x == 0) tl_mark(3, 1);
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
   __shared__ unsigned int s_count[256];
@@ -134,6 +137,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleParams p) 
     if (tid == 0) {
       p.out_tokens[row] = s_idx[0];
       if (rec) { rec[7] = s_idx[0]; rec[1] += 1; }
+      tl_mark(3, 4);
     }
     return;
   }
@@ -270,10 +274,13 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleParams p) 
   if (tid == 0) {
     p.out_tokens[row] = s_result;
     if (rec) { rec[7] = s_result; rec[1] += 1; }
+    tl_mark(3, 4);
   }
 }
 
 }  // namespace tk
+
+TK_TIMELINE_SETTER(sampling)
 
 TK_API int tk_sample(const float* logits, long long ld, const float* temperature, const int* top_k,
                      const float* top_p, const unsigned long long* seed, const unsigned int* counter,

@@ -24,6 +24,7 @@
 // Both kernels below apply the list first.  They run as ONE block, so that the order
 // "updates, then the step's own reads and writes of the records" is a __syncthreads().
 #include "common.cuh"
+#include "timeline.cuh"
 
 namespace tk {
 
@@ -93,7 +94,9 @@ decode_begin_kernel(UpdateList u, const int* __restrict__ dec_slots, int n_reqs,
                     int* __restrict__ token_ids, int* __restrict__ positions, int* __restrict__ req_kv_len,
                     int* err) {
   pdl_trigger();
+  if (threadIdx.x == 0) tl_mark(1, 0);
   pdl_wait();
+  if (threadIdx.x == 0) tl_mark(1, 1);
   apply_updates(u, err);
   __syncthreads();
   for (int r = threadIdx.x; r < n_reqs; r += blockDim.x) {
@@ -113,9 +116,12 @@ decode_begin_kernel(UpdateList u, const int* __restrict__ dec_slots, int n_reqs,
     positions[r] = pos;
     req_kv_len[r] = pos + 1;
   }
+  if (threadIdx.x == 0) tl_mark(1, 4);
 }
 
 }  // namespace tk
+
+TK_TIMELINE_SETTER(step_state)
 
 TK_API int tk_slot_words() { return tk::kSlotWords; }
 
