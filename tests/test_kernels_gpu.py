@@ -887,3 +887,105 @@ def test_step_state_kernels_alone():
     torch.cuda.synchronize()
     assert out_a.tolist() == out_b.tolist()
     assert records[1, 1] == 4 and records[4, 1] == 10 and records[1, 7] == out_a[0] and records[4, 7] == out_a[1]
+
+
+@pytest.mark.parametrize("tokens,hidden,k0,inter,vocab,heads", [(5, 384, 200, 320, 1000, (2, 1)), (64, 1024, 512, 1536, 777, (4, 2)),
+                                                                 (17, 4096, 4096, 12288, 2048, (32, 8)), (1, 256, 64, 64, 130, (1, 1))])
+def test_chain_of_products_in_one_kernel(tokens, hidden, k0, inter, vocab, heads):
+    """Products queued in a ProductChain and launched as one persistent kernel (output product with
+    the residual sum and the next norm prepared, gate/up with the activation, down with the
+    residual sum, q|k|v with norms, rotation and cache write, and a plain product with an owed
+    norm scale, each fed by the one before) against the same products launched one by one, and
+    the first of them against float64."""
+    from tokamak_b200.csrc import ops
+    gen = torch.Generator().manual_seed(tokens + hidden)
+    rnd = lambda *shape, s=1.0: (torch.randn(*shape, generator=gen) * s)
+    hq, hkv = heads
+    d, page, eps = 128, 16, 1e-6
+    x0 = rnd(tokens, k0).bfloat16().to(DEV)
+    w_o = rnd(hidden, k0, s=k0 ** -0.5).bfloat16().to(DEV)
+    w_gu = rnd(2 * inter, hidden, s=hidden ** -0.5).bfloat16().to(DEV)
+    w_d = rnd(hidden, inter, s=inter ** -0.5).bfloat16().to(DEV)
+    w_qkv = rnd((hq + 2 * hkv) * d, hidden, s=hidden ** -0.5).bfloat16().to(DEV)
+    w_head = rnd(vocab, hidden, s=hidden ** -0.5).bfloat16().to(DEV)
+    n1, n2 = (1 + 0.1 * rnd(hidden)).to(DEV), (1 + 0.1 * rnd(hidden)).to(DEV)
+    qn, kn = (1 + 0.1 * rnd(d)).to(DEV), (1 + 0.1 * rnd(d)).to(DEV)
+    resid0 = rnd(tokens, hidden).to(DEV)
+    positions = torch.arange(tokens, dtype=torch.int32, device=DEV) + 3
+    tok_req = torch.zeros(tokens, dtype=torch.int32, device=DEV)
+    slot = torch.zeros(1, dtype=torch.int32, device=DEV)
+    n_pages = -(-(tokens + 3) // page) + 2
+    table = torch.arange(n_pages, dtype=torch.int32, device=DEV).flip(0).view(1, n_pages).contiguous()
+    inv_freq = (1.0 / (1e4 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(DEV)
+    rope = ops.rope_table(positions, inv_freq)
+
+    plan = lambda w: ops.swapped_gemm_plan(w.shape[0], w.shape[1], tokens)
+    new_cache = lambda: torch.zeros(n_pages, hkv, page, d, dtype=torch.bfloat16, device=DEV)
+
+    def chained_run():
+        err = err_word()
+        resid, kc, vc = resid0.clone(), new_cache(), new_cache()
+        q = torch.zeros(tokens, hq, d, dtype=torch.bfloat16, device=DEV)
+        c = ops.ProductChain(tokens, err)
+        s, st, cl = plan(w_o)
+        xb1, ss1 = ops.gemm_tc_swapped(w_o, x0, err, s, max_stages=st, cluster=cl, residual_norm=(resid, n1), chain=c)
+        s, st, cl = plan(w_gu)
+        act = ops.gemm_tc_swapped(w_gu, xb1, err, s, max_stages=st, cluster=cl, swiglu=True,
+                                  colscale=(ss1, hidden, eps), chain=c)
+        s, st, cl = plan(w_d)
+        xb2, ss2 = ops.gemm_tc_swapped(w_d, act, err, s, max_stages=st, cluster=cl, residual_norm=(resid, n2), chain=c)
+        s, st, cl = plan(w_qkv)
+        ops.gemm_qkv_rope(w_qkv, xb2, err, s, q, kc, vc, positions, tok_req, slot, table, qn, kn, rope,
+                          n_q_heads=hq, n_kv_heads=hkv, eps=eps, max_stages=st, colscale=(ss2, hidden, eps), chain=c)
+        s, st, cl = plan(w_head)
+        logits = ops.gemm_tc_swapped(w_head, xb2, err, s, max_stages=st, cluster=cl, colscale=(ss2, hidden, eps), chain=c)
+        assert len(c.phases) == 5
+        before = ops.LAUNCHES
+        ops.flush_chains()
+        assert ops.LAUNCHES == before + 1 and not c.phases           # one kernel for the five products
+        torch.cuda.synchronize()
+        assert err.tolist()[0] == 0, err.tolist()
+        return dict(resid=resid, xb1=xb1, ss1=ss1, act=act, xb2=xb2, ss2=ss2, q=q, k=kc, v=vc, logits=logits)
+
+    C = chained_run()
+
+    def close(name, got, want, tol):
+        got, want = got.float(), want.float()
+        scale = float(want.abs().max()) + 1e-6
+        worst = float((got - want).abs().max())
+        assert worst <= tol * scale, (name, worst, scale)
+
+    # Every link again as a kernel of its own, fed with what the chain produced before it: the k
+    # ranges are cut at other places, so float32 sums come in another order (a few 1e-6 of the
+    # largest value) and a bfloat16 result may land on the neighbouring value
+    F32, B16 = 2e-5, 1.6e-2
+    err = err_word()
+    resid = resid0.clone()
+    s, st, cl = plan(w_o)
+    xb1, ss1 = ops.gemm_tc_swapped(w_o, x0, err, s, max_stages=st, cluster=cl, residual_norm=(resid, n1))
+    close("xb1", C["xb1"], xb1, B16); close("ss1", C["ss1"].sum(0), ss1.sum(0), F32)
+    s, st, cl = plan(w_gu)
+    act = ops.gemm_tc_swapped(w_gu, C["xb1"], err, s, max_stages=st, cluster=cl, swiglu=True, colscale=(C["ss1"], hidden, eps))
+    close("act", C["act"], act, B16)
+    s, st, cl = plan(w_d)
+    xb2, ss2 = ops.gemm_tc_swapped(w_d, C["act"], err, s, max_stages=st, cluster=cl, residual_norm=(resid, n2))
+    close("resid", C["resid"], resid, F32); close("xb2", C["xb2"], xb2, B16); close("ss2", C["ss2"].sum(0), ss2.sum(0), F32)
+    kc, vc, q = new_cache(), new_cache(), torch.zeros(tokens, hq, d, dtype=torch.bfloat16, device=DEV)
+    s, st, cl = plan(w_qkv)
+    ops.gemm_qkv_rope(w_qkv, C["xb2"], err, s, q, kc, vc, positions, tok_req, slot, table, qn, kn, rope,
+                      n_q_heads=hq, n_kv_heads=hkv, eps=eps, max_stages=st, colscale=(C["ss2"], hidden, eps))
+    close("q", C["q"], q, B16); close("k", C["k"], kc, B16); close("v", C["v"], vc, B16)
+    assert float(C["k"].float().abs().sum()) > 0
+    s, st, cl = plan(w_head)
+    logits = ops.gemm_tc_swapped(w_head, C["xb2"], err, s, max_stages=st, cluster=cl, colscale=(C["ss2"], hidden, eps))
+    close("logits", C["logits"].sum(0), logits.sum(0), F32)
+    torch.cuda.synchronize()
+    assert err.tolist()[0] == 0
+    chained = {"xb1": C["xb1"].float(), "ss1": C["ss1"].sum(0)}
+    # and the first link against float64: what resid + x0 W_o^T gives under the norm weight, and its squares
+    want = resid0.double() + x0.double() @ w_o.double().T
+    torch.testing.assert_close(chained["xb1"].double(), (want * n1.double()), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(chained["ss1"].double(), (want * want).sum(-1), rtol=1e-4, atol=1e-3)
+    # twice in a row: the counters of the first launch are back at zero, and the result is the same to the bit
+    again = chained_run()
+    assert all(torch.equal(again[n], C[n]) for n in C)

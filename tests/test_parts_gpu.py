@@ -674,7 +674,7 @@ class CappedHead:
         return {"out.weight": TensorReq((spec.vocab_size, spec.hidden_size)),
                 "out.bias": TensorReq((spec.vocab_size,), role="vector")}
 
-    def forward(self, h, err=None):
+    def forward(self, h, step=None):
         from tokamak_b200.parts.base import linear, sum_parts
         logits = sum_parts(linear(h, self.weight, out_dtype=torch.float32), torch.float32) + self.bias
         return self.spec.cap * torch.tanh(logits / self.spec.cap)

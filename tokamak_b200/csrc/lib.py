@@ -21,6 +21,9 @@ _SIGNATURES: dict[str, list] = {
     "tk_decode_begin": [_P, c_int, c_int, _P, c_int, _P, c_longlong, _P, c_int, c_int, _P, _P, _P, _P, _P],
     "tk_sample_slots": [_P, c_longlong, _P, _P, c_int, _P, c_int, c_int, _P, _P],
     "tk_wait_probe": [c_uint, _P, _P],
+    "tk_gemm_chain": [_P, c_int, c_int, _P, _P, _P, c_int, _P],
+    "tk_gemm_chain_blocks": [],
+    "tk_gemm_chain_max_phases": [],
     "tk_slot_words": [],
     "tk_add_rmsnorm": [_P, _P, _P, c_int, c_longlong, _P, _P, _P, c_int, c_int, c_float, c_int, _P],
     "tk_swiglu": [_P, _P, c_int, c_longlong, _P, c_int, c_int, c_int, c_int, _P],
@@ -68,6 +71,10 @@ def library() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = c_int
+    for name, args in (("tk_gemm_chain_scratch_floats", [c_int]), ("tk_gemm_chain_counter_ints", [c_int])):
+        fn = getattr(lib, name)
+        fn.argtypes = args
+        fn.restype = c_longlong
     lib.tk_philox_u32.argtypes = [c_ulonglong, c_uint, ctypes.POINTER(c_uint)]
     lib.tk_philox_u32.restype = None
     return lib

@@ -32,6 +32,7 @@ def _stream() -> int:
 
 
 LAUNCHES = 0     # kernels of this library launched (or recorded into a graph) so far
+_ACTIVE_CHAINS: list = []      # product chains with queued products (see ProductChain)
 
 
 def _check(code: int, what: str) -> None:
@@ -39,6 +40,14 @@ def _check(code: int, what: str) -> None:
     if code != 0:
         raise KernelError(f"{what}: CUDA error {code}")
     LAUNCHES += 1
+
+
+def _lib():
+    """The library, for a wrapper that is about to launch: products that are still queued in a
+    chain are launched first, so that no kernel reads a result that does not exist yet."""
+    if _ACTIVE_CHAINS:
+        flush_chains()
+    return library()
 
 
 def _ptr(t: torch.Tensor | None) -> int | None:
@@ -68,7 +77,7 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, resid: torch.Tensor, er
     vocab, hidden = table.shape
     if resid.shape[-1] != hidden or resid.numel() < n * hidden:
         raise KernelError("resid is too small for the tokens")
-    _check(library().tk_embed_gather(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(),
+    _check(_lib().tk_embed_gather(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(),
                                      resid.data_ptr(), n, hidden, vocab, err.data_ptr(), _stream()),
            "embed_gather")
 
@@ -103,7 +112,7 @@ def step_begin(upd: UpdateBuffers, token_ids: torch.Tensor, req_q_start: torch.T
     n = req_slot.numel()
     if req_q_start.numel() < n or req_kv_len.numel() < n or (req_fed is not None and req_fed.numel() < n):
         raise KernelError("a per-request array is shorter than the batch")
-    _check(library().tk_step_begin(*upd.args(), token_ids.data_ptr(), req_q_start.data_ptr(),
+    _check(_lib().tk_step_begin(*upd.args(), token_ids.data_ptr(), req_q_start.data_ptr(),
                                    req_kv_len.data_ptr(), req_slot.data_ptr(), _ptr(req_fed), n,
                                    token_ids.numel(), err.data_ptr(), _stream()), "step_begin")
 
@@ -118,7 +127,7 @@ def decode_begin(upd: UpdateBuffers, dec_slots: torch.Tensor, n_reqs: int, max_p
         _want(t, torch.int32, name)
         if t.numel() < n_reqs:
             raise KernelError(f"{name} is shorter than the batch")
-    _check(library().tk_decode_begin(*upd.args(), dec_slots.data_ptr(), n_reqs, max_positions,
+    _check(_lib().tk_decode_begin(*upd.args(), dec_slots.data_ptr(), n_reqs, max_positions,
                                      token_ids.data_ptr(), positions.data_ptr(), req_kv_len.data_ptr(),
                                      err.data_ptr(), _stream()), "decode_begin")
 
@@ -133,7 +142,7 @@ def sample_slots(logits: torch.Tensor, records: torch.Tensor, row_slot: torch.Te
     rows, vocab = logits.shape
     if row_slot.numel() < rows or out_tokens.numel() < rows:
         raise KernelError("a per-row sampling tensor is shorter than the batch")
-    _check(library().tk_sample_slots(logits.data_ptr(), logits.stride(0), records.data_ptr(),
+    _check(_lib().tk_sample_slots(logits.data_ptr(), logits.stride(0), records.data_ptr(),
                                      row_slot.data_ptr(), records.shape[0], out_tokens.data_ptr(), rows, vocab,
                                      err.data_ptr(), _stream()), "sample_slots")
 
@@ -142,7 +151,7 @@ def wait_probe(limit: int, err: torch.Tensor) -> None:
     """Test aid: one block waits on a barrier that nobody arrives at, gives up after ``limit``
     polls and reports it through the error word exactly as the tcgen05 kernels would."""
     _want(err, torch.int32, "err")
-    _check(library().tk_wait_probe(int(limit), err.data_ptr(), _stream()), "wait_probe")
+    _check(_lib().tk_wait_probe(int(limit), err.data_ptr(), _stream()), "wait_probe")
 
 
 def add_rmsnorm(resid: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor,
@@ -172,7 +181,7 @@ def add_rmsnorm(resid: torch.Tensor, delta: torch.Tensor | None, weight: torch.T
         n_rows = resid.numel() // hidden
     if out.numel() < n_rows * hidden:
         raise KernelError("out is too small")
-    _check(library().tk_add_rmsnorm(resid.data_ptr(), _ptr(delta), _ptr(parts), n_parts, part_stride,
+    _check(_lib().tk_add_rmsnorm(resid.data_ptr(), _ptr(delta), _ptr(parts), n_parts, part_stride,
                                     weight.data_ptr(), out.data_ptr(), _ptr(rows), n_rows, hidden,
                                     float(eps), dtype_code(out.dtype), _stream()), "add_rmsnorm")
 
@@ -198,7 +207,7 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
     block = block or two_i // 2
     if (two_i // 2) % block:
         raise KernelError("the gate/up block must divide the intermediate size")
-    _check(library().tk_swiglu(_ptr(gate_up), _ptr(parts), n_parts, part_stride, out.data_ptr(), n,
+    _check(_lib().tk_swiglu(_ptr(gate_up), _ptr(parts), n_parts, part_stride, out.data_ptr(), n,
                                two_i // 2, block, dtype_code(out.dtype), _stream()), "swiglu")
 
 
@@ -207,7 +216,7 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
     _want(positions, torch.int32, "positions"); _want(inv_freq, torch.float32, "inv_freq")
     n, half = positions.numel(), inv_freq.numel()
     table = torch.empty((n, half, 2), dtype=torch.float32, device=positions.device)
-    _check(library().tk_rope_table(positions.data_ptr(), inv_freq.data_ptr(), table.data_ptr(), n, 2 * half,
+    _check(_lib().tk_rope_table(positions.data_ptr(), inv_freq.data_ptr(), table.data_ptr(), n, 2 * half,
                                    _stream()), "rope_table")
     return table
 
@@ -263,7 +272,7 @@ def rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | None
             raise KernelError("cache pages do not match the heads")
     else:
         num_pages, page_size = 0, 1
-    _check(library().tk_rope_kv(_ptr(qkv), _ptr(parts), n_parts, q_out.data_ptr(), _ptr(k_cache), _ptr(v_cache),
+    _check(_lib().tk_rope_kv(_ptr(qkv), _ptr(parts), n_parts, q_out.data_ptr(), _ptr(k_cache), _ptr(v_cache),
                                 positions.data_ptr(), tok_req.data_ptr(), req_slot.data_ptr(),
                                 block_table.data_ptr(), _ptr(req_q_len), _ptr(req_kv_len),
                                 _ptr(q_norm_w), _ptr(k_norm_w), _ptr(table),
@@ -290,7 +299,7 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
         raise KernelError(f"{hq} query heads are not a multiple of {hkv} key/value heads")
     if d > 256:
         raise KernelError(f"head_dim {d} is beyond the kernels' limit of 256")
-    _check(library().tk_attention_plain(q.data_ptr(), out.data_ptr(), k_cache.data_ptr(),
+    _check(_lib().tk_attention_plain(q.data_ptr(), out.data_ptr(), k_cache.data_ptr(),
                                         v_cache.data_ptr(), positions.data_ptr(), tok_req.data_ptr(),
                                         req_slot.data_ptr(), block_table.data_ptr(), _ptr(items),
                                         err.data_ptr(), n if items is None else items.numel(),
@@ -338,7 +347,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
         _want(scratch, torch.float32, "scratch")
         if scratch.numel() < need:
             raise KernelError(f"scratch holds {scratch.numel()} floats, {need} needed")
-    _check(library().tk_attention_decode(q.data_ptr(), out.data_ptr(), k_cache.data_ptr(),
+    _check(_lib().tk_attention_decode(q.data_ptr(), out.data_ptr(), k_cache.data_ptr(),
                                          v_cache.data_ptr(), scratch.data_ptr(), counters.data_ptr(),
                                          items.data_ptr(),
                                          positions.data_ptr(), tok_req.data_ptr(), req_slot.data_ptr(),
@@ -363,7 +372,7 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
     num_pages, hkv, page_size, dk = k_cache.shape
     if not prefill_kernel_takes(hq, hkv, d, page_size) or dk != d:
         raise KernelError(f"the flash prefill kernel does not take heads {hq}/{hkv}, head_dim {d}")
-    _check(library().tk_attention_prefill(q.data_ptr(), out.data_ptr(), k_cache.data_ptr(),
+    _check(_lib().tk_attention_prefill(q.data_ptr(), out.data_ptr(), k_cache.data_ptr(),
                                           v_cache.data_ptr(), tiles.data_ptr(), req_q_start.data_ptr(),
                                           req_q_len.data_ptr(), req_kv_len.data_ptr(),
                                           req_slot.data_ptr(), block_table.data_ptr(), err.data_ptr(),
@@ -387,7 +396,7 @@ def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tens
     if not prefill_tc_kernel_takes(hq, hkv, d, page_size) or dk != d:
         raise KernelError(f"the tcgen05 prefill kernel does not take heads {hq}/{hkv}, head_dim {d}, "
                           f"page size {page_size}")
-    _check(library().tk_attention_prefill_tc(q.data_ptr(), out.data_ptr(), k_cache.data_ptr(),
+    _check(_lib().tk_attention_prefill_tc(q.data_ptr(), out.data_ptr(), k_cache.data_ptr(),
                                              v_cache.data_ptr(), tiles.data_ptr(), req_q_start.data_ptr(),
                                              req_q_len.data_ptr(), req_kv_len.data_ptr(),
                                              req_slot.data_ptr(), block_table.data_ptr(), err.data_ptr(),
@@ -445,7 +454,7 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
         _want(out, torch.float32, "out")
         if out.shape != (m, n):
             raise KernelError("out has the wrong shape")
-    _check(library().tk_gemm_f32(a.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, k, k, n,
+    _check(_lib().tk_gemm_f32(a.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, k, k, n,
                                  _stream()), "gemm_f32")
     return out
 
@@ -456,7 +465,7 @@ SWIGLU_TILE_BLOCK = 64     # gate/up rows alternate in blocks of this many for t
 def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_splits: int,
                     out: torch.Tensor | None = None, max_stages: int = 0, cluster: int = 0,
                     swiglu: bool = False, colscale: tuple | None = None,
-                    residual_norm: tuple | None = None):
+                    residual_norm: tuple | None = None, chain: "ProductChain | None" = None):
     """``x @ weight^T`` on tcgen05, the weight being the 128-row operand (for few tokens: every
     weight byte is streamed once by TMA), as float32 partial sums ``[parts, tokens, N_out]`` for
     the caller to add up.  ``parts = n_splits``, or ``n_splits / cluster`` with ``cluster`` in
@@ -474,7 +483,10 @@ def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_
     ``residual_norm=(resid, norm_weight)`` (all splits in one cluster, ``N_out`` a multiple of
     128): the sums are added to the float32 residual stream ``resid [tokens, N_out]`` in place and
     ``(xb, sumsq)`` is returned: ``xb = bf16(resid * norm_weight)`` and the tiles' sums of squares
-    ``[N_out / 128, tokens]``, ready to be the ``x`` and ``colscale`` of the next product."""
+    ``[N_out / 128, tokens]``, ready to be the ``x`` and ``colscale`` of the next product.
+
+    ``chain``: a :class:`ProductChain`; a product whose result is a single part is queued in it
+    instead of launched (the result tensors are returned all the same, to be filled at the flush)."""
     _want(weight, torch.bfloat16, "weight"); _want(x, torch.bfloat16, "x")
     n_out, k = weight.shape
     tokens, kx = x.shape
@@ -515,15 +527,133 @@ def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_
         if out is None:
             out = torch.empty((parts, tokens, n_out), dtype=torch.float32, device=x.device)
         out_ptr, result = out.data_ptr(), out
-    _check(library().tk_gemm_bf16_tcgen05(weight.data_ptr(), x.data_ptr(), out_ptr, err.data_ptr(),
-                                          n_out, tokens, k, k, k, bn, n_splits, max_stages,
-                                          cluster if cluster > 1 else 0, epilogue, cs_ptr, cs_n, cs_inv, cs_eps,
-                                          resid_ptr, w_ptr, _ptr(xb), _ptr(sums_out), _stream()),
-           "gemm_tc_swapped")
+    def alone():
+        _check(library().tk_gemm_bf16_tcgen05(weight.data_ptr(), x.data_ptr(), out_ptr, err.data_ptr(),
+                                              n_out, tokens, k, k, k, bn, n_splits, max_stages,
+                                              cluster if cluster > 1 else 0, epilogue, cs_ptr, cs_n, cs_inv, cs_eps,
+                                              resid_ptr, w_ptr, _ptr(xb), _ptr(sums_out), _stream()),
+               "gemm_tc_swapped")
+
+    if chain is not None and parts == 1 and ProductChain.takes(tokens, n_out):
+        a = _ChainPhaseArgs()
+        a.w, a.x, a.ld_w, a.ld_x, a.rows, a.k, a.epilogue = weight.data_ptr(), x.data_ptr(), k, k, n_out, k, epilogue
+        a.out, a.colscale_parts, a.n_colscale_parts = out_ptr, cs_ptr, cs_n
+        a.colscale_inv_dim, a.colscale_eps = cs_inv, cs_eps
+        a.resid, a.norm_w, a.xb_out, a.sumsq_out = resid_ptr, w_ptr, _ptr(xb), _ptr(sums_out)
+        chain.add(a, alone, (weight, x, result, colscale, residual_norm))
+        return result
+    flush_chains()
+    alone()
     return result
 
 
 QKV_ROPE_HEAD_DIM = 128    # the head size whose heads are whole 128-row tiles of the swapped product
+
+
+# ---- chains of decode products ---------------------------------------------------------------------
+
+CHAIN_MAX_TOKENS = 64
+# Whether the parts queue their decode products into chains ("on") or launch every product as a kernel
+# of its own ("off").  Measured at the Qwen3-8B sizes, batch 8: 4.9 ms a step chained against 3.8 ms
+# with one kernel per product, so the default is "off"; gemm_chain.cu says where the time goes.
+CHAIN_POLICY = os.environ.get("TOKAMAK_B200_CHAIN", "off")
+
+
+class _ChainPhaseArgs(__import__("ctypes").Structure):
+    """``TkChainPhaseArgs`` of gemm_chain.cu."""
+    import ctypes as _c
+    _fields_ = [("w", _c.c_void_p), ("x", _c.c_void_p), ("ld_w", _c.c_longlong), ("ld_x", _c.c_longlong),
+                ("rows", _c.c_int), ("k", _c.c_int), ("epilogue", _c.c_int), ("n_colscale_parts", _c.c_int),
+                ("out", _c.c_void_p), ("colscale_parts", _c.c_void_p),
+                ("colscale_inv_dim", _c.c_float), ("colscale_eps", _c.c_float),
+                ("resid", _c.c_void_p), ("norm_w", _c.c_void_p), ("xb_out", _c.c_void_p), ("sumsq_out", _c.c_void_p),
+                ("q_out", _c.c_void_p), ("k_cache", _c.c_void_p), ("v_cache", _c.c_void_p),
+                ("positions", _c.c_void_p), ("tok_req", _c.c_void_p), ("req_slot", _c.c_void_p),
+                ("block_table", _c.c_void_p), ("req_q_len", _c.c_void_p), ("req_kv_len", _c.c_void_p),
+                ("q_norm_w", _c.c_void_p), ("k_norm_w", _c.c_void_p), ("rope_table", _c.c_void_p),
+                ("n_reqs", _c.c_int), ("n_q_heads", _c.c_int), ("n_kv_heads", _c.c_int), ("page_size", _c.c_int),
+                ("max_pages", _c.c_int), ("num_pages", _c.c_int), ("eps", _c.c_float), ("reserved", _c.c_int)]
+    del _c
+
+
+_CHAIN_WORKSPACES: dict = {}
+_CHAIN_MAX_TILES = 2048          # most 128-row tiles of one product (a head of 262,144 rows)
+
+
+def _chain_workspace(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
+    """Scratch for the parts of tiles and the (zero) counters of the chain kernel, one per device."""
+    ws = _CHAIN_WORKSPACES.get(device)
+    if ws is None:
+        lib = library()
+        scratch = torch.empty(lib.tk_gemm_chain_scratch_floats(CHAIN_MAX_TOKENS), dtype=torch.float32, device=device)
+        counters = torch.zeros(lib.tk_gemm_chain_counter_ints(_CHAIN_MAX_TILES), dtype=torch.int32, device=device)
+        ws = _CHAIN_WORKSPACES[device] = (scratch, counters)
+    return ws
+
+
+def reset_workspaces() -> None:
+    """Put the counters that kernels expect at zero back to zero (after a kernel reported an error
+    and may have left them otherwise)."""
+    for _, counters in _CHAIN_WORKSPACES.values():
+        counters.zero_()
+    for buf in _DECODE_COUNTERS.values():
+        buf.zero_()
+
+
+class ProductChain:
+    """Decode products whose launch is put off so that consecutive ones run as ONE persistent
+    kernel (gemm_chain.cu): the weights of the next product stream in while the sums of the one
+    before are added up and stored.
+
+    :func:`gemm_tc_swapped` and :func:`gemm_qkv_rope` take a chain; with one, a product that ends
+    in a single part is queued instead of launched, and its result tensors are returned at once,
+    not yet computed.  :meth:`flush` launches what is queued; every other kernel wrapper of this
+    module calls it first, so a kernel of this library never reads a result that is still queued.
+    Code that reads such a tensor in any other way must call :meth:`flush` itself.
+    """
+
+    def __init__(self, tokens: int, err: torch.Tensor):
+        self.tokens = tokens
+        self.err = err
+        self.phases: list[tuple[_ChainPhaseArgs, object]] = []     # (arguments, launch on its own)
+        self.keep: list = []
+        self.max_phases = library().tk_gemm_chain_max_phases()
+
+    @staticmethod
+    def takes(tokens: int, n_out: int) -> bool:
+        return 1 <= tokens <= CHAIN_MAX_TOKENS and -(-n_out // 128) <= _CHAIN_MAX_TILES
+
+    def add(self, args: _ChainPhaseArgs, alone, keep: tuple) -> None:
+        if len(self.phases) == self.max_phases:
+            self.flush()
+        if not self.phases:
+            self.stream = _stream()
+        self.phases.append((args, alone))
+        self.keep.append(keep)               # operands stay allocated until the launch
+        if self not in _ACTIVE_CHAINS:
+            _ACTIVE_CHAINS.append(self)
+
+    def flush(self) -> None:
+        if not self.phases:
+            return
+        phases, self.phases, self.keep = self.phases, [], []
+        if _stream() != self.stream:
+            raise KernelError("queued products are being launched on another stream than they were queued on; "
+                              "call ops.flush_chains() before changing the stream")
+        if len(phases) == 1:
+            phases[0][1]()                     # a single product: the kernel tuned for it
+            return
+        arr = (_ChainPhaseArgs * len(phases))(*[a for a, _ in phases])
+        scratch, counters = _chain_workspace(self.err.device)
+        _check(library().tk_gemm_chain(arr, len(phases), self.tokens, self.err.data_ptr(), scratch.data_ptr(),
+                                       counters.data_ptr(), _CHAIN_MAX_TILES, _stream()), "gemm_chain")
+
+
+def flush_chains() -> None:
+    chains = list(_ACTIVE_CHAINS)
+    _ACTIVE_CHAINS.clear()
+    for chain in chains:
+        chain.flush()
 
 
 def gemm_qkv_rope(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_splits: int, q_out: torch.Tensor,
@@ -531,7 +661,8 @@ def gemm_qkv_rope(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_sp
                   req_slot: torch.Tensor, block_table: torch.Tensor, q_norm_w: torch.Tensor | None,
                   k_norm_w: torch.Tensor | None, table: torch.Tensor | None, *, n_q_heads: int, n_kv_heads: int,
                   eps: float, max_stages: int = 0, colscale: tuple | None = None,
-                  req_q_len: torch.Tensor | None = None, req_kv_len: torch.Tensor | None = None) -> None:
+                  req_q_len: torch.Tensor | None = None, req_kv_len: torch.Tensor | None = None,
+                  chain: "ProductChain | None" = None) -> None:
     """The stacked q|k|v projection of few tokens with :func:`rope_kv`'s work in its epilogue, for
     heads of 128 elements: ``weight`` is ``[(Hq + 2 Hkv) 128, K]``, ``x`` ``[tokens, K]``; ``q_out``
     receives the normed and rotated queries, the keys and values go to their pages.  All
@@ -576,14 +707,30 @@ def gemm_qkv_rope(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_sp
     bn = 16
     while bn < tokens:
         bn *= 2
-    _check(library().tk_gemm_qkv_rope(weight.data_ptr(), x.data_ptr(), err.data_ptr(), tokens, k, k, k, bn,
-                                      n_splits, max_stages, cs_ptr, cs_n, cs_inv, cs_eps,
-                                      q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
-                                      positions.data_ptr(), tok_req.data_ptr(), req_slot.data_ptr(),
-                                      block_table.data_ptr(), _ptr(req_q_len), _ptr(req_kv_len),
-                                      _ptr(q_norm_w), _ptr(k_norm_w), _ptr(table), req_slot.numel(),
-                                      n_q_heads, n_kv_heads, page_size, block_table.shape[1], num_pages,
-                                      float(eps), _stream()), "gemm_qkv_rope")
+    def alone():
+        _check(library().tk_gemm_qkv_rope(weight.data_ptr(), x.data_ptr(), err.data_ptr(), tokens, k, k, k, bn,
+                                          n_splits, max_stages, cs_ptr, cs_n, cs_inv, cs_eps,
+                                          q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                          positions.data_ptr(), tok_req.data_ptr(), req_slot.data_ptr(),
+                                          block_table.data_ptr(), _ptr(req_q_len), _ptr(req_kv_len),
+                                          _ptr(q_norm_w), _ptr(k_norm_w), _ptr(table), req_slot.numel(),
+                                          n_q_heads, n_kv_heads, page_size, block_table.shape[1], num_pages,
+                                          float(eps), _stream()), "gemm_qkv_rope")
+
+    if chain is not None and ProductChain.takes(tokens, n_out):
+        a = _ChainPhaseArgs()
+        a.w, a.x, a.ld_w, a.ld_x, a.rows, a.k, a.epilogue = weight.data_ptr(), x.data_ptr(), k, k, n_out, k, 3
+        a.colscale_parts, a.n_colscale_parts, a.colscale_inv_dim, a.colscale_eps = cs_ptr, cs_n, cs_inv, cs_eps
+        a.q_out, a.k_cache, a.v_cache = q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr()
+        a.positions, a.tok_req, a.req_slot = positions.data_ptr(), tok_req.data_ptr(), req_slot.data_ptr()
+        a.block_table, a.req_q_len, a.req_kv_len = block_table.data_ptr(), _ptr(req_q_len), _ptr(req_kv_len)
+        a.q_norm_w, a.k_norm_w, a.rope_table = _ptr(q_norm_w), _ptr(k_norm_w), _ptr(table)
+        a.n_reqs, a.n_q_heads, a.n_kv_heads, a.page_size = req_slot.numel(), n_q_heads, n_kv_heads, page_size
+        a.max_pages, a.num_pages, a.eps = block_table.shape[1], num_pages, float(eps)
+        chain.add(a, alone, (weight, x, q_out, colscale, table, q_norm_w, k_norm_w, positions))
+        return
+    flush_chains()
+    alone()
 
 
 def swapped_gemm_plan(n_out: int, k: int, tokens: int = 8) -> tuple[int, int, int]:
@@ -639,7 +786,7 @@ def gemm_pair(x: torch.Tensor, weight: torch.Tensor, err: torch.Tensor, swiglu: 
     if width % 8:
         raise KernelError("the output width must be a multiple of 8")
     out = torch.empty((tokens, width), dtype=torch.bfloat16, device=x.device)
-    _check(library().tk_gemm_bf16_pair(x.data_ptr(), weight.data_ptr(), out.data_ptr(), err.data_ptr(), tokens,
+    _check(_lib().tk_gemm_bf16_pair(x.data_ptr(), weight.data_ptr(), out.data_ptr(), err.data_ptr(), tokens,
                                        n_out, k, k, k, width, 1 if swiglu else 0, _stream()), "gemm_pair")
     return out
 
@@ -655,12 +802,12 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     for t in (temperature, top_k, top_p, seed, counter, out_tokens):
         if t.numel() < rows:
             raise KernelError("a per-row sampling tensor is shorter than the batch")
-    _check(library().tk_sample(logits.data_ptr(), logits.stride(0), temperature.data_ptr(),
+    _check(_lib().tk_sample(logits.data_ptr(), logits.stride(0), temperature.data_ptr(),
                                top_k.data_ptr(), top_p.data_ptr(), seed.data_ptr(), counter.data_ptr(),
                                out_tokens.data_ptr(), rows, vocab, _stream()), "sample")
 
 
-_TIMELINE_FILES = ("gemm_tcgen05", "attention_decode", "sampling", "step_state", "elementwise")
+_TIMELINE_FILES = ("gemm_tcgen05", "gemm_chain", "attention_decode", "sampling", "step_state", "elementwise")
 
 
 def timeline_start(capacity: int = 1 << 20) -> torch.Tensor:

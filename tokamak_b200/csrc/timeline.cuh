@@ -37,6 +37,27 @@ __device__ __forceinline__ void tl_mark(int kernel, int phase) {
   }
 }
 
+// A record that carries a number (e.g. nanoseconds spent waiting) in place of the block index.
+__device__ __forceinline__ void tl_value(int kernel, int phase, unsigned int value) {
+  const TimelineBuf tl = g_timeline;
+  if (tl.buf == nullptr) return;
+  unsigned long long t;
+  unsigned int sm;
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+  asm volatile("mov.u32 %0, %%smid;\n" : "=r"(sm));
+  const unsigned long long i = atomicAdd(tl.buf, 1ull);
+  if (i < tl.cap) {
+    tl.buf[1 + 2 * i] = t;
+    tl.buf[2 + 2 * i] = ((unsigned long long)(kernel & 0xFF) << 56) | ((unsigned long long)(phase & 0xFF) << 48) |
+                        ((unsigned long long)(sm & 0xFFFF) << 32) | (unsigned long long)value;
+  }
+}
+__device__ __forceinline__ unsigned long long tl_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+  return t;
+}
+
 }  // namespace tk
 
 #define TK_TIMELINE_SETTER(name)                                                        \
@@ -47,6 +68,8 @@ __device__ __forceinline__ void tl_mark(int kernel, int phase) {
 #else
 namespace tk {
 __device__ __forceinline__ void tl_mark(int, int) {}
+__device__ __forceinline__ void tl_value(int, int, unsigned int) {}
+__device__ __forceinline__ unsigned long long tl_now() { return 0ull; }
 }
 #define TK_TIMELINE_SETTER(name)
 #endif

@@ -508,5 +508,6 @@ class StepFunction:
     def _raise_on_error(self, word: list[int]) -> None:
         if word[0] != 0:
             self.buffers.result[:4].zero_()
+            ops.reset_workspaces()      # counters that a kernel which gave up may have left non-zero
             raise StepError(f"kernel error {word[0]} ({_ERR_NAMES.get(word[0], 'unknown')}); "
                             f"details {word[1:]}")

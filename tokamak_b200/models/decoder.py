@@ -138,4 +138,7 @@ class DecoderModel:
         h = self.final_norm.add_norm(resid, pending, rows=None if all_rows and isinstance(pending, OwedNorm) else step.logits_rows)
         if isinstance(h, OwedNorm) and not getattr(self.head, "TAKES_OWED_NORM", False):
             h = h.materialize()
-        return self.head.forward(h, step.err)
+        logits = self.head.forward(h, step)
+        from ..csrc import ops
+        ops.flush_chains()          # products that are still queued: the caller reads the logits
+        return logits

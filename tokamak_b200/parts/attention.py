@@ -9,8 +9,8 @@ import torch
 
 from ..cache.manager import KVPagesNeed
 from ..csrc import ops
-from .base import (MIXERS, POSITIONS, SWAPPED_GEMM_MAX_TOKENS, OwedNorm, Runtime, TensorReq, graph_safe,
-                   linear, tensor_bytes)
+from .base import (MIXERS, POSITIONS, SWAPPED_GEMM_MAX_TOKENS, OwedNorm, Runtime, TensorReq, chain_of,
+                   graph_safe, linear, tensor_bytes)
 
 
 @dataclass(frozen=True)
@@ -111,12 +111,13 @@ class Attention:
                               step.tok_req, step.req_slot, cache_view.table, self.q_norm_w, self.k_norm_w,
                               table, n_q_heads=spec.num_heads, n_kv_heads=spec.num_kv_heads,
                               eps=spec.qk_norm_eps or 0.0, max_stages=stages, colscale=colscale,
-                              req_q_len=step.req_q_len, req_kv_len=step.req_kv_len)
+                              req_q_len=step.req_q_len, req_kv_len=step.req_kv_len, chain=chain_of(step))
         else:
             self._project_and_rotate(h, q, table, rotary_dim, step, cache_view)
         out = torch.empty_like(q)
         paged_attention(q, out, cache_view, step, scale=self.scale, window=spec.window)
-        return linear(out.view(n, spec.num_heads * spec.head_dim), self.w_o, err=step.err, then_norm=then_norm)
+        return linear(out.view(n, spec.num_heads * spec.head_dim), self.w_o, err=step.err, then_norm=then_norm,
+                      chain=chain_of(step))
 
     def _project_and_rotate(self, h, q, table, rotary_dim, step, cache_view) -> None:
         """The q|k|v product, then norm, rotation and page write in a kernel of their own."""
@@ -152,6 +153,7 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
     prefill kernel (or to the mma.sync one for page sizes it does not take).  float32,
     and every other shape, runs on the general kernel.
     """
+    ops.flush_chains()     # q and the pages may come from a product that is still queued: launch it on this stream
     n, hq, d = q.shape
     hkv, page = cache_view.k.shape[1], cache_view.k.shape[2]
     bf16 = q.dtype == torch.bfloat16

@@ -27,7 +27,7 @@ block          ``expected_tensors(spec)``, ``__init__(spec, tensors, rt)``,
 embedding      ``expected_tensors(spec)``, ``__init__(spec, tensors, rt)``,
                ``forward(step) -> float32 residual rows [N, hidden]``, attribute ``weight``
 head           ``expected_tensors(spec)``, ``__init__(spec, embedding part, tensors, rt)``,
-               ``forward(h, err) -> float32 logits [rows, vocab]``
+               ``forward(h, step) -> float32 logits [rows, vocab]``
 =============  ==========================================================
 
 No part knows which model it is in: it sees its spec, its tensors, the step's
@@ -56,6 +56,17 @@ may return an :class:`OwedNorm` prepared for that norm instead of its output; on
 block with ``TAKES_NEXT_NORM = True`` is told which norm will consume what it leaves pending and
 names the norm that consumes its own input as ``entry_norm``.  Parts without these attributes
 never see any of it.
+
+**Queued products.**  In those same steps the products of consecutive parts (attention output,
+gate/up, down, the next block's q|k|v, the head) are not launched one by one: :func:`linear` and the
+fused product wrappers queue them in the step's :class:`~tokamak_b200.csrc.ops.ProductChain`
+(:func:`chain_of`), and the queue is launched as one persistent kernel when something else needs a
+result: every kernel wrapper of ``csrc/ops.py`` flushes it before it launches, and so do
+:meth:`OwedNorm.materialize` and the end of the model's forward pass.  Only an :class:`OwedNorm`
+carries results across parts that may still be queued, so the rule for a part that opts into owed
+norms is: hand its tensors to :func:`linear` or to kernels of this library, or call ``materialize()``;
+never read ``xb`` or ``sumsq`` with other code.  A part that passes ``chain=`` to :func:`linear` itself
+holds to the same rule for what it gets back.
 
 Where a row says ``[N, hidden]`` a mixer or feed-forward may instead return what
 :func:`linear` gave it: a 3-D float32 tensor of partial sums ``[parts, N, hidden]``
@@ -189,16 +200,35 @@ class OwedNorm:
 
     def materialize(self) -> torch.Tensor:
         """The normalised rows as an ordinary tensor (for a consumer that cannot pay the scale)."""
+        from ..csrc import ops
+        ops.flush_chains()          # the product that prepares xb and sumsq may still be queued
         rstd = torch.rsqrt(self.sumsq.sum(0) / self.dim + self.eps)
         return (self.xb.float() * rstd[:, None]).to(self.xb.dtype)
 
     def rows(self, index: torch.Tensor) -> "OwedNorm":
+        from ..csrc import ops
+        ops.flush_chains()
         return OwedNorm(self.xb.index_select(0, index.long()).contiguous(),
                         self.sumsq.index_select(1, index.long()).contiguous(), self.dim, self.eps, self.norm)
 
 
+def chain_of(step):
+    """The queue of products of a step of few tokens (made on first use), or ``None`` where products
+    are launched one by one: no step, more tokens than the chain kernel takes."""
+    from ..csrc import ops
+    scratch = getattr(step, "scratch", None)
+    n = getattr(step, "n_tokens", 0)
+    if scratch is None or ops.CHAIN_POLICY != "on" or not ops.ProductChain.takes(n, 128):
+        return None
+    chain = scratch.get("chain")
+    if chain is None:
+        chain = scratch["chain"] = ops.ProductChain(n, step.err)
+    return chain
+
+
 def linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
-           err: torch.Tensor | None = None, then_norm: tuple | None = None):
+           err: torch.Tensor | None = None, then_norm: tuple | None = None, chain=None,
+           queue_plain: bool = False):
     """``x @ weight^T`` for ``weight`` of shape [out, in].
 
     float32: the engine's own FFMA kernel (no TF32, no tensor cores).
@@ -211,7 +241,10 @@ def linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
     kernel multiplies its sums by the owed scale), and with ``then_norm=(resid, norm part)`` the
     kernel adds its sums to the float32 residual stream ``resid`` itself and an :class:`OwedNorm`
     for that norm is returned instead of the product (where the sizes allow it; otherwise the
-    product is returned as usual).
+    product is returned as usual).  With ``chain`` (see :func:`chain_of`) a product that returns an
+    :class:`OwedNorm` is queued rather than launched; a product that returns plain sums is launched
+    at once (with everything queued before it), so that a tensor handed on to other parts always
+    holds its values, unless the caller says ``queue_plain`` and flushes the queue itself.
 
     bfloat16, many tokens: the persistent tcgen05 kernel on pairs of SMs (``ops.gemm_pair``)
     where its grid fills the GPU; otherwise the library product, as the reference uses the
@@ -234,9 +267,13 @@ def linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
                     and resid.shape == (x.shape[0], weight.shape[0])):
                 norm_weight, eps = params
                 xb, sumsq = ops.gemm_tc_swapped(weight, x, err, splits, max_stages=stages, cluster=cluster,
-                                                colscale=colscale, residual_norm=(resid, norm_weight))
+                                                colscale=colscale, residual_norm=(resid, norm_weight), chain=chain)
                 return OwedNorm(xb, sumsq, weight.shape[0], eps, norm)
-        return ops.gemm_tc_swapped(weight, x, err, splits, max_stages=stages, cluster=cluster, colscale=colscale)
+        out = ops.gemm_tc_swapped(weight, x, err, splits, max_stages=stages, cluster=cluster, colscale=colscale,
+                                  chain=chain)
+        if chain is not None and not queue_plain:
+            ops.flush_chains()
+        return out
     if isinstance(x, OwedNorm):
         x = x.materialize()
     if out_dtype is not None and out_dtype != x.dtype:

@@ -7,7 +7,7 @@ from dataclasses import dataclass
 import torch
 
 from ..csrc import ops
-from .base import EMBEDDINGS, HEADS, Runtime, TensorReq, linear, sum_parts, tensor_bytes
+from .base import EMBEDDINGS, HEADS, Runtime, TensorReq, chain_of, linear, sum_parts, tensor_bytes
 
 
 @dataclass(frozen=True)
@@ -76,5 +76,8 @@ class Head:
         # a tied checkpoint may still carry the head; it is then ignored
         return {spec.name: TensorReq((spec.vocab_size, spec.hidden_size), optional=spec.tied)}
 
-    def forward(self, h: torch.Tensor, err: torch.Tensor | None = None) -> torch.Tensor:
-        return sum_parts(linear(h, self.weight, out_dtype=torch.float32, err=err), torch.float32)
+    def forward(self, h: torch.Tensor, step=None) -> torch.Tensor:
+        # queued with the products before it; the model flushes the queue before it returns the logits
+        logits = linear(h, self.weight, out_dtype=torch.float32, err=getattr(step, "err", None), chain=chain_of(step),
+                        queue_plain=True)
+        return sum_parts(logits, torch.float32)

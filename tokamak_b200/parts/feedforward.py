@@ -7,7 +7,8 @@ from dataclasses import dataclass
 import torch
 
 from ..csrc import ops
-from .base import FEED_FORWARDS, SWAPPED_GEMM_MAX_TOKENS, OwedNorm, Runtime, TensorReq, linear, tensor_bytes
+from .base import (FEED_FORWARDS, SWAPPED_GEMM_MAX_TOKENS, OwedNorm, Runtime, TensorReq, chain_of, linear,
+                   tensor_bytes)
 
 
 @dataclass(frozen=True)
@@ -63,6 +64,7 @@ class SwiGLU:
 
     def forward(self, h, step, then_norm=None):
         err = step.err if step is not None else None
+        chain = chain_of(step)
         n = h.shape[0]
         if (h.dtype == torch.bfloat16 and err is not None and n <= SWAPPED_GEMM_MAX_TOKENS
                 and self.block == ops.SWIGLU_TILE_BLOCK and self.spec.hidden_size % 8 == 0):
@@ -71,7 +73,7 @@ class SwiGLU:
             if isinstance(h, OwedNorm):
                 colscale, h = (h.sumsq, h.dim, h.eps), h.xb
             act = ops.gemm_tc_swapped(self.w_gate_up, h, err, splits, max_stages=stages, cluster=cluster,
-                                      swiglu=True, colscale=colscale)
+                                      swiglu=True, colscale=colscale, chain=chain)
         else:
             if isinstance(h, OwedNorm):
                 h = h.materialize()
@@ -83,4 +85,4 @@ class SwiGLU:
                 gate_up = linear(h, self.w_gate_up, err=err)
                 act = torch.empty((n, self.spec.intermediate_size), dtype=h.dtype, device=h.device)
                 ops.swiglu(gate_up, act, block=self.block)
-        return linear(act, self.w_down, err=err, then_norm=then_norm)
+        return linear(act, self.w_down, err=err, then_norm=then_norm, chain=chain)
