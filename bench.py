@@ -437,22 +437,27 @@ def kernel_case(name: str, batch: int, ctx: int, iters: int, peaks: dict) -> dic
     err = torch.zeros(4, dtype=torch.int32, device=dev)
     gen = torch.Generator(device=dev).manual_seed(0)
     flops = 0.0
-    if name in ("attention_decode", "attention_prefill", "attention_prefill_mma"):
+    if name in ("attention_decode", "attention_decode_split", "attention_prefill", "attention_prefill_mma"):
         pages_per_req = -(-ctx // page)
         num_pages = batch * pages_per_req
         kc = torch.randn((num_pages, hkv, page, d), device=dev, generator=gen).bfloat16()
         vc = torch.randn((num_pages, hkv, page, d), device=dev, generator=gen).bfloat16()
         table = torch.randperm(num_pages, device=dev, generator=gen).to(torch.int32).view(batch, pages_per_req)
         slots = i32(list(range(batch)))
-        if name == "attention_decode":
+        if name in ("attention_decode", "attention_decode_split"):
             q = torch.randn((batch, hq, d), device=dev, generator=gen).bfloat16()
             out = torch.empty_like(q)
             items, tok_req = i32(list(range(batch))), i32(list(range(batch)))
             positions = i32([ctx - 1] * batch)
-            n_splits = ops.decode_splits(batch, hkv, ctx)
-            scratch = torch.empty(batch * hq * n_splits * (d + 2), dtype=torch.float32, device=dev)
-            run = lambda: ops.attention_decode(q, out, kc, vc, items, positions, tok_req, slots, table, err,
-                                               scale=d ** -0.5, window=None, n_splits=n_splits, scratch=scratch)
+            if name == "attention_decode":          # the kernel the engine uses: key tiles dealt out evenly
+                blocks = ops.decode_balanced_blocks(q.device, batch, hkv, ctx)
+                run = lambda: ops.attention_decode_balanced(q, out, kc, vc, items, positions, tok_req, slots, table,
+                                                            err, scale=d ** -0.5, window=None, blocks=blocks)
+            else:                                   # the same number of splits for every (token, kv head)
+                n_splits = ops.decode_splits(batch, hkv, ctx)
+                scratch = torch.empty(batch * hq * n_splits * (d + 2), dtype=torch.float32, device=dev)
+                run = lambda: ops.attention_decode(q, out, kc, vc, items, positions, tok_req, slots, table, err,
+                                                   scale=d ** -0.5, window=None, n_splits=n_splits, scratch=scratch)
             nbytes = 2 * kc.numel() * 2 + 2 * q.numel() * 2
         else:
             q = torch.randn((batch * ctx, hq, d), device=dev, generator=gen).bfloat16()
@@ -594,7 +599,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="leave out the further batch sizes")
     ap.add_argument("--points", type=lambda v: [int(x) for x in v.split(",") if x], default=[1, 64],
                     help="further decode batch sizes to time, comma-separated (default 1,64)")
-    ap.add_argument("--kernel", default=None, help="time one kernel alone instead: attention_decode, "
+    ap.add_argument("--kernel", default=None, help="time one kernel alone instead: attention_decode, attention_decode_split, "
                     "attention_prefill (tcgen05), attention_prefill_mma, rope_kv, rmsnorm, gemm_tc_decode, gemm_decode (library), "
                     "gemm_pair_swiglu, gemm_prefill_library (--ctx tokens)")
     ap.add_argument("--ctx", type=int, default=CONTEXT, help="context length of a --kernel case")

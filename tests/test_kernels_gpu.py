@@ -373,16 +373,19 @@ def run_decode(q, kc, vc, items, positions, tok_req, table, scale, window, n_spl
     from tokamak_b200.csrc import ops
     err = err_word()
     out = torch.full_like(q, float("nan"))
-    ops.attention_decode(q, out, kc, vc, torch.tensor(items, dtype=torch.int32, device=DEV),
-                         torch.tensor(positions, dtype=torch.int32, device=DEV),
-                         torch.tensor(tok_req, dtype=torch.int32, device=DEV),
-                         torch.arange(table.shape[0], dtype=torch.int32, device=DEV), table.to(DEV), err,
-                         scale=scale, window=window, n_splits=n_splits)
+    args = (q, out, kc, vc, torch.tensor(items, dtype=torch.int32, device=DEV),
+            torch.tensor(positions, dtype=torch.int32, device=DEV),
+            torch.tensor(tok_req, dtype=torch.int32, device=DEV),
+            torch.arange(table.shape[0], dtype=torch.int32, device=DEV), table.to(DEV), err)
+    if n_splits > 0:
+        ops.attention_decode(*args, scale=scale, window=window, n_splits=n_splits)
+    else:           # the kernel that deals the key tiles out evenly, over -n_splits blocks
+        ops.attention_decode_balanced(*args, scale=scale, window=window, blocks=-n_splits)
     assert err.tolist()[0] == 0
     return out
 
 
-@pytest.mark.parametrize("n_splits", [1, 3, 8, 33])
+@pytest.mark.parametrize("n_splits", [1, 3, 8, 33, -1, -2, -7, -37, -296, -512])
 @pytest.mark.parametrize("hq,hkv,d,page,window", [(8, 2, 128, 16, None), (32, 8, 128, 16, None),
                                                     (6, 1, 64, 16, None), (16, 1, 64, 32, None),
                                                     (4, 4, 128, 16, 24), (14, 2, 64, 16, 7),
@@ -414,6 +417,10 @@ def test_attention_decode_split_k(hq, hkv, d, page, window, n_splits):
                                [tok_req[i] for i in items], scale, window)
     torch.testing.assert_close(out[items].double().cpu(), want, **tol(torch.bfloat16))
     assert torch.isnan(out[[i - 1 for i in items]].float()).all()       # other rows are not touched
+    if n_splits < 0:
+        # the counters are back at zero and the scratch may hold anything: a second call gives the same bits
+        again = run_decode(q.to(DEV), kc, vc, items, positions, tok_req, table, scale, window, n_splits)
+        assert torch.equal(again[items], out[items])
 
 
 @pytest.mark.parametrize("where", ["first", "far", "page_edge", "last", "window_edge", "just_outside"])
@@ -436,10 +443,11 @@ def test_attention_decode_finds_the_one_key_that_matters(where):
     max_pages = -(-kv_len // page)
     table = make_tables(1, max_pages, max_pages + 9, seed=2)
     kc, vc = fill_cache([k], [v], table, max_pages + 9, page, torch.bfloat16)
-    out = run_decode(q.bfloat16().to(DEV), kc, vc, [0], [kv_len - 1], [0], table, 1.0, window,
-                     n_splits=5).double().cpu()
     want = attention_reference(q, [k], [v], [kv_len - 1], [0], 1.0, window)
-    torch.testing.assert_close(out, want, **tol(torch.bfloat16))
+    for n_splits in (-11, 5):       # the kernel that deals the tiles out evenly (11 blocks), the one with 5 splits
+        out = run_decode(q.bfloat16().to(DEV), kc, vc, [0], [kv_len - 1], [0], table, 1.0, window,
+                         n_splits=n_splits).double().cpu()
+        torch.testing.assert_close(out, want, **tol(torch.bfloat16))
     hit = torch.stack([v[target, h // (hq // hkv)] for h in range(hq)]).double()
     if where == "just_outside":
         assert (out[0] - hit).abs().max() > 0.1

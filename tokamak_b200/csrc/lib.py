@@ -37,6 +37,9 @@ _SIGNATURES: dict[str, list] = {
     "tk_attention_decode": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                             c_float, _P],
+    "tk_attention_decode_balanced": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
+                                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                     c_float, _P],
     "tk_attention_prefill": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                              c_float, _P],
@@ -71,7 +74,8 @@ def library() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = c_int
-    for name, args in (("tk_gemm_chain_scratch_floats", [c_int]), ("tk_gemm_chain_counter_ints", [c_int])):
+    for name, args in (("tk_gemm_chain_scratch_floats", [c_int]), ("tk_gemm_chain_counter_ints", [c_int]),
+                       ("tk_attention_decode_balanced_scratch_floats", [c_int, c_int])):
         fn = getattr(lib, name)
         fn.argtypes = args
         fn.restype = c_longlong

@@ -357,6 +357,72 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
            "attention_decode")
 
 
+# Which decode attention kernel the mixer uses: "balanced" deals the key tiles of all (token, kv head)
+# pairs out evenly over two blocks per SM; "split" gives every pair the same number of splits; "auto"
+# takes the balanced kernel where there are more pairs than blocks that run at a time, so that
+# equal splits would run as a full wave and a partly filled one (at the Qwen3-8B head sizes and
+# context 4,096, inside the decode step: 6,700 against 6,300 tokens/s at batch 64, but 2,010 against
+# 2,090 at batch 8, where every block of the balanced kernel ends in a part that has to be merged).
+DECODE_ATTENTION = os.environ.get("TOKAMAK_B200_DECODE_ATTENTION", "auto")
+DECODE_BALANCED_MAX_ITEMS = 1024
+DECODE_BALANCED_MAX_BLOCKS = 512
+_SM_COUNT: dict = {}
+_BALANCED_SCRATCH: dict = {}
+
+
+def decode_balanced_blocks(device: torch.device, n_items: int, n_kv_heads: int, max_kv_len: int) -> int:
+    """Blocks of the balanced decode kernel: two per SM, fewer where that would leave a block with
+    less than eight 16-key tiles (``max_kv_len`` bounds the longest context)."""
+    sms = _SM_COUNT.get(device)
+    if sms is None:
+        sms = _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    tiles = n_items * n_kv_heads * max(1, -(-max_kv_len // 16))
+    return max(1, min(2 * sms, DECODE_BALANCED_MAX_BLOCKS, tiles // 8))
+
+
+def decode_uses_balanced(device: torch.device, n_items: int, n_kv_heads: int) -> bool:
+    """Whether the mixer should take the balanced decode kernel for this many single tokens."""
+    if DECODE_ATTENTION == "split" or n_items > DECODE_BALANCED_MAX_ITEMS:
+        return False
+    if DECODE_ATTENTION == "balanced":
+        return True
+    decode_balanced_blocks(device, 1, 1, 16)           # makes sure the SM count is known
+    return n_items * n_kv_heads > 2 * _SM_COUNT[device]
+
+
+def attention_decode_balanced(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                              items: torch.Tensor, positions: torch.Tensor, tok_req: torch.Tensor,
+                              req_slot: torch.Tensor, block_table: torch.Tensor, err: torch.Tensor, *,
+                              scale: float, window: int | None, blocks: int) -> None:
+    """Paged attention for the single next tokens listed in ``items`` (bfloat16 only), the key tiles of
+    all (token, kv head) pairs dealt out evenly over ``blocks`` blocks."""
+    _want(q, torch.bfloat16, "q"); _want(out, torch.bfloat16, "out")
+    _want(k_cache, torch.bfloat16, "k_cache"); _want(v_cache, torch.bfloat16, "v_cache")
+    _want(items, torch.int32, "items")
+    n, hq, d = q.shape
+    num_pages, hkv, page_size, dk = k_cache.shape
+    n_items = items.numel()
+    if (not decode_kernel_takes(hq, hkv, d, page_size) or n_items > DECODE_BALANCED_MAX_ITEMS
+            or not 1 <= blocks <= DECODE_BALANCED_MAX_BLOCKS):
+        raise KernelError(f"the balanced decode kernel does not take heads {hq}/{hkv}, head_dim {d}, "
+                          f"page size {page_size}, {n_items} tokens, {blocks} blocks")
+    lib = _lib()
+    need = lib.tk_attention_decode_balanced_scratch_floats(blocks, d)
+    scratch = _BALANCED_SCRATCH.get(q.device)
+    if scratch is None or scratch.numel() < need:
+        if scratch is not None:
+            _RETIRED_COUNTERS.append(scratch)        # captured graphs still hold its address
+        scratch = _BALANCED_SCRATCH[q.device] = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=q.device)
+    counters = _decode_counters(q.device, n_items * hkv)
+    _check(lib.tk_attention_decode_balanced(q.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                            scratch.data_ptr(), counters.data_ptr(), items.data_ptr(),
+                                            positions.data_ptr(), tok_req.data_ptr(), req_slot.data_ptr(),
+                                            block_table.data_ptr(), err.data_ptr(), n_items, req_slot.numel(),
+                                            hq, hkv, d, page_size, block_table.shape[1], num_pages,
+                                            int(window or 0), blocks, float(scale), _stream()),
+           "attention_decode_balanced")
+
+
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                       tiles: torch.Tensor, req_q_start: torch.Tensor, req_q_len: torch.Tensor,
                       req_kv_len: torch.Tensor, req_slot: torch.Tensor, block_table: torch.Tensor,

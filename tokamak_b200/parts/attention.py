@@ -171,9 +171,15 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
         side.wait_event(fork)
     if dec_tiled:
         with torch.cuda.stream(side) if beside else contextlib.nullcontext():
-            ops.attention_decode(q, out, cache_view.k, cache_view.v, step.decode_items, step.positions,
-                                 step.tok_req, step.req_slot, cache_view.table, step.err, scale=scale,
-                                 window=window, n_splits=ops.decode_splits(n_dec, hkv, step.max_kv_len))
+            if ops.decode_uses_balanced(q.device, n_dec, hkv):
+                ops.attention_decode_balanced(q, out, cache_view.k, cache_view.v, step.decode_items, step.positions,
+                                              step.tok_req, step.req_slot, cache_view.table, step.err, scale=scale,
+                                              window=window,
+                                              blocks=ops.decode_balanced_blocks(q.device, n_dec, hkv, step.max_kv_len))
+            else:
+                ops.attention_decode(q, out, cache_view.k, cache_view.v, step.decode_items, step.positions,
+                                     step.tok_req, step.req_slot, cache_view.table, step.err, scale=scale,
+                                     window=window, n_splits=ops.decode_splits(n_dec, hkv, step.max_kv_len))
             if beside:
                 join.record()
     if pf_tiled and ops.prefill_tc_kernel_takes(hq, hkv, d, page):
