@@ -558,6 +558,61 @@ def kernel_case(name: str, batch: int, ctx: int, iters: int, peaks: dict) -> dic
     return res
 
 
+def decode_timeline(batch: int, layers: int, ctx: int) -> int:
+    """Lay the blocks of every kernel of two decode steps out on one time axis (the library must have
+    been built with time stamps: TOKAMAK_B200_NVCC_FLAGS=-DTK_TIMELINE, see csrc/timeline.cuh).
+    Prints, per kernel instance, when its blocks started, were released by the kernel before, finished
+    their products and ended, in microseconds from the first stamp."""
+    import torch
+    from tokamak_b200.csrc import ops
+    from tokamak_b200.engine.core import random_core
+    from tokamak_b200.engine.step import SamplingRow, StepEntry
+    raw = dict(QWEN3_8B, num_hidden_layers=layers)
+    core = random_core(raw, seed=0, std=0.02, dtype="bfloat16", max_seq_len=ctx, page_size=16,
+                       pool_tokens=batch * ctx, max_slots=batch, max_step_tokens=2048)
+    step = core.step
+    ids = [f"r{i}" for i in range(batch)]
+    for r in ids:
+        step.admit(r, SamplingRow())
+    fill_context(core, ids, ctx - 40, raw["vocab_size"], seed=1)
+    step.run_and_sample([StepEntry(r, [1 + i], [0]) for i, r in enumerate(ids)])
+    entries = [StepEntry(r, None, [0]) for r in ids]
+    for _ in range(6):
+        step.run_and_sample(entries)
+    buf = ops.timeline_start(1 << 18)
+    first, second = step.launch_and_sample(entries), step.launch_and_sample(entries)
+    step.collect(first); step.collect(second)
+    recs = ops.timeline_read(buf)
+    names = {1: "begin", 2: "attention", 3: "sample", 4: "embed", 10: "product", 11: "product+swiglu",
+             12: "product+residual", 13: "q|k|v+rope", 20: "chain"}
+    t0 = recs[0][0]
+    by_kernel: dict = {}
+    for t, k, ph, sm, blk in recs:
+        by_kernel.setdefault(k, []).append((t - t0, ph))
+    instances = []
+    for k, rows in by_kernel.items():
+        if k not in names:
+            continue
+        cur, last_start = None, None
+        for t, ph in sorted(rows):
+            if ph == 0 and (last_start is None or t - last_start > 4000):     # a gap of 4 us: another launch
+                cur = {"k": k, "ph": {}}
+                instances.append(cur)
+            if ph == 0:
+                last_start = t
+            if cur is not None:
+                cur["ph"].setdefault(ph, []).append(t)
+    instances.sort(key=lambda i: min(i["ph"][0]))
+    rng = lambda v: f"{min(v) / 1e3:7.1f}-{max(v) / 1e3:7.1f}" if v else " " * 15
+    print(f"batch {batch}, {layers} layers of Qwen3-8B sizes, context {ctx}: two decode steps, us from the first stamp")
+    print(f"{'kernel':17s} {'blocks':>6s} {'started':>15s} {'released':>15s} {'products done':>15s} {'ended':>15s}")
+    for i in instances:
+        ph = i["ph"]
+        done = ph.get(2, []) if i["k"] != 20 else [t for q in ph if 31 <= q < 40 for t in ph[q]]
+        print(f"{names[i['k']]:17s} {len(ph[0]):6d} {rng(ph.get(0))} {rng(ph.get(1))} {rng(done)} {rng(ph.get(4))}")
+    return 0
+
+
 def reference_main(args) -> int:
     """``--impl reference``: the unmodified reference from ``baseline/_ref`` on the same metric, or
     one line that says why it cannot run.  Everything it does is in ``baseline/reference_arm.py``."""
@@ -601,7 +656,8 @@ def main() -> int:
                     help="further decode batch sizes to time, comma-separated (default 1,64)")
     ap.add_argument("--kernel", default=None, help="time one kernel alone instead: attention_decode, attention_decode_split, "
                     "attention_prefill (tcgen05), attention_prefill_mma, rope_kv, rmsnorm, gemm_tc_decode, gemm_decode (library), "
-                    "gemm_pair_swiglu, gemm_prefill_library (--ctx tokens)")
+                    "gemm_pair_swiglu, gemm_prefill_library (--ctx tokens); decode_timeline prints when the blocks of every "
+                    "kernel of a decode step run (needs a library built with TOKAMAK_B200_NVCC_FLAGS=-DTK_TIMELINE)")
     ap.add_argument("--ctx", type=int, default=CONTEXT, help="context length of a --kernel case")
     ap.add_argument("--workload", default=None, choices=["throughput", "latency", "mixed"],
                     help="run the reference's throughput workload through LLM.generate, or its single-sequence "
@@ -630,6 +686,8 @@ def main() -> int:
         return 2
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
+    if args.kernel == "decode_timeline":
+        return decode_timeline(args.batch, args.layers or 3, args.ctx)
     if args.kernel:
         print(json.dumps(kernel_case(args.kernel, args.batch, args.ctx, steps, load_peaks())))
         return 0
