@@ -359,10 +359,11 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
 
 # Which decode attention kernel the mixer uses: "balanced" deals the key tiles of all (token, kv head)
 # pairs out evenly over two blocks per SM; "split" gives every pair the same number of splits; "auto"
-# takes the balanced kernel where there are more pairs than blocks that run at a time, so that
-# equal splits would run as a full wave and a partly filled one (at the Qwen3-8B head sizes and
-# context 4,096, inside the decode step: 6,700 against 6,300 tokens/s at batch 64, but 2,010 against
-# 2,090 at batch 8, where every block of the balanced kernel ends in a part that has to be merged).
+# takes the balanced kernel where there are more pairs than blocks that run at a time (equal splits
+# would run as a full wave and a partly filled one) or where a block gets some 320 tiles or more, so
+# that its one or two merged parts weigh little.  Inside the decode step at the Qwen3-8B head sizes:
+# batch 64, context 4,096: 6,700 against 6,300 tokens/s; batch 8, context 32,768: 895 against 864;
+# batch 8, context 16,384: 1,313 against 1,327; batch 8, context 4,096: 2,010 against 2,090.
 DECODE_ATTENTION = os.environ.get("TOKAMAK_B200_DECODE_ATTENTION", "auto")
 DECODE_BALANCED_MAX_ITEMS = 1024
 DECODE_BALANCED_MAX_BLOCKS = 512
@@ -380,14 +381,17 @@ def decode_balanced_blocks(device: torch.device, n_items: int, n_kv_heads: int, 
     return max(1, min(2 * sms, DECODE_BALANCED_MAX_BLOCKS, tiles // 8))
 
 
-def decode_uses_balanced(device: torch.device, n_items: int, n_kv_heads: int) -> bool:
-    """Whether the mixer should take the balanced decode kernel for this many single tokens."""
+def decode_uses_balanced(device: torch.device, n_items: int, n_kv_heads: int, max_kv_len: int) -> bool:
+    """Whether the mixer should take the balanced decode kernel for this many single tokens whose
+    longest context is at most ``max_kv_len``."""
     if DECODE_ATTENTION == "split" or n_items > DECODE_BALANCED_MAX_ITEMS:
         return False
     if DECODE_ATTENTION == "balanced":
         return True
     decode_balanced_blocks(device, 1, 1, 16)           # makes sure the SM count is known
-    return n_items * n_kv_heads > 2 * _SM_COUNT[device]
+    blocks = 2 * _SM_COUNT[device]
+    pairs = n_items * n_kv_heads
+    return pairs > blocks or pairs * -(-max_kv_len // 16) >= 320 * blocks
 
 
 def attention_decode_balanced(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,

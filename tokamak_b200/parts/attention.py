@@ -171,7 +171,7 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
         side.wait_event(fork)
     if dec_tiled:
         with torch.cuda.stream(side) if beside else contextlib.nullcontext():
-            if ops.decode_uses_balanced(q.device, n_dec, hkv):
+            if ops.decode_uses_balanced(q.device, n_dec, hkv, step.max_kv_len):
                 ops.attention_decode_balanced(q, out, cache_view.k, cache_view.v, step.decode_items, step.positions,
                                               step.tok_req, step.req_slot, cache_view.table, step.err, scale=scale,
                                               window=window,
