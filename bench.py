@@ -521,6 +521,45 @@ def kernel_case(name: str, batch: int, ctx: int, iters: int, peaks: dict) -> dic
             turn[0] = (turn[0] + 1) % len(ws)
             torch.mm(x, ws[turn[0]].t())
         nbytes = w.numel() * 2
+    elif name in ("products_chain", "products_separate"):
+        # the four products between two attentions of a decode step (output, gate/up, down, the next
+        # q|k|v, each with its fused epilogue) for `batch` tokens: as one persistent kernel, or one by one
+        h, inter = cfg["hidden_size"], cfg["intermediate_size"]
+        mk = lambda *shape, s=1.0: (torch.randn(*shape, device=dev, generator=gen) * s).bfloat16()
+        sets = [dict(o=mk(h, hq * d, s=0.02), gu=mk(2 * inter, h, s=0.02), dn=mk(h, inter, s=0.02),
+                     qkv=mk((hq + 2 * hkv) * d, h, s=0.02)) for _ in range(3)]      # rotated: none stays in L2
+        x0 = mk(batch, hq * d)
+        n1, n2 = torch.ones(h, device=dev), torch.ones(h, device=dev)
+        qn, kn = torch.ones(d, device=dev), torch.ones(d, device=dev)
+        resid = torch.zeros(batch, h, device=dev)
+        pages = 4
+        kc = torch.zeros((pages, hkv, page, d), dtype=torch.bfloat16, device=dev)
+        vc = torch.zeros_like(kc)
+        q = torch.zeros((batch, hq, d), dtype=torch.bfloat16, device=dev)
+        positions = torch.arange(batch, dtype=torch.int32, device=dev) % (pages * page)
+        tok_req, slot0 = torch.zeros(batch, dtype=torch.int32, device=dev), i32([0])
+        table = torch.arange(pages, dtype=torch.int32, device=dev).view(1, pages)
+        inv_freq = (1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(dev)
+        rot = ops.rope_table(positions, inv_freq)
+        plan = lambda w: ops.swapped_gemm_plan(w.shape[0], w.shape[1], batch)
+        turn = [0]
+        def run():
+            turn[0] = (turn[0] + 1) % len(sets)
+            w = sets[turn[0]]
+            c = ops.ProductChain(batch, err) if name == "products_chain" else None
+            resid.zero_()
+            s_, st, cl = plan(w["o"])
+            xb1, ss1 = ops.gemm_tc_swapped(w["o"], x0, err, s_, max_stages=st, cluster=cl, residual_norm=(resid, n1), chain=c)
+            s_, st, cl = plan(w["gu"])
+            act = ops.gemm_tc_swapped(w["gu"], xb1, err, s_, max_stages=st, cluster=cl, swiglu=True,
+                                      colscale=(ss1, h, 1e-6), chain=c)
+            s_, st, cl = plan(w["dn"])
+            xb2, ss2 = ops.gemm_tc_swapped(w["dn"], act, err, s_, max_stages=st, cluster=cl, residual_norm=(resid, n2), chain=c)
+            s_, st, cl = plan(w["qkv"])
+            ops.gemm_qkv_rope(w["qkv"], xb2, err, s_, q, kc, vc, positions, tok_req, slot0, table, qn, kn, rot,
+                              n_q_heads=hq, n_kv_heads=hkv, eps=1e-6, max_stages=st, colscale=(ss2, h, 1e-6), chain=c)
+            ops.flush_chains()
+        nbytes = sum(t.numel() * 2 for t in sets[0].values())
     elif name in ("gemm_pair_swiglu", "gemm_prefill_library"):
         # the prefill gate/up product of one layer over ctx tokens with the activation: the engine's
         # kernel on pairs of SMs with the activation in its epilogue, or the library product followed
@@ -656,7 +695,8 @@ def main() -> int:
                     help="further decode batch sizes to time, comma-separated (default 1,64)")
     ap.add_argument("--kernel", default=None, help="time one kernel alone instead: attention_decode, attention_decode_split, "
                     "attention_prefill (tcgen05), attention_prefill_mma, rope_kv, rmsnorm, gemm_tc_decode, gemm_decode (library), "
-                    "gemm_pair_swiglu, gemm_prefill_library (--ctx tokens); decode_timeline prints when the blocks of every "
+                    "gemm_pair_swiglu, gemm_prefill_library (--ctx tokens), products_chain / products_separate (the four products "
+                    "between two attentions of a decode step, as one kernel or one by one); decode_timeline prints when the blocks of every "
                     "kernel of a decode step run (needs a library built with TOKAMAK_B200_NVCC_FLAGS=-DTK_TIMELINE)")
     ap.add_argument("--ctx", type=int, default=CONTEXT, help="context length of a --kernel case")
     ap.add_argument("--workload", default=None, choices=["throughput", "latency", "mixed"],
