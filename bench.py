@@ -425,13 +425,13 @@ def latency_workload(sizes: str, prompt_tokens: int, new_tokens: int, iters: int
             "inter_token_ms": round(1e3 / tok_s, 3), "iters": iters, "dtype": "bf16", "data": "synthetic"}
 
 
-def kernel_case(name: str, batch: int, ctx: int, iters: int, peaks: dict) -> dict:
+def kernel_case(name: str, batch: int, ctx: int, iters: int, peaks: dict, portion: int = 0, sizes: str = "8b") -> dict:
     """One kernel alone on inputs larger than L2, timed with CUDA events: achieved bytes or flops
     per second against the peak.  Also the small case that ncu captures are made on."""
     import torch
     from tokamak_b200.csrc import ops
     dev = "cuda"
-    cfg = QWEN3_8B
+    cfg = SIZES[sizes][1] if sizes in SIZES else QWEN3_8B
     hq, hkv, d, page = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], 16
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
     err = torch.zeros(4, dtype=torch.int32, device=dev)
@@ -460,17 +460,23 @@ def kernel_case(name: str, batch: int, ctx: int, iters: int, peaks: dict) -> dic
                                                    scale=d ** -0.5, window=None, n_splits=n_splits, scratch=scratch)
             nbytes = 2 * kc.numel() * 2 + 2 * q.numel() * 2
         else:
-            q = torch.randn((batch * ctx, hq, d), device=dev, generator=gen).bfloat16()
+            qn = min(portion or ctx, ctx)         # query tokens of every request: the end of its context
+            q = torch.randn((batch * qn, hq, d), device=dev, generator=gen).bfloat16()
             out = torch.empty_like(q)
-            rows = 64 if name == "attention_prefill_mma" else ops.PREFILL_TC_ROWS
-            fn = ops.attention_prefill if name == "attention_prefill_mma" else ops.attention_prefill_tc
-            tiles = [(r, t) for t in reversed(range(-(-ctx // rows))) for r in range(batch)]
-            tiles_t = i32([x for rt in tiles for x in rt])
-            q_start, q_len = i32([r * ctx for r in range(batch)]), i32([ctx] * batch)
-            run = lambda: fn(q, out, kc, vc, tiles_t, q_start, q_len, q_len, slots, table, err,
-                             scale=d ** -0.5, window=None)
+            q_start, q_len, kv_len = [r * qn for r in range(batch)], [qn] * batch, [ctx] * batch
+            if name == "attention_prefill_mma":
+                tiles = [(r, t) for t in reversed(range(-(-qn // 64))) for r in range(batch)]
+                tiles_t = i32([x for rt in tiles for x in rt])
+                args = (i32(q_start), i32(q_len), i32(kv_len))
+                run = lambda: ops.attention_prefill(q, out, kc, vc, tiles_t, *args, slots, table, err,
+                                                    scale=d ** -0.5, window=None)
+            else:
+                records, n_parts, n_split = ops.prefill_tc_records(q_start, q_len, kv_len, list(range(batch)),
+                                                                    heads=hq, sms=ops.sm_count(q.device))
+                items = ops.PrefillItems(torch.from_numpy(records).to(dev), n_parts, n_split)
+                run = lambda: ops.attention_prefill_tc(q, out, kc, vc, items, table, err, scale=d ** -0.5, window=None)
             nbytes = 2 * kc.numel() * 2 + 2 * q.numel() * 2
-            flops = batch * 2.0 * 2.0 * (ctx * (ctx + 1) / 2) * hq * d
+            flops = batch * 2.0 * 2.0 * (qn * (ctx - qn) + qn * (qn + 1) / 2) * hq * d
     elif name == "rope_kv":
         # q/k norm + rotation + cache write for `batch` tokens of one request (prefill shape)
         n = batch
@@ -705,6 +711,9 @@ def main() -> int:
                          "requests (prompts of 128 to 4,096 tokens in portions of 512 beside decode tokens, 256 "
                          "new tokens each; --sizes 14b is the configuration it is named for), instead")
     ap.add_argument("--prefill-chunk", type=int, default=512, help="portion size of --workload mixed")
+    ap.add_argument("--portion", type=int, default=0,
+                    help="query tokens per request of the attention_prefill kernel cases (the end of a context "
+                         "of --ctx tokens; default: the whole context)")
     ap.add_argument("--sizes", default="8b", choices=["0.6b", "8b", "14b", "32b"],
                     help="layer sizes: of --workload (0.6b, 8b), or of the decode/prefill run (8b, the metric's "
                          "own, 14b, 32b)")
@@ -729,7 +738,7 @@ def main() -> int:
     if args.kernel == "decode_timeline":
         return decode_timeline(args.batch, args.layers or 3, args.ctx)
     if args.kernel:
-        print(json.dumps(kernel_case(args.kernel, args.batch, args.ctx, steps, load_peaks())))
+        print(json.dumps(kernel_case(args.kernel, args.batch, args.ctx, steps, load_peaks(), args.portion, args.sizes)))
         return 0
     if args.workload == "latency":
         print(json.dumps(latency_workload(args.sizes, 512, 128, 3, args.seed)))

@@ -468,19 +468,28 @@ def zero_rest_of_last_pages(kc, vc, table, kv_lens, page):
 
 
 def run_prefill(kernel, q, out, kc, vc, q_lens, kv_lens, q_start, table, scale, window):
+    """kernel: "mma" (mma.sync, 64-token tiles), "tc" (tcgen05, the work list balanced for this
+    device) or "tc_parts" (the same with every block of tokens cut into as many parts as allowed)."""
     from tokamak_b200.csrc import ops
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
-    rows = ops.PREFILL_TC_ROWS if kernel == "tc" else 64
-    tiles = [(r, t) for r in range(len(q_lens)) for t in range(-(-q_lens[r] // rows))][::-1]
-    fn = ops.attention_prefill_tc if kernel == "tc" else ops.attention_prefill
     err = err_word()
-    fn(q, out, kc, vc, i32([x for rt in tiles for x in rt]), i32(q_start), i32(q_lens), i32(kv_lens),
-       i32(list(range(len(q_lens)))), table.to(DEV), err, scale=scale, window=window)
+    slots = list(range(len(q_lens)))
+    if kernel == "mma":
+        tiles = [(r, t) for r in range(len(q_lens)) for t in range(-(-q_lens[r] // 64))][::-1]
+        ops.attention_prefill(q, out, kc, vc, i32([x for rt in tiles for x in rt]), i32(q_start), i32(q_lens),
+                              i32(kv_lens), i32(slots), table.to(DEV), err, scale=scale, window=window)
+    else:
+        sms = ops.sm_count(torch.device(DEV)) if kernel == "tc" else 1 << 20
+        records, n_parts, n_split = ops.prefill_tc_records(q_start, q_lens, kv_lens, slots, heads=q.shape[1], sms=sms)
+        if kernel == "tc_parts":
+            assert n_split > 0 or max(kv_lens) < 2 * ops.PREFILL_TC_MIN_PART * ops.PREFILL_TC_KEYS
+        items = ops.PrefillItems(torch.from_numpy(records).to(DEV), n_parts, n_split)
+        ops.attention_prefill_tc(q, out, kc, vc, items, table.to(DEV), err, scale=scale, window=window)
     torch.cuda.synchronize()
     assert err.tolist()[0] == 0, err.tolist()
 
 
-@pytest.mark.parametrize("kernel", ["mma", "tc"])
+@pytest.mark.parametrize("kernel", ["mma", "tc", "tc_parts"])
 @pytest.mark.parametrize("hq,hkv,d,page,window", [(8, 2, 128, 16, None), (4, 4, 64, 16, None),
                                                     (6, 1, 64, 8, None), (8, 8, 128, 32, 50),
                                                     (3, 1, 128, 16, 200), (10, 5, 64, 4, 9),
@@ -489,10 +498,10 @@ def test_attention_prefill_portions(kernel, hq, hkv, d, page, window):
     """Whole prompts and portions that continue a request, with lengths around the tile sizes
     and the page edges; cache slots that no request has written are NaN."""
     from tokamak_b200.csrc import ops
-    if kernel == "tc" and not ops.prefill_tc_kernel_takes(hq, hkv, d, page):
+    if kernel != "mma" and not ops.prefill_tc_kernel_takes(hq, hkv, d, page):
         pytest.skip("page size not taken by the tcgen05 kernel")
-    kv_lens = [2, 64, 65, 300, 129, 1000, 47, 256, 385]
-    q_lens = [2, 64, 65, 37, 128, 130, 3, 256, 129]      # whole prompts and portions
+    kv_lens = [2, 64, 65, 300, 129, 1000, 47, 256, 385, 1500]
+    q_lens = [2, 64, 65, 37, 128, 130, 3, 256, 129, 700]      # whole prompts and portions
     n_reqs = len(kv_lens)
     max_pages = max(-(-l // page) for l in kv_lens)
     num_pages = n_reqs * max_pages + 5
@@ -501,7 +510,7 @@ def test_attention_prefill_portions(kernel, hq, hkv, d, page, window):
     k_all = [torch.randn(l, hkv, d, generator=gen).bfloat16().float() for l in kv_lens]
     v_all = [torch.randn(l, hkv, d, generator=gen).bfloat16().float() for l in kv_lens]
     kc, vc = fill_cache(k_all, v_all, table, num_pages, page, torch.bfloat16)
-    if kernel == "tc":
+    if kernel != "mma":
         zero_rest_of_last_pages(kc, vc, table, kv_lens, page)
     positions, tok_req, q_start = [], [], []
     for r, (kl, ql) in enumerate(zip(kv_lens, q_lens)):
@@ -516,12 +525,12 @@ def test_attention_prefill_portions(kernel, hq, hkv, d, page, window):
     torch.testing.assert_close(out.double().cpu(), want, **tol(torch.bfloat16))
 
 
-@pytest.mark.parametrize("kernel", ["mma", "tc"])
+@pytest.mark.parametrize("kernel", ["mma", "tc", "tc_parts"])
 @pytest.mark.parametrize("where", ["first", "far", "page_edge", "diagonal", "window_edge", "just_outside"])
 def test_attention_prefill_finds_the_one_key_that_matters(kernel, where):
-    """The last query of a 100-token portion at the end of 900 tokens must find one key."""
+    """The last query of a 100-token portion at the end of 1,300 tokens must find one key."""
     hq, hkv, d, page = 4, 2, 128, 16
-    kv_len, q_len, window = 900, 100, None
+    kv_len, q_len, window = 1300, 100, None
     target = {"first": 0, "far": 123, "page_edge": 16 * 30 - 1, "diagonal": kv_len - 1,
               "window_edge": kv_len - 300, "just_outside": kv_len - 301}[where]
     if where in ("window_edge", "just_outside"):
@@ -538,7 +547,7 @@ def test_attention_prefill_finds_the_one_key_that_matters(kernel, where):
     max_pages = -(-kv_len // page)
     table = make_tables(1, max_pages, max_pages + 9, seed=4)
     kc, vc = fill_cache([k], [v], table, max_pages + 9, page, torch.bfloat16)
-    if kernel == "tc":
+    if kernel != "mma":
         zero_rest_of_last_pages(kc, vc, table, [kv_len], page)
     out = torch.empty(q_len, hq, d, dtype=torch.bfloat16, device=DEV)
     run_prefill(kernel, q.bfloat16().to(DEV), out, kc, vc, [q_len], [kv_len], [0], table, 1.0, window)

@@ -44,10 +44,13 @@ _SIGNATURES: dict[str, list] = {
                              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                              c_float, _P],
     "tk_attention_prefill_tc": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
-                                c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                 c_float, _P],
     "tk_attention_prefill_tc_takes": [c_int, c_int, c_int, c_int],
     "tk_attention_prefill_tc_rows": [],
+    "tk_attention_prefill_tc_keys": [],
+    "tk_attention_prefill_tc_record_ints": [],
+    "tk_attention_prefill_tc_max_parts": [],
     "tk_gemm_bf16_tcgen05": [_P, _P, _P, _P, c_int, c_int, c_int, c_longlong, c_longlong,
                              c_int, c_int, c_int, c_int, c_int,
                              _P, c_int, c_float, c_float, _P, _P, _P, _P, _P],

@@ -8,7 +8,9 @@ is no CPU path: a tensor that is not on a CUDA device is an error.
 from __future__ import annotations
 
 import os
+from dataclasses import dataclass
 
+import numpy as np
 import torch
 
 from .lib import library
@@ -451,31 +453,129 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
                                           float(scale), _stream()), "attention_prefill")
 
 
+PREFILL_TC_ROWS = 256     # query tokens per item of the tcgen05 prefill kernel (two tiles of 128)
+PREFILL_TC_KEYS = 64      # keys per tile
+PREFILL_TC_RECORD = 12    # int32 fields of an item record
+PREFILL_TC_MAX_PARTS = 64
+PREFILL_TC_MIN_PART = 8   # key tiles: shorter parts cost more in hand-overs than they balance
+
+
+@dataclass
+class PrefillItems:
+    """Work list of :func:`attention_prefill_tc`, made by :func:`prefill_tc_records` and uploaded by
+    the caller: ``records`` int32 ``[n, PREFILL_TC_RECORD]`` on the device, and how many parts of cut
+    token blocks and how many cut token blocks it holds (sizes of the scratch memory)."""
+    records: torch.Tensor
+    n_parts: int
+    n_split: int
+
+
+def prefill_tc_records(q_start, q_len, kv_len, slots, *, heads: int, sms: int) -> tuple[np.ndarray, int, int]:
+    """Item records of the tcgen05 prefill kernel for the requests that bring more than one token.
+
+    The tokens of a request are cut into blocks of :data:`PREFILL_TC_ROWS`; block ``b`` visits the
+    64-key tiles ``0 .. (pos0 + rows - 1) // 64`` (``pos0 = kv_len - q_len + 256 b``; a window
+    shortens the walk inside the kernel).  Every block is one item per query head.  The kernel deals
+    items out longest first to one thread block per SM.  Where there are fewer items than half the
+    SMs (one short portion against a long context), every block is cut along its keys into parts of
+    equal length (at least :data:`PREFILL_TC_MIN_PART` tiles each), as many as keep all items in one
+    round over the SMs; the kernel adds the parts up.  Measured on a B200: a cut costs a part about
+    as much as writing its rows out, and the part that adds up a few microseconds more, so with a
+    round of items or more to deal out, cutting loses.  ``heads`` is the number of query heads the
+    list is balanced for (the kernel takes any).
+
+    Returns ``(records, n_parts, n_split)``: int32 ``[n, PREFILL_TC_RECORD]`` with the fields
+    ``tok0, rows, pos0, slot, kt_begin, kt_end, part, n_parts, poff, split, merger`` longest first, the total
+    number of parts of cut blocks, and the number of cut blocks."""
+    blocks = []
+    for r in range(len(q_len)):
+        if q_len[r] <= 1:
+            continue
+        base = kv_len[r] - q_len[r]
+        for b in range(-(-q_len[r] // PREFILL_TC_ROWS)):
+            rows = min(PREFILL_TC_ROWS, q_len[r] - PREFILL_TC_ROWS * b)
+            pos0 = base + PREFILL_TC_ROWS * b
+            blocks.append((q_start[r] + PREFILL_TC_ROWS * b, rows, pos0, slots[r],
+                           (pos0 + rows - 1) // PREFILL_TC_KEYS + 1))
+    # cutting pays only where the SMs would otherwise stand idle: with fewer items than half the SMs,
+    # every block is cut into as many parts as keeps all items in one round over the SMs
+    n_items = len(blocks) * max(1, heads)
+    parts_all = min(max(1, sms) // n_items, PREFILL_TC_MAX_PARTS) if n_items else 1
+    records, poff, split = [], 0, 0
+    for tok0, rows, pos0, slot, n_kt in blocks:
+        parts = max(1, min(parts_all, n_kt // PREFILL_TC_MIN_PART))
+        for i in range(parts):
+            records.append((tok0, rows, pos0, slot, n_kt * i // parts, n_kt * (i + 1) // parts, i, parts,
+                            poff if parts > 1 else 0, split if parts > 1 else 0, 0, 0))
+        if parts > 1:
+            poff += parts
+            split += 1
+    records.sort(key=lambda rec: rec[4] - rec[5])          # longest first; equal lengths keep their order
+    out = np.asarray(records, dtype=np.int32).reshape(-1, PREFILL_TC_RECORD)
+    # the part of a cut block that comes last in the list adds the parts up: the kernel hands items
+    # out in list order, so all the others are running or done when it gets there
+    last_of = {}
+    for i, rec in enumerate(records):
+        if rec[7] > 1:
+            last_of[rec[9]] = i
+    for i in last_of.values():
+        out[i, 10] = 1
+    return out, poff, split
+
+
+_PREFILL_TC_WS: dict = {}
+
+
+def _prefill_tc_workspace(device: torch.device, part_slots: int, counters: int, head_dim: int) -> dict:
+    """Counters (zero between launches) and scratch of the tcgen05 prefill kernel, one set per device."""
+    ws = _PREFILL_TC_WS.get(device)
+    if ws is None:
+        ws = _PREFILL_TC_WS[device] = {"sched": torch.zeros(2, dtype=torch.int32, device=device),
+                                       "count": torch.zeros(1024, dtype=torch.int32, device=device),
+                                       "o": None, "ml": None}
+    if ws["count"].numel() < counters:
+        ws["count"] = torch.zeros(max(counters, 2 * ws["count"].numel()), dtype=torch.int32, device=device)
+    floats = part_slots * 128 * head_dim
+    if floats > 0 and (ws["o"] is None or ws["o"].numel() < floats):
+        ws["o"] = torch.empty(floats, dtype=torch.float32, device=device)
+        ws["ml"] = torch.empty(part_slots * 128 * 2, dtype=torch.float32, device=device)
+    return ws
+
+
 def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
-                         tiles: torch.Tensor, req_q_start: torch.Tensor, req_q_len: torch.Tensor,
-                         req_kv_len: torch.Tensor, req_slot: torch.Tensor, block_table: torch.Tensor,
-                         err: torch.Tensor, *, scale: float, window: int | None) -> None:
-    """Paged flash attention on tcgen05 for the query tiles listed in ``tiles`` (int32
-    ``[n_tiles, 2]``: request row, tile index), each of :data:`PREFILL_TC_ROWS` tokens.  Loads whole pages: the cache must have been
-    written by :func:`rope_kv` with ``req_q_len`` and ``req_kv_len`` given."""
+                         items: PrefillItems, block_table: torch.Tensor, err: torch.Tensor, *,
+                         scale: float, window: int | None) -> None:
+    """Paged flash attention on tcgen05 for the work list ``items`` (see :func:`prefill_tc_records`),
+    a persistent kernel that deals the items out to one block per SM.  Loads whole pages: the cache
+    must have been written by :func:`rope_kv` with ``req_q_len`` and ``req_kv_len`` given.  One call
+    at a time per device: the calls share counters and scratch."""
     _want(q, torch.bfloat16, "q"); _want(out, torch.bfloat16, "out")
     _want(k_cache, torch.bfloat16, "k_cache"); _want(v_cache, torch.bfloat16, "v_cache")
-    _want(tiles, torch.int32, "tiles")
+    _want(items.records, torch.int32, "items.records")
     n, hq, d = q.shape
     num_pages, hkv, page_size, dk = k_cache.shape
     if not prefill_tc_kernel_takes(hq, hkv, d, page_size) or dk != d:
         raise KernelError(f"the tcgen05 prefill kernel does not take heads {hq}/{hkv}, head_dim {d}, "
                           f"page size {page_size}")
-    _check(_lib().tk_attention_prefill_tc(q.data_ptr(), out.data_ptr(), k_cache.data_ptr(),
-                                             v_cache.data_ptr(), tiles.data_ptr(), req_q_start.data_ptr(),
-                                             req_q_len.data_ptr(), req_kv_len.data_ptr(),
-                                             req_slot.data_ptr(), block_table.data_ptr(), err.data_ptr(),
-                                             n, tiles.numel() // 2, req_slot.numel(), hq, hkv, d, page_size,
-                                             block_table.shape[1], num_pages, int(window or 0),
-                                             float(scale), _stream()), "attention_prefill_tc")
+    if items.records.dim() != 2 or items.records.shape[1] != PREFILL_TC_RECORD:
+        raise KernelError(f"item records want {PREFILL_TC_RECORD} fields, got shape {tuple(items.records.shape)}")
+    ws = _prefill_tc_workspace(q.device, items.n_parts * hq * 2, items.n_split * hq * 2, d)
+    part_o = ws["o"].data_ptr() if items.n_parts > 0 else 0
+    part_ml = ws["ml"].data_ptr() if items.n_parts > 0 else 0
+    _check(_lib().tk_attention_prefill_tc(q.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                          items.records.data_ptr(), block_table.data_ptr(), err.data_ptr(),
+                                          ws["sched"].data_ptr(), part_o, part_ml, ws["count"].data_ptr(),
+                                          n, items.records.shape[0], hq, hkv, d, page_size,
+                                          block_table.shape[1], num_pages, int(window or 0),
+                                          float(scale), _stream()), "attention_prefill_tc")
 
 
-PREFILL_TC_ROWS = 256     # query tokens per block of the tcgen05 prefill kernel (two tiles of 128)
+def sm_count(device: torch.device) -> int:
+    """Streaming multiprocessors of the device."""
+    sms = _SM_COUNT.get(device)
+    if sms is None:
+        sms = _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return sms
 
 
 def prefill_tc_kernel_takes(n_q_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> bool:
@@ -668,6 +768,9 @@ def reset_workspaces() -> None:
         counters.zero_()
     for buf in _DECODE_COUNTERS.values():
         buf.zero_()
+    for ws in _PREFILL_TC_WS.values():
+        ws["sched"].zero_()
+        ws["count"].zero_()
 
 
 class ProductChain:
@@ -877,7 +980,8 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
                                out_tokens.data_ptr(), rows, vocab, _stream()), "sample")
 
 
-_TIMELINE_FILES = ("gemm_tcgen05", "gemm_chain", "attention_decode", "sampling", "step_state", "elementwise")
+_TIMELINE_FILES = ("gemm_tcgen05", "gemm_chain", "attention_decode", "attention_prefill_tc", "sampling", "step_state",
+                   "elementwise")
 
 
 def timeline_start(capacity: int = 1 << 20) -> torch.Tensor:

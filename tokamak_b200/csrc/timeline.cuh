@@ -57,6 +57,20 @@ __device__ __forceinline__ unsigned long long tl_now() {
   asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
   return t;
 }
+// A cheap mark for one chosen thread: no atomic, the thread counts its own records (`count`) in
+// its own range of 1,024 records at the end of the buffer (`lane` picks the range).  The host sets the buffer's count to
+// its capacity before it reads, and skips the empty records.
+__device__ __forceinline__ void tl_own(int lane, unsigned int& count, int kernel, int phase, unsigned int value) {
+  const TimelineBuf tl = g_timeline;
+  if (tl.buf == nullptr || count >= 1024u) return;
+  if (tl.cap < 1024u * (unsigned)(lane + 1)) return;
+  const unsigned long long i = tl.cap - 1024ull * (unsigned)(lane + 1) + count++;     // from the buffer's end
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+  tl.buf[1 + 2 * i] = t;
+  tl.buf[2 + 2 * i] = ((unsigned long long)(kernel & 0xFF) << 56) | ((unsigned long long)(phase & 0xFF) << 48) |
+                      (unsigned long long)value;
+}
 
 }  // namespace tk
 
@@ -70,6 +84,7 @@ namespace tk {
 __device__ __forceinline__ void tl_mark(int, int) {}
 __device__ __forceinline__ void tl_value(int, int, unsigned int) {}
 __device__ __forceinline__ unsigned long long tl_now() { return 0ull; }
+__device__ __forceinline__ void tl_own(int, unsigned int&, int, int, unsigned int) {}
 }
 #define TK_TIMELINE_SETTER(name)
 #endif

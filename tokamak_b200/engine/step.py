@@ -89,7 +89,7 @@ class StepBatch:
     decode_items: torch.Tensor      # token indices of requests that bring one token
     prefill_items: torch.Tensor     # token indices of requests that bring more than one
     prefill_tiles: torch.Tensor     # [n_tiles, 2] (request row, 64-token tile) of those requests, longest first
-    prefill_tiles_tc: torch.Tensor  # the same in the tile size of the tcgen05 kernel (ops.PREFILL_TC_ROWS)
+    prefill_tc: "ops.PrefillItems"  # the same requests as the work list of the tcgen05 kernel
     cache: DeviceCache
     err: torch.Tensor
     host_q_start: list[int] = field(default_factory=list)
@@ -151,7 +151,11 @@ class StepBuffers:
     def __init__(self, cache: DeviceCache, max_tokens: int):
         device, max_reqs = cache.device, cache.manager.max_slots
         self.device = device
-        self.capacity = 10 * max_reqs + 12 * max_tokens + 64
+        sms = ops.sm_count(device) if device.type == "cuda" else 148
+        # the prefill work list: a record per 256 tokens of a request, and up to 2 sms more for parts
+        self.capacity = (10 * max_reqs + 12 * max_tokens + 64
+                         + ops.PREFILL_TC_RECORD * (max_tokens // ops.PREFILL_TC_ROWS + max_reqs + 2 * sms + 8))
+        self.sms = sms
         self.staging = _PinnedRing(self.capacity, self.RING)
         self.dev = torch.zeros(self.capacity, dtype=torch.int32, device=device)
         max_tab = cache.tables.numel()
@@ -247,6 +251,10 @@ class StepFunction:
         self.max_seq_len = max_seq_len
         self.buffers = StepBuffers(cache, max_step_tokens)
         self.graph_safe = bool(model is not None and getattr(model, "graph_safe", lambda: False)())
+        # how many work items a part makes of one block of prompt tokens (its query heads, for an
+        # attention mixer): the work list of prompt portions is balanced for the smallest
+        parts = model.parts() if model is not None and hasattr(model, "parts") else []
+        self.prefill_heads = min((p.prefill_heads for p in parts if getattr(p, "prefill_heads", None)), default=32)
         self.steps_run = 0
         self.graph_launches = 0      # kernels replayed from CUDA graphs (not counted by ops.LAUNCHES)
         self.graph_replays = 0
@@ -353,16 +361,19 @@ class StepFunction:
             tiles.sort(reverse=True)
             return [x for _, r, t in tiles for x in (r, t)]
 
+        records, n_parts, n_split = ops.prefill_tc_records(q_start, q_len, kv_len, slots,
+                                                            heads=self.prefill_heads, sms=self.buffers.sms)
         arrays = [cat(tok_parts), cat(pos_parts), cat(req_parts), i32(q_start), i32(q_len), i32(kv_len),
                   i32(slots), i32(rows), i32(dec_items), cat(pf_parts), i32(tiles_of(64)),
-                  i32(tiles_of(ops.PREFILL_TC_ROWS)), i32(fed), i32(row_slot)]
+                  records.reshape(-1), i32(fed), i32(row_slot)]
         views = self.buffers.upload(arrays)
         self._send_updates()
         batch = StepBatch(
             n_tokens=n_tokens, n_reqs=n_reqs, n_want=len(rows),
             token_ids=views[0], positions=views[1], tok_req=views[2], req_q_start=views[3],
             req_q_len=views[4], req_kv_len=views[5], req_slot=views[6], logits_rows=views[7],
-            decode_items=views[8], prefill_items=views[9], prefill_tiles=views[10], prefill_tiles_tc=views[11],
+            decode_items=views[8], prefill_items=views[9], prefill_tiles=views[10],
+            prefill_tc=ops.PrefillItems(views[11].view(-1, ops.PREFILL_TC_RECORD), n_parts, n_split),
             cache=self.cache, err=self.buffers.result[:4],
             host_q_start=q_start, host_q_len=q_len, host_kv_len=kv_len, host_slot=slots,
             max_q_len=max(q_len), max_kv_len=_bucket(max(kv_len)), row_slot=views[13])
@@ -383,7 +394,8 @@ class StepFunction:
             token_ids=b.dec_token_ids[:n], positions=b.dec_positions[:n], tok_req=b.iota[:n],
             req_q_start=b.iota[:n], req_q_len=b.ones[:n], req_kv_len=b.dec_kv_len[:n],
             req_slot=b.dec_slots[:n], logits_rows=b.iota[:n], decode_items=b.iota[:n],
-            prefill_items=b.empty, prefill_tiles=b.empty, prefill_tiles_tc=b.empty,
+            prefill_items=b.empty, prefill_tiles=b.empty,
+            prefill_tc=ops.PrefillItems(b.empty.view(0, ops.PREFILL_TC_RECORD), 0, 0),
             cache=self.cache, err=b.result[:4],
             host_q_start=list(range(n)), host_q_len=[1] * n, host_kv_len=[s + 1 for s in starts],
             host_slot=slots, max_q_len=1, max_kv_len=_bucket(max(starts) + 1), row_slot=b.dec_slots[:n])

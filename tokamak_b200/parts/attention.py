@@ -65,6 +65,7 @@ class Attention:
             raise ValueError(f"position encoding {spec.position.kind!r} does not rotate queries and keys "
                              f"(no rotary_table); give it the model's embedding_position seat instead")
         self.scale = spec.softmax_scale if spec.softmax_scale is not None else spec.head_dim ** -0.5
+        self.prefill_heads = spec.num_heads      # work items per block of prompt tokens (see parts/base.py)
 
     @staticmethod
     def expected_tensors(spec: AttentionSpec, prefix: str) -> dict[str, TensorReq]:
@@ -183,8 +184,7 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
             if beside:
                 join.record()
     if pf_tiled and ops.prefill_tc_kernel_takes(hq, hkv, d, page):
-        ops.attention_prefill_tc(q, out, cache_view.k, cache_view.v, step.prefill_tiles_tc,
-                                 step.req_q_start, step.req_q_len, step.req_kv_len, step.req_slot,
+        ops.attention_prefill_tc(q, out, cache_view.k, cache_view.v, step.prefill_tc,
                                  cache_view.table, step.err, scale=scale, window=window)
     elif pf_tiled:
         ops.attention_prefill(q, out, cache_view.k, cache_view.v, step.prefill_tiles,

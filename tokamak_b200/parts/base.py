@@ -33,7 +33,7 @@ head           ``expected_tensors(spec)``, ``__init__(spec, embedding part, tens
 No part knows which model it is in: it sees its spec, its tensors, the step's
 batch description and the view of its own cache.
 
-**Two declarations every part may make** (both optional, both read with ``getattr``):
+**Declarations every part may make** (all optional, all read with ``getattr``):
 
 ``GRAPH_SAFE = True`` says that the part's ``forward`` launches the same kernels with the same
 arguments whatever the step's numbers are: it reads the step through the device tensors of the
@@ -45,6 +45,11 @@ CUDA graph only if every part of the model says so; a model with one part that d
 
 ``weight_bytes()`` returns the bytes of the tensors that one call of the part reads in full
 (an embedding table, read by row, reports 0); measurements sum it over the schedule.
+
+``prefill_heads`` (a mixer, or a block on its mixer's behalf) is a hint, not a contract: how many
+work items the part makes of one block of prompt tokens (an attention mixer: its query heads).
+The step function balances the work list of prompt portions (``step.prefill_tc``) for the smallest
+value among the parts; any value gives right results.
 
 **Owed norms.**  In bfloat16 steps of few tokens the kernel of a product that ends a branch can
 add its sums to the residual stream itself and hand on the input of the *next* norm with the

@@ -71,6 +71,11 @@ class PreNormBlock:
     def GRAPH_SAFE(self) -> bool:
         return graph_safe(self.norm1, self.mixer, self.norm2, self.feed_forward)
 
+    @property
+    def prefill_heads(self) -> int | None:
+        """The mixer's hint for the work list of prompt portions, if it gives one."""
+        return getattr(self.mixer, "prefill_heads", None)
+
     def weight_bytes(self) -> int:
         return weight_bytes(self.norm1, self.mixer, self.norm2, self.feed_forward)
 
