@@ -300,3 +300,31 @@ def test_random_workloads_finish_in_arrival_order_with_every_page_accounted_for(
         assert q.is_finished and q.num_output_tokens == q.sampling_params.max_new_tokens
     assert not m.live_requests()
     assert all(g.num_free == g.num_pages for g in m.kv_groups)
+
+
+def test_a_step_is_cut_down_to_a_multiple_of_the_token_tile():
+    """536 tokens would be five tiles of 128 in every matrix product; the portion gives 24 up."""
+    m = CacheManager([KVGroup(KVPagesNeed(1, 16), 400, 16, ["l0"])], [], 64)
+    s = Scheduler(m, 64, 544, 512, token_multiple=128)
+    for i in range(24):
+        s.add(seq(i, 3, max_new=50))
+    plan = s.schedule()
+    assert plan.num_tokens == 72                       # fewer than a tile: left as it is
+    run_plan(m, plan)
+    long = seq(99, 2000, max_new=5)
+    s.add(long)
+    plan = s.schedule()
+    assert plan.num_tokens == 512 and [e.count for e in plan.entries if e.seq is long] == [488]
+    run_plan(m, plan)
+    plan = s.schedule()
+    assert plan.num_tokens == 512
+    entry = [e for e in plan.entries if e.seq is long][0]
+    assert (entry.start, entry.count, entry.samples) == (488, 488, False)    # nothing lost, nothing twice
+
+
+def test_a_portion_that_ends_its_prompt_is_not_cut():
+    m, s = make(num_pages=100, page=16, budget=2048)
+    s = Scheduler(m, 4, 2048, None, token_multiple=128)
+    s.add(seq(0, 300))
+    plan = s.schedule()
+    assert [(e.count, e.samples) for e in plan.entries] == [(300, True)]

@@ -81,6 +81,9 @@ class LLM:
         attention_policy: ``"full"`` or ``"window:W"``, a window applied to every layer.
         kv_watermark: share of the page pool that an admission leaves free while other requests
             run (not in the reference; 0 is its behaviour).
+        step_token_multiple: a step of more tokens than this is shortened to a multiple of it by
+            cutting a prompt portion earlier (not in the reference, whose steps hold whole prompts;
+            128 is the token tile of the matrix products; 1 leaves steps as planned).
         kv_backend, scheduling, attention_backend, draft_model, num_speculative_tokens: accepted
             with the reference's defaults (``"paged"``, ``"continuous"``, ``"auto"``, ``None``), so
             that a call written for it still works; any other value is refused with the reason.
@@ -91,7 +94,8 @@ class LLM:
                  block_size: int = 16, kv_pool_tokens: int | str | None = None, max_batch_size: int = 16,
                  max_num_batched_tokens: int = 2048, prefill_chunk: int | None = None,
                  attention_policy: str = "full", gpu_memory_utilization: float = 0.9,
-                 kv_watermark: float = 0.0, kv_backend: str = "paged", scheduling: str = "continuous",
+                 kv_watermark: float = 0.0, step_token_multiple: int = 128,
+                 kv_backend: str = "paged", scheduling: str = "continuous",
                  attention_backend: str = "auto", draft_model: str | None = None,
                  num_speculative_tokens: int = 4, _core: EngineCore | None = None) -> None:
         # options of the reference whose other values name parts that this engine does not have
@@ -125,6 +129,9 @@ class LLM:
         if not 0.0 <= kv_watermark < 1.0:
             raise ValueError(f"kv_watermark must be in [0, 1), got {kv_watermark}")
         self.kv_watermark = kv_watermark
+        if step_token_multiple < 1:
+            raise ValueError(f"step_token_multiple must be >= 1, got {step_token_multiple}")
+        self.step_token_multiple = step_token_multiple
         self.cache_manager = self.core.manager
         self.model = self.core.model
         self._tokenizer = None
@@ -173,7 +180,7 @@ class LLM:
             sequences.append(seq)
 
         scheduler = Scheduler(self.cache_manager, self.max_batch_size, self.max_num_batched_tokens,
-                              self.prefill_chunk, self.kv_watermark)
+                              self.prefill_chunk, self.kv_watermark, self.step_token_multiple)
         for seq in sequences:
             scheduler.add(seq)
 

@@ -9,12 +9,15 @@ slot meanwhile, and with it the record of its random generator, as the reference
 a preempted request's generator (src/tokamak/engine/llm.py:339-340,441-445); since
 nobody is admitted ahead of it, the slot would have no other taker.
 
-What is added here is the token budget.  The reference computes a whole prompt
+What is added here is the token budget, and the rounding of a step's size.  The reference computes a whole prompt
 in one step and lets the decodes wait meanwhile (scheduler.py:114-117); this
 scheduler plans one mixed batch per step: every running sequence that only needs
 its next token gets one token, and what is left of ``max_num_batched_tokens``
 goes to prompt portions, running prefills first, then new admissions, each
-portion at most ``prefill_chunk`` tokens.
+portion at most ``prefill_chunk`` tokens.  With ``token_multiple`` m > 1 a step of more than m
+tokens is then shortened to a multiple of m by cutting a portion that does not end its prompt (it can
+be cut anywhere): the matrix products run in tiles of 128 tokens, so 536 tokens cost five tiles and
+512 cost four, and the tokens left out come first in the next step.
 
 Order within a plan: the running sequences reserve the pages of their next tokens first, and
 admissions take what is left.  The reference asks the admission question first and finds the
@@ -71,6 +74,8 @@ class Scheduler:
         max_num_batched_tokens: most tokens of one step.
         prefill_chunk: most tokens of one sequence's prompt portion in a step
             (``None``: limited by the budget only).
+        token_multiple: a step of more tokens than this is cut down to a multiple of it where a
+            prompt portion allows (1: steps are left as planned).
         watermark: share of every pool that an admission must leave free while other sequences
             run, as room for their growth (fewer preemptions at the price of later admissions).
             The reference has none (docs/design/003-continuous-batching.md:59-62), which is the
@@ -78,13 +83,15 @@ class Scheduler:
     """
 
     def __init__(self, manager: CacheManager, max_batch_size: int, max_num_batched_tokens: int,
-                 prefill_chunk: int | None = None, watermark: float = 0.0):
+                 prefill_chunk: int | None = None, watermark: float = 0.0, token_multiple: int = 1):
         if max_batch_size < 1:
             raise ValueError(f"max_batch_size must be >= 1, got {max_batch_size}")
         if max_num_batched_tokens < 1:
             raise ValueError(f"max_num_batched_tokens must be >= 1, got {max_num_batched_tokens}")
         if prefill_chunk is not None and prefill_chunk < 1:
             raise ValueError(f"prefill_chunk must be >= 1, got {prefill_chunk}")
+        if token_multiple < 1:
+            raise ValueError(f"token_multiple must be >= 1, got {token_multiple}")
         if not 0.0 <= watermark < 1.0:
             raise ValueError(f"watermark must be in [0, 1), got {watermark}")
         if max_batch_size > manager.max_slots:
@@ -95,6 +102,7 @@ class Scheduler:
         self._budget = max_num_batched_tokens
         self._chunk = prefill_chunk
         self._watermark = watermark
+        self._multiple = token_multiple
         self.waiting: deque[Sequence] = deque()
         self.running: list[Sequence] = []
         self.num_preemptions = 0
@@ -155,6 +163,7 @@ class Scheduler:
                 budget -= count
 
             if entries:
+                self._round_down(entries)
                 return StepPlan(entries, preempted, admitted)
             if self.running:
                 # unreachable: a running sequence is either planned or preempted above
@@ -162,6 +171,19 @@ class Scheduler:
             if self.waiting:
                 continue
             return None
+
+    def _round_down(self, entries: list[PlannedEntry]) -> None:
+        """Shorten the plan to a multiple of ``token_multiple`` tokens, if it has more than that and a
+        portion that does not end its prompt can give the remainder up (the latest such portion
+        does; pages reserved for the tokens left out are kept for the next step)."""
+        total = sum(e.count for e in entries)
+        rest = total % self._multiple
+        if total <= self._multiple or rest == 0:
+            return
+        for e in reversed(entries):
+            if not e.samples and e.count > rest:
+                e.count -= rest
+                return
 
     def plan_ahead(self, plan: StepPlan, max_total_tokens) -> StepPlan | None:
         """The step after ``plan``, decided before ``plan``'s tokens are known, or ``None``.
