@@ -161,38 +161,80 @@ def test_stop_rules_in_the_reference_order():
         Sequence(3, [], SamplingParams())
 
 
-def test_plan_ahead_only_when_the_next_step_is_certain():
-    """The step after a decode step may be planned before its tokens are known: same sequences,
-    one position on; not while a prompt portion runs, somebody waits, or pages are short; and
-    sequences that reach their length limit in the running step drop out."""
-    m, s = make(num_pages=8, page=4, budget=64)
+def launch(m, plan):
+    """What the engine does when it launches a planned step: lengths and cursors move on."""
+    for e in plan.entries:
+        m.advance(e.seq.seq_id, e.count)
+        e.seq.num_computed = e.start + e.count
+
+
+def arrive(plan, token=9, limit=10 ** 6):
+    """The tokens of a launched step are read."""
+    for e in plan.entries:
+        if e.samples and not e.seq.is_finished:
+            e.seq.append_checked(token, eos_token_ids=(), max_total_tokens=limit)
+
+
+def test_plan_ahead_while_a_step_is_in_flight():
+    """The step after a launched step is planned before its tokens are known: every sequence it
+    samples for brings one more token that only the device has, prompt portions go on, waiting
+    requests are admitted into free room, and sequences that reach their length limit in the step
+    in flight are left out."""
+    m, s = make(num_pages=16, page=4, budget=64)
     a, b = seq(0, 5, max_new=3), seq(1, 6, max_new=8)
     s.add(a); s.add(b)
     limit = lambda q: 10 ** 6
     first = s.schedule()                                # both prompts whole
-    assert s.plan_ahead(first, limit) is None           # prompt portions: the next step depends on nothing certain
-    run_plan(m, first)
-    dec = s.schedule()
-    assert describe(dec) == [(0, 5, 1, True), (1, 6, 1, True)]
-    for e in dec.entries:                               # what the engine does at launch
-        m.advance(e.seq.seq_id, e.count)
-        e.seq.num_computed = e.start + e.count
+    launch(m, first)
+    dec = s.plan_ahead(first, limit)
+    assert describe(dec) == [(0, 5, 1, True), (1, 6, 1, True)]     # their first tokens are still on the device
+    assert a.num_tokens == 5 and a.num_tokens_due == 6
+    arrive(first)
+    launch(m, dec)
     ahead = s.plan_ahead(dec, limit)
     assert describe(ahead) == [(0, 6, 1, True), (1, 7, 1, True)]
     assert m.length(0) == 6 and m.length(1) == 7        # lengths advance at launch, not at planning
-    for e in dec.entries:                               # the tokens of the running step arrive
-        e.seq.append_checked(9, eos_token_ids=(), max_total_tokens=10 ** 6)
-    for e in ahead.entries:
-        m.advance(e.seq.seq_id, e.count)
-        e.seq.num_computed = e.start + e.count
+    arrive(dec)
+    launch(m, ahead)
     # sequence 0 has two of its three tokens: the step in flight gives the third, so it drops out
     nxt = s.plan_ahead(ahead, limit)
     assert describe(nxt) == [(1, 8, 1, True)]
+    assert a.ending and not b.ending
+    arrive(ahead)
+    assert a.is_finished
+    launch(m, nxt)
     # a context limit does the same
-    assert s.plan_ahead(ahead, lambda q: q.num_tokens + 1) is None
-    # somebody waiting: the scheduler has to look at admissions first
-    s.add(seq(2, 3))
-    assert s.plan_ahead(ahead, limit) is None
+    assert s.plan_ahead(nxt, lambda q: q.num_tokens + 1) is None
+    # somebody waiting is admitted beside the token in flight (sequence 0 still holds its pages)
+    c = seq(2, 3)
+    s.add(c)
+    with_c = s.plan_ahead(nxt, limit)
+    assert describe(with_c) == [(1, 9, 1, True), (2, 0, 3, True)] and with_c.admitted == [c]
+    m.check_invariants()
+
+
+def test_plan_ahead_carries_prompt_portions_on():
+    m, s = make(num_pages=64, page=4, slots=4, batch=4, budget=16, chunk=8)
+    a, b = seq(0, 3, max_new=8), seq(1, 20, max_new=8)
+    s.add(a)
+    first = s.schedule()
+    launch(m, first)
+    s.add(b)
+    plan = s.plan_ahead(first, lambda q: 10 ** 6)
+    assert describe(plan) == [(0, 3, 1, True), (1, 0, 8, False)]
+    arrive(first)
+    launch(m, plan)
+    plan2 = s.plan_ahead(plan, lambda q: 10 ** 6)
+    assert describe(plan2) == [(0, 4, 1, True), (1, 8, 8, False)]
+    arrive(plan)
+    launch(m, plan2)
+    plan3 = s.plan_ahead(plan2, lambda q: 10 ** 6)
+    assert describe(plan3) == [(0, 5, 1, True), (1, 16, 4, True)]
+    arrive(plan2)
+    launch(m, plan3)
+    plan4 = s.plan_ahead(plan3, lambda q: 10 ** 6)
+    assert describe(plan4) == [(0, 6, 1, True), (1, 20, 1, True)]
+    m.check_invariants()
 
 
 def test_plan_ahead_gives_up_when_pages_are_short():
@@ -202,9 +244,7 @@ def test_plan_ahead_gives_up_when_pages_are_short():
     run_plan(m2, s2.schedule())                         # 7 computed, token 8 sampled
     dec = s2.schedule()                                 # position 7: still inside page 2
     assert describe(dec) == [(1, 7, 1, True)]
-    for e in dec.entries:
-        m2.advance(e.seq.seq_id, e.count)
-        e.seq.num_computed = e.start + e.count
+    launch(m2, dec)
     assert s2.plan_ahead(dec, lambda q: 10 ** 6) is None    # position 8 would need a third page
     m2.check_invariants()
 

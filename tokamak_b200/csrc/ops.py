@@ -470,7 +470,8 @@ class PrefillItems:
     n_split: int
 
 
-def prefill_tc_records(q_start, q_len, kv_len, slots, *, heads: int, sms: int) -> tuple[np.ndarray, int, int]:
+def prefill_tc_records(q_start, q_len, kv_len, slots, *, heads: int, sms: int,
+                       parts: int | None = None) -> tuple[np.ndarray, int, int]:
     """Item records of the tcgen05 prefill kernel for the requests that bring more than one token.
 
     The tokens of a request are cut into blocks of :data:`PREFILL_TC_ROWS`; block ``b`` visits the
@@ -501,14 +502,16 @@ def prefill_tc_records(q_start, q_len, kv_len, slots, *, heads: int, sms: int) -
     # every block is cut into as many parts as keeps all items in one round over the SMs
     n_items = len(blocks) * max(1, heads)
     parts_all = min(max(1, sms) // n_items, PREFILL_TC_MAX_PARTS) if n_items else 1
+    if parts is not None:
+        parts_all = parts        # a measurement's own choice
     records, poff, split = [], 0, 0
     for tok0, rows, pos0, slot, n_kt in blocks:
-        parts = max(1, min(parts_all, n_kt // PREFILL_TC_MIN_PART))
-        for i in range(parts):
-            records.append((tok0, rows, pos0, slot, n_kt * i // parts, n_kt * (i + 1) // parts, i, parts,
-                            poff if parts > 1 else 0, split if parts > 1 else 0, 0, 0))
-        if parts > 1:
-            poff += parts
+        n_cut = max(1, min(parts_all, n_kt // PREFILL_TC_MIN_PART))
+        for i in range(n_cut):
+            records.append((tok0, rows, pos0, slot, n_kt * i // n_cut, n_kt * (i + 1) // n_cut, i, n_cut,
+                            poff if n_cut > 1 else 0, split if n_cut > 1 else 0, 0, 0))
+        if n_cut > 1:
+            poff += n_cut
             split += 1
     records.sort(key=lambda rec: rec[4] - rec[5])          # longest first; equal lengths keep their order
     out = np.asarray(records, dtype=np.int32).reshape(-1, PREFILL_TC_RECORD)

@@ -204,8 +204,8 @@ class LLM:
                     if plan is None:
                         raise RuntimeError("scheduler returned no work but is unfinished")
                     flight = self._launch(plan)
-                # the step after a step of single next tokens is known but for the tokens, which
-                # stay on the device: it is launched before this step's tokens are read
+                # the step after this one is known but for the tokens that this one samples, and
+                # those stay on the device: it is launched before this step's tokens are read
                 ahead = None
                 plan_ahead = None if self.plain_steps else scheduler.plan_ahead(flight.plan, self._context_budget)
                 if plan_ahead is not None:
@@ -260,8 +260,12 @@ class LLM:
                                       fresh=True)
         for e in plan.entries:
             seq = e.seq
-            on_device = e.count == 1 and e.samples and seq.num_output_tokens > 0 and not self.plain_steps
+            # its last sampled token: known to the host or, in a step planned ahead, still to be read
+            on_device = (e.count == 1 and e.samples and not self.plain_steps
+                         and (seq.num_output_tokens > 0 or e.start >= seq.num_tokens))
             tokens = None if on_device else seq.tokens_from(e.start, e.count)
+            if tokens is not None and len(tokens) != e.count:
+                raise RuntimeError(f"sequence {seq.seq_id}: tokens {e.start}..{e.start + e.count} are not all known")
             entries.append(StepEntry(seq.seq_id, tokens, [e.count - 1] if e.samples else []))
             if e.samples:
                 samplers.append(seq)

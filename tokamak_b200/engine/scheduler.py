@@ -117,6 +117,13 @@ class Scheduler:
     # ------------------------------------------------------------------------------
     def schedule(self) -> StepPlan | None:
         """Plan the next step; ``None`` when everything is finished."""
+        return self._plan(ahead=False)
+
+    def _plan(self, ahead: bool) -> StepPlan | None:
+        """The next step.  ``ahead``: a step is in flight whose tokens are not known; sequences that
+        it samples for count one token more (``Sequence.expected``), those that it certainly ends
+        are left alone, and where the plan would need a preemption, or has nothing to run, the
+        answer is ``None``: that is decided once the step in flight has been read."""
         self.running = [s for s in self.running if not s.is_finished]
         preempted: list[Sequence] = []
         admitted: list[Sequence] = []
@@ -125,8 +132,9 @@ class Scheduler:
             budget = self._budget
 
             # 1. running sequences: single next tokens first, then prompt portions
-            decoding = [s for s in self.running if s.num_pending == 1]
-            prefilling = [s for s in self.running if s.num_pending > 1]
+            going = [s for s in self.running if not (ahead and s.ending)]
+            decoding = [s for s in going if s.num_pending == 1]
+            prefilling = [s for s in going if s.num_pending > 1]
             for seq in decoding + prefilling:
                 if seq not in self.running:
                     continue    # preempted while an earlier sequence was served
@@ -134,10 +142,16 @@ class Scheduler:
                     break
                 want = seq.num_pending
                 count = min(want, budget, self._chunk or want)
-                if self._reserve(seq, seq.num_computed + count, preempted, entries):
-                    entries.append(PlannedEntry(seq, seq.num_computed, count,
-                                                samples=seq.num_computed + count == seq.num_tokens))
-                    budget -= count
+                if ahead:
+                    try:
+                        self._manager.grow(seq.seq_id, seq.num_computed + count)
+                    except OutOfPagesError:
+                        return None     # somebody has to give way: not decided ahead
+                elif not self._reserve(seq, seq.num_computed + count, preempted, entries):
+                    continue
+                entries.append(PlannedEntry(seq, seq.num_computed, count,
+                                            samples=seq.num_computed + count == seq.num_tokens_due))
+                budget -= count
             # sequences that were preempted after they had been planned drop out
             entries = [e for e in entries if e.seq in self.running]
 
@@ -146,7 +160,7 @@ class Scheduler:
                 seq = self.waiting[0]
                 resumed = self._manager.has(seq.seq_id)     # preempted earlier: it kept its slot
                 if (not resumed and self._manager.num_free_slots == 0) or not self._fits_new(seq):
-                    if not self.running:
+                    if not self.running and not ahead:
                         raise OutOfPagesError(
                             f"sequence {seq.seq_id} needs more pages than the pool can ever provide")
                     break   # pages are busy; decode until some come free
@@ -165,6 +179,8 @@ class Scheduler:
             if entries:
                 self._round_down(entries)
                 return StepPlan(entries, preempted, admitted)
+            if ahead:
+                return None
             if self.running:
                 # unreachable: a running sequence is either planned or preempted above
                 raise RuntimeError("scheduler stalled with running sequences")
@@ -186,36 +202,21 @@ class Scheduler:
                 return
 
     def plan_ahead(self, plan: StepPlan, max_total_tokens) -> StepPlan | None:
-        """The step after ``plan``, decided before ``plan``'s tokens are known, or ``None``.
+        """The step after ``plan``, decided while ``plan`` is in flight and its tokens are not known
+        yet, or ``None``.
 
-        It exists when it is certain but for the token values: ``plan`` is a step of single
-        next tokens of every running sequence, every one of them sampling, nothing waits for
-        admission, and the pages for one more token are there.  Sequences that reach a length
-        limit in ``plan`` (``max_new_tokens``, or ``max_total_tokens(seq)``) drop out.  A
-        sequence that turns out to have stopped on an end-of-sequence token in ``plan`` is in
-        the step for nothing; the engine throws its token away.  When pages are short the answer
-        is ``None``: who gives way is decided by ``schedule`` once ``plan`` has been read.
+        Every sequence that ``plan`` samples for brings one more token, which only the device
+        knows; sequences that reach a length limit with it (``max_new_tokens``, or
+        ``max_total_tokens(seq)``) are left out, and so are their pages: they are freed when
+        ``plan`` has been read.  Prompt portions go on, and requests are admitted into the room
+        that is free now.  A sequence that turns out to have stopped on an end-of-sequence token in
+        ``plan`` is in the step for nothing; the engine throws its token away.  When pages are short
+        the answer is ``None``: who gives way is decided by ``schedule`` once ``plan`` has been read.
         """
-        if any(e.count != 1 or not e.samples for e in plan.entries):
-            return None
-        going = [e for e in plan.entries if not e.seq.is_finished]
-        if self.waiting or len(going) != sum(1 for s in self.running if not s.is_finished):
-            return None
-        entries = []
-        for e in going:
-            seq = e.seq
-            if (seq.num_output_tokens + 1 >= seq.sampling_params.max_new_tokens
-                    or seq.num_tokens + 1 >= max_total_tokens(seq)):
-                continue
-            entries.append(PlannedEntry(seq, e.start + 1, 1, samples=True))
-        if not entries:
-            return None
-        try:
-            for e in entries:
-                self._manager.grow(e.seq.seq_id, e.start + 1)
-        except OutOfPagesError:
-            return None
-        return StepPlan(entries)
+        for e in plan.entries:
+            if e.samples and not e.seq.is_finished:
+                e.seq.expect_token(max_total_tokens(e.seq))
+        return self._plan(ahead=True)
 
     # ------------------------------------------------------------------------------
     def _fits_new(self, seq: Sequence) -> bool:

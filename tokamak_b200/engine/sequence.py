@@ -8,6 +8,11 @@ moves the cursor back to 0 and changes nothing else, which is all that recomputa
 needs.  The request's random stream is its seed plus the number of tokens generated so
 far (the device keeps that count in the request's slot record).
 
+While a step that samples for the request is in flight, the stream has one token more than the
+host knows: ``expected`` counts it, so that the step after can be planned, and launched with
+that token fed on the device, before the first one's tokens are read.  ``ending`` says that the
+token in flight is certainly the last (a length limit), so nothing is planned after it.
+
 The stop rules and their order are the reference's
 (src/tokamak/engine/sequence.py:109-127): an end-of-sequence token unless ignored, then
 ``max_new_tokens``, then the context budget.
@@ -37,7 +42,7 @@ class Sequence:
 
     __slots__ = ("seq_id", "sampling_params", "seed", "status", "finish_reason", "num_computed",
                  "num_preemptions", "arrival_time", "first_token_time", "finish_time",
-                 "_stream", "_n_prompt")
+                 "_stream", "_n_prompt", "expected", "ending")
 
     def __init__(self, seq_id: int, prompt_token_ids: list[int], sampling_params: SamplingParams):
         if len(prompt_token_ids) == 0:
@@ -49,6 +54,8 @@ class Sequence:
         self._stream: list[int] = [int(t) for t in prompt_token_ids]
         self._n_prompt = len(self._stream)
         self.num_computed = 0           # the cursor: tokens of the stream that the cache holds
+        self.expected = 0               # tokens that a step in flight samples and the host has not read
+        self.ending = False             # the token in flight ends the request for certain
         self.num_preemptions = 0
         self.status = SequenceStatus.WAITING
         self.finish_reason: FinishReason | None = None
@@ -76,9 +83,20 @@ class Sequence:
         return self._stream[self._n_prompt:]
 
     @property
+    def num_tokens_due(self) -> int:
+        """Length of the stream with the token that a step in flight is sampling."""
+        return len(self._stream) + self.expected
+
+    @property
     def num_pending(self) -> int:
-        """Tokens between the cursor and the end of the stream."""
-        return len(self._stream) - self.num_computed
+        """Tokens between the cursor and the end of the stream (the expected one included)."""
+        return len(self._stream) + self.expected - self.num_computed
+
+    def expect_token(self, max_total_tokens: int) -> None:
+        """A step that samples for this request has been launched."""
+        self.expected = 1
+        self.ending = (self.num_output_tokens + 1 >= self.sampling_params.max_new_tokens
+                       or len(self._stream) + 1 >= max_total_tokens)
 
     def tokens_from(self, start: int, count: int) -> list[int]:
         """``count`` tokens of the stream from index ``start``."""
@@ -93,6 +111,7 @@ class Sequence:
         if self.is_finished:
             raise RuntimeError(f"Sequence {self.seq_id} is already finished")
         self._stream.append(int(token_id))
+        self.expected = 0
 
     def append_checked(self, token_id: int, *, eos_token_ids: tuple[int, ...],
                        max_total_tokens: int) -> bool:
@@ -114,6 +133,7 @@ class Sequence:
     def rewind(self) -> None:
         """Preemption: nothing of the stream is in the cache any more."""
         self.num_computed = 0
+        self.expected = 0
         self.num_preemptions += 1
         self.status = SequenceStatus.WAITING
 
