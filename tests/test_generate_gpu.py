@@ -209,6 +209,39 @@ def test_steps_launched_ahead_end_where_the_requests_end_alone():
     assert llm.cache_manager.num_free_slots == llm.cache_manager.max_slots
 
 
+def test_portions_and_admissions_launched_ahead_end_where_the_requests_end_alone():
+    """Every kind of step is launched before the step before it has been read: prompt portions
+    go on, requests are admitted, and the tokens that the step in flight samples are fed on the
+    device.  Six requests through two slots, prompts cut into portions of five, one request
+    stopping on an end-of-sequence token while the step after is already running: all end
+    exactly where they end alone, step by step with nothing launched ahead, and every page and
+    slot comes back."""
+    from tokamak_b200 import SamplingParams
+    llm = llm_for("A", "float32", max_batch_size=2, prefill_chunk=5, max_num_batched_tokens=9, max_seq_len=64, kv_pool_tokens=64)
+    prompts = prompts_for("A", [6, 11, 19, 8, 3, 14])
+    free_run = SamplingParams(temperature=0.0, max_new_tokens=16)
+    llm.plain_steps = True
+    alone = [llm.generate(prompt_token_ids=[p], sampling_params=free_run)[0].output_token_ids for p in prompts]
+    assert llm.last_stats["steps_launched_ahead"] == 0
+    eos = alone[2][5]
+    limits = [16, 9, 16, 4, 12, 16]
+    want = []
+    for toks, limit in zip(alone, limits):
+        toks = toks[:limit]
+        want.append(toks[:toks.index(eos) + 1] if eos in toks else toks)
+    llm.model_config = dataclasses.replace(llm.model_config, eos_token_ids=(eos,))
+    params = [SamplingParams(temperature=0.0, max_new_tokens=n) for n in limits]
+    llm.plain_steps = False
+    outs = llm.generate(prompt_token_ids=prompts, sampling_params=params)
+    stats = llm.last_stats
+    assert [o.output_token_ids for o in outs] == want
+    assert outs[2].finish_reason.value == "stop"
+    assert stats["portions_launched_ahead"] >= 6 and stats["steps_launched_ahead"] >= stats["steps"] // 2
+    llm.cache_manager.check_invariants()
+    assert all(g.num_free == g.num_pages for g in llm.cache_manager.kv_groups)
+    assert llm.cache_manager.num_free_slots == llm.cache_manager.max_slots
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_steps_driven_by_the_slot_records_equal_steps_laid_out_by_the_host(dtype):
     """Steps of single next tokens whose tokens, positions, sampling parameters and generator

@@ -191,6 +191,7 @@ class LLM:
         buffers = self.core.step.buffers
         stats = {"steps": 0, "tokens_run": 0, "prefill_tokens": 0, "decode_tokens": 0,
                  "mixed_steps": 0, "decode_steps": 0, "decode_step_time_s": 0.0,
+                 "steps_launched_ahead": 0, "portions_launched_ahead": 0,
                  "decode_step_tokens": 0, "decode_step_times": [], "decode_step_h2d_bytes": [],
                  "pages_free_min": min((g.num_free for g in self.cache_manager.kv_groups), default=0)}
         try:
@@ -210,6 +211,8 @@ class LLM:
                 plan_ahead = None if self.plain_steps else scheduler.plan_ahead(flight.plan, self._context_budget)
                 if plan_ahead is not None:
                     ahead = self._launch(plan_ahead)
+                    stats["steps_launched_ahead"] += 1
+                    stats["portions_launched_ahead"] += sum(1 for e in plan_ahead.entries if e.count > 1)
                 done = self._complete(flight, ahead)
                 plan = flight.plan
                 stats["steps"] += 1
