@@ -106,6 +106,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_r = blockIdx.x, tile_c = blockIdx.y, split = blockIdx.z;
+  // residual epilogue: what the thread's first column needs from global memory, asked for while
+  // the products still run (the sums are added to it some microseconds later)
+  float4 pre_r = make_float4(0.0f, 0.0f, 0.0f, 0.0f), pre_w = pre_r;
+  float4 pre_cs23 = pre_r;      // q|k|v epilogue: pre_w = norm weights, pre_r / pre_cs23 = (cos, sin) pairs
+  int pre_c = -1;
+  unsigned int tl_n = 0;        // time stamps of one thread of the blocks of row tile 1 (timeline builds only)
+  const bool tl_me = warp == 2 && lane == 0 && blockIdx.x == 1 && blockIdx.y == 0;
   const uint32_t r_bytes = kGtBM * kGtBK * 2;
   const uint32_t c_bytes = (uint32_t)p.bn * kGtBK * 2;
   const uint32_t stage_bytes = r_bytes + ((c_bytes + 1023u) & ~1023u);
@@ -219,6 +226,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
     const int quarter = warp & 3;
     bool ok = true;
     pdl_wait();   // nothing is stored before the previous kernels are done with the output buffer
+    if (p.epilogue == kGtEpiResidualNorm) {
+      const int cs = p.cluster_reduce > 1 ? p.cluster_reduce : 1;
+      const int t = (warp - 2) * 32 + lane;
+      const int c = (p.cluster_reduce > 1 ? (int)cluster_ctarank() : 0) + cs * (t >> 5);
+      const int row = tile_r * kGtBM + (t & 31) * 4;
+      if (c < p.bn && tile_c * p.bn + c < p.cols_total && row < p.rows_total) {
+        pre_c = c;
+        pre_r = *reinterpret_cast<const float4*>(p.resid + (size_t)(tile_c * p.bn + c) * p.rows_total + row);
+        pre_w = *reinterpret_cast<const float4*>(p.norm_w + row);
+      }
+    }
+    if (p.epilogue == kGtEpiQkvRope) {
+      const GemmQkvRope& e = p.qkv;
+      const int cs = p.cluster_reduce > 1 ? p.cluster_reduce : 1;
+      const int t = (warp - 2) * 32 + lane;
+      const int c = (p.cluster_reduce > 1 ? (int)cluster_ctarank() : 0) + cs * (t >> 5);
+      if (c < p.bn && tile_c * p.bn + c < p.cols_total) {
+        pre_c = c;
+        const int kind = tile_r < e.n_q_heads ? 0 : (tile_r < e.n_q_heads + e.n_kv_heads ? 1 : 2);
+        const float* nw = kind == 0 ? e.q_norm_w : (kind == 1 ? e.k_norm_w : nullptr);
+        if (nw != nullptr) pre_w = *reinterpret_cast<const float4*>(nw + (t & 31) * 4);
+        if (kind != 2 && e.rope_table != nullptr) {
+          const float4* cs4 = reinterpret_cast<const float4*>(e.rope_table + (size_t)(tile_c * p.bn + c) * (kGtHeadDim / 2) +
+                                                               4 * (lane & 15));
+          pre_r = cs4[0];
+          pre_cs23 = cs4[1];
+        }
+      }
+    }
     // the scale of this thread's column (token), while the products still run
     float my_scale = 1.0f;
     const int my_col = (warp - 2) * 32 + lane;
@@ -265,6 +301,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
       if (!ok && lane == 0) { set_error(p.err, kErrWait, 2, 0, 0); *abort_flag = 1; }
     }
     if (warp == 2 && lane == 0) tl_mark(10 + p.epilogue, 3);
+    if (tl_me) tl_own(8 + split, tl_n, 10 + p.epilogue, 20, (unsigned)split);
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const int row = tile_r * kGtBM + quarter * 32 + lane;      // row of R = lane of the accumulator
     if (staged && my_col < p.bn) {
@@ -302,10 +339,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
     }
   }
 
+  if (tl_me) tl_own(8 + split, tl_n, 10 + p.epilogue, 21, (unsigned)split);
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
+  if (tl_me) tl_own(8 + split, tl_n, 10 + p.epilogue, 22, (unsigned)split);
   if (staged) {
     cluster_sync_all();                    // every block of the cluster has staged its partial
+    if (tl_me) tl_own(8 + split, tl_n, 10 + p.epilogue, 23, (unsigned)split);
     const int csize = p.cluster_reduce > 1 ? p.cluster_reduce : 1;
     const uint32_t my_rank = p.cluster_reduce > 1 ? cluster_ctarank() : 0u;
     const float* s_scale = reinterpret_cast<const float*>(smem) + p.bn * kGtBM;   // this block's own copy
@@ -355,8 +395,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
           // the residual and the norm weight are on their way while the partials are added up
           float4 r = make_float4(0.0f, 0.0f, 0.0f, 0.0f), w = r;
           if (p.epilogue == kGtEpiResidualNorm) {
-            r = *reinterpret_cast<const float4*>(p.resid + (size_t)col * p.rows_total + row);
-            w = *reinterpret_cast<const float4*>(p.norm_w + row);
+            if (c == pre_c) {
+              r = pre_r;
+              w = pre_w;
+            } else {
+              r = *reinterpret_cast<const float4*>(p.resid + (size_t)col * p.rows_total + row);
+              w = *reinterpret_cast<const float4*>(p.norm_w + row);
+            }
           }
           float4 sum = cluster_sum_f32x4(base + (uint32_t)((c * kGtBM + r4) * 4), csize);
           if (p.colscale_parts != nullptr) {
@@ -369,7 +414,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
             const int kind = tile_r < e.n_q_heads ? 0 : (tile_r < e.n_q_heads + e.n_kv_heads ? 1 : 2);
             const float* nw = kind == 0 ? e.q_norm_w : (kind == 1 ? e.k_norm_w : nullptr);
             if (nw != nullptr) {
-              const float4 w4 = *reinterpret_cast<const float4*>(nw + r4);
+              const float4 w4 = c == pre_c ? pre_w : *reinterpret_cast<const float4*>(nw + r4);
               const float ss = warp_sum(sum.x * sum.x + sum.y * sum.y + sum.z * sum.z + sum.w * sum.w);
               const float rstd = rsqrtf(ss / (float)kGtHeadDim + e.eps);
               sum.x = sum.x * rstd * w4.x; sum.y = sum.y * rstd * w4.y;
@@ -379,7 +424,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
               // element i < 64 turns with element i + 64, which lane l ^ 16 holds
               const float4* cs = reinterpret_cast<const float4*>(e.rope_table + (size_t)col * (kGtHeadDim / 2) +
                                                                   4 * (lane & 15));
-              const float4 cs01 = cs[0], cs23 = cs[1];        // (cos, sin) of two elements each
+              const float4 cs01 = c == pre_c ? pre_r : cs[0];      // (cos, sin) of two elements each
+              const float4 cs23 = c == pre_c ? pre_cs23 : cs[1];
               float4 other;
               other.x = __shfl_xor_sync(0xffffffffu, sum.x, 16); other.y = __shfl_xor_sync(0xffffffffu, sum.y, 16);
               other.z = __shfl_xor_sync(0xffffffffu, sum.z, 16); other.w = __shfl_xor_sync(0xffffffffu, sum.w, 16);
@@ -435,12 +481,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
         }
       }
     }
-    cluster_sync_all();                    // nobody's shared memory is read any more
+    if (tl_me) tl_own(8 + split, tl_n, 10 + p.epilogue, 24, (unsigned)split);
+    // "I read nobody's shared memory any more"; the wait for the others stands at the very end
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
   }
   if (warp == 2) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(tmem_cols)
                  : "memory");
+    if (tl_me) tl_own(8 + split, tl_n, 10 + p.epilogue, 26, (unsigned)split);
     if (lane == 0) tl_mark(10 + p.epilogue, 4);
+  }
+  if (staged) {
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");   // nobody reads this block's either
+    if (tl_me) tl_own(8 + split, tl_n, 10 + p.epilogue, 25, (unsigned)split);
   }
 }
 
