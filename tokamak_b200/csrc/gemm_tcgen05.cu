@@ -144,6 +144,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
     mbar_init(gt_smem_u32(accum_bar), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    // The first ring of stages: the weight tiles (which no kernel writes) are requested at once,
+    // by the thread that made the barriers, before the block has tensor memory, has met at its
+    // first barrier or has waited for the previous kernel: they stream in meanwhile.  The
+    // activation tiles follow after that wait.
+    const int first = min(n_kb, p.n_stages);
+    for (int i = 0; i < first; ++i) {
+      const uint32_t full = gt_smem_u32(&full_bar[i]);
+      mbar_expect_tx(full, r_bytes + c_bytes);
+      tma_load_2d(base + (uint32_t)i * stage_bytes, &map_r, (kb_begin + i) * kGtBK, tile_r * kGtBM, full);
+    }
   }
   if (warp == 2) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
@@ -159,15 +169,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
     // ---- TMA producer ---------------------------------------------------------------------
     if (lane == 0) {
       tl_mark(10 + p.epilogue, 0);
-      // The first ring of stages: the weight tiles (which no kernel writes) are requested
-      // before the wait on the previous kernel, so they stream in while it finishes; the
-      // activation tiles follow after the wait.
-      const int first = min(n_kb, p.n_stages);
-      for (int i = 0; i < first; ++i) {
-        const uint32_t full = gt_smem_u32(&full_bar[i]);
-        mbar_expect_tx(full, r_bytes + c_bytes);
-        tma_load_2d(base + (uint32_t)i * stage_bytes, &map_r, (kb_begin + i) * kGtBK, tile_r * kGtBM, full);
-      }
+      const int first = min(n_kb, p.n_stages);       // their weight tiles are on the way already
       pdl_wait();
       tl_mark(10 + p.epilogue, 1);
       for (int i = 0; i < first; ++i) {
@@ -341,7 +343,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
 
   if (tl_me) tl_own(8 + split, tl_n, 10 + p.epilogue, 21, (unsigned)split);
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-  __syncthreads();
+  if (!staged) __syncthreads();            // (the cluster barrier below holds every thread of the block too)
   if (tl_me) tl_own(8 + split, tl_n, 10 + p.epilogue, 22, (unsigned)split);
   if (staged) {
     cluster_sync_all();                    // every block of the cluster has staged its partial
