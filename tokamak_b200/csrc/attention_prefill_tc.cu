@@ -60,7 +60,7 @@ constexpr float kAtRescale = 8.0f;    // log2 units
 //   1 rows      how many of the 256 exist
 //   2 pos0      position of the first one in its request (kv_len - q_len + its index)
 //   3 slot      the request's row of the block table
-//   4 kt_begin  first 128-key tile of this part
+//   4 kt_begin  first 64-key tile of this part
 //   5 kt_end    one past its last
 //   6 part      index of the part
 //   7 n_parts   parts that the tokens' keys were cut into (1: the rows are written out directly)
@@ -73,8 +73,8 @@ struct AttnTcParams {
   const int* block_table;
   int* err;
   int* sched;                    // [2] zero between launches: next item, blocks done
-  float* part_o;                 // [(poff + part) * n_q_heads + head][2][128][D] unnormalised outputs
-  float* part_ml;                // the same index: [2][128][2] reference maximum (log2 units), sum
+  float* part_o;                 // [((poff + part) * n_q_heads + head) * 2 + tile][D / 4][128 rows] float4: unnormalised outputs
+  float* part_ml;                // the same index: [2][128 rows] reference maximum (log2 units), then sum
   int* part_count;               // [(split * n_q_heads + head) * 2 + tile] zero between launches
   int n_records, n_q_heads, n_kv_heads, page_size, max_pages, num_pages, window;
   float scale_log2;
