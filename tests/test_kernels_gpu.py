@@ -525,6 +525,62 @@ def test_attention_prefill_portions(kernel, hq, hkv, d, page, window):
     torch.testing.assert_close(out.double().cpu(), want, **tol(torch.bfloat16))
 
 
+def causal_attention_float64(q, k, v, first_pos, scale, window):
+    """float64 attention of a request's new tokens (positions first_pos ..) over its keys, all heads at once."""
+    n, hq, d = q.shape
+    group = hq // k.shape[1]
+    kk = k.double().repeat_interleave(group, dim=1)          # [keys, hq, d]
+    vv = v.double().repeat_interleave(group, dim=1)
+    s = torch.einsum("nhd,khd->hnk", q.double(), kk) * scale
+    pos = torch.arange(first_pos, first_pos + n).view(1, n, 1)
+    key = torch.arange(k.shape[0]).view(1, 1, -1)
+    mask = key <= pos
+    if window:
+        mask = mask & (key >= pos - window + 1)
+    s = s.masked_fill(~mask, float("-inf"))
+    return torch.einsum("hnk,khd->nhd", torch.softmax(s, dim=-1), vv)
+
+
+@pytest.mark.parametrize("kernel", ["tc", "tc_parts"])
+@pytest.mark.parametrize("hq,hkv,d,page,window", [(16, 4, 64, 16, None), (16, 16, 128, 32, 300)])
+def test_attention_prefill_more_items_than_blocks(kernel, hq, hkv, d, page, window):
+    """The persistent kernel with two to three items per block: items run on into each other (the
+    queries' second buffer, the ring and the score buffers carry over), are dealt out by the
+    counter, and, cut into parts, are added up by parts that other blocks ran."""
+    from tokamak_b200.csrc import ops
+    q_lens = [1024, 1000, 700, 1024, 515, 900]
+    kv_lens = [q + extra for q, extra in zip(q_lens, [0, 300, 0, 1024, 77, 0])]
+    n_reqs = len(q_lens)
+    assert sum(-(-q // ops.PREFILL_TC_ROWS) for q in q_lens) * hq > 2 * ops.sm_count(torch.device(DEV))
+    max_pages = max(-(-l // page) for l in kv_lens)
+    num_pages = n_reqs * max_pages + 3
+    table = make_tables(n_reqs, max_pages, num_pages, seed=7 + hq)
+    gen = torch.Generator().manual_seed(11 * hq + d)
+    k_all = [torch.randn(l, hkv, d, generator=gen).bfloat16().float() for l in kv_lens]
+    v_all = [torch.randn(l, hkv, d, generator=gen).bfloat16().float() for l in kv_lens]
+    kc = torch.full((num_pages, hkv, page, d), float("nan"), dtype=torch.bfloat16)
+    vc = torch.full_like(kc, float("nan"))
+    for r in range(n_reqs):                      # whole pages at a time
+        for pg in range(-(-kv_lens[r] // page)):
+            rows = slice(pg * page, min((pg + 1) * page, kv_lens[r]))
+            kc[int(table[r, pg]), :, :rows.stop - rows.start] = k_all[r][rows].transpose(0, 1).bfloat16()
+            vc[int(table[r, pg]), :, :rows.stop - rows.start] = v_all[r][rows].transpose(0, 1).bfloat16()
+    kc, vc = kc.to(DEV), vc.to(DEV)
+    zero_rest_of_last_pages(kc, vc, table, kv_lens, page)
+    q_start = [sum(q_lens[:r]) for r in range(n_reqs)]
+    q = torch.randn(sum(q_lens), hq, d, generator=gen).bfloat16()
+    out = torch.full_like(q, float("nan")).to(DEV)
+    scale = d ** -0.5
+    for _ in range(2):                           # the second call finds the counters as the first left them
+        out.fill_(float("nan"))
+        run_prefill(kernel, q.to(DEV), out, kc, vc, q_lens, kv_lens, q_start, table, scale, window)
+    got = out.double().cpu()
+    for r in range(n_reqs):
+        want = causal_attention_float64(q[q_start[r]:q_start[r] + q_lens[r]].float(), k_all[r], v_all[r],
+                                        kv_lens[r] - q_lens[r], scale, window)
+        torch.testing.assert_close(got[q_start[r]:q_start[r] + q_lens[r]], want, **tol(torch.bfloat16))
+
+
 @pytest.mark.parametrize("kernel", ["mma", "tc", "tc_parts"])
 @pytest.mark.parametrize("where", ["first", "far", "page_edge", "diagonal", "window_edge", "just_outside"])
 def test_attention_prefill_finds_the_one_key_that_matters(kernel, where):

@@ -256,7 +256,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const int s = n & 1;
       if (n >= 2 &&
           !__all_sync(0xffffffffu, mbar_wait(gt_smem_u32(&work_empty[s]), (uint32_t)((n >> 1) - 1) & 1u, abort_flag))) {
-        if (lane == 0) { set_error(p.err, kErrWait, 9, n, s); *abort_flag = 1; }
+        if (lane == 0) { set_error(p.err, kErrWait, 9, n, s); *abort_flag = 1; tl_value(31, 9, (unsigned)n); }
         return false;
       }
       if (lane == 0) {
@@ -273,7 +273,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       for (int t = 0; t < kAtQT; ++t) {
         if (n >= 2 &&
             !__all_sync(0xffffffffu, mbar_wait(q_empty(t, s), (uint32_t)((n >> 1) - 1) & 1u, abort_flag))) {
-          if (lane == 0) { set_error(p.err, kErrWait, 10, n, t); *abort_flag = 1; }
+          if (lane == 0) { set_error(p.err, kErrWait, 10, n, t); *abort_flag = 1; tl_value(31, 10, (unsigned)(n * 2 + t)); }
           return false;
         }
         if (lane == 0) {
@@ -338,7 +338,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           const int page_next = lookup(walk, j + 1);       // under way while this stage waits and is issued
           // both issuers gave the stage back (a fresh barrier counts as given back once)
           ok = __all_sync(0xffffffffu, mbar_wait(gt_smem_u32(&kv_empty[st]), sph ^ 1u, abort_flag));
-          if (!ok) { if (lane == 0) { set_error(p.err, kErrWait, 11, j, st); *abort_flag = 1; } break; }
+          if (!ok) { if (lane == 0) { set_error(p.err, kErrWait, 11, j, st); *abort_flag = 1; tl_value(31, 11, (unsigned)((n << 16) | (j << 4) | st)); } break; }
           const uint32_t full = gt_smem_u32(&kv_full[st]);
           if (lane == 0) mbar_expect_tx(full, STAGE_BYTES);
           __syncwarp();
@@ -439,10 +439,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         if (!ended && pd_size < 2) {
           if (j >= n_kt) {
-            // the item is walked through: its queries are free after the products issued so far
-            if (!q_given) { umma_commit(q_empty(t, par)); q_given = true; }
+            // The item is walked through: its queries are free after the products issued so far.
+            // Only queries that have arrived are given back: an item without key tiles is walked
+            // through at once, and a release that came before the producer had waited for the
+            // release of the item two before would put the barrier a phase ahead of that wait.
+            if (!q_given) {
+              if (!q_seen) q_seen = mbar_test(q_full(t, par), (uint32_t)(n >> 1) & 1u);
+              if (q_seen) { umma_commit(q_empty(t, par)); q_given = true; progressed = true; }
+            }
             const int s = (n + 1) & 1;
-            if (mbar_test(gt_smem_u32(&work_full[s]), (uint32_t)((n + 1) >> 1) & 1u)) {
+            if (q_given && mbar_test(gt_smem_u32(&work_full[s]), (uint32_t)((n + 1) >> 1) & 1u)) {
               ++n;
               const AttnItem it = items[s];
               mbar_arrive(gt_smem_u32(&work_empty[s]));
@@ -500,7 +506,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (progressed) {
           idle = 0;
         } else if (++idle >= kGtSpinLimit || ((idle & 1023u) == 1023u && *abort_flag)) {
-          if (idle >= kGtSpinLimit) { set_error(p.err, kErrWait, 12, n, (int)g_pv); *abort_flag = 1; }
+          // what it was waiting for: tile, item, then pending key tiles | key tile of the item | products issued
+          if (idle >= kGtSpinLimit) {
+            set_error(p.err, kErrWait, 12 + 100 * t, n, (pd_size << 28) | ((j & 0xfff) << 16) | (int)(g_pv & 0xffffu));
+            *abort_flag = 1;
+          }
+          tl_value(31, 12, (unsigned)((t << 31) | (n << 24) | (pd_size << 22) | ((j & 0xff) << 14) | ((n_kt & 0xff) << 6) | (ended ? 32 : 0) | (q_seen ? 16 : 0) | (st << 2)));
           break;
         }
       }
@@ -521,7 +532,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     for (int n = 0; ok; ++n) {
       const int s = n & 1;
       ok = __all_sync(0xffffffffu, mbar_wait(gt_smem_u32(&work_full[s]), (uint32_t)(n >> 1) & 1u, abort_flag));
-      if (!ok) { if (lane == 0) { set_error(p.err, kErrWait, 17, n, t); *abort_flag = 1; } break; }
+      if (!ok) { if (lane == 0) { set_error(p.err, kErrWait, 17, n, t); *abort_flag = 1; tl_value(31, 17, (unsigned)(n * 2 + t)); } break; }
       const AttnItem it = items[s];
       __syncwarp();
       if (lane == 0) mbar_arrive(gt_smem_u32(&work_empty[s]));
@@ -538,7 +549,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       for (int j = 0; j < my_kt && ok; ++j, ++g) {
         const int b = g & 1;
         ok = __all_sync(0xffffffffu, mbar_wait(s_full(t, b), (g >> 1) & 1u, abort_flag));
-        if (!ok) { if (lane == 0) { set_error(p.err, kErrWait, 18, j, t); *abort_flag = 1; } break; }
+        if (!ok) { if (lane == 0) { set_error(p.err, kErrWait, 18, j, t); *abort_flag = 1; tl_value(31, 18, (unsigned)((n << 20) | (j << 8) | (my_kt << 1) | t)); } break; }
         tc_fence_after();
         if (blockIdx.x == 0 && row == 0) tl_own(2 + t, tl_n, 30, 70 + t, g);
         uint32_t sraw[kAtBN];
@@ -584,7 +595,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           if (j > 0) {
             // the product that added the key tile before to the output has to be done
             ok = __all_sync(0xffffffffu, mbar_wait(p_empty(t, (g - 1u) & 1u), ((g - 1u) >> 1) & 1u, abort_flag));
-            if (!ok) { if (lane == 0) { set_error(p.err, kErrWait, 19, j, t); *abort_flag = 1; } break; }
+            if (!ok) { if (lane == 0) { set_error(p.err, kErrWait, 19, j, t); *abort_flag = 1; tl_value(31, 19, (unsigned)(n * 2 + t)); } break; }
             tc_fence_after();
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
@@ -633,7 +644,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
       if (my_kt > 0) {
         ok = __all_sync(0xffffffffu, mbar_wait(o_full(t), n_out & 1u, abort_flag));
-        if (!ok) { if (lane == 0) { set_error(p.err, kErrWait, 20, n, t); *abort_flag = 1; } break; }
+        if (!ok) { if (lane == 0) { set_error(p.err, kErrWait, 20, n, t); *abort_flag = 1; tl_value(31, 20, (unsigned)(n * 2 + t)); } break; }
         ++n_out;
         tc_fence_after();
       }
@@ -709,7 +720,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       if (row == 0) {
         int seen = 0;
-        for (unsigned spin = 0; spin < kGtSpinLimit; ++spin) {
+        unsigned spin = 0;
+        for (; spin < kGtSpinLimit; ++spin) {
           asm volatile("ld.acquire.gpu.global.s32 %0, [%1];\n" : "=r"(seen) : "l"(count) : "memory");
           if (seen >= it.n_parts - 1 || ((spin & 1023u) == 1023u && *abort_flag)) break;
           __nanosleep(64);
@@ -719,6 +731,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           *count = 0;                   // ready for the next launch
         } else {
           set_error(p.err, kErrWait, 21, it.index, seen);
+          tl_value(31, 21, (unsigned)((n << 20) | (seen << 12) | (it.n_parts << 4) | t));
           *abort_flag = 1;
         }
         tl_value(30, 40 + t, (unsigned)it.index);
