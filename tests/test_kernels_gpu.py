@@ -4,6 +4,8 @@ from __future__ import annotations
 
 import math
 
+import random
+
 import pytest
 import torch
 
@@ -579,6 +581,50 @@ def test_attention_prefill_more_items_than_blocks(kernel, hq, hkv, d, page, wind
         want = causal_attention_float64(q[q_start[r]:q_start[r] + q_lens[r]].float(), k_all[r], v_all[r],
                                         kv_lens[r] - q_lens[r], scale, window)
         torch.testing.assert_close(got[q_start[r]:q_start[r] + q_lens[r]], want, **tol(torch.bfloat16))
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_attention_prefill_random_batches(seed):
+    """Random batches of whole prompts and portions, head counts, head sizes, page sizes and windows
+    through the tcgen05 kernel, with the work list as the engine makes it and with every block of
+    tokens cut into parts."""
+    from tokamak_b200.csrc import ops
+    rng = random.Random(100 + seed)
+    hq, hkv = rng.choice([(4, 2), (8, 1), (6, 6), (5, 5), (16, 4)])
+    d = rng.choice([64, 128])
+    page = rng.choice([8, 16, 32, 64, 128])
+    window = rng.choice([None, None, 37, 300, 1000])
+    n_reqs = rng.randint(1, 5)
+    q_lens = [rng.choice([2, 3, 63, 64, 65, 127, 128, 129, 255, 256, 257, rng.randint(2, 900)]) for _ in range(n_reqs)]
+    kv_lens = [q + rng.choice([0, 0, 1, 63, 64, 200, rng.randint(0, 1500)]) for q in q_lens]
+    max_pages = max(-(-l // page) for l in kv_lens)
+    num_pages = n_reqs * max_pages + 2
+    table = make_tables(n_reqs, max_pages, num_pages, seed=seed)
+    gen = torch.Generator().manual_seed(seed)
+    k_all = [torch.randn(l, hkv, d, generator=gen).bfloat16().float() for l in kv_lens]
+    v_all = [torch.randn(l, hkv, d, generator=gen).bfloat16().float() for l in kv_lens]
+    kc = torch.full((num_pages, hkv, page, d), float("nan"), dtype=torch.bfloat16)
+    vc = torch.full_like(kc, float("nan"))
+    for r in range(n_reqs):
+        for pg in range(-(-kv_lens[r] // page)):
+            rows = slice(pg * page, min((pg + 1) * page, kv_lens[r]))
+            kc[int(table[r, pg]), :, :rows.stop - rows.start] = k_all[r][rows].transpose(0, 1).bfloat16()
+            vc[int(table[r, pg]), :, :rows.stop - rows.start] = v_all[r][rows].transpose(0, 1).bfloat16()
+    kc, vc = kc.to(DEV), vc.to(DEV)
+    zero_rest_of_last_pages(kc, vc, table, kv_lens, page)
+    q_start = [sum(q_lens[:r]) for r in range(n_reqs)]
+    q = torch.randn(sum(q_lens), hq, d, generator=gen).bfloat16()
+    scale = d ** -0.5
+    want = [causal_attention_float64(q[q_start[r]:q_start[r] + q_lens[r]].float(), k_all[r], v_all[r],
+                                     kv_lens[r] - q_lens[r], scale, window) for r in range(n_reqs)]
+    for kernel in ("tc", "tc_parts"):
+        if kernel == "tc_parts" and max(kv_lens) < 2 * ops.PREFILL_TC_MIN_PART * ops.PREFILL_TC_KEYS:
+            continue
+        out = torch.full_like(q, float("nan")).to(DEV)
+        run_prefill(kernel, q.to(DEV), out, kc, vc, q_lens, kv_lens, q_start, table, scale, window)
+        got = out.double().cpu()
+        for r in range(n_reqs):
+            torch.testing.assert_close(got[q_start[r]:q_start[r] + q_lens[r]], want[r], **tol(torch.bfloat16))
 
 
 @pytest.mark.parametrize("kernel", ["mma", "tc", "tc_parts"])
