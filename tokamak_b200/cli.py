@@ -42,6 +42,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--attention-policy", default="full")
     ap.add_argument("--kv-watermark", type=float, default=0.0,
                     help="share of the page pool that an admission leaves free while other requests run")
+    ap.add_argument("--step-token-multiple", type=int, default=128,
+                    help="a step of more tokens than this is cut down to a multiple of it by ending a prompt "
+                         "portion earlier (the token tile of the matrix products; 1: steps as planned)")
     ap.add_argument("--write-random", metavar="DIR", help="write config.json and model.safetensors "
                     "with seeded random weights to DIR and exit")
     ap.add_argument("--config", help="config.json to take the sizes from (with --write-random)")
@@ -71,7 +74,8 @@ def main(argv: list[str] | None = None) -> int:
               kv_pool_tokens=args.kv_pool_tokens, max_batch_size=args.max_batch_size,
               gpu_memory_utilization=args.gpu_memory_utilization,
               max_num_batched_tokens=args.max_num_batched_tokens, prefill_chunk=args.prefill_chunk,
-              attention_policy=args.attention_policy, kv_watermark=args.kv_watermark)
+              attention_policy=args.attention_policy, kv_watermark=args.kv_watermark,
+              step_token_multiple=args.step_token_multiple)
     params = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
                             max_new_tokens=args.max_new_tokens, seed=args.seed,
                             ignore_eos=args.ignore_eos)
