@@ -110,6 +110,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
   // the products still run (the sums are added to it some microseconds later)
   float4 pre_r = make_float4(0.0f, 0.0f, 0.0f, 0.0f), pre_w = pre_r;
   float4 pre_cs23 = pre_r;      // q|k|v epilogue: pre_w = norm weights, pre_r / pre_cs23 = (cos, sin) pairs
+  float4 pre_r2 = pre_r;        // residual epilogue: the thread's second column (more than 32 tokens)
   int pre_c = -1;
   unsigned int tl_n = 0;        // time stamps of one thread of the blocks of row tile 1 (timeline builds only)
   const bool tl_me = warp == 2 && lane == 0 && blockIdx.x == 1 && blockIdx.y == 0;
@@ -237,6 +238,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
         pre_c = c;
         pre_r = *reinterpret_cast<const float4*>(p.resid + (size_t)(tile_c * p.bn + c) * p.rows_total + row);
         pre_w = *reinterpret_cast<const float4*>(p.norm_w + row);
+        const int c2 = c + 4 * cs;
+        if (c2 < p.bn && tile_c * p.bn + c2 < p.cols_total) {
+          pre_r2 = *reinterpret_cast<const float4*>(p.resid + (size_t)(tile_c * p.bn + c2) * p.rows_total + row);
+        }
       }
     }
     if (p.epilogue == kGtEpiQkvRope) {
@@ -399,6 +404,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
           if (p.epilogue == kGtEpiResidualNorm) {
             if (c == pre_c) {
               r = pre_r;
+              w = pre_w;
+            } else if (pre_c >= 0 && c == pre_c + 4 * csize) {
+              r = pre_r2;
               w = pre_w;
             } else {
               r = *reinterpret_cast<const float4*>(p.resid + (size_t)col * p.rows_total + row);
