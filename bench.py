@@ -603,6 +603,66 @@ def kernel_case(name: str, batch: int, ctx: int, iters: int, peaks: dict, portio
     return res
 
 
+def prefill_attention_timeline(batch: int, ctx: int, portion: int, sizes: str) -> int:
+    """Time stamps of the roles of the persistent prefill attention kernel on a few SMs (the library must
+    have been built with TOKAMAK_B200_NVCC_FLAGS=-DTK_TIMELINE): when the producer published an item, when
+    the softmax warps of query tile 0 / 1 started it, ended its key tiles, saw the last product and had
+    written their rows, and the stamps of one block's thread per role within the key tiles."""
+    import torch
+    from tokamak_b200.csrc import ops
+    cfg = SIZES[sizes][1] if sizes in SIZES else QWEN3_8B
+    hq, hkv, d, page = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], 16
+    dev = "cuda"
+    gen = torch.Generator(device=dev).manual_seed(0)
+    pages_per_req = -(-ctx // page)
+    num_pages = batch * pages_per_req
+    kc = torch.randn((num_pages, hkv, page, d), device=dev, generator=gen).bfloat16()
+    vc = torch.randn((num_pages, hkv, page, d), device=dev, generator=gen).bfloat16()
+    table = torch.randperm(num_pages, device=dev, generator=gen).to(torch.int32).view(batch, pages_per_req)
+    qn = min(portion or ctx, ctx)
+    q = torch.randn((batch * qn, hq, d), device=dev, generator=gen).bfloat16()
+    out = torch.empty_like(q)
+    err = torch.zeros(4, dtype=torch.int32, device=dev)
+    records, n_parts, n_split = ops.prefill_tc_records([r * qn for r in range(batch)], [qn] * batch, [ctx] * batch,
+                                                        list(range(batch)), heads=hq, sms=ops.sm_count(q.device))
+    items = ops.PrefillItems(torch.from_numpy(records).to(dev), n_parts, n_split)
+    run = lambda: ops.attention_prefill_tc(q, out, kc, vc, items, table, err, scale=d ** -0.5, window=None)
+    for _ in range(3):
+        run()
+    buf = ops.timeline_start(1 << 16)
+    torch.cuda.synchronize()
+    run()
+    torch.cuda.synchronize()
+    buf[0] = (buf.numel() - 1) // 2          # the roles' own ranges lie at the buffer's end
+    recs = [r for r in ops.timeline_read(buf) if r[0] > 0 and r[1] == 30]
+    if err.tolist()[0] != 0 or not recs:
+        print("error word", err.tolist(), "records", len(recs))
+        return 1
+    t0 = recs[0][0]
+    lengths = [int(r[5] - r[4]) for r in records]
+    what = {1: "published", 10: "tile 0 starts", 11: "tile 1 starts", 20: "tile 0 keys done", 21: "tile 1 keys done",
+            30: "tile 0 last product", 31: "tile 1 last product", 40: "tile 0 written", 41: "tile 1 written",
+            50: "tile 0 parts added up", 51: "tile 1 parts added up", 60: "issuer 0 has item", 61: "issuer 1 has item"}
+    coarse = [r for r in recs if r[2] < 70]
+    by_sm: dict = {}
+    for t, _, ph, sm, val in coarse:
+        by_sm.setdefault(sm, []).append(((t - t0) / 1e3, ph, val))
+    ends = sorted(max(x[0] for x in v) for v in by_sm.values())
+    print(f"{batch} x {qn} tokens at the end of {ctx}, {hq} heads: {len(records)} records, {n_split} blocks of tokens cut; "
+          f"blocks end after {ends[0]:.1f} / {ends[len(ends) // 2]:.1f} / {ends[-1]:.1f} us (first / median / last)")
+    for sm in sorted(by_sm)[1:3]:
+        print(f"SM {sm}")
+        for t, ph, val in by_sm[sm]:
+            n_rec = val // hq
+            tiles = lengths[n_rec] if n_rec < len(lengths) else 0
+            print(f"  {t:8.2f} us  item {val:5d} ({tiles:3d} key tiles)  {what.get(ph, ph)}")
+    fine = {70: "scores seen", 74: "probabilities given", 82: "S issued", 84: "probabilities seen", 86: "O += P V issued"}
+    print("one block, within its key tiles (the stamps of this block cost it a few percent)")
+    for t, _, ph, sm, val in [r for r in recs if r[2] >= 70][:64]:
+        print(f"  {(t - t0) / 1e3:8.2f} us  tile {ph & 1}  {fine.get(ph - (ph & 1), ph):20s} key tile {val}")
+    return 0
+
+
 def decode_timeline(batch: int, layers: int, ctx: int) -> int:
     """Lay the blocks of every kernel of two decode steps out on one time axis (the library must have
     been built with time stamps: TOKAMAK_B200_NVCC_FLAGS=-DTK_TIMELINE, see csrc/timeline.cuh).
@@ -702,7 +762,7 @@ def main() -> int:
     ap.add_argument("--kernel", default=None, help="time one kernel alone instead: attention_decode, attention_decode_split, "
                     "attention_prefill (tcgen05), attention_prefill_mma, rope_kv, rmsnorm, gemm_tc_decode, gemm_decode (library), "
                     "gemm_pair_swiglu, gemm_prefill_library (--ctx tokens), products_chain / products_separate (the four products "
-                    "between two attentions of a decode step, as one kernel or one by one); decode_timeline prints when the blocks of every "
+                    "between two attentions of a decode step, as one kernel or one by one); attention_prefill_timeline prints the time stamps of the persistent prefill attention kernel's roles; decode_timeline prints when the blocks of every "
                     "kernel of a decode step run (needs a library built with TOKAMAK_B200_NVCC_FLAGS=-DTK_TIMELINE)")
     ap.add_argument("--ctx", type=int, default=CONTEXT, help="context length of a --kernel case")
     ap.add_argument("--workload", default=None, choices=["throughput", "latency", "mixed"],
@@ -737,6 +797,8 @@ def main() -> int:
     steps = max(1, args.steps)
     if args.kernel == "decode_timeline":
         return decode_timeline(args.batch, args.layers or 3, args.ctx)
+    if args.kernel == "attention_prefill_timeline":
+        return prefill_attention_timeline(args.batch, args.ctx, args.portion, args.sizes)
     if args.kernel:
         print(json.dumps(kernel_case(args.kernel, args.batch, args.ctx, steps, load_peaks(), args.portion, args.sizes)))
         return 0
