@@ -12,8 +12,10 @@
 //                geometry in shared memory, and loads with TMA (cp.async.bulk.tensor, 128-byte
 //                swizzle, every block for itself): the query tiles into the buffers of the item's
 //                parity (two sets, so the next item's queries arrive while this one runs), then
-//                stages of one key tile and its value tile, page by page, into a ring that runs on
-//                across items; every lane looks one page up and issues one copy;
+//                key tiles and value tiles, page by page, into two rings that run on across items
+//                (a key tile is given back once its S is computed, a value tile after the second
+//                product, so keys are requested a step earlier than values); every lane looks one
+//                page up and issues one copy;
 //   warps 1, 10  one thread each issues tcgen05.mma for one query tile: S = Q K^T (M 128, N 64)
 //                into one of the tile's two score buffers in tensor memory, and O += P V
 //                (M 128, N head_dim) with P read from tensor memory and V straight from its page
@@ -154,7 +156,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   constexpr uint32_t Q_BYTES = kAtBM * D * 2;          // one query tile
   constexpr uint32_t KSUB_BYTES = kAtBN * 64 * 2;      // one sub-tile of a key or value tile
   constexpr uint32_t KV_BYTES = kAtBN * D * 2;         // one key tile (or one value tile)
-  constexpr uint32_t STAGE_BYTES = 2 * KV_BYTES;
+  constexpr uint32_t STAGE_BYTES = 2 * KV_BYTES;       // a key tile and its value tile
+  constexpr uint32_t V_RING = kAtStages * KV_BYTES;    // the value tiles' ring lies behind the key tiles'
   constexpr uint32_t TMEM_COLS = 512;   // query tile t: scores at t*128 + {0, 64}, outputs at 256 + t*128
   constexpr uint32_t DATA_BYTES = 2 * kAtQT * Q_BYTES + kAtStages * STAGE_BYTES;
 
@@ -165,9 +168,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const uint32_t q_smem = base;                        // [item parity][query tile]
   const uint32_t kv_smem = q_smem + 2 * kAtQT * Q_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + DATA_BYTES);
-  uint64_t* kv_full = bars;                       // kAtStages
-  uint64_t* kv_empty = kv_full + kAtStages;       // kAtStages
-  uint64_t* work_full = kv_empty + kAtStages;     // 2
+  // Key tiles and value tiles have rings of their own: a key tile is given back as soon as its
+  // S is computed, a value tile only after the softmax and the second product, so the keys of the
+  // tile after next can be on their way a whole step earlier than in a ring of (key, value) pairs.
+  uint64_t* k_full = bars;                        // kAtStages each
+  uint64_t* k_empty = k_full + kAtStages;
+  uint64_t* v_full = k_empty + kAtStages;
+  uint64_t* v_empty = v_full + kAtStages;
+  uint64_t* work_full = v_empty + kAtStages;      // 2
   uint64_t* work_empty = work_full + 2;           // 2
   uint64_t* tile_bars = work_empty + 2;           // per query tile: q_full[2] q_empty[2] s_full[2] p_full[2] p_empty[2] o_full
   auto q_full = [&](int t, int par) { return gt_smem_u32(tile_bars + t * 11 + par); };
@@ -188,8 +196,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   pdl_trigger();
   if (threadIdx.x == 0) {
     for (int s = 0; s < kAtStages; ++s) {
-      mbar_init(gt_smem_u32(&kv_full[s]), 1);
-      mbar_init(gt_smem_u32(&kv_empty[s]), kAtQT);      // one arrival per issuing warp
+      mbar_init(gt_smem_u32(&k_full[s]), 1);
+      mbar_init(gt_smem_u32(&k_empty[s]), kAtQT);       // one arrival per issuing warp
+      mbar_init(gt_smem_u32(&v_full[s]), 1);
+      mbar_init(gt_smem_u32(&v_empty[s]), kAtQT);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(gt_smem_u32(&work_full[s]), 1);
@@ -336,22 +346,25 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       for (int j = 0; (j < walk.n_kt || !nxt_out) && ok; ++j) {
         if (j < walk.n_kt) {
           const int page_next = lookup(walk, j + 1);       // under way while this stage waits and is issued
-          // both issuers gave the stage back (a fresh barrier counts as given back once)
-          ok = __all_sync(0xffffffffu, mbar_wait(gt_smem_u32(&kv_empty[st]), sph ^ 1u, abort_flag));
-          if (!ok) { if (lane == 0) { set_error(p.err, kErrWait, 11, j, st); *abort_flag = 1; tl_value(31, 11, (unsigned)((n << 16) | (j << 4) | st)); } break; }
-          const uint32_t full = gt_smem_u32(&kv_full[st]);
-          if (lane == 0) mbar_expect_tx(full, STAGE_BYTES);
-          __syncwarp();
-          if (loader) {
-            const int key0 = key0_of(walk, j);
-            if (page < 0 || page >= p.num_pages) {
-              set_error(p.err, kErrPage, cur.index / p.n_q_heads, key0 / p.page_size, page);
-              page = 0;
-            }
-            const int row = (page * p.n_kv_heads + walk.hkv) * p.page_size + (key0 % p.page_size);
-            const uint32_t dst = kv_smem + st * STAGE_BYTES + (is_v ? KV_BYTES : 0u) + c * KSUB_BYTES + u * kpl * 128;
-            tma_load_2d(dst, is_v ? &map_v : &map_k, c * 64, row, full);
+          const int key0 = key0_of(walk, j);
+          if (loader && (page < 0 || page >= p.num_pages)) {
+            set_error(p.err, kErrPage, cur.index / p.n_q_heads, key0 / p.page_size, page);
+            page = 0;
           }
+          const int row = (page * p.n_kv_heads + walk.hkv) * p.page_size + (key0 % p.page_size);
+          const uint32_t dst = kv_smem + st * KV_BYTES + c * KSUB_BYTES + u * kpl * 128;
+          // the key tile, then the value tile: both issuers gave the buffer back (a fresh barrier
+          // counts as given back once)
+          ok = __all_sync(0xffffffffu, mbar_wait(gt_smem_u32(&k_empty[st]), sph ^ 1u, abort_flag));
+          if (!ok) { if (lane == 0) { set_error(p.err, kErrWait, 11, j, st); *abort_flag = 1; tl_value(31, 11, (unsigned)((n << 16) | (j << 4) | st)); } break; }
+          if (lane == 0) mbar_expect_tx(gt_smem_u32(&k_full[st]), KV_BYTES);
+          __syncwarp();
+          if (loader && !is_v) tma_load_2d(dst, &map_k, c * 64, row, gt_smem_u32(&k_full[st]));
+          ok = __all_sync(0xffffffffu, mbar_wait(gt_smem_u32(&v_empty[st]), sph ^ 1u, abort_flag));
+          if (!ok) { if (lane == 0) { set_error(p.err, kErrWait, 11, j, 8 + st); *abort_flag = 1; tl_value(31, 11, (unsigned)((n << 16) | (j << 4) | 8 | st)); } break; }
+          if (lane == 0) mbar_expect_tx(gt_smem_u32(&v_full[st]), KV_BYTES);
+          __syncwarp();
+          if (loader && is_v) tma_load_2d(dst + V_RING, &map_v, c * 64, row, gt_smem_u32(&v_full[st]));
           if (++st == kAtStages) { st = 0; sph ^= 1u; }
           page = page_next;
         }
@@ -387,7 +400,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // issuing is a chain of dependent instructions in one thread, and every one of them counts.
       const uint64_t desc_q = umma_desc_sw128(q_smem + t * Q_BYTES);
       const uint64_t desc_k = umma_desc_sw128(kv_smem);
-      const uint64_t desc_v = umma_desc_sw128_mn(kv_smem + KV_BYTES, KSUB_BYTES);
+      const uint64_t desc_v = umma_desc_sw128_mn(kv_smem + V_RING, KSUB_BYTES);
       const uint32_t tmem_s_t = tmem_base + (uint32_t)(t * 128);
       const uint32_t tmem_o_t = tmem_base + (uint32_t)(256 + t * 128);
       int st = 0;                // stage of the key tile whose S comes next
@@ -400,7 +413,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       bool q_seen = false, q_given = true, ended = false;
       // up to two key tiles whose S has been issued (or that are not this tile's) and whose second
       // product and hand-back of the stage are still to come, oldest first
-      // (packed: bit 0 this tile's, bit 1 its first, bit 2 its last key tile, bits 3.. the stage)
+      // (packed: bit 0 this tile's, bit 1 its first, bit 2 its last key tile, bit 3 the phase, bits 4.. the stage)
       int pd0 = 0, pd1 = 0;
       int pd_head = 0, pd_size = 0;
       unsigned idle = 0;
@@ -413,10 +426,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (pd_size > 0) {
           const int pd = pd_head ? pd1 : pd0;
           const bool pd_mine = pd & 1, pd_first = pd & 2, pd_last = pd & 4;
-          const int pd_st = pd >> 3;
-          if (!pd_mine || mbar_test(p_full(t, g_pv & 1), (g_pv >> 1) & 1u)) {
+          const int pd_st = (pd >> 4) & 7;
+          const uint32_t pd_ph = (uint32_t)(pd >> 3) & 1u;
+          // the values have arrived (also where this tile does not read them: a buffer is given
+          // back only after it was seen filled, or the barrier could get a phase ahead of the
+          // producer's wait), and the probabilities are there
+          if (mbar_test(gt_smem_u32(&v_full[pd_st]), pd_ph) &&
+              (!pd_mine || mbar_test(p_full(t, g_pv & 1), (g_pv >> 1) & 1u))) {
             if (pd_mine) {
-              const uint64_t desc_vs = desc_v + (uint64_t)((uint32_t)pd_st * (STAGE_BYTES >> 4));
+              const uint64_t desc_vs = desc_v + (uint64_t)((uint32_t)pd_st * (KV_BYTES >> 4));
               const int b = g_pv & 1;
               if (blockIdx.x == 0) tl_own(t, tl_n, 30, 84 + t, g_pv);
               tc_fence_after();
@@ -431,7 +449,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
               ++g_pv;
               if (blockIdx.x == 0) tl_own(t, tl_n, 30, 86 + t, g_pv);
             }
-            umma_commit(gt_smem_u32(&kv_empty[pd_st]));    // this issuer is done with the stage
+            umma_commit(gt_smem_u32(&v_empty[pd_st]));     // this issuer is done with the value tile
             pd_head ^= 1;
             --pd_size;
             progressed = true;
@@ -472,7 +490,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // S of a key tile of this query tile goes into the buffer that held the probabilities
             // of the key tile two before: their second product must have been issued (the tensor
             // cores run this thread's products in order)
-            bool can = mbar_test(gt_smem_u32(&kv_full[st]), sph) && (!mine || g_qk - g_pv <= 1u);
+            bool can = mbar_test(gt_smem_u32(&k_full[st]), sph) && (!mine || g_qk - g_pv <= 1u);
             if (can && mine && !q_seen) {
               q_seen = mbar_test(q_full(t, par), (uint32_t)(n >> 1) & 1u);
               can = q_seen;
@@ -480,7 +498,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (can) {
               if (mine) {
                 const uint64_t desc_qs = desc_q + (uint64_t)((uint32_t)par * ((kAtQT * Q_BYTES) >> 4));
-                const uint64_t desc_ks = desc_k + (uint64_t)((uint32_t)st * (STAGE_BYTES >> 4));
+                const uint64_t desc_ks = desc_k + (uint64_t)((uint32_t)st * (KV_BYTES >> 4));
                 const int b = g_qk & 1;
                 tc_fence_after();
 #pragma unroll
@@ -493,7 +511,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 ++g_qk;
                 if (blockIdx.x == 0) tl_own(t, tl_n, 30, 82 + t, g_qk);
               }
-              const int pd_new = (mine ? 1 : 0) | (kt == my.first ? 2 : 0) | (kt == my.last ? 4 : 0) | (st << 3);
+              umma_commit(gt_smem_u32(&k_empty[st]));      // the key tile is free once S is computed
+              const int pd_new = (mine ? 1 : 0) | (kt == my.first ? 2 : 0) | (kt == my.last ? 4 : 0) | ((int)sph << 3) | (st << 4);
               if (pd_head ^ (pd_size & 1)) pd1 = pd_new; else pd0 = pd_new;     // behind the pending one, if there is one
               ++pd_size;
               ++j;
