@@ -634,7 +634,12 @@ def prefill_attention_timeline(batch: int, ctx: int, portion: int, sizes: str) -
     run()
     torch.cuda.synchronize()
     buf[0] = (buf.numel() - 1) // 2          # the roles' own ranges lie at the buffer's end
-    recs = [r for r in ops.timeline_read(buf) if r[0] > 0 and r[1] == 30]
+    every = [r for r in ops.timeline_read(buf) if r[0] > 0]
+    recs = [r for r in every if r[1] == 30]
+    clocks = [0] * 9
+    for _, kernel, phase, _, value in every:
+        if kernel == 32 and phase < 9:
+            clocks[phase] += value
     if err.tolist()[0] != 0 or not recs:
         print("error word", err.tolist(), "records", len(recs))
         return 1
@@ -656,10 +661,46 @@ def prefill_attention_timeline(batch: int, ctx: int, portion: int, sizes: str) -
             n_rec = val // hq
             tiles = lengths[n_rec] if n_rec < len(lengths) else 0
             print(f"  {t:8.2f} us  item {val:5d} ({tiles:3d} key tiles)  {what.get(ph, ph)}")
+    if clocks[8]:
+        parts = ["waiting for S", "S loaded", "maximum", "exponentials, sum, conversion, store issued", "store arrived",
+                 "fence and arrival", "loop", "between items"]
+        print(f"one softmax thread of each query tile of block 0, clocks per key tile ({clocks[8]} key tiles):")
+        for name, c in zip(parts, clocks):
+            print(f"  {c / clocks[8]:7.1f}  {name}")
     fine = {70: "scores seen", 74: "probabilities given", 82: "S issued", 84: "probabilities seen", 86: "O += P V issued"}
     print("one block, within its key tiles (the stamps of this block cost it a few percent)")
     for t, _, ph, sm, val in [r for r in recs if r[2] >= 70][:64]:
         print(f"  {(t - t0) / 1e3:8.2f} us  tile {ph & 1}  {fine.get(ph - (ph & 1), ph):20s} key tile {val}")
+    return 0
+
+
+def tcgen05_probe() -> int:
+    """Two tables of what the hardware gives the tcgen05 kernels (csrc/tcgen05_probe.cu): the cost of
+    issuing a tcgen05.mma by shape, operand source and number of issuing threads, and the clocks one
+    softmax warp of the prefill attention kernel needs for a 64-key tile in several forms of its loop."""
+    from tokamak_b200.csrc import ops
+    print("tcgen05.mma M 128 x N x K 16, bfloat16, 96 in a row: clocks per product until issued / until done")
+    modes = {0: "one thread, A and B in shared memory", 1: "one thread, A in tensor memory",
+             2: "two threads, A and B in shared memory", 3: "two threads, A in tensor memory",
+             4: "one thread, 8 x (N, shared) then 4 x (N 128, A in tensor memory)"}
+    for mode, name in modes.items():
+        for n in (16, 64, 128, 256):
+            if n > 128 and mode in (2, 3, 4) or mode == 4 and n == 16:
+                continue
+            for _ in range(2):
+                rows = ops.probe_mma_issue(mode, n)
+            cells = " | ".join(f"{r['issue_clk']:6.1f} / {r['done_clk']:6.1f} clk ({r['done_ns']:5.1f} ns)" for r in rows)
+            print(f"  {name:66s} N {n:3d}: {cells}")
+    print("one softmax warp, 64 keys: clocks per tile (load, maximum, exponentials + conversion + store, store arrived, fence)")
+    forms = {0: "as the kernel has it", 1: "four chains for the maximum", 2: "second half loaded under the first maximum",
+             3: "four chains and the split load", 4: "1 exponential in 4 by polynomial", 5: "2 in 4 by polynomial",
+             6: "all by polynomial"}
+    for variant, name in forms.items():
+        for wg in (1, 2):
+            for _ in range(2):
+                r = ops.probe_softmax_tile(variant, wg)
+            print(f"  {name:44s} {wg} warp(s) per scheduler: {r['tile']:7.1f}  ({r['load']:.0f}, {r['maximum']:.0f}, "
+                  f"{r['exponentials_store']:.0f}, {r['store_arrived']:.0f}, {r['fence']:.0f})")
     return 0
 
 
@@ -762,7 +803,7 @@ def main() -> int:
     ap.add_argument("--kernel", default=None, help="time one kernel alone instead: attention_decode, attention_decode_split, "
                     "attention_prefill (tcgen05), attention_prefill_mma, rope_kv, rmsnorm, gemm_tc_decode, gemm_decode (library), "
                     "gemm_pair_swiglu, gemm_prefill_library (--ctx tokens), products_chain / products_separate (the four products "
-                    "between two attentions of a decode step, as one kernel or one by one); attention_prefill_timeline prints the time stamps of the persistent prefill attention kernel's roles; decode_timeline prints when the blocks of every "
+                    "between two attentions of a decode step, as one kernel or one by one); attention_prefill_timeline prints the time stamps of the persistent prefill attention kernel's roles; tcgen05_probe prints what issuing a tcgen05.mma costs by shape and what a softmax warp needs for a key tile; decode_timeline prints when the blocks of every "
                     "kernel of a decode step run (needs a library built with TOKAMAK_B200_NVCC_FLAGS=-DTK_TIMELINE)")
     ap.add_argument("--ctx", type=int, default=CONTEXT, help="context length of a --kernel case")
     ap.add_argument("--workload", default=None, choices=["throughput", "latency", "mixed"],
@@ -797,6 +838,8 @@ def main() -> int:
     steps = max(1, args.steps)
     if args.kernel == "decode_timeline":
         return decode_timeline(args.batch, args.layers or 3, args.ctx)
+    if args.kernel == "tcgen05_probe":
+        return tcgen05_probe()
     if args.kernel == "attention_prefill_timeline":
         return prefill_attention_timeline(args.batch, args.ctx, args.portion, args.sizes)
     if args.kernel:

@@ -113,6 +113,25 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
+// In builds with time stamps the softmax threads also sum, in registers, the clocks they spend in
+// each part of a key tile; block 0's first row of each query tile reports the sums per item
+// (kernel 32, phase = part, value = clocks; phase 8 = key tiles).  TL_AFTER(x) keeps the clock
+// read behind the computation of x.
+#ifdef TK_TIMELINE
+#define TL_AFTER(x) asm volatile("" ::"r"(x) : "memory")
+#define TLC_DECL long long tlc_last = clock64(); unsigned tlc_acc[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u}; unsigned tlc_n = 0u
+#define TLC(i) { const long long tlc_now = clock64(); tlc_acc[i] += (unsigned)(tlc_now - tlc_last); tlc_last = tlc_now; }
+#define TLC_TILE ++tlc_n
+#define TLC_REPORT(on) { if (on) { for (int i_ = 0; i_ < 8; ++i_) tl_value(32, i_, tlc_acc[i_]); tl_value(32, 8, tlc_n); } \
+    for (int i_ = 0; i_ < 8; ++i_) tlc_acc[i_] = 0u; tlc_n = 0u; }
+#else
+#define TL_AFTER(x)
+#define TLC_DECL
+#define TLC(i)
+#define TLC_TILE
+#define TLC_REPORT(on)
+#endif
+
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
@@ -547,6 +566,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint32_t n_out = 0;          // items in which this query tile had key tiles
     unsigned int tl_n = 0;
     bool ok = true;
+    TLC_DECL;
 
     for (int n = 0; ok; ++n) {
       const int s = n & 1;
@@ -565,11 +585,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       float m_ref = -INFINITY, l_sum = 0.0f;
       if (row == 0) tl_value(30, 10 + t, (unsigned)it.index);
 
+      TLC(7);       // between items: the rows written out, the next item taken
       for (int j = 0; j < my_kt && ok; ++j, ++g) {
         const int b = g & 1;
+        TLC(6);     // the loop itself
         ok = __all_sync(0xffffffffu, mbar_wait(s_full(t, b), (g >> 1) & 1u, abort_flag));
         if (!ok) { if (lane == 0) { set_error(p.err, kErrWait, 18, j, t); *abort_flag = 1; tl_value(31, 18, (unsigned)((n << 20) | (j << 8) | (my_kt << 1) | t)); } break; }
         tc_fence_after();
+        TLC(0);     // waiting for S
         if (blockIdx.x == 0 && row == 0) tl_own(2 + t, tl_n, 30, 70 + t, g);
         uint32_t sraw[kAtBN];
         {
@@ -579,6 +602,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           tmem_ld32(tmem_s + (uint32_t)(b * kAtBN) + 32, hi);
           tmem_wait_ld();
         }
+        TL_AFTER(sraw[kAtBN - 1]);
+        TLC(1);     // S loaded
 
         // Scores stay unscaled in sv; the softmax scale (> 0) is folded into the exponent below.
         // A tile wholly below this row's diagonal and inside its window needs no mask.
@@ -608,6 +633,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         mx *= p.scale_log2;       // -inf stays -inf
         const float m_new = fmaxf(m_ref, mx);
         const bool need = m_new > m_ref + kAtRescale;     // also true when the first visible key arrives
+        TL_AFTER(__float_as_uint(m_new));
+        TLC(2);     // the maximum
         if (__any_sync(0xffffffffu, need)) {
           const float corr = need ? exp2f(m_ref - m_new) : 1.0f;
           if (need) { l_sum *= corr; m_ref = m_new; }
@@ -651,13 +678,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             packed[c] = *reinterpret_cast<const uint32_t*>(&h2);
           }
           tmem_st32(tmem_s + (uint32_t)(b * kAtBN), packed);
+          TL_AFTER(__float_as_uint(l_sum));
+          TLC(3);   // exponentials, sum, conversion, store issued (and a rescaled output, when it happens)
           tmem_wait_st();
         }
+        TLC(4);     // the store has arrived
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(p_full(t, b));
+        TLC(5);     // fence and arrival
+        TLC_TILE;
         if (blockIdx.x == 0 && row == 0) tl_own(2 + t, tl_n, 30, 74 + t, g);
       }
+      TLC_REPORT(blockIdx.x == 0 && row == 0);
       if (!ok) break;
       if (row == 0) tl_value(30, 20 + t, (unsigned)it.index);
 

@@ -21,6 +21,8 @@ _SIGNATURES: dict[str, list] = {
     "tk_decode_begin": [_P, c_int, c_int, _P, c_int, _P, c_longlong, _P, c_int, c_int, _P, _P, _P, _P, _P],
     "tk_sample_slots": [_P, c_longlong, _P, _P, c_int, _P, c_int, c_int, _P, _P],
     "tk_wait_probe": [c_uint, _P, _P],
+    "tk_probe_mma_issue": [c_int, c_int, c_int, _P, _P, _P],
+    "tk_probe_softmax_tile": [c_int, c_int, c_int, c_int, _P, _P],
     "tk_gemm_chain": [_P, c_int, c_int, _P, _P, _P, c_int, _P],
     "tk_gemm_chain_blocks": [],
     "tk_gemm_chain_max_phases": [],

@@ -156,6 +156,42 @@ def wait_probe(limit: int, err: torch.Tensor) -> None:
     _check(_lib().tk_wait_probe(int(limit), err.data_ptr(), _stream()), "wait_probe")
 
 
+def probe_mma_issue(mode: int, n: int, reps: int = 96) -> list[dict]:
+    """Measurement aid (csrc/tcgen05_probe.cu): what ``reps`` tcgen05.mma of M 128 x N ``n`` x K 16
+    cost the issuing thread.  ``mode`` 0: both operands in shared memory; 1: A in tensor memory;
+    2 / 3: the same with two issuing threads; 4: eight of N ``n`` from shared memory, then four of
+    N 128 with A in tensor memory, as the prefill attention kernel issues them.  Per issuing thread:
+    clocks and nanoseconds per product until issued and until done."""
+    out = torch.zeros(8, dtype=torch.int64, device="cuda")
+    err = torch.zeros(4, dtype=torch.int32, device="cuda")
+    _check(_lib().tk_probe_mma_issue(int(mode), int(n), int(reps), out.data_ptr(), err.data_ptr(), _stream()),
+           "probe_mma_issue")
+    torch.cuda.synchronize()
+    if int(err[0]) != 0:
+        raise KernelError(f"probe_mma_issue: a bounded wait ran out (code {int(err[0])})")
+    host = out.tolist()
+    threads = 2 if mode in (2, 3) else 1
+    return [{"issue_clk": host[4 * i] / reps, "done_clk": host[4 * i + 1] / reps,
+             "issue_ns": host[4 * i + 2] / reps, "done_ns": host[4 * i + 3] / reps} for i in range(threads)]
+
+
+def probe_softmax_tile(variant: int, warpgroups: int, tiles: int = 400) -> dict:
+    """Measurement aid (csrc/tcgen05_probe.cu): clocks per 64-key tile of one softmax warp, with
+    ``warpgroups`` warps on every scheduler (1 or 2), in one of the loop's forms (0: as the prefill
+    attention kernel has it; 1: four chains for the maximum; 2: the second half of the scores
+    loaded under the first half's maximum; 3: both; 4 / 5 / 6: one, two, all four of every four
+    exponentials by a polynomial on the multiply-add pipe)."""
+    out = torch.zeros(16, dtype=torch.int32, device="cuda")
+    _check(_lib().tk_probe_softmax_tile(int(variant), int(warpgroups), int(tiles), sm_count(out.device),
+                                        out.data_ptr(), _stream()), "probe_softmax_tile")
+    torch.cuda.synchronize()
+    h = [int(x) & 0xFFFFFFFF for x in out.tolist()]
+    names = ["load", "maximum", "exponentials_store", "store_arrived", "fence"]
+    res = {k: h[i] / tiles for i, k in enumerate(names)}
+    res["tile"] = h[5] / tiles
+    return res
+
+
 def add_rmsnorm(resid: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor,
                 out: torch.Tensor, eps: float, rows: torch.Tensor | None = None) -> None:
     """x = resid (+ delta), written back unless ``rows`` is given; out = weight * x * rsqrt(mean x^2 + eps).
