@@ -920,6 +920,25 @@ def test_gemm_tcgen05_swapped_at_the_real_vocabulary(tokens):
         torch.testing.assert_close(got[:, lo:lo + 16384], want, rtol=1e-4, atol=2e-3)
 
 
+def test_the_tcgen05_probes_run_and_give_sane_clocks():
+    """The measurement aids of csrc/tcgen05_probe.cu: they end by themselves, report no wait that ran
+    out, and what they measure lies where a product and a softmax tile can lie."""
+    one = ops.probe_mma_issue(0, 64)
+    assert len(one) == 1 and 8.0 < one[0]["issue_clk"] <= one[0]["done_clk"] < 2000.0
+    two = ops.probe_mma_issue(3, 128)
+    assert len(two) == 2 and all(32.0 < r["done_clk"] < 4000.0 for r in two)     # 64 clocks of tensor time each
+    step = ops.probe_mma_issue(4, 64)
+    assert 16.0 < step[0]["done_clk"] < 2000.0
+    with pytest.raises(ops.KernelError):
+        ops.probe_mma_issue(2, 256)          # two accumulators of 256 columns and the A operand do not fit
+    alone = ops.probe_softmax_tile(0, 1)
+    beside = ops.probe_softmax_tile(0, 2)
+    assert 512.0 < alone["tile"] < 20000.0       # 64 exponentials of a warp take the unit 512 clocks
+    assert beside["tile"] > 0.9 * alone["tile"]
+    with pytest.raises(ops.KernelError):
+        ops.probe_softmax_tile(99, 1)
+
+
 def test_a_bounded_wait_that_runs_out_is_reported_and_leaves_the_engine_usable():
     """No correct launch makes a barrier wait of the tcgen05 kernels run out, so a kernel made for
     this test does: one block waits, with the kernels' own bounded wait and a limit of 1,024
