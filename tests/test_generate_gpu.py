@@ -242,6 +242,46 @@ def test_portions_and_admissions_launched_ahead_end_where_the_requests_end_alone
     assert llm.cache_manager.num_free_slots == llm.cache_manager.max_slots
 
 
+@pytest.mark.parametrize("seed", range(6))
+def test_random_workloads_launched_ahead_equal_the_same_workloads_step_by_step(seed):
+    """Random requests (lengths, limits, greedy or seeded sampling, an end-of-sequence token that some
+    of them meet) through random engine settings (slots, token budget, portion size, a pool that makes
+    requests wait or be preempted): with every step launched ahead of the read of the step before it
+    the requests end token for token as with plain steps, and nothing is left held."""
+    import random
+    from tokamak_b200 import SamplingParams
+    rng = random.Random(1000 + seed)
+    tag = "BC"[seed % 2]
+    vocab = tiny_configs.ALL[tag][0]["vocab_size"]
+    n_req = rng.randint(5, 12)
+    lengths = [rng.randint(2, 70) for _ in range(n_req)]
+    prompts = [random_tokens(vocab, n, seed=seed * 100 + i) for i, n in enumerate(lengths)]
+    params = [SamplingParams(temperature=rng.choice([0.0, 0.0, 0.8]), top_k=rng.choice([0, 8]), top_p=rng.choice([1.0, 0.9]),
+                             seed=seed * 1000 + i, max_new_tokens=rng.randint(1, 24)) for i in range(n_req)]
+    chunk = rng.choice([3, 8, 33])
+    settings = dict(max_seq_len=96, kv_pool_tokens=rng.choice([96, 160, 384]), max_batch_size=rng.randint(1, 5),
+                    max_num_batched_tokens=chunk + rng.randint(2, 12), prefill_chunk=chunk,
+                    step_token_multiple=rng.choice([1, 4, 128]))
+    llm = llm_for(tag, "float32", **settings)
+    llm.plain_steps = True
+    free = llm.generate(prompt_token_ids=prompts, sampling_params=params)
+    # an end-of-sequence token that at least one request produces in the middle of its run
+    long_runs = [o.output_token_ids for o in free if len(o.output_token_ids) >= 4]
+    if long_runs:
+        eos = rng.choice(long_runs)[2]
+        llm.model_config = dataclasses.replace(llm.model_config, eos_token_ids=(eos,))
+    want = llm.generate(prompt_token_ids=prompts, sampling_params=params)
+    assert llm.last_stats["steps_launched_ahead"] == 0
+    llm.plain_steps = False
+    got = llm.generate(prompt_token_ids=prompts, sampling_params=params)
+    assert [o.output_token_ids for o in got] == [o.output_token_ids for o in want], settings
+    assert [o.finish_reason for o in got] == [o.finish_reason for o in want]
+    assert llm.last_stats["steps_launched_ahead"] > 0
+    llm.cache_manager.check_invariants()
+    assert all(g.num_free == g.num_pages for g in llm.cache_manager.kv_groups)
+    assert llm.cache_manager.num_free_slots == llm.cache_manager.max_slots
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_steps_driven_by_the_slot_records_equal_steps_laid_out_by_the_host(dtype):
     """Steps of single next tokens whose tokens, positions, sampling parameters and generator

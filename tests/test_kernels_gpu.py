@@ -923,6 +923,7 @@ def test_gemm_tcgen05_swapped_at_the_real_vocabulary(tokens):
 def test_the_tcgen05_probes_run_and_give_sane_clocks():
     """The measurement aids of csrc/tcgen05_probe.cu: they end by themselves, report no wait that ran
     out, and what they measure lies where a product and a softmax tile can lie."""
+    from tokamak_b200.csrc import ops
     one = ops.probe_mma_issue(0, 64)
     assert len(one) == 1 and 8.0 < one[0]["issue_clk"] <= one[0]["done_clk"] < 2000.0
     two = ops.probe_mma_issue(3, 128)

