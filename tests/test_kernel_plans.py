@@ -13,13 +13,15 @@ def test_decode_splits_stay_in_one_wave_and_keep_the_warps_level():
         assert 1 <= s <= 128
         tiles = -(-kv_len // 16)
         if s > 1:
-            assert n_items * hkv * s <= 296                      # one wave of two blocks per SM
+            assert n_items * hkv * s <= 444                      # one wave: three blocks of two stages per SM
             per_split = -(-tiles // s)
             assert per_split >= 8                                # a block has enough to stream
             assert s * per_split >= tiles
     # the measured cases
-    assert ops.decode_splits(8, 8, 4096) == 4
-    assert ops.decode_splits(1, 8, 4096) == 32
+    assert ops.decode_splits(8, 8, 4096) == 6            # 384 blocks: two stages, three to an SM
+    assert ops.decode_splits(16, 8, 4096) == 3
+    assert ops.decode_splits(1, 8, 4096) == 32           # 256 blocks: three stages, two to an SM
+    assert ops.decode_splits(32, 8, 4096) == 1
     assert ops.decode_splits(64, 8, 4096) == 1
 
 

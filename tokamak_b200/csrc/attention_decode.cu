@@ -52,7 +52,7 @@ struct DecodeParams {
   float scale_log2;             // softmax scale * log2(e)
 };
 
-template <int D>
+template <int D, int STAGES>
 __global__ void __launch_bounds__(kDecWarps * 32)
 attn_decode_split_kernel(DecodeParams p) {
   pdl_trigger();
@@ -82,7 +82,7 @@ attn_decode_split_kernel(DecodeParams p) {
   const int my_begin = first_tile + split * per_split;
   const int my_end = min(my_begin + per_split, last_tile + 1);
 
-  unsigned char* my_smem = smem + warp * kDecStages * STAGE_BYTES;
+  unsigned char* my_smem = smem + warp * STAGES * STAGE_BYTES;
   const uint32_t my_smem_u32 = smem_u32(my_smem);
 
   float o[D / 8][4];
@@ -126,7 +126,7 @@ attn_decode_split_kernel(DecodeParams p) {
   // requested before the wait on that kernel; the tile that holds `pos`, and the queries, after.
   int warm = 0;
 #pragma unroll
-  for (; warm < kDecStages - 1; ++warm) {
+  for (; warm < STAGES - 1; ++warm) {
     const int tile = my_begin + warp + warm * kDecWarps;
     if (warm >= n_mine || tile >= last_tile) break;
     issue_load(tile, warm);
@@ -149,7 +149,7 @@ attn_decode_split_kernel(DecodeParams p) {
     }
   }
 
-  for (int s = warm; s < kDecStages - 1; ++s) {
+  for (int s = warm; s < STAGES - 1; ++s) {
     if (s < n_mine) issue_load(my_begin + warp + s * kDecWarps, s);
     cp_async_commit();
   }
@@ -157,14 +157,14 @@ attn_decode_split_kernel(DecodeParams p) {
   for (int i = 0; i < n_mine; ++i) {
     const int tile = my_begin + warp + i * kDecWarps;
     {
-      const int nxt = i + kDecStages - 1;
-      if (nxt < n_mine) issue_load(my_begin + warp + nxt * kDecWarps, nxt % kDecStages);
+      const int nxt = i + STAGES - 1;
+      if (nxt < n_mine) issue_load(my_begin + warp + nxt * kDecWarps, nxt % STAGES);
       cp_async_commit();
     }
-    cp_async_wait<kDecStages - 1>();
+    cp_async_wait<STAGES - 1>();
     __syncwarp();
 
-    const uint32_t kbase = my_smem_u32 + (i % kDecStages) * STAGE_BYTES;
+    const uint32_t kbase = my_smem_u32 + (i % STAGES) * STAGE_BYTES;
     const uint32_t vbase = kbase + TILE_BYTES;
 
     // scores of 16 rows x 16 keys
@@ -783,19 +783,42 @@ static int launch_decode_balanced(const DecodeBalParams& p, int blocks, cudaStre
   return (int)launch(attn_decode_balanced_kernel<D>, dim3(blocks), dim3(kDecWarps * 32), smem_bytes, stream, p);
 }
 
-template <int D>
-static int launch_decode(const DecodeParams& p, cudaStream_t stream) {
-  constexpr int smem_bytes = kDecWarps * kDecStages * 2 * kDecTile * D * 2;
+template <int D, int STAGES>
+static int launch_decode_stages(const DecodeParams& p, cudaStream_t stream) {
+  constexpr int smem_bytes = kDecWarps * STAGES * 2 * kDecTile * D * 2;
   static_assert(kDecWarps * 16 * D * 4 + kDecWarps * 16 * 2 * 4 <= smem_bytes, "merge area too small");
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_split_kernel<D>,
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_split_kernel<D, STAGES>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   dim3 grid(p.n_splits, p.n_kv_heads, p.n_items);
-  return (int)launch(attn_decode_split_kernel<D>, grid, dim3(kDecWarps * 32), smem_bytes, stream, p);
+  return (int)launch(attn_decode_split_kernel<D, STAGES>, grid, dim3(kDecWarps * 32), smem_bytes, stream, p);
+}
+
+// Three stages per warp (96 KB at head_dim 128: two blocks to an SM) where the grid fits two
+// blocks to an SM anyway; two stages (64 KB, three blocks to an SM, by registers too) where it is
+// larger: a block more per SM is then resident and has its first tiles on the way while the
+// kernel before still runs.  Measured at Qwen3-8B sizes, context 4,096, whole decode steps: two
+// stages with up to three blocks per SM +1.2 % at batch 8 and +1.5 % at batch 16 (6 and 3 splits);
+// two stages for a grid of 256 blocks -1.1 % at batch 1 and -5 % at batch 32.
+template <int D>
+static int launch_decode(const DecodeParams& p, cudaStream_t stream) {
+  static int sm_count[64] = {0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  int sms = (dev >= 0 && dev < 64) ? sm_count[dev] : 0;
+  if (sms == 0) {
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev >= 0 && dev < 64) sm_count[dev] = sms;
+  }
+  const long long blocks = (long long)p.n_splits * p.n_kv_heads * p.n_items;
+  if (blocks > 2LL * sms) return launch_decode_stages<D, 2>(p, stream);
+  return launch_decode_stages<D, 3>(p, stream);
 }
 
 }  // namespace tk

@@ -350,16 +350,24 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
 def decode_splits(n_items: int, n_kv_heads: int, max_kv_len: int) -> int:
     """How many key splits the decode kernel gets.
 
-    Two blocks fit an SM, so 296 run at a time.  A second, partly filled wave costs as much as
-    the first (measured at Qwen3-8B head sizes: batch 8 takes 30 us with 4 splits = 256 blocks
-    and 43 us with 5), so the splits are chosen to stay within one wave.  A block keeps at least
-    eight 16-key tiles, and a multiple of four, so that each of its four warps has the same
-    number (one sequence of 4,096 keys: 9.6 us with 16 splits, 10.1 with 18, 8.8 with 32)."""
-    slots = 296
+    Two blocks of three stages fit an SM, or three blocks of two stages (the kernel takes two
+    stages when its grid is larger than two blocks per SM), so up to 444 run at a time.  A second,
+    partly filled wave costs as much as the first (measured at Qwen3-8B head sizes with two
+    blocks to an SM: batch 8 takes 30 us with 4 splits = 256 blocks and 43 us with 5), so the
+    splits are chosen to stay within one wave.  A block keeps at least eight 16-key tiles, and a
+    multiple of four, so that each of its four warps has the same number (one sequence of 4,096
+    keys: 9.6 us with 16 splits, 10.1 with 18, 8.8 with 32).  Where three blocks per SM do not
+    give more blocks than two per SM hold, the splits are those of two per SM."""
     tiles = max(1, -(-max_kv_len // 16))
-    most = max(1, min(slots // max(1, n_items * n_kv_heads), 128))
-    per_split = max(8, -(-(-(-tiles // most)) // 4) * 4)
-    return max(1, min(-(-tiles // per_split), most))
+    pairs = max(1, n_items * n_kv_heads)
+
+    def splits_for(slots: int) -> int:
+        most = max(1, min(slots // pairs, 128))
+        per_split = max(8, -(-(-(-tiles // most)) // 4) * 4)
+        return max(1, min(-(-tiles // per_split), most))
+
+    wide = splits_for(444)
+    return wide if pairs * wide > 296 else splits_for(296)
 
 
 def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
