@@ -353,6 +353,34 @@ def test_sample_draws_match_the_plain_sampler(vocab):
     assert miss == 0
 
 
+@pytest.mark.parametrize("rows,vocab", [(1, 151936), (5, 151936), (20, 151936), (3, 40001), (12, 33000), (70, 20000)])
+def test_sample_rows_shared_by_several_blocks(rows, vocab):
+    """A row is shared by a cluster of 8, 4 or 2 blocks where the batch leaves SMs free (or by one block): the
+    slices' maxima, histograms and sums meet in one block, and the token is the plain sampler's, whichever
+    slice it lies in; greedy rows take the first maximum also when its like lies in another slice."""
+    gen = torch.Generator().manual_seed(rows * 1000 + vocab)
+    logits = torch.randn(rows, vocab, generator=gen) * 3
+    temps = [[0.7, 1.0, 0.0, 1.4][i % 4] for i in range(rows)]
+    top_ks = [[0, 40, 0, 0, 3][i % 5] for i in range(rows)]
+    top_ps = [[1.0, 0.95, 1.0, 0.6, 1.0, 0.9][i % 6] for i in range(rows)]
+    seeds = [77 + 13 * i for i in range(rows)]
+    counters = [5 * i + 1 for i in range(rows)]
+    for i in range(rows):
+        if temps[i] == 0.0:          # two equal maxima far apart: the first one counts
+            logits[i, vocab // 7] = 40.0
+            logits[i, vocab - 3] = 40.0
+    got = sample_rows(logits, temps, top_ks, top_ps, seeds, counters)
+    for i in range(rows):
+        if temps[i] == 0.0:
+            assert got[i] == vocab // 7
+            continue
+        want = plain.sample_token(logits[i], temps[i], top_ks[i], top_ps[i], seeds[i], counters[i])
+        assert got[i] == want, (i, got[i], want)
+    # tokens drawn from all over the row: every slice gets to draw
+    spread = sample_rows(logits[:1].repeat(64, 1) * 0.05, [1.0] * 64, [0] * 64, [1.0] * 64, list(range(64)), [0] * 64)
+    assert len({t * 8 // vocab for t in spread}) >= 6
+
+
 def test_sample_support_sets_and_distribution():
     """top-k and top-p keep the right sets; draws follow the probabilities."""
     vocab = 64

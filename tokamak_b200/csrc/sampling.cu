@@ -74,7 +74,70 @@ __device__ __forceinline__ unsigned long long warp_incl_scan_u64(unsigned long l
   return v;
 }
 
-__global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleParams p) {
+__device__ __forceinline__ unsigned long long warp_sum_u64(unsigned long long v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// All 32 lanes of a warp add to a histogram in shared memory together: `valid` lanes bring a bin
+// and a weight.  Logits crowd into a few bins of the top byte, and a thousand threads adding to
+// the same word one by one took 0.5 ms per level (2 ms for a top-p threshold at a vocabulary of
+// 151,936); so the lanes that share the first lane's bin are added up in the warp and go in as
+// one, up to four bins in turn, and only what is left after that adds for itself.
+__device__ __forceinline__ void hist_add_mass(unsigned long long* hist, int lane, bool valid, unsigned int bin,
+                                              unsigned long long weight) {
+  unsigned int todo = __ballot_sync(0xffffffffu, valid);
+  // (a handful of lanes, as in the deeper levels of the descent, add for themselves at once)
+  for (int round = 0; round < 4 && __popc(todo) >= 6; ++round) {       // uniform over the warp
+    const int leader = __ffs(todo) - 1;
+    const unsigned int lb = __shfl_sync(0xffffffffu, bin, leader);
+    const bool mine = valid && bin == lb;
+    const unsigned int same = __ballot_sync(0xffffffffu, mine);
+    const unsigned long long sum = warp_sum_u64(mine ? weight : 0ull);
+    if (lane == leader) atomicAdd(&hist[lb], sum);
+    todo &= ~same;
+  }
+  if (valid && ((todo >> lane) & 1u)) atomicAdd(&hist[bin], weight);
+}
+__device__ __forceinline__ void hist_add_count(unsigned int* hist, int lane, bool valid, unsigned int bin) {
+  unsigned int todo = __ballot_sync(0xffffffffu, valid);
+  for (int round = 0; round < 4 && __popc(todo) >= 6; ++round) {
+    const int leader = __ffs(todo) - 1;
+    const unsigned int lb = __shfl_sync(0xffffffffu, bin, leader);
+    const unsigned int same = __ballot_sync(0xffffffffu, valid && bin == lb);
+    if (lane == leader) atomicAdd(&hist[lb], (unsigned int)__popc(same));
+    todo &= ~same;
+  }
+  if (valid && ((todo >> lane) & 1u)) atomicAdd(&hist[bin], 1u);
+}
+
+constexpr int kSampleCluster = 8;     // at most this many blocks share a row: a cluster, each with a slice of the vocabulary
+
+__device__ __forceinline__ unsigned int ld_cluster_u32(const void* local, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+  unsigned int v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];\n" : "=r"(v) : "r"(remote) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long ld_cluster_u64(const void* local, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+  unsigned long long v;
+  asm volatile("ld.shared::cluster.u64 %0, [%1];\n" : "=l"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+// One cluster of gridDim.x blocks (1, 2, 4 or 8: as many as keep all rows' blocks on the GPU at once) per
+// row (blockIdx.y = row): every
+// block works on its slice of the vocabulary, the blocks' histograms and sums meet in block 0 of the
+// cluster over distributed shared memory, and what block 0 decides is read back the same way.  One
+// block alone needed 15 us for every pass over a row of 151,936 logits, and a top-p threshold takes
+// nine passes.  All blocks of a cluster take the same branches (they depend on the row only), so
+// they meet at the same cluster barriers; the last barrier keeps every block's shared memory alive
+// until nobody reads it any more.
+__global__ void __launch_bounds__(kSampleThreads, 1) sample_kernel(SampleParams p) {
   pdl_trigger();
   if (threadIdx.x == 0) tl_mark(3, 0);
   pdl_wait();
@@ -84,11 +147,14 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleParams p) 
   __shared__ unsigned int s_count[256];
   __shared__ unsigned long long s_mass[256];
   __shared__ unsigned long long s_warp_tot[32];
+  __shared__ unsigned long long s_cta_tot;
   __shared__ unsigned int s_sel_key;
   __shared__ unsigned long long s_sel_rem;
   __shared__ int s_result;
 
-  const int row = blockIdx.x;
+  const int row = blockIdx.y;
+  const uint32_t rank = cluster_ctarank();
+  const int n_blocks = (int)gridDim.x;           // of this row's cluster
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
@@ -98,50 +164,53 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleParams p) 
   if (p.records != nullptr) {
     const int slot = p.row_slot[row];
     if (slot < 0 || slot >= p.max_slots) {
-      if (tid == 0) { set_error(p.err, kErrRequest, row, slot, p.max_slots); p.out_tokens[row] = 0; }
-      return;
+      if (tid == 0 && rank == 0) { set_error(p.err, kErrRequest, row, slot, p.max_slots); p.out_tokens[row] = 0; }
+      return;       // every block of the cluster, before any of them reads another's shared memory
     }
     rec = p.records + (size_t)slot * kSlotWords;
   }
+  // everything that the record says is read now: the block that draws the token writes the record at the end
   const float T = rec ? __int_as_float(rec[4]) : p.temperature[row];
+  const int k = rec ? rec[5] : p.top_k[row];
+  const float top_p = rec ? __int_as_float(rec[6]) : p.top_p[row];
+  const unsigned long long seed =
+      rec ? ((unsigned long long)(unsigned int)rec[3] << 32) | (unsigned int)rec[2] : p.seed[row];
+  const unsigned int counter = rec ? (unsigned int)rec[1] : p.counter[row];
+
+  // this block's slice of the row: a multiple of 128 tokens, so that 16-byte loads stay aligned
+  const int slice = ((V + n_blocks * 128 - 1) / (n_blocks * 128)) * 128;
+  const int s_begin = min(V, (int)rank * slice);
+  const int s_end = min(V, s_begin + slice);
+  const int n_slice = s_end - s_begin;
+  const float* ls = lg + s_begin;
+  const bool vec = (reinterpret_cast<uintptr_t>(lg) & 15u) == 0;
+  const int V4 = vec ? (n_slice >> 2) : 0;       // 16-byte loads of the slice
+  // Every pass below walks the slice warp by warp with all 32 lanes in step (a lane beyond the end
+  // brings nothing), 16 bytes a lane where the row starts on a 16-byte boundary.
+  auto for_each = [&](auto&& body) {       // body(valid, index in the row, logit), called by all lanes of a warp together
+    const float4* ls4 = reinterpret_cast<const float4*>(ls);
+    for (int base = warp * 32; base < V4; base += kSampleThreads) {
+      const int i4 = base + lane;
+      const bool ok = i4 < V4;
+      const float4 v = ok ? ls4[i4] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      body(ok, s_begin + 4 * i4, v.x);
+      body(ok, s_begin + 4 * i4 + 1, v.y);
+      body(ok, s_begin + 4 * i4 + 2, v.z);
+      body(ok, s_begin + 4 * i4 + 3, v.w);
+    }
+    for (int base = V4 * 4 + warp * 32; base < n_slice; base += kSampleThreads) {
+      const int i = base + lane;
+      const bool ok = i < n_slice;
+      body(ok, s_begin + i, ok ? ls[i] : 0.0f);
+    }
+  };
 
   // ---- pass 1: maximum and its lowest index ------------------------------------------
   float best = -INFINITY;
   int best_i = 0x7fffffff;
-  // (16-byte loads, four of them in flight per thread, where the row starts on a 16-byte boundary:
-  // one block reads the whole row, and with 4-byte loads one after the other a row of 151,936
-  // logits took 14 us)
-  const bool vec = (reinterpret_cast<uintptr_t>(lg) & 15u) == 0;
-  const int V4 = vec ? (V >> 2) : 0;
-  {
-    const float4* lg4 = reinterpret_cast<const float4*>(lg);
-    int i = tid;
-    for (; i + 3 * kSampleThreads < V4; i += 4 * kSampleThreads) {
-      float4 v[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) v[u] = lg4[i + u * kSampleThreads];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int at = (i + u * kSampleThreads) * 4;     // ascending within the thread: the first maximum is kept
-        if (v[u].x > best) { best = v[u].x; best_i = at; }
-        if (v[u].y > best) { best = v[u].y; best_i = at + 1; }
-        if (v[u].z > best) { best = v[u].z; best_i = at + 2; }
-        if (v[u].w > best) { best = v[u].w; best_i = at + 3; }
-      }
-    }
-    for (; i < V4; i += kSampleThreads) {
-      const float4 v = lg4[i];
-      const int at = i * 4;
-      if (v.x > best) { best = v.x; best_i = at; }
-      if (v.y > best) { best = v.y; best_i = at + 1; }
-      if (v.z > best) { best = v.z; best_i = at + 2; }
-      if (v.w > best) { best = v.w; best_i = at + 3; }
-    }
-  }
-  for (int i = V4 * 4 + tid; i < V; i += kSampleThreads) {
-    const float v = lg[i];
-    if (v > best) { best = v; best_i = i; }   // ascending i: the first maximum is kept
-  }
+  for_each([&](bool ok, int i, float v) {
+    if (ok && v > best) { best = v; best_i = i; }       // ascending i within a thread: the first maximum is kept
+  });
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, best, o);
@@ -161,22 +230,29 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleParams p) 
     }
     if (lane == 0) { s_val[0] = best; s_idx[0] = best_i; }
   }
-  __syncthreads();
-  const float max_logit = s_val[0];
+  cluster_sync_all();                  // every block's maximum stands in its s_val[0], s_idx[0]
+  best = -INFINITY;
+  best_i = 0x7fffffff;
+  for (uint32_t rk = 0; rk < (uint32_t)n_blocks; ++rk) {
+    const float ov = __uint_as_float(ld_cluster_u32(&s_val[0], rk));
+    const int oi = (int)ld_cluster_u32(&s_idx[0], rk);
+    if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+  }
+  const float max_logit = best;
+  const int arg_max = best_i;
   if (T == 0.0f) {
-    if (tid == 0) {
-      p.out_tokens[row] = s_idx[0];
-      if (rec) { rec[7] = s_idx[0]; rec[1] += 1; }
+    if (tid == 0 && rank == 0) {
+      p.out_tokens[row] = arg_max;
+      if (rec) { rec[7] = arg_max; rec[1] += 1; }
       tl_mark(3, 4);
     }
+    cluster_sync_all();                // nobody leaves while its maximum may still be read
     return;
   }
   const float zmax = max_logit / T;
 
   // ---- thresholds: radix descent over the order-preserving key of z = logit / T -------
   unsigned int thr_key = 0u;   // keep keys >= thr_key
-  const int k = rec ? rec[5] : p.top_k[row];
-  const float top_p = rec ? __int_as_float(rec[6]) : p.top_p[row];
   const bool use_k = (k > 0 && k < V);
   const bool use_p = (top_p < 1.0f);
 
@@ -190,122 +266,186 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleParams p) 
       const int shift = 24 - 8 * level;
       for (int b = tid; b < 256; b += kSampleThreads) { s_count[b] = 0u; s_mass[b] = 0ull; }
       __syncthreads();
-      for (int i = tid; i < V; i += kSampleThreads) {
-        const float z = lg[i] / T;
-        const unsigned int key = float_key(z);
-        if (key < thr_key || (key & prefix_mask) != prefix) continue;
-        const unsigned int b = (key >> shift) & 0xffu;
-        if (phase == 0) {
-          atomicAdd(&s_count[b], 1u);
-        } else {
-          const unsigned long long fx = __float2ull_rd(expf(z - zmax) * kMassScale);
-          atomicAdd(&s_mass[b], fx);
+      if (phase == 0) {
+        for_each([&](bool ok, int, float logit) {
+          const unsigned int key = float_key(logit / T);
+          const bool in = ok && key >= thr_key && (key & prefix_mask) == prefix;
+          if (level == 0) hist_add_count(s_count, lane, in, (key >> shift) & 0xffu);
+          else if (in) atomicAdd(&s_count[(key >> shift) & 0xffu], 1u);
+        });
+      } else {
+        for_each([&](bool ok, int, float logit) {
+          const float z = logit / T;
+          const unsigned int key = float_key(z);
+          const bool in = ok && key >= thr_key && (key & prefix_mask) == prefix;
+          const unsigned long long fx = in ? __float2ull_rd(expf(z - zmax) * kMassScale) : 0ull;
+          // (below the top byte the bins are many and the lanes in them few: they add for themselves)
+          if (level == 0) hist_add_mass(s_mass, lane, in, (key >> shift) & 0xffu, fx);
+          else if (in) atomicAdd(&s_mass[(key >> shift) & 0xffu], fx);
+        });
+      }
+      cluster_sync_all();                // every block's histogram of its slice is complete
+      if (rank == 0) {
+        // block 0 adds the histograms up, bin by bin (a thread a bin), and decides
+        unsigned int cnt = 0u;
+        unsigned long long mass = 0ull;
+        if (tid < 256) {
+          for (uint32_t rk = 0; rk < (uint32_t)n_blocks; ++rk) {
+            if (phase == 0) cnt += ld_cluster_u32(&s_count[tid], rk);
+            else mass += ld_cluster_u64(&s_mass[tid], rk);
+          }
+          s_count[tid] = cnt;
+          s_mass[tid] = mass;
+        }
+        __syncthreads();
+        if (warp == 0) {
+          // from the highest bin down: the first bin with anything in it whose count (mass), added to
+          // what lies above it, reaches what remains.  Lane l holds the bins 255 - 8 l .. 248 - 8 l.
+          unsigned long long w[8], mine = 0ull;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int b = 255 - (8 * lane + j);
+            w[j] = (phase == 0) ? (unsigned long long)s_count[b] : s_mass[b];
+            mine += w[j];
+          }
+          const unsigned long long all = warp_sum_u64(mine);
+          if (phase == 1 && level == 0) {
+            unsigned long long target = (unsigned long long)((double)top_p * (double)all);
+            if (target > all) target = all;
+            if (target == 0ull) target = 1ull;
+            remaining = target;
+          }
+          unsigned long long cum = warp_incl_scan_u64(mine, lane) - mine;      // above this lane's bins
+          int found = -1;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (found < 0) {
+              if (w[j] > 0ull && cum + w[j] >= remaining) found = 255 - (8 * lane + j);
+              else cum += w[j];
+            }
+          }
+          const unsigned int hits = __ballot_sync(0xffffffffu, found >= 0);
+          const int src = hits != 0u ? __ffs(hits) - 1 : 31;
+          const int chosen = hits != 0u ? __shfl_sync(0xffffffffu, found, src) : 0;
+          const unsigned long long above = __shfl_sync(0xffffffffu, cum, src);    // no hit: lane 31 has added all up
+          if (lane == 0) {
+            s_sel_key = (unsigned int)chosen;
+            s_sel_rem = remaining - above;
+          }
         }
       }
-      __syncthreads();
-      if (tid == 0) {
-        if (phase == 1 && level == 0) {
-          unsigned long long total = 0ull;
-          for (int b = 0; b < 256; ++b) total += s_mass[b];
-          unsigned long long target = (unsigned long long)((double)top_p * (double)total);
-          if (target > total) target = total;
-          if (target == 0ull) target = 1ull;
-          remaining = target;
-        }
-        unsigned long long cum = 0ull;
-        int chosen = 0;
-        for (int b = 255; b >= 0; --b) {
-          const unsigned long long w = (phase == 0) ? (unsigned long long)s_count[b] : s_mass[b];
-          if (cum + w >= remaining && w > 0ull) { chosen = b; break; }
-          cum += w;
-          if (b == 0) chosen = 0;
-        }
-        s_sel_key = (unsigned int)chosen;
-        s_sel_rem = remaining - cum;
-      }
-      __syncthreads();
-      prefix |= s_sel_key << shift;
+      cluster_sync_all();                // block 0 has decided; nobody clears a histogram before this
+      prefix |= ld_cluster_u32(&s_sel_key, 0u) << shift;
       prefix_mask |= 0xffu << shift;
-      remaining = s_sel_rem;
-      __syncthreads();
+      remaining = ld_cluster_u64(&s_sel_rem, 0u);
     }
     if (prefix > thr_key) thr_key = prefix;
   }
 
-  // ---- total kept mass ------------------------------------------------------------------
-  unsigned long long local = 0ull;
-  for (int i = tid; i < V; i += kSampleThreads) {
-    const float z = lg[i] / T;
-    if (float_key(z) >= thr_key) local += __float2ull_rd(expf(z - zmax) * kMassScale);
-  }
-  {
-    unsigned long long w = local;
+  // ---- kept mass: every warp adds up one contiguous range of the block's slice -------------
+  // (ranges of a multiple of 128 tokens, so that a lane's four tokens stay one 16-byte load)
+  const int range = ((slice + 32 * 128 - 1) / (32 * 128)) * 128;
+  const int r_begin = min(s_end, s_begin + warp * range);
+  const int r_end = min(s_end, r_begin + range);
+  auto mass_of = [&](float logit) -> unsigned long long {
+    const float z = logit / T;
+    return float_key(z) >= thr_key ? __float2ull_rd(expf(z - zmax) * kMassScale) : 0ull;
+  };
+  auto lane_masses = [&](int at, unsigned long long (&m)[4]) {      // tokens at .. at + 3 of this lane
+    if (vec && at + 3 < r_end) {
+      const float4 v = *reinterpret_cast<const float4*>(lg + at);
+      m[0] = mass_of(v.x); m[1] = mass_of(v.y); m[2] = mass_of(v.z); m[3] = mass_of(v.w);
+    } else {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) w += __shfl_xor_sync(0xffffffffu, w, o);
+      for (int j = 0; j < 4; ++j) m[j] = (at + j < r_end) ? mass_of(lg[at + j]) : 0ull;
+    }
+  };
+  {
+    unsigned long long local = 0ull;
+    for (int at = r_begin + 4 * lane; at < r_end; at += 128) {
+      unsigned long long m[4];
+      lane_masses(at, m);
+      local += m[0] + m[1] + m[2] + m[3];
+    }
+    local = warp_sum_u64(local);
+    if (lane == 0) s_warp_tot[warp] = local;
     __syncthreads();
-    if (lane == 0) s_warp_tot[warp] = w;
-    __syncthreads();
+    if (tid == 0) {
+      unsigned long long sum = 0ull;
+      for (int w = 0; w < kSampleThreads / 32; ++w) sum += s_warp_tot[w];
+      s_cta_tot = sum;
+    }
   }
-  unsigned long long total = 0ull;
-  for (int w = 0; w < kSampleThreads / 32; ++w) total += s_warp_tot[w];
+  cluster_sync_all();                    // every block's sum stands in its s_cta_tot
+  unsigned long long total = 0ull, before = 0ull;       // of the row; of the slices before this block's
+  for (uint32_t rk = 0; rk < (uint32_t)n_blocks; ++rk) {
+    const unsigned long long t = ld_cluster_u64(&s_cta_tot, rk);
+    if (rk < rank) before += t;
+    total += t;
+  }
+  const unsigned long long mine_total = ld_cluster_u64(&s_cta_tot, rank);
 
   // ---- the draw: first index whose inclusive prefix exceeds u * total -------------------
   unsigned int rnd[4];
-  const unsigned long long seed =
-      rec ? ((unsigned long long)(unsigned int)rec[3] << 32) | (unsigned int)rec[2] : p.seed[row];
-  const unsigned int counter = rec ? (unsigned int)rec[1] : p.counter[row];
   philox4x32_10(counter, 0u, 0u, 0u, (unsigned int)seed, (unsigned int)(seed >> 32), rnd);
   // target = floor(rnd / 2^32 * total) < total
   const unsigned long long target = __umul64hi(total, (unsigned long long)rnd[0] << 32);
-
-  if (tid == 0) s_result = best_i >= 0 ? s_idx[0] : 0;   // fallback: the most likely token
-  __syncthreads();
-  constexpr int kItems = 4;
-  unsigned long long base = 0ull;
-  bool done = false;
-  for (int start = 0; start < V && !done; start += kSampleThreads * kItems) {
-    unsigned long long item[kItems];
-    unsigned long long mine = 0ull;
-#pragma unroll
-    for (int j = 0; j < kItems; ++j) {
-      const int i = start + tid * kItems + j;
-      unsigned long long fx = 0ull;
-      if (i < V) {
-        const float z = lg[i] / T;
-        if (float_key(z) >= thr_key) fx = __float2ull_rd(expf(z - zmax) * kMassScale);
-      }
-      item[j] = fx;
-      mine += fx;
-    }
-    const unsigned long long incl = warp_incl_scan_u64(mine, lane);
+  // the block whose slice holds the target draws: its warp whose range holds it walks the range
+  // again, 128 tokens at a time.  (Without any mass, which cannot be, block 0 gives the most likely token.)
+  const bool owner = total > 0ull ? (before <= target && target < before + mine_total) : rank == 0u;
+  if (owner) {
+    if (tid == 0) s_result = arg_max;
     __syncthreads();
-    if (lane == 31) s_warp_tot[warp] = incl;
-    __syncthreads();
-    unsigned long long warp_base = 0ull, chunk_total = 0ull;
-    for (int w = 0; w < kSampleThreads / 32; ++w) {
-      const unsigned long long tw = s_warp_tot[w];
-      if (w < warp) warp_base += tw;
-      chunk_total += tw;
-    }
-    if (base + chunk_total > target) {
-      unsigned long long run = base + warp_base + incl - mine;   // exclusive prefix of this thread
-      if (run <= target && target < run + mine) {
+    for (int w = 0; w < warp; ++w) before += s_warp_tot[w];
+    if (before <= target && target < before + s_warp_tot[warp]) {
+      unsigned long long run = before;
+      for (int at = r_begin + 4 * lane; at - 4 * lane < r_end; at += 128) {     // all lanes in step
+        unsigned long long m[4];
+        lane_masses(at, m);
+        const unsigned long long mine = m[0] + m[1] + m[2] + m[3];
+        const unsigned long long incl = warp_incl_scan_u64(mine, lane);
+        const unsigned long long chunk = __shfl_sync(0xffffffffu, incl, 31);
+        if (run + chunk > target) {
+          unsigned long long at_me = run + incl - mine;          // mass before this lane's tokens
+          if (at_me <= target && target < at_me + mine) {
 #pragma unroll
-        for (int j = 0; j < kItems; ++j) {
-          if (target < run + item[j]) { s_result = start + tid * kItems + j; break; }
-          run += item[j];
+            for (int j = 0; j < 4; ++j) {
+              if (target < at_me + m[j]) { s_result = at + j; break; }
+              at_me += m[j];
+            }
+          }
+          break;
         }
+        run += chunk;
       }
-      done = true;
     }
-    base += chunk_total;
+    __syncthreads();
+    if (tid == 0) {
+      p.out_tokens[row] = s_result;
+      if (rec) { rec[7] = s_result; rec[1] += 1; }
+      tl_mark(3, 4);
+    }
   }
-  __syncthreads();
-  if (tid == 0) {
-    p.out_tokens[row] = s_result;
-    if (rec) { rec[7] = s_result; rec[1] += 1; }
-    tl_mark(3, 4);
+  cluster_sync_all();                    // nobody leaves while its sums may still be read
+}
+
+// As many blocks per row (a power of two, at most kSampleCluster) as keep all rows' blocks on the GPU at
+// once (a block of 1,024 threads has an SM to itself); few blocks for a short row.
+static int launch_sample(const SampleParams& p, int n_rows, cudaStream_t stream) {
+  if (n_rows > 65535) return (int)cudaErrorInvalidValue;
+  static int sm_count[64] = {0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  int sms = (dev >= 0 && dev < 64) ? sm_count[dev] : 0;
+  if (sms == 0) {
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev >= 0 && dev < 64) sm_count[dev] = sms;
   }
+  int blocks = kSampleCluster;
+  while (blocks > 1 && (n_rows * blocks > sms || p.vocab < blocks * 4096)) blocks >>= 1;
+  return (int)launch_cluster(sample_kernel, dim3(blocks, n_rows), dim3(kSampleThreads), 0, stream, dim3(blocks, 1, 1), p);
 }
 
 }  // namespace tk
@@ -321,7 +461,7 @@ TK_API int tk_sample(const float* logits, long long ld, const float* temperature
   p.logits = logits; p.temperature = temperature; p.top_k = top_k; p.top_p = top_p;
   p.seed = seed; p.counter = counter; p.out_tokens = out_tokens; p.vocab = vocab; p.ld = ld;
   p.records = nullptr; p.row_slot = nullptr; p.max_slots = 0; p.err = nullptr;
-  return (int)tk::launch(tk::sample_kernel, dim3(n_rows), dim3(tk::kSampleThreads), 0, stream, p);
+  return tk::launch_sample(p, n_rows, stream);
 }
 
 // The same with every row's parameters in the state record of its request's slot; the sampled
@@ -333,7 +473,7 @@ TK_API int tk_sample_slots(const float* logits, long long ld, int* records, cons
   tk::SampleParams p = {};
   p.logits = logits; p.out_tokens = out_tokens; p.vocab = vocab; p.ld = ld;
   p.records = records; p.row_slot = row_slot; p.max_slots = max_slots; p.err = err;
-  return (int)tk::launch(tk::sample_kernel, dim3(n_rows), dim3(tk::kSampleThreads), 0, stream, p);
+  return tk::launch_sample(p, n_rows, stream);
 }
 
 // Host copy of the generator, for callers that need the same uniform without a GPU.
