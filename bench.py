@@ -161,7 +161,7 @@ def fill_context(core, req_ids, length: int, vocab: int, seed: int) -> None:
     core.step.check_errors()
 
 
-def time_decode(core, batch: int, steps: int, warmup: int, ctx_end: int, vocab: int):
+def time_decode(core, batch: int, steps: int, warmup: int, ctx_end: int, vocab: int, sampling=None):
     """Device time of ``steps`` decode steps of ``batch`` requests whose context ends at ``ctx_end``.
 
     The steps run as generation runs them: each request's token, position and sampling state
@@ -177,7 +177,9 @@ def time_decode(core, batch: int, steps: int, warmup: int, ctx_end: int, vocab: 
     req_ids = [f"b{batch}_{i}" for i in range(batch)]
     start_len = ctx_end - (steps + warmup + 1)
     for rid in req_ids:
-        step.admit(rid, SamplingRow())                 # greedy
+        # greedy, or (temperature, top_k, top_p) with a seed per request
+        step.admit(rid, SamplingRow() if sampling is None else
+                   SamplingRow(temperature=sampling[0], top_k=int(sampling[1]), top_p=sampling[2], seed=1 + len(rid)))
     fill_context(core, req_ids, start_len - 1, vocab, seed=batch)
     last = [1 + i for i in range(batch)]
     # the last prompt token of every request, sampled: from here on the records carry the requests
@@ -215,7 +217,12 @@ def time_decode(core, batch: int, steps: int, warmup: int, ctx_end: int, vocab: 
     # the check: rewind every request to where the records took over and decode again, plainly
     replays = step.graph_replays
     for rid in req_ids:
-        step.restart(rid)
+        if sampling is None:
+            step.restart(rid)
+        else:           # a restarted request keeps its generator's count, as after a preemption: begin anew instead
+            step.free(rid)
+            step.admit(rid, SamplingRow(temperature=sampling[0], top_k=int(sampling[1]), top_p=sampling[2],
+                                        seed=1 + len(rid)))
     fill_context(core, req_ids, start_len - 1, vocab, seed=batch)
     graphs, step.use_graphs = step.use_graphs, False
     toks = step.run_and_sample([StepEntry(r, [t], [0]) for r, t in zip(req_ids, last)])
@@ -800,6 +807,10 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="leave out the further batch sizes")
     ap.add_argument("--points", type=lambda v: [int(x) for x in v.split(",") if x], default=[1, 64],
                     help="further decode batch sizes to time, comma-separated (default 1,64)")
+    ap.add_argument("--sampling", default=None,
+                    type=lambda v: tuple(float(x) for x in v.split(",")) if v else None,
+                    help="temperature,top_k,top_p of the timed decode steps of the main batch (default: greedy), "
+                         "e.g. 0.8,0,0.95; the points and the end-to-end run stay greedy")
     ap.add_argument("--kernel", default=None, help="time one kernel alone instead: attention_decode, attention_decode_split, "
                     "attention_prefill (tcgen05), attention_prefill_mma, rope_kv, rmsnorm, gemm_tc_decode, gemm_decode (library), "
                     "gemm_pair_swiglu, gemm_prefill_library (--ctx tokens), products_chain / products_separate (the four products "
@@ -879,7 +890,7 @@ def main() -> int:
 
     sampler = ClockSampler(torch.cuda.current_device())
     sampler.start()
-    main_run = time_decode(core, args.batch, steps, warmup, ctx, vocab)
+    main_run = time_decode(core, args.batch, steps, warmup, ctx, vocab, args.sampling)
     prefill_ms = time_prefill(core, vocab, pf_tokens)
     points = {}
     checked = main_run["checked"]
