@@ -80,38 +80,6 @@ __device__ __forceinline__ unsigned long long warp_sum_u64(unsigned long long v)
   return v;
 }
 
-// All 32 lanes of a warp add to a histogram in shared memory together: `valid` lanes bring a bin
-// and a weight.  Logits crowd into a few bins of the top byte, and a thousand threads adding to
-// the same word one by one took 0.5 ms per level (2 ms for a top-p threshold at a vocabulary of
-// 151,936); so the lanes that share the first lane's bin are added up in the warp and go in as
-// one, up to four bins in turn, and only what is left after that adds for itself.
-__device__ __forceinline__ void hist_add_mass(unsigned long long* hist, int lane, bool valid, unsigned int bin,
-                                              unsigned long long weight) {
-  unsigned int todo = __ballot_sync(0xffffffffu, valid);
-  // (a handful of lanes, as in the deeper levels of the descent, add for themselves at once)
-  for (int round = 0; round < 4 && __popc(todo) >= 6; ++round) {       // uniform over the warp
-    const int leader = __ffs(todo) - 1;
-    const unsigned int lb = __shfl_sync(0xffffffffu, bin, leader);
-    const bool mine = valid && bin == lb;
-    const unsigned int same = __ballot_sync(0xffffffffu, mine);
-    const unsigned long long sum = warp_sum_u64(mine ? weight : 0ull);
-    if (lane == leader) atomicAdd(&hist[lb], sum);
-    todo &= ~same;
-  }
-  if (valid && ((todo >> lane) & 1u)) atomicAdd(&hist[bin], weight);
-}
-__device__ __forceinline__ void hist_add_count(unsigned int* hist, int lane, bool valid, unsigned int bin) {
-  unsigned int todo = __ballot_sync(0xffffffffu, valid);
-  for (int round = 0; round < 4 && __popc(todo) >= 6; ++round) {
-    const int leader = __ffs(todo) - 1;
-    const unsigned int lb = __shfl_sync(0xffffffffu, bin, leader);
-    const unsigned int same = __ballot_sync(0xffffffffu, valid && bin == lb);
-    if (lane == leader) atomicAdd(&hist[lb], (unsigned int)__popc(same));
-    todo &= ~same;
-  }
-  if (valid && ((todo >> lane) & 1u)) atomicAdd(&hist[bin], 1u);
-}
-
 constexpr int kSampleCluster = 8;     // at most this many blocks share a row: a cluster, each with a slice of the vocabulary
 
 __device__ __forceinline__ unsigned int ld_cluster_u32(const void* local, uint32_t rank) {
@@ -151,6 +119,12 @@ __global__ void __launch_bounds__(kSampleThreads, 1) sample_kernel(SampleParams 
   __shared__ unsigned int s_sel_key;
   __shared__ unsigned long long s_sel_rem;
   __shared__ int s_result;
+  // Histograms of the first level, one per group of four warps: logits crowd into a few bins of the
+  // top byte, and a thousand threads adding 64-bit masses to the same few words one after the other
+  // took 0.5 ms per level (2 ms for a top-p threshold at a vocabulary of 151,936).  A mass (at most
+  // 2^40) goes in as three pieces of 14, 14 and 12 bits with the hardware's own 32-bit additions; a
+  // group adds at most vocab / 8 of them, fewer than 2^18 (the host checks the vocabulary).
+  __shared__ unsigned int s_grp[kSampleThreads / 128][256][3];
 
   const int row = blockIdx.y;
   const uint32_t rank = cluster_ctarank();
@@ -265,23 +239,51 @@ __global__ void __launch_bounds__(kSampleThreads, 1) sample_kernel(SampleParams 
     for (int level = 0; level < 4; ++level) {
       const int shift = 24 - 8 * level;
       for (int b = tid; b < 256; b += kSampleThreads) { s_count[b] = 0u; s_mass[b] = 0ull; }
+      if (level == 0) {
+        unsigned int* flat = &s_grp[0][0][0];
+        for (int i = tid; i < (kSampleThreads / 128) * 256 * 3; i += kSampleThreads) flat[i] = 0u;
+      }
       __syncthreads();
-      if (phase == 0) {
+      if (level == 0) {
+        // every token of the slice takes part, in a few bins: into the histogram of the warp's group
+        unsigned int (*mine)[3] = s_grp[warp >> 2];
+        if (phase == 0) {
+          for_each([&](bool ok, int, float logit) {
+            const unsigned int key = float_key(logit / T);
+            if (ok && key >= thr_key) atomicAdd(&mine[key >> 24][0], 1u);
+          });
+        } else {
+          for_each([&](bool ok, int, float logit) {
+            const float z = logit / T;
+            const unsigned int key = float_key(z);
+            if (ok && key >= thr_key) {
+              const unsigned long long fx = __float2ull_rd(expf(z - zmax) * kMassScale);      // <= 2^40
+              atomicAdd(&mine[key >> 24][0], (unsigned int)(fx & 0x3fffu));
+              atomicAdd(&mine[key >> 24][1], (unsigned int)((fx >> 14) & 0x3fffu));
+              atomicAdd(&mine[key >> 24][2], (unsigned int)(fx >> 28));
+            }
+          });
+        }
+        __syncthreads();
+        if (tid < 256) {
+          unsigned long long p0 = 0ull, p1 = 0ull, p2 = 0ull;
+          for (int w = 0; w < kSampleThreads / 128; ++w) { p0 += s_grp[w][tid][0]; p1 += s_grp[w][tid][1]; p2 += s_grp[w][tid][2]; }
+          s_count[tid] = (unsigned int)p0;
+          s_mass[tid] = p0 + (p1 << 14) + (p2 << 28);
+        }
+      } else if (phase == 0) {
+        // below the top byte the bins are many and the tokens in them few: they add for themselves
         for_each([&](bool ok, int, float logit) {
           const unsigned int key = float_key(logit / T);
-          const bool in = ok && key >= thr_key && (key & prefix_mask) == prefix;
-          if (level == 0) hist_add_count(s_count, lane, in, (key >> shift) & 0xffu);
-          else if (in) atomicAdd(&s_count[(key >> shift) & 0xffu], 1u);
+          if (ok && key >= thr_key && (key & prefix_mask) == prefix) atomicAdd(&s_count[(key >> shift) & 0xffu], 1u);
         });
       } else {
         for_each([&](bool ok, int, float logit) {
           const float z = logit / T;
           const unsigned int key = float_key(z);
-          const bool in = ok && key >= thr_key && (key & prefix_mask) == prefix;
-          const unsigned long long fx = in ? __float2ull_rd(expf(z - zmax) * kMassScale) : 0ull;
-          // (below the top byte the bins are many and the lanes in them few: they add for themselves)
-          if (level == 0) hist_add_mass(s_mass, lane, in, (key >> shift) & 0xffu, fx);
-          else if (in) atomicAdd(&s_mass[(key >> shift) & 0xffu], fx);
+          if (ok && key >= thr_key && (key & prefix_mask) == prefix) {
+            atomicAdd(&s_mass[(key >> shift) & 0xffu], __float2ull_rd(expf(z - zmax) * kMassScale));
+          }
         });
       }
       cluster_sync_all();                // every block's histogram of its slice is complete
@@ -432,7 +434,7 @@ __global__ void __launch_bounds__(kSampleThreads, 1) sample_kernel(SampleParams 
 // As many blocks per row (a power of two, at most kSampleCluster) as keep all rows' blocks on the GPU at
 // once (a block of 1,024 threads has an SM to itself); few blocks for a short row.
 static int launch_sample(const SampleParams& p, int n_rows, cudaStream_t stream) {
-  if (n_rows > 65535) return (int)cudaErrorInvalidValue;
+  if (n_rows > 65535 || p.vocab > (1 << 21)) return (int)cudaErrorInvalidValue;    // (the pieces of the first histograms)
   static int sm_count[64] = {0};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
