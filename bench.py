@@ -432,7 +432,8 @@ def latency_workload(sizes: str, prompt_tokens: int, new_tokens: int, iters: int
             "inter_token_ms": round(1e3 / tok_s, 3), "iters": iters, "dtype": "bf16", "data": "synthetic"}
 
 
-def kernel_case(name: str, batch: int, ctx: int, iters: int, peaks: dict, portion: int = 0, sizes: str = "8b") -> dict:
+def kernel_case(name: str, batch: int, ctx: int, iters: int, peaks: dict, portion: int = 0, sizes: str = "8b",
+                sampling=None) -> dict:
     """One kernel alone on inputs larger than L2, timed with CUDA events: achieved bytes or flops
     per second against the peak.  Also the small case that ncu captures are made on."""
     import torch
@@ -503,6 +504,19 @@ def kernel_case(name: str, batch: int, ctx: int, iters: int, peaks: dict, portio
                                   n_q_heads=hq, n_kv_heads=hkv, head_dim=d, rotary_dim=d, eps=1e-6,
                                   req_q_len=len_n, req_kv_len=len_n)
         nbytes = qkv.numel() * 2 + q_out.numel() * 2 + 2 * n * hkv * d * 2
+    elif name == "sampling":
+        # one token per row of float32 logits at the model's vocabulary; --sampling gives temperature,top_k,top_p
+        n, vocab = batch, cfg["vocab_size"]
+        t_, k_, p_ = sampling if sampling is not None else (0.8, 0, 0.95)
+        logits = torch.randn((n, vocab), device=dev, generator=gen) * 3
+        out_tok = torch.zeros(n, dtype=torch.int32, device=dev)
+        temp = torch.full((n,), float(t_), device=dev)
+        top_k = torch.full((n,), int(k_), dtype=torch.int32, device=dev)
+        top_p = torch.full((n,), float(p_), device=dev)
+        seeds = torch.arange(n, dtype=torch.int64, device=dev)
+        counters = torch.zeros(n, dtype=torch.int32, device=dev)
+        run = lambda: ops.sample(logits, temp, top_k, top_p, seeds, counters, out_tok)
+        nbytes = n * vocab * 4          # one reading of the row; a top-k or top-p threshold reads it four times more each
     elif name == "rmsnorm":
         n, h = batch, cfg["hidden_size"]
         resid = torch.randn((n, h), device=dev, generator=gen)
@@ -812,7 +826,7 @@ def main() -> int:
                     help="temperature,top_k,top_p of the timed decode steps of the main batch (default: greedy), "
                          "e.g. 0.8,0,0.95; the points and the end-to-end run stay greedy")
     ap.add_argument("--kernel", default=None, help="time one kernel alone instead: attention_decode, attention_decode_split, "
-                    "attention_prefill (tcgen05), attention_prefill_mma, rope_kv, rmsnorm, gemm_tc_decode, gemm_decode (library), "
+                    "attention_prefill (tcgen05), attention_prefill_mma, rope_kv, rmsnorm, sampling (--batch rows, --sampling T,K,P), gemm_tc_decode, gemm_decode (library), "
                     "gemm_pair_swiglu, gemm_prefill_library (--ctx tokens), products_chain / products_separate (the four products "
                     "between two attentions of a decode step, as one kernel or one by one); attention_prefill_timeline prints the time stamps of the persistent prefill attention kernel's roles; tcgen05_probe prints what issuing a tcgen05.mma costs by shape and what a softmax warp needs for a key tile; decode_timeline prints when the blocks of every "
                     "kernel of a decode step run (needs a library built with TOKAMAK_B200_NVCC_FLAGS=-DTK_TIMELINE)")
@@ -854,7 +868,8 @@ def main() -> int:
     if args.kernel == "attention_prefill_timeline":
         return prefill_attention_timeline(args.batch, args.ctx, args.portion, args.sizes)
     if args.kernel:
-        print(json.dumps(kernel_case(args.kernel, args.batch, args.ctx, steps, load_peaks(), args.portion, args.sizes)))
+        print(json.dumps(kernel_case(args.kernel, args.batch, args.ctx, steps, load_peaks(), args.portion, args.sizes,
+                                     args.sampling)))
         return 0
     if args.workload == "latency":
         print(json.dumps(latency_workload(args.sizes, 512, 128, 3, args.seed)))
