@@ -1,4 +1,4 @@
-// Token sampling over float32 logits, one thread block per row.
+// Token sampling over float32 logits, one cluster of thread blocks per row.
 //
 // Pipeline of the reference (src/tokamak/sampling/sampler.py:32-39,58-84):
 // temperature 0 -> argmax; else logits / T -> top-k (keep values >= the k-th
