@@ -47,3 +47,13 @@ def test_pair_gemm_is_for_grids_that_fill_the_gpu():
     assert ops.pair_gemm_takes(2048, 4096, 4096)
     assert not ops.pair_gemm_takes(256, 4096, 4096)               # 16 tiles: the library is faster
     assert not ops.pair_gemm_takes(2048, 4096, 4100)              # inner size no multiple of 8
+
+
+def test_sampling_refuses_sizes_its_histograms_cannot_hold():
+    import pytest
+    ops._sampling_takes(64, 151936)
+    ops._sampling_takes(ops.SAMPLING_MAX_ROWS, ops.SAMPLING_MAX_VOCAB)
+    with pytest.raises(ops.KernelError, match="sampling kernel takes"):
+        ops._sampling_takes(1, ops.SAMPLING_MAX_VOCAB + 1)
+    with pytest.raises(ops.KernelError, match="sampling kernel takes"):
+        ops._sampling_takes(ops.SAMPLING_MAX_ROWS + 1, 1000)

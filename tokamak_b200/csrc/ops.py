@@ -134,6 +134,16 @@ def decode_begin(upd: UpdateBuffers, dec_slots: torch.Tensor, n_reqs: int, max_p
                                      err.data_ptr(), _stream()), "decode_begin")
 
 
+SAMPLING_MAX_VOCAB = 1 << 21      # the pieces of the first histograms of sampling.cu hold vocab / 8 masses
+SAMPLING_MAX_ROWS = 65535
+
+
+def _sampling_takes(rows: int, vocab: int) -> None:
+    if vocab > SAMPLING_MAX_VOCAB or rows > SAMPLING_MAX_ROWS:
+        raise KernelError(f"the sampling kernel takes up to {SAMPLING_MAX_ROWS} rows of up to {SAMPLING_MAX_VOCAB} "
+                          f"logits, got {rows} x {vocab}")
+
+
 def sample_slots(logits: torch.Tensor, records: torch.Tensor, row_slot: torch.Tensor,
                  out_tokens: torch.Tensor, err: torch.Tensor) -> None:
     """One token per row of float32 logits, with the parameters, seed and counter of the slot
@@ -144,6 +154,7 @@ def sample_slots(logits: torch.Tensor, records: torch.Tensor, row_slot: torch.Te
     rows, vocab = logits.shape
     if row_slot.numel() < rows or out_tokens.numel() < rows:
         raise KernelError("a per-row sampling tensor is shorter than the batch")
+    _sampling_takes(rows, vocab)
     _check(_lib().tk_sample_slots(logits.data_ptr(), logits.stride(0), records.data_ptr(),
                                      row_slot.data_ptr(), records.shape[0], out_tokens.data_ptr(), rows, vocab,
                                      err.data_ptr(), _stream()), "sample_slots")
@@ -1027,6 +1038,7 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     for t in (temperature, top_k, top_p, seed, counter, out_tokens):
         if t.numel() < rows:
             raise KernelError("a per-row sampling tensor is shorter than the batch")
+    _sampling_takes(rows, vocab)
     _check(_lib().tk_sample(logits.data_ptr(), logits.stride(0), temperature.data_ptr(),
                                top_k.data_ptr(), top_p.data_ptr(), seed.data_ptr(), counter.data_ptr(),
                                out_tokens.data_ptr(), rows, vocab, _stream()), "sample")
